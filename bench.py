@@ -1,0 +1,365 @@
+#!/usr/bin/env python
+"""Benchmark of the grouped dual-NVFP4 GEMM hot path (one JSON line on stdout).
+
+    python bench.py [--gpus N] [--steps K] [--warmup W] [--workload c2|c3up|c3down|c4|c5] [--impl reference]
+
+A step is one call of ``m_grouped_bf16_dual_nvfp4_gemm_contiguous`` over one batch of
+seeded synthetic input.  At N = 1 the default workload is the Mixtral-8x7B-like expert
+up-projection (E=8, 512 rows per expert, N=28672, K=4096).  ``value`` is logical
+TFLOP/s (2*M*N*K / t, the figure the reference prints) with every operand resident in
+HBM; ``e2e`` is the same figure through the public call with the activations coming
+from pinned host memory and the output going back to the host inside the timed region.
+``roofline`` relates the kernel to the tensor-pipe ceiling (both NVFP4 passes count) or,
+for the decode workload, to HBM bandwidth.  ``--impl reference`` times the reference's
+CPU implementation of the same chain on the host cores, on a bounded sample.
+"""
+from __future__ import annotations
+
+import argparse
+import json
+import os
+import statistics
+import subprocess
+import sys
+import threading
+import time
+
+ROOT = os.path.dirname(os.path.abspath(__file__))
+sys.path.insert(0, ROOT)
+
+import torch  # noqa: E402
+
+WORKLOADS = {
+    # name: experts, N, K, description
+    "c2": dict(E=8, N=28672, K=4096, desc="Mixtral-8x7B-like up-projection: E=8 x 512 rows, N=28672, K=4096"),
+    "c3up": dict(E=256, N=4096, K=7168, desc="DeepSeek-V3-style prefill up: E=256, 32768 rows Zipf(1.1) padded to 128, N=4096, K=7168"),
+    "c3down": dict(E=256, N=7168, K=2048, desc="DeepSeek-V3-style prefill down: E=256, 32768 rows Zipf(1.1) padded to 128, N=7168, K=2048"),
+    "c4": dict(E=256, N=4096, K=7168, desc="decode: E=256, 64 tokens x top-8 (1-16 rows per active expert, padded to 16), N=4096, K=7168"),
+}
+
+
+def peaks() -> dict:
+    path = os.path.join(ROOT, "MEASURED_PEAKS.json")
+    if os.path.exists(path):
+        d = json.load(open(path))
+        d["source"] = "measured"
+        return d
+    return {"hbm_gbs": 6650.0, "bf16_tflops": 1590.0, "bf16_tflops_sustained": 1400.0, "source": "fallback"}
+
+
+class ClockSampler:
+    """nvidia-smi clocks / throttle reasons while the timed region runs."""
+    Q = ("clocks.sm,clocks.max.sm,power.draw,clocks_event_reasons.hw_slowdown,clocks_event_reasons.hw_thermal_slowdown,"
+         "clocks_event_reasons.sw_thermal_slowdown,clocks_event_reasons.sw_power_cap")
+
+    def __init__(self, index: int):
+        self.rows, self.proc, self.index = [], None, index
+
+    def start(self):
+        try:
+            self.proc = subprocess.Popen(["nvidia-smi", f"--query-gpu={self.Q}", "--format=csv,noheader,nounits",
+                                          "-i", str(self.index), "-lms", "50"], stdout=subprocess.PIPE, text=True)
+            threading.Thread(target=self._read, daemon=True).start()
+        except OSError:
+            self.proc = None
+
+    def _read(self):
+        for line in self.proc.stdout:
+            self.rows.append((time.time(), [x.strip() for x in line.split(",")]))
+
+    def stop(self, t0: float, t1: float) -> dict:
+        if self.proc is None:
+            return {"sm_mhz": None, "sm_max_mhz": None, "reasons": ["nvidia-smi unavailable"]}
+        time.sleep(0.12)
+        self.proc.terminate()
+        rows = [r for t, r in self.rows if t0 <= t <= t1 + 0.06] or [r for _, r in self.rows[-3:]]
+        mhz, reasons, mx = [], set(), None
+        for r in rows:
+            try:
+                mhz.append(float(r[0])); mx = float(r[1])
+            except (ValueError, IndexError):
+                continue
+            for name, v in zip(("hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap"), r[3:7]):
+                if v.lower().startswith("active"):
+                    reasons.add(name)
+        return {"sm_mhz": statistics.median(mhz) if mhz else None, "sm_max_mhz": mx, "reasons": sorted(reasons),
+                "samples": len(mhz)}
+
+
+# ----------------------------------------------------------------------------- workloads
+def routing_rows(workload: str, E: int, gen: torch.Generator):
+    """Real rows per expert and the padded group sizes the kernel sees."""
+    if workload == "c2":
+        real = [512] * E
+        return real, real, 128, False
+    if workload in ("c3up", "c3down"):
+        p = torch.arange(1, E + 1, dtype=torch.float64).pow(-1.1)
+        real = torch.multinomial(p / p.sum(), 32768, replacement=True, generator=gen).bincount(minlength=E).tolist()
+        return real, [((r + 127) // 128) * 128 for r in real], 128, False
+    if workload == "c4":
+        counts = torch.zeros(E, dtype=torch.int64)
+        for _ in range(64):                                 # 64 tokens, 8 distinct experts each
+            counts[torch.randperm(E, generator=gen)[:8]] += 1
+        real = counts.clamp(max=16).tolist()
+        return real, [((r + 15) // 16) * 16 for r in real], 16, True
+    raise ValueError(workload)
+
+
+def build_weights(E: int, N: int, K: int, dev, seed: int):
+    """Random-init BF16 weights ~N(0, 0.02), quantised expert by expert (bounds device memory)."""
+    import nvfp4_gemm
+    b = torch.empty(E * N, K // 2, dtype=torch.int8, device=dev)
+    sfb = torch.empty(E * K // 64, N, dtype=torch.int32, device=dev)
+    gw = torch.empty(E, dtype=torch.float32, device=dev)
+    g = torch.Generator(device=dev).manual_seed(seed)
+    for e in range(E):
+        w = (torch.randn(1, N, K, generator=g, device=dev) * 0.02).to(torch.bfloat16)
+        be, se, ge = nvfp4_gemm.quantize_weight_nvfp4(w)
+        b[e * N:(e + 1) * N] = be
+        sfb[e * (K // 64):(e + 1) * (K // 64)] = se
+        gw[e] = ge[0]
+    return b, sfb, gw
+
+
+def build_single_gpu_case(workload: str, dev):
+    import nvfp4_gemm
+    cfg = WORKLOADS[workload]
+    E, N, K = cfg["E"], cfg["N"], cfg["K"]
+    gen = torch.Generator().manual_seed(3)
+    real, padded, align, swap = routing_rows(workload, E, gen)
+    M = sum(padded)
+    ga = torch.Generator(device=dev).manual_seed(0)
+    a = torch.zeros(M, K, dtype=torch.bfloat16, device=dev)
+    x = torch.randn(sum(real), K, generator=ga, device=dev)
+    if workload == "c2":                                    # per-row lognormal(0, 0.5) scale
+        x = x * torch.exp(0.5 * torch.randn(sum(real), 1, generator=ga, device=dev))
+    if workload.startswith("c3"):                           # 0.1 % outlier channels x50
+        cols = torch.randperm(K, generator=torch.Generator().manual_seed(1))[:max(1, K // 1000)]
+        x[:, cols.to(dev)] *= 50.0
+    x = x.clamp(-2688.0, 2688.0).to(torch.bfloat16)
+    off_r = off_p = 0
+    for r, pz in zip(real, padded):
+        a[off_p:off_p + r] = x[off_r:off_r + r]
+        off_r += r
+        off_p += pz
+    m_indices = nvfp4_gemm.make_m_indices(padded, alignment=align).to(dev)
+    b, sfb, gw = build_weights(E, N, K, dev, seed=2)
+    kw = dict(tune_swap_ab=1, m_alignment=align) if swap else {}
+    active = sum(1 for r in real if r > 0)
+    return dict(a=a, b=b, sfb=sfb, gw=gw, m_indices=m_indices, M=M, N=N, K=K, E=E, real_rows=sum(real),
+                active_experts=active, kw=kw, swap=swap, padded=padded, real=real)
+
+
+def accuracy_sample(case, d, dev):
+    """rel-L2 / cosine of the kernel output against FP32 A_bf16 @ dequant(W)^T on the rows of one expert
+    and a 1024-column slice (torch ops are the checker here, never the product)."""
+    import nvfp4_gemm
+    E, N, K = case["E"], case["N"], case["K"]
+    e = max(range(E), key=lambda i: case["real"][i])
+    start = sum(case["padded"][:e])
+    rows = min(case["real"][e], 256)
+    ncols = min(N, 1024)
+    be = case["b"][e * N:e * N + ncols]
+    se = case["sfb"][e * (K // 64):(e + 1) * (K // 64), :ncols].contiguous()
+    wdq = nvfp4_gemm.dequantize_weight_nvfp4(be, se, case["gw"][e:e + 1], 1, ncols, K)[0]
+    ref = case["a"][start:start + rows].float() @ wdq.T
+    got = d[start:start + rows, :ncols].float()
+    rel = float((got - ref).norm() / ref.norm())
+    cos = float(torch.dot(got.flatten(), ref.flatten()) / (got.norm() * ref.norm()))
+    return rel, cos
+
+
+# ----------------------------------------------------------------------------- CPU baseline
+def cpu_reference_sample(workload: str, seconds_target: float = 12.0):
+    """The reference's CPU chain (decompose, dequantise, FP32 dot products) on a bounded sample of the
+    workload: one expert's rows x a slice of its output columns, full K.  Uses the reference's own C++
+    host twin (oracle/_ref) when it was built, else the C restatement (oracle/)."""
+    import oracle
+    cfg = WORKLOADS.get(workload, WORKLOADS["c2"])
+    K = cfg["K"]
+    g = torch.Generator().manual_seed(0)
+    use_ref = oracle.ref_twin() is not None and hasattr(oracle.ref_twin(), "ref_twin_dual_gemm_mt")
+    rows, ncols = (64, 128) if use_ref else (128, 256)
+    threads = os.cpu_count() or 1
+
+    def run(rows, ncols):
+        a = torch.randn(rows, K, generator=g).to(torch.bfloat16)
+        w = (torch.randn(1, ncols, K, generator=g) * 0.02).to(torch.bfloat16)
+        mi = torch.zeros(rows, dtype=torch.int32)
+        if use_ref:
+            q, sf, gg = oracle.ref_twin_quantize_weight(w.float())
+            t = time.perf_counter()
+            oracle.ref_twin_dual_gemm_mt(a.float(), q, sf, gg, mi, ncols, threads)
+            return time.perf_counter() - t
+        b, sfb, gw = oracle.quantize_weight(w)
+        t = time.perf_counter()
+        oracle.grouped_gemm(a, b, sfb, gw, mi, ncols, mode="dual")
+        return time.perf_counter() - t
+
+    t_probe = run(rows, ncols)
+    scale = max(1.0, seconds_target / max(t_probe, 1e-3))
+    ncols2 = min(cfg["N"], int(ncols * scale) // 64 * 64)
+    rows = min(512, max(rows, int(rows * scale * ncols / ncols2) // 8 * 8))
+    t = run(rows, ncols2)
+    flops = 2.0 * rows * ncols2 * K
+    return dict(value=flops / t / 1e12, unit="TFLOP/s", cores=threads if use_ref else oracle.num_threads(),
+                kind="reference" if use_ref else "port",
+                sample=f"{rows} rows of one expert x {ncols2} output columns x K={K} ({flops / 1e9:.1f} GFLOP, {t:.1f} s)",
+                seconds=t)
+
+
+def run_reference_arm(args):
+    rank = int(os.environ.get("RANK", "0"))
+    if rank != 0:
+        return
+    times = []
+    base = None
+    for i in range(args.warmup + args.steps):
+        base = cpu_reference_sample(args.workload or "c2", seconds_target=6.0)
+        if i >= args.warmup:
+            times.append(base["value"])
+    value = statistics.mean(times)
+    line = {"impl": "reference", "metric": "grouped_gemm_logical_tflops", "value": value, "unit": "TFLOP/s",
+            "n_gpus": args.gpus, "steps": args.steps, "warmup": args.warmup, "ms_per_step": base["seconds"] * 1e3,
+            "higher_is_better": True, "scaling": "weak", "vs_baseline": None, "dtype": "nvfp4 codes, fp32 accumulate",
+            "data": "synthetic", "config": {"workload": WORKLOADS.get(args.workload or "c2", {}).get("desc", args.workload),
+                                            "note": "bounded sample of the workload on the host cores"},
+            "cpu_baseline": {k: base[k] for k in ("value", "unit", "cores", "kind", "sample")},
+            "e2e": {"value": value, "unit": "TFLOP/s", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0}}
+    line["cpu_baseline"]["value"] = value
+    print(json.dumps(line))
+
+
+# ----------------------------------------------------------------------------- main arm
+def timed(fn, steps, warmup, barrier):
+    for _ in range(warmup):
+        fn()
+    barrier()
+    torch.cuda.synchronize()
+    s, e = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    t0 = time.time()
+    s.record()
+    for _ in range(steps):
+        fn()
+    e.record()
+    torch.cuda.synchronize()
+    barrier()
+    return s.elapsed_time(e) / steps, t0, time.time()
+
+
+def measure_fp4_peak():
+    from nvfp4_gemm import _C
+    _C.debug_mma_peak(256)
+    torch.cuda.synchronize()
+    best = 0.0
+    for _ in range(3):
+        s, e = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        s.record()
+        fl = _C.debug_mma_peak(4096)
+        e.record()
+        torch.cuda.synchronize()
+        best = max(best, fl / (s.elapsed_time(e) * 1e-3) / 1e12)
+    return best
+
+
+def main():
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--gpus", type=int, default=1)
+    ap.add_argument("--steps", type=int, default=None)
+    ap.add_argument("--warmup", type=int, default=None)
+    ap.add_argument("--workload", default=None, help="c2 (default at 1 GPU), c3up, c3down, c4, c5 (default at >1 GPU)")
+    ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
+    ap.add_argument("--no-cpu-baseline", action="store_true")
+    args = ap.parse_args()
+    if args.impl == "reference":
+        args.steps = args.steps or 2
+        args.warmup = args.warmup if args.warmup is not None else 1
+        return run_reference_arm(args)
+
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+    rank = int(os.environ.get("RANK", "0"))
+    local = int(os.environ.get("LOCAL_RANK", "0"))
+    workload = args.workload or ("c2" if world == 1 else "c5")
+    torch.cuda.set_device(local)
+    dev = torch.device("cuda", local)
+    if world > 1 or workload == "c5":
+        from nvfp4_cutlass_b200 import ep_bench
+        return ep_bench.run(args, workload, world, rank, local)
+
+    import nvfp4_gemm
+    steps = args.steps or (300 if workload != "c4" else 300)
+    warmup = args.warmup if args.warmup is not None else 10
+    warmup = max(warmup, 3)
+    case = build_single_gpu_case(workload, dev)
+    M, N, K = case["M"], case["N"], case["K"]
+    d = torch.empty(M, N, dtype=torch.bfloat16, device=dev)
+    status = torch.zeros(1, dtype=torch.int32, device=dev)
+
+    def step():
+        nvfp4_gemm.m_grouped_bf16_dual_nvfp4_gemm_contiguous(case["a"], case["b"], case["sfb"], case["gw"], d,
+                                                             case["m_indices"], device_status=status, **case["kw"])
+
+    sampler = ClockSampler(local)
+    sampler.start()
+    ms, t0, t1 = timed(step, steps, warmup, lambda: None)
+    clocks = sampler.stop(t0, t1)
+    assert int(status.item()) == 0, "kernel reported a device-side timeout"
+    rel, cos = accuracy_sample(case, d, dev)
+
+    logical = 2.0 * case["real_rows"] * N * K
+    value = logical / (ms * 1e-3) / 1e12
+    pk = peaks()
+    if case["swap"]:
+        algo_bytes = (case["active_experts"] * (N * K // 2 + N * K // 16) + 2 * case["real_rows"] * K +
+                      2 * case["real_rows"] * N + 4 * case["E"] + 4 * M)
+        achieved = algo_bytes / (ms * 1e-3) / 1e9
+        roofline = {"bound": "hbm", "achieved": achieved, "peak": pk["hbm_gbs"], "unit": "GB/s",
+                    "frac": achieved / pk["hbm_gbs"], "traffic": None, "peak_source": pk["source"],
+                    "algorithmic_bytes_per_launch": algo_bytes}
+    else:
+        fp4_peak = measure_fp4_peak()
+        achieved = 2.0 * logical / (ms * 1e-3) / 1e12       # both NVFP4 passes run on the tensor pipe
+        roofline = {"bound": "tensor", "achieved": achieved, "peak": fp4_peak, "unit": "TFLOP/s",
+                    "frac": achieved / fp4_peak, "traffic": None,
+                    "peak_source": "resident-operand tcgen05 kind::mxf4nvf4 loop measured in this run",
+                    "peak_4x_measured_bf16": 4.0 * pk["bf16_tflops"], "frac_of_4x_measured_bf16": achieved / (4.0 * pk["bf16_tflops"]),
+                    "peak_bf16_source": pk["source"], "tensor_flops_per_launch": 2.0 * logical,
+                    "hbm_gbs_min": (case["b"].numel() + case["sfb"].numel() * 4 + case["a"].numel() * 2 + d.numel() * 2) / (ms * 1e-3) / 1e9}
+
+    # end to end through the public call: activations and routing index come from pinned host
+    # memory every step and the output goes back to pinned host memory (weights are model state,
+    # resident on the device)
+    a_host = case["a"].cpu().pin_memory()
+    mi_host = case["m_indices"].cpu().pin_memory()
+    d_host = torch.empty(M, N, dtype=torch.bfloat16).pin_memory()
+    a_dev = torch.empty_like(case["a"])
+    mi_dev = torch.empty_like(case["m_indices"])
+
+    def e2e_step():
+        a_dev.copy_(a_host, non_blocking=True)
+        mi_dev.copy_(mi_host, non_blocking=True)
+        nvfp4_gemm.m_grouped_bf16_dual_nvfp4_gemm_contiguous(a_dev, case["b"], case["sfb"], case["gw"], d, mi_dev,
+                                                             device_status=status, **case["kw"])
+        d_host.copy_(d, non_blocking=True)
+
+    e2e_steps = max(5, min(steps, 30))
+    e2e_ms, _, _ = timed(e2e_step, e2e_steps, 3, lambda: None)
+    e2e = {"value": logical / (e2e_ms * 1e-3) / 1e12, "unit": "TFLOP/s", "ms_per_step": e2e_ms, "steps": e2e_steps,
+           "h2d_bytes_per_step": a_host.numel() * 2 + mi_host.numel() * 4, "d2h_bytes_per_step": d_host.numel() * 2}
+
+    line = {"metric": "grouped_gemm_logical_tflops", "value": value, "unit": "TFLOP/s", "n_gpus": 1, "steps": steps,
+            "warmup": warmup, "ms_per_step": ms, "higher_is_better": True, "scaling": "weak", "vs_baseline": None,
+            "dtype": "nvfp4 (e2m1 x ue4m3 block 16), fp32 accumulate, bf16 in/out", "data": "synthetic",
+            "config": {"workload": WORKLOADS[workload]["desc"], "name": workload, "M_padded": M, "M_real": case["real_rows"],
+                       "N": N, "K": K, "E": case["E"], "passes": 2, "orientation": "swap_ab" if case["swap"] else "normal",
+                       "l2": "operands larger than L2 (weights %.0f MB), no flush" % (case["b"].numel() / 1e6)},
+            "roofline": roofline, "e2e": e2e, "gpu_launches": steps, "clocks": clocks,
+            "rel_l2_vs_fp32": rel, "cosine_vs_fp32": cos}
+    if not args.no_cpu_baseline:
+        base = cpu_reference_sample(workload)
+        line["cpu_baseline"] = {k: base[k] for k in ("value", "unit", "cores", "kind", "sample")}
+    print(json.dumps(line))
+
+
+if __name__ == "__main__":
+    main()

@@ -1,0 +1,115 @@
+/*
+ * nvfp4_b200 -- C ABI of the B200 (sm_100a) grouped dual-NVFP4 GEMM.
+ *
+ * This is the drop-in boundary for the one hot path of the nvfp4-cutlass project:
+ * the contiguous-layout grouped MoE GEMM with BF16 activations decomposed on chip
+ * into two NVFP4 passes.  Plain pointers and sizes only; every pointer is a CUDA
+ * device pointer on the current device unless said otherwise; `stream` is a
+ * cudaStream_t / CUstream passed as void*.  Calls are asynchronous on `stream`.
+ *
+ * Every function returns 0 on success or one of the NVFP4_E_* codes; the text of the
+ * last error of the calling thread is available from nvfp4_last_error().  Nothing
+ * throws across this boundary and nothing here ever falls back to a CPU path.
+ *
+ * "Replaces" comments name the interface of the reference project that each entry
+ * point stands in for (path within that project : lines).
+ */
+#ifndef NVFP4_B200_H_
+#define NVFP4_B200_H_
+
+#include <stdint.h>
+
+#if defined(__GNUC__)
+#define NVFP4_API __attribute__((visibility("default")))
+#else
+#define NVFP4_API
+#endif
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+enum {
+    NVFP4_OK = 0,
+    NVFP4_E_INVALID_ARGUMENT = 1,  /* bad pointer, dtype code, shape relation or alignment */
+    NVFP4_E_UNSUPPORTED = 2,       /* well-formed request this build has no kernel for */
+    NVFP4_E_CUDA = 3,              /* a CUDA runtime / driver call failed */
+    NVFP4_E_DEVICE_TIMEOUT = 4     /* a bounded in-kernel wait expired (see nvfp4_read_status) */
+};
+
+/* activation scale policies (reference: src/api.hpp:106-112, transform/dual_nvfp4.cuh:31-61) */
+enum { NVFP4_POLICY_DERIVED_DIV8 = 0, NVFP4_POLICY_RESIDUAL_AMAX = 1 };
+/* operand orientation (reference: tune_swap_ab, src/api.hpp:84-104) */
+enum { NVFP4_ORIENT_NORMAL = 0, NVFP4_ORIENT_SWAP_AB = 1 };
+/* weight input dtypes of nvfp4_quantize_weight */
+enum { NVFP4_DTYPE_BF16 = 0, NVFP4_DTYPE_F32 = 1 };
+
+/* Text of the calling thread's last error ("" if none).  Never NULL. */
+NVFP4_API const char* nvfp4_last_error(void);
+
+/* Library / build identification, e.g. "nvfp4_b200 0.1 sm_100a". */
+NVFP4_API const char* nvfp4_version(void);
+
+/* SM count the persistent kernels size their grid with.
+ * Replaces: _C.get_num_sms / _C.set_num_sms (src/api.hpp:150,156; src/runtime/device.hpp:38-54).
+ * `device` < 0 means the current device.  set: 0 restores the hardware count; values
+ * above 2x the hardware count are rejected. */
+NVFP4_API int nvfp4_get_num_sms(int device, int* out);
+NVFP4_API int nvfp4_set_num_sms(int device, int value);
+
+/* Offline NVFP4 weight quantisation on the GPU, bit-exact with the reference's
+ * torch implementation.
+ * Replaces: nvfp4_gemm.quantize_weight_nvfp4 (python/nvfp4_gemm/layout.py:68-127).
+ *   w    (E, N, K) row-major, BF16 or FP32 (w_dtype)
+ *   b    (E*N, K/2) bytes, two E2M1 codes per byte, even element in the low nibble
+ *   sfb  (E*K/64, N) int32, byte j = E4M3 scale of 16-block j of the 64-element atom
+ *   gw   (E,) float
+ * K must be a multiple of 64 (NVFP4_E_INVALID_ARGUMENT otherwise, where the
+ * reference raises ValueError). */
+NVFP4_API int nvfp4_quantize_weight(const void* w, int w_dtype, int E, int N, int K,
+                          void* b, void* sfb, float* gw, void* stream);
+
+/* The hot path.  d[M,N] (BF16) = (A0 + A1) * W^T * gw[expert], experts by row group.
+ * Replaces: _C.m_grouped_bf16_dual_nvfp4_gemm_contiguous (src/api.hpp:26-144,
+ * kernels src/kernels/sm100_bf16_dual_nvfp4_gemm.hpp:226-480 and :489-632).
+ *   a          (M, K) BF16, K contiguous, row stride lda_elems
+ *   b, sfb, gw as produced by nvfp4_quantize_weight for E experts of shape (N, K)
+ *   d          (M, N) BF16, row stride ldd_elems, written in place
+ *   m_indices  (M,) int32 expert id of each row; each expert's rows start on an
+ *              m_alignment boundary (128 normal, 16/32/64/128 swap-AB); only the
+ *              first row of each aligned block is read, negative ids read as 0
+ *   enable_residual_pass 0 = the single_nvfp4 variant (second pass skipped)
+ *   tune       optional host array of 18 int32 in the order of the reference's
+ *              tune_* keywords (src/api.hpp:166-203), or NULL; 0 = default.  Knobs
+ *              without a counterpart here are accepted and ignored.
+ *   device_status optional device int32 the kernel ORs error bits into (bit 0 =
+ *              a bounded wait expired); may be NULL
+ * Constraints as in the reference (src/api.hpp:58-79): N % 128 == 0, K % 128 == 0,
+ * M % m_alignment == 0; M == 0 or N == 0 returns NVFP4_OK without a launch. */
+NVFP4_API int nvfp4_grouped_gemm_contiguous(const void* a, int64_t lda_elems, const void* b, const void* sfb,
+                                  const float* gw, void* d, int64_t ldd_elems,
+                                  const int32_t* m_indices, int M, int N, int K, int E,
+                                  int scale_policy, int enable_residual_pass, int orientation,
+                                  int m_alignment, const int32_t* tune, int32_t* device_status,
+                                  void* stream);
+
+/* Test hook: Algorithm 1 exactly as the GEMM's transform warps run it (same device
+ * code, same shared-memory layouts), with the codes copied out instead of being fed to
+ * the tensor cores.  The GEMM itself never writes a quantised activation to global
+ * memory; this exists so that q0/q1/s0/s1 can be compared bit for bit.
+ * Counterpart in the reference: tests/standalone/test_transform.cu:50-132.
+ *   a (M, K) BF16 row stride lda_elems; M % 128 == 0, K % 128 == 0
+ *   q0, q1 (M, K/2) bytes (two codes per byte, even element low); s0, s1 (M, K/16) bytes */
+NVFP4_API int nvfp4_debug_decompose(const void* a, int64_t lda_elems, int M, int K, int scale_policy,
+                          void* q0, void* q1, void* s0, void* s1, void* stream);
+
+/* Measurement hook: issues `iters` rounds of resident-operand block-scaled FP4 MMAs
+ * (128 x 256 x 64 each) per SM with no memory traffic and returns through
+ * `flops_per_launch` the number of floating-point operations one launch performs.
+ * Used to measure the tensor-pipe ceiling the roofline fractions are quoted against. */
+NVFP4_API int nvfp4_debug_mma_peak(int iters, double* flops_per_launch, void* stream);
+
+#ifdef __cplusplus
+}
+#endif
+#endif /* NVFP4_B200_H_ */

@@ -1,0 +1,172 @@
+"""Binding of the C ABI (include/nvfp4_b200.h) -- the stand-in for the reference's
+compiled ``_C`` extension module (src/python_api.cpp:10-14, src/api.hpp:146-204 there).
+
+Tensors cross the boundary as raw device pointers, sizes and strides; the launch
+goes onto torch's current CUDA stream, as in the reference (src/jit/launch.hpp:47).
+Failures of the library surface as ``RuntimeError`` carrying its error text, where
+the reference's pybind layer surfaces its C++ exception.  There is no fallback of
+any kind: without the compiled library, or without a CUDA tensor, calls raise.
+"""
+from __future__ import annotations
+
+import ctypes
+import os
+
+import torch
+
+_LIB_PATH = os.path.join(os.path.dirname(os.path.abspath(__file__)), "lib", "libnvfp4_b200.so")
+_lib = None
+
+POLICY_CODES = {"derived_div8": 0, "residual_amax": 1, "derived_div4": 2, "div4_radix8": 3}
+
+# keyword order of the reference's tune_* arguments (src/api.hpp:166-203)
+TUNE_KEYS = ("tune_block_n", "tune_transform_warps", "tune_epilogue_threads", "tune_num_stages",
+             "tune_swizzle_cd", "tune_block_k", "tune_epilogue_stages", "tune_swap_ab", "tune_cluster",
+             "tune_direct_a", "tune_l2_pin_weights", "tune_no_pdl", "tune_sched_group",
+             "tune_split_transform", "tune_timing_probe", "tune_tail_split", "tune_shallow_stages",
+             "tune_produced_stages")
+
+EXPORTS = ("nvfp4_last_error", "nvfp4_version", "nvfp4_get_num_sms", "nvfp4_set_num_sms",
+           "nvfp4_quantize_weight", "nvfp4_grouped_gemm_contiguous", "nvfp4_debug_decompose",
+           "nvfp4_debug_mma_peak")
+
+
+def library_path() -> str:
+    return _LIB_PATH
+
+
+def lib() -> ctypes.CDLL:
+    """The loaded shared library; raises if it has not been built."""
+    global _lib
+    if _lib is None:
+        if not os.path.exists(_LIB_PATH):
+            raise RuntimeError(
+                f"{_LIB_PATH} is missing: build it with `python nvfp4_cutlass_b200/csrc/build.py` "
+                "(there is no fallback path)")
+        L = ctypes.CDLL(_LIB_PATH)
+        vp, i32, i64 = ctypes.c_void_p, ctypes.c_int, ctypes.c_int64
+        L.nvfp4_last_error.restype = ctypes.c_char_p
+        L.nvfp4_version.restype = ctypes.c_char_p
+        L.nvfp4_get_num_sms.argtypes = [i32, ctypes.POINTER(i32)]
+        L.nvfp4_set_num_sms.argtypes = [i32, i32]
+        L.nvfp4_quantize_weight.argtypes = [vp, i32, i32, i32, i32, vp, vp, vp, vp]
+        L.nvfp4_grouped_gemm_contiguous.argtypes = [vp, i64, vp, vp, vp, vp, i64, vp, i32, i32, i32, i32,
+                                                    i32, i32, i32, i32, vp, vp, vp]
+        L.nvfp4_debug_decompose.argtypes = [vp, i64, i32, i32, i32, vp, vp, vp, vp, vp]
+        L.nvfp4_debug_mma_peak.argtypes = [i32, ctypes.POINTER(ctypes.c_double), vp]
+        _lib = L
+    return _lib
+
+
+def _check(rc: int) -> None:
+    if rc != 0:
+        raise RuntimeError(f"nvfp4_b200 error {rc}: {lib().nvfp4_last_error().decode()}")
+
+
+def _stream() -> int:
+    return torch.cuda.current_stream().cuda_stream
+
+
+def _require(cond: bool, what: str) -> None:
+    if not cond:
+        raise RuntimeError(f"nvfp4_gemm: assertion failed: {what}")
+
+
+def init(include_root: str = "", cuda_home: str = "") -> None:
+    """Kept for signature compatibility: the reference starts its JIT here; kernels
+    in this build are compiled ahead of time, so this only loads the library."""
+    lib()
+
+
+def get_num_sms() -> int:
+    out = ctypes.c_int(0)
+    _check(lib().nvfp4_get_num_sms(-1, ctypes.byref(out)))
+    return out.value
+
+
+def set_num_sms(num_sms: int) -> None:
+    _check(lib().nvfp4_set_num_sms(-1, int(num_sms)))
+
+
+def set_probe_buffer(t=None) -> None:
+    """The reference's in-kernel clock probe has no counterpart; accepted and ignored."""
+
+
+def m_grouped_bf16_dual_nvfp4_gemm_contiguous(a, b, sfb, gw, d, m_indices, scale_policy: str = "derived_div8",
+                                              enable_residual_pass: bool = True, *, device_status=None,
+                                              m_alignment: int = 0, **tune) -> None:
+    """d = (A0 + A1) @ W^T * gw per expert group; same contract as the reference entry
+    (src/api.hpp:26-144): dtype / shape assertions first, then a silent return for
+    M == 0 or N == 0, then an asynchronous launch on the current stream."""
+    for key in tune:
+        if key not in TUNE_KEYS:
+            raise TypeError(f"m_grouped_bf16_dual_nvfp4_gemm_contiguous() got an unexpected keyword argument {key!r}")
+    _require(a.dtype == torch.bfloat16, "a.dtype == bfloat16")
+    _require(d.dtype == torch.bfloat16, "d.dtype == bfloat16")
+    _require(b.dtype == torch.int8, "b.dtype == int8")
+    _require(sfb.dtype == torch.int32, "sfb.dtype == int32")
+    _require(gw.dtype == torch.float32, "gw.dtype == float32")
+    _require(m_indices.dtype == torch.int32, "m_indices.dtype == int32")
+    _require(a.dim() == 2 and d.dim() == 2, "a.dim() == 2 and d.dim() == 2")
+    m, k = a.shape
+    n = d.shape[1]
+    e = gw.numel()
+    _require(d.shape[0] == m, "d.size(0) == m")
+    _require(m_indices.dim() == 1 and m_indices.shape[0] == m, "m_indices.size(0) == m")
+    _require(b.dim() == 2 and b.shape[0] == e * n, "b.size(0) == num_groups * n")
+    _require(b.shape[1] == k // 2, "b.size(1) == k / 2")
+    _require(sfb.dim() == 2 and sfb.shape[0] == e * (k // 64), "sfb.size(0) == num_groups * (k / 64)")
+    _require(sfb.shape[1] == n, "sfb.size(1) == n")
+    for name, t in (("a", a), ("b", b), ("sfb", sfb), ("gw", gw), ("d", d), ("m_indices", m_indices)):
+        _require(t.is_cuda, f"{name} is a CUDA tensor")
+    _require(a.stride(1) == 1 and d.stride(1) == 1, "a and d are contiguous along their last dimension")
+    _require(b.is_contiguous() and sfb.is_contiguous() and gw.is_contiguous() and m_indices.is_contiguous(),
+             "b, sfb, gw, m_indices are contiguous")
+    if scale_policy not in POLICY_CODES:
+        raise RuntimeError("scale_policy must be 'derived_div8', 'derived_div4', 'div4_radix8' or 'residual_amax'")
+    swap = int(tune.get("tune_swap_ab", 0)) != 0
+    tune_arr = (ctypes.c_int32 * len(TUNE_KEYS))(*[int(tune.get(key, 0)) for key in TUNE_KEYS])
+    lda = a.stride(0) if m > 1 else max(a.stride(0), k)
+    ldd = d.stride(0) if m > 1 else max(d.stride(0), n)
+    _check(lib().nvfp4_grouped_gemm_contiguous(
+        a.data_ptr(), lda, b.data_ptr(), sfb.data_ptr(), gw.data_ptr(), d.data_ptr(), ldd,
+        m_indices.data_ptr(), m, n, k, e, POLICY_CODES[scale_policy], 1 if enable_residual_pass else 0,
+        1 if swap else 0, int(m_alignment), ctypes.cast(tune_arr, ctypes.c_void_p),
+        device_status.data_ptr() if device_status is not None else None, _stream()))
+
+
+def quantize_weight(w: torch.Tensor):
+    """CUDA tensor (E, N, K), BF16 or FP32 -> (b, sfb, gw) on the same device."""
+    _require(w.is_cuda, "w is a CUDA tensor")
+    if w.dtype not in (torch.bfloat16, torch.float32):
+        w = w.to(torch.float32)
+    w = w.contiguous()
+    e, n, k = w.shape
+    b = torch.empty(e * n, k // 2, dtype=torch.int8, device=w.device)
+    sfb = torch.empty(e * k // 64, n, dtype=torch.int32, device=w.device)
+    gw = torch.empty(e, dtype=torch.float32, device=w.device)
+    with torch.cuda.device(w.device):
+        _check(lib().nvfp4_quantize_weight(w.data_ptr(), 0 if w.dtype == torch.bfloat16 else 1, e, n, k,
+                                           b.data_ptr(), sfb.data_ptr(), gw.data_ptr(), _stream()))
+    return b, sfb, gw
+
+
+def debug_decompose(a: torch.Tensor, scale_policy: str = "derived_div8"):
+    """Algorithm 1 as the GEMM's transform warps run it; returns packed q0, q1 (M, K/2)
+    and s0, s1 (M, K/16) as uint8 CUDA tensors.  Test hook."""
+    _require(a.is_cuda and a.dtype == torch.bfloat16 and a.dim() == 2 and a.stride(1) == 1, "a is a 2-D BF16 CUDA tensor")
+    m, k = a.shape
+    q0 = torch.empty(m, k // 2, dtype=torch.uint8, device=a.device)
+    q1 = torch.empty_like(q0)
+    s0 = torch.empty(m, k // 16, dtype=torch.uint8, device=a.device)
+    s1 = torch.empty_like(s0)
+    _check(lib().nvfp4_debug_decompose(a.data_ptr(), a.stride(0), m, k, POLICY_CODES[scale_policy],
+                                       q0.data_ptr(), q1.data_ptr(), s0.data_ptr(), s1.data_ptr(), _stream()))
+    return q0, q1, s0, s1
+
+
+def debug_mma_peak(iters: int) -> float:
+    """Launches the resident-operand FP4 MMA loop once; returns the FLOPs of the launch."""
+    flops = ctypes.c_double(0.0)
+    _check(lib().nvfp4_debug_mma_peak(int(iters), ctypes.byref(flops), _stream()))
+    return flops.value

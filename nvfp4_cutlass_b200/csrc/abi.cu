@@ -1,0 +1,202 @@
+// The C ABI (include/nvfp4_b200.h): argument validation, per-device runtime
+// state, dispatch to the kernels.  Counterpart in the reference: src/api.hpp
+// (validation + dispatch), src/runtime/device.hpp, src/runtime/exception.hpp.
+#include <cstring>
+#include <mutex>
+
+#include "host_common.hpp"
+#include "launchers.hpp"
+
+namespace nvfp4::host {
+
+namespace {
+thread_local char g_error[512] = "";
+DeviceInfo g_devices[kMaxDevices];
+std::mutex g_mutex;
+}  // namespace
+
+int fail(int code, const char* fmt, ...)
+{
+    va_list ap;
+    va_start(ap, fmt);
+    vsnprintf(g_error, sizeof g_error, fmt, ap);
+    va_end(ap);
+    return code;
+}
+void clear_error() { g_error[0] = '\0'; }
+
+int device_info(int device, DeviceInfo** out)
+{
+    if (device < 0) NVFP4_CUDA_CHECK(cudaGetDevice(&device));
+    if (device >= kMaxDevices) return fail(NVFP4_E_INVALID_ARGUMENT, "device %d out of range", device);
+    std::lock_guard<std::mutex> lock(g_mutex);
+    DeviceInfo& d = g_devices[device];
+    if (!d.known) {
+        NVFP4_CUDA_CHECK(cudaDeviceGetAttribute(&d.hw_sms, cudaDevAttrMultiProcessorCount, device));
+        NVFP4_CUDA_CHECK(cudaDeviceGetAttribute(&d.cc_major, cudaDevAttrComputeCapabilityMajor, device));
+        NVFP4_CUDA_CHECK(cudaDeviceGetAttribute(&d.cc_minor, cudaDevAttrComputeCapabilityMinor, device));
+        NVFP4_CUDA_CHECK(cudaDeviceGetAttribute(&d.max_smem_optin, cudaDevAttrMaxSharedMemoryPerBlockOptin, device));
+        d.num_sms = d.hw_sms;
+        d.known = true;
+    }
+    *out = &d;
+    return NVFP4_OK;
+}
+
+int encode_tensor_map_2d(CUtensorMap* map, CUtensorMapDataType dtype, uint32_t elem_bytes, const void* base,
+                         uint64_t dim0, uint64_t dim1, uint64_t row_stride_bytes, uint32_t box0, uint32_t box1,
+                         CUtensorMapSwizzle swizzle)
+{
+    using EncodeFn = CUresult (*)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*,
+                                  const cuuint64_t*, const cuuint32_t*, const cuuint32_t*, CUtensorMapInterleave,
+                                  CUtensorMapSwizzle, CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
+    static EncodeFn encode = nullptr;
+    if (encode == nullptr) {
+        void* fn = nullptr;
+        cudaDriverEntryPointQueryResult qres;
+        NVFP4_CUDA_CHECK(cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &fn, cudaEnableDefault, &qres));
+        if (fn == nullptr || qres != cudaDriverEntryPointSuccess)
+            return fail(NVFP4_E_CUDA, "driver has no cuTensorMapEncodeTiled");
+        encode = reinterpret_cast<EncodeFn>(fn);
+    }
+    if ((reinterpret_cast<uintptr_t>(base) & 15u) != 0)
+        return fail(NVFP4_E_INVALID_ARGUMENT, "tensor base %p is not 16-byte aligned", base);
+    if (row_stride_bytes % 16 != 0)
+        return fail(NVFP4_E_INVALID_ARGUMENT, "row stride of %llu bytes is not a multiple of 16",
+                    static_cast<unsigned long long>(row_stride_bytes));
+    const cuuint64_t dims[2] = {dim0, dim1};
+    const cuuint64_t strides[1] = {row_stride_bytes};
+    const cuuint32_t box[2] = {box0, box1};
+    const cuuint32_t elem_strides[2] = {1, 1};
+    (void)elem_bytes;
+    const CUresult r = encode(map, dtype, 2, const_cast<void*>(base), dims, strides, box, elem_strides,
+                              CU_TENSOR_MAP_INTERLEAVE_NONE, swizzle, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
+                              CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+    if (r != CUDA_SUCCESS)
+        return fail(NVFP4_E_CUDA, "cuTensorMapEncodeTiled failed with CUresult %d (dims %llu x %llu, box %u x %u)",
+                    static_cast<int>(r), static_cast<unsigned long long>(dim0),
+                    static_cast<unsigned long long>(dim1), box0, box1);
+    return NVFP4_OK;
+}
+
+}  // namespace nvfp4::host
+
+using namespace nvfp4;
+
+extern "C" {
+
+const char* nvfp4_last_error(void) { return host::g_error; }
+const char* nvfp4_version(void) { return "nvfp4_b200 0.1 sm_100a"; }
+
+int nvfp4_get_num_sms(int device, int* out)
+{
+    host::clear_error();
+    NVFP4_REQUIRE(out != nullptr, "out is null");
+    host::DeviceInfo* d;
+    if (int rc = host::device_info(device, &d)) return rc;
+    *out = d->num_sms;
+    return NVFP4_OK;
+}
+
+int nvfp4_set_num_sms(int device, int value)
+{
+    host::clear_error();
+    host::DeviceInfo* d;
+    if (int rc = host::device_info(device, &d)) return rc;
+    NVFP4_REQUIRE(value >= 0 && value <= 2 * d->hw_sms, "num_sms %d outside [0, %d]", value, 2 * d->hw_sms);
+    d->num_sms = value == 0 ? d->hw_sms : value;
+    return NVFP4_OK;
+}
+
+int nvfp4_quantize_weight(const void* w, int w_dtype, int E, int N, int K, void* b, void* sfb, float* gw,
+                          void* stream)
+{
+    host::clear_error();
+    NVFP4_REQUIRE(E >= 0 && N >= 0 && K >= 0, "negative shape (E=%d, N=%d, K=%d)", E, N, K);
+    NVFP4_REQUIRE(K % 64 == 0, "K=%d must be a multiple of 64", K);
+    NVFP4_REQUIRE(w_dtype == NVFP4_DTYPE_BF16 || w_dtype == NVFP4_DTYPE_F32, "unknown weight dtype code %d", w_dtype);
+    if (E == 0 || N == 0 || K == 0) return NVFP4_OK;
+    NVFP4_REQUIRE(w && b && sfb && gw, "null pointer argument");
+    NVFP4_REQUIRE((reinterpret_cast<uintptr_t>(b) & 15u) == 0, "b must be 16-byte aligned");
+    host::DeviceInfo* d;
+    if (int rc = host::device_info(-1, &d)) return rc;
+    if (d->cc_major != 10) return host::fail(NVFP4_E_UNSUPPORTED, "needs an sm_100 GPU, found sm_%d%d", d->cc_major, d->cc_minor);
+    return launch_quantize_weight(w, w_dtype, E, N, K, b, sfb, gw, static_cast<cudaStream_t>(stream));
+}
+
+int nvfp4_grouped_gemm_contiguous(const void* a, int64_t lda_elems, const void* b, const void* sfb, const float* gw,
+                                  void* d, int64_t ldd_elems, const int32_t* m_indices, int M, int N, int K, int E,
+                                  int scale_policy, int enable_residual_pass, int orientation, int m_alignment,
+                                  const int32_t* tune, int32_t* device_status, void* stream)
+{
+    host::clear_error();
+    // the reference's checks, in its order (src/api.hpp:58-79 there)
+    NVFP4_REQUIRE(M >= 0 && N >= 0 && K >= 0 && E >= 0, "negative shape (M=%d, N=%d, K=%d, E=%d)", M, N, K, E);
+    NVFP4_REQUIRE(K % 128 == 0 && N % 128 == 0, "N and K must be multiples of 128 (N=%d, K=%d)", N, K);
+    NVFP4_REQUIRE(orientation == NVFP4_ORIENT_NORMAL || orientation == NVFP4_ORIENT_SWAP_AB, "unknown orientation %d", orientation);
+    if (orientation == NVFP4_ORIENT_NORMAL) {
+        if (m_alignment == 0) m_alignment = 128;
+        NVFP4_REQUIRE(m_alignment == 128, "normal orientation needs m_alignment 128, got %d", m_alignment);
+    } else {
+        if (m_alignment == 0) m_alignment = 32;
+        NVFP4_REQUIRE(m_alignment == 16 || m_alignment == 32 || m_alignment == 64 || m_alignment == 128,
+                      "swap-AB m_alignment must be 16, 32, 64 or 128, got %d", m_alignment);
+    }
+    NVFP4_REQUIRE(M % m_alignment == 0, "M must be a multiple of the token-tile alignment (M=%d, alignment=%d)", M, m_alignment);
+    if (M == 0 || N == 0) return NVFP4_OK;
+    NVFP4_REQUIRE(E > 0 && K > 0, "empty weights (E=%d, K=%d)", E, K);
+    NVFP4_REQUIRE(a && b && sfb && gw && d && m_indices, "null pointer argument");
+    NVFP4_REQUIRE(lda_elems >= K && ldd_elems >= N, "row strides too small (lda=%lld, ldd=%lld)",
+                  static_cast<long long>(lda_elems), static_cast<long long>(ldd_elems));
+    NVFP4_REQUIRE(lda_elems % 8 == 0 && ldd_elems % 8 == 0, "row strides must be multiples of 8 elements (16 bytes)");
+    NVFP4_REQUIRE((reinterpret_cast<uintptr_t>(d) & 15u) == 0, "d must be 16-byte aligned");
+    if (scale_policy != NVFP4_POLICY_DERIVED_DIV8)
+        return host::fail(NVFP4_E_UNSUPPORTED, "scale policy %d is not built; only derived_div8", scale_policy);
+
+    host::DeviceInfo* dev;
+    if (int rc = host::device_info(-1, &dev)) return rc;
+    if (dev->cc_major != 10) return host::fail(NVFP4_E_UNSUPPORTED, "needs an sm_100 GPU, found sm_%d%d", dev->cc_major, dev->cc_minor);
+
+    // tune[] follows the reference's keyword order: 0 block_n, 1 transform_warps, ..., 12 sched_group
+    const int tune_block_n = tune ? tune[0] : 0;
+    const int tune_xform_warps = tune ? tune[1] : 0;
+    const int tune_sched_group = tune ? tune[12] : 0;
+    cudaStream_t s = static_cast<cudaStream_t>(stream);
+    if (orientation == NVFP4_ORIENT_SWAP_AB) {
+        // token tile: the caller's choice if it divides the alignment, else the largest built tile that does
+        int tile = tune_block_n > 0 ? tune_block_n : (m_alignment >= 64 ? 64 : m_alignment);
+        NVFP4_REQUIRE((tile == 16 || tile == 32 || tile == 64) && m_alignment % tile == 0,
+                      "token tile %d must be 16, 32 or 64 and divide m_alignment %d", tile, m_alignment);
+        return launch_gemm_swap(a, lda_elems, b, sfb, gw, d, ldd_elems, m_indices, M, N, K, E, enable_residual_pass != 0,
+                                tile, dev->num_sms, device_status, s);
+    }
+    NVFP4_REQUIRE(tune_xform_warps == 0 || tune_xform_warps == 8 || tune_xform_warps == 16,
+                  "tune_transform_warps must be 0, 8 or 16");
+    return launch_gemm_normal(a, lda_elems, b, sfb, gw, d, ldd_elems, m_indices, M, N, K, E, enable_residual_pass != 0,
+                              tune_xform_warps, tune_sched_group, dev->num_sms, device_status, s);
+}
+
+int nvfp4_debug_decompose(const void* a, int64_t lda_elems, int M, int K, int scale_policy, void* q0, void* q1,
+                          void* s0, void* s1, void* stream)
+{
+    host::clear_error();
+    NVFP4_REQUIRE(M >= 0 && K >= 0 && M % 128 == 0 && K % 128 == 0, "M and K must be multiples of 128 (M=%d, K=%d)", M, K);
+    if (scale_policy != NVFP4_POLICY_DERIVED_DIV8)
+        return host::fail(NVFP4_E_UNSUPPORTED, "scale policy %d is not built; only derived_div8", scale_policy);
+    if (M == 0 || K == 0) return NVFP4_OK;
+    NVFP4_REQUIRE(a && q0 && q1 && s0 && s1, "null pointer argument");
+    NVFP4_REQUIRE(lda_elems >= K && lda_elems % 8 == 0, "bad row stride %lld", static_cast<long long>(lda_elems));
+    return launch_debug_decompose(a, lda_elems, M, K, q0, q1, s0, s1, static_cast<cudaStream_t>(stream));
+}
+
+int nvfp4_debug_mma_peak(int iters, double* flops_per_launch, void* stream)
+{
+    host::clear_error();
+    NVFP4_REQUIRE(iters > 0 && iters <= (1 << 20), "iters %d outside [1, 2^20]", iters);
+    host::DeviceInfo* dev;
+    if (int rc = host::device_info(-1, &dev)) return rc;
+    if (dev->cc_major != 10) return host::fail(NVFP4_E_UNSUPPORTED, "needs an sm_100 GPU");
+    return launch_mma_peak(iters, dev->hw_sms, flops_per_launch, static_cast<cudaStream_t>(stream));
+}
+
+}  // extern "C"

@@ -1,0 +1,394 @@
+// Grouped dual-NVFP4 GEMM, normal orientation: token rows on the MMA M axis.
+//
+//   d[m, n] = bf16( gw[e(m)] * sum_k (q0*s0 + q1*s1)[m, k] * (dec(W)*S)[e(m), n, k] )
+//
+// One persistent CTA per SM works through 128 x 256 output tiles.  Per 128-wide K
+// block the roles hand data along three rings of shared-memory slots:
+//
+//   A ring  (BF16 activations, 32 KB/slot)    TMA warp        -> transform warps
+//   P ring  (A0, A1, SFA0, SFA1, 18 KB/slot)  transform warps -> MMA warp
+//   B ring  (FP4 weights + SFB, 18 KB/slot)   TMA warp        -> SFB-transpose warp, MMA warp
+//
+// and the accumulator (128 lanes x 256 FP32 columns of tensor memory) goes from
+// the MMA warp to the epilogue warps.  Each ring has its own full / empty
+// mbarriers and its own depth, so a shallow ring never throttles a deep one.  The
+// quantised activations live only in shared memory.
+//
+// Counterpart in the reference: include/nvfp4_gemm/impls/sm100_bf16_dual_nvfp4_gemm.cuh
+// (kernel), scheduler/grouped_gemm.cuh (tile order), epilogue/sm100_store_cd.cuh
+// (G_W epilogue), src/kernels/sm100_bf16_dual_nvfp4_gemm.hpp:226-480 (launcher).
+#include <cuda_bf16.h>
+
+#include "host_common.hpp"
+#include "launchers.hpp"
+#include "transform.cuh"
+
+namespace nvfp4 {
+
+namespace {
+
+constexpr uint32_t BM = 128, BK = 128;
+constexpr uint32_t kKAtoms = BK / 64;               // MMA K = 64: one scale atom per instruction
+constexpr uint32_t kSlotA = BM * BK * 2;            // 32768
+constexpr uint32_t kSlotA0 = BM * BK / 2;           // 8192
+constexpr uint32_t kSlotSFA = kKAtoms * 512;        // 1024
+constexpr uint32_t kDepthA = 3, kDepthP = 2;
+
+// BN = 256 output columns per tile whenever N allows it (one transformed activation tile
+// then feeds twice the tensor work); BN = 128 serves N that is an odd multiple of 128.
+template <uint32_t BN>
+struct Cfg {
+    static constexpr uint32_t kSlotB = BN * BK / 2;                      // 16384 at BN = 256
+    static constexpr uint32_t kSlotSFB = kKAtoms * (BN / 128) * 512;     // 2048
+    static constexpr uint32_t kDepthB = BN == 256 ? 4 : 6;
+    static constexpr uint32_t kOffA = 0;
+    static constexpr uint32_t kOffA0 = kOffA + kDepthA * kSlotA;
+    static constexpr uint32_t kOffA1 = kOffA0 + kDepthP * kSlotA0;
+    static constexpr uint32_t kOffB = kOffA1 + kDepthP * kSlotA0;
+    static constexpr uint32_t kOffSFA0 = kOffB + kDepthB * kSlotB;
+    static constexpr uint32_t kOffSFA1 = kOffSFA0 + kDepthP * kSlotSFA;
+    static constexpr uint32_t kOffSFB = kOffSFA1 + kDepthP * kSlotSFA;
+    static constexpr uint32_t kOffBars = kOffSFB + kDepthB * kSlotSFB;
+    static constexpr uint32_t kNumBars = 2 * kDepthA + 2 * kDepthP + 3 * kDepthB + 2;
+    static constexpr uint32_t kSmemBytes = kOffBars + kNumBars * 8 + 16;
+    static constexpr uint32_t kSmemAlloc = kSmemBytes + 1024;            // slack to align the base to 1024 B
+    static_assert(kSmemAlloc <= 232448, "shared memory budget");
+};
+
+// tensor-memory columns
+constexpr uint32_t kTmemCols = 512;
+constexpr uint32_t kColAcc = 0, kColSFA0 = 256, kColSFA1 = kColSFA0 + 4 * kKAtoms, kColSFB = kColSFA1 + 4 * kKAtoms;
+
+// warp roles
+constexpr uint32_t kWarpTma = 0, kWarpMma = 1, kWarpSfb = 2, kWarpEpi0 = 4, kNumEpiWarps = 4, kWarpXform0 = 8;
+
+struct Params {
+    const float* gw;
+    const int32_t* m_indices;
+    __nv_bfloat16* d;
+    int64_t ldd;
+    uint32_t m, n, k, num_experts;
+    uint32_t group_m;          // m-blocks per scheduling group
+    int32_t* status;           // may be null
+};
+
+struct Ring {
+    uint32_t slot = 0, phase = 0;
+    template <uint32_t kDepth>
+    __device__ __forceinline__ void advance()
+    {
+        if (++slot == kDepth) { slot = 0; phase ^= 1; }
+    }
+};
+
+__device__ __forceinline__ void tile_coords(uint32_t tile, uint32_t num_m, uint32_t num_n, uint32_t group_m,
+                                            uint32_t& m_blk, uint32_t& n_blk)
+{
+    // groups of `group_m` row blocks; inside a group consecutive tiles walk the row
+    // blocks first, so CTAs running side by side share weight tiles and, across the
+    // wave, activation tiles (both served from L2).
+    const uint32_t per_group = group_m * num_n;
+    const uint32_t g = tile / per_group, r = tile % per_group;
+    const uint32_t first = g * group_m;
+    const uint32_t rows = min(group_m, num_m - first);
+    m_blk = first + r % rows;
+    n_blk = r / rows;
+}
+
+template <uint32_t BN, uint32_t kXformWarps, bool kResidual>
+__global__ void __launch_bounds__((kWarpXform0 + kXformWarps) * 32, 1)
+gemm_normal_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constant__ CUtensorMap tm_b,
+                   const __grid_constant__ CUtensorMap tm_sfb, const Params p)
+{
+    using C = Cfg<BN>;
+    constexpr uint32_t kSlotB = C::kSlotB, kSlotSFB = C::kSlotSFB, kDepthB = C::kDepthB;
+    constexpr uint32_t kOffA = C::kOffA, kOffA0 = C::kOffA0, kOffA1 = C::kOffA1, kOffB = C::kOffB, kOffSFA0 = C::kOffSFA0,
+                       kOffSFA1 = C::kOffSFA1, kOffSFB = C::kOffSFB, kOffBars = C::kOffBars;
+    constexpr uint32_t kXformThreads = kXformWarps * 32;
+    extern __shared__ uint8_t smem_raw[];
+    const uint32_t smem = (ptx::smem_u32(smem_raw) + 1023u) & ~1023u;
+    uint8_t* smem_gen = smem_raw + (smem - ptx::smem_u32(smem_raw));
+
+    uint64_t* bars = reinterpret_cast<uint64_t*>(smem_gen + kOffBars);
+    uint64_t* a_full = bars;
+    uint64_t* a_empty = a_full + kDepthA;
+    uint64_t* p_full = a_empty + kDepthA;
+    uint64_t* p_empty = p_full + kDepthP;
+    uint64_t* b_full = p_empty + kDepthP;
+    uint64_t* b_ready = b_full + kDepthB;
+    uint64_t* b_empty = b_ready + kDepthB;
+    uint64_t* tmem_full = b_empty + kDepthB;
+    uint64_t* tmem_empty = tmem_full + 1;
+    uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(tmem_empty + 1);
+    volatile uint32_t* abort_flag = tmem_slot + 1;
+
+    const uint32_t warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+
+    if (threadIdx.x == 0) {
+        for (uint32_t i = 0; i < kDepthA; ++i) { ptx::mbar_init(a_full + i, 1); ptx::mbar_init(a_empty + i, kXformWarps); }
+        for (uint32_t i = 0; i < kDepthP; ++i) { ptx::mbar_init(p_full + i, kXformWarps); ptx::mbar_init(p_empty + i, 1); }
+        for (uint32_t i = 0; i < kDepthB; ++i) {
+            ptx::mbar_init(b_full + i, 1);
+            ptx::mbar_init(b_ready + i, 1);
+            ptx::mbar_init(b_empty + i, 1);
+        }
+        ptx::mbar_init(tmem_full, 1);
+        ptx::mbar_init(tmem_empty, kNumEpiWarps);
+        *abort_flag = 0;
+        ptx::fence_mbar_init();
+        ptx::prefetch_tensormap(&tm_a);
+        ptx::prefetch_tensormap(&tm_b);
+        ptx::prefetch_tensormap(&tm_sfb);
+    }
+    if (warp == kWarpMma) ptx::tmem_alloc<kTmemCols>(tmem_slot);
+    ptx::tcgen05_fence_before_sync();
+    __syncthreads();
+    ptx::tcgen05_fence_after_sync();
+    const uint32_t tmem_base = *tmem_slot;
+
+    const uint32_t num_m = p.m / BM, num_n = p.n / BN, num_kb = p.k / BK;
+    const uint32_t num_tiles = num_m * num_n;
+    bool ok = true;
+    auto give_up = [&](uint32_t code) {
+        *abort_flag = 1;
+        if (p.status != nullptr) atomicOr(p.status, static_cast<int32_t>(code));
+        ok = false;
+    };
+
+    if (warp == kWarpTma) {
+        // ================= TMA producer (one lane) =================
+        if (lane == 0) {
+            Ring ra, rb;
+            for (uint32_t tile = blockIdx.x; tile < num_tiles && ok; tile += gridDim.x) {
+                uint32_t m_blk, n_blk;
+                tile_coords(tile, num_m, num_n, p.group_m, m_blk, n_blk);
+                const int32_t e = max(0, __ldg(p.m_indices + m_blk * BM));
+                for (uint32_t kb = 0; kb < num_kb; ++kb) {
+                    if (!ptx::mbar_wait(a_empty + ra.slot, ra.phase ^ 1, abort_flag)) { give_up(1); break; }
+                    ptx::mbar_arrive_expect_tx(a_full + ra.slot, kSlotA);
+                    const uint32_t a_dst = kOffA + ra.slot * kSlotA;
+                    ptx::tma_load_2d(smem_gen + a_dst, &tm_a, a_full + ra.slot, kb * BK, m_blk * BM);
+                    ptx::tma_load_2d(smem_gen + a_dst + kSlotA / 2, &tm_a, a_full + ra.slot, kb * BK + 64, m_blk * BM);
+                    ra.advance<kDepthA>();
+
+                    if (!ptx::mbar_wait(b_empty + rb.slot, rb.phase ^ 1, abort_flag)) { give_up(1); break; }
+                    ptx::mbar_arrive_expect_tx(b_full + rb.slot, kSlotB + kSlotSFB);
+                    ptx::tma_load_2d(smem_gen + kOffB + rb.slot * kSlotB, &tm_b, b_full + rb.slot, kb * (BK / 2),
+                                     e * p.n + n_blk * BN);
+                    ptx::tma_load_2d(smem_gen + kOffSFB + rb.slot * kSlotSFB, &tm_sfb, b_full + rb.slot, n_blk * BN,
+                                     e * (p.k / 64) + kb * kKAtoms);
+                    rb.advance<kDepthB>();
+                }
+            }
+        }
+    } else if (warp == kWarpMma) {
+        // ================= MMA issue (one lane) =================
+        Ring rp, rb;
+        uint32_t acc_phase = 0;
+        constexpr uint32_t idesc = ptx::make_idesc_nvf4(BM, BN);
+        for (uint32_t tile = blockIdx.x; tile < num_tiles && ok; tile += gridDim.x) {
+            if (!ptx::mbar_wait(tmem_empty, acc_phase ^ 1, abort_flag)) { give_up(1); break; }
+            ptx::tcgen05_fence_after_sync();
+            for (uint32_t kb = 0; kb < num_kb; ++kb) {
+                if (!ptx::mbar_wait(p_full + rp.slot, rp.phase, abort_flag) ||
+                    !ptx::mbar_wait(b_ready + rb.slot, rb.phase, abort_flag) ||
+                    !ptx::mbar_wait(b_full + rb.slot, rb.phase, abort_flag)) { give_up(1); break; }
+                ptx::tcgen05_fence_after_sync();
+                if (lane == 0) {
+                    const uint32_t sfa0 = smem + kOffSFA0 + rp.slot * kSlotSFA;
+                    const uint32_t sfa1 = smem + kOffSFA1 + rp.slot * kSlotSFA;
+                    const uint32_t sfb = smem + kOffSFB + rb.slot * kSlotSFB;
+#pragma unroll
+                    for (uint32_t a = 0; a < kKAtoms; ++a) {
+                        ptx::tcgen05_cp_32x128b_warpx4(tmem_base + kColSFA0 + 4 * a,
+                                                       ptx::make_smem_desc(sfa0 + a * 512, 128, ptx::kSwizzleNone));
+                        if constexpr (kResidual)
+                            ptx::tcgen05_cp_32x128b_warpx4(tmem_base + kColSFA1 + 4 * a,
+                                                           ptx::make_smem_desc(sfa1 + a * 512, 128, ptx::kSwizzleNone));
+#pragma unroll
+                        for (uint32_t i = 0; i < BN / 128; ++i)
+                            ptx::tcgen05_cp_32x128b_warpx4(
+                                tmem_base + kColSFB + 4 * (a * (BN / 128) + i),
+                                ptx::make_smem_desc(sfb + (a * (BN / 128) + i) * 512, 128, ptx::kSwizzleNone));
+                    }
+                    const uint32_t a0 = smem + kOffA0 + rp.slot * kSlotA0;
+                    const uint32_t a1 = smem + kOffA1 + rp.slot * kSlotA0;
+                    const uint32_t b = smem + kOffB + rb.slot * kSlotB;
+#pragma unroll
+                    for (uint32_t a = 0; a < kKAtoms; ++a) {
+                        // 64 K elements = 32 bytes further along each 64-byte swizzled row
+                        const uint64_t desc_b = ptx::make_smem_desc(b + a * 32, 512, ptx::kSwizzle64B);
+                        ptx::tcgen05_mma_nvf4(tmem_base + kColAcc, ptx::make_smem_desc(a0 + a * 32, 512, ptx::kSwizzle64B),
+                                              desc_b, idesc, tmem_base + kColSFA0 + 4 * a,
+                                              tmem_base + kColSFB + 4 * a * (BN / 128), (kb | a) != 0 ? 1u : 0u);
+                        if constexpr (kResidual)
+                            ptx::tcgen05_mma_nvf4(tmem_base + kColAcc,
+                                                  ptx::make_smem_desc(a1 + a * 32, 512, ptx::kSwizzle64B), desc_b, idesc,
+                                                  tmem_base + kColSFA1 + 4 * a,
+                                                  tmem_base + kColSFB + 4 * a * (BN / 128), 1u);
+                    }
+                    ptx::tcgen05_commit(p_empty + rp.slot);
+                    ptx::tcgen05_commit(b_empty + rb.slot);
+                    if (kb == num_kb - 1) ptx::tcgen05_commit(tmem_full);
+                }
+                __syncwarp();
+                rp.advance<kDepthP>();
+                rb.advance<kDepthB>();
+            }
+            acc_phase ^= 1;
+        }
+    } else if (warp == kWarpSfb) {
+        // ================= SFB transpose into tensor-memory-copy order =================
+        // TMA lands each 128-row atom as 128 consecutive words (row r at word r); the
+        // copy wants row r at word (r % 32) * 4 + r / 32.
+        Ring rb;
+        for (uint32_t tile = blockIdx.x; tile < num_tiles && ok; tile += gridDim.x) {
+            for (uint32_t kb = 0; kb < num_kb; ++kb) {
+                if (!ptx::mbar_wait(b_full + rb.slot, rb.phase, abort_flag)) { give_up(1); break; }
+                const uint32_t base = smem + kOffSFB + rb.slot * kSlotSFB;
+#pragma unroll
+                for (uint32_t i = 0; i < kKAtoms * (BN / 128); ++i) {
+                    const uint32_t atom = base + i * 512;
+                    const uint32_t v0 = ptx::lds32(atom + (lane) * 4);
+                    const uint32_t v1 = ptx::lds32(atom + (32 + lane) * 4);
+                    const uint32_t v2 = ptx::lds32(atom + (64 + lane) * 4);
+                    const uint32_t v3 = ptx::lds32(atom + (96 + lane) * 4);
+                    __syncwarp();
+                    ptx::sts128(atom + lane * 16, v0, v1, v2, v3);
+                }
+                ptx::fence_proxy_async_smem();
+                __syncwarp();
+                if (lane == 0) ptx::mbar_arrive(b_ready + rb.slot);
+                rb.advance<kDepthB>();
+            }
+        }
+    } else if (warp >= kWarpEpi0 && warp < kWarpEpi0 + kNumEpiWarps) {
+        // ================= epilogue: TMEM -> x G_W -> BF16 -> global =================
+        const uint32_t quad = warp & 3;                  // TMEM lane quadrant of this warp
+        uint32_t acc_phase = 0;
+        for (uint32_t tile = blockIdx.x; tile < num_tiles && ok; tile += gridDim.x) {
+            uint32_t m_blk, n_blk;
+            tile_coords(tile, num_m, num_n, p.group_m, m_blk, n_blk);
+            const int32_t e = max(0, __ldg(p.m_indices + m_blk * BM));
+            const float g = __ldg(p.gw + e);
+            if (!ptx::mbar_wait(tmem_full, acc_phase, abort_flag)) { give_up(1); break; }
+            ptx::tcgen05_fence_after_sync();
+            const uint32_t row = m_blk * BM + quad * 32 + lane;
+            __nv_bfloat16* drow = p.d + static_cast<int64_t>(row) * p.ldd + n_blk * BN;
+#pragma unroll 1
+            for (uint32_t c = 0; c < BN; c += 32) {
+                uint32_t v[32];
+                ptx::tmem_ld_32x32b_x32(tmem_base + ((quad * 32) << 16) + kColAcc + c, v);
+                ptx::tmem_ld_wait();
+                {
+                    uint32_t o[16];
+#pragma unroll
+                    for (int i = 0; i < 16; ++i) {
+                        const __nv_bfloat162 h = __floats2bfloat162_rn(__uint_as_float(v[2 * i]) * g,
+                                                                       __uint_as_float(v[2 * i + 1]) * g);
+                        o[i] = *reinterpret_cast<const uint32_t*>(&h);
+                    }
+                    uint4* dst = reinterpret_cast<uint4*>(drow + c);
+#pragma unroll
+                    for (int i = 0; i < 4; ++i) dst[i] = make_uint4(o[4 * i], o[4 * i + 1], o[4 * i + 2], o[4 * i + 3]);
+                }
+            }
+            ptx::tcgen05_fence_before_sync();
+            __syncwarp();
+            if (lane == 0) ptx::mbar_arrive(tmem_empty);
+            acc_phase ^= 1;
+        }
+    } else if (warp >= kWarpXform0) {
+        // ================= transform: Algorithm 1 on every activation tile =================
+        const uint32_t t = threadIdx.x - kWarpXform0 * 32;
+        Ring ra, rp;
+        for (uint32_t tile = blockIdx.x; tile < num_tiles && ok; tile += gridDim.x) {
+            for (uint32_t kb = 0; kb < num_kb; ++kb) {
+                if (!ptx::mbar_wait(a_full + ra.slot, ra.phase, abort_flag) ||
+                    !ptx::mbar_wait(p_empty + rp.slot, rp.phase ^ 1, abort_flag)) { give_up(1); break; }
+                xform::transform_tile<BM, BK, kXformThreads, kResidual>(
+                    smem + kOffA + ra.slot * kSlotA, smem + kOffA0 + rp.slot * kSlotA0, smem + kOffA1 + rp.slot * kSlotA0,
+                    smem + kOffSFA0 + rp.slot * kSlotSFA, smem + kOffSFA1 + rp.slot * kSlotSFA, t);
+                ptx::fence_proxy_async_smem();
+                __syncwarp();
+                if (lane == 0) {
+                    ptx::mbar_arrive(p_full + rp.slot);
+                    ptx::mbar_arrive(a_empty + ra.slot);
+                }
+                ra.advance<kDepthA>();
+                rp.advance<kDepthP>();
+            }
+        }
+    }
+
+    // teardown: everyone meets here, on the normal path and after a timeout alike
+    ptx::tcgen05_fence_before_sync();
+    __syncthreads();
+    if (warp == kWarpMma) {
+        ptx::tcgen05_fence_after_sync();
+        ptx::tmem_dealloc<kTmemCols>(tmem_base);
+    }
+}
+
+template <uint32_t BN, uint32_t kXformWarps, bool kResidual>
+int launch_variant(const void* a, int64_t lda, const void* b, const void* sfb, int M, int N, int K, int E,
+                   const Params& p, int num_sms, cudaStream_t stream)
+{
+    using C = Cfg<BN>;
+    CUtensorMap tm_a, tm_b, tm_sfb;
+    int rc = host::encode_tensor_map_2d(&tm_a, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, a, K, M, lda * 2, 64, BM,
+                                        CU_TENSOR_MAP_SWIZZLE_128B);
+    if (rc) return rc;
+    rc = host::encode_tensor_map_2d(&tm_b, CU_TENSOR_MAP_DATA_TYPE_UINT8, 1, b, K / 2, static_cast<uint64_t>(E) * N,
+                                    K / 2, BK / 2, BN, CU_TENSOR_MAP_SWIZZLE_64B);
+    if (rc) return rc;
+    rc = host::encode_tensor_map_2d(&tm_sfb, CU_TENSOR_MAP_DATA_TYPE_INT32, 4, sfb, N,
+                                    static_cast<uint64_t>(E) * (K / 64), static_cast<uint64_t>(N) * 4, BN, kKAtoms,
+                                    CU_TENSOR_MAP_SWIZZLE_NONE);
+    if (rc) return rc;
+    auto kernel = gemm_normal_kernel<BN, kXformWarps, kResidual>;
+    static bool attr_set[host::kMaxDevices] = {};
+    int dev = 0;
+    NVFP4_CUDA_CHECK(cudaGetDevice(&dev));
+    if (!attr_set[dev]) {
+        NVFP4_CUDA_CHECK(cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, C::kSmemAlloc));
+        attr_set[dev] = true;
+    }
+    const int num_tiles = (M / static_cast<int>(BM)) * (N / static_cast<int>(BN));
+    const int grid = num_tiles < num_sms ? num_tiles : num_sms;
+    kernel<<<grid, (kWarpXform0 + kXformWarps) * 32, C::kSmemAlloc, stream>>>(tm_a, tm_b, tm_sfb, p);
+    NVFP4_CUDA_CHECK(cudaGetLastError());
+    return NVFP4_OK;
+}
+
+template <uint32_t BN>
+int launch_for_bn(const void* a, int64_t lda, const void* b, const void* sfb, int M, int N, int K, int E,
+                  const Params& p, bool residual, int xform_warps, int num_sms, cudaStream_t stream)
+{
+    if (xform_warps == 16)
+        return residual ? launch_variant<BN, 16, true>(a, lda, b, sfb, M, N, K, E, p, num_sms, stream)
+                        : launch_variant<BN, 16, false>(a, lda, b, sfb, M, N, K, E, p, num_sms, stream);
+    return residual ? launch_variant<BN, 8, true>(a, lda, b, sfb, M, N, K, E, p, num_sms, stream)
+                    : launch_variant<BN, 8, false>(a, lda, b, sfb, M, N, K, E, p, num_sms, stream);
+}
+
+}  // namespace
+
+// Validated arguments in, launch out.  See nvfp4_grouped_gemm_contiguous for meanings.
+int launch_gemm_normal(const void* a, int64_t lda, const void* b, const void* sfb, const float* gw, void* d,
+                       int64_t ldd, const int32_t* m_indices, int M, int N, int K, int E, bool residual,
+                       int xform_warps, int group_m, int num_sms, int32_t* status, cudaStream_t stream)
+{
+    Params p;
+    p.gw = gw;
+    p.m_indices = m_indices;
+    p.d = static_cast<__nv_bfloat16*>(d);
+    p.ldd = ldd;
+    p.m = M; p.n = N; p.k = K; p.num_experts = E;
+    p.group_m = group_m > 0 ? group_m : 8;
+    p.status = status;
+    if (N % 256 == 0) return launch_for_bn<256>(a, lda, b, sfb, M, N, K, E, p, residual, xform_warps, num_sms, stream);
+    return launch_for_bn<128>(a, lda, b, sfb, M, N, K, E, p, residual, xform_warps, num_sms, stream);
+}
+
+}  // namespace nvfp4

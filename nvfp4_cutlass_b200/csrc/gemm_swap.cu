@@ -1,0 +1,371 @@
+// Grouped dual-NVFP4 GEMM, decode orientation ("swap-AB"): 128 weight rows on the
+// MMA M axis, a small token tile (16 / 32 / 64 rows) on the MMA N axis.
+//
+// In this regime every expert sees a handful of tokens, so the job is to stream
+// each active expert's FP4 weights from HBM exactly once at full bandwidth: a deep
+// TMA ring of weight tiles (128 rows x 256 K = 16 KB + 2 KB of scales per slot) feeds
+// tiny MMAs, while the token tile of the same K block is transformed by Algorithm 1
+// into the MMA's B operand.  Two accumulator stages in tensor memory let the
+// epilogue of one tile overlap the mainloop of the next.
+//
+//   W ring  (FP4 weights + their scales)   TMA warp        -> scale-transpose warp, MMA warp
+//   A ring  (BF16 token rows)              TMA warp        -> transform warps
+//   P ring  (A0, A1, SFT0, SFT1)           transform warps -> MMA warp
+//
+// Counterpart in the reference: include/nvfp4_gemm/impls/sm100_bf16_dual_nvfp4_gemm_swap_ab.cuh,
+// epilogue/sm100_store_cd_swap_ab.cuh, src/kernels/sm100_bf16_dual_nvfp4_gemm.hpp:489-632.
+#include <cuda_bf16.h>
+
+#include "host_common.hpp"
+#include "launchers.hpp"
+#include "transform.cuh"
+
+namespace nvfp4 {
+namespace {
+
+constexpr uint32_t BW = 128;                         // weight rows per tile (MMA M)
+constexpr uint32_t kWarpTma = 0, kWarpMma = 1, kWarpSf = 2, kWarpEpi0 = 4, kNumEpiWarps = 4, kWarpXform0 = 8;
+constexpr uint32_t kXformWarps = 8, kXformThreads = kXformWarps * 32, kThreads = (kWarpXform0 + kXformWarps) * 32;
+constexpr uint32_t kSmemBudget = 232448 - 1024;      // opt-in maximum minus alignment slack
+
+template <uint32_t T, uint32_t BK>
+struct Cfg {
+    static constexpr uint32_t kAtoms = BK / 64;
+    static constexpr uint32_t kSlotW = BW * BK / 2, kSlotSFW = kAtoms * 512;
+    static constexpr uint32_t kSlotA = T * BK * 2;
+    static constexpr uint32_t kSlotA0 = (T * BK / 2 + 1023u) & ~1023u, kSlotSFT = kAtoms * 512;
+    static constexpr uint32_t kDepthA = T >= 64 ? 2 : 3, kDepthP = 2;
+    static constexpr uint32_t kFixed = kDepthA * kSlotA + kDepthP * (2 * kSlotA0 + 2 * kSlotSFT) + 512;
+    static constexpr uint32_t kDepthWRaw = (kSmemBudget - kFixed) / (kSlotW + kSlotSFW);
+    static constexpr uint32_t kDepthW = kDepthWRaw > 12 ? 12 : kDepthWRaw;
+    static constexpr uint32_t kOffW = 0;
+    static constexpr uint32_t kOffA = kOffW + kDepthW * kSlotW;
+    static constexpr uint32_t kOffA0 = kOffA + kDepthA * kSlotA;
+    static constexpr uint32_t kOffA1 = kOffA0 + kDepthP * kSlotA0;
+    static constexpr uint32_t kOffSFW = kOffA1 + kDepthP * kSlotA0;
+    static constexpr uint32_t kOffSFT0 = kOffSFW + kDepthW * kSlotSFW;
+    static constexpr uint32_t kOffSFT1 = kOffSFT0 + kDepthP * kSlotSFT;
+    static constexpr uint32_t kOffBars = kOffSFT1 + kDepthP * kSlotSFT;
+    static constexpr uint32_t kNumBars = 3 * kDepthW + 2 * kDepthA + 2 * kDepthP + 4;
+    static constexpr uint32_t kSmemAlloc = kOffBars + kNumBars * 8 + 16 + 1024;
+    static_assert(kDepthW >= 3, "weight ring too shallow");
+    static_assert(kSmemAlloc <= 232448, "shared memory budget");
+    // tensor memory: two accumulator stages of T columns, then the three scale groups
+    static constexpr uint32_t kAccStride = T < 32 ? 32 : T;
+    static constexpr uint32_t kColSFW = 2 * kAccStride, kColSFT0 = kColSFW + 4 * kAtoms, kColSFT1 = kColSFT0 + 4 * kAtoms;
+    static constexpr uint32_t kColsUsed = kColSFT1 + 4 * kAtoms;
+    static constexpr uint32_t kTmemCols = kColsUsed <= 64 ? 64 : (kColsUsed <= 128 ? 128 : 256);
+    static constexpr uint64_t kSwizzle = BK == 256 ? ptx::kSwizzle128B : ptx::kSwizzle64B;
+    static constexpr uint32_t kSBO = 8 * (BK / 2);   // eight rows of one swizzle span
+};
+
+struct Params {
+    const float* gw;
+    const int32_t* m_indices;
+    __nv_bfloat16* d;
+    int64_t ldd;
+    uint32_t m, n, k;
+    int32_t* status;
+};
+
+struct Ring {
+    uint32_t slot = 0, phase = 0;
+    template <uint32_t kDepth>
+    __device__ __forceinline__ void advance()
+    {
+        if (++slot == kDepth) { slot = 0; phase ^= 1; }
+    }
+};
+
+template <uint32_t T, uint32_t BK, bool kResidual>
+__global__ void __launch_bounds__(kThreads, 1)
+gemm_swap_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constant__ CUtensorMap tm_w,
+                 const __grid_constant__ CUtensorMap tm_sfw, const Params p)
+{
+    using C = Cfg<T, BK>;
+    extern __shared__ uint8_t smem_raw[];
+    const uint32_t smem = (ptx::smem_u32(smem_raw) + 1023u) & ~1023u;
+    uint8_t* smem_gen = smem_raw + (smem - ptx::smem_u32(smem_raw));
+
+    uint64_t* bars = reinterpret_cast<uint64_t*>(smem_gen + C::kOffBars);
+    uint64_t* w_full = bars;
+    uint64_t* w_ready = w_full + C::kDepthW;
+    uint64_t* w_empty = w_ready + C::kDepthW;
+    uint64_t* a_full = w_empty + C::kDepthW;
+    uint64_t* a_empty = a_full + C::kDepthA;
+    uint64_t* p_full = a_empty + C::kDepthA;
+    uint64_t* p_empty = p_full + C::kDepthP;
+    uint64_t* tmem_full = p_empty + C::kDepthP;      // [2]
+    uint64_t* tmem_empty = tmem_full + 2;            // [2]
+    uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(tmem_empty + 2);
+    volatile uint32_t* abort_flag = tmem_slot + 1;
+
+    const uint32_t warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    if (threadIdx.x == 0) {
+        for (uint32_t i = 0; i < C::kDepthW; ++i) {
+            ptx::mbar_init(w_full + i, 1);
+            ptx::mbar_init(w_ready + i, 1);
+            ptx::mbar_init(w_empty + i, 1);
+        }
+        for (uint32_t i = 0; i < C::kDepthA; ++i) { ptx::mbar_init(a_full + i, 1); ptx::mbar_init(a_empty + i, kXformWarps); }
+        for (uint32_t i = 0; i < C::kDepthP; ++i) { ptx::mbar_init(p_full + i, kXformWarps); ptx::mbar_init(p_empty + i, 1); }
+        for (uint32_t i = 0; i < 2; ++i) { ptx::mbar_init(tmem_full + i, 1); ptx::mbar_init(tmem_empty + i, kNumEpiWarps); }
+        *abort_flag = 0;
+        ptx::fence_mbar_init();
+        ptx::prefetch_tensormap(&tm_a);
+        ptx::prefetch_tensormap(&tm_w);
+        ptx::prefetch_tensormap(&tm_sfw);
+    }
+    if (warp == kWarpMma) ptx::tmem_alloc<C::kTmemCols>(tmem_slot);
+    ptx::tcgen05_fence_before_sync();
+    __syncthreads();
+    ptx::tcgen05_fence_after_sync();
+    const uint32_t tmem_base = *tmem_slot;
+
+    // tiles: all weight-row blocks of one token block are neighbours, so the CTAs of a
+    // wave share that token block's activations through L2 while streaming disjoint weights
+    const uint32_t num_n = p.n / BW, num_kb = p.k / BK;
+    const uint32_t num_tiles = (p.m / T) * num_n;
+    bool ok = true;
+    auto give_up = [&](uint32_t code) {
+        *abort_flag = 1;
+        if (p.status != nullptr) atomicOr(p.status, static_cast<int32_t>(code));
+        ok = false;
+    };
+
+    if (warp == kWarpTma) {
+        if (lane == 0) {
+            Ring rw, ra;
+            const uint64_t stream_once = ptx::l2_policy_evict_first();
+            for (uint32_t tile = blockIdx.x; tile < num_tiles && ok; tile += gridDim.x) {
+                const uint32_t m_blk = tile / num_n, n_blk = tile % num_n;
+                const int32_t e = max(0, __ldg(p.m_indices + m_blk * T));
+                for (uint32_t kb = 0; kb < num_kb; ++kb) {
+                    if (!ptx::mbar_wait(w_empty + rw.slot, rw.phase ^ 1, abort_flag)) { give_up(1); break; }
+                    ptx::mbar_arrive_expect_tx(w_full + rw.slot, C::kSlotW + C::kSlotSFW);
+                    ptx::tma_load_2d_hint(smem_gen + C::kOffW + rw.slot * C::kSlotW, &tm_w, w_full + rw.slot, kb * (BK / 2),
+                                          e * p.n + n_blk * BW, stream_once);
+                    ptx::tma_load_2d_hint(smem_gen + C::kOffSFW + rw.slot * C::kSlotSFW, &tm_sfw, w_full + rw.slot,
+                                          n_blk * BW, e * (p.k / 64) + kb * C::kAtoms, stream_once);
+                    rw.advance<C::kDepthW>();
+
+                    if (!ptx::mbar_wait(a_empty + ra.slot, ra.phase ^ 1, abort_flag)) { give_up(1); break; }
+                    ptx::mbar_arrive_expect_tx(a_full + ra.slot, C::kSlotA);
+#pragma unroll
+                    for (uint32_t box = 0; box < BK / 64; ++box)
+                        ptx::tma_load_2d(smem_gen + C::kOffA + ra.slot * C::kSlotA + box * (T * 128), &tm_a,
+                                         a_full + ra.slot, kb * BK + box * 64, m_blk * T);
+                    ra.advance<C::kDepthA>();
+                }
+            }
+        }
+    } else if (warp == kWarpMma) {
+        Ring rw, rp;
+        uint32_t it = 0;
+        constexpr uint32_t idesc = ptx::make_idesc_nvf4(BW, T);
+        for (uint32_t tile = blockIdx.x; tile < num_tiles && ok; tile += gridDim.x, ++it) {
+            const uint32_t acc = it & 1, acc_phase = (it >> 1) & 1;
+            if (!ptx::mbar_wait(tmem_empty + acc, acc_phase ^ 1, abort_flag)) { give_up(1); break; }
+            ptx::tcgen05_fence_after_sync();
+            const uint32_t tmem_acc = tmem_base + acc * C::kAccStride;
+            for (uint32_t kb = 0; kb < num_kb; ++kb) {
+                if (!ptx::mbar_wait(p_full + rp.slot, rp.phase, abort_flag) ||
+                    !ptx::mbar_wait(w_ready + rw.slot, rw.phase, abort_flag) ||
+                    !ptx::mbar_wait(w_full + rw.slot, rw.phase, abort_flag)) { give_up(1); break; }
+                ptx::tcgen05_fence_after_sync();
+                if (lane == 0) {
+                    const uint32_t sfw = smem + C::kOffSFW + rw.slot * C::kSlotSFW;
+                    const uint32_t sft0 = smem + C::kOffSFT0 + rp.slot * C::kSlotSFT;
+                    const uint32_t sft1 = smem + C::kOffSFT1 + rp.slot * C::kSlotSFT;
+#pragma unroll
+                    for (uint32_t a = 0; a < C::kAtoms; ++a) {
+                        ptx::tcgen05_cp_32x128b_warpx4(tmem_base + C::kColSFW + 4 * a,
+                                                       ptx::make_smem_desc(sfw + a * 512, 128, ptx::kSwizzleNone));
+                        ptx::tcgen05_cp_32x128b_warpx4(tmem_base + C::kColSFT0 + 4 * a,
+                                                       ptx::make_smem_desc(sft0 + a * 512, 128, ptx::kSwizzleNone));
+                        if constexpr (kResidual)
+                            ptx::tcgen05_cp_32x128b_warpx4(tmem_base + C::kColSFT1 + 4 * a,
+                                                           ptx::make_smem_desc(sft1 + a * 512, 128, ptx::kSwizzleNone));
+                    }
+                    const uint32_t w = smem + C::kOffW + rw.slot * C::kSlotW;
+                    const uint32_t a0 = smem + C::kOffA0 + rp.slot * C::kSlotA0;
+                    const uint32_t a1 = smem + C::kOffA1 + rp.slot * C::kSlotA0;
+#pragma unroll
+                    for (uint32_t a = 0; a < C::kAtoms; ++a) {
+                        const uint64_t desc_w = ptx::make_smem_desc(w + a * 32, C::kSBO, C::kSwizzle);
+                        ptx::tcgen05_mma_nvf4(tmem_acc, desc_w, ptx::make_smem_desc(a0 + a * 32, C::kSBO, C::kSwizzle), idesc,
+                                              tmem_base + C::kColSFW + 4 * a, tmem_base + C::kColSFT0 + 4 * a,
+                                              (kb | a) != 0 ? 1u : 0u);
+                        if constexpr (kResidual)
+                            ptx::tcgen05_mma_nvf4(tmem_acc, desc_w, ptx::make_smem_desc(a1 + a * 32, C::kSBO, C::kSwizzle),
+                                                  idesc, tmem_base + C::kColSFW + 4 * a, tmem_base + C::kColSFT1 + 4 * a, 1u);
+                    }
+                    ptx::tcgen05_commit(p_empty + rp.slot);
+                    ptx::tcgen05_commit(w_empty + rw.slot);
+                    if (kb == num_kb - 1) ptx::tcgen05_commit(tmem_full + acc);
+                }
+                __syncwarp();
+                rp.advance<C::kDepthP>();
+                rw.advance<C::kDepthW>();
+            }
+        }
+    } else if (warp == kWarpSf) {
+        // weight scales: row r of each 128-row atom from word r to word (r % 32) * 4 + r / 32
+        Ring rw;
+        for (uint32_t tile = blockIdx.x; tile < num_tiles && ok; tile += gridDim.x) {
+            for (uint32_t kb = 0; kb < num_kb; ++kb) {
+                if (!ptx::mbar_wait(w_full + rw.slot, rw.phase, abort_flag)) { give_up(1); break; }
+                const uint32_t base = smem + C::kOffSFW + rw.slot * C::kSlotSFW;
+#pragma unroll
+                for (uint32_t i = 0; i < C::kAtoms; ++i) {
+                    const uint32_t atom = base + i * 512;
+                    const uint32_t v0 = ptx::lds32(atom + lane * 4);
+                    const uint32_t v1 = ptx::lds32(atom + (32 + lane) * 4);
+                    const uint32_t v2 = ptx::lds32(atom + (64 + lane) * 4);
+                    const uint32_t v3 = ptx::lds32(atom + (96 + lane) * 4);
+                    __syncwarp();
+                    ptx::sts128(atom + lane * 16, v0, v1, v2, v3);
+                }
+                ptx::fence_proxy_async_smem();
+                __syncwarp();
+                if (lane == 0) ptx::mbar_arrive(w_ready + rw.slot);
+                rw.advance<C::kDepthW>();
+            }
+        }
+    } else if (warp >= kWarpEpi0 && warp < kWarpEpi0 + kNumEpiWarps) {
+        // accumulator lane = weight row n, column = token t: D[m0 + t, n0 + lane] -- for a
+        // fixed token the 32 lanes of a warp write 32 consecutive BF16
+        const uint32_t quad = warp & 3;
+        uint32_t it = 0;
+        for (uint32_t tile = blockIdx.x; tile < num_tiles && ok; tile += gridDim.x, ++it) {
+            const uint32_t acc = it & 1, acc_phase = (it >> 1) & 1;
+            const uint32_t m_blk = tile / num_n, n_blk = tile % num_n;
+            const int32_t e = max(0, __ldg(p.m_indices + m_blk * T));
+            const float g = __ldg(p.gw + e);
+            if (!ptx::mbar_wait(tmem_full + acc, acc_phase, abort_flag)) { give_up(1); break; }
+            ptx::tcgen05_fence_after_sync();
+            __nv_bfloat16* dcol = p.d + static_cast<int64_t>(m_blk * T) * p.ldd + n_blk * BW + quad * 32 + lane;
+            const uint32_t taddr = tmem_base + ((quad * 32) << 16) + acc * C::kAccStride;
+            if constexpr (T == 16) {
+                uint32_t v[16];
+                ptx::tmem_ld_32x32b_x16(taddr, v);
+                ptx::tmem_ld_wait();
+                ptx::tcgen05_fence_before_sync();
+                __syncwarp();
+                if (lane == 0) ptx::mbar_arrive(tmem_empty + acc);
+#pragma unroll
+                for (uint32_t t = 0; t < 16; ++t) dcol[static_cast<int64_t>(t) * p.ldd] = __float2bfloat16_rn(__uint_as_float(v[t]) * g);
+            } else {
+#pragma unroll 1
+                for (uint32_t c = 0; c < T; c += 32) {
+                    uint32_t v[32];
+                    ptx::tmem_ld_32x32b_x32(taddr + c, v);
+                    ptx::tmem_ld_wait();
+                    if (c + 32 == T) {
+                        ptx::tcgen05_fence_before_sync();
+                        __syncwarp();
+                        if (lane == 0) ptx::mbar_arrive(tmem_empty + acc);
+                    }
+#pragma unroll
+                    for (uint32_t t = 0; t < 32; ++t)
+                        dcol[static_cast<int64_t>(c + t) * p.ldd] = __float2bfloat16_rn(__uint_as_float(v[t]) * g);
+                }
+            }
+        }
+    } else if (warp >= kWarpXform0) {
+        const uint32_t t = threadIdx.x - kWarpXform0 * 32;
+        Ring ra, rp;
+        for (uint32_t tile = blockIdx.x; tile < num_tiles && ok; tile += gridDim.x) {
+            for (uint32_t kb = 0; kb < num_kb; ++kb) {
+                if (!ptx::mbar_wait(a_full + ra.slot, ra.phase, abort_flag) ||
+                    !ptx::mbar_wait(p_empty + rp.slot, rp.phase ^ 1, abort_flag)) { give_up(1); break; }
+                xform::transform_tile<T, BK, kXformThreads, kResidual>(
+                    smem + C::kOffA + ra.slot * C::kSlotA, smem + C::kOffA0 + rp.slot * C::kSlotA0,
+                    smem + C::kOffA1 + rp.slot * C::kSlotA0, smem + C::kOffSFT0 + rp.slot * C::kSlotSFT,
+                    smem + C::kOffSFT1 + rp.slot * C::kSlotSFT, t);
+                ptx::fence_proxy_async_smem();
+                __syncwarp();
+                if (lane == 0) {
+                    ptx::mbar_arrive(p_full + rp.slot);
+                    ptx::mbar_arrive(a_empty + ra.slot);
+                }
+                ra.advance<C::kDepthA>();
+                rp.advance<C::kDepthP>();
+            }
+        }
+    }
+
+    ptx::tcgen05_fence_before_sync();
+    __syncthreads();
+    if (warp == kWarpMma) {
+        ptx::tcgen05_fence_after_sync();
+        ptx::tmem_dealloc<C::kTmemCols>(tmem_base);
+    }
+}
+
+template <uint32_t T, uint32_t BK, bool kResidual>
+int launch_variant(const void* a, int64_t lda, const void* b, const void* sfb, int M, int N, int K, int E,
+                   const Params& p, int num_sms, cudaStream_t stream)
+{
+    using C = Cfg<T, BK>;
+    CUtensorMap tm_a, tm_w, tm_sfw;
+    int rc = host::encode_tensor_map_2d(&tm_a, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, a, K, M, lda * 2, 64, T,
+                                        CU_TENSOR_MAP_SWIZZLE_128B);
+    if (rc) return rc;
+    rc = host::encode_tensor_map_2d(&tm_w, CU_TENSOR_MAP_DATA_TYPE_UINT8, 1, b, K / 2, static_cast<uint64_t>(E) * N,
+                                    K / 2, BK / 2, BW, BK == 256 ? CU_TENSOR_MAP_SWIZZLE_128B : CU_TENSOR_MAP_SWIZZLE_64B);
+    if (rc) return rc;
+    rc = host::encode_tensor_map_2d(&tm_sfw, CU_TENSOR_MAP_DATA_TYPE_INT32, 4, sfb, N,
+                                    static_cast<uint64_t>(E) * (K / 64), static_cast<uint64_t>(N) * 4, BW, C::kAtoms,
+                                    CU_TENSOR_MAP_SWIZZLE_NONE);
+    if (rc) return rc;
+    auto kernel = gemm_swap_kernel<T, BK, kResidual>;
+    static bool attr_set[host::kMaxDevices] = {};
+    int dev = 0;
+    NVFP4_CUDA_CHECK(cudaGetDevice(&dev));
+    if (!attr_set[dev]) {
+        NVFP4_CUDA_CHECK(cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, C::kSmemAlloc));
+        attr_set[dev] = true;
+    }
+    const int num_tiles = (M / static_cast<int>(T)) * (N / static_cast<int>(BW));
+    const int grid = num_tiles < num_sms ? num_tiles : num_sms;
+    kernel<<<grid, kThreads, C::kSmemAlloc, stream>>>(tm_a, tm_w, tm_sfw, p);
+    NVFP4_CUDA_CHECK(cudaGetLastError());
+    return NVFP4_OK;
+}
+
+template <uint32_t T>
+int launch_for_tile(const void* a, int64_t lda, const void* b, const void* sfb, int M, int N, int K, int E,
+                    const Params& p, bool residual, int num_sms, cudaStream_t stream)
+{
+    if (K % 256 == 0)
+        return residual ? launch_variant<T, 256, true>(a, lda, b, sfb, M, N, K, E, p, num_sms, stream)
+                        : launch_variant<T, 256, false>(a, lda, b, sfb, M, N, K, E, p, num_sms, stream);
+    return residual ? launch_variant<T, 128, true>(a, lda, b, sfb, M, N, K, E, p, num_sms, stream)
+                    : launch_variant<T, 128, false>(a, lda, b, sfb, M, N, K, E, p, num_sms, stream);
+}
+
+}  // namespace
+
+// token_tile: rows per tile (16, 32 or 64); every expert's row range must start on a
+// multiple of it, which the caller guarantees through m_alignment % token_tile == 0.
+int launch_gemm_swap(const void* a, int64_t lda, const void* b, const void* sfb, const float* gw, void* d,
+                     int64_t ldd, const int32_t* m_indices, int M, int N, int K, int E, bool residual,
+                     int token_tile, int num_sms, int32_t* status, cudaStream_t stream)
+{
+    Params p;
+    p.gw = gw;
+    p.m_indices = m_indices;
+    p.d = static_cast<__nv_bfloat16*>(d);
+    p.ldd = ldd;
+    p.m = M; p.n = N; p.k = K;
+    p.status = status;
+    switch (token_tile) {
+        case 16: return launch_for_tile<16>(a, lda, b, sfb, M, N, K, E, p, residual, num_sms, stream);
+        case 32: return launch_for_tile<32>(a, lda, b, sfb, M, N, K, E, p, residual, num_sms, stream);
+        case 64: return launch_for_tile<64>(a, lda, b, sfb, M, N, K, E, p, residual, num_sms, stream);
+        default: return host::fail(NVFP4_E_INVALID_ARGUMENT, "token tile %d is not 16, 32 or 64", token_tile);
+    }
+}
+
+}  // namespace nvfp4

@@ -1,0 +1,24 @@
+// Internal launch functions behind the C ABI (arguments already validated).
+#pragma once
+#include <cstdint>
+#include <cuda_runtime.h>
+
+namespace nvfp4 {
+
+int launch_gemm_normal(const void* a, int64_t lda, const void* b, const void* sfb, const float* gw, void* d,
+                       int64_t ldd, const int32_t* m_indices, int M, int N, int K, int E, bool residual,
+                       int xform_warps, int group_m, int num_sms, int32_t* status, cudaStream_t stream);
+
+int launch_gemm_swap(const void* a, int64_t lda, const void* b, const void* sfb, const float* gw, void* d,
+                     int64_t ldd, const int32_t* m_indices, int M, int N, int K, int E, bool residual,
+                     int token_tile, int num_sms, int32_t* status, cudaStream_t stream);
+
+int launch_quantize_weight(const void* w, int w_dtype, int E, int N, int K, void* b, void* sfb, float* gw,
+                           cudaStream_t stream);
+
+int launch_debug_decompose(const void* a, int64_t lda, int M, int K, void* q0, void* q1, void* s0, void* s1,
+                           cudaStream_t stream);
+
+int launch_mma_peak(int iters, int num_sms, double* flops_per_launch, cudaStream_t stream);
+
+}  // namespace nvfp4

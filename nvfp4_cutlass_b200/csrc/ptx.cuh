@@ -1,0 +1,303 @@
+// Raw PTX for sm_100a: mbarrier, TMA (non-multicast only), tcgen05 (TMEM
+// allocation, block-scaled FP4 MMA, scale-factor copy, commit, load), proxy
+// fences and the FP4 / E4M3 converts.  Nothing here depends on CUTLASS or CuTe.
+//
+// Every wait in this file is bounded: a waiter that runs out of time reports it
+// and the caller unwinds, so a protocol bug ends as an error status, never as a
+// hung GPU.
+#pragma once
+#include <cstdint>
+#include <cuda.h>
+#include <cuda_runtime.h>
+
+namespace nvfp4::ptx {
+
+#define NVFP4_DEVICE __device__ __forceinline__
+
+NVFP4_DEVICE uint32_t smem_u32(const void* p) { return static_cast<uint32_t>(__cvta_generic_to_shared(p)); }
+NVFP4_DEVICE uint32_t lane_id() { uint32_t l; asm volatile("mov.u32 %0, %%laneid;" : "=r"(l)); return l; }
+
+NVFP4_DEVICE bool elect_one()
+{
+    uint32_t pred;
+    asm volatile(
+        "{\n .reg .pred p;\n elect.sync _|p, 0xffffffff;\n selp.u32 %0, 1, 0, p;\n}" : "=r"(pred));
+    return pred != 0;
+}
+
+// ---- mbarrier ---------------------------------------------------------------
+NVFP4_DEVICE void mbar_init(uint64_t* bar, uint32_t count)
+{
+    asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(smem_u32(bar)), "r"(count) : "memory");
+}
+NVFP4_DEVICE void fence_mbar_init() { asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory"); }
+NVFP4_DEVICE void mbar_arrive(uint64_t* bar)
+{
+    asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(smem_u32(bar)) : "memory");
+}
+NVFP4_DEVICE void mbar_arrive_expect_tx(uint64_t* bar, uint32_t bytes)
+{
+    asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(smem_u32(bar)), "r"(bytes)
+                 : "memory");
+}
+NVFP4_DEVICE bool mbar_try_wait(uint64_t* bar, uint32_t parity)
+{
+    uint32_t ok;
+    asm volatile(
+        "{\n .reg .pred p;\n mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n selp.u32 %0, 1, 0, p;\n}"
+        : "=r"(ok)
+        : "r"(smem_u32(bar)), "r"(parity)
+        : "memory");
+    return ok != 0;
+}
+
+// Clock budget of one wait (about a second at B200 clocks).  Legitimate waits
+// in these kernels last microseconds.
+constexpr long long kWaitBudgetCycles = 2000000000ll;
+
+// Returns false if the phase did not complete within the budget, or if another
+// thread of the CTA already gave up (`*abort_flag != 0`).
+NVFP4_DEVICE bool mbar_wait(uint64_t* bar, uint32_t parity, volatile uint32_t* abort_flag)
+{
+    if (mbar_try_wait(bar, parity)) return true;
+    const long long t0 = clock64();
+    for (;;) {
+#pragma unroll 1
+        for (int i = 0; i < 32; ++i)
+            if (mbar_try_wait(bar, parity)) return true;
+        if (*abort_flag != 0 || clock64() - t0 > kWaitBudgetCycles) return false;
+    }
+}
+
+// ---- proxy fences -------------------------------------------------------------
+// Generic-proxy shared-memory writes must be made visible to the async proxy
+// (TMA stores, tcgen05.mma / tcgen05.cp operand reads) before the hand-off.
+NVFP4_DEVICE void fence_proxy_async_smem() { asm volatile("fence.proxy.async.shared::cta;" ::: "memory"); }
+
+// ---- TMA (cp.async.bulk.tensor, never multicast) -------------------------------
+NVFP4_DEVICE void prefetch_tensormap(const CUtensorMap* map)
+{
+    asm volatile("prefetch.tensormap [%0];" ::"l"(reinterpret_cast<uint64_t>(map)) : "memory");
+}
+NVFP4_DEVICE void tma_load_2d(void* smem_dst, const CUtensorMap* map, uint64_t* bar, int32_t c0, int32_t c1)
+{
+    asm volatile(
+        "cp.async.bulk.tensor.2d.shared::cluster.global.tile.mbarrier::complete_tx::bytes [%0], [%1, {%3, %4}], [%2];"
+        ::"r"(smem_u32(smem_dst)), "l"(reinterpret_cast<uint64_t>(map)), "r"(smem_u32(bar)), "r"(c0), "r"(c1)
+        : "memory");
+}
+NVFP4_DEVICE void tma_load_2d_hint(void* smem_dst, const CUtensorMap* map, uint64_t* bar, int32_t c0, int32_t c1,
+                                   uint64_t policy)
+{
+    asm volatile(
+        "cp.async.bulk.tensor.2d.shared::cluster.global.tile.mbarrier::complete_tx::bytes.L2::cache_hint "
+        "[%0], [%1, {%3, %4}], [%2], %5;"
+        ::"r"(smem_u32(smem_dst)), "l"(reinterpret_cast<uint64_t>(map)), "r"(smem_u32(bar)), "r"(c0), "r"(c1),
+        "l"(policy)
+        : "memory");
+}
+NVFP4_DEVICE void tma_store_2d(const CUtensorMap* map, const void* smem_src, int32_t c0, int32_t c1)
+{
+    asm volatile("cp.async.bulk.tensor.2d.global.shared::cta.tile.bulk_group [%0, {%2, %3}], [%1];"
+                 ::"l"(reinterpret_cast<uint64_t>(map)), "r"(smem_u32(smem_src)), "r"(c0), "r"(c1)
+                 : "memory");
+}
+NVFP4_DEVICE void tma_store_commit() { asm volatile("cp.async.bulk.commit_group;" ::: "memory"); }
+template <int kPending>
+NVFP4_DEVICE void tma_store_wait_read() { asm volatile("cp.async.bulk.wait_group.read %0;" ::"n"(kPending) : "memory"); }
+template <int kPending>
+NVFP4_DEVICE void tma_store_wait_all() { asm volatile("cp.async.bulk.wait_group %0;" ::"n"(kPending) : "memory"); }
+
+NVFP4_DEVICE uint64_t l2_policy_evict_first()
+{
+    uint64_t p;
+    asm volatile("createpolicy.fractional.L2::evict_first.b64 %0, 1.0;" : "=l"(p));
+    return p;
+}
+NVFP4_DEVICE uint64_t l2_policy_evict_last()
+{
+    uint64_t p;
+    asm volatile("createpolicy.fractional.L2::evict_last.b64 %0, 1.0;" : "=l"(p));
+    return p;
+}
+
+// ---- programmatic dependent launch -----------------------------------------------
+NVFP4_DEVICE void grid_dependency_wait() { asm volatile("griddepcontrol.wait;" ::: "memory"); }
+NVFP4_DEVICE void grid_launch_dependents() { asm volatile("griddepcontrol.launch_dependents;" ::: "memory"); }
+
+// ---- tensor memory -----------------------------------------------------------------
+// TMEM address: lane in bits [31:16], column in bits [15:0].
+template <uint32_t kCols>
+NVFP4_DEVICE void tmem_alloc(uint32_t* smem_result)
+{
+    static_assert(kCols >= 32 && kCols <= 512 && (kCols & (kCols - 1)) == 0, "TMEM columns: power of two in [32, 512]");
+    asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_u32(smem_result)),
+                 "n"(kCols)
+                 : "memory");
+    asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
+}
+template <uint32_t kCols>
+NVFP4_DEVICE void tmem_dealloc(uint32_t taddr)
+{
+    asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(taddr), "n"(kCols) : "memory");
+}
+NVFP4_DEVICE void tcgen05_fence_before_sync() { asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory"); }
+NVFP4_DEVICE void tcgen05_fence_after_sync() { asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory"); }
+
+// All earlier tcgen05.mma / tcgen05.cp of this thread arrive (once) on `bar` when they retire.
+NVFP4_DEVICE void tcgen05_commit(uint64_t* bar)
+{
+    asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(smem_u32(bar))
+                 : "memory");
+}
+
+// 32 rows x 128 bit from shared memory, replicated into the four 32-lane
+// quadrants: one 128-row x 4-byte scale-factor atom into 4 TMEM columns.
+NVFP4_DEVICE void tcgen05_cp_32x128b_warpx4(uint32_t taddr, uint64_t smem_desc)
+{
+    asm volatile("tcgen05.cp.cta_group::1.32x128b.warpx4 [%0], %1;" ::"r"(taddr), "l"(smem_desc) : "memory");
+}
+
+// D[tmem] (+)= A[smem] * B[smem] with per-16-element E4M3 block scales read from TMEM.
+// E2M1 operands, K = 64 per instruction.
+NVFP4_DEVICE void tcgen05_mma_nvf4(uint32_t tmem_d, uint64_t desc_a, uint64_t desc_b, uint32_t idesc,
+                                   uint32_t tmem_sfa, uint32_t tmem_sfb, uint32_t accumulate)
+{
+    asm volatile(
+        "{\n"
+        " .reg .pred p;\n"
+        " setp.ne.b32 p, %6, 0;\n"
+        " tcgen05.mma.cta_group::1.kind::mxf4nvf4.block_scale.block16 [%0], %1, %2, %3, [%4], [%5], p;\n"
+        "}\n" ::"r"(tmem_d),
+        "l"(desc_a), "l"(desc_b), "r"(idesc), "r"(tmem_sfa), "r"(tmem_sfb), "r"(accumulate)
+        : "memory");
+}
+
+// Instruction descriptor of kind::mxf4nvf4: E2M1 x E2M1, UE4M3 scales, both operands K-major.
+//   [4,6) B scale id  [7,10) A format (1 = E2M1)  [10,13) B format  [15] A major  [16] B major
+//   [17,23) N >> 3  [23] scale format (0 = UE4M3)  [24,29) M >> 4  [29,31) A scale id  [31] K size (0 = 64)
+__host__ __device__ constexpr uint32_t make_idesc_nvf4(uint32_t m, uint32_t n)
+{
+    return (1u << 7) | (1u << 10) | ((n >> 3) << 17) | ((m >> 4) << 24);
+}
+
+// Shared-memory matrix descriptor (K-major):
+//   [0,14) address >> 4   [16,30) leading byte offset >> 4   [32,46) stride byte offset >> 4
+//   [46,48) version (1 on sm_100)   [61,64) swizzle: 0 none, 2 = 128 B, 4 = 64 B, 6 = 32 B
+enum : uint64_t { kSwizzleNone = 0, kSwizzle128B = 2, kSwizzle64B = 4, kSwizzle32B = 6 };
+NVFP4_DEVICE uint64_t make_smem_desc(uint32_t smem_addr, uint32_t stride_bytes, uint64_t swizzle)
+{
+    return static_cast<uint64_t>((smem_addr & 0x3ffffu) >> 4) | (static_cast<uint64_t>(stride_bytes >> 4) << 32) |
+           (1ull << 46) | (swizzle << 61);
+}
+
+// 32 lanes x 32 columns of 32-bit: thread i of the warp gets row (lane base + i), columns [c, c + 32).
+NVFP4_DEVICE void tmem_ld_32x32b_x32(uint32_t taddr, uint32_t (&r)[32])
+{
+    asm volatile(
+        "tcgen05.ld.sync.aligned.32x32b.x32.b32 "
+        "{%0, %1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15, "
+        "%16, %17, %18, %19, %20, %21, %22, %23, %24, %25, %26, %27, %28, %29, %30, %31}, [%32];"
+        : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]), "=r"(r[7]),
+          "=r"(r[8]), "=r"(r[9]), "=r"(r[10]), "=r"(r[11]), "=r"(r[12]), "=r"(r[13]), "=r"(r[14]), "=r"(r[15]),
+          "=r"(r[16]), "=r"(r[17]), "=r"(r[18]), "=r"(r[19]), "=r"(r[20]), "=r"(r[21]), "=r"(r[22]), "=r"(r[23]),
+          "=r"(r[24]), "=r"(r[25]), "=r"(r[26]), "=r"(r[27]), "=r"(r[28]), "=r"(r[29]), "=r"(r[30]), "=r"(r[31])
+        : "r"(taddr)
+        : "memory");
+}
+NVFP4_DEVICE void tmem_ld_32x32b_x16(uint32_t taddr, uint32_t (&r)[16])
+{
+    asm volatile(
+        "tcgen05.ld.sync.aligned.32x32b.x16.b32 "
+        "{%0, %1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15}, [%16];"
+        : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]), "=r"(r[7]),
+          "=r"(r[8]), "=r"(r[9]), "=r"(r[10]), "=r"(r[11]), "=r"(r[12]), "=r"(r[13]), "=r"(r[14]), "=r"(r[15])
+        : "r"(taddr)
+        : "memory");
+}
+NVFP4_DEVICE void tmem_ld_wait() { asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory"); }
+
+// ---- shared-memory vector access -------------------------------------------------------
+NVFP4_DEVICE uint4 lds128(uint32_t addr)
+{
+    uint4 v;
+    asm volatile("ld.shared.v4.u32 {%0, %1, %2, %3}, [%4];" : "=r"(v.x), "=r"(v.y), "=r"(v.z), "=r"(v.w) : "r"(addr));
+    return v;
+}
+NVFP4_DEVICE void sts128(uint32_t addr, uint32_t a, uint32_t b, uint32_t c, uint32_t d)
+{
+    asm volatile("st.shared.v4.u32 [%0], {%1, %2, %3, %4};" ::"r"(addr), "r"(a), "r"(b), "r"(c), "r"(d) : "memory");
+}
+NVFP4_DEVICE void sts64(uint32_t addr, uint32_t a, uint32_t b)
+{
+    asm volatile("st.shared.v2.u32 [%0], {%1, %2};" ::"r"(addr), "r"(a), "r"(b) : "memory");
+}
+NVFP4_DEVICE void sts32(uint32_t addr, uint32_t a) { asm volatile("st.shared.u32 [%0], %1;" ::"r"(addr), "r"(a) : "memory"); }
+NVFP4_DEVICE void sts16(uint32_t addr, uint32_t a)
+{
+    asm volatile("st.shared.u16 [%0], %1;" ::"r"(addr), "h"(static_cast<unsigned short>(a)) : "memory");
+}
+NVFP4_DEVICE void sts8(uint32_t addr, uint32_t a)
+{
+    asm volatile("st.shared.u8 [%0], %1;" ::"r"(addr), "r"(a) : "memory");
+}
+NVFP4_DEVICE uint32_t lds32(uint32_t addr)
+{
+    uint32_t v;
+    asm volatile("ld.shared.u32 %0, [%1];" : "=r"(v) : "r"(addr));
+    return v;
+}
+
+// ---- number-format converts ---------------------------------------------------------------
+// Eight FP32 -> eight E2M1 codes in one word (RNE, saturating); element 0 in the lowest nibble.
+NVFP4_DEVICE uint32_t cvt_e2m1x8(float f0, float f1, float f2, float f3, float f4, float f5, float f6, float f7)
+{
+    uint32_t r;
+    asm("{\n"
+        " .reg .b8 t0, t1, t2, t3;\n"
+        " cvt.rn.satfinite.e2m1x2.f32 t0, %2, %1;\n"
+        " cvt.rn.satfinite.e2m1x2.f32 t1, %4, %3;\n"
+        " cvt.rn.satfinite.e2m1x2.f32 t2, %6, %5;\n"
+        " cvt.rn.satfinite.e2m1x2.f32 t3, %8, %7;\n"
+        " mov.b32 %0, {t0, t1, t2, t3};\n"
+        "}\n"
+        : "=r"(r)
+        : "f"(f0), "f"(f1), "f"(f2), "f"(f3), "f"(f4), "f"(f5), "f"(f6), "f"(f7));
+    return r;
+}
+// One byte holding two E2M1 codes -> two FP16 values (low nibble in the low half).
+NVFP4_DEVICE uint32_t cvt_e2m1x2_to_f16x2(uint32_t byte)
+{
+    uint32_t r;
+    asm("{\n .reg .b8 t;\n cvt.u8.u32 t, %1;\n cvt.rn.f16x2.e2m1x2 %0, t;\n}" : "=r"(r) : "r"(byte));
+    return r;
+}
+// FP32 -> E4M3 byte (RNE, saturating to 448).
+NVFP4_DEVICE uint32_t cvt_e4m3(float x)
+{
+    unsigned short s;
+    asm("cvt.rn.satfinite.e4m3x2.f32 %0, %1, %2;" : "=h"(s) : "f"(0.0f), "f"(x));
+    return static_cast<uint32_t>(s) & 0xffu;
+}
+// d = a * b + c with a, b FP16 and c, d FP32 (one rounding).
+NVFP4_DEVICE float fma_f32_f16(unsigned short a, unsigned short b, float c)
+{
+    float d;
+    asm("fma.rn.f32.f16 %0, %1, %2, %3;" : "=f"(d) : "h"(a), "h"(b), "f"(c));
+    return d;
+}
+// max(|a|, |b|) per BF16 lane; the sign of the result is the xor of the signs.
+NVFP4_DEVICE uint32_t max_abs_bf16x2(uint32_t a, uint32_t b)
+{
+    uint32_t r;
+    asm("max.xorsign.abs.bf16x2 %0, %1, %2;" : "=r"(r) : "r"(a), "r"(b));
+    return r;
+}
+NVFP4_DEVICE float rcp_approx(float x)
+{
+    float r;
+    asm("rcp.approx.ftz.f32 %0, %1;" : "=f"(r) : "f"(x));
+    return r;
+}
+
+}  // namespace nvfp4::ptx

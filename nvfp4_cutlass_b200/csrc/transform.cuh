@@ -1,0 +1,185 @@
+// Algorithm 1 on the device: one BF16 block of 16 elements -> a most-significant
+// NVFP4 pass (q0, s0) and a x8 residual NVFP4 pass (q1, s1), bit-exact with the
+// reference's CPU emulation (tests/python/reference/dual_nvfp4.py:123-158 there),
+// plus the shared-memory addressing of everything the transform reads and writes.
+//
+// Exactness.  The emulation divides: u = x / s0 in FP32, q0 = RNE_e2m1(u),
+// q1 = RNE_e2m1((u - q0) * 8).  A single multiply by a rounded reciprocal breaks
+// exact ties (x = midpoint * s0), which are common because BF16 inputs and E4M3
+// scales carry few significant bits.  Here the reciprocal is carried as an
+// unevaluated sum r_hi + r_lo (r_lo = r_hi * (1 - s0 * r_hi), the residual formed
+// exactly by one FMA) and u = fma(x, r_hi, x * r_lo).  The pre-rounding error is
+// ~2^-46 relative while a quotient of an 8-bit by a 4-bit significand is either
+// exactly representable or at least 2^-17 away from any rounding threshold, so u
+// rounds like the true quotient wherever a code depends on it.  This holds for any
+// r_hi within a few ulp of 1/s0 (checked exhaustively over all BF16 x and all E4M3
+// s0, with r_hi perturbed by +-2 ulp), so the approximate reciprocal is enough.
+#pragma once
+#include "ptx.cuh"
+
+namespace nvfp4::xform {
+
+enum ScalePolicy : int { kDerivedDiv8 = 0, kResidualAmax = 1 };
+
+// ---- shared-memory addressing ----------------------------------------------------
+// BF16 activation tile as TMA lands it: boxes of 64 columns (128 B rows) x kRows,
+// 128-byte swizzle: 16-byte chunk index ^= row % 8.
+template <uint32_t kRows>
+NVFP4_DEVICE uint32_t a_bf16_offset(uint32_t row, uint32_t k)   // byte offset of element (row, k), k % 8 == 0
+{
+    const uint32_t box = k >> 6;
+    const uint32_t chunk = ((k & 63u) >> 3) ^ (row & 7u);
+    return box * (kRows * 128u) + row * 128u + (chunk << 4);
+}
+// Packed-FP4 operand tile, K-major, one swizzle span per row: 64-byte rows (128 K
+// elements) under the 64-byte swizzle, 16-byte chunk index ^= (row / 2) % 4; 128-byte
+// rows (256 K elements) under the 128-byte swizzle, chunk index ^= row % 8.  The same
+// function serves the TMA-written weights and the A0 / A1 tiles the transform writes,
+// which is what the MMA descriptors assume.
+template <uint32_t kBK>
+NVFP4_DEVICE uint32_t fp4_offset(uint32_t row, uint32_t k)   // byte offset of element (row, k), k % 32 == 0
+{
+    static_assert(kBK == 128 || kBK == 256, "one swizzle span per row");
+    if constexpr (kBK == 128) return row * 64u + (((k >> 5) ^ ((row >> 1) & 3u)) << 4);
+    else return row * 128u + (((k >> 5) ^ (row & 7u)) << 4);
+}
+NVFP4_DEVICE uint32_t fp4_sw64_offset(uint32_t row, uint32_t k) { return fp4_offset<128>(row, k); }
+// Scale-factor atom (128 rows x four 16-blocks = 64 K elements) in the order the
+// 32x128b.warpx4 tensor-memory copy wants: row r at word (r % 32) * 4 + r / 32,
+// byte j of the word = 16-block j.
+NVFP4_DEVICE uint32_t sf_word_offset(uint32_t row) { return (((row & 31u) << 2) + (row >> 5)) << 2; }
+
+// ---- Algorithm 1 on one 16-element block -------------------------------------------
+struct Block16 {
+    uint32_t q0[2];   // 16 E2M1 codes, element 0 in the lowest nibble of q0[0]
+    uint32_t q1[2];
+    uint32_t s0;      // E4M3 byte
+    uint32_t s1;
+};
+
+template <bool kResidual>
+NVFP4_DEVICE void decompose_block16(const uint32_t (&w)[8], Block16& out)
+{
+    // block amax over 16 BF16 values (pairs packed low = even element)
+    uint32_t m0 = ptx::max_abs_bf16x2(w[0], w[1]);
+    uint32_t m1 = ptx::max_abs_bf16x2(w[2], w[3]);
+    uint32_t m2 = ptx::max_abs_bf16x2(w[4], w[5]);
+    uint32_t m3 = ptx::max_abs_bf16x2(w[6], w[7]);
+    m0 = ptx::max_abs_bf16x2(m0, m1);
+    m2 = ptx::max_abs_bf16x2(m2, m3);
+    m0 = ptx::max_abs_bf16x2(m0, m2);
+    m0 = ptx::max_abs_bf16x2(m0, m0 >> 16);
+    const float amax = __uint_as_float((m0 & 0x7fffu) << 16);
+
+    // s0 = Q_e4m3(max(amax * fl(1/6), 2^-6)); always a normal E4M3 value
+    const float s0_pre = fmaxf(__fmul_rn(amax, 0.16666667163372040f), 0.015625f);
+    const uint32_t s0c = ptx::cvt_e4m3(s0_pre);
+    const float s0 = __uint_as_float((s0c << 20) + 0x3C000000u);
+    out.s0 = s0c;
+    out.s1 = ptx::cvt_e4m3(__fmul_rn(s0, 0.125f));
+
+    const float r_hi = ptx::rcp_approx(s0);
+    const float r_lo = __fmul_rn(__fmaf_rn(-s0, r_hi, 1.0f), r_hi);
+
+    float u[16];
+#pragma unroll
+    for (int i = 0; i < 8; ++i) {
+        const float x0 = __uint_as_float(w[i] << 16);
+        const float x1 = __uint_as_float(w[i] & 0xffff0000u);
+        u[2 * i] = __fmaf_rn(x0, r_hi, __fmul_rn(x0, r_lo));
+        u[2 * i + 1] = __fmaf_rn(x1, r_hi, __fmul_rn(x1, r_lo));
+    }
+    out.q0[0] = ptx::cvt_e2m1x8(u[0], u[1], u[2], u[3], u[4], u[5], u[6], u[7]);
+    out.q0[1] = ptx::cvt_e2m1x8(u[8], u[9], u[10], u[11], u[12], u[13], u[14], u[15]);
+
+    if constexpr (kResidual) {
+        // r = (u - dec(q0)) * 8 = 8u + dec(q0) * (-8): exact, the decode comes back as FP16
+        float r[16];
+#pragma unroll
+        for (int i = 0; i < 8; ++i) {
+            const uint32_t byte = (out.q0[i >> 2] >> (8 * (i & 3))) & 0xffu;
+            const uint32_t d = ptx::cvt_e2m1x2_to_f16x2(byte);
+            r[2 * i] = ptx::fma_f32_f16(static_cast<unsigned short>(d & 0xffffu), 0xC800u, __fmul_rn(u[2 * i], 8.0f));
+            r[2 * i + 1] = ptx::fma_f32_f16(static_cast<unsigned short>(d >> 16), 0xC800u, __fmul_rn(u[2 * i + 1], 8.0f));
+        }
+        out.q1[0] = ptx::cvt_e2m1x8(r[0], r[1], r[2], r[3], r[4], r[5], r[6], r[7]);
+        out.q1[1] = ptx::cvt_e2m1x8(r[8], r[9], r[10], r[11], r[12], r[13], r[14], r[15]);
+    } else {
+        out.q1[0] = out.q1[1] = 0u;
+    }
+}
+
+// ---- one activation tile ------------------------------------------------------------
+// kRows x kBK BF16 (as TMA landed it at `a_smem`, in boxes of 64 columns) -> A0 / A1
+// (packed FP4, one swizzle span per row) and the SFA0 / SFA1 atoms (one 512-byte atom
+// per 64 K elements; rows past kRows of an atom are left untouched).  Called by
+// kThreads threads with t = 0..kThreads-1.  Thread t owns row t % kRows and a run of
+// consecutive 16-blocks in it: lanes walk consecutive rows, which keeps the 128-bit
+// loads and stores free of bank conflicts under both swizzles.
+template <uint32_t kRows, uint32_t kBK, uint32_t kThreads, bool kResidual>
+NVFP4_DEVICE void transform_tile(uint32_t a_smem, uint32_t a0_smem, uint32_t a1_smem, uint32_t sfa0_smem,
+                                 uint32_t sfa1_smem, uint32_t t)
+{
+    constexpr uint32_t kBlocks = kRows * (kBK / 16u);
+    constexpr uint32_t kActive = kThreads < kBlocks ? kThreads : kBlocks;   // surplus threads idle
+    constexpr uint32_t kBlocksPerThread = kBlocks / kActive;
+    static_assert(kBlocksPerThread * kActive == kBlocks, "threads must tile the blocks");
+    if (t >= kActive) return;
+    static_assert(kBlocksPerThread == 1 || kBlocksPerThread == 2 || kBlocksPerThread == 4 || kBlocksPerThread == 8 ||
+                  kBlocksPerThread == 16, "unsupported split");
+    static_assert(kRows % 16 == 0 && kRows <= 128 && kActive % kRows == 0, "row count");
+    constexpr uint32_t kSfAtomBytes = 512u;                        // one 128-row x 4-byte atom per 64 K
+    const uint32_t row = t % kRows;
+    const uint32_t first_block = (t / kRows) * kBlocksPerThread;
+
+    if constexpr (kBlocksPerThread == 1) {
+        const uint32_t k = first_block * 16u;
+        const uint4 lo = ptx::lds128(a_smem + a_bf16_offset<kRows>(row, k));
+        const uint4 hi = ptx::lds128(a_smem + a_bf16_offset<kRows>(row, k + 8));
+        const uint32_t w[8] = {lo.x, lo.y, lo.z, lo.w, hi.x, hi.y, hi.z, hi.w};
+        Block16 blk;
+        decompose_block16<kResidual>(w, blk);
+        const uint32_t off = fp4_offset<kBK>(row, k & ~31u) + ((first_block & 1u) << 3);
+        ptx::sts64(a0_smem + off, blk.q0[0], blk.q0[1]);
+        if constexpr (kResidual) ptx::sts64(a1_smem + off, blk.q1[0], blk.q1[1]);
+        const uint32_t addr = (first_block >> 2) * kSfAtomBytes + sf_word_offset(row) + (first_block & 3u);
+        ptx::sts8(sfa0_smem + addr, blk.s0);
+        if constexpr (kResidual) ptx::sts8(sfa1_smem + addr, blk.s1);
+        return;
+    } else {
+        uint32_t sf0 = 0, sf1 = 0;
+#pragma unroll
+        for (uint32_t pair = 0; pair < kBlocksPerThread / 2; ++pair) {
+            Block16 blk[2];
+#pragma unroll
+            for (uint32_t h = 0; h < 2; ++h) {
+                const uint32_t k = (first_block + pair * 2 + h) * 16u;
+                const uint4 lo = ptx::lds128(a_smem + a_bf16_offset<kRows>(row, k));
+                const uint4 hi = ptx::lds128(a_smem + a_bf16_offset<kRows>(row, k + 8));
+                const uint32_t w[8] = {lo.x, lo.y, lo.z, lo.w, hi.x, hi.y, hi.z, hi.w};
+                decompose_block16<kResidual>(w, blk[h]);
+            }
+            // two blocks = 32 elements = one 16-byte chunk of each packed row
+            const uint32_t off = fp4_offset<kBK>(row, (first_block + pair * 2) * 16u);
+            ptx::sts128(a0_smem + off, blk[0].q0[0], blk[0].q0[1], blk[1].q0[0], blk[1].q0[1]);
+            if constexpr (kResidual)
+                ptx::sts128(a1_smem + off, blk[0].q1[0], blk[0].q1[1], blk[1].q1[0], blk[1].q1[1]);
+            const uint32_t shift = ((pair * 2) & 3u) * 8u;
+            sf0 |= (blk[0].s0 | (blk[1].s0 << 8)) << shift;
+            sf1 |= (blk[0].s1 | (blk[1].s1 << 8)) << shift;
+            // flush a scale word (or half word) whenever this thread's share of a K atom is complete
+            if constexpr (kBlocksPerThread == 2) {
+                const uint32_t addr = (first_block >> 2) * kSfAtomBytes + sf_word_offset(row) + (first_block & 2u);
+                ptx::sts16(sfa0_smem + addr, sf0);
+                if constexpr (kResidual) ptx::sts16(sfa1_smem + addr, sf1);
+            } else if ((pair & 1u) == 1u) {
+                const uint32_t addr = ((first_block + pair * 2) >> 2) * kSfAtomBytes + sf_word_offset(row);
+                ptx::sts32(sfa0_smem + addr, sf0);
+                if constexpr (kResidual) ptx::sts32(sfa1_smem + addr, sf1);
+                sf0 = sf1 = 0;
+            }
+        }
+    }
+}
+
+}  // namespace nvfp4::xform

@@ -199,3 +199,14 @@ def ref_twin_dual_gemm(a, q, sf, g, expert_of_row, n: int) -> torch.Tensor:
     r.ref_twin_dual_gemm(_ptr(a), _ptr(_cpu(q)), _ptr(_cpu(sf)), _ptr(_cpu(g, torch.float32)),
                          _ptr(_cpu(expert_of_row, torch.int32)), m, n, k, g.numel(), _ptr(out))
     return out
+
+
+def ref_twin_dual_gemm_mt(a, q, sf, g, expert_of_row, n: int, threads: int) -> torch.Tensor:
+    """ref::dual_gemm on every host thread (row chunks handed to independent calls)."""
+    r = ref_twin()
+    a = _cpu(a, torch.float32)
+    m, k = a.shape
+    out = torch.empty(m, n, dtype=torch.float32)
+    r.ref_twin_dual_gemm_mt(_ptr(a), _ptr(_cpu(q)), _ptr(_cpu(sf)), _ptr(_cpu(g, torch.float32)),
+                            _ptr(_cpu(expert_of_row, torch.int32)), m, n, k, g.numel(), _ptr(out), int(threads))
+    return out

@@ -59,4 +59,26 @@ int ref_twin_dual_gemm(const float* a, const uint8_t* q, const uint8_t* sf, cons
     return 0;
 }
 
+// The same chain on all host threads: the reference's function is serial, so row chunks
+// of the input are handed to independent calls of it (each call runs the reference's
+// own code start to end on its rows).
+int ref_twin_dual_gemm_mt(const float* a, const uint8_t* q, const uint8_t* sf, const float* g,
+                          const int32_t* expert_of_row, int M, int N, int K, int E, float* out, int threads)
+{
+    const int chunk = 8;
+    const int nchunks = (M + chunk - 1) / chunk;
+    std::vector<uint8_t> qv(q, q + static_cast<size_t>(E) * N * K);
+    std::vector<uint8_t> sv(sf, sf + static_cast<size_t>(E) * N * (K / ref::kBlockSize));
+    std::vector<float> gv(g, g + E);
+#pragma omp parallel for schedule(dynamic, 1) num_threads(threads)
+    for (int c = 0; c < nchunks; ++c) {
+        const int lo = c * chunk, hi = lo + chunk < M ? lo + chunk : M;
+        std::vector<float> av(a + static_cast<size_t>(lo) * K, a + static_cast<size_t>(hi) * K);
+        std::vector<int> ev(expert_of_row + lo, expert_of_row + hi);
+        std::vector<float> r = ref::dual_gemm(av, qv, sv, gv, ev, hi - lo, N, K, E);
+        std::memcpy(out + static_cast<size_t>(lo) * N, r.data(), r.size() * sizeof(float));
+    }
+    return 0;
+}
+
 }  // extern "C"

@@ -1,0 +1,127 @@
+"""CPU: the host side of the drop-in surface -- layout helpers with the reference's
+known answers (tests/python/test_layout.py there), argument checking, and that the
+C-ABI library loads and exports every symbol include/nvfp4_b200.h declares."""
+import ctypes
+import os
+import re
+
+import pytest
+import torch
+
+from conftest import ROOT, bf16_from_bits, load_golden
+
+import nvfp4_gemm
+from nvfp4_gemm import layout
+
+
+def test_public_surface():
+    for name in ("m_grouped_bf16_dual_nvfp4_gemm_contiguous", "quantize_weight_nvfp4", "dequantize_weight_nvfp4",
+                 "make_m_indices", "layout", "get_num_sms", "set_num_sms"):
+        assert hasattr(nvfp4_gemm, name), name
+    assert set(nvfp4_gemm.__all__) >= {"m_grouped_bf16_dual_nvfp4_gemm_contiguous", "quantize_weight_nvfp4"}
+
+
+def test_library_exports_every_declared_symbol():
+    header = open(os.path.join(ROOT, "include", "nvfp4_b200.h")).read()
+    declared = set(re.findall(r"NVFP4_API\s+[\w\s\*]+?\b(nvfp4_\w+)\s*\(", header))
+    assert declared and declared == set(nvfp4_gemm._C.EXPORTS)
+    lib = ctypes.CDLL(nvfp4_gemm._C.library_path())          # loading needs no GPU
+    for sym in declared:
+        assert hasattr(lib, sym), sym
+    lib.nvfp4_version.restype = ctypes.c_char_p
+    assert b"sm_100a" in lib.nvfp4_version()
+
+
+def test_e2m1_codes_known_answers():
+    # test_layout.py:33-46: codes incl. sign bit and ties
+    x = torch.tensor([0.0, 0.5, 1.0, 1.5, 2.0, 3.0, 4.0, 6.0, -0.5, -6.0, 0.25, 0.75, 1.25, 1.75, 2.5, 3.5, 5.0, 100.0, -0.0])
+    assert layout.quantize_e2m1_codes(x).tolist() == [0, 1, 2, 3, 4, 5, 6, 7, 9, 15, 0, 2, 2, 4, 4, 6, 6, 7, 8]
+    g = load_golden("e2m1.npz")
+    assert torch.equal(layout.quantize_e2m1_codes(torch.from_numpy(g["x"])), torch.from_numpy(g["codes"]))
+
+
+def test_nibble_order_and_scale_words():
+    # test_layout.py:49-58 and :61-83
+    assert (layout.pack_e2m1_pairs(torch.tensor([1, 2, 3, 4], dtype=torch.uint8)).view(torch.uint8).tolist()
+            == [0x21, 0x43])
+    with pytest.raises(ValueError):
+        layout.pack_e2m1_pairs(torch.zeros(3, dtype=torch.uint8))
+    s = torch.arange(2 * 3 * 8, dtype=torch.uint8).reshape(2, 3, 8)
+    words = layout.pack_sf_atoms(s)
+    assert words.shape == (2 * 2, 3) and words.dtype == torch.int32
+    for e in range(2):
+        for n in range(3):
+            for at in range(2):
+                w = int(words[e * 2 + at, n]) & 0xffffffff
+                assert [(w >> (8 * j)) & 0xff for j in range(4)] == s[e, n, at * 4:at * 4 + 4].tolist()
+
+
+def test_host_quantiser_matches_golden():
+    g = load_golden("weights.npz")
+    w = bf16_from_bits(g["w_bits"])
+    b, sfb, gw = layout.quantize_weight_nvfp4(w)
+    assert b.dtype == torch.int8 and sfb.dtype == torch.int32 and gw.dtype == torch.float32
+    assert torch.equal(b, torch.from_numpy(g["b"]))
+    assert torch.equal(sfb, torch.from_numpy(g["sfb"]))
+    assert torch.equal(gw, torch.from_numpy(g["gw"]))
+    assert torch.equal(layout.dequantize_weight_nvfp4(b, sfb, gw, 3, 64, 128), torch.from_numpy(g["deq"]))
+    # round trip quality the reference reports (test_layout.py:86-114)
+    torch.manual_seed(0)
+    w = torch.randn(2, 128, 256)
+    deq = layout.dequantize_weight_nvfp4(*layout.quantize_weight_nvfp4(w), 2, 128, 256)
+    rel = float((deq - w).norm() / w.norm())
+    cos = float(torch.dot(deq.flatten(), w.flatten()) / (deq.norm() * w.norm()))
+    assert rel < 0.12 and cos > 0.995
+
+
+def test_quantize_weight_errors():
+    with pytest.raises(ValueError):
+        layout.quantize_weight_nvfp4(torch.zeros(4, 64))
+    with pytest.raises(ValueError):
+        layout.quantize_weight_nvfp4(torch.zeros(1, 4, 96))
+
+
+def test_make_m_indices():
+    # test_layout.py:139-152
+    out = layout.make_m_indices([128, 256, 0, 128])
+    assert out.dtype == torch.int32 and out.shape == (512,)
+    assert out[:128].eq(0).all() and out[128:384].eq(1).all() and out[384:].eq(3).all()
+    with pytest.raises(ValueError):
+        layout.make_m_indices([128, 100])
+    assert layout.make_m_indices([32, 64], alignment=32).shape == (96,)
+    assert layout.make_m_indices(torch.tensor([128])).tolist() == [0] * 128
+
+
+def test_gemm_argument_checks_need_no_gpu():
+    a = torch.zeros(128, 256, dtype=torch.bfloat16)
+    d = torch.zeros(128, 128, dtype=torch.bfloat16)
+    b = torch.zeros(128, 128, dtype=torch.int8)
+    sfb = torch.zeros(4, 128, dtype=torch.int32)
+    gw = torch.ones(1)
+    mi = torch.zeros(128, dtype=torch.int32)
+    f = nvfp4_gemm.m_grouped_bf16_dual_nvfp4_gemm_contiguous
+    with pytest.raises(RuntimeError):                      # wrong dtype
+        f(a.float(), b, sfb, gw, d, mi)
+    with pytest.raises(RuntimeError):                      # wrong b shape
+        f(a, b[:64], sfb, gw, d, mi)
+    with pytest.raises(RuntimeError):                      # CPU tensors: no CPU path exists
+        f(a, b, sfb, gw, d, mi)
+    with pytest.raises(TypeError):
+        f(a, b, sfb, gw, d, mi, tune_nonsense=1)
+    with pytest.raises(RuntimeError):
+        f(a, b, sfb, gw, d, mi, scale_policy="bogus")
+
+
+def test_c_abi_validation_without_gpu():
+    """Shape validation happens before any CUDA call, so the codes can be checked here."""
+    lib = nvfp4_gemm._C.lib()
+    rc = lib.nvfp4_grouped_gemm_contiguous(None, 0, None, None, None, None, 0, None, 128, 100, 256, 1, 0, 1, 0, 0,
+                                           None, None, None)
+    assert rc == 1 and b"multiples of 128" in lib.nvfp4_last_error()
+    rc = lib.nvfp4_grouped_gemm_contiguous(None, 0, None, None, None, None, 0, None, 100, 128, 256, 1, 0, 1, 0, 0,
+                                           None, None, None)
+    assert rc == 1 and b"alignment" in lib.nvfp4_last_error()
+    rc = lib.nvfp4_grouped_gemm_contiguous(None, 0, None, None, None, None, 0, None, 0, 128, 256, 1, 0, 1, 0, 0,
+                                           None, None, None)
+    assert rc == 0                                          # M == 0 returns silently
+    assert lib.nvfp4_quantize_weight(None, 0, 1, 4, 96, None, None, None, None) == 1
