@@ -35,6 +35,9 @@ WORKLOADS = {
     "c3up": dict(E=256, N=4096, K=7168, desc="DeepSeek-V3-style prefill up: E=256, 32768 rows Zipf(1.1) padded to 128, N=4096, K=7168"),
     "c3down": dict(E=256, N=7168, K=2048, desc="DeepSeek-V3-style prefill down: E=256, 32768 rows Zipf(1.1) padded to 128, N=7168, K=2048"),
     "c4": dict(E=256, N=4096, K=7168, desc="decode: E=256, 64 tokens x top-8 (1-16 rows per active expert, padded to 16), N=4096, K=7168"),
+    # reduced copies of c2 / c4 (operands still larger than L2) for profiler captures
+    "c2s": dict(E=8, N=8192, K=4096, desc="reduced c2 for profiling: E=8 x 512 rows, N=8192, K=4096"),
+    "c4s": dict(E=64, N=4096, K=7168, desc="reduced c4 for profiling: E=64, 16 tokens x top-8, N=4096, K=7168"),
 }
 
 
@@ -89,16 +92,16 @@ class ClockSampler:
 # ----------------------------------------------------------------------------- workloads
 def routing_rows(workload: str, E: int, gen: torch.Generator):
     """Real rows per expert and the padded group sizes the kernel sees."""
-    if workload == "c2":
+    if workload in ("c2", "c2s"):
         real = [512] * E
         return real, real, 128, False
     if workload in ("c3up", "c3down"):
         p = torch.arange(1, E + 1, dtype=torch.float64).pow(-1.1)
         real = torch.multinomial(p / p.sum(), 32768, replacement=True, generator=gen).bincount(minlength=E).tolist()
         return real, [((r + 127) // 128) * 128 for r in real], 128, False
-    if workload == "c4":
+    if workload in ("c4", "c4s"):
         counts = torch.zeros(E, dtype=torch.int64)
-        for _ in range(64):                                 # 64 tokens, 8 distinct experts each
+        for _ in range(64 if workload == "c4" else 16):     # 64 tokens, 8 distinct experts each
             counts[torch.randperm(E, generator=gen)[:8]] += 1
         real = counts.clamp(max=16).tolist()
         return real, [((r + 15) // 16) * 16 for r in real], 16, True
@@ -121,7 +124,7 @@ def build_weights(E: int, N: int, K: int, dev, seed: int):
     return b, sfb, gw
 
 
-def build_single_gpu_case(workload: str, dev):
+def build_single_gpu_case(workload: str, dev, extra_kw=None):
     import nvfp4_gemm
     cfg = WORKLOADS[workload]
     E, N, K = cfg["E"], cfg["N"], cfg["K"]
@@ -131,7 +134,7 @@ def build_single_gpu_case(workload: str, dev):
     ga = torch.Generator(device=dev).manual_seed(0)
     a = torch.zeros(M, K, dtype=torch.bfloat16, device=dev)
     x = torch.randn(sum(real), K, generator=ga, device=dev)
-    if workload == "c2":                                    # per-row lognormal(0, 0.5) scale
+    if workload in ("c2", "c2s"):                           # per-row lognormal(0, 0.5) scale
         x = x * torch.exp(0.5 * torch.randn(sum(real), 1, generator=ga, device=dev))
     if workload.startswith("c3"):                           # 0.1 % outlier channels x50
         cols = torch.randperm(K, generator=torch.Generator().manual_seed(1))[:max(1, K // 1000)]
@@ -145,6 +148,7 @@ def build_single_gpu_case(workload: str, dev):
     m_indices = nvfp4_gemm.make_m_indices(padded, alignment=align).to(dev)
     b, sfb, gw = build_weights(E, N, K, dev, seed=2)
     kw = dict(tune_swap_ab=1, m_alignment=align) if swap else {}
+    kw.update(extra_kw or {})
     active = sum(1 for r in real if r > 0)
     return dict(a=a, b=b, sfb=sfb, gw=gw, m_indices=m_indices, M=M, N=N, K=K, E=E, real_rows=sum(real),
                 active_experts=active, kw=kw, swap=swap, padded=padded, real=real)
@@ -270,6 +274,7 @@ def main():
     ap.add_argument("--workload", default=None, help="c2 (default at 1 GPU), c3up, c3down, c4, c5 (default at >1 GPU)")
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--no-cpu-baseline", action="store_true")
+    ap.add_argument("--tune", action="append", default=[], help="tune_xxx=int passed to the GEMM call (experiments)")
     args = ap.parse_args()
     if args.impl == "reference":
         args.steps = args.steps or 2
@@ -290,7 +295,8 @@ def main():
     steps = args.steps or (300 if workload != "c4" else 300)
     warmup = args.warmup if args.warmup is not None else 10
     warmup = max(warmup, 3)
-    case = build_single_gpu_case(workload, dev)
+    extra = {kv.split('=')[0]: int(kv.split('=')[1]) for kv in args.tune}
+    case = build_single_gpu_case(workload, dev, extra)
     M, N, K = case["M"], case["N"], case["K"]
     d = torch.empty(M, N, dtype=torch.bfloat16, device=dev)
     status = torch.zeros(1, dtype=torch.int32, device=dev)
@@ -352,7 +358,7 @@ def main():
             "dtype": "nvfp4 (e2m1 x ue4m3 block 16), fp32 accumulate, bf16 in/out", "data": "synthetic",
             "config": {"workload": WORKLOADS[workload]["desc"], "name": workload, "M_padded": M, "M_real": case["real_rows"],
                        "N": N, "K": K, "E": case["E"], "passes": 2, "orientation": "swap_ab" if case["swap"] else "normal",
-                       "l2": "operands larger than L2 (weights %.0f MB), no flush" % (case["b"].numel() / 1e6)},
+                       "tune": extra, "l2": "operands larger than L2 (weights %.0f MB), no flush" % (case["b"].numel() / 1e6)},
             "roofline": roofline, "e2e": e2e, "gpu_launches": steps, "clocks": clocks,
             "rel_l2_vs_fp32": rel, "cosine_vs_fp32": cos}
     if not args.no_cpu_baseline:

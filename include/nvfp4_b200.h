@@ -109,6 +109,13 @@ NVFP4_API int nvfp4_debug_decompose(const void* a, int64_t lda_elems, int M, int
  * Used to measure the tensor-pipe ceiling the roofline fractions are quoted against. */
 NVFP4_API int nvfp4_debug_mma_peak(int iters, double* flops_per_launch, void* stream);
 
+/* Measurement hook: like nvfp4_debug_mma_peak, with the issue pattern of a K block made
+ * explicit: per round `num_cp` scale-factor copies (tcgen05.cp 32x128b.warpx4) followed by
+ * `num_mma` MMAs of 128 x mma_n x 64 (mma_n in {16, 32, 64, 128, 256}); alt_cols != 0
+ * alternates the scale columns between two sets.  Used to size the per-K-block issue cost. */
+NVFP4_API int nvfp4_debug_mma_pattern(int iters, int num_cp, int num_mma, int mma_n, int alt_cols,
+                                      double* flops_per_launch, void* stream);
+
 #ifdef __cplusplus
 }
 #endif

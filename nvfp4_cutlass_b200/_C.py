@@ -28,7 +28,7 @@ TUNE_KEYS = ("tune_block_n", "tune_transform_warps", "tune_epilogue_threads", "t
 
 EXPORTS = ("nvfp4_last_error", "nvfp4_version", "nvfp4_get_num_sms", "nvfp4_set_num_sms",
            "nvfp4_quantize_weight", "nvfp4_grouped_gemm_contiguous", "nvfp4_debug_decompose",
-           "nvfp4_debug_mma_peak")
+           "nvfp4_debug_mma_peak", "nvfp4_debug_mma_pattern")
 
 
 def library_path() -> str:
@@ -54,6 +54,7 @@ def lib() -> ctypes.CDLL:
                                                     i32, i32, i32, i32, vp, vp, vp]
         L.nvfp4_debug_decompose.argtypes = [vp, i64, i32, i32, i32, vp, vp, vp, vp, vp]
         L.nvfp4_debug_mma_peak.argtypes = [i32, ctypes.POINTER(ctypes.c_double), vp]
+        L.nvfp4_debug_mma_pattern.argtypes = [i32, i32, i32, i32, i32, ctypes.POINTER(ctypes.c_double), vp]
         _lib = L
     return _lib
 
@@ -169,4 +170,12 @@ def debug_mma_peak(iters: int) -> float:
     """Launches the resident-operand FP4 MMA loop once; returns the FLOPs of the launch."""
     flops = ctypes.c_double(0.0)
     _check(lib().nvfp4_debug_mma_peak(int(iters), ctypes.byref(flops), _stream()))
+    return flops.value
+
+
+def debug_mma_pattern(iters: int, num_cp: int, num_mma: int, mma_n: int, alt_cols: int = 0) -> float:
+    """One launch of the copy + MMA issue pattern study; returns the FLOPs of the launch."""
+    flops = ctypes.c_double(0.0)
+    _check(lib().nvfp4_debug_mma_pattern(int(iters), int(num_cp), int(num_mma), int(mma_n), int(alt_cols),
+                                         ctypes.byref(flops), _stream()))
     return flops.value

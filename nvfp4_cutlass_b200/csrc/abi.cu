@@ -199,4 +199,17 @@ int nvfp4_debug_mma_peak(int iters, double* flops_per_launch, void* stream)
     return launch_mma_peak(iters, dev->hw_sms, flops_per_launch, static_cast<cudaStream_t>(stream));
 }
 
+int nvfp4_debug_mma_pattern(int iters, int num_cp, int num_mma, int mma_n, int alt_cols, double* flops_per_launch,
+                            void* stream)
+{
+    host::clear_error();
+    NVFP4_REQUIRE(iters > 0 && iters <= (1 << 20) && num_cp >= 0 && num_cp <= 64 && num_mma >= 0 && num_mma <= 64,
+                  "iters / num_cp / num_mma out of range");
+    host::DeviceInfo* dev;
+    if (int rc = host::device_info(-1, &dev)) return rc;
+    if (dev->cc_major != 10) return host::fail(NVFP4_E_UNSUPPORTED, "needs an sm_100 GPU");
+    return launch_mma_pattern(iters, num_cp, num_mma, mma_n, alt_cols, dev->hw_sms, flops_per_launch,
+                              static_cast<cudaStream_t>(stream));
+}
+
 }  // extern "C"

@@ -33,7 +33,7 @@ __global__ void __launch_bounds__(kThreads) decompose_dump_kernel(const __nv_bfl
     }
     __syncthreads();
     xform::transform_tile<128, 128, kThreads, true>(ptx::smem_u32(tile), ptx::smem_u32(a0), ptx::smem_u32(a1),
-                                               ptx::smem_u32(sfa0), ptx::smem_u32(sfa1), t);
+                                               ptx::smem_u32(sfa0), ptx::smem_u32(sfa1), t, [] {});
     __syncthreads();
     for (uint32_t c = t; c < 128 * 4; c += kThreads) {           // 16-byte chunks of packed codes: 4 per row
         const uint32_t row = c >> 2, k = (c & 3u) * 32u;
@@ -49,9 +49,13 @@ __global__ void __launch_bounds__(kThreads) decompose_dump_kernel(const __nv_bfl
     }
 }
 
-// Resident-operand tensor-pipe ceiling: every CTA issues `iters` x 8 block-scaled
-// FP4 MMAs of 128 x 256 x 64 on operands that never leave shared / tensor memory.
-__global__ void __launch_bounds__(128, 1) mma_peak_kernel(int iters, int32_t* status)
+// Resident-operand tensor-pipe study: every CTA issues `iters` rounds of `num_cp`
+// scale-factor copies (tcgen05.cp 32x128b.warpx4) followed by `num_mma` block-scaled FP4
+// MMAs of 128 x mma_n x 64 on operands that never leave shared / tensor memory.  With
+// num_cp = 0, num_mma = 8, mma_n = 256 this is the tensor-pipe ceiling.  `alt_cols`
+// alternates the scale columns between two sets from round to round.
+template <uint32_t kN>
+__global__ void __launch_bounds__(128, 1) mma_pattern_kernel(int iters, int num_cp, int num_mma, int alt_cols, int32_t* status)
 {
     extern __shared__ uint8_t smem_raw[];
     const uint32_t smem = (ptx::smem_u32(smem_raw) + 1023u) & ~1023u;
@@ -72,18 +76,20 @@ __global__ void __launch_bounds__(128, 1) mma_peak_kernel(int iters, int32_t* st
     ptx::tcgen05_fence_after_sync();
     const uint32_t tmem = *tmem_slot;
     if (threadIdx.x == 0) {
-        for (uint32_t i = 0; i < 4; ++i)
-            ptx::tcgen05_cp_32x128b_warpx4(tmem + 256 + 4 * i, ptx::make_smem_desc(smem + kSF + i * 512, 128, ptx::kSwizzleNone));
-        constexpr uint32_t idesc = ptx::make_idesc_nvf4(128, 256);
+        for (uint32_t i = 0; i < 16; ++i)
+            ptx::tcgen05_cp_32x128b_warpx4(tmem + 256 + 4 * i, ptx::make_smem_desc(smem + kSF + (i & 3) * 512, 128, ptx::kSwizzleNone));
+        constexpr uint32_t idesc = ptx::make_idesc_nvf4(128, kN);
         for (int it = 0; it < iters; ++it) {
-#pragma unroll
-            for (uint32_t j = 0; j < 8; ++j)
+            const uint32_t col = 256 + ((alt_cols && (it & 1)) ? 32 : 0);
+            for (int j = 0; j < num_cp; ++j)
+                ptx::tcgen05_cp_32x128b_warpx4(tmem + col + 4 * (j & 7), ptx::make_smem_desc(smem + kSF + (j & 3) * 512, 128, ptx::kSwizzleNone));
+            for (int j = 0; j < num_mma; ++j)
                 ptx::tcgen05_mma_nvf4(tmem, ptx::make_smem_desc(smem + kA + (j & 1u) * 32, 512, ptx::kSwizzle64B),
                                       ptx::make_smem_desc(smem + kB + (j & 1u) * 32, 512, ptx::kSwizzle64B), idesc,
-                                      tmem + 256, tmem + 264, (it | j) != 0 ? 1u : 0u);
+                                      tmem + col, tmem + col + 8, (it | j) != 0 ? 1u : 0u);
         }
         ptx::tcgen05_commit(bar);
-        if (!ptx::mbar_wait(bar, 0, abort_flag) && status != nullptr) atomicOr(status, 1);
+        if (!ptx::mbar_wait_impl(bar, 0, abort_flag) && status != nullptr) atomicOr(status, 1);
     }
     ptx::tcgen05_fence_before_sync();
     __syncthreads();
@@ -111,20 +117,29 @@ int launch_debug_decompose(const void* a, int64_t lda, int M, int K, void* q0, v
     return NVFP4_OK;
 }
 
-int launch_mma_peak(int iters, int num_sms, double* flops_per_launch, cudaStream_t stream)
+int launch_mma_pattern(int iters, int num_cp, int num_mma, int mma_n, int alt_cols, int num_sms, double* flops_per_launch,
+                       cudaStream_t stream)
 {
     constexpr int kSmem = 8192 + 16384 + 2048 + 64 + 1024;
-    static bool attr_set[host::kMaxDevices] = {};
-    int dev = 0;
-    NVFP4_CUDA_CHECK(cudaGetDevice(&dev));
-    if (!attr_set[dev]) {
-        NVFP4_CUDA_CHECK(cudaFuncSetAttribute(mma_peak_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, kSmem));
-        attr_set[dev] = true;
+    void (*kernel)(int, int, int, int, int32_t*) = nullptr;
+    switch (mma_n) {
+        case 16: kernel = mma_pattern_kernel<16>; break;
+        case 32: kernel = mma_pattern_kernel<32>; break;
+        case 64: kernel = mma_pattern_kernel<64>; break;
+        case 128: kernel = mma_pattern_kernel<128>; break;
+        case 256: kernel = mma_pattern_kernel<256>; break;
+        default: return host::fail(NVFP4_E_INVALID_ARGUMENT, "mma_n %d not in {16, 32, 64, 128, 256}", mma_n);
     }
-    mma_peak_kernel<<<num_sms, 128, kSmem, stream>>>(iters, nullptr);
+    NVFP4_CUDA_CHECK(cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, kSmem));
+    kernel<<<num_sms, 128, kSmem, stream>>>(iters, num_cp, num_mma, alt_cols, nullptr);
     NVFP4_CUDA_CHECK(cudaGetLastError());
-    if (flops_per_launch) *flops_per_launch = 2.0 * 128 * 256 * 64 * 8.0 * iters * num_sms;
+    if (flops_per_launch) *flops_per_launch = 2.0 * 128 * mma_n * 64 * static_cast<double>(num_mma) * iters * num_sms;
     return NVFP4_OK;
+}
+
+int launch_mma_peak(int iters, int num_sms, double* flops_per_launch, cudaStream_t stream)
+{
+    return launch_mma_pattern(iters, 0, 8, 256, 0, num_sms, flops_per_launch, stream);
 }
 
 }  // namespace nvfp4

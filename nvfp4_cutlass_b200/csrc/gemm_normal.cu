@@ -60,7 +60,7 @@ constexpr uint32_t kTmemCols = 512;
 constexpr uint32_t kColAcc = 0, kColSFA0 = 256, kColSFA1 = kColSFA0 + 4 * kKAtoms, kColSFB = kColSFA1 + 4 * kKAtoms;
 
 // warp roles
-constexpr uint32_t kWarpTma = 0, kWarpMma = 1, kWarpSfb = 2, kWarpEpi0 = 4, kNumEpiWarps = 4, kWarpXform0 = 8;
+constexpr uint32_t kWarpTma = 0, kWarpMma = 1, kWarpSfb = 2, kWarpTmaA = 3, kWarpEpi0 = 4, kNumEpiWarps = 4, kWarpXform0 = 8;
 
 struct Params {
     const float* gw;
@@ -146,9 +146,11 @@ gemm_normal_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_consta
     ptx::tcgen05_fence_after_sync();
     const uint32_t tmem_base = *tmem_slot;
 
+    const long long probe_start = ptx::probe_clock();
     const uint32_t num_m = p.m / BM, num_n = p.n / BN, num_kb = p.k / BK;
     const uint32_t num_tiles = num_m * num_n;
     bool ok = true;
+    ptx::ProbeAcc pa;
     auto give_up = [&](uint32_t code) {
         *abort_flag = 1;
         if (p.status != nullptr) atomicOr(p.status, static_cast<int32_t>(code));
@@ -156,22 +158,15 @@ gemm_normal_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_consta
     };
 
     if (warp == kWarpTma) {
-        // ================= TMA producer (one lane) =================
+        // ================= weight producer (one lane) =================
         if (lane == 0) {
-            Ring ra, rb;
+            Ring rb;
             for (uint32_t tile = blockIdx.x; tile < num_tiles && ok; tile += gridDim.x) {
                 uint32_t m_blk, n_blk;
                 tile_coords(tile, num_m, num_n, p.group_m, m_blk, n_blk);
                 const int32_t e = max(0, __ldg(p.m_indices + m_blk * BM));
                 for (uint32_t kb = 0; kb < num_kb; ++kb) {
-                    if (!ptx::mbar_wait(a_empty + ra.slot, ra.phase ^ 1, abort_flag)) { give_up(1); break; }
-                    ptx::mbar_arrive_expect_tx(a_full + ra.slot, kSlotA);
-                    const uint32_t a_dst = kOffA + ra.slot * kSlotA;
-                    ptx::tma_load_2d(smem_gen + a_dst, &tm_a, a_full + ra.slot, kb * BK, m_blk * BM);
-                    ptx::tma_load_2d(smem_gen + a_dst + kSlotA / 2, &tm_a, a_full + ra.slot, kb * BK + 64, m_blk * BM);
-                    ra.advance<kDepthA>();
-
-                    if (!ptx::mbar_wait(b_empty + rb.slot, rb.phase ^ 1, abort_flag)) { give_up(1); break; }
+                    if (!ptx::mbar_wait(b_empty + rb.slot, rb.phase ^ 1, abort_flag, pa, 0)) { give_up(1); break; }
                     ptx::mbar_arrive_expect_tx(b_full + rb.slot, kSlotB + kSlotSFB);
                     ptx::tma_load_2d(smem_gen + kOffB + rb.slot * kSlotB, &tm_b, b_full + rb.slot, kb * (BK / 2),
                                      e * p.n + n_blk * BN);
@@ -181,18 +176,35 @@ gemm_normal_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_consta
                 }
             }
         }
+    } else if (warp == kWarpTmaA) {
+        // ================= activation producer (its own lane: neither ring holds the other back) =====
+        if (lane == 0) {
+            Ring ra;
+            for (uint32_t tile = blockIdx.x; tile < num_tiles && ok; tile += gridDim.x) {
+                uint32_t m_blk, n_blk;
+                tile_coords(tile, num_m, num_n, p.group_m, m_blk, n_blk);
+                for (uint32_t kb = 0; kb < num_kb; ++kb) {
+                    if (!ptx::mbar_wait(a_empty + ra.slot, ra.phase ^ 1, abort_flag, pa, 0)) { give_up(1); break; }
+                    ptx::mbar_arrive_expect_tx(a_full + ra.slot, kSlotA);
+                    const uint32_t a_dst = kOffA + ra.slot * kSlotA;
+                    ptx::tma_load_2d(smem_gen + a_dst, &tm_a, a_full + ra.slot, kb * BK, m_blk * BM);
+                    ptx::tma_load_2d(smem_gen + a_dst + kSlotA / 2, &tm_a, a_full + ra.slot, kb * BK + 64, m_blk * BM);
+                    ra.advance<kDepthA>();
+                }
+            }
+        }
     } else if (warp == kWarpMma) {
         // ================= MMA issue (one lane) =================
         Ring rp, rb;
         uint32_t acc_phase = 0;
         constexpr uint32_t idesc = ptx::make_idesc_nvf4(BM, BN);
         for (uint32_t tile = blockIdx.x; tile < num_tiles && ok; tile += gridDim.x) {
-            if (!ptx::mbar_wait(tmem_empty, acc_phase ^ 1, abort_flag)) { give_up(1); break; }
+            if (!ptx::mbar_wait(tmem_empty, acc_phase ^ 1, abort_flag, pa, 0)) { give_up(1); break; }
             ptx::tcgen05_fence_after_sync();
             for (uint32_t kb = 0; kb < num_kb; ++kb) {
-                if (!ptx::mbar_wait(p_full + rp.slot, rp.phase, abort_flag) ||
-                    !ptx::mbar_wait(b_ready + rb.slot, rb.phase, abort_flag) ||
-                    !ptx::mbar_wait(b_full + rb.slot, rb.phase, abort_flag)) { give_up(1); break; }
+                if (!ptx::mbar_wait(p_full + rp.slot, rp.phase, abort_flag, pa, 1) ||
+                    !ptx::mbar_wait(b_ready + rb.slot, rb.phase, abort_flag, pa, 2) ||
+                    !ptx::mbar_wait(b_full + rb.slot, rb.phase, abort_flag, pa, 3)) { give_up(1); break; }
                 ptx::tcgen05_fence_after_sync();
                 if (lane == 0) {
                     const uint32_t sfa0 = smem + kOffSFA0 + rp.slot * kSlotSFA;
@@ -244,7 +256,7 @@ gemm_normal_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_consta
         Ring rb;
         for (uint32_t tile = blockIdx.x; tile < num_tiles && ok; tile += gridDim.x) {
             for (uint32_t kb = 0; kb < num_kb; ++kb) {
-                if (!ptx::mbar_wait(b_full + rb.slot, rb.phase, abort_flag)) { give_up(1); break; }
+                if (!ptx::mbar_wait(b_full + rb.slot, rb.phase, abort_flag, pa, 0)) { give_up(1); break; }
                 const uint32_t base = smem + kOffSFB + rb.slot * kSlotSFB;
 #pragma unroll
                 for (uint32_t i = 0; i < kKAtoms * (BN / 128); ++i) {
@@ -271,7 +283,7 @@ gemm_normal_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_consta
             tile_coords(tile, num_m, num_n, p.group_m, m_blk, n_blk);
             const int32_t e = max(0, __ldg(p.m_indices + m_blk * BM));
             const float g = __ldg(p.gw + e);
-            if (!ptx::mbar_wait(tmem_full, acc_phase, abort_flag)) { give_up(1); break; }
+            if (!ptx::mbar_wait(tmem_full, acc_phase, abort_flag, pa, 0)) { give_up(1); break; }
             ptx::tcgen05_fence_after_sync();
             const uint32_t row = m_blk * BM + quad * 32 + lane;
             __nv_bfloat16* drow = p.d + static_cast<int64_t>(row) * p.ldd + n_blk * BN;
@@ -304,23 +316,33 @@ gemm_normal_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_consta
         Ring ra, rp;
         for (uint32_t tile = blockIdx.x; tile < num_tiles && ok; tile += gridDim.x) {
             for (uint32_t kb = 0; kb < num_kb; ++kb) {
-                if (!ptx::mbar_wait(a_full + ra.slot, ra.phase, abort_flag) ||
-                    !ptx::mbar_wait(p_empty + rp.slot, rp.phase ^ 1, abort_flag)) { give_up(1); break; }
+                if (!ptx::mbar_wait(a_full + ra.slot, ra.phase, abort_flag, pa, 0)) { give_up(1); break; }
+                bool p_ok = true;
                 xform::transform_tile<BM, BK, kXformThreads, kResidual>(
                     smem + kOffA + ra.slot * kSlotA, smem + kOffA0 + rp.slot * kSlotA0, smem + kOffA1 + rp.slot * kSlotA0,
-                    smem + kOffSFA0 + rp.slot * kSlotSFA, smem + kOffSFA1 + rp.slot * kSlotSFA, t);
+                    smem + kOffSFA0 + rp.slot * kSlotSFA, smem + kOffSFA1 + rp.slot * kSlotSFA, t, [&] {
+                        // the tile now lives in registers: hand the BF16 slot back before the arithmetic
+                        __syncwarp();
+                        if (lane == 0) ptx::mbar_arrive(a_empty + ra.slot);
+                        p_ok = ptx::mbar_wait(p_empty + rp.slot, rp.phase ^ 1, abort_flag, pa, 1);
+                    });
+                if (!p_ok) { give_up(1); break; }
                 ptx::fence_proxy_async_smem();
                 __syncwarp();
-                if (lane == 0) {
-                    ptx::mbar_arrive(p_full + rp.slot);
-                    ptx::mbar_arrive(a_empty + ra.slot);
-                }
+                if (lane == 0) ptx::mbar_arrive(p_full + rp.slot);
                 ra.advance<kDepthA>();
                 rp.advance<kDepthP>();
             }
         }
     }
 
+    ptx::probe_add(32 + (warp < 8 ? warp : 8), ptx::probe_clock() - probe_start);
+    if (warp == 0) ptx::probe_flush(pa, 0);
+    else if (warp == 3) ptx::probe_flush(pa, 1);
+    else if (warp == 1) ptx::probe_flush(pa, 2, 3, 4, 5);
+    else if (warp == 2) ptx::probe_flush(pa, 7);
+    else if (warp < 8) ptx::probe_flush(pa, 9);
+    else ptx::probe_flush(pa, 11, 12);
     // teardown: everyone meets here, on the normal path and after a timeout alike
     ptx::tcgen05_fence_before_sync();
     __syncthreads();
@@ -390,5 +412,14 @@ int launch_gemm_normal(const void* a, int64_t lda, const void* b, const void* sf
     if (N % 256 == 0) return launch_for_bn<256>(a, lda, b, sfb, M, N, K, E, p, residual, xform_warps, num_sms, stream);
     return launch_for_bn<128>(a, lda, b, sfb, M, N, K, E, p, residual, xform_warps, num_sms, stream);
 }
+
+#ifdef NVFP4_PROBE
+extern "C" __attribute__((visibility("default"))) int nvfp4_probe_read_normal(unsigned long long* out64, int reset)
+{
+    cudaMemcpyFromSymbol(out64, ptx::g_probe, sizeof(unsigned long long) * 64);
+    if (reset) { unsigned long long z[64] = {}; cudaMemcpyToSymbol(ptx::g_probe, z, sizeof z); }
+    return 0;
+}
+#endif
 
 }  // namespace nvfp4

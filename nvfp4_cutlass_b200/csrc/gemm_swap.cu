@@ -24,37 +24,43 @@ namespace nvfp4 {
 namespace {
 
 constexpr uint32_t BW = 128;                         // weight rows per tile (MMA M)
-constexpr uint32_t kWarpTma = 0, kWarpMma = 1, kWarpSf = 2, kWarpEpi0 = 4, kNumEpiWarps = 4, kWarpXform0 = 8;
+constexpr uint32_t kWarpTma = 0, kWarpMma = 1, kWarpSf = 2, kWarpTmaA = 3, kWarpEpi0 = 4, kNumEpiWarps = 4, kWarpXform0 = 8;
 constexpr uint32_t kXformWarps = 8, kXformThreads = kXformWarps * 32, kThreads = (kWarpXform0 + kXformWarps) * 32;
 constexpr uint32_t kSmemBudget = 232448 - 1024;      // opt-in maximum minus alignment slack
 
-template <uint32_t T, uint32_t BK>
+// With the residual pass on, A0 and A1 of a token tile are stacked along the MMA N axis
+// (rows [0, T) = A0, rows [T, 2T) = A1, scales likewise in one atom): one MMA of N = 2T
+// per 64-K atom computes both passes into two column groups that the epilogue adds.  An
+// MMA of N <= 128 costs the same issue time whatever N is, and the stacked scales need one
+// tensor-memory copy instead of two, so the per-K-block issue cost almost halves.
+template <uint32_t T, uint32_t BK, bool kResidual>
 struct Cfg {
     static constexpr uint32_t kAtoms = BK / 64;
+    static constexpr uint32_t kRowsP = kResidual ? 2 * T : T;             // rows of the stacked operand tile
     static constexpr uint32_t kSlotW = BW * BK / 2, kSlotSFW = kAtoms * 512;
     static constexpr uint32_t kSlotA = T * BK * 2;
-    static constexpr uint32_t kSlotA0 = (T * BK / 2 + 1023u) & ~1023u, kSlotSFT = kAtoms * 512;
-    static constexpr uint32_t kDepthA = T >= 64 ? 2 : 3, kDepthP = 2;
-    static constexpr uint32_t kFixed = kDepthA * kSlotA + kDepthP * (2 * kSlotA0 + 2 * kSlotSFT) + 512;
+    static constexpr uint32_t kSlotP = (kRowsP * BK / 2 + 1023u) & ~1023u, kSlotSFT = kAtoms * 512;
+    static constexpr uint32_t kA1Bytes = T * (BK / 2);                     // A1 rows start T rows below A0
+    static constexpr uint32_t kSF1Bytes = T == 16 ? 256 : (T / 32) * 4;    // scale word of row T + r relative to row r
+    static constexpr uint32_t kDepthA = T >= 64 ? 3 : (T == 32 ? 5 : 6), kDepthP = 3;   // A must cover the TMA latency
+    static constexpr uint32_t kFixed = kDepthA * kSlotA + kDepthP * (kSlotP + kSlotSFT) + 512;
     static constexpr uint32_t kDepthWRaw = (kSmemBudget - kFixed) / (kSlotW + kSlotSFW);
     static constexpr uint32_t kDepthW = kDepthWRaw > 12 ? 12 : kDepthWRaw;
     static constexpr uint32_t kOffW = 0;
     static constexpr uint32_t kOffA = kOffW + kDepthW * kSlotW;
-    static constexpr uint32_t kOffA0 = kOffA + kDepthA * kSlotA;
-    static constexpr uint32_t kOffA1 = kOffA0 + kDepthP * kSlotA0;
-    static constexpr uint32_t kOffSFW = kOffA1 + kDepthP * kSlotA0;
-    static constexpr uint32_t kOffSFT0 = kOffSFW + kDepthW * kSlotSFW;
-    static constexpr uint32_t kOffSFT1 = kOffSFT0 + kDepthP * kSlotSFT;
-    static constexpr uint32_t kOffBars = kOffSFT1 + kDepthP * kSlotSFT;
+    static constexpr uint32_t kOffP = kOffA + kDepthA * kSlotA;
+    static constexpr uint32_t kOffSFW = kOffP + kDepthP * kSlotP;
+    static constexpr uint32_t kOffSFT = kOffSFW + kDepthW * kSlotSFW;
+    static constexpr uint32_t kOffBars = kOffSFT + kDepthP * kSlotSFT;
     static constexpr uint32_t kNumBars = 3 * kDepthW + 2 * kDepthA + 2 * kDepthP + 4;
     static constexpr uint32_t kSmemAlloc = kOffBars + kNumBars * 8 + 16 + 1024;
     static_assert(kDepthW >= 3, "weight ring too shallow");
     static_assert(kSmemAlloc <= 232448, "shared memory budget");
-    // tensor memory: two accumulator stages of T columns, then the three scale groups
-    static constexpr uint32_t kAccStride = T < 32 ? 32 : T;
-    static constexpr uint32_t kColSFW = 2 * kAccStride, kColSFT0 = kColSFW + 4 * kAtoms, kColSFT1 = kColSFT0 + 4 * kAtoms;
-    static constexpr uint32_t kColsUsed = kColSFT1 + 4 * kAtoms;
-    static constexpr uint32_t kTmemCols = kColsUsed <= 64 ? 64 : (kColsUsed <= 128 ? 128 : 256);
+    // tensor memory: two accumulator stages of kRowsP columns, then the two scale groups
+    static constexpr uint32_t kAccStride = kRowsP < 32 ? 32 : kRowsP;
+    static constexpr uint32_t kColSFW = 2 * kAccStride, kColSFT = kColSFW + 4 * kAtoms;
+    static constexpr uint32_t kColsUsed = kColSFT + 4 * kAtoms;
+    static constexpr uint32_t kTmemCols = kColsUsed <= 64 ? 64 : (kColsUsed <= 128 ? 128 : (kColsUsed <= 256 ? 256 : 512));
     static constexpr uint64_t kSwizzle = BK == 256 ? ptx::kSwizzle128B : ptx::kSwizzle64B;
     static constexpr uint32_t kSBO = 8 * (BK / 2);   // eight rows of one swizzle span
 };
@@ -82,7 +88,7 @@ __global__ void __launch_bounds__(kThreads, 1)
 gemm_swap_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constant__ CUtensorMap tm_w,
                  const __grid_constant__ CUtensorMap tm_sfw, const Params p)
 {
-    using C = Cfg<T, BK>;
+    using C = Cfg<T, BK, kResidual>;
     extern __shared__ uint8_t smem_raw[];
     const uint32_t smem = (ptx::smem_u32(smem_raw) + 1023u) & ~1023u;
     uint8_t* smem_gen = smem_raw + (smem - ptx::smem_u32(smem_raw));
@@ -124,9 +130,11 @@ gemm_swap_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constant
 
     // tiles: all weight-row blocks of one token block are neighbours, so the CTAs of a
     // wave share that token block's activations through L2 while streaming disjoint weights
+    const long long probe_start = ptx::probe_clock();
     const uint32_t num_n = p.n / BW, num_kb = p.k / BK;
     const uint32_t num_tiles = (p.m / T) * num_n;
     bool ok = true;
+    ptx::ProbeAcc pa;
     auto give_up = [&](uint32_t code) {
         *abort_flag = 1;
         if (p.status != nullptr) atomicOr(p.status, static_cast<int32_t>(code));
@@ -134,22 +142,32 @@ gemm_swap_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constant
     };
 
     if (warp == kWarpTma) {
+        // weight producer: runs ahead by the full depth of the W ring, whatever the transform does
         if (lane == 0) {
-            Ring rw, ra;
+            Ring rw;
             const uint64_t stream_once = ptx::l2_policy_evict_first();
             for (uint32_t tile = blockIdx.x; tile < num_tiles && ok; tile += gridDim.x) {
                 const uint32_t m_blk = tile / num_n, n_blk = tile % num_n;
                 const int32_t e = max(0, __ldg(p.m_indices + m_blk * T));
                 for (uint32_t kb = 0; kb < num_kb; ++kb) {
-                    if (!ptx::mbar_wait(w_empty + rw.slot, rw.phase ^ 1, abort_flag)) { give_up(1); break; }
+                    if (!ptx::mbar_wait(w_empty + rw.slot, rw.phase ^ 1, abort_flag, pa, 0)) { give_up(1); break; }
                     ptx::mbar_arrive_expect_tx(w_full + rw.slot, C::kSlotW + C::kSlotSFW);
                     ptx::tma_load_2d_hint(smem_gen + C::kOffW + rw.slot * C::kSlotW, &tm_w, w_full + rw.slot, kb * (BK / 2),
                                           e * p.n + n_blk * BW, stream_once);
                     ptx::tma_load_2d_hint(smem_gen + C::kOffSFW + rw.slot * C::kSlotSFW, &tm_sfw, w_full + rw.slot,
                                           n_blk * BW, e * (p.k / 64) + kb * C::kAtoms, stream_once);
                     rw.advance<C::kDepthW>();
-
-                    if (!ptx::mbar_wait(a_empty + ra.slot, ra.phase ^ 1, abort_flag)) { give_up(1); break; }
+                }
+            }
+        }
+    } else if (warp == kWarpTmaA) {
+        // activation producer (a separate thread, so a full A ring never holds the weights back)
+        if (lane == 0) {
+            Ring ra;
+            for (uint32_t tile = blockIdx.x; tile < num_tiles && ok; tile += gridDim.x) {
+                const uint32_t m_blk = tile / num_n;
+                for (uint32_t kb = 0; kb < num_kb; ++kb) {
+                    if (!ptx::mbar_wait(a_empty + ra.slot, ra.phase ^ 1, abort_flag, pa, 0)) { give_up(1); break; }
                     ptx::mbar_arrive_expect_tx(a_full + ra.slot, C::kSlotA);
 #pragma unroll
                     for (uint32_t box = 0; box < BK / 64; ++box)
@@ -162,44 +180,35 @@ gemm_swap_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constant
     } else if (warp == kWarpMma) {
         Ring rw, rp;
         uint32_t it = 0;
-        constexpr uint32_t idesc = ptx::make_idesc_nvf4(BW, T);
+        constexpr uint32_t idesc = ptx::make_idesc_nvf4(BW, C::kRowsP);
         for (uint32_t tile = blockIdx.x; tile < num_tiles && ok; tile += gridDim.x, ++it) {
             const uint32_t acc = it & 1, acc_phase = (it >> 1) & 1;
-            if (!ptx::mbar_wait(tmem_empty + acc, acc_phase ^ 1, abort_flag)) { give_up(1); break; }
+            if (!ptx::mbar_wait(tmem_empty + acc, acc_phase ^ 1, abort_flag, pa, 0)) { give_up(1); break; }
             ptx::tcgen05_fence_after_sync();
             const uint32_t tmem_acc = tmem_base + acc * C::kAccStride;
             for (uint32_t kb = 0; kb < num_kb; ++kb) {
-                if (!ptx::mbar_wait(p_full + rp.slot, rp.phase, abort_flag) ||
-                    !ptx::mbar_wait(w_ready + rw.slot, rw.phase, abort_flag) ||
-                    !ptx::mbar_wait(w_full + rw.slot, rw.phase, abort_flag)) { give_up(1); break; }
+                if (!ptx::mbar_wait(p_full + rp.slot, rp.phase, abort_flag, pa, 1) ||
+                    !ptx::mbar_wait(w_ready + rw.slot, rw.phase, abort_flag, pa, 2) ||
+                    !ptx::mbar_wait(w_full + rw.slot, rw.phase, abort_flag, pa, 3)) { give_up(1); break; }
                 ptx::tcgen05_fence_after_sync();
                 if (lane == 0) {
                     const uint32_t sfw = smem + C::kOffSFW + rw.slot * C::kSlotSFW;
-                    const uint32_t sft0 = smem + C::kOffSFT0 + rp.slot * C::kSlotSFT;
-                    const uint32_t sft1 = smem + C::kOffSFT1 + rp.slot * C::kSlotSFT;
+                    const uint32_t sft = smem + C::kOffSFT + rp.slot * C::kSlotSFT;
 #pragma unroll
                     for (uint32_t a = 0; a < C::kAtoms; ++a) {
                         ptx::tcgen05_cp_32x128b_warpx4(tmem_base + C::kColSFW + 4 * a,
                                                        ptx::make_smem_desc(sfw + a * 512, 128, ptx::kSwizzleNone));
-                        ptx::tcgen05_cp_32x128b_warpx4(tmem_base + C::kColSFT0 + 4 * a,
-                                                       ptx::make_smem_desc(sft0 + a * 512, 128, ptx::kSwizzleNone));
-                        if constexpr (kResidual)
-                            ptx::tcgen05_cp_32x128b_warpx4(tmem_base + C::kColSFT1 + 4 * a,
-                                                           ptx::make_smem_desc(sft1 + a * 512, 128, ptx::kSwizzleNone));
+                        ptx::tcgen05_cp_32x128b_warpx4(tmem_base + C::kColSFT + 4 * a,
+                                                       ptx::make_smem_desc(sft + a * 512, 128, ptx::kSwizzleNone));
                     }
                     const uint32_t w = smem + C::kOffW + rw.slot * C::kSlotW;
-                    const uint32_t a0 = smem + C::kOffA0 + rp.slot * C::kSlotA0;
-                    const uint32_t a1 = smem + C::kOffA1 + rp.slot * C::kSlotA0;
+                    const uint32_t pt = smem + C::kOffP + rp.slot * C::kSlotP;
 #pragma unroll
-                    for (uint32_t a = 0; a < C::kAtoms; ++a) {
-                        const uint64_t desc_w = ptx::make_smem_desc(w + a * 32, C::kSBO, C::kSwizzle);
-                        ptx::tcgen05_mma_nvf4(tmem_acc, desc_w, ptx::make_smem_desc(a0 + a * 32, C::kSBO, C::kSwizzle), idesc,
-                                              tmem_base + C::kColSFW + 4 * a, tmem_base + C::kColSFT0 + 4 * a,
+                    for (uint32_t a = 0; a < C::kAtoms; ++a)
+                        ptx::tcgen05_mma_nvf4(tmem_acc, ptx::make_smem_desc(w + a * 32, C::kSBO, C::kSwizzle),
+                                              ptx::make_smem_desc(pt + a * 32, C::kSBO, C::kSwizzle), idesc,
+                                              tmem_base + C::kColSFW + 4 * a, tmem_base + C::kColSFT + 4 * a,
                                               (kb | a) != 0 ? 1u : 0u);
-                        if constexpr (kResidual)
-                            ptx::tcgen05_mma_nvf4(tmem_acc, desc_w, ptx::make_smem_desc(a1 + a * 32, C::kSBO, C::kSwizzle),
-                                                  idesc, tmem_base + C::kColSFW + 4 * a, tmem_base + C::kColSFT1 + 4 * a, 1u);
-                    }
                     ptx::tcgen05_commit(p_empty + rp.slot);
                     ptx::tcgen05_commit(w_empty + rw.slot);
                     if (kb == num_kb - 1) ptx::tcgen05_commit(tmem_full + acc);
@@ -214,7 +223,7 @@ gemm_swap_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constant
         Ring rw;
         for (uint32_t tile = blockIdx.x; tile < num_tiles && ok; tile += gridDim.x) {
             for (uint32_t kb = 0; kb < num_kb; ++kb) {
-                if (!ptx::mbar_wait(w_full + rw.slot, rw.phase, abort_flag)) { give_up(1); break; }
+                if (!ptx::mbar_wait(w_full + rw.slot, rw.phase, abort_flag, pa, 0)) { give_up(1); break; }
                 const uint32_t base = smem + C::kOffSFW + rw.slot * C::kSlotSFW;
 #pragma unroll
                 for (uint32_t i = 0; i < C::kAtoms; ++i) {
@@ -242,33 +251,46 @@ gemm_swap_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constant
             const uint32_t m_blk = tile / num_n, n_blk = tile % num_n;
             const int32_t e = max(0, __ldg(p.m_indices + m_blk * T));
             const float g = __ldg(p.gw + e);
-            if (!ptx::mbar_wait(tmem_full + acc, acc_phase, abort_flag)) { give_up(1); break; }
+            if (!ptx::mbar_wait(tmem_full + acc, acc_phase, abort_flag, pa, 0)) { give_up(1); break; }
             ptx::tcgen05_fence_after_sync();
             __nv_bfloat16* dcol = p.d + static_cast<int64_t>(m_blk * T) * p.ldd + n_blk * BW + quad * 32 + lane;
             const uint32_t taddr = tmem_base + ((quad * 32) << 16) + acc * C::kAccStride;
-            if constexpr (T == 16) {
-                uint32_t v[16];
-                ptx::tmem_ld_32x32b_x16(taddr, v);
-                ptx::tmem_ld_wait();
+            // token t of the tile: columns t (pass 0) and T + t (pass 1, when present)
+            auto release = [&] {
                 ptx::tcgen05_fence_before_sync();
                 __syncwarp();
                 if (lane == 0) ptx::mbar_arrive(tmem_empty + acc);
+            };
+            if constexpr (T == 16) {
+                uint32_t v[32];
+                if constexpr (kResidual) {
+                    ptx::tmem_ld_32x32b_x32(taddr, v);
+                } else {
+                    uint32_t h[16];
+                    ptx::tmem_ld_32x32b_x16(taddr, h);
 #pragma unroll
-                for (uint32_t t = 0; t < 16; ++t) dcol[static_cast<int64_t>(t) * p.ldd] = __float2bfloat16_rn(__uint_as_float(v[t]) * g);
+                    for (uint32_t t = 0; t < 16; ++t) { v[t] = h[t]; v[16 + t] = 0u; }
+                }
+                ptx::tmem_ld_wait();
+                release();
+#pragma unroll
+                for (uint32_t t = 0; t < 16; ++t)
+                    dcol[static_cast<int64_t>(t) * p.ldd] =
+                        __float2bfloat16_rn((__uint_as_float(v[t]) + __uint_as_float(v[16 + t])) * g);
             } else {
 #pragma unroll 1
                 for (uint32_t c = 0; c < T; c += 32) {
-                    uint32_t v[32];
+                    uint32_t v[32], r[32];
                     ptx::tmem_ld_32x32b_x32(taddr + c, v);
+                    if constexpr (kResidual) ptx::tmem_ld_32x32b_x32(taddr + T + c, r);
                     ptx::tmem_ld_wait();
-                    if (c + 32 == T) {
-                        ptx::tcgen05_fence_before_sync();
-                        __syncwarp();
-                        if (lane == 0) ptx::mbar_arrive(tmem_empty + acc);
-                    }
+                    if (c + 32 == T) release();
 #pragma unroll
-                    for (uint32_t t = 0; t < 32; ++t)
-                        dcol[static_cast<int64_t>(c + t) * p.ldd] = __float2bfloat16_rn(__uint_as_float(v[t]) * g);
+                    for (uint32_t t = 0; t < 32; ++t) {
+                        float x = __uint_as_float(v[t]);
+                        if constexpr (kResidual) x += __uint_as_float(r[t]);
+                        dcol[static_cast<int64_t>(c + t) * p.ldd] = __float2bfloat16_rn(x * g);
+                    }
                 }
             }
         }
@@ -277,24 +299,33 @@ gemm_swap_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constant
         Ring ra, rp;
         for (uint32_t tile = blockIdx.x; tile < num_tiles && ok; tile += gridDim.x) {
             for (uint32_t kb = 0; kb < num_kb; ++kb) {
-                if (!ptx::mbar_wait(a_full + ra.slot, ra.phase, abort_flag) ||
-                    !ptx::mbar_wait(p_empty + rp.slot, rp.phase ^ 1, abort_flag)) { give_up(1); break; }
+                if (!ptx::mbar_wait(a_full + ra.slot, ra.phase, abort_flag, pa, 0)) { give_up(1); break; }
+                bool p_ok = true;
                 xform::transform_tile<T, BK, kXformThreads, kResidual>(
-                    smem + C::kOffA + ra.slot * C::kSlotA, smem + C::kOffA0 + rp.slot * C::kSlotA0,
-                    smem + C::kOffA1 + rp.slot * C::kSlotA0, smem + C::kOffSFT0 + rp.slot * C::kSlotSFT,
-                    smem + C::kOffSFT1 + rp.slot * C::kSlotSFT, t);
+                    smem + C::kOffA + ra.slot * C::kSlotA, smem + C::kOffP + rp.slot * C::kSlotP,
+                    smem + C::kOffP + rp.slot * C::kSlotP + C::kA1Bytes, smem + C::kOffSFT + rp.slot * C::kSlotSFT,
+                    smem + C::kOffSFT + rp.slot * C::kSlotSFT + C::kSF1Bytes, t, [&] {
+                        __syncwarp();
+                        if (lane == 0) ptx::mbar_arrive(a_empty + ra.slot);
+                        p_ok = ptx::mbar_wait(p_empty + rp.slot, rp.phase ^ 1, abort_flag, pa, 1);
+                    });
+                if (!p_ok) { give_up(1); break; }
                 ptx::fence_proxy_async_smem();
                 __syncwarp();
-                if (lane == 0) {
-                    ptx::mbar_arrive(p_full + rp.slot);
-                    ptx::mbar_arrive(a_empty + ra.slot);
-                }
+                if (lane == 0) ptx::mbar_arrive(p_full + rp.slot);
                 ra.advance<C::kDepthA>();
                 rp.advance<C::kDepthP>();
             }
         }
     }
 
+    ptx::probe_add(32 + (warp < 8 ? warp : 8), ptx::probe_clock() - probe_start);
+    if (warp == 0) ptx::probe_flush(pa, 0);
+    else if (warp == 3) ptx::probe_flush(pa, 1);
+    else if (warp == 1) ptx::probe_flush(pa, 2, 3, 4, 5);
+    else if (warp == 2) ptx::probe_flush(pa, 7);
+    else if (warp < 8) ptx::probe_flush(pa, 9);
+    else ptx::probe_flush(pa, 11, 12);
     ptx::tcgen05_fence_before_sync();
     __syncthreads();
     if (warp == kWarpMma) {
@@ -307,7 +338,7 @@ template <uint32_t T, uint32_t BK, bool kResidual>
 int launch_variant(const void* a, int64_t lda, const void* b, const void* sfb, int M, int N, int K, int E,
                    const Params& p, int num_sms, cudaStream_t stream)
 {
-    using C = Cfg<T, BK>;
+    using C = Cfg<T, BK, kResidual>;
     CUtensorMap tm_a, tm_w, tm_sfw;
     int rc = host::encode_tensor_map_2d(&tm_a, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, a, K, M, lda * 2, 64, T,
                                         CU_TENSOR_MAP_SWIZZLE_128B);
@@ -367,5 +398,14 @@ int launch_gemm_swap(const void* a, int64_t lda, const void* b, const void* sfb,
         default: return host::fail(NVFP4_E_INVALID_ARGUMENT, "token tile %d is not 16, 32 or 64", token_tile);
     }
 }
+
+#ifdef NVFP4_PROBE
+extern "C" __attribute__((visibility("default"))) int nvfp4_probe_read_swap(unsigned long long* out64, int reset)
+{
+    cudaMemcpyFromSymbol(out64, ptx::g_probe, sizeof(unsigned long long) * 64);
+    if (reset) { unsigned long long z[64] = {}; cudaMemcpyToSymbol(ptx::g_probe, z, sizeof z); }
+    return 0;
+}
+#endif
 
 }  // namespace nvfp4

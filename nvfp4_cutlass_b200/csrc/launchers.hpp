@@ -21,4 +21,7 @@ int launch_debug_decompose(const void* a, int64_t lda, int M, int K, void* q0, v
 
 int launch_mma_peak(int iters, int num_sms, double* flops_per_launch, cudaStream_t stream);
 
+int launch_mma_pattern(int iters, int num_cp, int num_mma, int mma_n, int alt_cols, int num_sms, double* flops_per_launch,
+                       cudaStream_t stream);
+
 }  // namespace nvfp4

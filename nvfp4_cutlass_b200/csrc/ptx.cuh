@@ -57,7 +57,7 @@ constexpr long long kWaitBudgetCycles = 2000000000ll;
 
 // Returns false if the phase did not complete within the budget, or if another
 // thread of the CTA already gave up (`*abort_flag != 0`).
-NVFP4_DEVICE bool mbar_wait(uint64_t* bar, uint32_t parity, volatile uint32_t* abort_flag)
+NVFP4_DEVICE bool mbar_wait_impl(uint64_t* bar, uint32_t parity, volatile uint32_t* abort_flag)
 {
     if (mbar_try_wait(bar, parity)) return true;
     const long long t0 = clock64();
@@ -68,6 +68,45 @@ NVFP4_DEVICE bool mbar_wait(uint64_t* bar, uint32_t parity, volatile uint32_t* a
         if (*abort_flag != 0 || clock64() - t0 > kWaitBudgetCycles) return false;
     }
 }
+
+// Optional per-site wait accounting for timing studies (NVFP4_PROBE is never defined in
+// the shipped build): waits add their duration to a thread-local counter that the role
+// flushes once, when it leaves its loop.
+struct ProbeAcc {
+#ifdef NVFP4_PROBE
+    long long v[4] = {0, 0, 0, 0};
+#endif
+};
+#ifdef NVFP4_PROBE
+static __device__ unsigned long long g_probe[64];
+NVFP4_DEVICE void probe_flush(const ProbeAcc& a, int s0, int s1 = -1, int s2 = -1, int s3 = -1)
+{
+    if ((threadIdx.x & 31u) != 0) return;
+    const int sites[4] = {s0, s1, s2, s3};
+    for (int i = 0; i < 4; ++i)
+        if (sites[i] >= 0) atomicAdd(&g_probe[sites[i]], static_cast<unsigned long long>(a.v[i]));
+}
+NVFP4_DEVICE void probe_add(int site, long long cycles)
+{
+    if ((threadIdx.x & 31u) == 0) atomicAdd(&g_probe[site], static_cast<unsigned long long>(cycles));
+}
+NVFP4_DEVICE long long probe_clock() { return clock64(); }
+NVFP4_DEVICE bool mbar_wait(uint64_t* bar, uint32_t parity, volatile uint32_t* abort_flag, ProbeAcc& acc, int idx)
+{
+    const long long t0 = clock64();
+    const bool ok = mbar_wait_impl(bar, parity, abort_flag);
+    acc.v[idx] += clock64() - t0;
+    return ok;
+}
+#else
+NVFP4_DEVICE void probe_flush(const ProbeAcc&, int, int = -1, int = -1, int = -1) {}
+NVFP4_DEVICE void probe_add(int, long long) {}
+NVFP4_DEVICE long long probe_clock() { return 0; }
+NVFP4_DEVICE bool mbar_wait(uint64_t* bar, uint32_t parity, volatile uint32_t* abort_flag, ProbeAcc&, int)
+{
+    return mbar_wait_impl(bar, parity, abort_flag);
+}
+#endif
 
 // ---- proxy fences -------------------------------------------------------------
 // Generic-proxy shared-memory writes must be made visible to the async proxy

@@ -60,6 +60,11 @@ struct Block16 {
 template <bool kResidual>
 NVFP4_DEVICE void decompose_block16(const uint32_t (&w)[8], Block16& out)
 {
+#ifdef NVFP4_ABLATE_XFORM   // timing experiments only (wrong results); never defined in the shipped build
+    out.q0[0] = w[0] ^ w[1]; out.q0[1] = w[2] ^ w[3]; out.q1[0] = w[4] ^ w[5]; out.q1[1] = w[6] ^ w[7];
+    out.s0 = 0x38; out.s1 = 0x20;
+    return;
+#endif
     // block amax over 16 BF16 values (pairs packed low = even element)
     uint32_t m0 = ptx::max_abs_bf16x2(w[0], w[1]);
     uint32_t m1 = ptx::max_abs_bf16x2(w[2], w[3]);
@@ -116,49 +121,56 @@ NVFP4_DEVICE void decompose_block16(const uint32_t (&w)[8], Block16& out)
 // kThreads threads with t = 0..kThreads-1.  Thread t owns row t % kRows and a run of
 // consecutive 16-blocks in it: lanes walk consecutive rows, which keeps the 128-bit
 // loads and stores free of bank conflicts under both swizzles.
-template <uint32_t kRows, uint32_t kBK, uint32_t kThreads, bool kResidual>
+//
+// The whole share of a thread is read into registers first and `on_loaded()` is called
+// before any arithmetic: the caller releases the BF16 slot there, so the slot's round
+// trip is TMA latency + a few loads instead of TMA latency + the whole transform.
+template <uint32_t kRows, uint32_t kBK, uint32_t kThreads, bool kResidual, typename OnLoaded>
 NVFP4_DEVICE void transform_tile(uint32_t a_smem, uint32_t a0_smem, uint32_t a1_smem, uint32_t sfa0_smem,
-                                 uint32_t sfa1_smem, uint32_t t)
+                                 uint32_t sfa1_smem, uint32_t t, OnLoaded&& on_loaded)
 {
     constexpr uint32_t kBlocks = kRows * (kBK / 16u);
     constexpr uint32_t kActive = kThreads < kBlocks ? kThreads : kBlocks;   // surplus threads idle
     constexpr uint32_t kBlocksPerThread = kBlocks / kActive;
     static_assert(kBlocksPerThread * kActive == kBlocks, "threads must tile the blocks");
-    if (t >= kActive) return;
-    static_assert(kBlocksPerThread == 1 || kBlocksPerThread == 2 || kBlocksPerThread == 4 || kBlocksPerThread == 8 ||
-                  kBlocksPerThread == 16, "unsupported split");
+    static_assert(kBlocksPerThread == 1 || kBlocksPerThread == 2 || kBlocksPerThread == 4 || kBlocksPerThread == 8,
+                  "unsupported split");
     static_assert(kRows % 16 == 0 && kRows <= 128 && kActive % kRows == 0, "row count");
     constexpr uint32_t kSfAtomBytes = 512u;                        // one 128-row x 4-byte atom per 64 K
+    const bool active = t < kActive;
     const uint32_t row = t % kRows;
     const uint32_t first_block = (t / kRows) * kBlocksPerThread;
 
+    uint32_t w[kBlocksPerThread][8];
+    if (active) {
+#pragma unroll
+        for (uint32_t j = 0; j < kBlocksPerThread; ++j) {
+            const uint32_t k = (first_block + j) * 16u;
+            const uint4 lo = ptx::lds128(a_smem + a_bf16_offset<kRows>(row, k));
+            const uint4 hi = ptx::lds128(a_smem + a_bf16_offset<kRows>(row, k + 8));
+            w[j][0] = lo.x; w[j][1] = lo.y; w[j][2] = lo.z; w[j][3] = lo.w;
+            w[j][4] = hi.x; w[j][5] = hi.y; w[j][6] = hi.z; w[j][7] = hi.w;
+        }
+    }
+    on_loaded();
+    if (!active) return;
+
     if constexpr (kBlocksPerThread == 1) {
-        const uint32_t k = first_block * 16u;
-        const uint4 lo = ptx::lds128(a_smem + a_bf16_offset<kRows>(row, k));
-        const uint4 hi = ptx::lds128(a_smem + a_bf16_offset<kRows>(row, k + 8));
-        const uint32_t w[8] = {lo.x, lo.y, lo.z, lo.w, hi.x, hi.y, hi.z, hi.w};
         Block16 blk;
-        decompose_block16<kResidual>(w, blk);
-        const uint32_t off = fp4_offset<kBK>(row, k & ~31u) + ((first_block & 1u) << 3);
+        decompose_block16<kResidual>(w[0], blk);
+        const uint32_t off = fp4_offset<kBK>(row, (first_block * 16u) & ~31u) + ((first_block & 1u) << 3);
         ptx::sts64(a0_smem + off, blk.q0[0], blk.q0[1]);
         if constexpr (kResidual) ptx::sts64(a1_smem + off, blk.q1[0], blk.q1[1]);
         const uint32_t addr = (first_block >> 2) * kSfAtomBytes + sf_word_offset(row) + (first_block & 3u);
         ptx::sts8(sfa0_smem + addr, blk.s0);
         if constexpr (kResidual) ptx::sts8(sfa1_smem + addr, blk.s1);
-        return;
     } else {
         uint32_t sf0 = 0, sf1 = 0;
 #pragma unroll
         for (uint32_t pair = 0; pair < kBlocksPerThread / 2; ++pair) {
             Block16 blk[2];
-#pragma unroll
-            for (uint32_t h = 0; h < 2; ++h) {
-                const uint32_t k = (first_block + pair * 2 + h) * 16u;
-                const uint4 lo = ptx::lds128(a_smem + a_bf16_offset<kRows>(row, k));
-                const uint4 hi = ptx::lds128(a_smem + a_bf16_offset<kRows>(row, k + 8));
-                const uint32_t w[8] = {lo.x, lo.y, lo.z, lo.w, hi.x, hi.y, hi.z, hi.w};
-                decompose_block16<kResidual>(w, blk[h]);
-            }
+            decompose_block16<kResidual>(w[pair * 2], blk[0]);
+            decompose_block16<kResidual>(w[pair * 2 + 1], blk[1]);
             // two blocks = 32 elements = one 16-byte chunk of each packed row
             const uint32_t off = fp4_offset<kBK>(row, (first_block + pair * 2) * 16u);
             ptx::sts128(a0_smem + off, blk[0].q0[0], blk[0].q0[1], blk[1].q0[0], blk[1].q0[1]);

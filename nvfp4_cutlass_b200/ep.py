@@ -1,0 +1,152 @@
+"""Expert-parallel MoE layer around the grouped dual-NVFP4 GEMM.
+
+The GEMM shards by expert: tiles of different experts never meet, so rank r of R owns
+experts [r*E/R, (r+1)*E/R) with their quantised weights resident, tokens stay data
+parallel, and there is one exchange before and one after the two GEMMs:
+
+  dispatch   every (token, chosen expert) pair is sent as one BF16 row to the rank that
+             owns the expert: one ``all_to_all_single`` with per-peer split sizes, after a
+             small all-to-all of the per-expert row counts
+  compute    the receiver lays the rows out expert by expert, each group padded to the
+             kernel's row alignment, and runs up-GEMM -> SwiGLU -> down-GEMM
+  combine    rows travel back through the reverse all-to-all and are summed per token
+             with the routing weights
+
+The reference project has no multi-GPU mode; this one follows the contiguous-layout
+contract of its GEMM (python/nvfp4_gemm/layout.py:155-169 there: rows grouped by expert,
+group starts aligned).  Collectives go through ``torch.distributed`` (NCCL over NVLink on
+GPUs, gloo in the CPU tests); the routing and permutation logic is plain tensor code and
+runs on either.  The GEMM is injectable so that the CPU tests can stand in a checker.
+"""
+from __future__ import annotations
+
+from dataclasses import dataclass
+from typing import Callable, Optional
+
+import torch
+import torch.distributed as dist
+
+
+def route_topk(logits: torch.Tensor, k: int):
+    """Softmax routing: top-k expert ids (T, k) and their weights renormalised to sum to 1."""
+    probs = torch.softmax(logits.float(), dim=-1)
+    w, ids = torch.topk(probs, k, dim=-1)
+    return ids, w / w.sum(dim=-1, keepdim=True)
+
+
+@dataclass
+class Dispatch:
+    """Everything the combine step needs to undo the dispatch."""
+    order: torch.Tensor          # (T*k,) pair index sorted by global expert id
+    send_counts: list            # rows sent to each rank
+    recv_counts: list            # rows received from each rank
+    place: torch.Tensor          # (rows received,) row of the padded expert-major buffer
+    group_sizes: list            # padded rows per local expert
+    real_sizes: list             # real rows per local expert
+    rows_padded: int
+
+
+def _pad(n: torch.Tensor, alignment: int) -> torch.Tensor:
+    return (n + alignment - 1) // alignment * alignment
+
+
+def plan_dispatch(topk_ids: torch.Tensor, num_experts: int, world: int, alignment: int,
+                  group: Optional[dist.ProcessGroup] = None) -> Dispatch:
+    """Sort the (token, expert) pairs by destination, exchange the count matrix and work out
+    where each received row lands in the padded expert-major buffer."""
+    e_local = num_experts // world
+    flat = topk_ids.reshape(-1)
+    order = torch.argsort(flat, stable=True)
+    counts = torch.bincount(flat, minlength=num_experts).reshape(world, e_local)   # [dest rank, local expert]
+    if world > 1:
+        recv = torch.empty_like(counts)
+        dist.all_to_all_single(recv, counts.contiguous(), group=group)             # recv[src, e] rows src sends for my expert e
+    else:
+        recv = counts
+    send_counts = counts.sum(dim=1).tolist()
+    recv_counts = recv.sum(dim=1).tolist()
+    per_expert = recv.sum(dim=0)                                                   # real rows per local expert
+    padded = _pad(per_expert, alignment)
+    starts = torch.cumsum(padded, 0) - padded                                      # padded start of each expert
+    # rows arrive source-major, expert-minor; inside expert e the rows of source s follow those of sources < s
+    before = torch.cumsum(recv, dim=0) - recv                                      # [src, e] rows of e from earlier sources
+    seg_start = (starts.unsqueeze(0) + before).reshape(-1)                         # start of segment (src, e)
+    seg_len = recv.reshape(-1)
+    seg_id = torch.repeat_interleave(torch.arange(seg_len.numel(), device=flat.device), seg_len)
+    first = torch.cumsum(seg_len, 0) - seg_len
+    place = seg_start[seg_id] + (torch.arange(seg_id.numel(), device=flat.device) - first[seg_id])
+    return Dispatch(order=order, send_counts=send_counts, recv_counts=recv_counts, place=place,
+                    group_sizes=padded.tolist(), real_sizes=per_expert.tolist(), rows_padded=int(padded.sum()))
+
+
+def _exchange(rows: torch.Tensor, send_counts, recv_counts, group) -> torch.Tensor:
+    out = rows.new_empty(sum(recv_counts), rows.shape[1])
+    dist.all_to_all_single(out, rows.contiguous(), output_split_sizes=recv_counts, input_split_sizes=send_counts,
+                           group=group)
+    return out
+
+
+def swiglu(gate_up: torch.Tensor) -> torch.Tensor:
+    """silu(gate) * up on the fused (rows, 2*I) up-projection output, BF16 in and out."""
+    gate, up = gate_up.float().chunk(2, dim=-1)
+    return (torch.nn.functional.silu(gate) * up).to(torch.bfloat16)
+
+
+class ExpertParallelMoE:
+    """One MoE layer with its experts split evenly over the ranks of ``group``.
+
+    ``up`` / ``down`` are (b, sfb, gw) triples of this rank's experts as produced by
+    ``quantize_weight_nvfp4``: up (E_local, 2*I, H), down (E_local, H, I).
+    ``gemm(a, b, sfb, gw, d, m_indices)`` defaults to the CUDA kernel.
+    """
+
+    def __init__(self, num_experts: int, hidden: int, inter: int, up, down, group=None, alignment: int = 128,
+                 gemm: Optional[Callable] = None):
+        self.group = group
+        self.world = dist.get_world_size(group) if dist.is_initialized() else 1
+        self.rank = dist.get_rank(group) if dist.is_initialized() else 0
+        if num_experts % self.world != 0:
+            raise ValueError(f"{num_experts} experts do not split evenly over {self.world} ranks")
+        self.num_experts, self.hidden, self.inter, self.alignment = num_experts, hidden, inter, alignment
+        self.e_local = num_experts // self.world
+        self.up, self.down = up, down
+        if gemm is None:
+            from . import _C
+            gemm = _C.m_grouped_bf16_dual_nvfp4_gemm_contiguous
+        self.gemm = gemm
+        self.last = None                       # Dispatch of the most recent call (for accounting)
+
+    def dispatch(self, x: torch.Tensor, topk_ids: torch.Tensor):
+        k = topk_ids.shape[1]
+        plan = plan_dispatch(topk_ids, self.num_experts, self.world, self.alignment, self.group)
+        rows = x[plan.order // k]
+        recv = _exchange(rows, plan.send_counts, plan.recv_counts, self.group) if self.world > 1 else rows
+        a = x.new_zeros(plan.rows_padded, x.shape[1])
+        a[plan.place] = recv
+        return plan, a
+
+    def experts(self, a: torch.Tensor, plan: Dispatch) -> torch.Tensor:
+        from .layout import make_m_indices
+        m_indices = make_m_indices(plan.group_sizes, device=a.device, alignment=self.alignment)
+        h = torch.empty(a.shape[0], 2 * self.inter, dtype=torch.bfloat16, device=a.device)
+        self.gemm(a, *self.up, h, m_indices)
+        act = swiglu(h)
+        out = torch.empty(a.shape[0], self.hidden, dtype=torch.bfloat16, device=a.device)
+        self.gemm(act, *self.down, out, m_indices)
+        return out
+
+    def combine(self, out: torch.Tensor, plan: Dispatch, topk_w: torch.Tensor, tokens: int) -> torch.Tensor:
+        k = topk_w.shape[1]
+        rows = out[plan.place]
+        back = _exchange(rows, plan.recv_counts, plan.send_counts, self.group) if self.world > 1 else rows
+        y = torch.zeros(tokens, self.hidden, dtype=torch.float32, device=out.device)
+        y.index_add_(0, plan.order // k, back.float() * topk_w.reshape(-1)[plan.order].unsqueeze(1))
+        return y.to(torch.bfloat16)
+
+    def forward(self, x: torch.Tensor, topk_ids: torch.Tensor, topk_w: torch.Tensor) -> torch.Tensor:
+        plan, a = self.dispatch(x, topk_ids)
+        self.last = plan
+        out = self.experts(a, plan)
+        return self.combine(out, plan, topk_w, x.shape[0])
+
+    __call__ = forward
