@@ -172,8 +172,11 @@ int nvfp4_grouped_gemm_contiguous(const void* a, int64_t lda_elems, const void* 
     }
     NVFP4_REQUIRE(tune_xform_warps == 0 || tune_xform_warps == 8 || tune_xform_warps == 16,
                   "tune_transform_warps must be 0, 8 or 16");
+    // tune_direct_a = 1: the transform reads activations straight from global memory instead of a TMA-fed
+    // shared-memory ring (measured slower on B200: 1.89 ms against 1.06 ms on the Mixtral-like shape)
+    const bool direct_a = tune && tune[9] == 1 && tune_xform_warps != 16;
     return launch_gemm_normal(a, lda_elems, b, sfb, gw, d, ldd_elems, m_indices, M, N, K, E, enable_residual_pass != 0,
-                              tune_xform_warps, tune_sched_group, dev->num_sms, device_status, s);
+                              tune_xform_warps, tune_sched_group, direct_a, dev->num_sms, device_status, s);
 }
 
 int nvfp4_debug_decompose(const void* a, int64_t lda_elems, int M, int K, int scale_policy, void* q0, void* q1,

@@ -3,11 +3,18 @@
 //   d[m, n] = bf16( gw[e(m)] * sum_k (q0*s0 + q1*s1)[m, k] * (dec(W)*S)[e(m), n, k] )
 //
 // One persistent CTA per SM works through 128 x 256 output tiles.  Per 128-wide K
-// block the roles hand data along three rings of shared-memory slots:
+// block the roles hand data along rings of shared-memory slots:
 //
-//   A ring  (BF16 activations, 32 KB/slot)    TMA warp        -> transform warps
 //   P ring  (A0, A1, SFA0, SFA1, 18 KB/slot)  transform warps -> MMA warp
 //   B ring  (FP4 weights + SFB, 18 KB/slot)   TMA warp        -> SFB-transpose warp, MMA warp
+//
+//   A ring  (BF16 activations, 32 KB/slot)    TMA warp        -> transform warps
+//
+// A second variant (tune_direct_a = 1) skips the A ring: each transform thread reads its 128
+// contiguous bytes of the next K block straight from global memory into registers while it
+// runs Algorithm 1 on the current one.  It saves a 32 KB write and a 32 KB read of shared
+// memory per K block but measured 1.8x slower on B200 (a warp's 16-byte loads touch 32
+// different lines per instruction), so TMA staging stays the default.
 //
 // and the accumulator (128 lanes x 256 FP32 columns of tensor memory) goes from
 // the MMA warp to the epilogue warps.  Each ring has its own full / empty
@@ -32,15 +39,15 @@ constexpr uint32_t kKAtoms = BK / 64;               // MMA K = 64: one scale ato
 constexpr uint32_t kSlotA = BM * BK * 2;            // 32768
 constexpr uint32_t kSlotA0 = BM * BK / 2;           // 8192
 constexpr uint32_t kSlotSFA = kKAtoms * 512;        // 1024
-constexpr uint32_t kDepthA = 3, kDepthP = 2;
 
 // BN = 256 output columns per tile whenever N allows it (one transformed activation tile
 // then feeds twice the tensor work); BN = 128 serves N that is an odd multiple of 128.
-template <uint32_t BN>
+template <uint32_t BN, bool kDirectA>
 struct Cfg {
     static constexpr uint32_t kSlotB = BN * BK / 2;                      // 16384 at BN = 256
     static constexpr uint32_t kSlotSFB = kKAtoms * (BN / 128) * 512;     // 2048
-    static constexpr uint32_t kDepthB = BN == 256 ? 4 : 6;
+    static constexpr uint32_t kDepthA = kDirectA ? 0 : 3, kDepthP = kDirectA ? 3 : 2;
+    static constexpr uint32_t kDepthB = kDirectA ? (BN == 256 ? 7 : 10) : (BN == 256 ? 4 : 6);
     static constexpr uint32_t kOffA = 0;
     static constexpr uint32_t kOffA0 = kOffA + kDepthA * kSlotA;
     static constexpr uint32_t kOffA1 = kOffA0 + kDepthP * kSlotA0;
@@ -49,7 +56,7 @@ struct Cfg {
     static constexpr uint32_t kOffSFA1 = kOffSFA0 + kDepthP * kSlotSFA;
     static constexpr uint32_t kOffSFB = kOffSFA1 + kDepthP * kSlotSFA;
     static constexpr uint32_t kOffBars = kOffSFB + kDepthB * kSlotSFB;
-    static constexpr uint32_t kNumBars = 2 * kDepthA + 2 * kDepthP + 3 * kDepthB + 2;
+    static constexpr uint32_t kNumBars = 2 * 3 + 2 * kDepthP + 3 * kDepthB + 2;
     static constexpr uint32_t kSmemBytes = kOffBars + kNumBars * 8 + 16;
     static constexpr uint32_t kSmemAlloc = kSmemBytes + 1024;            // slack to align the base to 1024 B
     static_assert(kSmemAlloc <= 232448, "shared memory budget");
@@ -63,6 +70,8 @@ constexpr uint32_t kColAcc = 0, kColSFA0 = 256, kColSFA1 = kColSFA0 + 4 * kKAtom
 constexpr uint32_t kWarpTma = 0, kWarpMma = 1, kWarpSfb = 2, kWarpTmaA = 3, kWarpEpi0 = 4, kNumEpiWarps = 4, kWarpXform0 = 8;
 
 struct Params {
+    const __nv_bfloat16* a;    // activations and their row stride (the direct-read variant)
+    int64_t lda;
     const float* gw;
     const int32_t* m_indices;
     __nv_bfloat16* d;
@@ -95,13 +104,14 @@ __device__ __forceinline__ void tile_coords(uint32_t tile, uint32_t num_m, uint3
     n_blk = r / rows;
 }
 
-template <uint32_t BN, uint32_t kXformWarps, bool kResidual>
+template <uint32_t BN, uint32_t kXformWarps, bool kResidual, bool kDirectA>
 __global__ void __launch_bounds__((kWarpXform0 + kXformWarps) * 32, 1)
 gemm_normal_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constant__ CUtensorMap tm_b,
                    const __grid_constant__ CUtensorMap tm_sfb, const Params p)
 {
-    using C = Cfg<BN>;
-    constexpr uint32_t kSlotB = C::kSlotB, kSlotSFB = C::kSlotSFB, kDepthB = C::kDepthB;
+    using C = Cfg<BN, kDirectA>;
+    constexpr uint32_t kSlotB = C::kSlotB, kSlotSFB = C::kSlotSFB, kDepthB = C::kDepthB, kDepthP = C::kDepthP;
+    constexpr uint32_t kDepthA = kDirectA ? 3 : C::kDepthA;   // barrier slots exist either way
     constexpr uint32_t kOffA = C::kOffA, kOffA0 = C::kOffA0, kOffA1 = C::kOffA1, kOffB = C::kOffB, kOffSFA0 = C::kOffSFA0,
                        kOffSFA1 = C::kOffSFA1, kOffSFB = C::kOffSFB, kOffBars = C::kOffBars;
     constexpr uint32_t kXformThreads = kXformWarps * 32;
@@ -177,8 +187,8 @@ gemm_normal_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_consta
             }
         }
     } else if (warp == kWarpTmaA) {
-        // ================= activation producer (its own lane: neither ring holds the other back) =====
-        if (lane == 0) {
+        // ================= activation producer of the staged variant (its own lane) =====
+        if (!kDirectA && lane == 0) {
             Ring ra;
             for (uint32_t tile = blockIdx.x; tile < num_tiles && ok; tile += gridDim.x) {
                 uint32_t m_blk, n_blk;
@@ -314,24 +324,61 @@ gemm_normal_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_consta
         // ================= transform: Algorithm 1 on every activation tile =================
         const uint32_t t = threadIdx.x - kWarpXform0 * 32;
         Ring ra, rp;
-        for (uint32_t tile = blockIdx.x; tile < num_tiles && ok; tile += gridDim.x) {
-            for (uint32_t kb = 0; kb < num_kb; ++kb) {
-                if (!ptx::mbar_wait(a_full + ra.slot, ra.phase, abort_flag, pa, 0)) { give_up(1); break; }
-                bool p_ok = true;
-                xform::transform_tile<BM, BK, kXformThreads, kResidual>(
-                    smem + kOffA + ra.slot * kSlotA, smem + kOffA0 + rp.slot * kSlotA0, smem + kOffA1 + rp.slot * kSlotA0,
-                    smem + kOffSFA0 + rp.slot * kSlotSFA, smem + kOffSFA1 + rp.slot * kSlotSFA, t, [&] {
-                        // the tile now lives in registers: hand the BF16 slot back before the arithmetic
-                        __syncwarp();
-                        if (lane == 0) ptx::mbar_arrive(a_empty + ra.slot);
-                        p_ok = ptx::mbar_wait(p_empty + rp.slot, rp.phase ^ 1, abort_flag, pa, 1);
-                    });
-                if (!p_ok) { give_up(1); break; }
+        if constexpr (kDirectA) {
+            // registers <- global for K block i + 1 while Algorithm 1 runs on K block i
+            using Share = xform::TileShare<BM, BK, kXformThreads>;
+            Share bufs[2];
+            uint32_t tile = blockIdx.x, kb = 0, m_blk = 0, n_blk = 0;
+            auto tile_ptr = [&](uint32_t mb, uint32_t k_block) {
+                return p.a + static_cast<int64_t>(mb) * BM * p.lda + k_block * BK;
+            };
+            if (tile < num_tiles) {
+                tile_coords(tile, num_m, num_n, p.group_m, m_blk, n_blk);
+                xform::load_tile_global(bufs[0], tile_ptr(m_blk, 0), p.lda, t);
+            }
+            auto one_block = [&](Share& cur, Share& nxt) {
+                uint32_t ntile = tile, nkb = kb + 1, nm = m_blk;
+                if (nkb == num_kb) {
+                    nkb = 0;
+                    ntile += gridDim.x;
+                    if (ntile < num_tiles) tile_coords(ntile, num_m, num_n, p.group_m, nm, n_blk);
+                }
+                if (ntile < num_tiles) xform::load_tile_global(nxt, tile_ptr(nm, nkb), p.lda, t);
+                if (!ptx::mbar_wait(p_empty + rp.slot, rp.phase ^ 1, abort_flag, pa, 1)) { give_up(1); return; }
+                xform::emit_tile<BM, BK, kXformThreads, kResidual>(
+                    cur, smem + kOffA0 + rp.slot * kSlotA0, smem + kOffA1 + rp.slot * kSlotA0,
+                    smem + kOffSFA0 + rp.slot * kSlotSFA, smem + kOffSFA1 + rp.slot * kSlotSFA, t);
                 ptx::fence_proxy_async_smem();
                 __syncwarp();
                 if (lane == 0) ptx::mbar_arrive(p_full + rp.slot);
-                ra.advance<kDepthA>();
                 rp.advance<kDepthP>();
+                tile = ntile; kb = nkb; m_blk = nm;
+            };
+            while (tile < num_tiles && ok) {
+                one_block(bufs[0], bufs[1]);
+                if (!(tile < num_tiles && ok)) break;
+                one_block(bufs[1], bufs[0]);
+            }
+        } else {
+            for (uint32_t tile = blockIdx.x; tile < num_tiles && ok; tile += gridDim.x) {
+                for (uint32_t kb = 0; kb < num_kb; ++kb) {
+                    if (!ptx::mbar_wait(a_full + ra.slot, ra.phase, abort_flag, pa, 0)) { give_up(1); break; }
+                    bool p_ok = true;
+                    xform::transform_tile<BM, BK, kXformThreads, kResidual>(
+                        smem + kOffA + ra.slot * kSlotA, smem + kOffA0 + rp.slot * kSlotA0, smem + kOffA1 + rp.slot * kSlotA0,
+                        smem + kOffSFA0 + rp.slot * kSlotSFA, smem + kOffSFA1 + rp.slot * kSlotSFA, t, [&] {
+                            // the tile now lives in registers: hand the BF16 slot back before the arithmetic
+                            __syncwarp();
+                            if (lane == 0) ptx::mbar_arrive(a_empty + ra.slot);
+                            p_ok = ptx::mbar_wait(p_empty + rp.slot, rp.phase ^ 1, abort_flag, pa, 1);
+                        });
+                    if (!p_ok) { give_up(1); break; }
+                    ptx::fence_proxy_async_smem();
+                    __syncwarp();
+                    if (lane == 0) ptx::mbar_arrive(p_full + rp.slot);
+                    ra.advance<kDepthA>();
+                    rp.advance<kDepthP>();
+                }
             }
         }
     }
@@ -352,11 +399,11 @@ gemm_normal_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_consta
     }
 }
 
-template <uint32_t BN, uint32_t kXformWarps, bool kResidual>
+template <uint32_t BN, uint32_t kXformWarps, bool kResidual, bool kDirectA>
 int launch_variant(const void* a, int64_t lda, const void* b, const void* sfb, int M, int N, int K, int E,
                    const Params& p, int num_sms, cudaStream_t stream)
 {
-    using C = Cfg<BN>;
+    using C = Cfg<BN, kDirectA>;
     CUtensorMap tm_a, tm_b, tm_sfb;
     int rc = host::encode_tensor_map_2d(&tm_a, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, a, K, M, lda * 2, 64, BM,
                                         CU_TENSOR_MAP_SWIZZLE_128B);
@@ -368,7 +415,7 @@ int launch_variant(const void* a, int64_t lda, const void* b, const void* sfb, i
                                     static_cast<uint64_t>(E) * (K / 64), static_cast<uint64_t>(N) * 4, BN, kKAtoms,
                                     CU_TENSOR_MAP_SWIZZLE_NONE);
     if (rc) return rc;
-    auto kernel = gemm_normal_kernel<BN, kXformWarps, kResidual>;
+    auto kernel = gemm_normal_kernel<BN, kXformWarps, kResidual, kDirectA>;
     static bool attr_set[host::kMaxDevices] = {};
     int dev = 0;
     NVFP4_CUDA_CHECK(cudaGetDevice(&dev));
@@ -385,13 +432,17 @@ int launch_variant(const void* a, int64_t lda, const void* b, const void* sfb, i
 
 template <uint32_t BN>
 int launch_for_bn(const void* a, int64_t lda, const void* b, const void* sfb, int M, int N, int K, int E,
-                  const Params& p, bool residual, int xform_warps, int num_sms, cudaStream_t stream)
+                  const Params& p, bool residual, int xform_warps, bool direct_a, int num_sms, cudaStream_t stream)
 {
-    if (xform_warps == 16)
-        return residual ? launch_variant<BN, 16, true>(a, lda, b, sfb, M, N, K, E, p, num_sms, stream)
-                        : launch_variant<BN, 16, false>(a, lda, b, sfb, M, N, K, E, p, num_sms, stream);
-    return residual ? launch_variant<BN, 8, true>(a, lda, b, sfb, M, N, K, E, p, num_sms, stream)
-                    : launch_variant<BN, 8, false>(a, lda, b, sfb, M, N, K, E, p, num_sms, stream);
+    if (!direct_a) {
+        if (xform_warps == 16)
+            return residual ? launch_variant<BN, 16, true, false>(a, lda, b, sfb, M, N, K, E, p, num_sms, stream)
+                            : launch_variant<BN, 16, false, false>(a, lda, b, sfb, M, N, K, E, p, num_sms, stream);
+        return residual ? launch_variant<BN, 8, true, false>(a, lda, b, sfb, M, N, K, E, p, num_sms, stream)
+                        : launch_variant<BN, 8, false, false>(a, lda, b, sfb, M, N, K, E, p, num_sms, stream);
+    }
+    return residual ? launch_variant<BN, 8, true, true>(a, lda, b, sfb, M, N, K, E, p, num_sms, stream)
+                    : launch_variant<BN, 8, false, true>(a, lda, b, sfb, M, N, K, E, p, num_sms, stream);
 }
 
 }  // namespace
@@ -399,9 +450,11 @@ int launch_for_bn(const void* a, int64_t lda, const void* b, const void* sfb, in
 // Validated arguments in, launch out.  See nvfp4_grouped_gemm_contiguous for meanings.
 int launch_gemm_normal(const void* a, int64_t lda, const void* b, const void* sfb, const float* gw, void* d,
                        int64_t ldd, const int32_t* m_indices, int M, int N, int K, int E, bool residual,
-                       int xform_warps, int group_m, int num_sms, int32_t* status, cudaStream_t stream)
+                       int xform_warps, int group_m, bool direct_a, int num_sms, int32_t* status, cudaStream_t stream)
 {
     Params p;
+    p.a = static_cast<const __nv_bfloat16*>(a);
+    p.lda = lda;
     p.gw = gw;
     p.m_indices = m_indices;
     p.d = static_cast<__nv_bfloat16*>(d);
@@ -409,8 +462,8 @@ int launch_gemm_normal(const void* a, int64_t lda, const void* b, const void* sf
     p.m = M; p.n = N; p.k = K; p.num_experts = E;
     p.group_m = group_m > 0 ? group_m : 8;
     p.status = status;
-    if (N % 256 == 0) return launch_for_bn<256>(a, lda, b, sfb, M, N, K, E, p, residual, xform_warps, num_sms, stream);
-    return launch_for_bn<128>(a, lda, b, sfb, M, N, K, E, p, residual, xform_warps, num_sms, stream);
+    if (N % 256 == 0) return launch_for_bn<256>(a, lda, b, sfb, M, N, K, E, p, residual, xform_warps, direct_a, num_sms, stream);
+    return launch_for_bn<128>(a, lda, b, sfb, M, N, K, E, p, residual, xform_warps, direct_a, num_sms, stream);
 }
 
 #ifdef NVFP4_PROBE

@@ -98,7 +98,9 @@ NVFP4_DEVICE bool mbar_wait(uint64_t* bar, uint32_t parity, volatile uint32_t* a
     acc.v[idx] += clock64() - t0;
     return ok;
 }
+NVFP4_DEVICE void probe_count(ProbeAcc& acc, int idx, long long cycles) { acc.v[idx] += cycles; }
 #else
+NVFP4_DEVICE void probe_count(ProbeAcc&, int, long long) {}
 NVFP4_DEVICE void probe_flush(const ProbeAcc&, int, int = -1, int = -1, int = -1) {}
 NVFP4_DEVICE void probe_add(int, long long) {}
 NVFP4_DEVICE long long probe_clock() { return 0; }
@@ -338,5 +340,84 @@ NVFP4_DEVICE float rcp_approx(float x)
     asm("rcp.approx.ftz.f32 %0, %1;" : "=f"(r) : "f"(x));
     return r;
 }
+
+}  // namespace nvfp4::ptx
+
+// ---- thread-block clusters: distributed shared memory and cluster-scope barriers --------
+namespace nvfp4::ptx {
+
+NVFP4_DEVICE uint32_t cluster_cta_rank() { uint32_t r; asm volatile("mov.u32 %0, %%cluster_ctarank;" : "=r"(r)); return r; }
+NVFP4_DEVICE uint32_t cluster_id_x() { uint32_t r; asm volatile("mov.u32 %0, %%clusterid.x;" : "=r"(r)); return r; }
+NVFP4_DEVICE uint32_t num_clusters_x() { uint32_t r; asm volatile("mov.u32 %0, %%nclusterid.x;" : "=r"(r)); return r; }
+
+// Address of the same shared-memory location in CTA `rank` of the cluster.
+NVFP4_DEVICE uint32_t map_to_cta(uint32_t smem_addr, uint32_t rank)
+{
+    uint32_t r;
+    asm volatile("mapa.shared::cluster.u32 %0, %1, %2;" : "=r"(r) : "r"(smem_addr), "r"(rank));
+    return r;
+}
+NVFP4_DEVICE void cluster_sync()
+{
+    asm volatile("barrier.cluster.arrive.release.aligned;\n barrier.cluster.wait.acquire.aligned;" ::: "memory");
+}
+// Ordinary stores into another CTA's shared memory.
+NVFP4_DEVICE void st_cluster128(uint32_t addr, uint32_t a, uint32_t b, uint32_t c, uint32_t d)
+{
+    asm volatile("st.shared::cluster.v4.u32 [%0], {%1, %2, %3, %4};" ::"r"(addr), "r"(a), "r"(b), "r"(c), "r"(d) : "memory");
+}
+NVFP4_DEVICE void st_cluster32(uint32_t addr, uint32_t a) { asm volatile("st.shared::cluster.u32 [%0], %1;" ::"r"(addr), "r"(a) : "memory"); }
+NVFP4_DEVICE void st_cluster16(uint32_t addr, uint32_t a)
+{
+    asm volatile("st.shared::cluster.u16 [%0], %1;" ::"r"(addr), "h"(static_cast<unsigned short>(a)) : "memory");
+}
+// Arrive on an mbarrier of any CTA of the cluster (address from map_to_cta), releasing
+// this thread's earlier writes at cluster scope.
+NVFP4_DEVICE void mbar_arrive_cluster(uint32_t cluster_addr)
+{
+    asm volatile("mbarrier.arrive.release.cluster.shared::cluster.b64 _, [%0];" ::"r"(cluster_addr) : "memory");
+}
+NVFP4_DEVICE bool mbar_try_wait_cluster(uint64_t* bar, uint32_t parity)
+{
+    uint32_t ok;
+    asm volatile(
+        "{\n .reg .pred p;\n mbarrier.try_wait.parity.acquire.cluster.shared::cta.b64 p, [%1], %2;\n selp.u32 %0, 1, 0, p;\n}"
+        : "=r"(ok)
+        : "r"(smem_u32(bar)), "r"(parity)
+        : "memory");
+    return ok != 0;
+}
+// Bounded wait that acquires at cluster scope (the data was written by other CTAs).
+NVFP4_DEVICE bool mbar_wait_cluster(uint64_t* bar, uint32_t parity, volatile uint32_t* abort_flag)
+{
+    if (mbar_try_wait_cluster(bar, parity)) return true;
+    const long long t0 = clock64();
+    for (;;) {
+#pragma unroll 1
+        for (int i = 0; i < 32; ++i)
+            if (mbar_try_wait_cluster(bar, parity)) return true;
+        if (*abort_flag != 0 || clock64() - t0 > kWaitBudgetCycles) return false;
+    }
+}
+NVFP4_DEVICE bool mbar_wait_cluster(uint64_t* bar, uint32_t parity, volatile uint32_t* abort_flag, ProbeAcc& acc, int idx)
+{
+    const long long t0 = probe_clock();
+    const bool ok = mbar_wait_cluster(bar, parity, abort_flag);
+    probe_count(acc, idx, probe_clock() - t0);
+    return ok;
+}
+// All earlier tcgen05 operations of this thread arrive, when they retire, on the barrier at
+// this offset in every CTA of the cluster named by `cta_mask`.
+NVFP4_DEVICE void tcgen05_commit_cluster(uint64_t* bar, uint16_t cta_mask)
+{
+    asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.multicast::cluster.b64 [%0], %1;"
+                 ::"r"(smem_u32(bar)), "h"(cta_mask)
+                 : "memory");
+}
+NVFP4_DEVICE void fence_proxy_async_all() { asm volatile("fence.proxy.async;" ::: "memory"); }
+// Generic-proxy writes into the cluster's shared memory -> async proxy (tensor-core operand reads).
+NVFP4_DEVICE void fence_proxy_async_cluster_smem() { asm volatile("fence.proxy.async.shared::cluster;" ::: "memory"); }
+// Makes this thread's earlier writes (remote shared memory included) visible cluster-wide.
+NVFP4_DEVICE void fence_acq_rel_cluster() { asm volatile("fence.acq_rel.cluster;" ::: "memory"); }
 
 }  // namespace nvfp4::ptx

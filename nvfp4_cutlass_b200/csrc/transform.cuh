@@ -115,49 +115,78 @@ NVFP4_DEVICE void decompose_block16(const uint32_t (&w)[8], Block16& out)
 }
 
 // ---- one activation tile ------------------------------------------------------------
-// kRows x kBK BF16 (as TMA landed it at `a_smem`, in boxes of 64 columns) -> A0 / A1
-// (packed FP4, one swizzle span per row) and the SFA0 / SFA1 atoms (one 512-byte atom
-// per 64 K elements; rows past kRows of an atom are left untouched).  Called by
-// kThreads threads with t = 0..kThreads-1.  Thread t owns row t % kRows and a run of
-// consecutive 16-blocks in it: lanes walk consecutive rows, which keeps the 128-bit
-// loads and stores free of bank conflicts under both swizzles.
+// kRows x kBK BF16 -> A0 / A1 (packed FP4, one swizzle span per row) and the SFA0 / SFA1
+// atoms (one 512-byte atom per 64 K elements; rows past kRows of an atom are left
+// untouched).  kThreads threads cooperate, t = 0..kThreads-1.  Thread t owns row
+// t % kRows and a run of consecutive 16-blocks in it: lanes walk consecutive rows, which
+// keeps the 128-bit shared-memory accesses free of bank conflicts under both swizzles and
+// makes every thread's global read one contiguous run of whole cache lines.
 //
-// The whole share of a thread is read into registers first and `on_loaded()` is called
-// before any arithmetic: the caller releases the BF16 slot there, so the slot's round
-// trip is TMA latency + a few loads instead of TMA latency + the whole transform.
-template <uint32_t kRows, uint32_t kBK, uint32_t kThreads, bool kResidual, typename OnLoaded>
-NVFP4_DEVICE void transform_tile(uint32_t a_smem, uint32_t a0_smem, uint32_t a1_smem, uint32_t sfa0_smem,
-                                 uint32_t sfa1_smem, uint32_t t, OnLoaded&& on_loaded)
-{
-    constexpr uint32_t kBlocks = kRows * (kBK / 16u);
-    constexpr uint32_t kActive = kThreads < kBlocks ? kThreads : kBlocks;   // surplus threads idle
-    constexpr uint32_t kBlocksPerThread = kBlocks / kActive;
+// The work is split in two so that callers can overlap: `load_*` brings a thread's share
+// into registers (from a TMA-landed shared-memory tile, or straight from global memory),
+// `emit_tile` runs Algorithm 1 on the registers and writes the products.
+template <uint32_t kRows, uint32_t kBK, uint32_t kThreads>
+struct TileShare {
+    static constexpr uint32_t kBlocks = kRows * (kBK / 16u);
+    static constexpr uint32_t kActive = kThreads < kBlocks ? kThreads : kBlocks;   // surplus threads idle
+    static constexpr uint32_t kBlocksPerThread = kBlocks / kActive;
     static_assert(kBlocksPerThread * kActive == kBlocks, "threads must tile the blocks");
     static_assert(kBlocksPerThread == 1 || kBlocksPerThread == 2 || kBlocksPerThread == 4 || kBlocksPerThread == 8,
                   "unsupported split");
     static_assert(kRows % 16 == 0 && kRows <= 128 && kActive % kRows == 0, "row count");
-    constexpr uint32_t kSfAtomBytes = 512u;                        // one 128-row x 4-byte atom per 64 K
-    const bool active = t < kActive;
-    const uint32_t row = t % kRows;
-    const uint32_t first_block = (t / kRows) * kBlocksPerThread;
-
     uint32_t w[kBlocksPerThread][8];
-    if (active) {
+};
+
+// From the tile as TMA landed it at `a_smem` (boxes of 64 columns, 128-byte swizzle).
+template <uint32_t kRows, uint32_t kBK, uint32_t kThreads>
+NVFP4_DEVICE void load_tile_smem(TileShare<kRows, kBK, kThreads>& s, uint32_t a_smem, uint32_t t)
+{
+    using S = TileShare<kRows, kBK, kThreads>;
+    if (t >= S::kActive) return;
+    const uint32_t row = t % kRows, first_block = (t / kRows) * S::kBlocksPerThread;
 #pragma unroll
-        for (uint32_t j = 0; j < kBlocksPerThread; ++j) {
-            const uint32_t k = (first_block + j) * 16u;
-            const uint4 lo = ptx::lds128(a_smem + a_bf16_offset<kRows>(row, k));
-            const uint4 hi = ptx::lds128(a_smem + a_bf16_offset<kRows>(row, k + 8));
-            w[j][0] = lo.x; w[j][1] = lo.y; w[j][2] = lo.z; w[j][3] = lo.w;
-            w[j][4] = hi.x; w[j][5] = hi.y; w[j][6] = hi.z; w[j][7] = hi.w;
-        }
+    for (uint32_t j = 0; j < S::kBlocksPerThread; ++j) {
+        const uint32_t k = (first_block + j) * 16u;
+        const uint4 lo = ptx::lds128(a_smem + a_bf16_offset<kRows>(row, k));
+        const uint4 hi = ptx::lds128(a_smem + a_bf16_offset<kRows>(row, k + 8));
+        s.w[j][0] = lo.x; s.w[j][1] = lo.y; s.w[j][2] = lo.z; s.w[j][3] = lo.w;
+        s.w[j][4] = hi.x; s.w[j][5] = hi.y; s.w[j][6] = hi.z; s.w[j][7] = hi.w;
     }
-    on_loaded();
-    if (!active) return;
+}
+
+// Straight from global memory: `tile` points at element (first row of the tile, first K of
+// the block); rows are `lda` elements apart.  Read-only, streaming (no L1 allocation: the
+// reuse of an activation tile is across CTAs, through L2).
+template <uint32_t kRows, uint32_t kBK, uint32_t kThreads>
+NVFP4_DEVICE void load_tile_global(TileShare<kRows, kBK, kThreads>& s, const void* tile, int64_t lda, uint32_t t)
+{
+    using S = TileShare<kRows, kBK, kThreads>;
+    if (t >= S::kActive) return;
+    const uint32_t row = t % kRows, first_block = (t / kRows) * S::kBlocksPerThread;
+    const char* src = static_cast<const char*>(tile) + (static_cast<int64_t>(row) * lda + first_block * 16) * 2;
+#pragma unroll
+    for (uint32_t j = 0; j < S::kBlocksPerThread; ++j) {
+#pragma unroll
+        for (uint32_t h = 0; h < 2; ++h)
+            asm volatile("ld.global.nc.L1::no_allocate.v4.u32 {%0, %1, %2, %3}, [%4];"
+                         : "=r"(s.w[j][4 * h]), "=r"(s.w[j][4 * h + 1]), "=r"(s.w[j][4 * h + 2]), "=r"(s.w[j][4 * h + 3])
+                         : "l"(src + j * 32 + h * 16));
+    }
+}
+
+template <uint32_t kRows, uint32_t kBK, uint32_t kThreads, bool kResidual>
+NVFP4_DEVICE void emit_tile(const TileShare<kRows, kBK, kThreads>& s, uint32_t a0_smem, uint32_t a1_smem,
+                            uint32_t sfa0_smem, uint32_t sfa1_smem, uint32_t t)
+{
+    using S = TileShare<kRows, kBK, kThreads>;
+    constexpr uint32_t kBlocksPerThread = S::kBlocksPerThread;
+    constexpr uint32_t kSfAtomBytes = 512u;                        // one 128-row x 4-byte atom per 64 K
+    if (t >= S::kActive) return;
+    const uint32_t row = t % kRows, first_block = (t / kRows) * kBlocksPerThread;
 
     if constexpr (kBlocksPerThread == 1) {
         Block16 blk;
-        decompose_block16<kResidual>(w[0], blk);
+        decompose_block16<kResidual>(s.w[0], blk);
         const uint32_t off = fp4_offset<kBK>(row, (first_block * 16u) & ~31u) + ((first_block & 1u) << 3);
         ptx::sts64(a0_smem + off, blk.q0[0], blk.q0[1]);
         if constexpr (kResidual) ptx::sts64(a1_smem + off, blk.q1[0], blk.q1[1]);
@@ -169,8 +198,8 @@ NVFP4_DEVICE void transform_tile(uint32_t a_smem, uint32_t a0_smem, uint32_t a1_
 #pragma unroll
         for (uint32_t pair = 0; pair < kBlocksPerThread / 2; ++pair) {
             Block16 blk[2];
-            decompose_block16<kResidual>(w[pair * 2], blk[0]);
-            decompose_block16<kResidual>(w[pair * 2 + 1], blk[1]);
+            decompose_block16<kResidual>(s.w[pair * 2], blk[0]);
+            decompose_block16<kResidual>(s.w[pair * 2 + 1], blk[1]);
             // two blocks = 32 elements = one 16-byte chunk of each packed row
             const uint32_t off = fp4_offset<kBK>(row, (first_block + pair * 2) * 16u);
             ptx::sts128(a0_smem + off, blk[0].q0[0], blk[0].q0[1], blk[1].q0[0], blk[1].q0[1]);
@@ -192,6 +221,18 @@ NVFP4_DEVICE void transform_tile(uint32_t a_smem, uint32_t a0_smem, uint32_t a1_
             }
         }
     }
+}
+
+// Shared-memory tile in, products out; `on_loaded()` runs between the reads and the
+// arithmetic (the caller releases the BF16 slot there).
+template <uint32_t kRows, uint32_t kBK, uint32_t kThreads, bool kResidual, typename OnLoaded>
+NVFP4_DEVICE void transform_tile(uint32_t a_smem, uint32_t a0_smem, uint32_t a1_smem, uint32_t sfa0_smem,
+                                 uint32_t sfa1_smem, uint32_t t, OnLoaded&& on_loaded)
+{
+    TileShare<kRows, kBK, kThreads> s;
+    load_tile_smem(s, a_smem, t);
+    on_loaded();
+    emit_tile<kRows, kBK, kThreads, kResidual>(s, a0_smem, a1_smem, sfa0_smem, sfa1_smem, t);
 }
 
 }  // namespace nvfp4::xform

@@ -1,0 +1,123 @@
+"""Benchmark leg of the expert-parallel MoE layer (called by bench.py for workload c5).
+
+Qwen3-235B-A22B-like layer: E = 128 experts split evenly over the ranks, 16384 tokens per
+rank (weak scaling), top-8 softmax routing of Gaussian logits, hidden 4096, expert
+intermediate 1536 (up N = 3072 = 2 x 1536, K = 4096; down N = 4096, K = 1536), Student-t(4)
+activations clamped to +-2688.  A step is dispatch all-to-all -> up GEMM -> SwiGLU -> down
+GEMM -> combine all-to-all + weighted sum.  ``value`` is the logical GEMM TFLOP/s of the
+whole job: sum over ranks of 2 * real rows * (N_up * K_up + N_down * K_down), divided by
+the slowest rank's device time.
+"""
+from __future__ import annotations
+
+import json
+import os
+import statistics
+import time
+
+import torch
+import torch.distributed as dist
+
+E_TOTAL, HIDDEN, INTER, TOKENS, TOP_K = 128, 4096, 1536, 16384, 8
+
+
+def run(args, workload: str, world: int, rank: int, local: int) -> None:
+    import bench
+    import nvfp4_gemm
+    from .ep import ExpertParallelMoE, route_topk
+
+    dev = torch.device("cuda", local)
+    if world > 1 and not dist.is_initialized():
+        dist.init_process_group("nccl", device_id=dev)
+    steps = args.steps or 20
+    warmup = max(args.warmup if args.warmup is not None else 3, 3)
+    e_local = E_TOTAL // world
+    tokens = TOKENS
+
+    # this rank's experts, random-init BF16 ~ N(0, 0.02), quantised on the device
+    up = bench.build_weights(e_local, 2 * INTER, HIDDEN, dev, seed=20 + rank)
+    down = bench.build_weights(e_local, HIDDEN, INTER, dev, seed=40 + rank)
+    g = torch.Generator(device=dev).manual_seed(10 + rank)
+    z = torch.randn(tokens, HIDDEN, generator=g, device=dev)
+    chi = torch.randn(tokens, HIDDEN, 4, generator=g, device=dev).pow(2).mean(-1).sqrt()
+    x = (z / chi).clamp(-2688.0, 2688.0).to(torch.bfloat16)
+    del z, chi
+    logits = torch.randn(tokens, E_TOTAL, generator=torch.Generator(device=dev).manual_seed(30 + rank), device=dev)
+    ids, wts = route_topk(logits, TOP_K)
+    layer = ExpertParallelMoE(E_TOTAL, HIDDEN, INTER, up, down, alignment=128)
+
+    def barrier():
+        if world > 1:
+            dist.barrier()
+
+    def step():
+        return layer(x, ids, wts)
+
+    sampler = bench.ClockSampler(local)
+    sampler.start()
+    ms, t0, t1 = bench.timed(step, steps, warmup, barrier)
+    clocks = sampler.stop(t0, t1)
+
+    # per-phase device times on this rank (one extra, untimed pass)
+    ev = [torch.cuda.Event(enable_timing=True) for _ in range(4)]
+    ev[0].record()
+    plan, a = layer.dispatch(x, ids)
+    ev[1].record()
+    out = layer.experts(a, plan)
+    ev[2].record()
+    y = layer.combine(out, plan, wts, tokens)
+    ev[3].record()
+    torch.cuda.synchronize()
+    phases = [ev[i].elapsed_time(ev[i + 1]) for i in range(3)]
+    real_rows = float(sum(plan.real_sizes))
+
+    # end to end: activations and routing come from pinned host memory, the layer output goes back
+    x_host, ids_host, w_host = x.cpu().pin_memory(), ids.cpu().pin_memory(), wts.cpu().pin_memory()
+    y_host = torch.empty(tokens, HIDDEN, dtype=torch.bfloat16).pin_memory()
+    xd, idd, wd = torch.empty_like(x), torch.empty_like(ids), torch.empty_like(wts)
+
+    def e2e_step():
+        xd.copy_(x_host, non_blocking=True)
+        idd.copy_(ids_host, non_blocking=True)
+        wd.copy_(w_host, non_blocking=True)
+        y_host.copy_(layer(xd, idd, wd), non_blocking=True)
+
+    e2e_ms, _, _ = bench.timed(e2e_step, max(3, min(steps, 10)), 3, barrier)
+
+    flops_rank = 2.0 * real_rows * (2 * INTER * HIDDEN + HIDDEN * INTER)
+    stats = torch.tensor([ms, e2e_ms, flops_rank, phases[0], phases[1], phases[2]], dtype=torch.float64, device=dev)
+    if world > 1:
+        mx = stats.clone()
+        dist.all_reduce(mx, op=dist.ReduceOp.MAX)
+        sm = stats.clone()
+        dist.all_reduce(sm, op=dist.ReduceOp.SUM)
+    else:
+        mx, sm = stats, stats
+    ms_max, e2e_max, flops_all = float(mx[0]), float(mx[1]), float(sm[2])
+    if rank == 0:
+        fp4_peak = bench.measure_fp4_peak()
+        value = flops_all / (ms_max * 1e-3) / 1e12
+        gemm_ms = float(mx[4])
+        achieved = 2.0 * flops_rank / (gemm_ms * 1e-3) / 1e12
+        off_rank_bytes = tokens * TOP_K * HIDDEN * 2 * (world - 1) / world
+        line = {"metric": "grouped_gemm_logical_tflops", "value": value, "unit": "TFLOP/s", "n_gpus": world, "steps": steps,
+                "warmup": warmup, "ms_per_step": ms_max, "higher_is_better": True, "scaling": "weak", "vs_baseline": None,
+                "dtype": "nvfp4 (e2m1 x ue4m3 block 16), fp32 accumulate, bf16 in/out", "data": "synthetic",
+                "config": {"workload": f"expert-parallel MoE layer: E={E_TOTAL} over {world} ranks, {TOKENS} tokens/rank, top-{TOP_K}, "
+                                       f"up N={2 * INTER} K={HIDDEN}, down N={HIDDEN} K={INTER}", "name": "c5",
+                           "parallelism": f"ep{world}", "l2": "operands larger than L2, no flush",
+                           "step": "dispatch all-to-all, up GEMM, SwiGLU (torch op), down GEMM, combine all-to-all"},
+                "roofline": {"bound": "tensor", "achieved": achieved, "peak": fp4_peak, "unit": "TFLOP/s",
+                             "frac": achieved / fp4_peak, "traffic": None,
+                             "note": "the two grouped GEMMs + SwiGLU glue of rank 0, both NVFP4 passes counted",
+                             "peak_source": "resident-operand tcgen05 kind::mxf4nvf4 loop measured in this run"},
+                "phases_ms_max_over_ranks": {"dispatch": float(mx[3]), "experts": gemm_ms, "combine": float(mx[5])},
+                "all_to_all_bytes_per_rank_per_direction": off_rank_bytes,
+                "e2e": {"value": flops_all / (e2e_max * 1e-3) / 1e12, "unit": "TFLOP/s", "ms_per_step": e2e_max,
+                        "h2d_bytes_per_step": x_host.numel() * 2 + ids_host.numel() * 8 + w_host.numel() * 4,
+                        "d2h_bytes_per_step": y_host.numel() * 2},
+                "gpu_launches": 2 * steps, "clocks": clocks}
+        print(json.dumps(line))
+    if world > 1:
+        dist.barrier()
+        dist.destroy_process_group()

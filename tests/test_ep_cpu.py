@@ -1,0 +1,106 @@
+"""CPU: the expert-parallel layer's routing, dispatch, padding and combine logic on gloo
+ranks (world size 1 and 2), with the CPU oracle standing in for the CUDA GEMM."""
+import os
+import socket
+import sys
+
+import pytest
+import torch
+import torch.distributed as dist
+import torch.multiprocessing as mp
+
+from conftest import ROOT
+
+
+def _oracle_gemm(a, b, sfb, gw, d, m_indices, **_):
+    import oracle
+    d.copy_(oracle.grouped_gemm(a, b, sfb, gw, m_indices, d.shape[1]))
+
+
+def _make_layer_inputs(num_experts, hidden, inter, tokens, top_k, seed):
+    g = torch.Generator().manual_seed(seed)
+    w_up = (torch.randn(num_experts, 2 * inter, hidden, generator=g) * 0.05).to(torch.bfloat16)
+    w_down = (torch.randn(num_experts, hidden, inter, generator=g) * 0.05).to(torch.bfloat16)
+    return w_up, w_down
+
+
+def _dense_reference(x, ids, wts, w_up, w_down, alignment):
+    """Single-process statement of the same layer: per expert, oracle GEMMs on its rows."""
+    import oracle
+    from nvfp4_cutlass_b200.ep import swiglu
+    y = torch.zeros(x.shape[0], x.shape[1], dtype=torch.float32)
+    for e in range(w_up.shape[0]):
+        tok, slot = torch.nonzero(ids == e, as_tuple=True)
+        if tok.numel() == 0:
+            continue
+        up = oracle.quantize_weight(w_up[e:e + 1])
+        down = oracle.quantize_weight(w_down[e:e + 1])
+        mi = torch.zeros(tok.numel(), dtype=torch.int32)
+        h = oracle.grouped_gemm(x[tok], *up, mi, w_up.shape[1])
+        o = oracle.grouped_gemm(swiglu(h), *down, mi, w_down.shape[1])
+        y.index_add_(0, tok, o.float() * wts[tok, slot].unsqueeze(1))
+    return y.to(torch.bfloat16)
+
+
+def _worker(rank, world, port, results):
+    sys.path.insert(0, ROOT)
+    os.environ.update(MASTER_ADDR="127.0.0.1", MASTER_PORT=str(port))
+    dist.init_process_group("gloo", rank=rank, world_size=world)
+    try:
+        import oracle
+        from nvfp4_cutlass_b200.ep import ExpertParallelMoE, route_topk
+        num_experts, hidden, inter, tokens, top_k, alignment = 8, 128, 64, 40, 2, 16
+        w_up, w_down = _make_layer_inputs(num_experts, hidden, inter, tokens, top_k, seed=5)
+        e_local = num_experts // world
+        lo = rank * e_local
+        up = oracle.quantize_weight(w_up[lo:lo + e_local])
+        down = oracle.quantize_weight(w_down[lo:lo + e_local])
+        g = torch.Generator().manual_seed(100 + rank)
+        x = torch.randn(tokens, hidden, generator=g).to(torch.bfloat16)
+        logits = torch.randn(tokens, num_experts, generator=g)
+        logits[:, 5] = -1e9                                   # an expert nobody routes to
+        ids, wts = route_topk(logits, top_k)
+        layer = ExpertParallelMoE(num_experts, hidden, inter, up, down, alignment=alignment, gemm=_oracle_gemm)
+        y = layer(x, ids, wts)
+        ref = _dense_reference(x, ids, wts, w_up, w_down, alignment)
+        err = float((y.float() - ref.float()).norm() / ref.float().norm())
+        plan = layer.last
+        ok_pad = all(s % alignment == 0 for s in plan.group_sizes) and plan.rows_padded == sum(plan.group_sizes)
+        results[rank] = (err, ok_pad, sum(plan.real_sizes))
+    finally:
+        dist.destroy_process_group()
+
+
+def _free_port():
+    with socket.socket() as s:
+        s.bind(("127.0.0.1", 0))
+        return s.getsockname()[1]
+
+
+@pytest.mark.parametrize("world", [1, 2])
+def test_expert_parallel_layer_matches_dense(world):
+    mgr = mp.Manager()
+    results = mgr.dict()
+    mp.spawn(_worker, args=(world, _free_port(), results), nprocs=world, join=True)
+    assert len(results) == world
+    total_rows = 0
+    for rank in range(world):
+        err, ok_pad, rows = results[rank]
+        assert ok_pad
+        assert err < 2e-2, err          # same rows, same codes; only BF16 rounding of the weighted sum differs
+        total_rows += rows
+    assert total_rows == world * 40 * 2  # every (token, expert) pair arrived somewhere exactly once
+
+
+def test_plan_dispatch_places_rows_by_expert():
+    from nvfp4_cutlass_b200.ep import plan_dispatch
+    ids = torch.tensor([[0, 3], [3, 1], [2, 3], [0, 1]])
+    plan = plan_dispatch(ids, num_experts=4, world=1, alignment=4)
+    assert plan.real_sizes == [2, 2, 1, 3] and plan.group_sizes == [4, 4, 4, 4]
+    flat = ids.reshape(-1)
+    experts_in_order = flat[plan.order]
+    assert experts_in_order.tolist() == sorted(flat.tolist())
+    # rows of expert e land in [4e, 4e + real)
+    for pos, e in zip(plan.place.tolist(), experts_in_order.tolist()):
+        assert 4 * e <= pos < 4 * e + plan.real_sizes[e]
+    assert len(set(plan.place.tolist())) == flat.numel()

@@ -170,6 +170,34 @@ def test_gemm_matches_oracle(dev, oracle, shape, residual):
         assert rel_l2(d, truth) <= rel_l2(want, truth) * 1.02 + 1e-4     # no worse than the reference chain
 
 
+@pytest.mark.parametrize("tune", [dict(tune_direct_a=1), dict(tune_transform_warps=16), dict(tune_sched_group=4)])
+@pytest.mark.parametrize("residual", [True, False])
+def test_gemm_kernel_variants_agree(dev, oracle, tune, residual):
+    """The direct-global-read transform, the 16-warp transform and another tile order against the
+    oracle; K blocks odd in number and more tiles than SMs so that every ring wraps."""
+    e, rows, n, k = 3, 256, 2048, 640
+    a, w = make_case(e, rows, n, k, seed=31)
+    b, sfb, gw = nvfp4_gemm.quantize_weight_nvfp4(w.to(dev))
+    mi = nvfp4_gemm.make_m_indices([rows] * e)
+    d = run_gemm(dev, a, b, sfb, gw, mi, n, enable_residual_pass=residual, **tune)
+    want = oracle.grouped_gemm(a, b.cpu(), sfb.cpu(), gw.cpu(), mi, n, mode="dual" if residual else "single")
+    assert rel_l2(d, want) < REL_L2_VS_ORACLE
+
+
+def test_gemm_many_tiles_ragged_experts(dev, oracle):
+    """More tiles than SMs, ragged expert sizes: every CTA loops over several tiles."""
+    sizes = [128, 384, 256, 128, 512, 128, 256, 640]
+    n, k = 4096, 256
+    g = torch.Generator().manual_seed(99)
+    a = torch.randn(sum(sizes), k, generator=g).to(torch.bfloat16)
+    w = (torch.randn(len(sizes), n, k, generator=g) * 0.02).to(torch.bfloat16)
+    b, sfb, gw = nvfp4_gemm.quantize_weight_nvfp4(w.to(dev))
+    mi = nvfp4_gemm.make_m_indices(sizes)
+    d = run_gemm(dev, a, b, sfb, gw, mi, n)
+    want = oracle.grouped_gemm(a, b.cpu(), sfb.cpu(), gw.cpu(), mi, n)
+    assert rel_l2(d, want) < REL_L2_VS_ORACLE
+
+
 def test_gemm_rejects_n_below_contract(dev):
     g = load_golden("gemm.npz")                       # E=2 x 32 rows: pad each expert to 128 rows
     a = bf16_from_bits(g["a_bits"])
