@@ -195,10 +195,14 @@ gemm_normal_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_consta
                 tile_coords(tile, num_m, num_n, p.group_m, m_blk, n_blk);
                 for (uint32_t kb = 0; kb < num_kb; ++kb) {
                     if (!ptx::mbar_wait(a_empty + ra.slot, ra.phase ^ 1, abort_flag, pa, 0)) { give_up(1); break; }
+#ifdef NVFP4_ABLATE_A_TMA   // timing experiments only (wrong results); never defined in the shipped build
+                    ptx::mbar_arrive(a_full + ra.slot);
+#else
                     ptx::mbar_arrive_expect_tx(a_full + ra.slot, kSlotA);
                     const uint32_t a_dst = kOffA + ra.slot * kSlotA;
                     ptx::tma_load_2d(smem_gen + a_dst, &tm_a, a_full + ra.slot, kb * BK, m_blk * BM);
                     ptx::tma_load_2d(smem_gen + a_dst + kSlotA / 2, &tm_a, a_full + ra.slot, kb * BK + 64, m_blk * BM);
+#endif
                     ra.advance<kDepthA>();
                 }
             }

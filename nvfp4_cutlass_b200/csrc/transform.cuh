@@ -144,6 +144,11 @@ NVFP4_DEVICE void load_tile_smem(TileShare<kRows, kBK, kThreads>& s, uint32_t a_
     using S = TileShare<kRows, kBK, kThreads>;
     if (t >= S::kActive) return;
     const uint32_t row = t % kRows, first_block = (t / kRows) * S::kBlocksPerThread;
+#ifdef NVFP4_ABLATE_LDS   // timing experiments only (wrong results); never defined in the shipped build
+    for (uint32_t j = 0; j < S::kBlocksPerThread; ++j)
+        for (uint32_t i = 0; i < 8; ++i) s.w[j][i] = a_smem + row + j + i;
+    return;
+#endif
 #pragma unroll
     for (uint32_t j = 0; j < S::kBlocksPerThread; ++j) {
         const uint32_t k = (first_block + j) * 16u;
