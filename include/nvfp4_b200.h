@@ -69,6 +69,28 @@ NVFP4_API int nvfp4_set_num_sms(int device, int value);
 NVFP4_API int nvfp4_quantize_weight(const void* w, int w_dtype, int E, int N, int K,
                           void* b, void* sfb, float* gw, void* stream);
 
+/* nvfp4_quantize_weight for callers that must not allocate.  It has no counterpart in the
+ * reference project.
+ *
+ * nvfp4_quantize_weight keeps a small cudaMalloc'ed scratch buffer per device (one word per
+ * expert, grown on demand).  Some callers cannot afford that: code running while a stream is
+ * being captured, latency-critical loops in which a cudaMalloc would synchronise the whole
+ * device, processes whose device memory has been handed out completely to a pool of their
+ * own.  This variant does the same work with its scratch in a fixed array inside the library
+ * image: it calls no cudaMalloc, no cudaFree and no allocating library routine.
+ *
+ *   - At most NVFP4_STATIC_MAX_EXPERTS experts per call; more is NVFP4_E_INVALID_ARGUMENT.
+ *   - The array (4 KB) exists once per GPU per process for as long as the library is loaded.
+ *   - The first call made on a device looks the array's device address up (one
+ *     cudaGetSymbolAddress); make that first call outside any stream capture.
+ *   - All calls on a device share the array, which is cleared at the start of each call on
+ *     the call's stream.  Two calls whose kernels may overlap on the GPU (different streams
+ *     without an ordering between them) race on it; order them.
+ * Arguments, layouts and results are those of nvfp4_quantize_weight, bit for bit. */
+#define NVFP4_STATIC_MAX_EXPERTS 1024
+NVFP4_API int nvfp4_quantize_weight_static(const void* w, int w_dtype, int E, int N, int K,
+                                           void* b, void* sfb, float* gw, void* stream);
+
 /* The hot path.  d[M,N] (BF16) = (A0 + A1) * W^T * gw[expert], experts by row group.
  * Replaces: _C.m_grouped_bf16_dual_nvfp4_gemm_contiguous (src/api.hpp:26-144,
  * kernels src/kernels/sm100_bf16_dual_nvfp4_gemm.hpp:226-480 and :489-632).

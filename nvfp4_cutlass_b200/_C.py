@@ -27,7 +27,7 @@ TUNE_KEYS = ("tune_block_n", "tune_transform_warps", "tune_epilogue_threads", "t
              "tune_produced_stages")
 
 EXPORTS = ("nvfp4_last_error", "nvfp4_version", "nvfp4_get_num_sms", "nvfp4_set_num_sms",
-           "nvfp4_quantize_weight", "nvfp4_grouped_gemm_contiguous", "nvfp4_debug_decompose",
+           "nvfp4_quantize_weight", "nvfp4_quantize_weight_static", "nvfp4_grouped_gemm_contiguous", "nvfp4_debug_decompose",
            "nvfp4_debug_mma_peak", "nvfp4_debug_mma_pattern")
 
 
@@ -50,6 +50,7 @@ def lib() -> ctypes.CDLL:
         L.nvfp4_get_num_sms.argtypes = [i32, ctypes.POINTER(i32)]
         L.nvfp4_set_num_sms.argtypes = [i32, i32]
         L.nvfp4_quantize_weight.argtypes = [vp, i32, i32, i32, i32, vp, vp, vp, vp]
+        L.nvfp4_quantize_weight_static.argtypes = [vp, i32, i32, i32, i32, vp, vp, vp, vp]
         L.nvfp4_grouped_gemm_contiguous.argtypes = [vp, i64, vp, vp, vp, vp, i64, vp, i32, i32, i32, i32,
                                                     i32, i32, i32, i32, vp, vp, vp]
         L.nvfp4_debug_decompose.argtypes = [vp, i64, i32, i32, i32, vp, vp, vp, vp, vp]

@@ -124,6 +124,25 @@ int nvfp4_quantize_weight(const void* w, int w_dtype, int E, int N, int K, void*
     return launch_quantize_weight(w, w_dtype, E, N, K, b, sfb, gw, static_cast<cudaStream_t>(stream));
 }
 
+int nvfp4_quantize_weight_static(const void* w, int w_dtype, int E, int N, int K, void* b, void* sfb, float* gw,
+                                 void* stream)
+{
+    host::clear_error();
+    NVFP4_REQUIRE(E >= 0 && N >= 0 && K >= 0, "negative shape (E=%d, N=%d, K=%d)", E, N, K);
+    NVFP4_REQUIRE(K % 64 == 0, "K=%d must be a multiple of 64", K);
+    NVFP4_REQUIRE(w_dtype == NVFP4_DTYPE_BF16 || w_dtype == NVFP4_DTYPE_F32, "unknown weight dtype code %d", w_dtype);
+    NVFP4_REQUIRE(E <= NVFP4_STATIC_MAX_EXPERTS,
+                  "E=%d exceeds the %d experts the static scratch array holds; use nvfp4_quantize_weight or split the call",
+                  E, NVFP4_STATIC_MAX_EXPERTS);
+    if (E == 0 || N == 0 || K == 0) return NVFP4_OK;
+    NVFP4_REQUIRE(w && b && sfb && gw, "null pointer argument");
+    NVFP4_REQUIRE((reinterpret_cast<uintptr_t>(b) & 15u) == 0, "b must be 16-byte aligned");
+    host::DeviceInfo* d;
+    if (int rc = host::device_info(-1, &d)) return rc;
+    if (d->cc_major != 10) return host::fail(NVFP4_E_UNSUPPORTED, "needs an sm_100 GPU, found sm_%d%d", d->cc_major, d->cc_minor);
+    return launch_quantize_weight_static(w, w_dtype, E, N, K, b, sfb, gw, static_cast<cudaStream_t>(stream));
+}
+
 int nvfp4_grouped_gemm_contiguous(const void* a, int64_t lda_elems, const void* b, const void* sfb, const float* gw,
                                   void* d, int64_t ldd_elems, const int32_t* m_indices, int M, int N, int K, int E,
                                   int scale_policy, int enable_residual_pass, int orientation, int m_alignment,

@@ -16,6 +16,9 @@ int launch_gemm_swap(const void* a, int64_t lda, const void* b, const void* sfb,
 int launch_quantize_weight(const void* w, int w_dtype, int E, int N, int K, void* b, void* sfb, float* gw,
                            cudaStream_t stream);
 
+int launch_quantize_weight_static(const void* w, int w_dtype, int E, int N, int K, void* b, void* sfb, float* gw,
+                                  cudaStream_t stream);
+
 int launch_debug_decompose(const void* a, int64_t lda, int M, int K, void* q0, void* q1, void* s0, void* s1,
                            cudaStream_t stream);
 

@@ -119,4 +119,51 @@ int launch_quantize_weight(const void* w, int w_dtype, int E, int N, int K, void
     return NVFP4_OK;
 }
 
+// ---- allocation-free variant ----------------------------------------------------------
+// Same two kernels, but the per-expert maxima are staged in a fixed array that is part of
+// the library image instead of a cudaMalloc'ed buffer.  Every process that loads the
+// library holds NVFP4_STATIC_MAX_EXPERTS words of it on every GPU it uses, until it exits.
+namespace {
+static __device__ __align__(256) uint32_t g_static_amax[NVFP4_STATIC_MAX_EXPERTS];
+}  // namespace
+
+// In host code `g_static_amax` is only the host-side handle of the symbol, not an address
+// a kernel can dereference.  The device address comes from cudaGetSymbolAddress, asked once
+// per device with that device current -- here on the first call made on that device.
+int launch_quantize_weight_static(const void* w, int w_dtype, int E, int N, int K, void* b, void* sfb, float* gw,
+                                  cudaStream_t stream)
+{
+    if (E == 0 || N == 0 || K == 0) return NVFP4_OK;
+    static uint32_t* scratch_addr[host::kMaxDevices] = {};
+    int dev = 0;
+    NVFP4_CUDA_CHECK(cudaGetDevice(&dev));
+    if (dev < 0 || dev >= host::kMaxDevices) return host::fail(NVFP4_E_INVALID_ARGUMENT, "device %d out of range", dev);
+    if (scratch_addr[dev] == nullptr) {
+        void* addr = nullptr;
+        NVFP4_CUDA_CHECK(cudaGetSymbolAddress(&addr, g_static_amax));
+        if (addr == nullptr) return host::fail(NVFP4_E_CUDA, "cudaGetSymbolAddress gave no address for the scratch array");
+        scratch_addr[dev] = static_cast<uint32_t*>(addr);
+    }
+    uint32_t* amax_bits = scratch_addr[dev];
+    // the array keeps whatever the previous call left in it: the maxima must start from zero
+    NVFP4_CUDA_CHECK(cudaMemsetAsync(amax_bits, 0, sizeof(uint32_t) * E, stream));
+    const int64_t per_expert = static_cast<int64_t>(N) * K;
+    int blocks = static_cast<int>((per_expert + 256 * 16 - 1) / (256 * 16));
+    blocks = blocks < 1 ? 1 : (blocks > 1024 ? 1024 : blocks);
+    const dim3 qgrid((N + 127) / 128, K / 64, E);
+    if (w_dtype == NVFP4_DTYPE_BF16) {
+        auto* wt = static_cast<const __nv_bfloat16*>(w);
+        expert_amax_kernel<<<dim3(blocks, E), 256, 0, stream>>>(wt, per_expert, amax_bits);
+        quantize_weight_kernel<<<qgrid, 128, 0, stream>>>(wt, N, K, amax_bits, static_cast<uint8_t*>(b),
+                                                          static_cast<int32_t*>(sfb), gw);
+    } else {
+        auto* wt = static_cast<const float*>(w);
+        expert_amax_kernel<<<dim3(blocks, E), 256, 0, stream>>>(wt, per_expert, amax_bits);
+        quantize_weight_kernel<<<qgrid, 128, 0, stream>>>(wt, N, K, amax_bits, static_cast<uint8_t*>(b),
+                                                          static_cast<int32_t*>(sfb), gw);
+    }
+    NVFP4_CUDA_CHECK(cudaGetLastError());
+    return NVFP4_OK;
+}
+
 }  // namespace nvfp4
