@@ -1,0 +1,462 @@
+// Grouped dual-NVFP4 GEMM, normal orientation, with the activation transform shared by
+// the two CTAs of a thread-block cluster.
+//
+// Both CTAs work on the same 128 token rows and on two neighbouring 256-column weight
+// tiles.  The quantised activation tile (A0, A1 and their scales) is the same for both, so
+// each CTA loads and transforms only 64 of the rows, writes its products into its own
+// shared memory and then pushes the finished share to its peer with a handful of bulk
+// shared-to-shared copies (cp.async.bulk, shared::cta -> shared::cluster, completing bytes on
+// the peer's P-full barrier).  Per CTA and K block that halves the Algorithm-1 arithmetic,
+// which saturates the integer/convert pipe of the single-CTA kernel, and the BF16 bytes
+// coming in; the tensor work per CTA is unchanged.
+//
+// For the pushed share to be a few contiguous runs, MMA row m of the tile is token row
+// 64 * ((m % 32) / 16) + 16 * (m / 32) + m % 16: the CTA of rank c owns the MMA rows whose
+// m % 32 lies in [16c, 16c + 16) -- four runs of 16 packed rows (1 KB each) and one run of
+// 256 bytes inside every 512-byte scale atom.  The epilogue applies the same map to the
+// accumulator lanes.
+//
+// Barriers: P-full of a CTA counts its own eight transform warps plus the bytes of the
+// peer's copies; P-empty counts one tcgen05.commit per CTA, delivered to both CTAs by the
+// commit's cluster mask, so a slot is rewritten (locally or by the peer's copies) only after
+// both tensor cores have read it.  No load in this file is a multicast: the cross-CTA
+// traffic is the bulk copies, mbarrier signalling and the commit mask.
+#include <cuda_bf16.h>
+
+#include "host_common.hpp"
+#include "launchers.hpp"
+#include "transform.cuh"
+
+namespace nvfp4 {
+namespace {
+
+constexpr uint32_t BM = 128, BN = 256, BK = 128, kKAtoms = 2;
+constexpr uint32_t kSlotP0 = BM * BK / 2;                       // 8192: one packed pass
+constexpr uint32_t kSlotSFA = kKAtoms * 512;                    // 1024
+constexpr uint32_t kSlotB = BN * BK / 2, kSlotSFB = kKAtoms * 2 * 512;
+constexpr uint32_t kWarpTma = 0, kWarpMma = 1, kWarpSfb = 2, kWarpTmaA = 3, kWarpEpi0 = 4, kNumEpiWarps = 4, kWarpXform0 = 8;
+constexpr uint32_t kXformWarps = 8, kXformThreads = kXformWarps * 32;
+constexpr uint32_t kThreads = (kWarpXform0 + kXformWarps) * 32;   // 512
+constexpr uint32_t kTmemCols = 512, kColAcc = 0, kColSFA0 = 256, kColSFA1 = 264, kColSFB = 272;
+
+template <uint32_t CL>
+struct Cfg {
+    static_assert(CL == 2, "the row map and the copy list below are written for pairs");
+    static constexpr uint32_t kRows = BM / CL;                  // rows this CTA loads and transforms
+    static constexpr uint32_t kSlotA = kRows * BK * 2;          // 16384
+    static constexpr uint32_t kDepthA = 4, kDepthP = 3, kDepthB = 5;
+    static constexpr uint32_t kOffA = 0;
+    static constexpr uint32_t kOffA0 = kOffA + kDepthA * kSlotA;
+    static constexpr uint32_t kOffA1 = kOffA0 + kDepthP * kSlotP0;
+    static constexpr uint32_t kOffB = kOffA1 + kDepthP * kSlotP0;
+    static constexpr uint32_t kOffSFA0 = kOffB + kDepthB * kSlotB;
+    static constexpr uint32_t kOffSFA1 = kOffSFA0 + kDepthP * kSlotSFA;
+    static constexpr uint32_t kOffSFB = kOffSFA1 + kDepthP * kSlotSFA;
+    static constexpr uint32_t kOffBars = kOffSFB + kDepthB * kSlotSFB;
+    static constexpr uint32_t kNumBars = 2 * kDepthA + 2 * kDepthP + 3 * kDepthB + 2;
+    static constexpr uint32_t kSmemAlloc = kOffBars + kNumBars * 8 + 16 + 1024;
+    static_assert(kSmemAlloc <= 232448, "shared memory budget");
+    static constexpr uint32_t kBlocksPerThread = kRows * (BK / 16) / kXformThreads;   // 2
+    static_assert(kBlocksPerThread == 2, "two 16-blocks (one 16-byte chunk) per thread");
+};
+
+struct Params {
+    const float* gw;
+    const int32_t* m_indices;
+    __nv_bfloat16* d;
+    int64_t ldd;
+    uint32_t m, n, k;
+    uint32_t group_m;
+    int32_t* status;
+};
+
+struct Ring {
+    uint32_t slot = 0, phase = 0;
+    template <uint32_t kDepth>
+    __device__ __forceinline__ void advance()
+    {
+        if (++slot == kDepth) { slot = 0; phase ^= 1; }
+    }
+};
+
+__device__ __forceinline__ void super_tile_coords(uint32_t st, uint32_t num_m, uint32_t num_ns, uint32_t group_m,
+                                                  uint32_t& m_blk, uint32_t& ns)
+{
+    const uint32_t per_group = group_m * num_ns;
+    const uint32_t g = st / per_group, r = st % per_group;
+    const uint32_t first = g * group_m;
+    const uint32_t rows = min(group_m, num_m - first);
+    m_blk = first + r % rows;
+    ns = r / rows;
+}
+
+template <uint32_t CL, bool kResidual>
+__global__ void __launch_bounds__(kThreads, 1)
+gemm_cluster_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constant__ CUtensorMap tm_b,
+                    const __grid_constant__ CUtensorMap tm_sfb, const Params p)
+{
+    using C = Cfg<CL>;
+    extern __shared__ uint8_t smem_raw[];
+    const uint32_t smem = (ptx::smem_u32(smem_raw) + 1023u) & ~1023u;
+    uint8_t* smem_gen = smem_raw + (smem - ptx::smem_u32(smem_raw));
+
+    uint64_t* bars = reinterpret_cast<uint64_t*>(smem_gen + C::kOffBars);
+    uint64_t* a_full = bars;
+    uint64_t* a_empty = a_full + C::kDepthA;
+    uint64_t* p_full = a_empty + C::kDepthA;
+    uint64_t* p_empty = p_full + C::kDepthP;
+    uint64_t* b_full = p_empty + C::kDepthP;
+    uint64_t* b_ready = b_full + C::kDepthB;
+    uint64_t* b_empty = b_ready + C::kDepthB;
+    uint64_t* tmem_full = b_empty + C::kDepthB;
+    uint64_t* tmem_empty = tmem_full + 1;
+    uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(tmem_empty + 1);
+    volatile uint32_t* abort_flag = tmem_slot + 1;
+
+    const uint32_t warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const uint32_t rank = ptx::cluster_cta_rank();
+
+    if (threadIdx.x == 0) {
+        for (uint32_t i = 0; i < C::kDepthA; ++i) { ptx::mbar_init(a_full + i, 1); ptx::mbar_init(a_empty + i, kXformWarps); }
+        for (uint32_t i = 0; i < C::kDepthP; ++i) {
+            ptx::mbar_init(p_full + i, kXformWarps);            // own transform warps; the peer's share arrives as bytes
+            ptx::mbar_init(p_empty + i, CL);                    // one commit per CTA of the cluster
+        }
+        for (uint32_t i = 0; i < C::kDepthB; ++i) {
+            ptx::mbar_init(b_full + i, 1);
+            ptx::mbar_init(b_ready + i, 1);
+            ptx::mbar_init(b_empty + i, 1);
+        }
+        ptx::mbar_init(tmem_full, 1);
+        ptx::mbar_init(tmem_empty, kNumEpiWarps);
+        *abort_flag = 0;
+        ptx::fence_mbar_init();
+        ptx::prefetch_tensormap(&tm_a);
+        ptx::prefetch_tensormap(&tm_b);
+        ptx::prefetch_tensormap(&tm_sfb);
+    }
+    if (warp == kWarpMma) ptx::tmem_alloc<kTmemCols>(tmem_slot);
+    ptx::tcgen05_fence_before_sync();
+    __syncthreads();
+    ptx::cluster_sync();                                         // every CTA's barriers exist before any remote arrival
+    ptx::tcgen05_fence_after_sync();
+    const uint32_t tmem_base = *tmem_slot;
+
+    const uint32_t num_m = p.m / BM, num_ns = p.n / (BN * CL), num_kb = p.k / BK;
+    const uint32_t num_super = num_m * num_ns;
+    const uint32_t cid = ptx::cluster_id_x(), ncl = ptx::num_clusters_x();
+    bool ok = true;
+    ptx::ProbeAcc pa;
+    const long long probe_start = ptx::probe_clock();
+    auto give_up = [&](uint32_t code) {
+        *abort_flag = 1;
+        if (p.status != nullptr) atomicOr(p.status, static_cast<int32_t>(code));
+        ok = false;
+    };
+
+    if (warp == kWarpTma) {
+        // ================= weight producer =================
+        if (lane == 0) {
+            Ring rb;
+            for (uint32_t st = cid; st < num_super && ok; st += ncl) {
+                uint32_t m_blk, ns;
+                super_tile_coords(st, num_m, num_ns, p.group_m, m_blk, ns);
+                const uint32_t n_blk = ns * CL + rank;
+                const int32_t e = max(0, __ldg(p.m_indices + m_blk * BM));
+                for (uint32_t kb = 0; kb < num_kb; ++kb) {
+                    if (!ptx::mbar_wait_impl(b_empty + rb.slot, rb.phase ^ 1, abort_flag)) { give_up(1); break; }
+                    ptx::mbar_arrive_expect_tx(b_full + rb.slot, kSlotB + kSlotSFB);
+                    ptx::tma_load_2d(smem_gen + C::kOffB + rb.slot * kSlotB, &tm_b, b_full + rb.slot, kb * (BK / 2),
+                                     e * p.n + n_blk * BN);
+                    ptx::tma_load_2d(smem_gen + C::kOffSFB + rb.slot * kSlotSFB, &tm_sfb, b_full + rb.slot, n_blk * BN,
+                                     e * (p.k / 64) + kb * kKAtoms);
+                    rb.advance<C::kDepthB>();
+                }
+            }
+        }
+    } else if (warp == kWarpTmaA) {
+        // ================= activation producer: this CTA's share of the rows =================
+        if (lane == 0) {
+            Ring ra;
+            for (uint32_t st = cid; st < num_super && ok; st += ncl) {
+                uint32_t m_blk, ns;
+                super_tile_coords(st, num_m, num_ns, p.group_m, m_blk, ns);
+                const uint32_t row0 = m_blk * BM + rank * C::kRows;
+                for (uint32_t kb = 0; kb < num_kb; ++kb) {
+                    if (!ptx::mbar_wait_impl(a_empty + ra.slot, ra.phase ^ 1, abort_flag)) { give_up(1); break; }
+                    ptx::mbar_arrive_expect_tx(a_full + ra.slot, C::kSlotA);
+                    const uint32_t a_dst = C::kOffA + ra.slot * C::kSlotA;
+                    ptx::tma_load_2d(smem_gen + a_dst, &tm_a, a_full + ra.slot, kb * BK, row0);
+                    ptx::tma_load_2d(smem_gen + a_dst + C::kSlotA / 2, &tm_a, a_full + ra.slot, kb * BK + 64, row0);
+                    ra.advance<C::kDepthA>();
+                }
+            }
+        }
+    } else if (warp == kWarpMma) {
+        // ================= MMA issue =================
+        Ring rp, rb;
+        uint32_t acc_phase = 0;
+        constexpr uint32_t idesc = ptx::make_idesc_nvf4(BM, BN);
+        constexpr uint16_t kAllCtas = static_cast<uint16_t>((1u << CL) - 1u);
+        for (uint32_t st = cid; st < num_super && ok; st += ncl) {
+            if (!ptx::mbar_wait(tmem_empty, acc_phase ^ 1, abort_flag, pa, 0)) { give_up(1); break; }
+            ptx::tcgen05_fence_after_sync();
+            for (uint32_t kb = 0; kb < num_kb; ++kb) {
+                if (!ptx::mbar_wait_cluster(p_full + rp.slot, rp.phase, abort_flag, pa, 1) ||
+                    !ptx::mbar_wait(b_ready + rb.slot, rb.phase, abort_flag, pa, 2) ||
+                    !ptx::mbar_wait(b_full + rb.slot, rb.phase, abort_flag, pa, 3)) { give_up(1); break; }
+                ptx::tcgen05_fence_after_sync();
+                if (lane == 0) {
+                    const uint32_t sfa0 = smem + C::kOffSFA0 + rp.slot * kSlotSFA;
+                    const uint32_t sfa1 = smem + C::kOffSFA1 + rp.slot * kSlotSFA;
+                    const uint32_t sfb = smem + C::kOffSFB + rb.slot * kSlotSFB;
+#pragma unroll
+                    for (uint32_t a = 0; a < kKAtoms; ++a) {
+                        ptx::tcgen05_cp_32x128b_warpx4(tmem_base + kColSFA0 + 4 * a,
+                                                       ptx::make_smem_desc(sfa0 + a * 512, 128, ptx::kSwizzleNone));
+                        if constexpr (kResidual)
+                            ptx::tcgen05_cp_32x128b_warpx4(tmem_base + kColSFA1 + 4 * a,
+                                                           ptx::make_smem_desc(sfa1 + a * 512, 128, ptx::kSwizzleNone));
+#pragma unroll
+                        for (uint32_t i = 0; i < 2; ++i)
+                            ptx::tcgen05_cp_32x128b_warpx4(tmem_base + kColSFB + 4 * (a * 2 + i),
+                                                           ptx::make_smem_desc(sfb + (a * 2 + i) * 512, 128, ptx::kSwizzleNone));
+                    }
+                    const uint32_t a0 = smem + C::kOffA0 + rp.slot * kSlotP0;
+                    const uint32_t a1 = smem + C::kOffA1 + rp.slot * kSlotP0;
+                    const uint32_t b = smem + C::kOffB + rb.slot * kSlotB;
+#pragma unroll
+                    for (uint32_t a = 0; a < kKAtoms; ++a) {
+                        const uint64_t desc_b = ptx::make_smem_desc(b + a * 32, 512, ptx::kSwizzle64B);
+                        ptx::tcgen05_mma_nvf4(tmem_base + kColAcc, ptx::make_smem_desc(a0 + a * 32, 512, ptx::kSwizzle64B), desc_b,
+                                              idesc, tmem_base + kColSFA0 + 4 * a, tmem_base + kColSFB + 8 * a,
+                                              (kb | a) != 0 ? 1u : 0u);
+                        if constexpr (kResidual)
+                            ptx::tcgen05_mma_nvf4(tmem_base + kColAcc, ptx::make_smem_desc(a1 + a * 32, 512, ptx::kSwizzle64B),
+                                                  desc_b, idesc, tmem_base + kColSFA1 + 4 * a, tmem_base + kColSFB + 8 * a, 1u);
+                    }
+                    ptx::tcgen05_commit_cluster(p_empty + rp.slot, kAllCtas);   // frees this slot in every CTA's count
+                    ptx::tcgen05_commit(b_empty + rb.slot);
+                    if (kb == num_kb - 1) ptx::tcgen05_commit(tmem_full);
+                }
+                __syncwarp();
+                rp.advance<C::kDepthP>();
+                rb.advance<C::kDepthB>();
+            }
+            acc_phase ^= 1;
+        }
+    } else if (warp == kWarpSfb) {
+        // ================= weight-scale transpose into tensor-memory-copy order =================
+        Ring rb;
+        for (uint32_t st = cid; st < num_super && ok; st += ncl) {
+            for (uint32_t kb = 0; kb < num_kb; ++kb) {
+                if (!ptx::mbar_wait_impl(b_full + rb.slot, rb.phase, abort_flag)) { give_up(1); break; }
+                const uint32_t base = smem + C::kOffSFB + rb.slot * kSlotSFB;
+#pragma unroll
+                for (uint32_t i = 0; i < kKAtoms * 2; ++i) {
+                    const uint32_t atom = base + i * 512;
+                    const uint32_t v0 = ptx::lds32(atom + lane * 4);
+                    const uint32_t v1 = ptx::lds32(atom + (32 + lane) * 4);
+                    const uint32_t v2 = ptx::lds32(atom + (64 + lane) * 4);
+                    const uint32_t v3 = ptx::lds32(atom + (96 + lane) * 4);
+                    __syncwarp();
+                    ptx::sts128(atom + lane * 16, v0, v1, v2, v3);
+                }
+                ptx::fence_proxy_async_smem();
+                __syncwarp();
+                if (lane == 0) ptx::mbar_arrive(b_ready + rb.slot);
+                rb.advance<C::kDepthB>();
+            }
+        }
+    } else if (warp >= kWarpEpi0 && warp < kWarpEpi0 + kNumEpiWarps) {
+        // ================= epilogue: TMEM -> x G_W -> BF16 -> global =================
+        const uint32_t quad = warp & 3;
+        uint32_t acc_phase = 0;
+        for (uint32_t st = cid; st < num_super && ok; st += ncl) {
+            uint32_t m_blk, ns;
+            super_tile_coords(st, num_m, num_ns, p.group_m, m_blk, ns);
+            const uint32_t n_blk = ns * CL + rank;
+            const int32_t e = max(0, __ldg(p.m_indices + m_blk * BM));
+            const float g = __ldg(p.gw + e);
+            if (!ptx::mbar_wait_impl(tmem_full, acc_phase, abort_flag)) { give_up(1); break; }
+            ptx::tcgen05_fence_after_sync();
+            // accumulator lane m = 32 * quad + lane holds token row 64 * (lane / 16) + 16 * quad + lane % 16
+            const uint32_t row = m_blk * BM + 64 * (lane >> 4) + 16 * quad + (lane & 15);
+            __nv_bfloat16* drow = p.d + static_cast<int64_t>(row) * p.ldd + n_blk * BN;
+#pragma unroll 1
+            for (uint32_t c = 0; c < BN; c += 32) {
+                uint32_t v[32];
+                ptx::tmem_ld_32x32b_x32(tmem_base + ((quad * 32) << 16) + kColAcc + c, v);
+                ptx::tmem_ld_wait();
+                uint32_t o[16];
+#pragma unroll
+                for (int i = 0; i < 16; ++i) {
+                    const __nv_bfloat162 h = __floats2bfloat162_rn(__uint_as_float(v[2 * i]) * g, __uint_as_float(v[2 * i + 1]) * g);
+                    o[i] = *reinterpret_cast<const uint32_t*>(&h);
+                }
+                uint4* dst = reinterpret_cast<uint4*>(drow + c);
+#pragma unroll
+                for (int i = 0; i < 4; ++i) dst[i] = make_uint4(o[4 * i], o[4 * i + 1], o[4 * i + 2], o[4 * i + 3]);
+            }
+            ptx::tcgen05_fence_before_sync();
+            __syncwarp();
+            if (lane == 0) ptx::mbar_arrive(tmem_empty);
+            acc_phase ^= 1;
+        }
+    } else if (warp >= kWarpXform0) {
+        // ================= transform: this CTA's 64 rows, then the share goes to the peer =================
+        const uint32_t t = threadIdx.x - kWarpXform0 * 32;
+        const uint32_t lrow = t % C::kRows;                                              // row inside this CTA's share
+        const uint32_t mrow = 32 * (lrow >> 4) + 16 * rank + (lrow & 15);               // its row in the MMA tile
+        const uint32_t first_block = (t / C::kRows) * C::kBlocksPerThread;
+        const uint32_t peer_smem = ptx::map_to_cta(smem, rank ^ 1u);
+        const uint32_t peer_pfull = ptx::map_to_cta(ptx::smem_u32(p_full), rank ^ 1u);
+        constexpr uint32_t kPeerBytes = kResidual ? 2 * (4 * 1024 + 2 * 256) : (4 * 1024 + 2 * 256);
+        Ring ra, rp;
+        for (uint32_t st = cid; st < num_super && ok; st += ncl) {
+            for (uint32_t kb = 0; kb < num_kb; ++kb) {
+                if (!ptx::mbar_wait(a_full + ra.slot, ra.phase, abort_flag, pa, 0)) { give_up(1); break; }
+                const uint32_t a_smem = smem + C::kOffA + ra.slot * C::kSlotA;
+                uint32_t w[2][8];
+#pragma unroll
+                for (uint32_t j = 0; j < 2; ++j) {
+                    const uint32_t k = (first_block + j) * 16u;
+                    const uint4 lo = ptx::lds128(a_smem + xform::a_bf16_offset<C::kRows>(lrow, k));
+                    const uint4 hi = ptx::lds128(a_smem + xform::a_bf16_offset<C::kRows>(lrow, k + 8));
+                    w[j][0] = lo.x; w[j][1] = lo.y; w[j][2] = lo.z; w[j][3] = lo.w;
+                    w[j][4] = hi.x; w[j][5] = hi.y; w[j][6] = hi.z; w[j][7] = hi.w;
+                }
+                __syncwarp();
+                if (lane == 0) ptx::mbar_arrive(a_empty + ra.slot);   // the tile now lives in registers
+                // both tensor cores must be done with this slot before anyone rewrites it
+                if (!ptx::mbar_wait_cluster(p_empty + rp.slot, rp.phase ^ 1, abort_flag, pa, 1)) { give_up(1); break; }
+                const uint32_t off_a0 = C::kOffA0 + rp.slot * kSlotP0, off_a1 = C::kOffA1 + rp.slot * kSlotP0;
+                const uint32_t off_s0 = C::kOffSFA0 + rp.slot * kSlotSFA, off_s1 = C::kOffSFA1 + rp.slot * kSlotSFA;
+                xform::Block16 blk[2];
+                xform::decompose_block16<kResidual>(w[0], blk[0]);
+                xform::decompose_block16<kResidual>(w[1], blk[1]);
+                const uint32_t off = xform::fp4_offset<BK>(mrow, first_block * 16u);
+                ptx::sts128(smem + off_a0 + off, blk[0].q0[0], blk[0].q0[1], blk[1].q0[0], blk[1].q0[1]);
+                if constexpr (kResidual)
+                    ptx::sts128(smem + off_a1 + off, blk[0].q1[0], blk[0].q1[1], blk[1].q1[0], blk[1].q1[1]);
+                const uint32_t sf_addr = (first_block >> 2) * 512u + xform::sf_word_offset(mrow) + (first_block & 2u);
+                ptx::sts16(smem + off_s0 + sf_addr, blk[0].s0 | (blk[1].s0 << 8));
+                if constexpr (kResidual) ptx::sts16(smem + off_s1 + sf_addr, blk[0].s1 | (blk[1].s1 << 8));
+                ptx::fence_proxy_async_smem();                   // own stores -> async proxy (MMA reads, bulk-copy reads)
+                asm volatile("bar.sync 1, %0;" ::"n"(kXformThreads) : "memory");   // the whole share is written
+                if (t == 0) {
+                    // four runs of 16 packed rows per pass, one 256-byte run per scale atom, to the same
+                    // offsets in the peer; their bytes complete on the peer's P-full barrier of this slot
+                    const uint32_t bar = peer_pfull + rp.slot * 8;
+#pragma unroll
+                    for (uint32_t g = 0; g < 4; ++g) {
+                        const uint32_t o = (32 * g + 16 * rank) * 64;
+                        ptx::bulk_copy_to_cta(peer_smem + off_a0 + o, smem + off_a0 + o, 1024, bar);
+                        if constexpr (kResidual) ptx::bulk_copy_to_cta(peer_smem + off_a1 + o, smem + off_a1 + o, 1024, bar);
+                    }
+#pragma unroll
+                    for (uint32_t a = 0; a < kKAtoms; ++a) {
+                        const uint32_t o = a * 512 + 16 * rank * 16;
+                        ptx::bulk_copy_to_cta(peer_smem + off_s0 + o, smem + off_s0 + o, 256, bar);
+                        if constexpr (kResidual) ptx::bulk_copy_to_cta(peer_smem + off_s1 + o, smem + off_s1 + o, 256, bar);
+                    }
+                }
+                if (lane == 0) {
+                    if (warp == kWarpXform0) ptx::mbar_arrive_expect_tx(p_full + rp.slot, kPeerBytes);
+                    else ptx::mbar_arrive(p_full + rp.slot);
+                }
+                ra.advance<C::kDepthA>();
+                rp.advance<C::kDepthP>();
+            }
+        }
+    }
+
+    ptx::probe_add(32 + (warp < 8 ? warp : 8), ptx::probe_clock() - probe_start);
+    if (warp == 1) ptx::probe_flush(pa, 2, 3, 4, 5);
+    else if (warp >= kWarpXform0) ptx::probe_flush(pa, 11, 12);
+    // teardown: nobody leaves while a peer may still write into its shared memory
+    ptx::tcgen05_fence_before_sync();
+    __syncthreads();
+    ptx::cluster_sync();
+    if (warp == kWarpMma) {
+        ptx::tcgen05_fence_after_sync();
+        ptx::tmem_dealloc<kTmemCols>(tmem_base);
+    }
+}
+
+template <uint32_t CL, bool kResidual>
+int launch_variant(const void* a, int64_t lda, const void* b, const void* sfb, int M, int N, int K, int E,
+                   const Params& p, int num_sms, cudaStream_t stream)
+{
+    using C = Cfg<CL>;
+    CUtensorMap tm_a, tm_b, tm_sfb;
+    int rc = host::encode_tensor_map_2d(&tm_a, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, a, K, M, lda * 2, 64, C::kRows,
+                                        CU_TENSOR_MAP_SWIZZLE_128B);
+    if (rc) return rc;
+    rc = host::encode_tensor_map_2d(&tm_b, CU_TENSOR_MAP_DATA_TYPE_UINT8, 1, b, K / 2, static_cast<uint64_t>(E) * N,
+                                    K / 2, BK / 2, BN, CU_TENSOR_MAP_SWIZZLE_64B);
+    if (rc) return rc;
+    rc = host::encode_tensor_map_2d(&tm_sfb, CU_TENSOR_MAP_DATA_TYPE_INT32, 4, sfb, N,
+                                    static_cast<uint64_t>(E) * (K / 64), static_cast<uint64_t>(N) * 4, BN, kKAtoms,
+                                    CU_TENSOR_MAP_SWIZZLE_NONE);
+    if (rc) return rc;
+    auto kernel = gemm_cluster_kernel<CL, kResidual>;
+    static int max_clusters[host::kMaxDevices] = {};
+    int dev = 0;
+    NVFP4_CUDA_CHECK(cudaGetDevice(&dev));
+    cudaLaunchConfig_t cfg = {};
+    cudaLaunchAttribute attr[1];
+    attr[0].id = cudaLaunchAttributeClusterDimension;
+    attr[0].val.clusterDim.x = CL;
+    attr[0].val.clusterDim.y = 1;
+    attr[0].val.clusterDim.z = 1;
+    cfg.blockDim = dim3(kThreads);
+    cfg.dynamicSmemBytes = C::kSmemAlloc;
+    cfg.stream = stream;
+    cfg.attrs = attr;
+    cfg.numAttrs = 1;
+    if (max_clusters[dev] == 0) {
+        NVFP4_CUDA_CHECK(cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, C::kSmemAlloc));
+        cfg.gridDim = dim3(static_cast<unsigned>(num_sms / CL * CL));
+        int n = 0;
+        NVFP4_CUDA_CHECK(cudaOccupancyMaxActiveClusters(&n, kernel, &cfg));
+        if (n <= 0) return host::fail(NVFP4_E_CUDA, "no cluster of %u CTAs fits on this device", CL);
+        max_clusters[dev] = n;
+    }
+    const int num_super = (M / static_cast<int>(BM)) * (N / static_cast<int>(BN * CL));
+    int clusters = max_clusters[dev] < num_sms / static_cast<int>(CL) ? max_clusters[dev] : num_sms / static_cast<int>(CL);
+    if (clusters > num_super) clusters = num_super;
+    cfg.gridDim = dim3(static_cast<unsigned>(clusters * CL));
+    NVFP4_CUDA_CHECK(cudaLaunchKernelEx(&cfg, kernel, tm_a, tm_b, tm_sfb, p));
+    return NVFP4_OK;
+}
+
+}  // namespace
+
+// N must be a multiple of 512 (two 256-column tiles per cluster).
+int launch_gemm_cluster(const void* a, int64_t lda, const void* b, const void* sfb, const float* gw, void* d,
+                        int64_t ldd, const int32_t* m_indices, int M, int N, int K, int E, bool residual,
+                        int group_m, int num_sms, int32_t* status, cudaStream_t stream)
+{
+    Params p;
+    p.gw = gw;
+    p.m_indices = m_indices;
+    p.d = static_cast<__nv_bfloat16*>(d);
+    p.ldd = ldd;
+    p.m = M; p.n = N; p.k = K;
+    p.group_m = group_m > 0 ? group_m : 8;
+    p.status = status;
+    return residual ? launch_variant<2, true>(a, lda, b, sfb, M, N, K, E, p, num_sms, stream)
+                    : launch_variant<2, false>(a, lda, b, sfb, M, N, K, E, p, num_sms, stream);
+}
+
+#ifdef NVFP4_PROBE
+extern "C" __attribute__((visibility("default"))) int nvfp4_probe_read_cluster(unsigned long long* out64, int reset)
+{
+    cudaMemcpyFromSymbol(out64, ptx::g_probe, sizeof(unsigned long long) * 64);
+    if (reset) { unsigned long long z[64] = {}; cudaMemcpyToSymbol(ptx::g_probe, z, sizeof z); }
+    return 0;
+}
+#endif
+
+}  // namespace nvfp4

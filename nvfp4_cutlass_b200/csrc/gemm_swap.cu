@@ -39,7 +39,12 @@ struct Cfg {
     static constexpr uint32_t kRowsP = kResidual ? 2 * T : T;             // rows of the stacked operand tile
     static constexpr uint32_t kSlotW = BW * BK / 2, kSlotSFW = kAtoms * 512;
     static constexpr uint32_t kSlotA = T * BK * 2;
-    static constexpr uint32_t kSlotP = (kRowsP * BK / 2 + 1023u) & ~1023u, kSlotSFT = kAtoms * 512;
+    static constexpr uint32_t kSlotP = (kRowsP * BK / 2 + 1023u) & ~1023u;
+    // token scales: one 512-byte atom and one tensor-memory copy per K atom.  (Packing the scales of several
+    // K atoms side by side into one atom, with the MMA reading them at a column that is not a multiple of
+    // four, raised a CUDA error on B200: the scale address of the MMA has to stay 4-column aligned.)
+    static constexpr uint32_t kSfCols = 4, kAtomsPerCp = 4 / kSfCols;
+    static constexpr uint32_t kNumSftCp = (kAtoms + kAtomsPerCp - 1) / kAtomsPerCp, kSlotSFT = kNumSftCp * 512;
     static constexpr uint32_t kA1Bytes = T * (BK / 2);                     // A1 rows start T rows below A0
     static constexpr uint32_t kSF1Bytes = T == 16 ? 256 : (T / 32) * 4;    // scale word of row T + r relative to row r
     static constexpr uint32_t kDepthA = T >= 64 ? 3 : (T == 32 ? 5 : 6), kDepthP = 3;   // A must cover the TMA latency
@@ -59,7 +64,7 @@ struct Cfg {
     // tensor memory: two accumulator stages of kRowsP columns, then the two scale groups
     static constexpr uint32_t kAccStride = kRowsP < 32 ? 32 : kRowsP;
     static constexpr uint32_t kColSFW = 2 * kAccStride, kColSFT = kColSFW + 4 * kAtoms;
-    static constexpr uint32_t kColsUsed = kColSFT + 4 * kAtoms;
+    static constexpr uint32_t kColsUsed = kColSFT + 4 * kNumSftCp;
     static constexpr uint32_t kTmemCols = kColsUsed <= 64 ? 64 : (kColsUsed <= 128 ? 128 : (kColsUsed <= 256 ? 256 : 512));
     static constexpr uint64_t kSwizzle = BK == 256 ? ptx::kSwizzle128B : ptx::kSwizzle64B;
     static constexpr uint32_t kSBO = 8 * (BK / 2);   // eight rows of one swizzle span
@@ -195,19 +200,21 @@ gemm_swap_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constant
                     const uint32_t sfw = smem + C::kOffSFW + rw.slot * C::kSlotSFW;
                     const uint32_t sft = smem + C::kOffSFT + rp.slot * C::kSlotSFT;
 #pragma unroll
-                    for (uint32_t a = 0; a < C::kAtoms; ++a) {
+                    for (uint32_t a = 0; a < C::kAtoms; ++a)
                         ptx::tcgen05_cp_32x128b_warpx4(tmem_base + C::kColSFW + 4 * a,
                                                        ptx::make_smem_desc(sfw + a * 512, 128, ptx::kSwizzleNone));
-                        ptx::tcgen05_cp_32x128b_warpx4(tmem_base + C::kColSFT + 4 * a,
-                                                       ptx::make_smem_desc(sft + a * 512, 128, ptx::kSwizzleNone));
-                    }
+#pragma unroll
+                    for (uint32_t i = 0; i < C::kNumSftCp; ++i)
+                        ptx::tcgen05_cp_32x128b_warpx4(tmem_base + C::kColSFT + 4 * i,
+                                                       ptx::make_smem_desc(sft + i * 512, 128, ptx::kSwizzleNone));
                     const uint32_t w = smem + C::kOffW + rw.slot * C::kSlotW;
                     const uint32_t pt = smem + C::kOffP + rp.slot * C::kSlotP;
 #pragma unroll
                     for (uint32_t a = 0; a < C::kAtoms; ++a)
                         ptx::tcgen05_mma_nvf4(tmem_acc, ptx::make_smem_desc(w + a * 32, C::kSBO, C::kSwizzle),
                                               ptx::make_smem_desc(pt + a * 32, C::kSBO, C::kSwizzle), idesc,
-                                              tmem_base + C::kColSFW + 4 * a, tmem_base + C::kColSFT + 4 * a,
+                                              tmem_base + C::kColSFW + 4 * a,
+                                              tmem_base + C::kColSFT + (a / C::kAtomsPerCp) * 4 + (a % C::kAtomsPerCp) * C::kSfCols,
                                               (kb | a) != 0 ? 1u : 0u);
                     ptx::tcgen05_commit(p_empty + rp.slot);
                     ptx::tcgen05_commit(w_empty + rw.slot);
@@ -301,7 +308,7 @@ gemm_swap_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constant
             for (uint32_t kb = 0; kb < num_kb; ++kb) {
                 if (!ptx::mbar_wait(a_full + ra.slot, ra.phase, abort_flag, pa, 0)) { give_up(1); break; }
                 bool p_ok = true;
-                xform::transform_tile<T, BK, kXformThreads, kResidual>(
+                xform::transform_tile<T, BK, kXformThreads, kResidual, C::kSfCols>(
                     smem + C::kOffA + ra.slot * C::kSlotA, smem + C::kOffP + rp.slot * C::kSlotP,
                     smem + C::kOffP + rp.slot * C::kSlotP + C::kA1Bytes, smem + C::kOffSFT + rp.slot * C::kSlotSFT,
                     smem + C::kOffSFT + rp.slot * C::kSlotSFT + C::kSF1Bytes, t, [&] {

@@ -414,6 +414,15 @@ NVFP4_DEVICE void tcgen05_commit_cluster(uint64_t* bar, uint16_t cta_mask)
                  ::"r"(smem_u32(bar)), "h"(cta_mask)
                  : "memory");
 }
+// Bulk copy of `bytes` (multiple of 16, both addresses 16-byte aligned) from this CTA's shared
+// memory to the shared memory of another CTA of the cluster; the bytes complete on `dst_bar`,
+// an mbarrier of the destination CTA.  Addresses of the destination come from map_to_cta.
+NVFP4_DEVICE void bulk_copy_to_cta(uint32_t dst_cluster_addr, uint32_t src_cta_addr, uint32_t bytes, uint32_t dst_bar)
+{
+    asm volatile("cp.async.bulk.shared::cluster.shared::cta.mbarrier::complete_tx::bytes [%0], [%1], %2, [%3];"
+                 ::"r"(dst_cluster_addr), "r"(src_cta_addr), "r"(bytes), "r"(dst_bar)
+                 : "memory");
+}
 NVFP4_DEVICE void fence_proxy_async_all() { asm volatile("fence.proxy.async;" ::: "memory"); }
 // Generic-proxy writes into the cluster's shared memory -> async proxy (tensor-core operand reads).
 NVFP4_DEVICE void fence_proxy_async_cluster_smem() { asm volatile("fence.proxy.async.shared::cluster;" ::: "memory"); }

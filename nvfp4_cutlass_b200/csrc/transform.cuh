@@ -48,6 +48,18 @@ NVFP4_DEVICE uint32_t fp4_sw64_offset(uint32_t row, uint32_t k) { return fp4_off
 // 32x128b.warpx4 tensor-memory copy wants: row r at word (r % 32) * 4 + r / 32,
 // byte j of the word = 16-block j.
 NVFP4_DEVICE uint32_t sf_word_offset(uint32_t row) { return (((row & 31u) << 2) + (row >> 5)) << 2; }
+// Byte offset of the scale word of (64-K atom, row) in a run of 512-byte atoms.  An operand
+// of R <= 128 rows uses only kCols = ceil(R / 32) of the four words of each 16-byte unit,
+// so 4 / kCols consecutive K atoms are packed side by side into one 512-byte atom: one
+// tensor-memory copy then brings the scales of several K atoms at once, and the MMA of K
+// atom a reads them at column (a / per) * 4 + (a % per) * kCols of the scale region.
+template <uint32_t kCols>
+NVFP4_DEVICE uint32_t sf_atom_offset(uint32_t atom, uint32_t row)
+{
+    static_assert(kCols == 1 || kCols == 2 || kCols == 4, "columns per K atom");
+    constexpr uint32_t per = 4u / kCols;
+    return (atom / per) * 512u + ((row & 31u) << 4) + (((atom % per) * kCols + (row >> 5)) << 2);
+}
 
 // ---- Algorithm 1 on one 16-element block -------------------------------------------
 struct Block16 {
@@ -74,7 +86,11 @@ NVFP4_DEVICE void decompose_block16(const uint32_t (&w)[8], Block16& out)
     m2 = ptx::max_abs_bf16x2(m2, m3);
     m0 = ptx::max_abs_bf16x2(m0, m2);
     m0 = ptx::max_abs_bf16x2(m0, m0 >> 16);
+#if defined(NVFP4_XFV) && NVFP4_XFV == 1   // timing studies only (wrong results)
+    const float amax = __uint_as_float((w[0] & 0x7fffu) << 16);
+#else
     const float amax = __uint_as_float((m0 & 0x7fffu) << 16);
+#endif
 
     // s0 = Q_e4m3(max(amax * fl(1/6), 2^-6)); always a normal E4M3 value
     const float s0_pre = fmaxf(__fmul_rn(amax, 0.16666667163372040f), 0.015625f);
@@ -89,15 +105,28 @@ NVFP4_DEVICE void decompose_block16(const uint32_t (&w)[8], Block16& out)
     float u[16];
 #pragma unroll
     for (int i = 0; i < 8; ++i) {
+#if defined(NVFP4_XFV) && NVFP4_XFV == 2   // timing studies only (wrong results)
+        const float x0 = __uint_as_float(w[i]), x1 = __uint_as_float(w[(i + 1) & 7]);
+#else
         const float x0 = __uint_as_float(w[i] << 16);
         const float x1 = __uint_as_float(w[i] & 0xffff0000u);
+#endif
         u[2 * i] = __fmaf_rn(x0, r_hi, __fmul_rn(x0, r_lo));
         u[2 * i + 1] = __fmaf_rn(x1, r_hi, __fmul_rn(x1, r_lo));
     }
+#if defined(NVFP4_XFV) && NVFP4_XFV == 3   // timing studies only (wrong results)
+    out.q0[0] = __float_as_uint(u[0]) ^ __float_as_uint(u[3]) ^ __float_as_uint(u[5]) ^ __float_as_uint(u[7]);
+    out.q0[1] = __float_as_uint(u[8]) ^ __float_as_uint(u[11]) ^ __float_as_uint(u[13]) ^ __float_as_uint(u[15]);
+#else
     out.q0[0] = ptx::cvt_e2m1x8(u[0], u[1], u[2], u[3], u[4], u[5], u[6], u[7]);
     out.q0[1] = ptx::cvt_e2m1x8(u[8], u[9], u[10], u[11], u[12], u[13], u[14], u[15]);
+#endif
 
+#if defined(NVFP4_XFV) && NVFP4_XFV == 4
+    if constexpr (false) {
+#else
     if constexpr (kResidual) {
+#endif
         // r = (u - dec(q0)) * 8 = 8u + dec(q0) * (-8): exact, the decode comes back as FP16
         float r[16];
 #pragma unroll
@@ -179,13 +208,12 @@ NVFP4_DEVICE void load_tile_global(TileShare<kRows, kBK, kThreads>& s, const voi
     }
 }
 
-template <uint32_t kRows, uint32_t kBK, uint32_t kThreads, bool kResidual>
+template <uint32_t kRows, uint32_t kBK, uint32_t kThreads, bool kResidual, uint32_t kSfCols = 4>
 NVFP4_DEVICE void emit_tile(const TileShare<kRows, kBK, kThreads>& s, uint32_t a0_smem, uint32_t a1_smem,
                             uint32_t sfa0_smem, uint32_t sfa1_smem, uint32_t t)
 {
     using S = TileShare<kRows, kBK, kThreads>;
     constexpr uint32_t kBlocksPerThread = S::kBlocksPerThread;
-    constexpr uint32_t kSfAtomBytes = 512u;                        // one 128-row x 4-byte atom per 64 K
     if (t >= S::kActive) return;
     const uint32_t row = t % kRows, first_block = (t / kRows) * kBlocksPerThread;
 
@@ -195,7 +223,7 @@ NVFP4_DEVICE void emit_tile(const TileShare<kRows, kBK, kThreads>& s, uint32_t a
         const uint32_t off = fp4_offset<kBK>(row, (first_block * 16u) & ~31u) + ((first_block & 1u) << 3);
         ptx::sts64(a0_smem + off, blk.q0[0], blk.q0[1]);
         if constexpr (kResidual) ptx::sts64(a1_smem + off, blk.q1[0], blk.q1[1]);
-        const uint32_t addr = (first_block >> 2) * kSfAtomBytes + sf_word_offset(row) + (first_block & 3u);
+        const uint32_t addr = sf_atom_offset<kSfCols>(first_block >> 2, row) + (first_block & 3u);
         ptx::sts8(sfa0_smem + addr, blk.s0);
         if constexpr (kResidual) ptx::sts8(sfa1_smem + addr, blk.s1);
     } else {
@@ -215,11 +243,11 @@ NVFP4_DEVICE void emit_tile(const TileShare<kRows, kBK, kThreads>& s, uint32_t a
             sf1 |= (blk[0].s1 | (blk[1].s1 << 8)) << shift;
             // flush a scale word (or half word) whenever this thread's share of a K atom is complete
             if constexpr (kBlocksPerThread == 2) {
-                const uint32_t addr = (first_block >> 2) * kSfAtomBytes + sf_word_offset(row) + (first_block & 2u);
+                const uint32_t addr = sf_atom_offset<kSfCols>(first_block >> 2, row) + (first_block & 2u);
                 ptx::sts16(sfa0_smem + addr, sf0);
                 if constexpr (kResidual) ptx::sts16(sfa1_smem + addr, sf1);
             } else if ((pair & 1u) == 1u) {
-                const uint32_t addr = ((first_block + pair * 2) >> 2) * kSfAtomBytes + sf_word_offset(row);
+                const uint32_t addr = sf_atom_offset<kSfCols>((first_block + pair * 2) >> 2, row);
                 ptx::sts32(sfa0_smem + addr, sf0);
                 if constexpr (kResidual) ptx::sts32(sfa1_smem + addr, sf1);
                 sf0 = sf1 = 0;
@@ -230,14 +258,14 @@ NVFP4_DEVICE void emit_tile(const TileShare<kRows, kBK, kThreads>& s, uint32_t a
 
 // Shared-memory tile in, products out; `on_loaded()` runs between the reads and the
 // arithmetic (the caller releases the BF16 slot there).
-template <uint32_t kRows, uint32_t kBK, uint32_t kThreads, bool kResidual, typename OnLoaded>
+template <uint32_t kRows, uint32_t kBK, uint32_t kThreads, bool kResidual, uint32_t kSfCols = 4, typename OnLoaded>
 NVFP4_DEVICE void transform_tile(uint32_t a_smem, uint32_t a0_smem, uint32_t a1_smem, uint32_t sfa0_smem,
                                  uint32_t sfa1_smem, uint32_t t, OnLoaded&& on_loaded)
 {
     TileShare<kRows, kBK, kThreads> s;
     load_tile_smem(s, a_smem, t);
     on_loaded();
-    emit_tile<kRows, kBK, kThreads, kResidual>(s, a0_smem, a1_smem, sfa0_smem, sfa1_smem, t);
+    emit_tile<kRows, kBK, kThreads, kResidual, kSfCols>(s, a0_smem, a1_smem, sfa0_smem, sfa1_smem, t);
 }
 
 }  // namespace nvfp4::xform
