@@ -84,7 +84,7 @@ int encode_tensor_map_2d(CUtensorMap* map, CUtensorMapDataType dtype, uint32_t e
 using namespace nvfp4;
 
 // cluster size the dispatcher picks when the caller leaves tune_cluster at 0
-static constexpr int kDefaultCluster = 1;
+static constexpr int kDefaultCluster = 2;
 
 extern "C" {
 

@@ -34,9 +34,9 @@ constexpr uint32_t BM = 128, BN = 256, BK = 128, kKAtoms = 2;
 constexpr uint32_t kSlotP0 = BM * BK / 2;                       // 8192: one packed pass
 constexpr uint32_t kSlotSFA = kKAtoms * 512;                    // 1024
 constexpr uint32_t kSlotB = BN * BK / 2, kSlotSFB = kKAtoms * 2 * 512;
-constexpr uint32_t kWarpTma = 0, kWarpMma = 1, kWarpSfb = 2, kWarpTmaA = 3, kWarpEpi0 = 4, kNumEpiWarps = 4, kWarpXform0 = 8;
+constexpr uint32_t kWarpTma = 0, kWarpMma = 1, kWarpSfb = 2, kWarpTmaA = 3, kWarpEpi0 = 4, kNumEpiWarps = 8, kWarpXform0 = 12;
 constexpr uint32_t kXformWarps = 8, kXformThreads = kXformWarps * 32;
-constexpr uint32_t kThreads = (kWarpXform0 + kXformWarps) * 32;   // 512
+constexpr uint32_t kThreads = (kWarpXform0 + kXformWarps) * 32;   // 640
 constexpr uint32_t kTmemCols = 512, kColAcc = 0, kColSFA0 = 256, kColSFA1 = 264, kColSFB = 272;
 
 template <uint32_t CL>
@@ -206,6 +206,7 @@ gemm_cluster_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_const
                     !ptx::mbar_wait(b_ready + rb.slot, rb.phase, abort_flag, pa, 2) ||
                     !ptx::mbar_wait(b_full + rb.slot, rb.phase, abort_flag, pa, 3)) { give_up(1); break; }
                 ptx::tcgen05_fence_after_sync();
+                const long long pt0 = ptx::probe_clock();
                 if (lane == 0) {
                     const uint32_t sfa0 = smem + C::kOffSFA0 + rp.slot * kSlotSFA;
                     const uint32_t sfa1 = smem + C::kOffSFA1 + rp.slot * kSlotSFA;
@@ -222,6 +223,8 @@ gemm_cluster_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_const
                             ptx::tcgen05_cp_32x128b_warpx4(tmem_base + kColSFB + 4 * (a * 2 + i),
                                                            ptx::make_smem_desc(sfb + (a * 2 + i) * 512, 128, ptx::kSwizzleNone));
                     }
+                    const long long pt1 = ptx::probe_clock();
+                    ptx::probe_count(pa, 4, pt1 - pt0);
                     const uint32_t a0 = smem + C::kOffA0 + rp.slot * kSlotP0;
                     const uint32_t a1 = smem + C::kOffA1 + rp.slot * kSlotP0;
                     const uint32_t b = smem + C::kOffB + rb.slot * kSlotB;
@@ -235,9 +238,12 @@ gemm_cluster_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_const
                             ptx::tcgen05_mma_nvf4(tmem_base + kColAcc, ptx::make_smem_desc(a1 + a * 32, 512, ptx::kSwizzle64B),
                                                   desc_b, idesc, tmem_base + kColSFA1 + 4 * a, tmem_base + kColSFB + 8 * a, 1u);
                     }
+                    const long long pt2 = ptx::probe_clock();
+                    ptx::probe_count(pa, 5, pt2 - pt1);
                     ptx::tcgen05_commit_cluster(p_empty + rp.slot, kAllCtas);   // frees this slot in every CTA's count
                     ptx::tcgen05_commit(b_empty + rb.slot);
                     if (kb == num_kb - 1) ptx::tcgen05_commit(tmem_full);
+                    ptx::probe_count(pa, 6, ptx::probe_clock() - pt2);
                 }
                 __syncwarp();
                 rp.advance<C::kDepthP>();
@@ -270,7 +276,11 @@ gemm_cluster_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_const
         }
     } else if (warp >= kWarpEpi0 && warp < kWarpEpi0 + kNumEpiWarps) {
         // ================= epilogue: TMEM -> x G_W -> BF16 -> global =================
-        const uint32_t quad = warp & 3;
+        // Eight warps: two per 32-lane quadrant of tensor memory, each draining 128 of the 256 columns in
+        // chunks of 16, with the load of the next chunk in flight while the current one is scaled, packed
+        // and stored.  The accumulator is handed back to the MMA warp as soon as its last chunk has left
+        // tensor memory, before that chunk is stored.
+        const uint32_t quad = warp & 3, half = (warp - kWarpEpi0) >> 2;
         uint32_t acc_phase = 0;
         for (uint32_t st = cid; st < num_super && ok; st += ncl) {
             uint32_t m_blk, ns;
@@ -282,25 +292,37 @@ gemm_cluster_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_const
             ptx::tcgen05_fence_after_sync();
             // accumulator lane m = 32 * quad + lane holds token row 64 * (lane / 16) + 16 * quad + lane % 16
             const uint32_t row = m_blk * BM + 64 * (lane >> 4) + 16 * quad + (lane & 15);
-            __nv_bfloat16* drow = p.d + static_cast<int64_t>(row) * p.ldd + n_blk * BN;
-#pragma unroll 1
-            for (uint32_t c = 0; c < BN; c += 32) {
-                uint32_t v[32];
-                ptx::tmem_ld_32x32b_x32(tmem_base + ((quad * 32) << 16) + kColAcc + c, v);
-                ptx::tmem_ld_wait();
-                uint32_t o[16];
+            __nv_bfloat16* drow = p.d + static_cast<int64_t>(row) * p.ldd + n_blk * BN + half * (BN / 2);
+            const uint32_t taddr = tmem_base + ((quad * 32) << 16) + kColAcc + half * (BN / 2);
+            auto emit = [&](const uint32_t (&v)[16], uint32_t c) {
+                uint32_t o[8];
 #pragma unroll
-                for (int i = 0; i < 16; ++i) {
+                for (int i = 0; i < 8; ++i) {
                     const __nv_bfloat162 h = __floats2bfloat162_rn(__uint_as_float(v[2 * i]) * g, __uint_as_float(v[2 * i + 1]) * g);
                     o[i] = *reinterpret_cast<const uint32_t*>(&h);
                 }
                 uint4* dst = reinterpret_cast<uint4*>(drow + c);
+                dst[0] = make_uint4(o[0], o[1], o[2], o[3]);
+                dst[1] = make_uint4(o[4], o[5], o[6], o[7]);
+            };
+            uint32_t va[16], vb[16];
+            ptx::tmem_ld_32x32b_x16(taddr, va);
+            ptx::tmem_ld_wait();
 #pragma unroll
-                for (int i = 0; i < 4; ++i) dst[i] = make_uint4(o[4 * i], o[4 * i + 1], o[4 * i + 2], o[4 * i + 3]);
+            for (uint32_t c = 0; c < BN / 2; c += 32) {
+                ptx::tmem_ld_32x32b_x16(taddr + c + 16, vb);
+                emit(va, c);
+                ptx::tmem_ld_wait();
+                if (c + 32 < BN / 2) {
+                    ptx::tmem_ld_32x32b_x16(taddr + c + 32, va);
+                } else {
+                    ptx::tcgen05_fence_before_sync();             // everything has left tensor memory
+                    __syncwarp();
+                    if (lane == 0) ptx::mbar_arrive(tmem_empty);
+                }
+                emit(vb, c + 16);
+                if (c + 32 < BN / 2) ptx::tmem_ld_wait();
             }
-            ptx::tcgen05_fence_before_sync();
-            __syncwarp();
-            if (lane == 0) ptx::mbar_arrive(tmem_empty);
             acc_phase ^= 1;
         }
     } else if (warp >= kWarpXform0) {
@@ -344,21 +366,28 @@ gemm_cluster_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_const
                 if constexpr (kResidual) ptx::sts16(smem + off_s1 + sf_addr, blk[0].s1 | (blk[1].s1 << 8));
                 ptx::fence_proxy_async_smem();                   // own stores -> async proxy (MMA reads, bulk-copy reads)
                 asm volatile("bar.sync 1, %0;" ::"n"(kXformThreads) : "memory");   // the whole share is written
-                if (t == 0) {
-                    // four runs of 16 packed rows per pass, one 256-byte run per scale atom, to the same
-                    // offsets in the peer; their bytes complete on the peer's P-full barrier of this slot
+                if (lane == 0) {
+                    // the share goes to the same offsets in the peer as a few contiguous runs (four runs of 16
+                    // packed rows per pass, one 256-byte run per scale atom); their bytes complete on the peer's
+                    // P-full barrier of this slot.  Each warp issues its part of the list, so that no single
+                    // warp falls behind the others by the time of twelve copy instructions.
                     const uint32_t bar = peer_pfull + rp.slot * 8;
-#pragma unroll
-                    for (uint32_t g = 0; g < 4; ++g) {
-                        const uint32_t o = (32 * g + 16 * rank) * 64;
+                    const uint32_t xw = warp - kWarpXform0;                  // 0..7
+                    if (xw < 4) {
+                        const uint32_t o = (32 * xw + 16 * rank) * 64;
                         ptx::bulk_copy_to_cta(peer_smem + off_a0 + o, smem + off_a0 + o, 1024, bar);
-                        if constexpr (kResidual) ptx::bulk_copy_to_cta(peer_smem + off_a1 + o, smem + off_a1 + o, 1024, bar);
+                    } else if constexpr (kResidual) {
+                        const uint32_t o = (32 * (xw - 4) + 16 * rank) * 64;
+                        ptx::bulk_copy_to_cta(peer_smem + off_a1 + o, smem + off_a1 + o, 1024, bar);
                     }
-#pragma unroll
-                    for (uint32_t a = 0; a < kKAtoms; ++a) {
-                        const uint32_t o = a * 512 + 16 * rank * 16;
+                    if (xw < kKAtoms) {
+                        const uint32_t o = xw * 512 + 16 * rank * 16;
                         ptx::bulk_copy_to_cta(peer_smem + off_s0 + o, smem + off_s0 + o, 256, bar);
-                        if constexpr (kResidual) ptx::bulk_copy_to_cta(peer_smem + off_s1 + o, smem + off_s1 + o, 256, bar);
+                    } else if (xw < 2 * kKAtoms) {
+                        if constexpr (kResidual) {
+                            const uint32_t o = (xw - kKAtoms) * 512 + 16 * rank * 16;
+                            ptx::bulk_copy_to_cta(peer_smem + off_s1 + o, smem + off_s1 + o, 256, bar);
+                        }
                     }
                 }
                 if (lane == 0) {
@@ -371,8 +400,8 @@ gemm_cluster_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_const
         }
     }
 
-    ptx::probe_add(32 + (warp < 8 ? warp : 8), ptx::probe_clock() - probe_start);
-    if (warp == 1) ptx::probe_flush(pa, 2, 3, 4, 5);
+    ptx::probe_add(32 + (warp < 4 ? warp : (warp < kWarpXform0 ? 4 : 8)), ptx::probe_clock() - probe_start);
+    if (warp == 1) ptx::probe_flush(pa, 2, 3, 4, 5, 20, 21, 22);
     else if (warp >= kWarpXform0) ptx::probe_flush(pa, 11, 12);
     // teardown: nobody leaves while a peer may still write into its shared memory
     ptx::tcgen05_fence_before_sync();

@@ -74,16 +74,17 @@ NVFP4_DEVICE bool mbar_wait_impl(uint64_t* bar, uint32_t parity, volatile uint32
 // flushes once, when it leaves its loop.
 struct ProbeAcc {
 #ifdef NVFP4_PROBE
-    long long v[4] = {0, 0, 0, 0};
+    long long v[8] = {0, 0, 0, 0, 0, 0, 0, 0};
 #endif
 };
 #ifdef NVFP4_PROBE
 static __device__ unsigned long long g_probe[64];
-NVFP4_DEVICE void probe_flush(const ProbeAcc& a, int s0, int s1 = -1, int s2 = -1, int s3 = -1)
+NVFP4_DEVICE void probe_flush(const ProbeAcc& a, int s0, int s1 = -1, int s2 = -1, int s3 = -1, int s4 = -1, int s5 = -1,
+                              int s6 = -1, int s7 = -1)
 {
     if ((threadIdx.x & 31u) != 0) return;
-    const int sites[4] = {s0, s1, s2, s3};
-    for (int i = 0; i < 4; ++i)
+    const int sites[8] = {s0, s1, s2, s3, s4, s5, s6, s7};
+    for (int i = 0; i < 8; ++i)
         if (sites[i] >= 0) atomicAdd(&g_probe[sites[i]], static_cast<unsigned long long>(a.v[i]));
 }
 NVFP4_DEVICE void probe_add(int site, long long cycles)
@@ -101,7 +102,7 @@ NVFP4_DEVICE bool mbar_wait(uint64_t* bar, uint32_t parity, volatile uint32_t* a
 NVFP4_DEVICE void probe_count(ProbeAcc& acc, int idx, long long cycles) { acc.v[idx] += cycles; }
 #else
 NVFP4_DEVICE void probe_count(ProbeAcc&, int, long long) {}
-NVFP4_DEVICE void probe_flush(const ProbeAcc&, int, int = -1, int = -1, int = -1) {}
+NVFP4_DEVICE void probe_flush(const ProbeAcc&, int, int = -1, int = -1, int = -1, int = -1, int = -1, int = -1, int = -1) {}
 NVFP4_DEVICE void probe_add(int, long long) {}
 NVFP4_DEVICE long long probe_clock() { return 0; }
 NVFP4_DEVICE bool mbar_wait(uint64_t* bar, uint32_t parity, volatile uint32_t* abort_flag, ProbeAcc&, int)
