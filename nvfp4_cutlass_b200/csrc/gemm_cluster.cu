@@ -16,6 +16,9 @@
 // 256 bytes inside every 512-byte scale atom.  The epilogue applies the same map to the
 // accumulator lanes.
 //
+// The scale factors reach tensor memory through tcgen05.st issued by the (otherwise idle) epilogue
+// warps, not through tensor-memory copies issued by the MMA thread; see the MMA role below.
+//
 // Barriers: P-full of a CTA counts its own eight transform warps plus the bytes of the
 // peer's copies; P-empty counts one tcgen05.commit per CTA, delivered to both CTAs by the
 // commit's cluster mask, so a slot is rewritten (locally or by the peer's copies) only after
@@ -37,7 +40,9 @@ constexpr uint32_t kSlotB = BN * BK / 2, kSlotSFB = kKAtoms * 2 * 512;
 constexpr uint32_t kWarpTma = 0, kWarpMma = 1, kWarpSfb = 2, kWarpTmaA = 3, kWarpEpi0 = 4, kNumEpiWarps = 8, kWarpXform0 = 12;
 constexpr uint32_t kXformWarps = 8, kXformThreads = kXformWarps * 32;
 constexpr uint32_t kThreads = (kWarpXform0 + kXformWarps) * 32;   // 640
-constexpr uint32_t kTmemCols = 512, kColAcc = 0, kColSFA0 = 256, kColSFA1 = 264, kColSFB = 272;
+// tensor memory: 256 accumulator columns, then two buffers of 32 scale columns (SFA0 8, SFA1 8, SFB 16) that
+// alternate from K block to K block
+constexpr uint32_t kTmemCols = 512, kColAcc = 0, kColSF = 256, kSfBufCols = 32, kSfA0 = 0, kSfA1 = 8, kSfB = 16;
 
 template <uint32_t CL>
 struct Cfg {
@@ -53,7 +58,7 @@ struct Cfg {
     static constexpr uint32_t kOffSFA1 = kOffSFA0 + kDepthP * kSlotSFA;
     static constexpr uint32_t kOffSFB = kOffSFA1 + kDepthP * kSlotSFA;
     static constexpr uint32_t kOffBars = kOffSFB + kDepthB * kSlotSFB;
-    static constexpr uint32_t kNumBars = 2 * kDepthA + 2 * kDepthP + 3 * kDepthB + 2;
+    static constexpr uint32_t kNumBars = 2 * kDepthA + 2 * kDepthP + 2 * kDepthB + 2 + 2;
     static constexpr uint32_t kSmemAlloc = kOffBars + kNumBars * 8 + 16 + 1024;
     static_assert(kSmemAlloc <= 232448, "shared memory budget");
     static constexpr uint32_t kBlocksPerThread = kRows * (BK / 16) / kXformThreads;   // 2
@@ -106,9 +111,9 @@ gemm_cluster_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_const
     uint64_t* p_full = a_empty + C::kDepthA;
     uint64_t* p_empty = p_full + C::kDepthP;
     uint64_t* b_full = p_empty + C::kDepthP;
-    uint64_t* b_ready = b_full + C::kDepthB;
-    uint64_t* b_empty = b_ready + C::kDepthB;
-    uint64_t* tmem_full = b_empty + C::kDepthB;
+    uint64_t* b_empty = b_full + C::kDepthB;
+    uint64_t* sf_full = b_empty + C::kDepthB;        // [2]: scales of a K block are in tensor memory
+    uint64_t* tmem_full = sf_full + 2;
     uint64_t* tmem_empty = tmem_full + 1;
     uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(tmem_empty + 1);
     volatile uint32_t* abort_flag = tmem_slot + 1;
@@ -124,9 +129,10 @@ gemm_cluster_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_const
         }
         for (uint32_t i = 0; i < C::kDepthB; ++i) {
             ptx::mbar_init(b_full + i, 1);
-            ptx::mbar_init(b_ready + i, 1);
             ptx::mbar_init(b_empty + i, 1);
         }
+        ptx::mbar_init(sf_full, kNumEpiWarps);
+        ptx::mbar_init(sf_full + 1, kNumEpiWarps);
         ptx::mbar_init(tmem_full, 1);
         ptx::mbar_init(tmem_empty, kNumEpiWarps);
         *abort_flag = 0;
@@ -194,49 +200,37 @@ gemm_cluster_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_const
         }
     } else if (warp == kWarpMma) {
         // ================= MMA issue =================
+        // The scale factors are already in tensor memory when a K block is issued (the scale warps
+        // put them there with tcgen05.st), so a K block costs this thread four MMAs and its commits:
+        // a tensor-memory copy of one scale atom costs as much issue time as an MMA of N <= 128, and
+        // eight of them per K block were the larger half of the tensor-side time.
         Ring rp, rb;
-        uint32_t acc_phase = 0;
+        uint32_t acc_phase = 0, cnt = 0;
         constexpr uint32_t idesc = ptx::make_idesc_nvf4(BM, BN);
         constexpr uint16_t kAllCtas = static_cast<uint16_t>((1u << CL) - 1u);
         for (uint32_t st = cid; st < num_super && ok; st += ncl) {
             if (!ptx::mbar_wait(tmem_empty, acc_phase ^ 1, abort_flag, pa, 0)) { give_up(1); break; }
             ptx::tcgen05_fence_after_sync();
-            for (uint32_t kb = 0; kb < num_kb; ++kb) {
+            for (uint32_t kb = 0; kb < num_kb; ++kb, ++cnt) {
+                const uint32_t buf = cnt & 1u;
                 if (!ptx::mbar_wait_cluster(p_full + rp.slot, rp.phase, abort_flag, pa, 1) ||
-                    !ptx::mbar_wait(b_ready + rb.slot, rb.phase, abort_flag, pa, 2) ||
-                    !ptx::mbar_wait(b_full + rb.slot, rb.phase, abort_flag, pa, 3)) { give_up(1); break; }
+                    !ptx::mbar_wait(b_full + rb.slot, rb.phase, abort_flag, pa, 2) ||
+                    !ptx::mbar_wait(sf_full + buf, (cnt >> 1) & 1u, abort_flag, pa, 3)) { give_up(1); break; }
                 ptx::tcgen05_fence_after_sync();
-                const long long pt0 = ptx::probe_clock();
+                const long long pt1 = ptx::probe_clock();
                 if (lane == 0) {
-                    const uint32_t sfa0 = smem + C::kOffSFA0 + rp.slot * kSlotSFA;
-                    const uint32_t sfa1 = smem + C::kOffSFA1 + rp.slot * kSlotSFA;
-                    const uint32_t sfb = smem + C::kOffSFB + rb.slot * kSlotSFB;
-#pragma unroll
-                    for (uint32_t a = 0; a < kKAtoms; ++a) {
-                        ptx::tcgen05_cp_32x128b_warpx4(tmem_base + kColSFA0 + 4 * a,
-                                                       ptx::make_smem_desc(sfa0 + a * 512, 128, ptx::kSwizzleNone));
-                        if constexpr (kResidual)
-                            ptx::tcgen05_cp_32x128b_warpx4(tmem_base + kColSFA1 + 4 * a,
-                                                           ptx::make_smem_desc(sfa1 + a * 512, 128, ptx::kSwizzleNone));
-#pragma unroll
-                        for (uint32_t i = 0; i < 2; ++i)
-                            ptx::tcgen05_cp_32x128b_warpx4(tmem_base + kColSFB + 4 * (a * 2 + i),
-                                                           ptx::make_smem_desc(sfb + (a * 2 + i) * 512, 128, ptx::kSwizzleNone));
-                    }
-                    const long long pt1 = ptx::probe_clock();
-                    ptx::probe_count(pa, 4, pt1 - pt0);
                     const uint32_t a0 = smem + C::kOffA0 + rp.slot * kSlotP0;
                     const uint32_t a1 = smem + C::kOffA1 + rp.slot * kSlotP0;
                     const uint32_t b = smem + C::kOffB + rb.slot * kSlotB;
+                    const uint32_t sf = tmem_base + kColSF + buf * kSfBufCols;
 #pragma unroll
                     for (uint32_t a = 0; a < kKAtoms; ++a) {
                         const uint64_t desc_b = ptx::make_smem_desc(b + a * 32, 512, ptx::kSwizzle64B);
                         ptx::tcgen05_mma_nvf4(tmem_base + kColAcc, ptx::make_smem_desc(a0 + a * 32, 512, ptx::kSwizzle64B), desc_b,
-                                              idesc, tmem_base + kColSFA0 + 4 * a, tmem_base + kColSFB + 8 * a,
-                                              (kb | a) != 0 ? 1u : 0u);
+                                              idesc, sf + kSfA0 + 4 * a, sf + kSfB + 8 * a, (kb | a) != 0 ? 1u : 0u);
                         if constexpr (kResidual)
                             ptx::tcgen05_mma_nvf4(tmem_base + kColAcc, ptx::make_smem_desc(a1 + a * 32, 512, ptx::kSwizzle64B),
-                                                  desc_b, idesc, tmem_base + kColSFA1 + 4 * a, tmem_base + kColSFB + 8 * a, 1u);
+                                                  desc_b, idesc, sf + kSfA1 + 4 * a, sf + kSfB + 8 * a, 1u);
                     }
                     const long long pt2 = ptx::probe_clock();
                     ptx::probe_count(pa, 5, pt2 - pt1);
@@ -251,38 +245,60 @@ gemm_cluster_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_const
             }
             acc_phase ^= 1;
         }
-    } else if (warp == kWarpSfb) {
-        // ================= weight-scale transpose into tensor-memory-copy order =================
-        Ring rb;
-        for (uint32_t st = cid; st < num_super && ok; st += ncl) {
-            for (uint32_t kb = 0; kb < num_kb; ++kb) {
-                if (!ptx::mbar_wait_impl(b_full + rb.slot, rb.phase, abort_flag)) { give_up(1); break; }
-                const uint32_t base = smem + C::kOffSFB + rb.slot * kSlotSFB;
-#pragma unroll
-                for (uint32_t i = 0; i < kKAtoms * 2; ++i) {
-                    const uint32_t atom = base + i * 512;
-                    const uint32_t v0 = ptx::lds32(atom + lane * 4);
-                    const uint32_t v1 = ptx::lds32(atom + (32 + lane) * 4);
-                    const uint32_t v2 = ptx::lds32(atom + (64 + lane) * 4);
-                    const uint32_t v3 = ptx::lds32(atom + (96 + lane) * 4);
-                    __syncwarp();
-                    ptx::sts128(atom + lane * 16, v0, v1, v2, v3);
-                }
-                ptx::fence_proxy_async_smem();
-                __syncwarp();
-                if (lane == 0) ptx::mbar_arrive(b_ready + rb.slot);
-                rb.advance<C::kDepthB>();
-            }
-        }
     } else if (warp >= kWarpEpi0 && warp < kWarpEpi0 + kNumEpiWarps) {
         // ================= epilogue: TMEM -> x G_W -> BF16 -> global =================
         // Eight warps: two per 32-lane quadrant of tensor memory, each draining 128 of the 256 columns in
         // chunks of 16, with the load of the next chunk in flight while the current one is scaled, packed
         // and stored.  The accumulator is handed back to the MMA warp as soon as its last chunk has left
         // tensor memory, before that chunk is stored.
+        //
+        // During the mainloop the same warps carry the scale factors from shared to tensor memory with
+        // tcgen05.st (a warp reaches only its own quadrant of lanes, and the MMA wants each quadrant to hold
+        // a copy): lane r of each quadrant gets the scale words of rows r, r + 32, r + 64, r + 96 in four
+        // consecutive columns.  Warps 4-7 take the weight scales straight from the rows TMA landed (which also
+        // does the transposition a tensor-memory copy would have needed), warps 8-11 the activation scales of
+        // both passes.  Two column buffers alternate; a buffer is rewritten once the MMAs of two K blocks
+        // earlier have retired (their commit on the B-empty barrier).
         const uint32_t quad = warp & 3, half = (warp - kWarpEpi0) >> 2;
-        uint32_t acc_phase = 0;
+        uint32_t acc_phase = 0, cnt = 0;
+        Ring rp, rb;
         for (uint32_t st = cid; st < num_super && ok; st += ncl) {
+            for (uint32_t kb = 0; kb < num_kb; ++kb, ++cnt) {
+                const uint32_t buf = cnt & 1u;
+                const uint32_t sf = tmem_base + ((quad * 32) << 16) + kColSF + buf * kSfBufCols;
+                const bool src_ok = half == 0 ? ptx::mbar_wait(b_full + rb.slot, rb.phase, abort_flag, pa, 1)
+                                              : ptx::mbar_wait_cluster(p_full + rp.slot, rp.phase, abort_flag, pa, 1);
+                if (!src_ok) { give_up(1); break; }
+                if (cnt >= 2 && !ptx::mbar_wait(b_empty + (cnt - 2) % C::kDepthB, ((cnt - 2) / C::kDepthB) & 1u, abort_flag, pa, 2)) {
+                    give_up(1);
+                    break;
+                }
+                ptx::tcgen05_fence_after_sync();
+                if (half == 0) {
+                    const uint32_t sfb = smem + C::kOffSFB + rb.slot * kSlotSFB + lane * 4;
+#pragma unroll
+                    for (uint32_t i = 0; i < kKAtoms * 2; ++i)
+                        ptx::tmem_st_32x32b_x4(sf + kSfB + 4 * i, ptx::lds32(sfb + i * 512), ptx::lds32(sfb + i * 512 + 128),
+                                               ptx::lds32(sfb + i * 512 + 256), ptx::lds32(sfb + i * 512 + 384));
+                } else {
+#pragma unroll
+                    for (uint32_t a = 0; a < kKAtoms; ++a) {
+                        const uint4 v0 = ptx::lds128(smem + C::kOffSFA0 + rp.slot * kSlotSFA + a * 512 + lane * 16);
+                        ptx::tmem_st_32x32b_x4(sf + kSfA0 + 4 * a, v0.x, v0.y, v0.z, v0.w);
+                        if constexpr (kResidual) {
+                            const uint4 v1 = ptx::lds128(smem + C::kOffSFA1 + rp.slot * kSlotSFA + a * 512 + lane * 16);
+                            ptx::tmem_st_32x32b_x4(sf + kSfA1 + 4 * a, v1.x, v1.y, v1.z, v1.w);
+                        }
+                    }
+                }
+                ptx::tmem_st_wait();
+                ptx::tcgen05_fence_before_sync();
+                __syncwarp();
+                if (lane == 0) ptx::mbar_arrive(sf_full + buf);
+                rp.advance<C::kDepthP>();
+                rb.advance<C::kDepthB>();
+            }
+            if (!ok) break;
             uint32_t m_blk, ns;
             super_tile_coords(st, num_m, num_ns, p.group_m, m_blk, ns);
             const uint32_t n_blk = ns * CL + rank;
@@ -402,6 +418,7 @@ gemm_cluster_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_const
 
     ptx::probe_add(32 + (warp < 4 ? warp : (warp < kWarpXform0 ? 4 : 8)), ptx::probe_clock() - probe_start);
     if (warp == 1) ptx::probe_flush(pa, 2, 3, 4, 5, 20, 21, 22);
+    else if (warp >= kWarpEpi0 && warp < kWarpXform0) ptx::probe_flush(pa, 9, 10, 13);
     else if (warp >= kWarpXform0) ptx::probe_flush(pa, 11, 12);
     // teardown: nobody leaves while a peer may still write into its shared memory
     ptx::tcgen05_fence_before_sync();
