@@ -194,15 +194,18 @@ int nvfp4_grouped_gemm_contiguous(const void* a, int64_t lda_elems, const void* 
     }
     NVFP4_REQUIRE(tune_xform_warps == 0 || tune_xform_warps == 8 || tune_xform_warps == 16,
                   "tune_transform_warps must be 0, 8 or 16");
-    // tune_cluster: 2 = two CTAs share one transformed activation tile (needs N % 512 == 0), 1 = single-CTA
-    // kernel, 0 = the library's choice
+    // tune_cluster: 2 / 4 = that many CTAs share one transformed activation tile (needs N % (256 * cluster) == 0),
+    // 1 = single-CTA kernel, 0 = the library's choice
     int cluster = tune ? tune[8] : 0;
-    NVFP4_REQUIRE(cluster == 0 || cluster == 1 || cluster == 2, "tune_cluster must be 0, 1 or 2");
-    NVFP4_REQUIRE(cluster != 2 || N % 512 == 0, "tune_cluster 2 needs N %% 512 == 0 (N=%d)", N);
-    if (cluster == 0) cluster = kDefaultCluster == 2 && N % 512 == 0 && tune_xform_warps == 0 && !(tune && tune[9]) ? 2 : 1;
-    if (cluster == 2 && dev->num_sms >= 2)
+    NVFP4_REQUIRE(cluster == 0 || cluster == 1 || cluster == 2 || cluster == 4, "tune_cluster must be 0, 1, 2 or 4");
+    NVFP4_REQUIRE(cluster < 2 || N % (256 * cluster) == 0, "tune_cluster %d needs N %% %d == 0 (N=%d)", cluster, 256 * cluster, N);
+    if (cluster == 0) {
+        const bool plain = tune_xform_warps == 0 && !(tune && tune[9]);
+        cluster = plain && N % (256 * kDefaultCluster) == 0 ? kDefaultCluster : (plain && N % 512 == 0 ? 2 : 1);
+    }
+    if (cluster >= 2 && dev->num_sms >= cluster)
         return launch_gemm_cluster(a, lda_elems, b, sfb, gw, d, ldd_elems, m_indices, M, N, K, E,
-                                   enable_residual_pass != 0, tune_sched_group, dev->num_sms, device_status, s);
+                                   enable_residual_pass != 0, cluster, tune_sched_group, dev->num_sms, device_status, s);
     // tune_direct_a = 1: the transform reads activations straight from global memory instead of a TMA-fed
     // shared-memory ring (measured slower on B200: 1.89 ms against 1.06 ms on the Mixtral-like shape)
     const bool direct_a = tune && tune[9] == 1 && tune_xform_warps != 16;

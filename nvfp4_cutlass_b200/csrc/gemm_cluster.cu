@@ -1,5 +1,6 @@
 // Grouped dual-NVFP4 GEMM, normal orientation, with the activation transform shared by
-// the two CTAs of a thread-block cluster.
+// the CTAs of a thread-block cluster (two, or four: the text below describes pairs; with four
+// CTAs every share is half as large and goes to three peers).
 //
 // Both CTAs work on the same 128 token rows and on two neighbouring 256-column weight
 // tiles.  The quantised activation tile (A0, A1 and their scales) is the same for both, so
@@ -37,7 +38,7 @@ constexpr uint32_t BM = 128, BN = 256, BK = 128, kKAtoms = 2;
 constexpr uint32_t kSlotP0 = BM * BK / 2;                       // 8192: one packed pass
 constexpr uint32_t kSlotSFA = kKAtoms * 512;                    // 1024
 constexpr uint32_t kSlotB = BN * BK / 2, kSlotSFB = kKAtoms * 2 * 512;
-constexpr uint32_t kWarpTma = 0, kWarpMma = 1, kWarpSfb = 2, kWarpTmaA = 3, kWarpEpi0 = 4, kNumEpiWarps = 8, kWarpXform0 = 12;
+constexpr uint32_t kWarpTma = 0, kWarpMma = 1, kWarpPush = 2, kWarpTmaA = 3, kWarpEpi0 = 4, kNumEpiWarps = 8, kWarpXform0 = 12;
 constexpr uint32_t kXformWarps = 8, kXformThreads = kXformWarps * 32;
 constexpr uint32_t kThreads = (kWarpXform0 + kXformWarps) * 32;   // 640
 // tensor memory: 256 accumulator columns, then two buffers of 32 scale columns (SFA0 8, SFA1 8, SFB 16) that
@@ -46,10 +47,12 @@ constexpr uint32_t kTmemCols = 512, kColAcc = 0, kColSF = 256, kSfBufCols = 32, 
 
 template <uint32_t CL>
 struct Cfg {
-    static_assert(CL == 2, "the row map and the copy list below are written for pairs");
+    static_assert(CL == 2 || CL == 4, "cluster of two or four CTAs");
     static constexpr uint32_t kRows = BM / CL;                  // rows this CTA loads and transforms
-    static constexpr uint32_t kSlotA = kRows * BK * 2;          // 16384
-    static constexpr uint32_t kDepthA = 4, kDepthP = 3, kDepthB = 5;
+    static constexpr uint32_t kRun = 32 / CL;                   // consecutive MMA rows it owns in every group of 32
+    static constexpr uint32_t kSlotA = kRows * BK * 2;          // 16 KB (pairs), 8 KB (quads)
+    static constexpr uint32_t kActiveWarps = CL == 4 ? 4 : 8;   // transform warps in use: two 16-blocks per thread
+    static constexpr uint32_t kDepthA = CL == 4 ? 6 : 4, kDepthP = 3, kDepthB = 5;
     static constexpr uint32_t kOffA = 0;
     static constexpr uint32_t kOffA0 = kOffA + kDepthA * kSlotA;
     static constexpr uint32_t kOffA1 = kOffA0 + kDepthP * kSlotP0;
@@ -58,11 +61,13 @@ struct Cfg {
     static constexpr uint32_t kOffSFA1 = kOffSFA0 + kDepthP * kSlotSFA;
     static constexpr uint32_t kOffSFB = kOffSFA1 + kDepthP * kSlotSFA;
     static constexpr uint32_t kOffBars = kOffSFB + kDepthB * kSlotSFB;
-    static constexpr uint32_t kNumBars = 2 * kDepthA + 2 * kDepthP + 2 * kDepthB + 2 + 2;
+    static constexpr uint32_t kNumBars = 2 * kDepthA + 3 * kDepthP + 2 * kDepthB + 2 + 2;
     static constexpr uint32_t kSmemAlloc = kOffBars + kNumBars * 8 + 16 + 1024;
     static_assert(kSmemAlloc <= 232448, "shared memory budget");
-    static constexpr uint32_t kBlocksPerThread = kRows * (BK / 16) / kXformThreads;   // 2
-    static_assert(kBlocksPerThread == 2, "two 16-blocks (one 16-byte chunk) per thread");
+    static_assert(kRows * (BK / 16) == kActiveWarps * 32 * 2, "two 16-blocks (one 16-byte chunk) per thread");
+    // what one CTA pushes to one peer per K block and pass: four runs of kRun packed rows, one run per scale atom
+    static constexpr uint32_t kRunBytes = kRun * 64, kSfRunBytes = kRun * 16;
+    static constexpr uint32_t kBytesPerPass = 4 * kRunBytes + kKAtoms * kSfRunBytes;
 };
 
 struct Params {
@@ -112,7 +117,8 @@ gemm_cluster_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_const
     uint64_t* p_empty = p_full + C::kDepthP;
     uint64_t* b_full = p_empty + C::kDepthP;
     uint64_t* b_empty = b_full + C::kDepthB;
-    uint64_t* sf_full = b_empty + C::kDepthB;        // [2]: scales of a K block are in tensor memory
+    uint64_t* share_full = b_empty + C::kDepthB;     // [kDepthP]: this CTA's share of a slot is written
+    uint64_t* sf_full = share_full + C::kDepthP;     // [2]: scales of a K block are in tensor memory
     uint64_t* tmem_full = sf_full + 2;
     uint64_t* tmem_empty = tmem_full + 1;
     uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(tmem_empty + 1);
@@ -122,9 +128,10 @@ gemm_cluster_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_const
     const uint32_t rank = ptx::cluster_cta_rank();
 
     if (threadIdx.x == 0) {
-        for (uint32_t i = 0; i < C::kDepthA; ++i) { ptx::mbar_init(a_full + i, 1); ptx::mbar_init(a_empty + i, kXformWarps); }
+        for (uint32_t i = 0; i < C::kDepthA; ++i) { ptx::mbar_init(a_full + i, 1); ptx::mbar_init(a_empty + i, C::kActiveWarps); }
         for (uint32_t i = 0; i < C::kDepthP; ++i) {
-            ptx::mbar_init(p_full + i, kXformWarps);            // own transform warps; the peer's share arrives as bytes
+            ptx::mbar_init(p_full + i, C::kActiveWarps + 1);    // own transform warps + the push warp; peers' shares arrive as bytes
+            ptx::mbar_init(share_full + i, C::kActiveWarps);
             ptx::mbar_init(p_empty + i, CL);                    // one commit per CTA of the cluster
         }
         for (uint32_t i = 0; i < C::kDepthB; ++i) {
@@ -245,6 +252,40 @@ gemm_cluster_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_const
             }
             acc_phase ^= 1;
         }
+    } else if (warp == kWarpPush) {
+        // ================= push: this CTA's finished share to every peer =================
+        // One bulk shared-to-shared copy per contiguous run, to the same offsets in the peer's slot; the bytes
+        // complete on the peer's P-full barrier.  The lanes of the warp issue one copy each, so the transform
+        // warps never wait for copy issue and the list costs one instruction slot per 32 copies.
+        constexpr uint32_t kPerPeer = (kResidual ? 2u : 1u) * (4u + kKAtoms);
+        constexpr uint32_t kCopies = (CL - 1) * kPerPeer;
+        constexpr uint32_t kPeerBytes = (CL - 1) * (kResidual ? 2u : 1u) * C::kBytesPerPass;
+        Ring rp;
+        for (uint32_t st = cid; st < num_super && ok; st += ncl) {
+            for (uint32_t kb = 0; kb < num_kb; ++kb) {
+                if (!ptx::mbar_wait_impl(share_full + rp.slot, rp.phase, abort_flag)) { give_up(1); break; }
+                const uint32_t off_a0 = C::kOffA0 + rp.slot * kSlotP0, off_a1 = C::kOffA1 + rp.slot * kSlotP0;
+                const uint32_t off_s0 = C::kOffSFA0 + rp.slot * kSlotSFA, off_s1 = C::kOffSFA1 + rp.slot * kSlotSFA;
+                for (uint32_t i = lane; i < kCopies; i += 32) {
+                    const uint32_t peer = (rank + 1 + i / kPerPeer) % CL;
+                    uint32_t j = i % kPerPeer, off, bytes;
+                    const bool second = j >= 4 + kKAtoms;        // second pass (A1 / SFA1)
+                    if (second) j -= 4 + kKAtoms;
+                    if (j < 4) {
+                        off = (second ? off_a1 : off_a0) + (32 * j + C::kRun * rank) * 64;
+                        bytes = C::kRunBytes;
+                    } else {
+                        off = (second ? off_s1 : off_s0) + (j - 4) * 512 + C::kRun * rank * 16;
+                        bytes = C::kSfRunBytes;
+                    }
+                    ptx::bulk_copy_to_cta(ptx::map_to_cta(smem + off, peer), smem + off, bytes,
+                                          ptx::map_to_cta(ptx::smem_u32(p_full + rp.slot), peer));
+                }
+                if (lane == 0) ptx::mbar_arrive_expect_tx(p_full + rp.slot, kPeerBytes);
+                __syncwarp();
+                rp.advance<C::kDepthP>();
+            }
+        }
     } else if (warp >= kWarpEpi0 && warp < kWarpEpi0 + kNumEpiWarps) {
         // ================= epilogue: TMEM -> x G_W -> BF16 -> global =================
         // Eight warps: two per 32-lane quadrant of tensor memory, each draining 128 of the 256 columns in
@@ -306,8 +347,8 @@ gemm_cluster_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_const
             const float g = __ldg(p.gw + e);
             if (!ptx::mbar_wait_impl(tmem_full, acc_phase, abort_flag)) { give_up(1); break; }
             ptx::tcgen05_fence_after_sync();
-            // accumulator lane m = 32 * quad + lane holds token row 64 * (lane / 16) + 16 * quad + lane % 16
-            const uint32_t row = m_blk * BM + 64 * (lane >> 4) + 16 * quad + (lane & 15);
+            // accumulator lane m = 32 * quad + lane holds token row kRows * (lane / kRun) + kRun * quad + lane % kRun
+            const uint32_t row = m_blk * BM + C::kRows * (lane / C::kRun) + C::kRun * quad + lane % C::kRun;
             __nv_bfloat16* drow = p.d + static_cast<int64_t>(row) * p.ldd + n_blk * BN + half * (BN / 2);
             const uint32_t taddr = tmem_base + ((quad * 32) << 16) + kColAcc + half * (BN / 2);
             auto emit = [&](const uint32_t (&v)[16], uint32_t c) {
@@ -342,76 +383,51 @@ gemm_cluster_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_const
             acc_phase ^= 1;
         }
     } else if (warp >= kWarpXform0) {
-        // ================= transform: this CTA's 64 rows, then the share goes to the peer =================
+        // ================= transform: this CTA's rows into its own P slot =================
         const uint32_t t = threadIdx.x - kWarpXform0 * 32;
-        const uint32_t lrow = t % C::kRows;                                              // row inside this CTA's share
-        const uint32_t mrow = 32 * (lrow >> 4) + 16 * rank + (lrow & 15);               // its row in the MMA tile
-        const uint32_t first_block = (t / C::kRows) * C::kBlocksPerThread;
-        const uint32_t peer_smem = ptx::map_to_cta(smem, rank ^ 1u);
-        const uint32_t peer_pfull = ptx::map_to_cta(ptx::smem_u32(p_full), rank ^ 1u);
-        constexpr uint32_t kPeerBytes = kResidual ? 2 * (4 * 1024 + 2 * 256) : (4 * 1024 + 2 * 256);
-        Ring ra, rp;
-        for (uint32_t st = cid; st < num_super && ok; st += ncl) {
-            for (uint32_t kb = 0; kb < num_kb; ++kb) {
-                if (!ptx::mbar_wait(a_full + ra.slot, ra.phase, abort_flag, pa, 0)) { give_up(1); break; }
-                const uint32_t a_smem = smem + C::kOffA + ra.slot * C::kSlotA;
-                uint32_t w[2][8];
+        if (warp - kWarpXform0 < C::kActiveWarps) {
+            const uint32_t lrow = t % C::kRows;                                                      // row inside this CTA's share
+            const uint32_t mrow = 32 * (lrow / C::kRun) + C::kRun * rank + lrow % C::kRun;           // its row in the MMA tile
+            const uint32_t first_block = (t / C::kRows) * 2;
+            Ring ra, rp;
+            for (uint32_t st = cid; st < num_super && ok; st += ncl) {
+                for (uint32_t kb = 0; kb < num_kb; ++kb) {
+                    if (!ptx::mbar_wait(a_full + ra.slot, ra.phase, abort_flag, pa, 0)) { give_up(1); break; }
+                    const uint32_t a_smem = smem + C::kOffA + ra.slot * C::kSlotA;
+                    uint32_t w[2][8];
 #pragma unroll
-                for (uint32_t j = 0; j < 2; ++j) {
-                    const uint32_t k = (first_block + j) * 16u;
-                    const uint4 lo = ptx::lds128(a_smem + xform::a_bf16_offset<C::kRows>(lrow, k));
-                    const uint4 hi = ptx::lds128(a_smem + xform::a_bf16_offset<C::kRows>(lrow, k + 8));
-                    w[j][0] = lo.x; w[j][1] = lo.y; w[j][2] = lo.z; w[j][3] = lo.w;
-                    w[j][4] = hi.x; w[j][5] = hi.y; w[j][6] = hi.z; w[j][7] = hi.w;
-                }
-                __syncwarp();
-                if (lane == 0) ptx::mbar_arrive(a_empty + ra.slot);   // the tile now lives in registers
-                // both tensor cores must be done with this slot before anyone rewrites it
-                if (!ptx::mbar_wait_cluster(p_empty + rp.slot, rp.phase ^ 1, abort_flag, pa, 1)) { give_up(1); break; }
-                const uint32_t off_a0 = C::kOffA0 + rp.slot * kSlotP0, off_a1 = C::kOffA1 + rp.slot * kSlotP0;
-                const uint32_t off_s0 = C::kOffSFA0 + rp.slot * kSlotSFA, off_s1 = C::kOffSFA1 + rp.slot * kSlotSFA;
-                xform::Block16 blk[2];
-                xform::decompose_block16<kResidual>(w[0], blk[0]);
-                xform::decompose_block16<kResidual>(w[1], blk[1]);
-                const uint32_t off = xform::fp4_offset<BK>(mrow, first_block * 16u);
-                ptx::sts128(smem + off_a0 + off, blk[0].q0[0], blk[0].q0[1], blk[1].q0[0], blk[1].q0[1]);
-                if constexpr (kResidual)
-                    ptx::sts128(smem + off_a1 + off, blk[0].q1[0], blk[0].q1[1], blk[1].q1[0], blk[1].q1[1]);
-                const uint32_t sf_addr = (first_block >> 2) * 512u + xform::sf_word_offset(mrow) + (first_block & 2u);
-                ptx::sts16(smem + off_s0 + sf_addr, blk[0].s0 | (blk[1].s0 << 8));
-                if constexpr (kResidual) ptx::sts16(smem + off_s1 + sf_addr, blk[0].s1 | (blk[1].s1 << 8));
-                ptx::fence_proxy_async_smem();                   // own stores -> async proxy (MMA reads, bulk-copy reads)
-                asm volatile("bar.sync 1, %0;" ::"n"(kXformThreads) : "memory");   // the whole share is written
-                if (lane == 0) {
-                    // the share goes to the same offsets in the peer as a few contiguous runs (four runs of 16
-                    // packed rows per pass, one 256-byte run per scale atom); their bytes complete on the peer's
-                    // P-full barrier of this slot.  Each warp issues its part of the list, so that no single
-                    // warp falls behind the others by the time of twelve copy instructions.
-                    const uint32_t bar = peer_pfull + rp.slot * 8;
-                    const uint32_t xw = warp - kWarpXform0;                  // 0..7
-                    if (xw < 4) {
-                        const uint32_t o = (32 * xw + 16 * rank) * 64;
-                        ptx::bulk_copy_to_cta(peer_smem + off_a0 + o, smem + off_a0 + o, 1024, bar);
-                    } else if constexpr (kResidual) {
-                        const uint32_t o = (32 * (xw - 4) + 16 * rank) * 64;
-                        ptx::bulk_copy_to_cta(peer_smem + off_a1 + o, smem + off_a1 + o, 1024, bar);
+                    for (uint32_t j = 0; j < 2; ++j) {
+                        const uint32_t k = (first_block + j) * 16u;
+                        const uint4 lo = ptx::lds128(a_smem + xform::a_bf16_offset<C::kRows>(lrow, k));
+                        const uint4 hi = ptx::lds128(a_smem + xform::a_bf16_offset<C::kRows>(lrow, k + 8));
+                        w[j][0] = lo.x; w[j][1] = lo.y; w[j][2] = lo.z; w[j][3] = lo.w;
+                        w[j][4] = hi.x; w[j][5] = hi.y; w[j][6] = hi.z; w[j][7] = hi.w;
                     }
-                    if (xw < kKAtoms) {
-                        const uint32_t o = xw * 512 + 16 * rank * 16;
-                        ptx::bulk_copy_to_cta(peer_smem + off_s0 + o, smem + off_s0 + o, 256, bar);
-                    } else if (xw < 2 * kKAtoms) {
-                        if constexpr (kResidual) {
-                            const uint32_t o = (xw - kKAtoms) * 512 + 16 * rank * 16;
-                            ptx::bulk_copy_to_cta(peer_smem + off_s1 + o, smem + off_s1 + o, 256, bar);
-                        }
+                    __syncwarp();
+                    if (lane == 0) ptx::mbar_arrive(a_empty + ra.slot);   // the tile now lives in registers
+                    // every tensor core of the cluster must be done with this slot before anyone rewrites it
+                    if (!ptx::mbar_wait_cluster(p_empty + rp.slot, rp.phase ^ 1, abort_flag, pa, 1)) { give_up(1); break; }
+                    const uint32_t off_a0 = C::kOffA0 + rp.slot * kSlotP0, off_a1 = C::kOffA1 + rp.slot * kSlotP0;
+                    const uint32_t off_s0 = C::kOffSFA0 + rp.slot * kSlotSFA, off_s1 = C::kOffSFA1 + rp.slot * kSlotSFA;
+                    xform::Block16 blk[2];
+                    xform::decompose_block16<kResidual>(w[0], blk[0]);
+                    xform::decompose_block16<kResidual>(w[1], blk[1]);
+                    const uint32_t off = xform::fp4_offset<BK>(mrow, first_block * 16u);
+                    ptx::sts128(smem + off_a0 + off, blk[0].q0[0], blk[0].q0[1], blk[1].q0[0], blk[1].q0[1]);
+                    if constexpr (kResidual)
+                        ptx::sts128(smem + off_a1 + off, blk[0].q1[0], blk[0].q1[1], blk[1].q1[0], blk[1].q1[1]);
+                    const uint32_t sf_addr = (first_block >> 2) * 512u + xform::sf_word_offset(mrow) + (first_block & 2u);
+                    ptx::sts16(smem + off_s0 + sf_addr, blk[0].s0 | (blk[1].s0 << 8));
+                    if constexpr (kResidual) ptx::sts16(smem + off_s1 + sf_addr, blk[0].s1 | (blk[1].s1 << 8));
+                    ptx::fence_proxy_async_smem();                   // own stores -> async proxy (MMA reads, bulk-copy reads)
+                    __syncwarp();
+                    if (lane == 0) {
+                        ptx::mbar_arrive(p_full + rp.slot);
+                        ptx::mbar_arrive(share_full + rp.slot);      // the push warp takes it from here
                     }
+                    ra.advance<C::kDepthA>();
+                    rp.advance<C::kDepthP>();
                 }
-                if (lane == 0) {
-                    if (warp == kWarpXform0) ptx::mbar_arrive_expect_tx(p_full + rp.slot, kPeerBytes);
-                    else ptx::mbar_arrive(p_full + rp.slot);
-                }
-                ra.advance<C::kDepthA>();
-                rp.advance<C::kDepthP>();
             }
         }
     }
@@ -479,10 +495,10 @@ int launch_variant(const void* a, int64_t lda, const void* b, const void* sfb, i
 
 }  // namespace
 
-// N must be a multiple of 512 (two 256-column tiles per cluster).
+// cluster = 2 or 4 CTAs per activation tile; N must be a multiple of 256 * cluster.
 int launch_gemm_cluster(const void* a, int64_t lda, const void* b, const void* sfb, const float* gw, void* d,
                         int64_t ldd, const int32_t* m_indices, int M, int N, int K, int E, bool residual,
-                        int group_m, int num_sms, int32_t* status, cudaStream_t stream)
+                        int cluster, int group_m, int num_sms, int32_t* status, cudaStream_t stream)
 {
     Params p;
     p.gw = gw;
@@ -492,6 +508,9 @@ int launch_gemm_cluster(const void* a, int64_t lda, const void* b, const void* s
     p.m = M; p.n = N; p.k = K;
     p.group_m = group_m > 0 ? group_m : 8;
     p.status = status;
+    if (cluster == 4)
+        return residual ? launch_variant<4, true>(a, lda, b, sfb, M, N, K, E, p, num_sms, stream)
+                        : launch_variant<4, false>(a, lda, b, sfb, M, N, K, E, p, num_sms, stream);
     return residual ? launch_variant<2, true>(a, lda, b, sfb, M, N, K, E, p, num_sms, stream)
                     : launch_variant<2, false>(a, lda, b, sfb, M, N, K, E, p, num_sms, stream);
 }

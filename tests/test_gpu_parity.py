@@ -186,14 +186,17 @@ def test_gemm_kernel_variants_agree(dev, oracle, tune, residual):
 
 @pytest.mark.parametrize("shape", [(1, 128, 512, 128), (1, 128, 512, 1024), (4, 256, 1024, 2048), (3, 256, 2048, 640)])
 @pytest.mark.parametrize("residual", [True, False])
-def test_gemm_pair_cluster_matches_oracle(dev, oracle, shape, residual):
-    """tune_cluster=2: two CTAs transform half a tile each and exchange the halves; short and long
-    K (every ring wraps), one and many tiles per cluster."""
+@pytest.mark.parametrize("cluster", [2, 4])
+def test_gemm_cluster_matches_oracle(dev, oracle, shape, residual, cluster):
+    """tune_cluster=2 / 4: the CTAs of a cluster transform a share of the tile each and exchange the
+    shares; short and long K (every ring wraps), one and many tiles per cluster."""
+    if shape[2] % (256 * cluster):
+        pytest.skip("N is not a multiple of the cluster's column span")
     e, rows, n, k = shape
     a, w = make_case(e, rows, n, k, seed=500 + n + k)
     b, sfb, gw = nvfp4_gemm.quantize_weight_nvfp4(w.to(dev))
     mi = nvfp4_gemm.make_m_indices([rows] * e)
-    d = run_gemm(dev, a, b, sfb, gw, mi, n, enable_residual_pass=residual, tune_cluster=2)
+    d = run_gemm(dev, a, b, sfb, gw, mi, n, enable_residual_pass=residual, tune_cluster=cluster)
     want = oracle.grouped_gemm(a, b.cpu(), sfb.cpu(), gw.cpu(), mi, n, mode="dual" if residual else "single")
     assert rel_l2(d, want) < REL_L2_VS_ORACLE
 
