@@ -52,7 +52,7 @@ struct Cfg {
     static constexpr uint32_t kRun = 32 / CL;                   // consecutive MMA rows it owns in every group of 32
     static constexpr uint32_t kSlotA = kRows * BK * 2;          // 16 KB (pairs), 8 KB (quads)
     static constexpr uint32_t kActiveWarps = CL == 4 ? 4 : 8;   // transform warps in use: two 16-blocks per thread
-    static constexpr uint32_t kDepthA = CL == 4 ? 6 : 4, kDepthP = 3, kDepthB = 5;
+    static constexpr uint32_t kDepthA = CL == 4 ? 6 : 4, kDepthP = 4, kDepthB = 4;
     static constexpr uint32_t kOffA = 0;
     static constexpr uint32_t kOffA0 = kOffA + kDepthA * kSlotA;
     static constexpr uint32_t kOffA1 = kOffA0 + kDepthP * kSlotP0;

@@ -8,9 +8,12 @@
 // into the MMA's B operand.  Two accumulator stages in tensor memory let the
 // epilogue of one tile overlap the mainloop of the next.
 //
-//   W ring  (FP4 weights + their scales)   TMA warp        -> scale-transpose warp, MMA warp
+//   W ring  (FP4 weights + their scales)   TMA warp        -> scale warps, MMA warp
 //   A ring  (BF16 token rows)              TMA warp        -> transform warps
-//   P ring  (A0, A1, SFT0, SFT1)           transform warps -> MMA warp
+//   P ring  (A0, A1, SFT0, SFT1)           transform warps -> scale warps, MMA warp
+//
+// Scale factors go from shared to tensor memory through tcgen05.st issued by four scale warps, not
+// through tensor-memory copies issued by the MMA thread.
 //
 // Counterpart in the reference: include/nvfp4_gemm/impls/sm100_bf16_dual_nvfp4_gemm_swap_ab.cuh,
 // epilogue/sm100_store_cd_swap_ab.cuh, src/kernels/sm100_bf16_dual_nvfp4_gemm.hpp:489-632.
@@ -24,8 +27,10 @@ namespace nvfp4 {
 namespace {
 
 constexpr uint32_t BW = 128;                         // weight rows per tile (MMA M)
-constexpr uint32_t kWarpTma = 0, kWarpMma = 1, kWarpSf = 2, kWarpTmaA = 3, kWarpEpi0 = 4, kNumEpiWarps = 4, kWarpXform0 = 8;
-constexpr uint32_t kXformWarps = 8, kXformThreads = kXformWarps * 32, kThreads = (kWarpXform0 + kXformWarps) * 32;
+constexpr uint32_t kWarpTma = 0, kWarpMma = 1, kWarpTmaA = 3, kWarpEpi0 = 4, kNumEpiWarps = 4, kWarpXform0 = 8;
+constexpr uint32_t kXformWarps = 8, kXformThreads = kXformWarps * 32;
+constexpr uint32_t kWarpSf0 = kWarpXform0 + kXformWarps, kNumSfWarps = 4;      // one scale warp per TMEM lane quadrant
+constexpr uint32_t kThreads = (kWarpSf0 + kNumSfWarps) * 32;                 // 640
 constexpr uint32_t kSmemBudget = 232448 - 1024;      // opt-in maximum minus alignment slack
 
 // With the residual pass on, A0 and A1 of a token tile are stacked along the MMA N axis
@@ -57,14 +62,15 @@ struct Cfg {
     static constexpr uint32_t kOffSFW = kOffP + kDepthP * kSlotP;
     static constexpr uint32_t kOffSFT = kOffSFW + kDepthW * kSlotSFW;
     static constexpr uint32_t kOffBars = kOffSFT + kDepthP * kSlotSFT;
-    static constexpr uint32_t kNumBars = 3 * kDepthW + 2 * kDepthA + 2 * kDepthP + 4;
+    static constexpr uint32_t kNumBars = 2 * kDepthW + 2 * kDepthA + 2 * kDepthP + 4 + 2;
     static constexpr uint32_t kSmemAlloc = kOffBars + kNumBars * 8 + 16 + 1024;
     static_assert(kDepthW >= 3, "weight ring too shallow");
     static_assert(kSmemAlloc <= 232448, "shared memory budget");
     // tensor memory: two accumulator stages of kRowsP columns, then the two scale groups
     static constexpr uint32_t kAccStride = kRowsP < 32 ? 32 : kRowsP;
-    static constexpr uint32_t kColSFW = 2 * kAccStride, kColSFT = kColSFW + 4 * kAtoms;
-    static constexpr uint32_t kColsUsed = kColSFT + 4 * kNumSftCp;
+    // then two alternating buffers of scale columns: weight scales (4 per K atom), token scales (4 per K atom)
+    static constexpr uint32_t kColSF = 2 * kAccStride, kSfBufCols = 8 * kAtoms, kSfW = 0, kSfT = 4 * kAtoms;
+    static constexpr uint32_t kColsUsed = kColSF + 2 * kSfBufCols;
     static constexpr uint32_t kTmemCols = kColsUsed <= 64 ? 64 : (kColsUsed <= 128 ? 128 : (kColsUsed <= 256 ? 256 : 512));
     static constexpr uint64_t kSwizzle = BK == 256 ? ptx::kSwizzle128B : ptx::kSwizzle64B;
     static constexpr uint32_t kSBO = 8 * (BK / 2);   // eight rows of one swizzle span
@@ -100,13 +106,13 @@ gemm_swap_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constant
 
     uint64_t* bars = reinterpret_cast<uint64_t*>(smem_gen + C::kOffBars);
     uint64_t* w_full = bars;
-    uint64_t* w_ready = w_full + C::kDepthW;
-    uint64_t* w_empty = w_ready + C::kDepthW;
+    uint64_t* w_empty = w_full + C::kDepthW;
     uint64_t* a_full = w_empty + C::kDepthW;
     uint64_t* a_empty = a_full + C::kDepthA;
     uint64_t* p_full = a_empty + C::kDepthA;
     uint64_t* p_empty = p_full + C::kDepthP;
-    uint64_t* tmem_full = p_empty + C::kDepthP;      // [2]
+    uint64_t* sf_full = p_empty + C::kDepthP;        // [2]: scales of a K block are in tensor memory
+    uint64_t* tmem_full = sf_full + 2;               // [2]
     uint64_t* tmem_empty = tmem_full + 2;            // [2]
     uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(tmem_empty + 2);
     volatile uint32_t* abort_flag = tmem_slot + 1;
@@ -115,12 +121,15 @@ gemm_swap_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constant
     if (threadIdx.x == 0) {
         for (uint32_t i = 0; i < C::kDepthW; ++i) {
             ptx::mbar_init(w_full + i, 1);
-            ptx::mbar_init(w_ready + i, 1);
             ptx::mbar_init(w_empty + i, 1);
         }
         for (uint32_t i = 0; i < C::kDepthA; ++i) { ptx::mbar_init(a_full + i, 1); ptx::mbar_init(a_empty + i, kXformWarps); }
         for (uint32_t i = 0; i < C::kDepthP; ++i) { ptx::mbar_init(p_full + i, kXformWarps); ptx::mbar_init(p_empty + i, 1); }
-        for (uint32_t i = 0; i < 2; ++i) { ptx::mbar_init(tmem_full + i, 1); ptx::mbar_init(tmem_empty + i, kNumEpiWarps); }
+        for (uint32_t i = 0; i < 2; ++i) {
+            ptx::mbar_init(tmem_full + i, 1);
+            ptx::mbar_init(tmem_empty + i, kNumEpiWarps);
+            ptx::mbar_init(sf_full + i, kNumSfWarps);
+        }
         *abort_flag = 0;
         ptx::fence_mbar_init();
         ptx::prefetch_tensormap(&tm_a);
@@ -184,38 +193,30 @@ gemm_swap_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constant
         }
     } else if (warp == kWarpMma) {
         Ring rw, rp;
-        uint32_t it = 0;
+        uint32_t it = 0, cnt = 0;
         constexpr uint32_t idesc = ptx::make_idesc_nvf4(BW, C::kRowsP);
         for (uint32_t tile = blockIdx.x; tile < num_tiles && ok; tile += gridDim.x, ++it) {
             const uint32_t acc = it & 1, acc_phase = (it >> 1) & 1;
             if (!ptx::mbar_wait(tmem_empty + acc, acc_phase ^ 1, abort_flag, pa, 0)) { give_up(1); break; }
             ptx::tcgen05_fence_after_sync();
             const uint32_t tmem_acc = tmem_base + acc * C::kAccStride;
-            for (uint32_t kb = 0; kb < num_kb; ++kb) {
+            for (uint32_t kb = 0; kb < num_kb; ++kb, ++cnt) {
+                const uint32_t buf = cnt & 1u;
                 if (!ptx::mbar_wait(p_full + rp.slot, rp.phase, abort_flag, pa, 1) ||
-                    !ptx::mbar_wait(w_ready + rw.slot, rw.phase, abort_flag, pa, 2) ||
-                    !ptx::mbar_wait(w_full + rw.slot, rw.phase, abort_flag, pa, 3)) { give_up(1); break; }
+                    !ptx::mbar_wait(w_full + rw.slot, rw.phase, abort_flag, pa, 2) ||
+                    !ptx::mbar_wait(sf_full + buf, (cnt >> 1) & 1u, abort_flag, pa, 3)) { give_up(1); break; }
                 ptx::tcgen05_fence_after_sync();
                 if (lane == 0) {
-                    const uint32_t sfw = smem + C::kOffSFW + rw.slot * C::kSlotSFW;
-                    const uint32_t sft = smem + C::kOffSFT + rp.slot * C::kSlotSFT;
-#pragma unroll
-                    for (uint32_t a = 0; a < C::kAtoms; ++a)
-                        ptx::tcgen05_cp_32x128b_warpx4(tmem_base + C::kColSFW + 4 * a,
-                                                       ptx::make_smem_desc(sfw + a * 512, 128, ptx::kSwizzleNone));
-#pragma unroll
-                    for (uint32_t i = 0; i < C::kNumSftCp; ++i)
-                        ptx::tcgen05_cp_32x128b_warpx4(tmem_base + C::kColSFT + 4 * i,
-                                                       ptx::make_smem_desc(sft + i * 512, 128, ptx::kSwizzleNone));
+                    // the scales are already in tensor memory (scale warps, tcgen05.st): a tensor-memory copy per
+                    // scale atom cost this thread as much issue time as an MMA, and there were two per K atom
                     const uint32_t w = smem + C::kOffW + rw.slot * C::kSlotW;
                     const uint32_t pt = smem + C::kOffP + rp.slot * C::kSlotP;
+                    const uint32_t sf = tmem_base + C::kColSF + buf * C::kSfBufCols;
 #pragma unroll
                     for (uint32_t a = 0; a < C::kAtoms; ++a)
                         ptx::tcgen05_mma_nvf4(tmem_acc, ptx::make_smem_desc(w + a * 32, C::kSBO, C::kSwizzle),
                                               ptx::make_smem_desc(pt + a * 32, C::kSBO, C::kSwizzle), idesc,
-                                              tmem_base + C::kColSFW + 4 * a,
-                                              tmem_base + C::kColSFT + (a / C::kAtomsPerCp) * 4 + (a % C::kAtomsPerCp) * C::kSfCols,
-                                              (kb | a) != 0 ? 1u : 0u);
+                                              sf + C::kSfW + 4 * a, sf + C::kSfT + 4 * a, (kb | a) != 0 ? 1u : 0u);
                     ptx::tcgen05_commit(p_empty + rp.slot);
                     ptx::tcgen05_commit(w_empty + rw.slot);
                     if (kb == num_kb - 1) ptx::tcgen05_commit(tmem_full + acc);
@@ -225,27 +226,42 @@ gemm_swap_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constant
                 rw.advance<C::kDepthW>();
             }
         }
-    } else if (warp == kWarpSf) {
-        // weight scales: row r of each 128-row atom from word r to word (r % 32) * 4 + r / 32
-        Ring rw;
+    } else if (warp >= kWarpSf0) {
+        // scale warps: shared -> tensor memory with tcgen05.st, one warp per 32-lane quadrant (the MMA wants a
+        // copy in each).  Lane r gets the scale words of rows r, r + 32, r + 64, r + 96 of an atom in four
+        // consecutive columns: for the weight scales straight from the row-major words TMA landed (the
+        // transposition a tensor-memory copy would have needed comes for free), for the token scales from the
+        // atoms the transform wrote.  Two column buffers alternate; a buffer is rewritten once the MMAs of two K
+        // blocks earlier have retired (their commit on the W-empty barrier).
+        const uint32_t quad = warp & 3;
+        Ring rw, rp;
+        uint32_t cnt = 0;
         for (uint32_t tile = blockIdx.x; tile < num_tiles && ok; tile += gridDim.x) {
-            for (uint32_t kb = 0; kb < num_kb; ++kb) {
-                if (!ptx::mbar_wait(w_full + rw.slot, rw.phase, abort_flag, pa, 0)) { give_up(1); break; }
-                const uint32_t base = smem + C::kOffSFW + rw.slot * C::kSlotSFW;
-#pragma unroll
-                for (uint32_t i = 0; i < C::kAtoms; ++i) {
-                    const uint32_t atom = base + i * 512;
-                    const uint32_t v0 = ptx::lds32(atom + lane * 4);
-                    const uint32_t v1 = ptx::lds32(atom + (32 + lane) * 4);
-                    const uint32_t v2 = ptx::lds32(atom + (64 + lane) * 4);
-                    const uint32_t v3 = ptx::lds32(atom + (96 + lane) * 4);
-                    __syncwarp();
-                    ptx::sts128(atom + lane * 16, v0, v1, v2, v3);
+            for (uint32_t kb = 0; kb < num_kb; ++kb, ++cnt) {
+                const uint32_t buf = cnt & 1u;
+                const uint32_t sf = tmem_base + ((quad * 32) << 16) + C::kColSF + buf * C::kSfBufCols;
+                if (!ptx::mbar_wait(w_full + rw.slot, rw.phase, abort_flag, pa, 0) ||
+                    !ptx::mbar_wait(p_full + rp.slot, rp.phase, abort_flag, pa, 1)) { give_up(1); break; }
+                if (cnt >= 2 && !ptx::mbar_wait(w_empty + (cnt - 2) % C::kDepthW, ((cnt - 2) / C::kDepthW) & 1u, abort_flag, pa, 2)) {
+                    give_up(1);
+                    break;
                 }
-                ptx::fence_proxy_async_smem();
+                ptx::tcgen05_fence_after_sync();
+                const uint32_t sfw = smem + C::kOffSFW + rw.slot * C::kSlotSFW + lane * 4;
+                const uint32_t sft = smem + C::kOffSFT + rp.slot * C::kSlotSFT + lane * 16;
+#pragma unroll
+                for (uint32_t a = 0; a < C::kAtoms; ++a) {
+                    ptx::tmem_st_32x32b_x4(sf + C::kSfW + 4 * a, ptx::lds32(sfw + a * 512), ptx::lds32(sfw + a * 512 + 128),
+                                           ptx::lds32(sfw + a * 512 + 256), ptx::lds32(sfw + a * 512 + 384));
+                    const uint4 v = ptx::lds128(sft + a * 512);
+                    ptx::tmem_st_32x32b_x4(sf + C::kSfT + 4 * a, v.x, v.y, v.z, v.w);
+                }
+                ptx::tmem_st_wait();
+                ptx::tcgen05_fence_before_sync();
                 __syncwarp();
-                if (lane == 0) ptx::mbar_arrive(w_ready + rw.slot);
+                if (lane == 0) ptx::mbar_arrive(sf_full + buf);
                 rw.advance<C::kDepthW>();
+                rp.advance<C::kDepthP>();
             }
         }
     } else if (warp >= kWarpEpi0 && warp < kWarpEpi0 + kNumEpiWarps) {
@@ -301,7 +317,7 @@ gemm_swap_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constant
                 }
             }
         }
-    } else if (warp >= kWarpXform0) {
+    } else if (warp >= kWarpXform0 && warp < kWarpSf0) {
         const uint32_t t = threadIdx.x - kWarpXform0 * 32;
         Ring ra, rp;
         for (uint32_t tile = blockIdx.x; tile < num_tiles && ok; tile += gridDim.x) {
@@ -330,9 +346,9 @@ gemm_swap_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constant
     if (warp == 0) ptx::probe_flush(pa, 0);
     else if (warp == 3) ptx::probe_flush(pa, 1);
     else if (warp == 1) ptx::probe_flush(pa, 2, 3, 4, 5);
-    else if (warp == 2) ptx::probe_flush(pa, 7);
     else if (warp < 8) ptx::probe_flush(pa, 9);
-    else ptx::probe_flush(pa, 11, 12);
+    else if (warp < kWarpSf0) ptx::probe_flush(pa, 11, 12);
+    else ptx::probe_flush(pa, 7, 8, 10);
     ptx::tcgen05_fence_before_sync();
     __syncthreads();
     if (warp == kWarpMma) {
