@@ -189,8 +189,11 @@ int nvfp4_grouped_gemm_contiguous(const void* a, int64_t lda_elems, const void* 
         int tile = tune_block_n > 0 ? tune_block_n : (m_alignment >= 64 ? 64 : m_alignment);
         NVFP4_REQUIRE((tile == 16 || tile == 32 || tile == 64) && m_alignment % tile == 0,
                       "token tile %d must be 16, 32 or 64 and divide m_alignment %d", tile, m_alignment);
+        const int tune_block_k = tune ? tune[5] : 0;   // 0 = the largest of 512 / 256 / 128 that divides K and fits
+        NVFP4_REQUIRE(tune_block_k == 0 || tune_block_k == 128 || tune_block_k == 256 || tune_block_k == 512,
+                      "tune_block_k must be 0, 128, 256 or 512");
         return launch_gemm_swap(a, lda_elems, b, sfb, gw, d, ldd_elems, m_indices, M, N, K, E, enable_residual_pass != 0,
-                                tile, dev->num_sms, device_status, s);
+                                tile, tune_block_k, dev->num_sms, device_status, s);
     }
     NVFP4_REQUIRE(tune_xform_warps == 0 || tune_xform_warps == 8 || tune_xform_warps == 16,
                   "tune_transform_warps must be 0, 8 or 16");

@@ -42,6 +42,8 @@ template <uint32_t T, uint32_t BK, bool kResidual>
 struct Cfg {
     static constexpr uint32_t kAtoms = BK / 64;
     static constexpr uint32_t kRowsP = kResidual ? 2 * T : T;             // rows of the stacked operand tile
+    static constexpr uint32_t kRowBytes = BK >= 256 ? 128 : BK / 2;       // one swizzle span; BK = 512 is two sub-tiles
+    static constexpr uint32_t kSubW = BW * kRowBytes, kSubP = kRowsP * kRowBytes;   // bytes of one sub-tile
     static constexpr uint32_t kSlotW = BW * BK / 2, kSlotSFW = kAtoms * 512;
     static constexpr uint32_t kSlotA = T * BK * 2;
     static constexpr uint32_t kSlotP = (kRowsP * BK / 2 + 1023u) & ~1023u;
@@ -50,9 +52,10 @@ struct Cfg {
     // four, raised a CUDA error on B200: the scale address of the MMA has to stay 4-column aligned.)
     static constexpr uint32_t kSfCols = 4, kAtomsPerCp = 4 / kSfCols;
     static constexpr uint32_t kNumSftCp = (kAtoms + kAtomsPerCp - 1) / kAtomsPerCp, kSlotSFT = kNumSftCp * 512;
-    static constexpr uint32_t kA1Bytes = T * (BK / 2);                     // A1 rows start T rows below A0
+    static constexpr uint32_t kA1Bytes = T * kRowBytes;                    // A1 rows start T rows below A0 (in every sub-tile)
     static constexpr uint32_t kSF1Bytes = T == 16 ? 256 : (T / 32) * 4;    // scale word of row T + r relative to row r
-    static constexpr uint32_t kDepthA = T >= 64 ? 3 : (T == 32 ? 5 : 6), kDepthP = 3;   // A must cover the TMA latency
+    static constexpr uint32_t kDepthA = BK == 512 ? (T == 16 ? 3 : 2) : (T >= 64 ? 3 : (T == 32 ? 5 : 6));   // covers the TMA latency
+    static constexpr uint32_t kDepthP = BK == 512 ? 2 : 3;
     static constexpr uint32_t kFixed = kDepthA * kSlotA + kDepthP * (kSlotP + kSlotSFT) + 512;
     static constexpr uint32_t kDepthWRaw = (kSmemBudget - kFixed) / (kSlotW + kSlotSFW);
     static constexpr uint32_t kDepthW = kDepthWRaw > 12 ? 12 : kDepthWRaw;
@@ -62,7 +65,7 @@ struct Cfg {
     static constexpr uint32_t kOffSFW = kOffP + kDepthP * kSlotP;
     static constexpr uint32_t kOffSFT = kOffSFW + kDepthW * kSlotSFW;
     static constexpr uint32_t kOffBars = kOffSFT + kDepthP * kSlotSFT;
-    static constexpr uint32_t kNumBars = 2 * kDepthW + 2 * kDepthA + 2 * kDepthP + 4 + 2;
+    static constexpr uint32_t kNumBars = 2 * kDepthW + 2 * kDepthA + kDepthP + 4 + 2;
     static constexpr uint32_t kSmemAlloc = kOffBars + kNumBars * 8 + 16 + 1024;
     static_assert(kDepthW >= 3, "weight ring too shallow");
     static_assert(kSmemAlloc <= 232448, "shared memory budget");
@@ -72,8 +75,8 @@ struct Cfg {
     static constexpr uint32_t kColSF = 2 * kAccStride, kSfBufCols = 8 * kAtoms, kSfW = 0, kSfT = 4 * kAtoms;
     static constexpr uint32_t kColsUsed = kColSF + 2 * kSfBufCols;
     static constexpr uint32_t kTmemCols = kColsUsed <= 64 ? 64 : (kColsUsed <= 128 ? 128 : (kColsUsed <= 256 ? 256 : 512));
-    static constexpr uint64_t kSwizzle = BK == 256 ? ptx::kSwizzle128B : ptx::kSwizzle64B;
-    static constexpr uint32_t kSBO = 8 * (BK / 2);   // eight rows of one swizzle span
+    static constexpr uint64_t kSwizzle = BK >= 256 ? ptx::kSwizzle128B : ptx::kSwizzle64B;
+    static constexpr uint32_t kSBO = 8 * kRowBytes;  // eight rows of one swizzle span
 };
 
 struct Params {
@@ -110,8 +113,7 @@ gemm_swap_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constant
     uint64_t* a_full = w_empty + C::kDepthW;
     uint64_t* a_empty = a_full + C::kDepthA;
     uint64_t* p_full = a_empty + C::kDepthA;
-    uint64_t* p_empty = p_full + C::kDepthP;
-    uint64_t* sf_full = p_empty + C::kDepthP;        // [2]: scales of a K block are in tensor memory
+    uint64_t* sf_full = p_full + C::kDepthP;         // [2]: scales of a K block are in tensor memory
     uint64_t* tmem_full = sf_full + 2;               // [2]
     uint64_t* tmem_empty = tmem_full + 2;            // [2]
     uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(tmem_empty + 2);
@@ -124,7 +126,7 @@ gemm_swap_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constant
             ptx::mbar_init(w_empty + i, 1);
         }
         for (uint32_t i = 0; i < C::kDepthA; ++i) { ptx::mbar_init(a_full + i, 1); ptx::mbar_init(a_empty + i, kXformWarps); }
-        for (uint32_t i = 0; i < C::kDepthP; ++i) { ptx::mbar_init(p_full + i, kXformWarps); ptx::mbar_init(p_empty + i, 1); }
+        for (uint32_t i = 0; i < C::kDepthP; ++i) ptx::mbar_init(p_full + i, kXformWarps);
         for (uint32_t i = 0; i < 2; ++i) {
             ptx::mbar_init(tmem_full + i, 1);
             ptx::mbar_init(tmem_empty + i, kNumEpiWarps);
@@ -166,8 +168,10 @@ gemm_swap_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constant
                 for (uint32_t kb = 0; kb < num_kb; ++kb) {
                     if (!ptx::mbar_wait(w_empty + rw.slot, rw.phase ^ 1, abort_flag, pa, 0)) { give_up(1); break; }
                     ptx::mbar_arrive_expect_tx(w_full + rw.slot, C::kSlotW + C::kSlotSFW);
-                    ptx::tma_load_2d_hint(smem_gen + C::kOffW + rw.slot * C::kSlotW, &tm_w, w_full + rw.slot, kb * (BK / 2),
-                                          e * p.n + n_blk * BW, stream_once);
+#pragma unroll
+                    for (uint32_t sub = 0; sub < (BK / 2) / C::kRowBytes; ++sub)
+                        ptx::tma_load_2d_hint(smem_gen + C::kOffW + rw.slot * C::kSlotW + sub * C::kSubW, &tm_w, w_full + rw.slot,
+                                              kb * (BK / 2) + sub * C::kRowBytes, e * p.n + n_blk * BW, stream_once);
                     ptx::tma_load_2d_hint(smem_gen + C::kOffSFW + rw.slot * C::kSlotSFW, &tm_sfw, w_full + rw.slot,
                                           n_blk * BW, e * (p.k / 64) + kb * C::kAtoms, stream_once);
                     rw.advance<C::kDepthW>();
@@ -214,10 +218,12 @@ gemm_swap_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constant
                     const uint32_t sf = tmem_base + C::kColSF + buf * C::kSfBufCols;
 #pragma unroll
                     for (uint32_t a = 0; a < C::kAtoms; ++a)
-                        ptx::tcgen05_mma_nvf4(tmem_acc, ptx::make_smem_desc(w + a * 32, C::kSBO, C::kSwizzle),
-                                              ptx::make_smem_desc(pt + a * 32, C::kSBO, C::kSwizzle), idesc,
+                        ptx::tcgen05_mma_nvf4(tmem_acc,
+                                              ptx::make_smem_desc(w + (a / 4) * C::kSubW + (a % 4) * 32, C::kSBO, C::kSwizzle),
+                                              ptx::make_smem_desc(pt + (a / 4) * C::kSubP + (a % 4) * 32, C::kSBO, C::kSwizzle), idesc,
                                               sf + C::kSfW + 4 * a, sf + C::kSfT + 4 * a, (kb | a) != 0 ? 1u : 0u);
-                    ptx::tcgen05_commit(p_empty + rp.slot);
+                    // one commit per K block: the weight producer, the scale warps and the transform warps all
+                    // read "the MMAs of K block i have retired" from this barrier
                     ptx::tcgen05_commit(w_empty + rw.slot);
                     if (kb == num_kb - 1) ptx::tcgen05_commit(tmem_full + acc);
                 }
@@ -320,17 +326,21 @@ gemm_swap_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constant
     } else if (warp >= kWarpXform0 && warp < kWarpSf0) {
         const uint32_t t = threadIdx.x - kWarpXform0 * 32;
         Ring ra, rp;
+        uint32_t cnt = 0;
         for (uint32_t tile = blockIdx.x; tile < num_tiles && ok; tile += gridDim.x) {
-            for (uint32_t kb = 0; kb < num_kb; ++kb) {
+            for (uint32_t kb = 0; kb < num_kb; ++kb, ++cnt) {
                 if (!ptx::mbar_wait(a_full + ra.slot, ra.phase, abort_flag, pa, 0)) { give_up(1); break; }
                 bool p_ok = true;
-                xform::transform_tile<T, BK, kXformThreads, kResidual, C::kSfCols>(
+                xform::transform_tile<T, BK, kXformThreads, kResidual, C::kSfCols, C::kRowsP>(
                     smem + C::kOffA + ra.slot * C::kSlotA, smem + C::kOffP + rp.slot * C::kSlotP,
                     smem + C::kOffP + rp.slot * C::kSlotP + C::kA1Bytes, smem + C::kOffSFT + rp.slot * C::kSlotSFT,
                     smem + C::kOffSFT + rp.slot * C::kSlotSFT + C::kSF1Bytes, t, [&] {
                         __syncwarp();
                         if (lane == 0) ptx::mbar_arrive(a_empty + ra.slot);
-                        p_ok = ptx::mbar_wait(p_empty + rp.slot, rp.phase ^ 1, abort_flag, pa, 1);
+                        // the slot is free once the MMAs of kDepthP K blocks ago have retired
+                        p_ok = cnt < C::kDepthP ||
+                               ptx::mbar_wait(w_empty + (cnt - C::kDepthP) % C::kDepthW, ((cnt - C::kDepthP) / C::kDepthW) & 1u,
+                                              abort_flag, pa, 1);
                     });
                 if (!p_ok) { give_up(1); break; }
                 ptx::fence_proxy_async_smem();
@@ -367,7 +377,7 @@ int launch_variant(const void* a, int64_t lda, const void* b, const void* sfb, i
                                         CU_TENSOR_MAP_SWIZZLE_128B);
     if (rc) return rc;
     rc = host::encode_tensor_map_2d(&tm_w, CU_TENSOR_MAP_DATA_TYPE_UINT8, 1, b, K / 2, static_cast<uint64_t>(E) * N,
-                                    K / 2, BK / 2, BW, BK == 256 ? CU_TENSOR_MAP_SWIZZLE_128B : CU_TENSOR_MAP_SWIZZLE_64B);
+                                    K / 2, C::kRowBytes, BW, BK >= 256 ? CU_TENSOR_MAP_SWIZZLE_128B : CU_TENSOR_MAP_SWIZZLE_64B);
     if (rc) return rc;
     rc = host::encode_tensor_map_2d(&tm_sfw, CU_TENSOR_MAP_DATA_TYPE_INT32, 4, sfb, N,
                                     static_cast<uint64_t>(E) * (K / 64), static_cast<uint64_t>(N) * 4, BW, C::kAtoms,
@@ -390,9 +400,15 @@ int launch_variant(const void* a, int64_t lda, const void* b, const void* sfb, i
 
 template <uint32_t T>
 int launch_for_tile(const void* a, int64_t lda, const void* b, const void* sfb, int M, int N, int K, int E,
-                    const Params& p, bool residual, int num_sms, cudaStream_t stream)
+                    const Params& p, bool residual, int block_k, int num_sms, cudaStream_t stream)
 {
-    if (K % 256 == 0)
+    // K blocks of 512 halve the per-block barrier traffic and commits; a 64-token tile has no room for them
+    if constexpr (T <= 32) {
+        if (K % 512 == 0 && (block_k == 0 || block_k == 512))
+            return residual ? launch_variant<T, 512, true>(a, lda, b, sfb, M, N, K, E, p, num_sms, stream)
+                            : launch_variant<T, 512, false>(a, lda, b, sfb, M, N, K, E, p, num_sms, stream);
+    }
+    if (K % 256 == 0 && block_k != 128)
         return residual ? launch_variant<T, 256, true>(a, lda, b, sfb, M, N, K, E, p, num_sms, stream)
                         : launch_variant<T, 256, false>(a, lda, b, sfb, M, N, K, E, p, num_sms, stream);
     return residual ? launch_variant<T, 128, true>(a, lda, b, sfb, M, N, K, E, p, num_sms, stream)
@@ -405,7 +421,7 @@ int launch_for_tile(const void* a, int64_t lda, const void* b, const void* sfb, 
 // multiple of it, which the caller guarantees through m_alignment % token_tile == 0.
 int launch_gemm_swap(const void* a, int64_t lda, const void* b, const void* sfb, const float* gw, void* d,
                      int64_t ldd, const int32_t* m_indices, int M, int N, int K, int E, bool residual,
-                     int token_tile, int num_sms, int32_t* status, cudaStream_t stream)
+                     int token_tile, int block_k, int num_sms, int32_t* status, cudaStream_t stream)
 {
     Params p;
     p.gw = gw;
@@ -415,9 +431,9 @@ int launch_gemm_swap(const void* a, int64_t lda, const void* b, const void* sfb,
     p.m = M; p.n = N; p.k = K;
     p.status = status;
     switch (token_tile) {
-        case 16: return launch_for_tile<16>(a, lda, b, sfb, M, N, K, E, p, residual, num_sms, stream);
-        case 32: return launch_for_tile<32>(a, lda, b, sfb, M, N, K, E, p, residual, num_sms, stream);
-        case 64: return launch_for_tile<64>(a, lda, b, sfb, M, N, K, E, p, residual, num_sms, stream);
+        case 16: return launch_for_tile<16>(a, lda, b, sfb, M, N, K, E, p, residual, block_k, num_sms, stream);
+        case 32: return launch_for_tile<32>(a, lda, b, sfb, M, N, K, E, p, residual, block_k, num_sms, stream);
+        case 64: return launch_for_tile<64>(a, lda, b, sfb, M, N, K, E, p, residual, block_k, num_sms, stream);
         default: return host::fail(NVFP4_E_INVALID_ARGUMENT, "token tile %d is not 16, 32 or 64", token_tile);
     }
 }

@@ -36,12 +36,17 @@ NVFP4_DEVICE uint32_t a_bf16_offset(uint32_t row, uint32_t k)   // byte offset o
 // rows (256 K elements) under the 128-byte swizzle, chunk index ^= row % 8.  The same
 // function serves the TMA-written weights and the A0 / A1 tiles the transform writes,
 // which is what the MMA descriptors assume.
-template <uint32_t kBK>
+template <uint32_t kBK, uint32_t kSubRows = 0>
 NVFP4_DEVICE uint32_t fp4_offset(uint32_t row, uint32_t k)   // byte offset of element (row, k), k % 32 == 0
 {
-    static_assert(kBK == 128 || kBK == 256, "one swizzle span per row");
+    static_assert(kBK == 128 || kBK == 256 || kBK == 512, "one or two swizzle spans per row");
     if constexpr (kBK == 128) return row * 64u + (((k >> 5) ^ ((row >> 1) & 3u)) << 4);
-    else return row * 128u + (((k >> 5) ^ (row & 7u)) << 4);
+    else if constexpr (kBK == 256) return row * 128u + (((k >> 5) ^ (row & 7u)) << 4);
+    else {
+        // 512 K elements = two 128-byte-swizzled sub-tiles of kSubRows rows each, side by side along K
+        static_assert(kSubRows > 0, "sub-tile height");
+        return (k >> 8) * (kSubRows * 128u) + row * 128u + ((((k & 255u) >> 5) ^ (row & 7u)) << 4);
+    }
 }
 NVFP4_DEVICE uint32_t fp4_sw64_offset(uint32_t row, uint32_t k) { return fp4_offset<128>(row, k); }
 // Scale-factor atom (128 rows x four 16-blocks = 64 K elements) in the order the
@@ -240,7 +245,7 @@ NVFP4_DEVICE void load_tile_global(TileShare<kRows, kBK, kThreads>& s, const voi
     }
 }
 
-template <uint32_t kRows, uint32_t kBK, uint32_t kThreads, bool kResidual, uint32_t kSfCols = 4>
+template <uint32_t kRows, uint32_t kBK, uint32_t kThreads, bool kResidual, uint32_t kSfCols = 4, uint32_t kSubRows = 0>
 NVFP4_DEVICE void emit_tile(const TileShare<kRows, kBK, kThreads>& s, uint32_t a0_smem, uint32_t a1_smem,
                             uint32_t sfa0_smem, uint32_t sfa1_smem, uint32_t t)
 {
@@ -252,7 +257,7 @@ NVFP4_DEVICE void emit_tile(const TileShare<kRows, kBK, kThreads>& s, uint32_t a
     if constexpr (kBlocksPerThread == 1) {
         Block16 blk;
         decompose_block16<kResidual>(s.w[0], blk);
-        const uint32_t off = fp4_offset<kBK>(row, (first_block * 16u) & ~31u) + ((first_block & 1u) << 3);
+        const uint32_t off = fp4_offset<kBK, kSubRows>(row, (first_block * 16u) & ~31u) + ((first_block & 1u) << 3);
         ptx::sts64(a0_smem + off, blk.q0[0], blk.q0[1]);
         if constexpr (kResidual) ptx::sts64(a1_smem + off, blk.q1[0], blk.q1[1]);
         const uint32_t addr = sf_atom_offset<kSfCols>(first_block >> 2, row) + (first_block & 3u);
@@ -266,7 +271,7 @@ NVFP4_DEVICE void emit_tile(const TileShare<kRows, kBK, kThreads>& s, uint32_t a
             decompose_block16<kResidual>(s.w[pair * 2], blk[0]);
             decompose_block16<kResidual>(s.w[pair * 2 + 1], blk[1]);
             // two blocks = 32 elements = one 16-byte chunk of each packed row
-            const uint32_t off = fp4_offset<kBK>(row, (first_block + pair * 2) * 16u);
+            const uint32_t off = fp4_offset<kBK, kSubRows>(row, (first_block + pair * 2) * 16u);
             ptx::sts128(a0_smem + off, blk[0].q0[0], blk[0].q0[1], blk[1].q0[0], blk[1].q0[1]);
             if constexpr (kResidual)
                 ptx::sts128(a1_smem + off, blk[0].q1[0], blk[0].q1[1], blk[1].q1[0], blk[1].q1[1]);
@@ -290,14 +295,15 @@ NVFP4_DEVICE void emit_tile(const TileShare<kRows, kBK, kThreads>& s, uint32_t a
 
 // Shared-memory tile in, products out; `on_loaded()` runs between the reads and the
 // arithmetic (the caller releases the BF16 slot there).
-template <uint32_t kRows, uint32_t kBK, uint32_t kThreads, bool kResidual, uint32_t kSfCols = 4, typename OnLoaded>
+template <uint32_t kRows, uint32_t kBK, uint32_t kThreads, bool kResidual, uint32_t kSfCols = 4, uint32_t kSubRows = 0,
+          typename OnLoaded>
 NVFP4_DEVICE void transform_tile(uint32_t a_smem, uint32_t a0_smem, uint32_t a1_smem, uint32_t sfa0_smem,
                                  uint32_t sfa1_smem, uint32_t t, OnLoaded&& on_loaded)
 {
     TileShare<kRows, kBK, kThreads> s;
     load_tile_smem(s, a_smem, t);
     on_loaded();
-    emit_tile<kRows, kBK, kThreads, kResidual, kSfCols>(s, a0_smem, a1_smem, sfa0_smem, sfa1_smem, t);
+    emit_tile<kRows, kBK, kThreads, kResidual, kSfCols, kSubRows>(s, a0_smem, a1_smem, sfa0_smem, sfa1_smem, t);
 }
 
 }  // namespace nvfp4::xform

@@ -358,6 +358,24 @@ def test_gemm_swap_ab_decode_routing(dev, oracle):
     assert float(d[zero_rows].float().abs().max()) == 0.0
 
 
+@pytest.mark.parametrize("tile", [16, 32])
+def test_gemm_swap_ab_k_block_variants_agree(dev, oracle, tile):
+    """The decode kernel has 128-, 256- and 512-wide K blocks; on a K all three divide they must agree with
+    the oracle and with each other (same codes and products, same summation order per accumulator)."""
+    sizes, n, k = [tile, 3 * tile, tile], 384, 1536
+    g = torch.Generator().manual_seed(77 + tile)
+    a = torch.randn(sum(sizes), k, generator=g).to(torch.bfloat16)
+    w = (torch.randn(len(sizes), n, k, generator=g) * 0.02).to(torch.bfloat16)
+    b, sfb, gw = nvfp4_gemm.quantize_weight_nvfp4(w.to(dev))
+    mi = nvfp4_gemm.make_m_indices(sizes, alignment=tile)
+    want = oracle.grouped_gemm(a, b.cpu(), sfb.cpu(), gw.cpu(), mi, n)
+    outs = [run_gemm(dev, a, b, sfb, gw, mi, n, tune_swap_ab=1, m_alignment=tile, tune_block_k=bk)
+            for bk in (128, 256, 512)]
+    for d in outs:
+        assert rel_l2(d, want) < REL_L2_VS_ORACLE
+    assert torch.equal(outs[0], outs[1]) and torch.equal(outs[1], outs[2])
+
+
 def test_both_orientations_agree(dev):
     e, rows, n, k = 2, 128, 256, 512
     a, w = make_case(e, rows, n, k, seed=5)
