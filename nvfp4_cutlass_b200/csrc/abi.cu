@@ -199,6 +199,19 @@ int nvfp4_grouped_gemm_contiguous(const void* a, int64_t lda_elems, const void* 
                   "tune_transform_warps must be 0, 8 or 16");
     // tune_cluster: 2 / 4 = that many CTAs share one transformed activation tile (needs N % (256 * cluster) == 0),
     // 1 = single-CTA kernel, 0 = the library's choice
+    // tune_split_transform: 1 = quantise the activations once, in a kernel of their own, ahead of a GEMM without
+    // transform warps (N % 256 == 0); 2 = decompose inside the GEMM main loop; 0 = the library's choice
+    const int tune_split = tune ? tune[13] : 0;
+    NVFP4_REQUIRE(tune_split >= 0 && tune_split <= 2, "tune_split_transform must be 0, 1 or 2");
+    NVFP4_REQUIRE(tune_split != 1 || N % 256 == 0, "tune_split_transform=1 needs N %% 256 == 0 (N=%d)", N);
+    // The library's choice: the separate pass wins as soon as an activation tile is visited by several column
+    // tiles (N >= 1024); explicit fused-kernel knobs (cluster, transform warps, direct A) keep the fused kernels.
+    const bool fused_knobs = tune && (tune[8] != 0 || tune[1] != 0 || tune[9] != 0);
+    if (tune_split == 1 || (tune_split == 0 && !fused_knobs && N % 256 == 0 && N >= 1024)) {
+        const int tune_block_k = tune ? tune[5] : 0;
+        return launch_gemm_split(a, lda_elems, b, sfb, gw, d, ldd_elems, m_indices, M, N, K, E, enable_residual_pass != 0,
+                                 tune_block_k, tune_sched_group, !(tune && tune[11]), dev->num_sms, device_status, s);
+    }
     int cluster = tune ? tune[8] : 0;
     NVFP4_REQUIRE(cluster == 0 || cluster == 1 || cluster == 2 || cluster == 4, "tune_cluster must be 0, 1, 2 or 4");
     NVFP4_REQUIRE(cluster < 2 || N % (256 * cluster) == 0, "tune_cluster %d needs N %% %d == 0 (N=%d)", cluster, 256 * cluster, N);
@@ -208,7 +221,7 @@ int nvfp4_grouped_gemm_contiguous(const void* a, int64_t lda_elems, const void* 
     }
     if (cluster >= 2 && dev->num_sms >= cluster)
         return launch_gemm_cluster(a, lda_elems, b, sfb, gw, d, ldd_elems, m_indices, M, N, K, E,
-                                   enable_residual_pass != 0, cluster, tune_sched_group, dev->num_sms, device_status, s);
+                                   enable_residual_pass != 0, cluster, tune_xform_warps, tune_sched_group, dev->num_sms, device_status, s);
     // tune_direct_a = 1: the transform reads activations straight from global memory instead of a TMA-fed
     // shared-memory ring (measured slower on B200: 1.89 ms against 1.06 ms on the Mixtral-like shape)
     const bool direct_a = tune && tune[9] == 1 && tune_xform_warps != 16;

@@ -23,8 +23,12 @@
 // Barriers: P-full of a CTA counts its own eight transform warps plus the bytes of the
 // peer's copies; P-empty counts one tcgen05.commit per CTA, delivered to both CTAs by the
 // commit's cluster mask, so a slot is rewritten (locally or by the peer's copies) only after
-// both tensor cores have read it.  No load in this file is a multicast: the cross-CTA
-// traffic is the bulk copies, mbarrier signalling and the commit mask.
+// both tensor cores have read it.  The P ring, the weight ring and the scale columns in tensor
+// memory have the same depth and advance together, so that one commit per K block frees all
+// three, and the MMA thread waits on a single barrier per K block (scales-in-tensor-memory, which
+// the scale warps signal only after they have seen P-full and B-full themselves).  No load in
+// this file is a multicast: the cross-CTA traffic is the bulk copies, mbarrier signalling and
+// the commit mask.
 #include <cuda_bf16.h>
 
 #include "host_common.hpp"
@@ -39,20 +43,23 @@ constexpr uint32_t kSlotP0 = BM * BK / 2;                       // 8192: one pac
 constexpr uint32_t kSlotSFA = kKAtoms * 512;                    // 1024
 constexpr uint32_t kSlotB = BN * BK / 2, kSlotSFB = kKAtoms * 2 * 512;
 constexpr uint32_t kWarpTma = 0, kWarpMma = 1, kWarpPush = 2, kWarpTmaA = 3, kWarpEpi0 = 4, kNumEpiWarps = 8, kWarpXform0 = 12;
-constexpr uint32_t kXformWarps = 8, kXformThreads = kXformWarps * 32;
-constexpr uint32_t kThreads = (kWarpXform0 + kXformWarps) * 32;   // 640
-// tensor memory: 256 accumulator columns, then two buffers of 32 scale columns (SFA0 8, SFA1 8, SFB 16) that
-// alternate from K block to K block
+constexpr uint32_t kThreadsFor(uint32_t xform_warps) { return (kWarpXform0 + xform_warps) * 32; }   // 640 or 896
+// tensor memory: 256 accumulator columns, then one buffer of 32 scale columns (SFA0 8, SFA1 8, SFB 16) per
+// slot of the operand rings
 constexpr uint32_t kTmemCols = 512, kColAcc = 0, kColSF = 256, kSfBufCols = 32, kSfA0 = 0, kSfA1 = 8, kSfB = 16;
 
-template <uint32_t CL>
+template <uint32_t CL, uint32_t kXW>
 struct Cfg {
     static_assert(CL == 2 || CL == 4, "cluster of two or four CTAs");
+    static_assert(kXW == 8 || kXW == 16, "transform warps");
     static constexpr uint32_t kRows = BM / CL;                  // rows this CTA loads and transforms
     static constexpr uint32_t kRun = 32 / CL;                   // consecutive MMA rows it owns in every group of 32
     static constexpr uint32_t kSlotA = kRows * BK * 2;          // 16 KB (pairs), 8 KB (quads)
-    static constexpr uint32_t kActiveWarps = CL == 4 ? 4 : 8;   // transform warps in use: two 16-blocks per thread
-    static constexpr uint32_t kDepthA = CL == 4 ? 6 : 4, kDepthP = 4, kDepthB = 4;
+    static constexpr uint32_t kActiveWarps = kXW;               // every transform warp takes part
+    static constexpr uint32_t kBpt = kRows * (BK / 16) / (kXW * 32);   // 16-blocks per transform thread: 1 or 2
+    static_assert(kBpt == 1 || kBpt == 2, "one or two 16-blocks per thread");
+    static constexpr uint32_t kDepthA = CL == 4 ? 6 : 4, kDepthP = 4, kDepthB = kDepthP;   // P, B and scale columns move together
+    static_assert(kColSF + kDepthP * kSfBufCols <= kTmemCols, "scale columns");
     static constexpr uint32_t kOffA = 0;
     static constexpr uint32_t kOffA0 = kOffA + kDepthA * kSlotA;
     static constexpr uint32_t kOffA1 = kOffA0 + kDepthP * kSlotP0;
@@ -61,10 +68,9 @@ struct Cfg {
     static constexpr uint32_t kOffSFA1 = kOffSFA0 + kDepthP * kSlotSFA;
     static constexpr uint32_t kOffSFB = kOffSFA1 + kDepthP * kSlotSFA;
     static constexpr uint32_t kOffBars = kOffSFB + kDepthB * kSlotSFB;
-    static constexpr uint32_t kNumBars = 2 * kDepthA + 3 * kDepthP + 2 * kDepthB + 2 + 2;
+    static constexpr uint32_t kNumBars = 2 * kDepthA + 4 * kDepthP + kDepthB + 2;
     static constexpr uint32_t kSmemAlloc = kOffBars + kNumBars * 8 + 16 + 1024;
     static_assert(kSmemAlloc <= 232448, "shared memory budget");
-    static_assert(kRows * (BK / 16) == kActiveWarps * 32 * 2, "two 16-blocks (one 16-byte chunk) per thread");
     // what one CTA pushes to one peer per K block and pass: four runs of kRun packed rows, one run per scale atom
     static constexpr uint32_t kRunBytes = kRun * 64, kSfRunBytes = kRun * 16;
     static constexpr uint32_t kBytesPerPass = 4 * kRunBytes + kKAtoms * kSfRunBytes;
@@ -100,12 +106,12 @@ __device__ __forceinline__ void super_tile_coords(uint32_t st, uint32_t num_m, u
     ns = r / rows;
 }
 
-template <uint32_t CL, bool kResidual>
-__global__ void __launch_bounds__(kThreads, 1)
+template <uint32_t CL, bool kResidual, uint32_t kXW>
+__global__ void __launch_bounds__(kThreadsFor(kXW), 1)
 gemm_cluster_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constant__ CUtensorMap tm_b,
                     const __grid_constant__ CUtensorMap tm_sfb, const Params p)
 {
-    using C = Cfg<CL>;
+    using C = Cfg<CL, kXW>;
     extern __shared__ uint8_t smem_raw[];
     const uint32_t smem = (ptx::smem_u32(smem_raw) + 1023u) & ~1023u;
     uint8_t* smem_gen = smem_raw + (smem - ptx::smem_u32(smem_raw));
@@ -116,10 +122,9 @@ gemm_cluster_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_const
     uint64_t* p_full = a_empty + C::kDepthA;
     uint64_t* p_empty = p_full + C::kDepthP;
     uint64_t* b_full = p_empty + C::kDepthP;
-    uint64_t* b_empty = b_full + C::kDepthB;
-    uint64_t* share_full = b_empty + C::kDepthB;     // [kDepthP]: this CTA's share of a slot is written
-    uint64_t* sf_full = share_full + C::kDepthP;     // [2]: scales of a K block are in tensor memory
-    uint64_t* tmem_full = sf_full + 2;
+    uint64_t* share_full = b_full + C::kDepthB;      // [kDepthP]: this CTA's share of a slot is written
+    uint64_t* sf_full = share_full + C::kDepthP;     // [kDepthP]: scales of a K block are in tensor memory
+    uint64_t* tmem_full = sf_full + C::kDepthP;
     uint64_t* tmem_empty = tmem_full + 1;
     uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(tmem_empty + 1);
     volatile uint32_t* abort_flag = tmem_slot + 1;
@@ -133,13 +138,9 @@ gemm_cluster_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_const
             ptx::mbar_init(p_full + i, C::kActiveWarps + 1);    // own transform warps + the push warp; peers' shares arrive as bytes
             ptx::mbar_init(share_full + i, C::kActiveWarps);
             ptx::mbar_init(p_empty + i, CL);                    // one commit per CTA of the cluster
+            ptx::mbar_init(sf_full + i, kNumEpiWarps);
         }
-        for (uint32_t i = 0; i < C::kDepthB; ++i) {
-            ptx::mbar_init(b_full + i, 1);
-            ptx::mbar_init(b_empty + i, 1);
-        }
-        ptx::mbar_init(sf_full, kNumEpiWarps);
-        ptx::mbar_init(sf_full + 1, kNumEpiWarps);
+        for (uint32_t i = 0; i < C::kDepthB; ++i) ptx::mbar_init(b_full + i, 1);
         ptx::mbar_init(tmem_full, 1);
         ptx::mbar_init(tmem_empty, kNumEpiWarps);
         *abort_flag = 0;
@@ -177,7 +178,8 @@ gemm_cluster_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_const
                 const uint32_t n_blk = ns * CL + rank;
                 const int32_t e = max(0, __ldg(p.m_indices + m_blk * BM));
                 for (uint32_t kb = 0; kb < num_kb; ++kb) {
-                    if (!ptx::mbar_wait_impl(b_empty + rb.slot, rb.phase ^ 1, abort_flag)) { give_up(1); break; }
+                    // slot i of the weight ring is free when slot i of the P ring is: one commit covers both
+                    if (!ptx::mbar_wait_cluster(p_empty + rb.slot, rb.phase ^ 1, abort_flag)) { give_up(1); break; }
                     ptx::mbar_arrive_expect_tx(b_full + rb.slot, kSlotB + kSlotSFB);
                     ptx::tma_load_2d(smem_gen + C::kOffB + rb.slot * kSlotB, &tm_b, b_full + rb.slot, kb * (BK / 2),
                                      e * p.n + n_blk * BN);
@@ -211,25 +213,24 @@ gemm_cluster_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_const
         // put them there with tcgen05.st), so a K block costs this thread four MMAs and its commits:
         // a tensor-memory copy of one scale atom costs as much issue time as an MMA of N <= 128, and
         // eight of them per K block were the larger half of the tensor-side time.
-        Ring rp, rb;
-        uint32_t acc_phase = 0, cnt = 0;
+        Ring rp;
+        uint32_t acc_phase = 0;
         constexpr uint32_t idesc = ptx::make_idesc_nvf4(BM, BN);
         constexpr uint16_t kAllCtas = static_cast<uint16_t>((1u << CL) - 1u);
         for (uint32_t st = cid; st < num_super && ok; st += ncl) {
             if (!ptx::mbar_wait(tmem_empty, acc_phase ^ 1, abort_flag, pa, 0)) { give_up(1); break; }
             ptx::tcgen05_fence_after_sync();
-            for (uint32_t kb = 0; kb < num_kb; ++kb, ++cnt) {
-                const uint32_t buf = cnt & 1u;
-                if (!ptx::mbar_wait_cluster(p_full + rp.slot, rp.phase, abort_flag, pa, 1) ||
-                    !ptx::mbar_wait(b_full + rb.slot, rb.phase, abort_flag, pa, 2) ||
-                    !ptx::mbar_wait(sf_full + buf, (cnt >> 1) & 1u, abort_flag, pa, 3)) { give_up(1); break; }
+            for (uint32_t kb = 0; kb < num_kb; ++kb) {
+                // the scale warps arrive here only after they have seen this slot's P-full and B-full complete, so
+                // this one wait also covers the operand tiles in shared memory
+                if (!ptx::mbar_wait(sf_full + rp.slot, rp.phase, abort_flag, pa, 3)) { give_up(1); break; }
                 ptx::tcgen05_fence_after_sync();
                 const long long pt1 = ptx::probe_clock();
                 if (lane == 0) {
                     const uint32_t a0 = smem + C::kOffA0 + rp.slot * kSlotP0;
                     const uint32_t a1 = smem + C::kOffA1 + rp.slot * kSlotP0;
-                    const uint32_t b = smem + C::kOffB + rb.slot * kSlotB;
-                    const uint32_t sf = tmem_base + kColSF + buf * kSfBufCols;
+                    const uint32_t b = smem + C::kOffB + rp.slot * kSlotB;
+                    const uint32_t sf = tmem_base + kColSF + rp.slot * kSfBufCols;
 #pragma unroll
                     for (uint32_t a = 0; a < kKAtoms; ++a) {
                         const uint64_t desc_b = ptx::make_smem_desc(b + a * 32, 512, ptx::kSwizzle64B);
@@ -241,14 +242,14 @@ gemm_cluster_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_const
                     }
                     const long long pt2 = ptx::probe_clock();
                     ptx::probe_count(pa, 5, pt2 - pt1);
-                    ptx::tcgen05_commit_cluster(p_empty + rp.slot, kAllCtas);   // frees this slot in every CTA's count
-                    ptx::tcgen05_commit(b_empty + rb.slot);
+                    // one commit per K block, to every CTA of the cluster: it frees the P slot, the weight slot and
+                    // the scale columns of this ring position
+                    ptx::tcgen05_commit_cluster(p_empty + rp.slot, kAllCtas);
                     if (kb == num_kb - 1) ptx::tcgen05_commit(tmem_full);
                     ptx::probe_count(pa, 6, ptx::probe_clock() - pt2);
                 }
                 __syncwarp();
                 rp.advance<C::kDepthP>();
-                rb.advance<C::kDepthB>();
             }
             acc_phase ^= 1;
         }
@@ -298,25 +299,22 @@ gemm_cluster_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_const
         // a copy): lane r of each quadrant gets the scale words of rows r, r + 32, r + 64, r + 96 in four
         // consecutive columns.  Warps 4-7 take the weight scales straight from the rows TMA landed (which also
         // does the transposition a tensor-memory copy would have needed), warps 8-11 the activation scales of
-        // both passes.  Two column buffers alternate; a buffer is rewritten once the MMAs of two K blocks
-        // earlier have retired (their commit on the B-empty barrier).
+        // both passes.  There is one set of scale columns per ring position; it is rewritten once the MMAs
+        // that used it have retired (the P-empty barrier).
         const uint32_t quad = warp & 3, half = (warp - kWarpEpi0) >> 2;
-        uint32_t acc_phase = 0, cnt = 0;
-        Ring rp, rb;
+        uint32_t acc_phase = 0;
+        Ring rp;
         for (uint32_t st = cid; st < num_super && ok; st += ncl) {
-            for (uint32_t kb = 0; kb < num_kb; ++kb, ++cnt) {
-                const uint32_t buf = cnt & 1u;
-                const uint32_t sf = tmem_base + ((quad * 32) << 16) + kColSF + buf * kSfBufCols;
-                const bool src_ok = half == 0 ? ptx::mbar_wait(b_full + rb.slot, rb.phase, abort_flag, pa, 1)
+            for (uint32_t kb = 0; kb < num_kb; ++kb) {
+                const uint32_t sf = tmem_base + ((quad * 32) << 16) + kColSF + rp.slot * kSfBufCols;
+                const bool src_ok = half == 0 ? ptx::mbar_wait(b_full + rp.slot, rp.phase, abort_flag, pa, 1)
                                               : ptx::mbar_wait_cluster(p_full + rp.slot, rp.phase, abort_flag, pa, 1);
                 if (!src_ok) { give_up(1); break; }
-                if (cnt >= 2 && !ptx::mbar_wait(b_empty + (cnt - 2) % C::kDepthB, ((cnt - 2) / C::kDepthB) & 1u, abort_flag, pa, 2)) {
-                    give_up(1);
-                    break;
-                }
+                // the columns of this ring position are free once its previous MMAs have retired
+                if (!ptx::mbar_wait_cluster(p_empty + rp.slot, rp.phase ^ 1, abort_flag, pa, 2)) { give_up(1); break; }
                 ptx::tcgen05_fence_after_sync();
                 if (half == 0) {
-                    const uint32_t sfb = smem + C::kOffSFB + rb.slot * kSlotSFB + lane * 4;
+                    const uint32_t sfb = smem + C::kOffSFB + rp.slot * kSlotSFB + lane * 4;
 #pragma unroll
                     for (uint32_t i = 0; i < kKAtoms * 2; ++i)
                         ptx::tmem_st_32x32b_x4(sf + kSfB + 4 * i, ptx::lds32(sfb + i * 512), ptx::lds32(sfb + i * 512 + 128),
@@ -335,9 +333,8 @@ gemm_cluster_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_const
                 ptx::tmem_st_wait();
                 ptx::tcgen05_fence_before_sync();
                 __syncwarp();
-                if (lane == 0) ptx::mbar_arrive(sf_full + buf);
+                if (lane == 0) ptx::mbar_arrive(sf_full + rp.slot);
                 rp.advance<C::kDepthP>();
-                rb.advance<C::kDepthB>();
             }
             if (!ok) break;
             uint32_t m_blk, ns;
@@ -385,30 +382,31 @@ gemm_cluster_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_const
     } else if (warp >= kWarpXform0) {
         // ================= transform: this CTA's rows into its own P slot =================
         const uint32_t t = threadIdx.x - kWarpXform0 * 32;
-        if (warp - kWarpXform0 < C::kActiveWarps) {
-            const uint32_t lrow = t % C::kRows;                                                      // row inside this CTA's share
-            const uint32_t mrow = 32 * (lrow / C::kRun) + C::kRun * rank + lrow % C::kRun;           // its row in the MMA tile
-            const uint32_t first_block = (t / C::kRows) * 2;
-            Ring ra, rp;
-            for (uint32_t st = cid; st < num_super && ok; st += ncl) {
-                for (uint32_t kb = 0; kb < num_kb; ++kb) {
-                    if (!ptx::mbar_wait(a_full + ra.slot, ra.phase, abort_flag, pa, 0)) { give_up(1); break; }
-                    const uint32_t a_smem = smem + C::kOffA + ra.slot * C::kSlotA;
-                    uint32_t w[2][8];
+        const uint32_t lrow = t % C::kRows;                                                      // row inside this CTA's share
+        const uint32_t mrow = 32 * (lrow / C::kRun) + C::kRun * rank + lrow % C::kRun;           // its row in the MMA tile
+        const uint32_t first_block = (t / C::kRows) * C::kBpt;
+        Ring ra, rp;
+        for (uint32_t st = cid; st < num_super && ok; st += ncl) {
+            for (uint32_t kb = 0; kb < num_kb; ++kb) {
+                if (!ptx::mbar_wait(a_full + ra.slot, ra.phase, abort_flag, pa, 0)) { give_up(1); break; }
+                const uint32_t a_smem = smem + C::kOffA + ra.slot * C::kSlotA;
+                uint32_t w[C::kBpt][8];
 #pragma unroll
-                    for (uint32_t j = 0; j < 2; ++j) {
-                        const uint32_t k = (first_block + j) * 16u;
-                        const uint4 lo = ptx::lds128(a_smem + xform::a_bf16_offset<C::kRows>(lrow, k));
-                        const uint4 hi = ptx::lds128(a_smem + xform::a_bf16_offset<C::kRows>(lrow, k + 8));
-                        w[j][0] = lo.x; w[j][1] = lo.y; w[j][2] = lo.z; w[j][3] = lo.w;
-                        w[j][4] = hi.x; w[j][5] = hi.y; w[j][6] = hi.z; w[j][7] = hi.w;
-                    }
-                    __syncwarp();
-                    if (lane == 0) ptx::mbar_arrive(a_empty + ra.slot);   // the tile now lives in registers
-                    // every tensor core of the cluster must be done with this slot before anyone rewrites it
-                    if (!ptx::mbar_wait_cluster(p_empty + rp.slot, rp.phase ^ 1, abort_flag, pa, 1)) { give_up(1); break; }
-                    const uint32_t off_a0 = C::kOffA0 + rp.slot * kSlotP0, off_a1 = C::kOffA1 + rp.slot * kSlotP0;
-                    const uint32_t off_s0 = C::kOffSFA0 + rp.slot * kSlotSFA, off_s1 = C::kOffSFA1 + rp.slot * kSlotSFA;
+                for (uint32_t j = 0; j < C::kBpt; ++j) {
+                    const uint32_t k = (first_block + j) * 16u;
+                    const uint4 lo = ptx::lds128(a_smem + xform::a_bf16_offset<C::kRows>(lrow, k));
+                    const uint4 hi = ptx::lds128(a_smem + xform::a_bf16_offset<C::kRows>(lrow, k + 8));
+                    w[j][0] = lo.x; w[j][1] = lo.y; w[j][2] = lo.z; w[j][3] = lo.w;
+                    w[j][4] = hi.x; w[j][5] = hi.y; w[j][6] = hi.z; w[j][7] = hi.w;
+                }
+                __syncwarp();
+                if (lane == 0) ptx::mbar_arrive(a_empty + ra.slot);   // the tile now lives in registers
+                // every tensor core of the cluster must be done with this slot before anyone rewrites it
+                if (!ptx::mbar_wait_cluster(p_empty + rp.slot, rp.phase ^ 1, abort_flag, pa, 1)) { give_up(1); break; }
+                const uint32_t off_a0 = C::kOffA0 + rp.slot * kSlotP0, off_a1 = C::kOffA1 + rp.slot * kSlotP0;
+                const uint32_t off_s0 = C::kOffSFA0 + rp.slot * kSlotSFA, off_s1 = C::kOffSFA1 + rp.slot * kSlotSFA;
+                const uint32_t sf_base = (first_block >> 2) * 512u + xform::sf_word_offset(mrow);
+                if constexpr (C::kBpt == 2) {
                     xform::Block16 blk[2];
                     xform::decompose_block16<kResidual>(w[0], blk[0]);
                     xform::decompose_block16<kResidual>(w[1], blk[1]);
@@ -416,18 +414,27 @@ gemm_cluster_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_const
                     ptx::sts128(smem + off_a0 + off, blk[0].q0[0], blk[0].q0[1], blk[1].q0[0], blk[1].q0[1]);
                     if constexpr (kResidual)
                         ptx::sts128(smem + off_a1 + off, blk[0].q1[0], blk[0].q1[1], blk[1].q1[0], blk[1].q1[1]);
-                    const uint32_t sf_addr = (first_block >> 2) * 512u + xform::sf_word_offset(mrow) + (first_block & 2u);
+                    const uint32_t sf_addr = sf_base + (first_block & 2u);
                     ptx::sts16(smem + off_s0 + sf_addr, blk[0].s0 | (blk[1].s0 << 8));
                     if constexpr (kResidual) ptx::sts16(smem + off_s1 + sf_addr, blk[0].s1 | (blk[1].s1 << 8));
-                    ptx::fence_proxy_async_smem();                   // own stores -> async proxy (MMA reads, bulk-copy reads)
-                    __syncwarp();
-                    if (lane == 0) {
-                        ptx::mbar_arrive(p_full + rp.slot);
-                        ptx::mbar_arrive(share_full + rp.slot);      // the push warp takes it from here
-                    }
-                    ra.advance<C::kDepthA>();
-                    rp.advance<C::kDepthP>();
+                } else {
+                    xform::Block16 blk;
+                    xform::decompose_block16<kResidual>(w[0], blk);
+                    const uint32_t off = xform::fp4_offset<BK>(mrow, (first_block * 16u) & ~31u) + ((first_block & 1u) << 3);
+                    ptx::sts64(smem + off_a0 + off, blk.q0[0], blk.q0[1]);
+                    if constexpr (kResidual) ptx::sts64(smem + off_a1 + off, blk.q1[0], blk.q1[1]);
+                    const uint32_t sf_addr = sf_base + (first_block & 3u);
+                    ptx::sts8(smem + off_s0 + sf_addr, blk.s0);
+                    if constexpr (kResidual) ptx::sts8(smem + off_s1 + sf_addr, blk.s1);
                 }
+                ptx::fence_proxy_async_smem();                   // own stores -> async proxy (MMA reads, bulk-copy reads)
+                __syncwarp();
+                if (lane == 0) {
+                    ptx::mbar_arrive(p_full + rp.slot);
+                    ptx::mbar_arrive(share_full + rp.slot);      // the push warp takes it from here
+                }
+                ra.advance<C::kDepthA>();
+                rp.advance<C::kDepthP>();
             }
         }
     }
@@ -446,11 +453,11 @@ gemm_cluster_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_const
     }
 }
 
-template <uint32_t CL, bool kResidual>
+template <uint32_t CL, bool kResidual, uint32_t kXW>
 int launch_variant(const void* a, int64_t lda, const void* b, const void* sfb, int M, int N, int K, int E,
                    const Params& p, int num_sms, cudaStream_t stream)
 {
-    using C = Cfg<CL>;
+    using C = Cfg<CL, kXW>;
     CUtensorMap tm_a, tm_b, tm_sfb;
     int rc = host::encode_tensor_map_2d(&tm_a, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, a, K, M, lda * 2, 64, C::kRows,
                                         CU_TENSOR_MAP_SWIZZLE_128B);
@@ -462,7 +469,7 @@ int launch_variant(const void* a, int64_t lda, const void* b, const void* sfb, i
                                     static_cast<uint64_t>(E) * (K / 64), static_cast<uint64_t>(N) * 4, BN, kKAtoms,
                                     CU_TENSOR_MAP_SWIZZLE_NONE);
     if (rc) return rc;
-    auto kernel = gemm_cluster_kernel<CL, kResidual>;
+    auto kernel = gemm_cluster_kernel<CL, kResidual, kXW>;
     static int max_clusters[host::kMaxDevices] = {};
     int dev = 0;
     NVFP4_CUDA_CHECK(cudaGetDevice(&dev));
@@ -472,7 +479,7 @@ int launch_variant(const void* a, int64_t lda, const void* b, const void* sfb, i
     attr[0].val.clusterDim.x = CL;
     attr[0].val.clusterDim.y = 1;
     attr[0].val.clusterDim.z = 1;
-    cfg.blockDim = dim3(kThreads);
+    cfg.blockDim = dim3(kThreadsFor(kXW));
     cfg.dynamicSmemBytes = C::kSmemAlloc;
     cfg.stream = stream;
     cfg.attrs = attr;
@@ -498,7 +505,7 @@ int launch_variant(const void* a, int64_t lda, const void* b, const void* sfb, i
 // cluster = 2 or 4 CTAs per activation tile; N must be a multiple of 256 * cluster.
 int launch_gemm_cluster(const void* a, int64_t lda, const void* b, const void* sfb, const float* gw, void* d,
                         int64_t ldd, const int32_t* m_indices, int M, int N, int K, int E, bool residual,
-                        int cluster, int group_m, int num_sms, int32_t* status, cudaStream_t stream)
+                        int cluster, int xform_warps, int group_m, int num_sms, int32_t* status, cudaStream_t stream)
 {
     Params p;
     p.gw = gw;
@@ -508,11 +515,15 @@ int launch_gemm_cluster(const void* a, int64_t lda, const void* b, const void* s
     p.m = M; p.n = N; p.k = K;
     p.group_m = group_m > 0 ? group_m : 8;
     p.status = status;
+    // transform warps: 16 (one 16-block per thread) for pairs, 8 for quads, unless the caller asks for 8
     if (cluster == 4)
-        return residual ? launch_variant<4, true>(a, lda, b, sfb, M, N, K, E, p, num_sms, stream)
-                        : launch_variant<4, false>(a, lda, b, sfb, M, N, K, E, p, num_sms, stream);
-    return residual ? launch_variant<2, true>(a, lda, b, sfb, M, N, K, E, p, num_sms, stream)
-                    : launch_variant<2, false>(a, lda, b, sfb, M, N, K, E, p, num_sms, stream);
+        return residual ? launch_variant<4, true, 8>(a, lda, b, sfb, M, N, K, E, p, num_sms, stream)
+                        : launch_variant<4, false, 8>(a, lda, b, sfb, M, N, K, E, p, num_sms, stream);
+    if (xform_warps == 8)
+        return residual ? launch_variant<2, true, 8>(a, lda, b, sfb, M, N, K, E, p, num_sms, stream)
+                        : launch_variant<2, false, 8>(a, lda, b, sfb, M, N, K, E, p, num_sms, stream);
+    return residual ? launch_variant<2, true, 16>(a, lda, b, sfb, M, N, K, E, p, num_sms, stream)
+                    : launch_variant<2, false, 16>(a, lda, b, sfb, M, N, K, E, p, num_sms, stream);
 }
 
 #ifdef NVFP4_PROBE

@@ -1,0 +1,458 @@
+// Grouped dual-NVFP4 GEMM, normal orientation, with the activation decomposition done once, ahead of
+// the GEMM, instead of once per weight-column tile inside it.
+//
+// The fused kernels (gemm_normal.cu, gemm_cluster.cu) run Algorithm 1 on a 128-row activation tile every
+// time a CTA visits it, i.e. N / 256 (or N / 512) times per element; on wide layers that arithmetic, not
+// the tensor pipe, sets the pace.  Here a first, bandwidth-bound kernel quantises every activation element
+// exactly once into a workspace in global memory -- A0 and A1 packed row-major, their block scales already
+// in the 512-byte atoms the tensor core reads -- at a cost of 1.125 bytes written (and later re-read through
+// L2) per BF16 element.  The second kernel is then a plain block-scaled FP4 GEMM with two MMAs per K atom:
+// every operand arrives by TMA / bulk copy, no warp does arithmetic in the main loop, and the MMA thread
+// issues back to back.  The two launches are chained with programmatic dependent launch, so that the
+// prologue of the GEMM (barriers, tensor-memory allocation, descriptor prefetch) overlaps the first kernel.
+//
+// The codes and scales are produced by the same device function as in the fused kernels
+// (xform::decompose_block16), so the result is the same bit for bit up to FP32 summation order.
+#include <cuda_bf16.h>
+
+#include "host_common.hpp"
+#include "launchers.hpp"
+#include "transform.cuh"
+
+namespace nvfp4 {
+namespace {
+
+constexpr uint32_t BM = 128, BN = 256;
+constexpr uint32_t kWarpTma = 0, kWarpMma = 1, kWarpEpi0 = 4, kNumEpiWarps = 8;
+constexpr uint32_t kThreads = (kWarpEpi0 + kNumEpiWarps) * 32;   // 384
+constexpr uint32_t kSmemBudget = 232448 - 1024;
+
+// ---------------------------------------------------------------------------------------------------
+// Kernel 1: BF16 activations -> workspace.
+//   a0, a1  (M, K/2) bytes, two E2M1 codes per byte, even element in the low nibble
+//   sfa     (M/128, K/64, passes, 512) bytes: one scale atom per 128 rows x 64 K x pass; inside an atom the
+//           four scale bytes of row r sit at (r % 32) * 16 + (r / 32) * 4 (the tensor-memory image)
+// One thread per 16-element block; the four threads of a 64-K atom row combine their scale bytes into one
+// 32-bit store.
+// ---------------------------------------------------------------------------------------------------
+template <bool kResidual>
+__global__ void __launch_bounds__(256)
+quantize_activation_kernel(const __nv_bfloat16* __restrict__ a, int64_t lda, uint32_t m, uint32_t k,
+                           uint8_t* __restrict__ a0, uint8_t* __restrict__ a1, uint8_t* __restrict__ sfa)
+{
+    ptx::grid_launch_dependents();                       // the GEMM's prologue may start; it waits for our stores itself
+    constexpr uint32_t kPass = kResidual ? 2 : 1;
+    const uint32_t k16 = k / 16;
+    const uint64_t idx = static_cast<uint64_t>(blockIdx.x) * blockDim.x + threadIdx.x;
+    const uint64_t total = static_cast<uint64_t>(m) * k16;
+    // the grid is padded to whole warps of valid work: m * k16 is a multiple of 128 * 4
+    if (idx >= total) return;
+    const uint32_t row = static_cast<uint32_t>(idx / k16), blk16 = static_cast<uint32_t>(idx % k16);
+    const uint4* src = reinterpret_cast<const uint4*>(a + static_cast<int64_t>(row) * lda + blk16 * 16);
+    uint32_t w[8];
+    {
+        uint4 lo, hi;
+        asm volatile("ld.global.nc.L1::no_allocate.v4.u32 {%0, %1, %2, %3}, [%4];"
+                     : "=r"(lo.x), "=r"(lo.y), "=r"(lo.z), "=r"(lo.w) : "l"(src));
+        asm volatile("ld.global.nc.L1::no_allocate.v4.u32 {%0, %1, %2, %3}, [%4];"
+                     : "=r"(hi.x), "=r"(hi.y), "=r"(hi.z), "=r"(hi.w) : "l"(src + 1));
+        w[0] = lo.x; w[1] = lo.y; w[2] = lo.z; w[3] = lo.w;
+        w[4] = hi.x; w[5] = hi.y; w[6] = hi.z; w[7] = hi.w;
+    }
+    xform::Block16 out;
+    xform::decompose_block16<kResidual>(w, out);
+    const uint64_t code_off = static_cast<uint64_t>(row) * (k / 2) + blk16 * 8;
+    *reinterpret_cast<uint2*>(a0 + code_off) = make_uint2(out.q0[0], out.q0[1]);
+    if constexpr (kResidual) *reinterpret_cast<uint2*>(a1 + code_off) = make_uint2(out.q1[0], out.q1[1]);
+    // scale bytes of the four blocks of a K atom -> one word (the four threads are neighbours in a warp)
+    const uint32_t sh = (threadIdx.x & 3u) * 8u;
+    uint32_t s0 = static_cast<uint32_t>(out.s0) << sh, s1 = static_cast<uint32_t>(out.s1) << sh;
+    s0 |= __shfl_xor_sync(0xffffffffu, s0, 1); s0 |= __shfl_xor_sync(0xffffffffu, s0, 2);
+    if constexpr (kResidual) { s1 |= __shfl_xor_sync(0xffffffffu, s1, 1); s1 |= __shfl_xor_sync(0xffffffffu, s1, 2); }
+    if ((threadIdx.x & 3u) == 0) {
+        const uint32_t r = row % BM;
+        const uint64_t atom = (static_cast<uint64_t>(row / BM) * (k / 64) + blk16 / 4) * kPass;
+        uint8_t* dst = sfa + atom * 512 + (r % 32) * 16 + (r / 32) * 4;
+        *reinterpret_cast<uint32_t*>(dst) = s0;
+        if constexpr (kResidual) *reinterpret_cast<uint32_t*>(dst + 512) = s1;
+    }
+}
+
+// ---------------------------------------------------------------------------------------------------
+// Kernel 2: block-scaled FP4 GEMM over the workspace.
+// ---------------------------------------------------------------------------------------------------
+template <uint32_t BK, bool kResidual>
+struct Cfg {
+    static_assert(BK == 128 || BK == 256, "K block");
+    static constexpr uint32_t kAtoms = BK / 64, kPass = kResidual ? 2 : 1;
+    static constexpr uint32_t kRowBytes = BK / 2;                             // 64 or 128: one swizzle span per row
+    static constexpr uint64_t kSwizzle = BK == 256 ? ptx::kSwizzle128B : ptx::kSwizzle64B;
+    static constexpr uint32_t kSBO = 8 * kRowBytes;
+    static constexpr uint32_t kSlotA = BM * kRowBytes;                         // one pass
+    static constexpr uint32_t kSlotB = BN * kRowBytes;
+    static constexpr uint32_t kSlotSFA = kAtoms * kPass * 512, kSlotSFB = kAtoms * 2 * 512;
+    static constexpr uint32_t kStage = kPass * kSlotA + kSlotB + kSlotSFA + kSlotSFB;
+    // tensor memory: 256 accumulator columns, then per ring position SFA (4 columns per atom and pass) and SFB
+    // (8 columns per atom: two 128-row groups)
+    static constexpr uint32_t kTmemCols = 512, kColAcc = 0, kColSF = 256;
+    static constexpr uint32_t kSfA = 0, kSfB = 4 * kAtoms * kPass, kSfCols = kSfB + 8 * kAtoms;
+    static constexpr uint32_t kDepthSmem = (kSmemBudget - 1024) / kStage, kDepthTmem = (kTmemCols - kColSF) / kSfCols;
+    static constexpr uint32_t kDepthRaw = kDepthSmem < kDepthTmem ? kDepthSmem : kDepthTmem;
+    static constexpr uint32_t kDepth = kDepthRaw > 8 ? 8 : kDepthRaw;
+    static_assert(kDepth >= 3, "ring too shallow");
+    static constexpr uint32_t kOffA = 0;                                       // [kDepth][kPass][kSlotA]
+    static constexpr uint32_t kOffB = kOffA + kDepth * kPass * kSlotA;
+    static constexpr uint32_t kOffSFA = kOffB + kDepth * kSlotB;
+    static constexpr uint32_t kOffSFB = kOffSFA + kDepth * kSlotSFA;
+    static constexpr uint32_t kOffBars = kOffSFB + kDepth * kSlotSFB;
+    static constexpr uint32_t kNumBars = 3 * kDepth + 2;
+    static constexpr uint32_t kSmemAlloc = kOffBars + kNumBars * 8 + 16 + 1024;
+    static_assert(kSmemAlloc <= 232448, "shared memory budget");
+};
+
+struct Params {
+    const float* gw;
+    const int32_t* m_indices;
+    const uint8_t* sfa;
+    __nv_bfloat16* d;
+    int64_t ldd;
+    uint32_t m, n, k;
+    uint32_t group_m;
+    int32_t* status;
+};
+
+struct Ring {
+    uint32_t slot = 0, phase = 0;
+    template <uint32_t kDepth>
+    __device__ __forceinline__ void advance()
+    {
+        if (++slot == kDepth) { slot = 0; phase ^= 1; }
+    }
+};
+
+// Tiles are walked in groups of `group_m` row blocks: inside a group the row block changes fastest, so the
+// CTAs running at the same time share a few weight tiles and a few activation tiles in L2.
+__device__ __forceinline__ void tile_coords(uint32_t tile, uint32_t num_m, uint32_t num_n, uint32_t group_m,
+                                            uint32_t& m_blk, uint32_t& n_blk)
+{
+    const uint32_t per_group = group_m * num_n;
+    const uint32_t g = tile / per_group, r = tile % per_group;
+    const uint32_t first = g * group_m;
+    const uint32_t rows = min(group_m, num_m - first);
+    m_blk = first + r % rows;
+    n_blk = r / rows;
+}
+
+template <uint32_t BK, bool kResidual>
+__global__ void __launch_bounds__(kThreads, 1)
+gemm_split_kernel(const __grid_constant__ CUtensorMap tm_a0, const __grid_constant__ CUtensorMap tm_a1,
+                  const __grid_constant__ CUtensorMap tm_b, const __grid_constant__ CUtensorMap tm_sfb, const Params p)
+{
+    using C = Cfg<BK, kResidual>;
+    extern __shared__ uint8_t smem_raw[];
+    const uint32_t smem = (ptx::smem_u32(smem_raw) + 1023u) & ~1023u;
+    uint8_t* smem_gen = smem_raw + (smem - ptx::smem_u32(smem_raw));
+
+    uint64_t* bars = reinterpret_cast<uint64_t*>(smem_gen + C::kOffBars);
+    uint64_t* full = bars;                           // operands of a K block have landed (one arrive + bytes)
+    uint64_t* empty = full + C::kDepth;              // the MMAs that read a ring position have retired (one commit)
+    uint64_t* sf_full = empty + C::kDepth;           // its scales are in tensor memory (eight warps)
+    uint64_t* tmem_full = sf_full + C::kDepth;
+    uint64_t* tmem_empty = tmem_full + 1;
+    uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(tmem_empty + 1);
+    volatile uint32_t* abort_flag = tmem_slot + 1;
+
+    const uint32_t warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    if (threadIdx.x == 0) {
+        for (uint32_t i = 0; i < C::kDepth; ++i) {
+            ptx::mbar_init(full + i, 1);
+            ptx::mbar_init(empty + i, 1);
+            ptx::mbar_init(sf_full + i, kNumEpiWarps);
+        }
+        ptx::mbar_init(tmem_full, 1);
+        ptx::mbar_init(tmem_empty, kNumEpiWarps);
+        *abort_flag = 0;
+        ptx::fence_mbar_init();
+        ptx::prefetch_tensormap(&tm_a0);
+        if constexpr (kResidual) ptx::prefetch_tensormap(&tm_a1);
+        ptx::prefetch_tensormap(&tm_b);
+        ptx::prefetch_tensormap(&tm_sfb);
+    }
+    if (warp == kWarpMma) ptx::tmem_alloc<C::kTmemCols>(tmem_slot);
+    ptx::tcgen05_fence_before_sync();
+    __syncthreads();
+    ptx::tcgen05_fence_after_sync();
+    const uint32_t tmem_base = *tmem_slot;
+    // everything above overlapped the quantisation kernel; its stores are visible from here on
+    ptx::grid_dependency_wait();
+
+    const uint32_t num_m = p.m / BM, num_n = p.n / BN, num_kb = p.k / BK;
+    const uint32_t num_tiles = num_m * num_n;
+    bool ok = true;
+    ptx::ProbeAcc pa;
+    auto give_up = [&](uint32_t code) {
+        *abort_flag = 1;
+        if (p.status != nullptr) atomicOr(p.status, static_cast<int32_t>(code));
+        ok = false;
+    };
+
+    if (warp == kWarpTma) {
+        // ================= producer: every operand of a K block on one barrier =================
+        if (lane == 0) {
+            Ring r;
+            for (uint32_t tile = blockIdx.x; tile < num_tiles && ok; tile += gridDim.x) {
+                uint32_t m_blk, n_blk;
+                tile_coords(tile, num_m, num_n, p.group_m, m_blk, n_blk);
+                const int32_t e = max(0, __ldg(p.m_indices + m_blk * BM));
+                const uint8_t* sfa_row = p.sfa + static_cast<uint64_t>(m_blk) * (p.k / 64) * (C::kPass * 512);
+                for (uint32_t kb = 0; kb < num_kb; ++kb) {
+                    if (!ptx::mbar_wait(empty + r.slot, r.phase ^ 1, abort_flag, pa, 0)) { give_up(1); break; }
+                    ptx::mbar_arrive_expect_tx(full + r.slot, C::kStage);
+                    uint8_t* a_dst = smem_gen + C::kOffA + r.slot * C::kPass * C::kSlotA;
+                    ptx::tma_load_2d(a_dst, &tm_a0, full + r.slot, kb * C::kRowBytes, m_blk * BM);
+                    if constexpr (kResidual)
+                        ptx::tma_load_2d(a_dst + C::kSlotA, &tm_a1, full + r.slot, kb * C::kRowBytes, m_blk * BM);
+                    ptx::tma_load_2d(smem_gen + C::kOffB + r.slot * C::kSlotB, &tm_b, full + r.slot, kb * C::kRowBytes,
+                                     e * p.n + n_blk * BN);
+                    ptx::tma_load_2d(smem_gen + C::kOffSFB + r.slot * C::kSlotSFB, &tm_sfb, full + r.slot, n_blk * BN,
+                                     e * (p.k / 64) + kb * C::kAtoms);
+                    ptx::bulk_load(smem_gen + C::kOffSFA + r.slot * C::kSlotSFA,
+                                   sfa_row + static_cast<uint64_t>(kb) * C::kSlotSFA, C::kSlotSFA, full + r.slot);
+                    r.advance<C::kDepth>();
+                }
+            }
+        }
+    } else if (warp == kWarpMma) {
+        // ================= MMA issue: one wait, 2 x kAtoms (x passes) MMAs, one commit per K block =================
+        Ring r;
+        uint32_t acc_phase = 0;
+        constexpr uint32_t idesc = ptx::make_idesc_nvf4(BM, BN);
+        for (uint32_t tile = blockIdx.x; tile < num_tiles && ok; tile += gridDim.x) {
+            if (!ptx::mbar_wait(tmem_empty, acc_phase ^ 1, abort_flag, pa, 0)) { give_up(1); break; }
+            ptx::tcgen05_fence_after_sync();
+            for (uint32_t kb = 0; kb < num_kb; ++kb) {
+                // the scale warps arrive only after they have seen `full` of this ring position themselves
+                if (!ptx::mbar_wait(sf_full + r.slot, r.phase, abort_flag, pa, 1)) { give_up(1); break; }
+                ptx::tcgen05_fence_after_sync();
+                if (lane == 0) {
+                    const uint32_t a0 = smem + C::kOffA + r.slot * C::kPass * C::kSlotA, a1 = a0 + C::kSlotA;
+                    const uint32_t b = smem + C::kOffB + r.slot * C::kSlotB;
+                    const uint32_t sf = tmem_base + C::kColSF + r.slot * C::kSfCols;
+#pragma unroll
+                    for (uint32_t a = 0; a < C::kAtoms; ++a) {
+                        const uint64_t desc_b = ptx::make_smem_desc(b + a * 32, C::kSBO, C::kSwizzle);
+                        ptx::tcgen05_mma_nvf4(tmem_base + C::kColAcc, ptx::make_smem_desc(a0 + a * 32, C::kSBO, C::kSwizzle),
+                                              desc_b, idesc, sf + C::kSfA + 4 * (a * C::kPass), sf + C::kSfB + 8 * a,
+                                              (kb | a) != 0 ? 1u : 0u);
+                        if constexpr (kResidual)
+                            ptx::tcgen05_mma_nvf4(tmem_base + C::kColAcc, ptx::make_smem_desc(a1 + a * 32, C::kSBO, C::kSwizzle),
+                                                  desc_b, idesc, sf + C::kSfA + 4 * (a * C::kPass + 1), sf + C::kSfB + 8 * a, 1u);
+                    }
+                    ptx::tcgen05_commit(empty + r.slot);
+                    if (kb == num_kb - 1) ptx::tcgen05_commit(tmem_full);
+                }
+                __syncwarp();
+                r.advance<C::kDepth>();
+            }
+            acc_phase ^= 1;
+        }
+    } else if (warp >= kWarpEpi0) {
+        // ================= scale duty in the main loop, then the epilogue =================
+        // Scales go from shared to tensor memory with tcgen05.st: a warp reaches only its own quadrant of lanes and
+        // the MMA wants a copy in each, so four warps (one per quadrant) carry the weight scales and four the
+        // activation scales.  Lane r of a quadrant gets the scale words of rows r, r + 32, r + 64, r + 96 of an
+        // atom in four consecutive columns: for the weights straight from the row-major words TMA landed, for the
+        // activations from the atoms the quantisation kernel laid out in that order.
+        const uint32_t quad = warp & 3, half = (warp - kWarpEpi0) >> 2;
+        uint32_t acc_phase = 0;
+        Ring r;
+        for (uint32_t tile = blockIdx.x; tile < num_tiles && ok; tile += gridDim.x) {
+            for (uint32_t kb = 0; kb < num_kb; ++kb) {
+                // `full` of this phase implies the previous MMAs of the ring position have retired (the producer
+                // waited for that), so its scale columns are free as well
+                if (!ptx::mbar_wait(full + r.slot, r.phase, abort_flag, pa, 2)) { give_up(1); break; }
+                const uint32_t sf = tmem_base + ((quad * 32) << 16) + C::kColSF + r.slot * C::kSfCols;
+                if (half == 0) {
+                    const uint32_t sfb = smem + C::kOffSFB + r.slot * C::kSlotSFB + lane * 4;
+#pragma unroll
+                    for (uint32_t i = 0; i < C::kAtoms * 2; ++i)
+                        ptx::tmem_st_32x32b_x4(sf + C::kSfB + 4 * i, ptx::lds32(sfb + i * 512), ptx::lds32(sfb + i * 512 + 128),
+                                               ptx::lds32(sfb + i * 512 + 256), ptx::lds32(sfb + i * 512 + 384));
+                } else {
+                    const uint32_t sfa = smem + C::kOffSFA + r.slot * C::kSlotSFA + lane * 16;
+#pragma unroll
+                    for (uint32_t i = 0; i < C::kAtoms * C::kPass; ++i) {
+                        const uint4 v = ptx::lds128(sfa + i * 512);
+                        ptx::tmem_st_32x32b_x4(sf + C::kSfA + 4 * i, v.x, v.y, v.z, v.w);
+                    }
+                }
+                ptx::tmem_st_wait();
+                ptx::tcgen05_fence_before_sync();
+                __syncwarp();
+                if (lane == 0) ptx::mbar_arrive(sf_full + r.slot);
+                r.advance<C::kDepth>();
+            }
+            if (!ok) break;
+            // ---- epilogue: TMEM -> x G_W -> BF16 -> global; two warps per quadrant, 128 columns each ----
+            uint32_t m_blk, n_blk;
+            tile_coords(tile, num_m, num_n, p.group_m, m_blk, n_blk);
+            const int32_t e = max(0, __ldg(p.m_indices + m_blk * BM));
+            const float g = __ldg(p.gw + e);
+            if (!ptx::mbar_wait(tmem_full, acc_phase, abort_flag, pa, 3)) { give_up(1); break; }
+            ptx::tcgen05_fence_after_sync();
+            const uint32_t row = m_blk * BM + quad * 32 + lane;
+            __nv_bfloat16* drow = p.d + static_cast<int64_t>(row) * p.ldd + n_blk * BN + half * (BN / 2);
+            const uint32_t taddr = tmem_base + ((quad * 32) << 16) + C::kColAcc + half * (BN / 2);
+            auto emit = [&](const uint32_t (&v)[32], uint32_t c) {
+#pragma unroll
+                for (int q = 0; q < 4; ++q) {
+                    uint32_t o[4];
+#pragma unroll
+                    for (int i = 0; i < 4; ++i) {
+                        const __nv_bfloat162 h = __floats2bfloat162_rn(__uint_as_float(v[8 * q + 2 * i]) * g,
+                                                                       __uint_as_float(v[8 * q + 2 * i + 1]) * g);
+                        o[i] = *reinterpret_cast<const uint32_t*>(&h);
+                    }
+                    *reinterpret_cast<uint4*>(drow + c + 8 * q) = make_uint4(o[0], o[1], o[2], o[3]);
+                }
+            };
+            uint32_t va[32], vb[32];
+            ptx::tmem_ld_32x32b_x32(taddr, va);
+            ptx::tmem_ld_wait();
+            ptx::tmem_ld_32x32b_x32(taddr + 32, vb);
+            emit(va, 0);
+            ptx::tmem_ld_wait();
+            ptx::tmem_ld_32x32b_x32(taddr + 64, va);
+            emit(vb, 32);
+            ptx::tmem_ld_wait();
+            ptx::tmem_ld_32x32b_x32(taddr + 96, vb);
+            emit(va, 64);
+            ptx::tmem_ld_wait();
+            ptx::tcgen05_fence_before_sync();                 // everything has left tensor memory
+            __syncwarp();
+            if (lane == 0) ptx::mbar_arrive(tmem_empty);
+            emit(vb, 96);
+            acc_phase ^= 1;
+        }
+    }
+
+    ptx::tcgen05_fence_before_sync();
+    __syncthreads();
+    if (warp == kWarpMma) {
+        ptx::tcgen05_fence_after_sync();
+        ptx::tmem_dealloc<C::kTmemCols>(tmem_base);
+    }
+}
+
+// Stream-ordered workspace: a private memory pool per device that keeps what it has been given, so that after
+// the first call an allocation is a pool look-up ordered on the caller's stream (no device synchronisation,
+// safe with concurrent streams, legal during stream capture).
+int workspace_pool(int dev, cudaMemPool_t* out)
+{
+    static cudaMemPool_t pools[host::kMaxDevices] = {};
+    if (pools[dev] == nullptr) {
+        cudaMemPoolProps props = {};
+        props.allocType = cudaMemAllocationTypePinned;
+        props.handleTypes = cudaMemHandleTypeNone;
+        props.location.type = cudaMemLocationTypeDevice;
+        props.location.id = dev;
+        cudaMemPool_t pool = nullptr;
+        NVFP4_CUDA_CHECK(cudaMemPoolCreate(&pool, &props));
+        uint64_t keep = UINT64_MAX;
+        NVFP4_CUDA_CHECK(cudaMemPoolSetAttribute(pool, cudaMemPoolAttrReleaseThreshold, &keep));
+        pools[dev] = pool;
+    }
+    *out = pools[dev];
+    return NVFP4_OK;
+}
+
+template <uint32_t BK, bool kResidual>
+int launch_variant(const void* a, int64_t lda, const void* b, const void* sfb, int M, int N, int K, int E, Params p,
+                   bool pdl, int num_sms, cudaStream_t stream)
+{
+    using C = Cfg<BK, kResidual>;
+    int dev = 0;
+    NVFP4_CUDA_CHECK(cudaGetDevice(&dev));
+    cudaMemPool_t pool;
+    if (int rc = workspace_pool(dev, &pool)) return rc;
+    const size_t code_bytes = static_cast<size_t>(M) * (K / 2);
+    const size_t sf_bytes = static_cast<size_t>(M) * (K / 16) * C::kPass;
+    const size_t total = C::kPass * code_bytes + sf_bytes;
+    uint8_t* ws = nullptr;
+    NVFP4_CUDA_CHECK(cudaMallocFromPoolAsync(reinterpret_cast<void**>(&ws), total, pool, stream));
+    uint8_t* a0 = ws;
+    uint8_t* a1 = kResidual ? ws + code_bytes : ws;
+    uint8_t* sfa = ws + C::kPass * code_bytes;
+    p.sfa = sfa;
+
+    auto release = [&](int rc) {
+        cudaFreeAsync(ws, stream);
+        return rc;
+    };
+    CUtensorMap tm_a0, tm_a1, tm_b, tm_sfb;
+    const CUtensorMapSwizzle sw = BK == 256 ? CU_TENSOR_MAP_SWIZZLE_128B : CU_TENSOR_MAP_SWIZZLE_64B;
+    int rc = host::encode_tensor_map_2d(&tm_a0, CU_TENSOR_MAP_DATA_TYPE_UINT8, 1, a0, K / 2, M, K / 2, C::kRowBytes, BM, sw);
+    if (rc) return release(rc);
+    rc = host::encode_tensor_map_2d(&tm_a1, CU_TENSOR_MAP_DATA_TYPE_UINT8, 1, a1, K / 2, M, K / 2, C::kRowBytes, BM, sw);
+    if (rc) return release(rc);
+    rc = host::encode_tensor_map_2d(&tm_b, CU_TENSOR_MAP_DATA_TYPE_UINT8, 1, b, K / 2, static_cast<uint64_t>(E) * N, K / 2,
+                                    C::kRowBytes, BN, sw);
+    if (rc) return release(rc);
+    rc = host::encode_tensor_map_2d(&tm_sfb, CU_TENSOR_MAP_DATA_TYPE_INT32, 4, sfb, N, static_cast<uint64_t>(E) * (K / 64),
+                                    static_cast<uint64_t>(N) * 4, BN, C::kAtoms, CU_TENSOR_MAP_SWIZZLE_NONE);
+    if (rc) return release(rc);
+
+    const uint64_t blocks16 = static_cast<uint64_t>(M) * (K / 16);
+    quantize_activation_kernel<kResidual><<<static_cast<unsigned>((blocks16 + 255) / 256), 256, 0, stream>>>(
+        static_cast<const __nv_bfloat16*>(a), lda, static_cast<uint32_t>(M), static_cast<uint32_t>(K), a0, a1, sfa);
+    if (cudaError_t err = cudaGetLastError(); err != cudaSuccess)
+        return release(host::fail(NVFP4_E_CUDA, "activation quantisation launch failed: %s", cudaGetErrorString(err)));
+
+    auto kernel = gemm_split_kernel<BK, kResidual>;
+    static bool attr_set[host::kMaxDevices] = {};
+    if (!attr_set[dev]) {
+        if (cudaError_t err = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, C::kSmemAlloc);
+            err != cudaSuccess)
+            return release(host::fail(NVFP4_E_CUDA, "cudaFuncSetAttribute failed: %s", cudaGetErrorString(err)));
+        attr_set[dev] = true;
+    }
+    const int num_tiles = (M / static_cast<int>(BM)) * (N / static_cast<int>(BN));
+    cudaLaunchConfig_t cfg = {};
+    cudaLaunchAttribute attr[1];
+    attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+    attr[0].val.programmaticStreamSerializationAllowed = 1;
+    cfg.gridDim = dim3(static_cast<unsigned>(num_tiles < num_sms ? num_tiles : num_sms));
+    cfg.blockDim = dim3(kThreads);
+    cfg.dynamicSmemBytes = C::kSmemAlloc;
+    cfg.stream = stream;
+    cfg.attrs = attr;
+    cfg.numAttrs = pdl ? 1 : 0;
+    if (cudaError_t err = cudaLaunchKernelEx(&cfg, kernel, tm_a0, tm_a1, tm_b, tm_sfb, p); err != cudaSuccess)
+        return release(host::fail(NVFP4_E_CUDA, "GEMM launch failed: %s", cudaGetErrorString(err)));
+    return release(NVFP4_OK);
+}
+
+}  // namespace
+
+// Two launches: activations -> NVFP4 workspace, then the block-scaled GEMM over it.  N % 256 == 0.
+int launch_gemm_split(const void* a, int64_t lda, const void* b, const void* sfb, const float* gw, void* d,
+                      int64_t ldd, const int32_t* m_indices, int M, int N, int K, int E, bool residual,
+                      int block_k, int group_m, bool pdl, int num_sms, int32_t* status, cudaStream_t stream)
+{
+    Params p;
+    p.gw = gw;
+    p.m_indices = m_indices;
+    p.sfa = nullptr;
+    p.d = static_cast<__nv_bfloat16*>(d);
+    p.ldd = ldd;
+    p.m = M; p.n = N; p.k = K;
+    p.group_m = group_m > 0 ? group_m : 8;
+    p.status = status;
+    if (K % 256 == 0 && block_k != 128)
+        return residual ? launch_variant<256, true>(a, lda, b, sfb, M, N, K, E, p, pdl, num_sms, stream)
+                        : launch_variant<256, false>(a, lda, b, sfb, M, N, K, E, p, pdl, num_sms, stream);
+    return residual ? launch_variant<128, true>(a, lda, b, sfb, M, N, K, E, p, pdl, num_sms, stream)
+                    : launch_variant<128, false>(a, lda, b, sfb, M, N, K, E, p, pdl, num_sms, stream);
+}
+
+}  // namespace nvfp4

@@ -12,7 +12,11 @@ int launch_gemm_normal(const void* a, int64_t lda, const void* b, const void* sf
 // Cluster variant of the normal orientation (cluster = 2 or 4, N % (256 * cluster) == 0).
 int launch_gemm_cluster(const void* a, int64_t lda, const void* b, const void* sfb, const float* gw, void* d,
                         int64_t ldd, const int32_t* m_indices, int M, int N, int K, int E, bool residual,
-                        int cluster, int group_m, int num_sms, int32_t* status, cudaStream_t stream);
+                        int cluster, int xform_warps, int group_m, int num_sms, int32_t* status, cudaStream_t stream);
+
+int launch_gemm_split(const void* a, int64_t lda, const void* b, const void* sfb, const float* gw, void* d,
+                      int64_t ldd, const int32_t* m_indices, int M, int N, int K, int E, bool residual,
+                      int block_k, int group_m, bool pdl, int num_sms, int32_t* status, cudaStream_t stream);
 
 int launch_gemm_swap(const void* a, int64_t lda, const void* b, const void* sfb, const float* gw, void* d,
                      int64_t ldd, const int32_t* m_indices, int M, int N, int K, int E, bool residual,

@@ -201,6 +201,49 @@ def test_gemm_cluster_matches_oracle(dev, oracle, shape, residual, cluster):
     assert rel_l2(d, want) < REL_L2_VS_ORACLE
 
 
+@pytest.mark.parametrize("shape", [(1, 128, 256, 128), (1, 128, 512, 1024), (4, 256, 1024, 2048), (3, 256, 2048, 640),
+                                   (2, 384, 768, 256)])
+@pytest.mark.parametrize("residual", [True, False])
+@pytest.mark.parametrize("block_k", [0, 128])
+def test_gemm_split_matches_oracle(dev, oracle, shape, residual, block_k):
+    """tune_split_transform=1: the activations are quantised once by a kernel of their own and the GEMM reads
+    codes and scale atoms from the workspace; short and long K, K that only the 128-wide block divides,
+    both K-block widths."""
+    e, rows, n, k = shape
+    a, w = make_case(e, rows, n, k, seed=700 + n + k)
+    b, sfb, gw = nvfp4_gemm.quantize_weight_nvfp4(w.to(dev))
+    mi = nvfp4_gemm.make_m_indices([rows] * e)
+    d = run_gemm(dev, a, b, sfb, gw, mi, n, enable_residual_pass=residual, tune_split_transform=1, tune_block_k=block_k)
+    want = oracle.grouped_gemm(a, b.cpu(), sfb.cpu(), gw.cpu(), mi, n, mode="dual" if residual else "single")
+    assert torch.isfinite(d.float()).all()
+    assert rel_l2(d, want) < REL_L2_VS_ORACLE
+    fused = run_gemm(dev, a, b, sfb, gw, mi, n, enable_residual_pass=residual, tune_split_transform=2)
+    assert rel_l2(d, fused) < 1e-3        # same codes and scales; only the summation order may differ
+
+
+def test_gemm_split_many_tiles_strided(dev, oracle):
+    """Split path with more tiles than SMs, ragged experts, a strided activation matrix and a strided output."""
+    sizes = [128, 384, 256, 128, 512, 128, 256, 640]
+    n, k = 4096, 512
+    g = torch.Generator().manual_seed(123)
+    a_wide = torch.randn(sum(sizes), k + 64, generator=g).to(torch.bfloat16).to(dev)
+    a = a_wide[:, :k]
+    w = (torch.randn(len(sizes), n, k, generator=g) * 0.02).to(torch.bfloat16)
+    b, sfb, gw = nvfp4_gemm.quantize_weight_nvfp4(w.to(dev))
+    mi = nvfp4_gemm.make_m_indices(sizes)
+    d_wide = torch.full((sum(sizes), n + 128), float("nan"), dtype=torch.bfloat16, device=dev)
+    d = d_wide[:, :n]
+    status = torch.zeros(1, dtype=torch.int32, device=dev)
+    for _ in range(3):                    # repeated calls reuse the pooled workspace
+        nvfp4_gemm.m_grouped_bf16_dual_nvfp4_gemm_contiguous(a, b, sfb, gw, d, mi.to(dev), device_status=status,
+                                                             tune_split_transform=1)
+    torch.cuda.synchronize()
+    assert int(status.item()) == 0
+    want = oracle.grouped_gemm(a.cpu().contiguous(), b.cpu(), sfb.cpu(), gw.cpu(), mi, n)
+    assert rel_l2(d.cpu(), want) < REL_L2_VS_ORACLE
+    assert torch.isnan(d_wide[:, n:].float()).all()          # nothing written past the N columns
+
+
 def test_gemm_many_tiles_ragged_experts(dev, oracle):
     """More tiles than SMs, ragged expert sizes: every CTA loops over several tiles."""
     sizes = [128, 384, 256, 128, 512, 128, 256, 640]
