@@ -23,8 +23,12 @@ namespace nvfp4 {
 namespace {
 
 constexpr uint32_t BM = 128, BN = 256;
-constexpr uint32_t kWarpTma = 0, kWarpMma = 1, kWarpEpi0 = 4, kNumEpiWarps = 8;
-constexpr uint32_t kThreads = (kWarpEpi0 + kNumEpiWarps) * 32;   // 384
+// Eight scale warps (two per tensor-memory quadrant: weight scales, activation scales) and sixteen epilogue warps
+// (four per quadrant, 64 accumulator columns each).  They are separate so that the scale factors of the next
+// tile's first K blocks go up while the epilogue of the current tile is still storing.
+constexpr uint32_t kWarpTma = 0, kWarpMma = 1, kWarpSf0 = 2, kNumSfWarps = 8, kWarpEpi0 = kWarpSf0 + kNumSfWarps,
+                   kNumEpiWarps = 16;
+constexpr uint32_t kThreads = (kWarpEpi0 + kNumEpiWarps) * 32;   // 832
 constexpr uint32_t kSmemBudget = 232448 - 1024;
 
 // ---------------------------------------------------------------------------------------------------
@@ -40,13 +44,12 @@ __global__ void __launch_bounds__(256)
 quantize_activation_kernel(const __nv_bfloat16* __restrict__ a, int64_t lda, uint32_t m, uint32_t k,
                            uint8_t* __restrict__ a0, uint8_t* __restrict__ a1, uint8_t* __restrict__ sfa)
 {
-    ptx::grid_launch_dependents();                       // the GEMM's prologue may start; it waits for our stores itself
     constexpr uint32_t kPass = kResidual ? 2 : 1;
     const uint32_t k16 = k / 16;
     const uint64_t idx = static_cast<uint64_t>(blockIdx.x) * blockDim.x + threadIdx.x;
     const uint64_t total = static_cast<uint64_t>(m) * k16;
     // the grid is padded to whole warps of valid work: m * k16 is a multiple of 128 * 4
-    if (idx >= total) return;
+    if (idx >= total) { ptx::grid_launch_dependents(); return; }
     const uint32_t row = static_cast<uint32_t>(idx / k16), blk16 = static_cast<uint32_t>(idx % k16);
     const uint4* src = reinterpret_cast<const uint4*>(a + static_cast<int64_t>(row) * lda + blk16 * 16);
     uint32_t w[8];
@@ -76,6 +79,9 @@ quantize_activation_kernel(const __nv_bfloat16* __restrict__ a, int64_t lda, uin
         *reinterpret_cast<uint32_t*>(dst) = s0;
         if constexpr (kResidual) *reinterpret_cast<uint32_t*>(dst + 512) = s1;
     }
+    // the GEMM may be scheduled once every block has come this far (its prologue then overlaps our tail; it waits
+    // for the completion of this grid before it reads the workspace)
+    ptx::grid_launch_dependents();
 }
 
 // ---------------------------------------------------------------------------------------------------
@@ -96,7 +102,7 @@ struct Cfg {
     // (8 columns per atom: two 128-row groups)
     static constexpr uint32_t kTmemCols = 512, kColAcc = 0, kColSF = 256;
     static constexpr uint32_t kSfA = 0, kSfB = 4 * kAtoms * kPass, kSfCols = kSfB + 8 * kAtoms;
-    static constexpr uint32_t kDepthSmem = (kSmemBudget - 1024) / kStage, kDepthTmem = (kTmemCols - kColSF) / kSfCols;
+    static constexpr uint32_t kDepthSmem = (kSmemBudget - 1024 - kNumEpiWarps * 4 * 144) / kStage, kDepthTmem = (kTmemCols - kColSF) / kSfCols;
     static constexpr uint32_t kDepthRaw = kDepthSmem < kDepthTmem ? kDepthSmem : kDepthTmem;
     static constexpr uint32_t kDepth = kDepthRaw > 8 ? 8 : kDepthRaw;
     static_assert(kDepth >= 3, "ring too shallow");
@@ -104,7 +110,10 @@ struct Cfg {
     static constexpr uint32_t kOffB = kOffA + kDepth * kPass * kSlotA;
     static constexpr uint32_t kOffSFA = kOffB + kDepth * kSlotB;
     static constexpr uint32_t kOffSFB = kOffSFA + kDepth * kSlotSFA;
-    static constexpr uint32_t kOffBars = kOffSFB + kDepth * kSlotSFB;
+    // epilogue staging: per warp four output rows of 64 BF16 (128 bytes, padded to 144 against bank conflicts)
+    static constexpr uint32_t kStageRow = 144, kStageWarp = 4 * kStageRow;
+    static constexpr uint32_t kOffStage = kOffSFB + kDepth * kSlotSFB;
+    static constexpr uint32_t kOffBars = kOffStage + kNumEpiWarps * kStageWarp;
     static constexpr uint32_t kNumBars = 3 * kDepth + 2;
     static constexpr uint32_t kSmemAlloc = kOffBars + kNumBars * 8 + 16 + 1024;
     static_assert(kSmemAlloc <= 232448, "shared memory budget");
@@ -120,6 +129,14 @@ struct Params {
     uint32_t group_m;
     int32_t* status;
 };
+
+#ifdef NVFP4_PROBE
+// event trace of block 0 (timing studies): g_trace[point][stage] = clock64 at the event
+__device__ long long g_trace[10][64];
+#define NVFP4_TRACE(point, stage) do { if (blockIdx.x == 0 && (stage) < 64 && (threadIdx.x & 31u) == 0) g_trace[point][stage] = clock64(); } while (0)
+#else
+#define NVFP4_TRACE(point, stage) do { } while (0)
+#endif
 
 struct Ring {
     uint32_t slot = 0, phase = 0;
@@ -156,7 +173,7 @@ gemm_split_kernel(const __grid_constant__ CUtensorMap tm_a0, const __grid_consta
     uint64_t* bars = reinterpret_cast<uint64_t*>(smem_gen + C::kOffBars);
     uint64_t* full = bars;                           // operands of a K block have landed (one arrive + bytes)
     uint64_t* empty = full + C::kDepth;              // the MMAs that read a ring position have retired (one commit)
-    uint64_t* sf_full = empty + C::kDepth;           // its scales are in tensor memory (eight warps)
+    uint64_t* sf_full = empty + C::kDepth;           // its scales are in tensor memory (the eight scale warps)
     uint64_t* tmem_full = sf_full + C::kDepth;
     uint64_t* tmem_empty = tmem_full + 1;
     uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(tmem_empty + 1);
@@ -167,7 +184,7 @@ gemm_split_kernel(const __grid_constant__ CUtensorMap tm_a0, const __grid_consta
         for (uint32_t i = 0; i < C::kDepth; ++i) {
             ptx::mbar_init(full + i, 1);
             ptx::mbar_init(empty + i, 1);
-            ptx::mbar_init(sf_full + i, kNumEpiWarps);
+            ptx::mbar_init(sf_full + i, kNumSfWarps);
         }
         ptx::mbar_init(tmem_full, 1);
         ptx::mbar_init(tmem_empty, kNumEpiWarps);
@@ -190,6 +207,7 @@ gemm_split_kernel(const __grid_constant__ CUtensorMap tm_a0, const __grid_consta
     const uint32_t num_tiles = num_m * num_n;
     bool ok = true;
     ptx::ProbeAcc pa;
+    const long long probe_start = ptx::probe_clock();
     auto give_up = [&](uint32_t code) {
         *abort_flag = 1;
         if (p.status != nullptr) atomicOr(p.status, static_cast<int32_t>(code));
@@ -207,13 +225,24 @@ gemm_split_kernel(const __grid_constant__ CUtensorMap tm_a0, const __grid_consta
                 const uint8_t* sfa_row = p.sfa + static_cast<uint64_t>(m_blk) * (p.k / 64) * (C::kPass * 512);
                 for (uint32_t kb = 0; kb < num_kb; ++kb) {
                     if (!ptx::mbar_wait(empty + r.slot, r.phase ^ 1, abort_flag, pa, 0)) { give_up(1); break; }
+                    NVFP4_TRACE(0, (tile - blockIdx.x) / gridDim.x * num_kb + kb);
+#if defined(NVFP4_ABLATE_NO_B)      // timing experiments only (wrong results); never defined in the shipped build
+                    ptx::mbar_arrive_expect_tx(full + r.slot, C::kStage - C::kSlotB);
+#elif defined(NVFP4_ABLATE_NO_A)
+                    ptx::mbar_arrive_expect_tx(full + r.slot, C::kStage - C::kPass * C::kSlotA);
+#else
                     ptx::mbar_arrive_expect_tx(full + r.slot, C::kStage);
+#endif
                     uint8_t* a_dst = smem_gen + C::kOffA + r.slot * C::kPass * C::kSlotA;
+#ifndef NVFP4_ABLATE_NO_A
                     ptx::tma_load_2d(a_dst, &tm_a0, full + r.slot, kb * C::kRowBytes, m_blk * BM);
                     if constexpr (kResidual)
                         ptx::tma_load_2d(a_dst + C::kSlotA, &tm_a1, full + r.slot, kb * C::kRowBytes, m_blk * BM);
+#endif
+#ifndef NVFP4_ABLATE_NO_B
                     ptx::tma_load_2d(smem_gen + C::kOffB + r.slot * C::kSlotB, &tm_b, full + r.slot, kb * C::kRowBytes,
                                      e * p.n + n_blk * BN);
+#endif
                     ptx::tma_load_2d(smem_gen + C::kOffSFB + r.slot * C::kSlotSFB, &tm_sfb, full + r.slot, n_blk * BN,
                                      e * (p.k / 64) + kb * C::kAtoms);
                     ptx::bulk_load(smem_gen + C::kOffSFA + r.slot * C::kSlotSFA,
@@ -225,7 +254,7 @@ gemm_split_kernel(const __grid_constant__ CUtensorMap tm_a0, const __grid_consta
     } else if (warp == kWarpMma) {
         // ================= MMA issue: one wait, 2 x kAtoms (x passes) MMAs, one commit per K block =================
         Ring r;
-        uint32_t acc_phase = 0;
+        uint32_t acc_phase = 0, prev_slot = 0;
         constexpr uint32_t idesc = ptx::make_idesc_nvf4(BM, BN);
         for (uint32_t tile = blockIdx.x; tile < num_tiles && ok; tile += gridDim.x) {
             if (!ptx::mbar_wait(tmem_empty, acc_phase ^ 1, abort_flag, pa, 0)) { give_up(1); break; }
@@ -233,7 +262,9 @@ gemm_split_kernel(const __grid_constant__ CUtensorMap tm_a0, const __grid_consta
             for (uint32_t kb = 0; kb < num_kb; ++kb) {
                 // the scale warps arrive only after they have seen `full` of this ring position themselves
                 if (!ptx::mbar_wait(sf_full + r.slot, r.phase, abort_flag, pa, 1)) { give_up(1); break; }
+                NVFP4_TRACE(3, (tile - blockIdx.x) / gridDim.x * num_kb + kb);
                 ptx::tcgen05_fence_after_sync();
+                const long long pt1 = ptx::probe_clock();
                 if (lane == 0) {
                     const uint32_t a0 = smem + C::kOffA + r.slot * C::kPass * C::kSlotA, a1 = a0 + C::kSlotA;
                     const uint32_t b = smem + C::kOffB + r.slot * C::kSlotB;
@@ -247,95 +278,140 @@ gemm_split_kernel(const __grid_constant__ CUtensorMap tm_a0, const __grid_consta
                         if constexpr (kResidual)
                             ptx::tcgen05_mma_nvf4(tmem_base + C::kColAcc, ptx::make_smem_desc(a1 + a * 32, C::kSBO, C::kSwizzle),
                                                   desc_b, idesc, sf + C::kSfA + 4 * (a * C::kPass + 1), sf + C::kSfB + 8 * a, 1u);
+                        // A commit holds this thread until the MMAs before it have been handed to the tensor pipe.
+                        // Issued at the end of a K block it would leave the pipe with nothing queued while this
+                        // thread finds the next K block; issued after the first atom of the NEXT block it costs the
+                        // ring position a few hundred cycles but the pipe keeps its queue.
+                        if (a == 0 && kb != 0) ptx::tcgen05_commit(empty + prev_slot);
                     }
-                    ptx::tcgen05_commit(empty + r.slot);
-                    if (kb == num_kb - 1) ptx::tcgen05_commit(tmem_full);
+                    const long long pt2 = ptx::probe_clock();
+                    ptx::probe_count(pa, 5, pt2 - pt1);
+                    if (kb == num_kb - 1) {
+                        ptx::tcgen05_commit(empty + r.slot);
+                        ptx::tcgen05_commit(tmem_full);
+                    }
+                    ptx::probe_count(pa, 6, ptx::probe_clock() - pt2);
                 }
+                prev_slot = r.slot;
+                NVFP4_TRACE(4, (tile - blockIdx.x) / gridDim.x * num_kb + kb);
                 __syncwarp();
                 r.advance<C::kDepth>();
             }
             acc_phase ^= 1;
         }
-    } else if (warp >= kWarpEpi0) {
-        // ================= scale duty in the main loop, then the epilogue =================
+    } else if (warp >= kWarpSf0 && warp < kWarpEpi0) {
+        // ================= scale warps =================
         // Scales go from shared to tensor memory with tcgen05.st: a warp reaches only its own quadrant of lanes and
         // the MMA wants a copy in each, so four warps (one per quadrant) carry the weight scales and four the
         // activation scales.  Lane r of a quadrant gets the scale words of rows r, r + 32, r + 64, r + 96 of an
         // atom in four consecutive columns: for the weights straight from the row-major words TMA landed, for the
-        // activations from the atoms the quantisation kernel laid out in that order.
-        const uint32_t quad = warp & 3, half = (warp - kWarpEpi0) >> 2;
-        uint32_t acc_phase = 0;
+        // activations from the atoms the quantisation kernel laid out in that order.  All the columns of a K block
+        // go up in one store.
+        const uint32_t quad = warp & 3, group = (warp - kWarpSf0) >> 2;     // group 0: weight scales, 1: activation scales
         Ring r;
         for (uint32_t tile = blockIdx.x; tile < num_tiles && ok; tile += gridDim.x) {
             for (uint32_t kb = 0; kb < num_kb; ++kb) {
                 // `full` of this phase implies the previous MMAs of the ring position have retired (the producer
                 // waited for that), so its scale columns are free as well
                 if (!ptx::mbar_wait(full + r.slot, r.phase, abort_flag, pa, 2)) { give_up(1); break; }
+                if (warp == kWarpSf0) NVFP4_TRACE(1, (tile - blockIdx.x) / gridDim.x * num_kb + kb);
                 const uint32_t sf = tmem_base + ((quad * 32) << 16) + C::kColSF + r.slot * C::kSfCols;
-                if (half == 0) {
+                const long long duty0 = ptx::probe_clock();
+                if (group == 0) {
+                    // word i * 4 + j = row 32 j + lane of 128-row group i (two groups per K atom)
                     const uint32_t sfb = smem + C::kOffSFB + r.slot * C::kSlotSFB + lane * 4;
+                    uint32_t v[8 * C::kAtoms];
 #pragma unroll
                     for (uint32_t i = 0; i < C::kAtoms * 2; ++i)
-                        ptx::tmem_st_32x32b_x4(sf + C::kSfB + 4 * i, ptx::lds32(sfb + i * 512), ptx::lds32(sfb + i * 512 + 128),
-                                               ptx::lds32(sfb + i * 512 + 256), ptx::lds32(sfb + i * 512 + 384));
+#pragma unroll
+                        for (uint32_t j = 0; j < 4; ++j) v[4 * i + j] = ptx::lds32(sfb + i * 512 + j * 128);
+                    ptx::tmem_st_32x32b(sf + C::kSfB, v);
                 } else {
                     const uint32_t sfa = smem + C::kOffSFA + r.slot * C::kSlotSFA + lane * 16;
+                    uint32_t v[4 * C::kAtoms * C::kPass];
 #pragma unroll
                     for (uint32_t i = 0; i < C::kAtoms * C::kPass; ++i) {
-                        const uint4 v = ptx::lds128(sfa + i * 512);
-                        ptx::tmem_st_32x32b_x4(sf + C::kSfA + 4 * i, v.x, v.y, v.z, v.w);
+                        const uint4 q = ptx::lds128(sfa + i * 512);
+                        v[4 * i] = q.x; v[4 * i + 1] = q.y; v[4 * i + 2] = q.z; v[4 * i + 3] = q.w;
                     }
+                    ptx::tmem_st_32x32b(sf + C::kSfA, v);
                 }
                 ptx::tmem_st_wait();
                 ptx::tcgen05_fence_before_sync();
                 __syncwarp();
                 if (lane == 0) ptx::mbar_arrive(sf_full + r.slot);
+                ptx::probe_count(pa, 4, ptx::probe_clock() - duty0);
+                if (warp == kWarpSf0) NVFP4_TRACE(2, (tile - blockIdx.x) / gridDim.x * num_kb + kb);
                 r.advance<C::kDepth>();
             }
-            if (!ok) break;
-            // ---- epilogue: TMEM -> x G_W -> BF16 -> global; two warps per quadrant, 128 columns each ----
+        }
+    } else if (warp >= kWarpEpi0) {
+        // ================= epilogue: TMEM -> x G_W -> BF16 -> global =================
+        // The warp's 32 lanes x 64 columns leave tensor memory in one go and the accumulator goes straight back to
+        // the MMA warp; scaling, packing and the stores then run under the next tile's main loop.
+        const uint32_t quad = warp & 3, group = (warp - kWarpEpi0) >> 2;
+        uint32_t acc_phase = 0;
+        for (uint32_t tile = blockIdx.x; tile < num_tiles && ok; tile += gridDim.x) {
             uint32_t m_blk, n_blk;
             tile_coords(tile, num_m, num_n, p.group_m, m_blk, n_blk);
             const int32_t e = max(0, __ldg(p.m_indices + m_blk * BM));
             const float g = __ldg(p.gw + e);
             if (!ptx::mbar_wait(tmem_full, acc_phase, abort_flag, pa, 3)) { give_up(1); break; }
+            if (warp == kWarpEpi0) NVFP4_TRACE(5, (tile - blockIdx.x) / gridDim.x);
             ptx::tcgen05_fence_after_sync();
-            const uint32_t row = m_blk * BM + quad * 32 + lane;
-            __nv_bfloat16* drow = p.d + static_cast<int64_t>(row) * p.ldd + n_blk * BN + half * (BN / 2);
-            const uint32_t taddr = tmem_base + ((quad * 32) << 16) + C::kColAcc + half * (BN / 2);
-            auto emit = [&](const uint32_t (&v)[32], uint32_t c) {
+            const uint32_t taddr = tmem_base + ((quad * 32) << 16) + C::kColAcc + group * 64;
+            uint32_t o[32];                                    // this lane's row, 64 columns as BF16 pairs
+            {
+                uint32_t va[32], vb[32];
+                ptx::tmem_ld_32x32b_x32(taddr, va);
+                ptx::tmem_ld_32x32b_x32(taddr + 32, vb);
+                ptx::tmem_ld_wait();
+                ptx::tcgen05_fence_before_sync();
+                __syncwarp();
+                if (lane == 0) ptx::mbar_arrive(tmem_empty);
+                if (warp == kWarpEpi0) NVFP4_TRACE(6, (tile - blockIdx.x) / gridDim.x);
 #pragma unroll
-                for (int q = 0; q < 4; ++q) {
-                    uint32_t o[4];
-#pragma unroll
-                    for (int i = 0; i < 4; ++i) {
-                        const __nv_bfloat162 h = __floats2bfloat162_rn(__uint_as_float(v[8 * q + 2 * i]) * g,
-                                                                       __uint_as_float(v[8 * q + 2 * i + 1]) * g);
-                        o[i] = *reinterpret_cast<const uint32_t*>(&h);
-                    }
-                    *reinterpret_cast<uint4*>(drow + c + 8 * q) = make_uint4(o[0], o[1], o[2], o[3]);
+                for (int i = 0; i < 16; ++i) {
+                    const __nv_bfloat162 h0 = __floats2bfloat162_rn(__uint_as_float(va[2 * i]) * g, __uint_as_float(va[2 * i + 1]) * g);
+                    const __nv_bfloat162 h1 = __floats2bfloat162_rn(__uint_as_float(vb[2 * i]) * g, __uint_as_float(vb[2 * i + 1]) * g);
+                    o[i] = *reinterpret_cast<const uint32_t*>(&h0);
+                    o[16 + i] = *reinterpret_cast<const uint32_t*>(&h1);
                 }
-            };
-            uint32_t va[32], vb[32];
-            ptx::tmem_ld_32x32b_x32(taddr, va);
-            ptx::tmem_ld_wait();
-            ptx::tmem_ld_32x32b_x32(taddr + 32, vb);
-            emit(va, 0);
-            ptx::tmem_ld_wait();
-            ptx::tmem_ld_32x32b_x32(taddr + 64, va);
-            emit(vb, 32);
-            ptx::tmem_ld_wait();
-            ptx::tmem_ld_32x32b_x32(taddr + 96, vb);
-            emit(va, 64);
-            ptx::tmem_ld_wait();
-            ptx::tcgen05_fence_before_sync();                 // everything has left tensor memory
-            __syncwarp();
-            if (lane == 0) ptx::mbar_arrive(tmem_empty);
-            emit(vb, 96);
+            }
+            // Lane = row in tensor memory, but a store instruction should write whole 128-byte lines: with one row
+            // per lane every 16-byte store of the warp lands in a different line -- 4096 partial-line requests per
+            // tile, which were measured to hold up the operand loads and the tensor pipe of the next tile for
+            // thousands of cycles.  So four rows at a time go through a 576-byte staging area: four lanes write
+            // their 128 bytes, then the whole warp reads 16 bytes per lane and stores four full lines.
+            const uint32_t stage = smem + C::kOffStage + (warp - kWarpEpi0) * C::kStageWarp;
+            const uint32_t rd = stage + (lane >> 3) * C::kStageRow + (lane & 7u) * 16;
+            __nv_bfloat16* dbase = p.d + static_cast<int64_t>(m_blk * BM + quad * 32 + (lane >> 3)) * p.ldd + n_blk * BN +
+                                   group * 64 + (lane & 7u) * 8;
+#pragma unroll 1
+            for (uint32_t pass = 0; pass < 8; ++pass) {
+                if ((lane >> 2) == pass) {
+                    const uint32_t wr = stage + (lane & 3u) * C::kStageRow;
+#pragma unroll
+                    for (uint32_t c = 0; c < 8; ++c) ptx::sts128(wr + c * 16, o[4 * c], o[4 * c + 1], o[4 * c + 2], o[4 * c + 3]);
+                }
+                __syncwarp();
+                const uint4 q = ptx::lds128(rd);
+#ifndef NVFP4_ABLATE_NO_STORE      // timing experiments only (wrong results); never defined in the shipped build
+                *reinterpret_cast<uint4*>(dbase + static_cast<int64_t>(pass * 4) * p.ldd) = q;
+#else
+                if (q.x == 0x12345678u && p.m == 1) *reinterpret_cast<uint4*>(dbase) = q;
+#endif
+                __syncwarp();
+            }
+            if (warp == kWarpEpi0) NVFP4_TRACE(8, (tile - blockIdx.x) / gridDim.x);
             acc_phase ^= 1;
         }
     }
 
+    ptx::probe_add(32 + (warp < 2 ? warp : (warp < kWarpEpi0 ? 2 : 4)), ptx::probe_clock() - probe_start);
+    if (warp == kWarpTma) ptx::probe_flush(pa, 0);
+    else if (warp == kWarpMma) ptx::probe_flush(pa, 2, 3, -1, -1, -1, 21, 22);
+    else if (warp >= kWarpSf0) ptx::probe_flush(pa, -1, -1, 10, 13, 14);
     ptx::tcgen05_fence_before_sync();
     __syncthreads();
     if (warp == kWarpMma) {
@@ -454,5 +530,19 @@ int launch_gemm_split(const void* a, int64_t lda, const void* b, const void* sfb
     return residual ? launch_variant<128, true>(a, lda, b, sfb, M, N, K, E, p, pdl, num_sms, stream)
                     : launch_variant<128, false>(a, lda, b, sfb, M, N, K, E, p, pdl, num_sms, stream);
 }
+
+#ifdef NVFP4_PROBE
+extern "C" __attribute__((visibility("default"))) int nvfp4_probe_read_split(unsigned long long* out64, int reset)
+{
+    cudaMemcpyFromSymbol(out64, ptx::g_probe, sizeof(unsigned long long) * 64);
+    if (reset) { unsigned long long z[64] = {}; cudaMemcpyToSymbol(ptx::g_probe, z, sizeof z); }
+    return 0;
+}
+extern "C" __attribute__((visibility("default"))) int nvfp4_probe_read_trace(long long* out)
+{
+    cudaMemcpyFromSymbol(out, g_trace, sizeof(long long) * 10 * 64);
+    return 0;
+}
+#endif
 
 }  // namespace nvfp4
