@@ -114,7 +114,7 @@ struct Cfg {
     static constexpr uint32_t kStageRow = 144, kStageWarp = 4 * kStageRow;
     static constexpr uint32_t kOffStage = kOffSFB + kDepth * kSlotSFB;
     static constexpr uint32_t kOffBars = kOffStage + kNumEpiWarps * kStageWarp;
-    static constexpr uint32_t kNumBars = 3 * kDepth + 2;
+    static constexpr uint32_t kNumBars = 4 * kDepth + 2;
     static constexpr uint32_t kSmemAlloc = kOffBars + kNumBars * 8 + 16 + 1024;
     static_assert(kSmemAlloc <= 232448, "shared memory budget");
 };
@@ -171,9 +171,12 @@ gemm_split_kernel(const __grid_constant__ CUtensorMap tm_a0, const __grid_consta
     uint8_t* smem_gen = smem_raw + (smem - ptx::smem_u32(smem_raw));
 
     uint64_t* bars = reinterpret_cast<uint64_t*>(smem_gen + C::kOffBars);
-    uint64_t* full = bars;                           // operands of a K block have landed (one arrive + bytes)
+    uint64_t* full = bars;                           // operand tiles of a K block have landed (one arrive + bytes)
     uint64_t* empty = full + C::kDepth;              // the MMAs that read a ring position have retired (one commit)
-    uint64_t* sf_full = empty + C::kDepth;           // its scales are in tensor memory (the eight scale warps)
+    uint64_t* sf_in = empty + C::kDepth;             // the scale factors of a K block have landed (they are requested
+                                                     // first and are small, so the scale warps finish their copy
+                                                     // while the operand tiles are still arriving)
+    uint64_t* sf_full = sf_in + C::kDepth;           // its scales are in tensor memory (the eight scale warps)
     uint64_t* tmem_full = sf_full + C::kDepth;
     uint64_t* tmem_empty = tmem_full + 1;
     uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(tmem_empty + 1);
@@ -184,6 +187,7 @@ gemm_split_kernel(const __grid_constant__ CUtensorMap tm_a0, const __grid_consta
         for (uint32_t i = 0; i < C::kDepth; ++i) {
             ptx::mbar_init(full + i, 1);
             ptx::mbar_init(empty + i, 1);
+            ptx::mbar_init(sf_in + i, 1);
             ptx::mbar_init(sf_full + i, kNumSfWarps);
         }
         ptx::mbar_init(tmem_full, 1);
@@ -226,27 +230,18 @@ gemm_split_kernel(const __grid_constant__ CUtensorMap tm_a0, const __grid_consta
                 for (uint32_t kb = 0; kb < num_kb; ++kb) {
                     if (!ptx::mbar_wait(empty + r.slot, r.phase ^ 1, abort_flag, pa, 0)) { give_up(1); break; }
                     NVFP4_TRACE(0, (tile - blockIdx.x) / gridDim.x * num_kb + kb);
-#if defined(NVFP4_ABLATE_NO_B)      // timing experiments only (wrong results); never defined in the shipped build
-                    ptx::mbar_arrive_expect_tx(full + r.slot, C::kStage - C::kSlotB);
-#elif defined(NVFP4_ABLATE_NO_A)
-                    ptx::mbar_arrive_expect_tx(full + r.slot, C::kStage - C::kPass * C::kSlotA);
-#else
-                    ptx::mbar_arrive_expect_tx(full + r.slot, C::kStage);
-#endif
+                    ptx::mbar_arrive_expect_tx(sf_in + r.slot, C::kSlotSFA + C::kSlotSFB);
+                    ptx::tma_load_2d(smem_gen + C::kOffSFB + r.slot * C::kSlotSFB, &tm_sfb, sf_in + r.slot, n_blk * BN,
+                                     e * (p.k / 64) + kb * C::kAtoms);
+                    ptx::bulk_load(smem_gen + C::kOffSFA + r.slot * C::kSlotSFA,
+                                   sfa_row + static_cast<uint64_t>(kb) * C::kSlotSFA, C::kSlotSFA, sf_in + r.slot);
+                    ptx::mbar_arrive_expect_tx(full + r.slot, C::kPass * C::kSlotA + C::kSlotB);
                     uint8_t* a_dst = smem_gen + C::kOffA + r.slot * C::kPass * C::kSlotA;
-#ifndef NVFP4_ABLATE_NO_A
                     ptx::tma_load_2d(a_dst, &tm_a0, full + r.slot, kb * C::kRowBytes, m_blk * BM);
                     if constexpr (kResidual)
                         ptx::tma_load_2d(a_dst + C::kSlotA, &tm_a1, full + r.slot, kb * C::kRowBytes, m_blk * BM);
-#endif
-#ifndef NVFP4_ABLATE_NO_B
                     ptx::tma_load_2d(smem_gen + C::kOffB + r.slot * C::kSlotB, &tm_b, full + r.slot, kb * C::kRowBytes,
                                      e * p.n + n_blk * BN);
-#endif
-                    ptx::tma_load_2d(smem_gen + C::kOffSFB + r.slot * C::kSlotSFB, &tm_sfb, full + r.slot, n_blk * BN,
-                                     e * (p.k / 64) + kb * C::kAtoms);
-                    ptx::bulk_load(smem_gen + C::kOffSFA + r.slot * C::kSlotSFA,
-                                   sfa_row + static_cast<uint64_t>(kb) * C::kSlotSFA, C::kSlotSFA, full + r.slot);
                     r.advance<C::kDepth>();
                 }
             }
@@ -260,8 +255,8 @@ gemm_split_kernel(const __grid_constant__ CUtensorMap tm_a0, const __grid_consta
             if (!ptx::mbar_wait(tmem_empty, acc_phase ^ 1, abort_flag, pa, 0)) { give_up(1); break; }
             ptx::tcgen05_fence_after_sync();
             for (uint32_t kb = 0; kb < num_kb; ++kb) {
-                // the scale warps arrive only after they have seen `full` of this ring position themselves
-                if (!ptx::mbar_wait(sf_full + r.slot, r.phase, abort_flag, pa, 1)) { give_up(1); break; }
+                if (!ptx::mbar_wait(sf_full + r.slot, r.phase, abort_flag, pa, 1) ||
+                    !ptx::mbar_wait(full + r.slot, r.phase, abort_flag, pa, 2)) { give_up(1); break; }
                 NVFP4_TRACE(3, (tile - blockIdx.x) / gridDim.x * num_kb + kb);
                 ptx::tcgen05_fence_after_sync();
                 const long long pt1 = ptx::probe_clock();
@@ -311,9 +306,9 @@ gemm_split_kernel(const __grid_constant__ CUtensorMap tm_a0, const __grid_consta
         Ring r;
         for (uint32_t tile = blockIdx.x; tile < num_tiles && ok; tile += gridDim.x) {
             for (uint32_t kb = 0; kb < num_kb; ++kb) {
-                // `full` of this phase implies the previous MMAs of the ring position have retired (the producer
-                // waited for that), so its scale columns are free as well
-                if (!ptx::mbar_wait(full + r.slot, r.phase, abort_flag, pa, 2)) { give_up(1); break; }
+                // the scales of this phase were requested after the producer had seen the ring position free, so the
+                // MMAs that used its scale columns have retired
+                if (!ptx::mbar_wait(sf_in + r.slot, r.phase, abort_flag, pa, 2)) { give_up(1); break; }
                 if (warp == kWarpSf0) NVFP4_TRACE(1, (tile - blockIdx.x) / gridDim.x * num_kb + kb);
                 const uint32_t sf = tmem_base + ((quad * 32) << 16) + C::kColSF + r.slot * C::kSfCols;
                 const long long duty0 = ptx::probe_clock();
