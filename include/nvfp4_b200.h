@@ -115,6 +115,26 @@ NVFP4_API int nvfp4_grouped_gemm_contiguous(const void* a, int64_t lda_elems, co
                                   int m_alignment, const int32_t* tune, int32_t* device_status,
                                   void* stream);
 
+/* Row movers and activation of the expert-parallel MoE layer around the GEMM (dispatch, SwiGLU, combine).
+ * They have no counterpart in the reference project, which has no multi-GPU mode; they exist because the
+ * contiguous layout the GEMM wants (rows grouped by expert, groups padded to the tile height) has to be
+ * produced from, and folded back into, token-major activations on every step.  All pointers are device
+ * pointers, rows are BF16 with 16-byte-aligned starts and strides, index arrays are int64.
+ *
+ * nvfp4_permute_rows: dst[dst_idx ? dst_idx[i] : i] = src[(src_idx ? src_idx[i] : i) / src_div] for
+ *   i < n_rows; row_bytes % 16 == 0.  src_div = k turns a (token, choice) pair index into its token.
+ * nvfp4_swiglu: out[r, j] = silu(h[r, j]) * h[r, inter + j] for r < rows, j < inter (inter % 8 == 0),
+ *   computed in FP32 and rounded once.
+ * nvfp4_combine_rows: y[t] = sum over j < k of w[t * k + j] * rows[pos[t * k + j]], accumulated in FP32 in
+ *   ascending j (deterministic), hidden % 8 == 0. */
+NVFP4_API int nvfp4_permute_rows(const void* src, int64_t src_ld_bytes, const int64_t* src_idx, int src_div,
+                                 const int64_t* dst_idx, int64_t n_rows, int row_bytes, void* dst,
+                                 int64_t dst_ld_bytes, void* stream);
+NVFP4_API int nvfp4_swiglu(const void* h, int64_t h_ld_elems, int64_t rows, int inter, void* out,
+                           int64_t out_ld_elems, void* stream);
+NVFP4_API int nvfp4_combine_rows(const void* rows, int64_t rows_ld_elems, const int64_t* pos, const float* w,
+                                 int64_t tokens, int k, int hidden, void* y, int64_t y_ld_elems, void* stream);
+
 /* Test hook: Algorithm 1 exactly as the GEMM's transform warps run it (same device
  * code, same shared-memory layouts), with the codes copied out instead of being fed to
  * the tensor cores.  The GEMM itself never writes a quantised activation to global

@@ -28,7 +28,7 @@ TUNE_KEYS = ("tune_block_n", "tune_transform_warps", "tune_epilogue_threads", "t
 
 EXPORTS = ("nvfp4_last_error", "nvfp4_version", "nvfp4_get_num_sms", "nvfp4_set_num_sms",
            "nvfp4_quantize_weight", "nvfp4_quantize_weight_static", "nvfp4_grouped_gemm_contiguous", "nvfp4_debug_decompose",
-           "nvfp4_debug_mma_peak", "nvfp4_debug_mma_pattern")
+           "nvfp4_debug_mma_peak", "nvfp4_debug_mma_pattern", "nvfp4_permute_rows", "nvfp4_swiglu", "nvfp4_combine_rows")
 
 
 def library_path() -> str:
@@ -54,6 +54,9 @@ def lib() -> ctypes.CDLL:
         L.nvfp4_grouped_gemm_contiguous.argtypes = [vp, i64, vp, vp, vp, vp, i64, vp, i32, i32, i32, i32,
                                                     i32, i32, i32, i32, vp, vp, vp]
         L.nvfp4_debug_decompose.argtypes = [vp, i64, i32, i32, i32, vp, vp, vp, vp, vp]
+        L.nvfp4_permute_rows.argtypes = [vp, i64, vp, i32, vp, i64, i32, vp, i64, vp]
+        L.nvfp4_swiglu.argtypes = [vp, i64, i64, i32, vp, i64, vp]
+        L.nvfp4_combine_rows.argtypes = [vp, i64, vp, vp, i64, i32, i32, vp, i64, vp]
         L.nvfp4_debug_mma_peak.argtypes = [i32, ctypes.POINTER(ctypes.c_double), vp]
         L.nvfp4_debug_mma_pattern.argtypes = [i32, i32, i32, i32, i32, ctypes.POINTER(ctypes.c_double), vp]
         _lib = L
@@ -151,6 +154,44 @@ def quantize_weight(w: torch.Tensor):
         _check(lib().nvfp4_quantize_weight(w.data_ptr(), 0 if w.dtype == torch.bfloat16 else 1, e, n, k,
                                            b.data_ptr(), sfb.data_ptr(), gw.data_ptr(), _stream()))
     return b, sfb, gw
+
+
+def _rows_ok(t: torch.Tensor) -> bool:
+    return t.is_cuda and t.dtype == torch.bfloat16 and t.dim() == 2 and t.stride(1) == 1
+
+
+def permute_rows(src: torch.Tensor, n_rows: int, dst: torch.Tensor, src_idx: torch.Tensor = None, src_div: int = 1,
+                 dst_idx: torch.Tensor = None) -> None:
+    """dst[dst_idx[i] or i] = src[(src_idx[i] or i) // src_div] for i < n_rows (BF16 rows, int64 indices)."""
+    _require(_rows_ok(src) and _rows_ok(dst) and src.shape[1] == dst.shape[1], "src and dst are 2-D BF16 CUDA tensors of one width")
+    for idx in (src_idx, dst_idx):
+        _require(idx is None or (idx.is_cuda and idx.dtype == torch.int64 and idx.is_contiguous() and idx.numel() >= n_rows),
+                 "indices are contiguous int64 CUDA tensors with at least n_rows entries")
+    _check(lib().nvfp4_permute_rows(src.data_ptr(), src.stride(0) * 2, src_idx.data_ptr() if src_idx is not None else None,
+                                    src_div, dst_idx.data_ptr() if dst_idx is not None else None, n_rows, src.shape[1] * 2,
+                                    dst.data_ptr(), dst.stride(0) * 2, _stream()))
+
+
+def swiglu(h: torch.Tensor) -> torch.Tensor:
+    """silu(h[:, :I]) * h[:, I:] for a (rows, 2 I) BF16 CUDA tensor."""
+    _require(_rows_ok(h) and h.shape[1] % 16 == 0, "h is a 2-D BF16 CUDA tensor whose width is a multiple of 16")
+    inter = h.shape[1] // 2
+    out = torch.empty(h.shape[0], inter, dtype=torch.bfloat16, device=h.device)
+    _check(lib().nvfp4_swiglu(h.data_ptr(), h.stride(0), h.shape[0], inter, out.data_ptr(), out.stride(0), _stream()))
+    return out
+
+
+def combine_rows(rows: torch.Tensor, pos: torch.Tensor, w: torch.Tensor, tokens: int) -> torch.Tensor:
+    """y[t] = sum_j w[t, j] * rows[pos[t, j]] (FP32 accumulation, ascending j), BF16 out."""
+    _require(_rows_ok(rows), "rows is a 2-D BF16 CUDA tensor")
+    _require(pos.is_cuda and pos.dtype == torch.int64 and pos.is_contiguous() and w.is_cuda and w.dtype == torch.float32 and
+             w.is_contiguous() and pos.numel() == w.numel() and pos.numel() % max(tokens, 1) == 0,
+             "pos (int64) and w (float32) are contiguous CUDA tensors of tokens * k entries")
+    y = torch.empty(tokens, rows.shape[1], dtype=torch.bfloat16, device=rows.device)
+    k = pos.numel() // tokens if tokens else 1
+    _check(lib().nvfp4_combine_rows(rows.data_ptr(), rows.stride(0), pos.data_ptr(), w.data_ptr(), tokens, k, rows.shape[1],
+                                    y.data_ptr(), y.stride(0), _stream()))
+    return y
 
 
 def debug_decompose(a: torch.Tensor, scale_policy: str = "derived_div8"):

@@ -18,6 +18,13 @@ int launch_gemm_split(const void* a, int64_t lda, const void* b, const void* sfb
                       int64_t ldd, const int32_t* m_indices, int M, int N, int K, int E, bool residual,
                       int block_k, int group_m, bool pdl, int num_sms, int32_t* status, cudaStream_t stream);
 
+int launch_permute_rows(const void* src, int64_t src_ld_bytes, const int64_t* src_idx, int src_div, const int64_t* dst_idx,
+                        int64_t n_rows, int row_bytes, void* dst, int64_t dst_ld_bytes, int num_sms, cudaStream_t stream);
+int launch_swiglu(const void* h, int64_t h_ld_elems, int64_t rows, int inter, void* out, int64_t out_ld_elems, int num_sms,
+                  cudaStream_t stream);
+int launch_combine_rows(const void* rows, int64_t rows_ld_elems, const int64_t* pos, const float* w, int64_t tokens, int k,
+                        int hidden, void* y, int64_t y_ld_elems, int num_sms, cudaStream_t stream);
+
 int launch_gemm_swap(const void* a, int64_t lda, const void* b, const void* sfb, const float* gw, void* d,
                      int64_t ldd, const int32_t* m_indices, int M, int N, int K, int E, bool residual,
                      int token_tile, int block_k, int num_sms, int32_t* status, cudaStream_t stream);

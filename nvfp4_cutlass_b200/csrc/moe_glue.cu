@@ -1,0 +1,125 @@
+// Row movers and the activation function of the expert-parallel MoE layer around the grouped GEMM.
+//
+// The grouped GEMM wants its rows expert-major with every group padded to the tile height; tokens arrive
+// token-major with k experts each.  Between the two sit a gather (token rows -> send order), a scatter
+// (received rows -> padded expert-major buffer), SwiGLU between the two GEMMs, and the weighted sum of the k
+// expert outputs of every token.  All four are plain HBM-bound passes over rows of a few KB: one block per
+// row (grid-stride), 16-byte accesses, nothing staged in shared memory.  Written as kernels because the
+// equivalent chains of framework index operations took four times as long as the two GEMMs between them.
+// The reference project has no multi-GPU mode; these have no counterpart there.
+#include <cuda_bf16.h>
+
+#include "host_common.hpp"
+#include "launchers.hpp"
+
+namespace nvfp4 {
+namespace {
+
+// dst[dst_idx ? dst_idx[i] : i] = src[(src_idx ? src_idx[i] : i) / src_div], rows of row16 16-byte words
+__global__ void __launch_bounds__(256)
+permute_rows_kernel(const uint4* __restrict__ src, int64_t src_ld16, const int64_t* __restrict__ src_idx, int src_div,
+                    const int64_t* __restrict__ dst_idx, int64_t n_rows, int row16, uint4* __restrict__ dst, int64_t dst_ld16)
+{
+    for (int64_t i = blockIdx.x; i < n_rows; i += gridDim.x) {
+        const int64_t s = (src_idx ? src_idx[i] : i) / src_div;
+        const int64_t d = dst_idx ? dst_idx[i] : i;
+        const uint4* sp = src + s * src_ld16;
+        uint4* dp = dst + d * dst_ld16;
+        for (int c = threadIdx.x; c < row16; c += blockDim.x) dp[c] = __ldg(sp + c);
+    }
+}
+
+__device__ __forceinline__ float silu(float g) { return g / (1.0f + __expf(-g)); }
+
+// out[r, j] = silu(h[r, j]) * h[r, inter + j], BF16 in and out, products rounded once from FP32
+__global__ void __launch_bounds__(256)
+swiglu_kernel(const uint4* __restrict__ h, int64_t h_ld16, int64_t rows, int inter16, uint4* __restrict__ out, int64_t out_ld16)
+{
+    for (int64_t r = blockIdx.x; r < rows; r += gridDim.x) {
+        const uint4* gate = h + r * h_ld16;
+        const uint4* up = gate + inter16;
+        uint4* o = out + r * out_ld16;
+        for (int c = threadIdx.x; c < inter16; c += blockDim.x) {
+            const uint4 g = __ldg(gate + c), u = __ldg(up + c);
+            const uint32_t gw[4] = {g.x, g.y, g.z, g.w}, uw[4] = {u.x, u.y, u.z, u.w};
+            uint32_t ow[4];
+#pragma unroll
+            for (int i = 0; i < 4; ++i) {
+                const float2 gf = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162*>(&gw[i]));
+                const float2 uf = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162*>(&uw[i]));
+                const __nv_bfloat162 p = __floats2bfloat162_rn(silu(gf.x) * uf.x, silu(gf.y) * uf.y);
+                ow[i] = *reinterpret_cast<const uint32_t*>(&p);
+            }
+            o[c] = make_uint4(ow[0], ow[1], ow[2], ow[3]);
+        }
+    }
+}
+
+// y[t] = sum_j w[t, j] * rows[pos[t * k + j]] in FP32, j ascending (deterministic), BF16 out
+__global__ void __launch_bounds__(256)
+combine_rows_kernel(const uint4* __restrict__ rows, int64_t rows_ld16, const int64_t* __restrict__ pos,
+                    const float* __restrict__ w, int64_t tokens, int k, int row16, uint4* __restrict__ y, int64_t y_ld16)
+{
+    for (int64_t t = blockIdx.x; t < tokens; t += gridDim.x) {
+        for (int c = threadIdx.x; c < row16; c += blockDim.x) {
+            float acc[8] = {0, 0, 0, 0, 0, 0, 0, 0};
+            for (int j = 0; j < k; ++j) {
+                const float wj = __ldg(w + t * k + j);
+                const uint4 v = __ldg(rows + __ldg(pos + t * k + j) * rows_ld16 + c);
+                const uint32_t vw[4] = {v.x, v.y, v.z, v.w};
+#pragma unroll
+                for (int i = 0; i < 4; ++i) {
+                    const float2 f = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162*>(&vw[i]));
+                    acc[2 * i] = fmaf(wj, f.x, acc[2 * i]);
+                    acc[2 * i + 1] = fmaf(wj, f.y, acc[2 * i + 1]);
+                }
+            }
+            uint32_t ow[4];
+#pragma unroll
+            for (int i = 0; i < 4; ++i) {
+                const __nv_bfloat162 p = __floats2bfloat162_rn(acc[2 * i], acc[2 * i + 1]);
+                ow[i] = *reinterpret_cast<const uint32_t*>(&p);
+            }
+            y[t * y_ld16 + c] = make_uint4(ow[0], ow[1], ow[2], ow[3]);
+        }
+    }
+}
+
+unsigned grid_for(int64_t rows, int num_sms)
+{
+    const int64_t cap = static_cast<int64_t>(num_sms) * 8;
+    return static_cast<unsigned>(rows < cap ? (rows > 0 ? rows : 1) : cap);
+}
+
+}  // namespace
+
+int launch_permute_rows(const void* src, int64_t src_ld_bytes, const int64_t* src_idx, int src_div, const int64_t* dst_idx,
+                        int64_t n_rows, int row_bytes, void* dst, int64_t dst_ld_bytes, int num_sms, cudaStream_t stream)
+{
+    permute_rows_kernel<<<grid_for(n_rows, num_sms), 256, 0, stream>>>(
+        static_cast<const uint4*>(src), src_ld_bytes / 16, src_idx, src_div, dst_idx, n_rows, row_bytes / 16,
+        static_cast<uint4*>(dst), dst_ld_bytes / 16);
+    NVFP4_CUDA_CHECK(cudaGetLastError());
+    return NVFP4_OK;
+}
+
+int launch_swiglu(const void* h, int64_t h_ld_elems, int64_t rows, int inter, void* out, int64_t out_ld_elems, int num_sms,
+                  cudaStream_t stream)
+{
+    swiglu_kernel<<<grid_for(rows, num_sms), 256, 0, stream>>>(static_cast<const uint4*>(h), h_ld_elems / 8, rows, inter / 8,
+                                                                static_cast<uint4*>(out), out_ld_elems / 8);
+    NVFP4_CUDA_CHECK(cudaGetLastError());
+    return NVFP4_OK;
+}
+
+int launch_combine_rows(const void* rows, int64_t rows_ld_elems, const int64_t* pos, const float* w, int64_t tokens, int k,
+                        int hidden, void* y, int64_t y_ld_elems, int num_sms, cudaStream_t stream)
+{
+    combine_rows_kernel<<<grid_for(tokens, num_sms), 256, 0, stream>>>(static_cast<const uint4*>(rows), rows_ld_elems / 8, pos, w,
+                                                                        tokens, k, hidden / 8, static_cast<uint4*>(y),
+                                                                        y_ld_elems / 8);
+    NVFP4_CUDA_CHECK(cudaGetLastError());
+    return NVFP4_OK;
+}
+
+}  // namespace nvfp4

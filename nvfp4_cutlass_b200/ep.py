@@ -15,8 +15,10 @@ parallel, and there is one exchange before and one after the two GEMMs:
 The reference project has no multi-GPU mode; this one follows the contiguous-layout
 contract of its GEMM (python/nvfp4_gemm/layout.py:155-169 there: rows grouped by expert,
 group starts aligned).  Collectives go through ``torch.distributed`` (NCCL over NVLink on
-GPUs, gloo in the CPU tests); the routing and permutation logic is plain tensor code and
-runs on either.  The GEMM is injectable so that the CPU tests can stand in a checker.
+GPUs, gloo in the CPU tests).  The routing plan is plain tensor code and runs on either; the
+row movement, SwiGLU and the weighted sum run as CUDA kernels of the library for CUDA tensors
+and as tensor operations for the CPU tests of the host logic.  The GEMM is injectable so that
+the CPU tests can stand in a checker.
 """
 from __future__ import annotations
 
@@ -86,8 +88,11 @@ def _exchange(rows: torch.Tensor, send_counts, recv_counts, group) -> torch.Tens
     return out
 
 
-def swiglu(gate_up: torch.Tensor) -> torch.Tensor:
+def swiglu(gate_up: torch.Tensor, native: bool = True) -> torch.Tensor:
     """silu(gate) * up on the fused (rows, 2*I) up-projection output, BF16 in and out."""
+    if gate_up.is_cuda and native:
+        from . import _C
+        return _C.swiglu(gate_up)
     gate, up = gate_up.float().chunk(2, dim=-1)
     return (torch.nn.functional.silu(gate) * up).to(torch.bfloat16)
 
@@ -101,7 +106,7 @@ class ExpertParallelMoE:
     """
 
     def __init__(self, num_experts: int, hidden: int, inter: int, up, down, group=None, alignment: int = 128,
-                 gemm: Optional[Callable] = None):
+                 gemm: Optional[Callable] = None, native_glue: bool = True):
         self.group = group
         self.world = dist.get_world_size(group) if dist.is_initialized() else 1
         self.rank = dist.get_rank(group) if dist.is_initialized() else 0
@@ -114,14 +119,26 @@ class ExpertParallelMoE:
             from . import _C
             gemm = _C.m_grouped_bf16_dual_nvfp4_gemm_contiguous
         self.gemm = gemm
+        self.native_glue = native_glue         # False: tensor operations even for CUDA tensors (a test's comparison arm)
         self.last = None                       # Dispatch of the most recent call (for accounting)
 
     def dispatch(self, x: torch.Tensor, topk_ids: torch.Tensor):
         k = topk_ids.shape[1]
         plan = plan_dispatch(topk_ids, self.num_experts, self.world, self.alignment, self.group)
+        a = x.new_zeros(plan.rows_padded, x.shape[1])
+        if x.is_cuda and self.native_glue:
+            from . import _C
+            n = plan.order.numel()
+            if self.world > 1:
+                rows = x.new_empty(n, x.shape[1])
+                _C.permute_rows(x, n, rows, src_idx=plan.order, src_div=k)                  # token rows in send order
+                recv = _exchange(rows, plan.send_counts, plan.recv_counts, self.group)
+                _C.permute_rows(recv, recv.shape[0], a, dst_idx=plan.place)                 # into the padded groups
+            else:
+                _C.permute_rows(x, n, a, src_idx=plan.order, src_div=k, dst_idx=plan.place)  # both in one pass
+            return plan, a
         rows = x[plan.order // k]
         recv = _exchange(rows, plan.send_counts, plan.recv_counts, self.group) if self.world > 1 else rows
-        a = x.new_zeros(plan.rows_padded, x.shape[1])
         a[plan.place] = recv
         return plan, a
 
@@ -130,13 +147,25 @@ class ExpertParallelMoE:
         m_indices = make_m_indices(plan.group_sizes, device=a.device, alignment=self.alignment)
         h = torch.empty(a.shape[0], 2 * self.inter, dtype=torch.bfloat16, device=a.device)
         self.gemm(a, *self.up, h, m_indices)
-        act = swiglu(h)
+        act = swiglu(h, native=self.native_glue)
         out = torch.empty(a.shape[0], self.hidden, dtype=torch.bfloat16, device=a.device)
         self.gemm(act, *self.down, out, m_indices)
         return out
 
     def combine(self, out: torch.Tensor, plan: Dispatch, topk_w: torch.Tensor, tokens: int) -> torch.Tensor:
         k = topk_w.shape[1]
+        if out.is_cuda and self.native_glue:
+            from . import _C
+            n = plan.place.numel()
+            inverse = torch.empty_like(plan.order)
+            inverse[plan.order] = torch.arange(plan.order.numel(), device=out.device)      # pair (t, j) -> its row in send order
+            if self.world > 1:
+                rows = out.new_empty(n, out.shape[1])
+                _C.permute_rows(out, n, rows, src_idx=plan.place)
+                back = _exchange(rows, plan.recv_counts, plan.send_counts, self.group)
+                return _C.combine_rows(back, inverse, topk_w.float().contiguous().reshape(-1), tokens)
+            # one rank: row i of the send order sits at place[i] of the expert-major buffer
+            return _C.combine_rows(out, plan.place[inverse], topk_w.float().contiguous().reshape(-1), tokens)
         rows = out[plan.place]
         back = _exchange(rows, plan.recv_counts, plan.send_counts, self.group) if self.world > 1 else rows
         y = torch.zeros(tokens, self.hidden, dtype=torch.float32, device=out.device)

@@ -116,7 +116,7 @@ def run(args, workload: str, world: int, rank: int, local: int) -> None:
                 "e2e": {"value": flops_all / (e2e_max * 1e-3) / 1e12, "unit": "TFLOP/s", "ms_per_step": e2e_max,
                         "h2d_bytes_per_step": x_host.numel() * 2 + ids_host.numel() * 8 + w_host.numel() * 4,
                         "d2h_bytes_per_step": y_host.numel() * 2},
-                "gpu_launches": 2 * steps, "clocks": clocks}
+                "gpu_launches": 4 * steps, "clocks": clocks}
         print(json.dumps(line))
     if world > 1:
         dist.barrier()

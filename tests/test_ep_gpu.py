@@ -1,0 +1,80 @@
+"""GPU tests of the expert-parallel layer's own kernels (row movers, SwiGLU, weighted combine) and of one
+layer step on one rank, against the same computation written with tensor operations."""
+import pytest
+import torch
+
+import nvfp4_gemm
+from nvfp4_cutlass_b200 import _C
+from nvfp4_cutlass_b200.ep import ExpertParallelMoE, route_topk
+
+pytestmark = pytest.mark.gpu
+
+
+@pytest.fixture(scope="module")
+def dev():
+    if not torch.cuda.is_available():
+        pytest.skip("needs a CUDA device")
+    return torch.device("cuda", 0)
+
+
+def rel_l2(a, b):
+    a, b = a.float(), b.float()
+    return float((a - b).norm() / b.norm().clamp_min(1e-30))
+
+
+def test_permute_rows_gather_scatter_and_fused(dev):
+    g = torch.Generator().manual_seed(1)
+    x = torch.randn(37, 264, generator=g).to(torch.bfloat16).to(dev)[:, :256]       # strided rows
+    k, n = 3, 37 * 3
+    order = torch.randperm(n, generator=g).to(dev)
+    place = torch.randperm(200, generator=g)[:n].to(dev)
+    gathered = torch.empty(n, 256, dtype=torch.bfloat16, device=dev)
+    _C.permute_rows(x, n, gathered, src_idx=order, src_div=k)
+    assert torch.equal(gathered, x[order // k])
+    scattered = torch.zeros(200, 256, dtype=torch.bfloat16, device=dev)
+    _C.permute_rows(gathered, n, scattered, dst_idx=place)
+    want = torch.zeros_like(scattered)
+    want[place] = x[order // k]
+    assert torch.equal(scattered, want)
+    fused = torch.zeros_like(scattered)
+    _C.permute_rows(x, n, fused, src_idx=order, src_div=k, dst_idx=place)
+    assert torch.equal(fused, want)
+    _C.permute_rows(x, 0, fused)                                                     # empty: no launch, no error
+
+
+def test_swiglu_matches_tensor_ops(dev):
+    g = torch.Generator().manual_seed(2)
+    h = (torch.randn(300, 512, generator=g) * 3).to(torch.bfloat16).to(dev)
+    got = _C.swiglu(h)
+    gate, up = h.float().chunk(2, dim=-1)
+    want = (torch.nn.functional.silu(gate) * up).to(torch.bfloat16)
+    assert got.shape == want.shape
+    assert rel_l2(got, want) < 2e-3          # same FP32 formula; exp differs in the last bits
+
+
+def test_combine_rows_matches_tensor_ops(dev):
+    g = torch.Generator().manual_seed(3)
+    tokens, k, hidden = 50, 4, 384
+    rows = torch.randn(tokens * k + 9, hidden, generator=g).to(torch.bfloat16).to(dev)
+    pos = torch.randperm(tokens * k + 9, generator=g)[:tokens * k].to(dev)
+    w = torch.rand(tokens * k, generator=g).to(dev)
+    got = _C.combine_rows(rows, pos, w, tokens)
+    want = (rows[pos].float() * w.unsqueeze(1)).reshape(tokens, k, hidden).sum(dim=1).to(torch.bfloat16)
+    assert rel_l2(got, want) < 2e-3
+
+
+def test_layer_step_native_glue_matches_tensor_glue(dev):
+    """One rank, 8 experts: the layer with the library's kernels against the layer with tensor operations
+    around the same GEMM calls."""
+    e, hidden, inter, tokens, k = 8, 512, 256, 640, 2
+    g = torch.Generator().manual_seed(4)
+    up_w = (torch.randn(e, 2 * inter, hidden, generator=g) * 0.05).to(torch.bfloat16).to(dev)
+    down_w = (torch.randn(e, hidden, inter, generator=g) * 0.05).to(torch.bfloat16).to(dev)
+    up, down = nvfp4_gemm.quantize_weight_nvfp4(up_w), nvfp4_gemm.quantize_weight_nvfp4(down_w)
+    x = torch.randn(tokens, hidden, generator=g).to(torch.bfloat16).to(dev)
+    ids, wts = route_topk(torch.randn(tokens, e, generator=g).to(dev), k)
+    native = ExpertParallelMoE(e, hidden, inter, up, down, alignment=128)(x, ids, wts)
+    plain = ExpertParallelMoE(e, hidden, inter, up, down, alignment=128, native_glue=False)(x, ids, wts)
+    torch.cuda.synchronize()
+    assert native.shape == (tokens, hidden) and torch.isfinite(native.float()).all()
+    assert rel_l2(native, plain) < 5e-3
