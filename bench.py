@@ -337,12 +337,41 @@ def main():
         nvfp4_gemm.m_grouped_bf16_dual_nvfp4_gemm_contiguous(case["a"], case["b"], case["sfb"], case["gw"], d,
                                                              case["m_indices"], device_status=status, **case["kw"])
 
+    # which kernels a step launches (mirrors the dispatch in csrc/abi.cu)
+    fused_knobs = any(extra.get(k, 0) for k in ("tune_cluster", "tune_transform_warps", "tune_direct_a"))
+    split_mode = extra.get("tune_split_transform", 0)
+    is_split = (not case["swap"]) and N % 256 == 0 and (split_mode == 1 or (split_mode == 0 and not fused_knobs and N >= 1024))
+    kernels_per_step = 2 if is_split else 1
+    path = ("split: quantize_activation_kernel (Algorithm 1 once per element, into an L2-resident workspace) + "
+            "gemm_split_kernel (block-scaled FP4 GEMM)") if is_split else (
+            "decode: gemm_swap_kernel, Algorithm 1 in the main loop" if case["swap"] else
+            "fused: Algorithm 1 in the main loop of the GEMM kernel")
+
     sampler = ClockSampler(local)
     sampler.start()
     ms, t0, t1 = timed(step, steps, warmup, lambda: None)
     clocks = sampler.stop(t0, t1)
     assert int(status.item()) == 0, "kernel reported a device-side timeout"
     rel, cos = accuracy_sample(case, d, dev)
+
+    # the fused kernel (activations decomposed inside the GEMM main loop, nothing quantised ever written to
+    # global memory) on the same inputs, for comparison with the split default
+    fused = None
+    if is_split and split_mode == 0:
+        fused_kw = dict(case["kw"], tune_split_transform=2)
+
+        def fused_step():
+            nvfp4_gemm.m_grouped_bf16_dual_nvfp4_gemm_contiguous(case["a"], case["b"], case["sfb"], case["gw"], d,
+                                                                 case["m_indices"], device_status=status, **fused_kw)
+
+        f_steps = max(5, min(steps, 50))
+        f_ms, _, _ = timed(fused_step, f_steps, 3, lambda: None)
+        assert int(status.item()) == 0, "kernel reported a device-side timeout"
+        f_rel, f_cos = accuracy_sample(case, d, dev)
+        fused = {"ms_per_step": f_ms, "steps": f_steps, "value": 2.0 * case["real_rows"] * N * K / (f_ms * 1e-3) / 1e12,
+                 "unit": "TFLOP/s", "rel_l2_vs_fp32": f_rel, "cosine_vs_fp32": f_cos, "kernels_per_step": 1,
+                 "note": "tune_split_transform=2: Algorithm 1 inside the GEMM main loop (pair-cluster kernel)"}
+        step()                                    # leave the default path's output in d
 
     logical = 2.0 * case["real_rows"] * N * K
     value = logical / (ms * 1e-3) / 1e12
@@ -395,9 +424,13 @@ def main():
             "dtype": "nvfp4 (e2m1 x ue4m3 block 16), fp32 accumulate, bf16 in/out", "data": "synthetic",
             "config": {"workload": WORKLOADS[workload]["desc"], "name": workload, "M_padded": M, "M_real": case["real_rows"],
                        "N": N, "K": K, "E": case["E"], "passes": 2, "orientation": "swap_ab" if case["swap"] else "normal",
-                       "tune": extra, "l2": "operands larger than L2 (weights %.0f MB), no flush" % (case["b"].numel() / 1e6)},
-            "roofline": roofline, "e2e": e2e, "gpu_launches": steps, "clocks": clocks,
+                       "tune": extra, "path": path, "kernels_per_step": kernels_per_step,
+                       "l2": "operands larger than L2 (weights %.0f MB), no flush" % (case["b"].numel() / 1e6)},
+            "roofline": roofline, "e2e": e2e, "gpu_launches": steps * kernels_per_step, "clocks": clocks,
             "rel_l2_vs_fp32": rel, "cosine_vs_fp32": cos}
+    if fused is not None:
+        fused["roofline_frac"] = 2.0 * fused["value"] / roofline["peak"]
+        line["fused_in_mainloop"] = fused
     if not args.no_cpu_baseline:
         base = cpu_reference_sample(workload)
         line["cpu_baseline"] = {k: base[k] for k in ("value", "unit", "cores", "kind", "sample")}

@@ -135,6 +135,22 @@ NVFP4_API int nvfp4_swiglu(const void* h, int64_t h_ld_elems, int64_t rows, int 
 NVFP4_API int nvfp4_combine_rows(const void* rows, int64_t rows_ld_elems, const int64_t* pos, const float* w,
                                  int64_t tokens, int k, int hidden, void* y, int64_t y_ld_elems, void* stream);
 
+/* The same two steps over peer memory, for ranks on the GPUs of one NVLink domain.  `peers` is a device array
+ * with one int64 per rank: the address, in THIS process, of that rank's copy of a symmetric buffer (rows of
+ * `row_bytes`, stride dst_ld_bytes / rows_ld_elems, the same on every rank).  No counterpart in the reference.
+ *
+ * nvfp4_dispatch_rows_peer: for i < n_rows, row src[src_idx[i] / src_div] is stored into row dst_row[i] of
+ *   rank dst_rank[i]'s buffer (gather + all-to-all + scatter in one pass of plain stores).  The caller orders
+ *   it after every rank has finished reading its buffer and tells the peers when the stores are complete.
+ * nvfp4_combine_rows_peer: y[t] = sum over j < k of w[t*k+j] * (row src_row[t*k+j] of rank src_rank[t*k+j]'s
+ *   buffer), read with plain loads over NVLink.  The caller orders it after every rank has written its buffer. */
+NVFP4_API int nvfp4_dispatch_rows_peer(const void* src, int64_t src_ld_bytes, const int64_t* src_idx, int src_div,
+                                       const int64_t* peers, const int64_t* dst_rank, const int64_t* dst_row,
+                                       int64_t n_rows, int row_bytes, int64_t dst_ld_bytes, void* stream);
+NVFP4_API int nvfp4_combine_rows_peer(const int64_t* peers, int64_t rows_ld_elems, const int64_t* src_rank,
+                                      const int64_t* src_row, const float* w, int64_t tokens, int k, int hidden,
+                                      void* y, int64_t y_ld_elems, void* stream);
+
 /* Test hook: Algorithm 1 exactly as the GEMM's transform warps run it (same device
  * code, same shared-memory layouts), with the codes copied out instead of being fed to
  * the tensor cores.  The GEMM itself never writes a quantised activation to global

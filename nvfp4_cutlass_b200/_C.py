@@ -28,7 +28,8 @@ TUNE_KEYS = ("tune_block_n", "tune_transform_warps", "tune_epilogue_threads", "t
 
 EXPORTS = ("nvfp4_last_error", "nvfp4_version", "nvfp4_get_num_sms", "nvfp4_set_num_sms",
            "nvfp4_quantize_weight", "nvfp4_quantize_weight_static", "nvfp4_grouped_gemm_contiguous", "nvfp4_debug_decompose",
-           "nvfp4_debug_mma_peak", "nvfp4_debug_mma_pattern", "nvfp4_permute_rows", "nvfp4_swiglu", "nvfp4_combine_rows")
+           "nvfp4_debug_mma_peak", "nvfp4_debug_mma_pattern", "nvfp4_permute_rows", "nvfp4_swiglu", "nvfp4_combine_rows",
+           "nvfp4_dispatch_rows_peer", "nvfp4_combine_rows_peer")
 
 
 def library_path() -> str:
@@ -56,6 +57,8 @@ def lib() -> ctypes.CDLL:
         L.nvfp4_debug_decompose.argtypes = [vp, i64, i32, i32, i32, vp, vp, vp, vp, vp]
         L.nvfp4_permute_rows.argtypes = [vp, i64, vp, i32, vp, i64, i32, vp, i64, vp]
         L.nvfp4_swiglu.argtypes = [vp, i64, i64, i32, vp, i64, vp]
+        L.nvfp4_dispatch_rows_peer.argtypes = [vp, i64, vp, i32, vp, vp, vp, i64, i32, i64, vp]
+        L.nvfp4_combine_rows_peer.argtypes = [vp, i64, vp, vp, vp, i64, i32, i32, vp, i64, vp]
         L.nvfp4_combine_rows.argtypes = [vp, i64, vp, vp, i64, i32, i32, vp, i64, vp]
         L.nvfp4_debug_mma_peak.argtypes = [i32, ctypes.POINTER(ctypes.c_double), vp]
         L.nvfp4_debug_mma_pattern.argtypes = [i32, i32, i32, i32, i32, ctypes.POINTER(ctypes.c_double), vp]
@@ -191,6 +194,34 @@ def combine_rows(rows: torch.Tensor, pos: torch.Tensor, w: torch.Tensor, tokens:
     k = pos.numel() // tokens if tokens else 1
     _check(lib().nvfp4_combine_rows(rows.data_ptr(), rows.stride(0), pos.data_ptr(), w.data_ptr(), tokens, k, rows.shape[1],
                                     y.data_ptr(), y.stride(0), _stream()))
+    return y
+
+
+def _i64_ok(t: torch.Tensor, n: int) -> bool:
+    return t.is_cuda and t.dtype == torch.int64 and t.is_contiguous() and t.numel() >= n
+
+
+def dispatch_rows_peer(src: torch.Tensor, src_idx: torch.Tensor, src_div: int, peers: torch.Tensor, dst_rank: torch.Tensor,
+                       dst_row: torch.Tensor, dst_ld_elems: int) -> None:
+    """Row src[src_idx[i] // src_div] -> row dst_row[i] of rank dst_rank[i]'s buffer (`peers`: int64 base addresses)."""
+    n = src_idx.numel()
+    _require(_rows_ok(src), "src is a 2-D BF16 CUDA tensor")
+    _require(_i64_ok(src_idx, n) and _i64_ok(dst_rank, n) and _i64_ok(dst_row, n) and _i64_ok(peers, 1),
+             "indices and peer addresses are contiguous int64 CUDA tensors")
+    _check(lib().nvfp4_dispatch_rows_peer(src.data_ptr(), src.stride(0) * 2, src_idx.data_ptr(), src_div, peers.data_ptr(),
+                                          dst_rank.data_ptr(), dst_row.data_ptr(), n, src.shape[1] * 2, dst_ld_elems * 2, _stream()))
+
+
+def combine_rows_peer(peers: torch.Tensor, rows_ld_elems: int, src_rank: torch.Tensor, src_row: torch.Tensor, w: torch.Tensor,
+                      tokens: int, hidden: int) -> torch.Tensor:
+    """y[t] = sum_j w[t, j] * (row src_row[t, j] of rank src_rank[t, j]'s buffer), BF16 out."""
+    n = src_rank.numel()
+    _require(_i64_ok(src_rank, n) and _i64_ok(src_row, n) and _i64_ok(peers, 1) and w.is_cuda and w.dtype == torch.float32 and
+             w.is_contiguous() and w.numel() == n and n % max(tokens, 1) == 0, "bad index / weight tensors")
+    y = torch.empty(tokens, hidden, dtype=torch.bfloat16, device=w.device)
+    k = n // tokens if tokens else 1
+    _check(lib().nvfp4_combine_rows_peer(peers.data_ptr(), rows_ld_elems, src_rank.data_ptr(), src_row.data_ptr(), w.data_ptr(),
+                                         tokens, k, hidden, y.data_ptr(), y.stride(0), _stream()))
     return y
 
 

@@ -276,6 +276,40 @@ int nvfp4_combine_rows(const void* rows, int64_t rows_ld_elems, const int64_t* p
                                static_cast<cudaStream_t>(stream));
 }
 
+int nvfp4_dispatch_rows_peer(const void* src, int64_t src_ld_bytes, const int64_t* src_idx, int src_div, const int64_t* peers,
+                             const int64_t* dst_rank, const int64_t* dst_row, int64_t n_rows, int row_bytes, int64_t dst_ld_bytes,
+                             void* stream)
+{
+    host::clear_error();
+    NVFP4_REQUIRE(n_rows >= 0 && row_bytes > 0 && row_bytes % 16 == 0, "row_bytes must be a positive multiple of 16 (got %d)", row_bytes);
+    if (n_rows == 0) return NVFP4_OK;
+    NVFP4_REQUIRE(src && src_idx && peers && dst_rank && dst_row, "null pointer argument");
+    NVFP4_REQUIRE(src_div >= 1, "src_div must be at least 1");
+    NVFP4_REQUIRE(src_ld_bytes % 16 == 0 && dst_ld_bytes % 16 == 0 && src_ld_bytes >= row_bytes && dst_ld_bytes >= row_bytes,
+                  "row strides must be multiples of 16 bytes and at least row_bytes");
+    NVFP4_REQUIRE((reinterpret_cast<uintptr_t>(src) & 15u) == 0, "rows must be 16-byte aligned");
+    host::DeviceInfo* dev;
+    if (int rc = host::device_info(-1, &dev)) return rc;
+    return launch_dispatch_rows_peer(src, src_ld_bytes, src_idx, src_div, peers, dst_rank, dst_row, n_rows, row_bytes, dst_ld_bytes,
+                                     dev->hw_sms, static_cast<cudaStream_t>(stream));
+}
+
+int nvfp4_combine_rows_peer(const int64_t* peers, int64_t rows_ld_elems, const int64_t* src_rank, const int64_t* src_row,
+                            const float* w, int64_t tokens, int k, int hidden, void* y, int64_t y_ld_elems, void* stream)
+{
+    host::clear_error();
+    NVFP4_REQUIRE(tokens >= 0 && k >= 1 && hidden > 0 && hidden % 8 == 0, "k >= 1 and hidden a positive multiple of 8 (k=%d, hidden=%d)", k, hidden);
+    if (tokens == 0) return NVFP4_OK;
+    NVFP4_REQUIRE(peers && src_rank && src_row && w && y, "null pointer argument");
+    NVFP4_REQUIRE(rows_ld_elems % 8 == 0 && y_ld_elems % 8 == 0 && rows_ld_elems >= hidden && y_ld_elems >= hidden,
+                  "row strides must be multiples of 8 elements and cover the row");
+    NVFP4_REQUIRE((reinterpret_cast<uintptr_t>(y) & 15u) == 0, "rows must be 16-byte aligned");
+    host::DeviceInfo* dev;
+    if (int rc = host::device_info(-1, &dev)) return rc;
+    return launch_combine_rows_peer(peers, rows_ld_elems, src_rank, src_row, w, tokens, k, hidden, y, y_ld_elems, dev->hw_sms,
+                                    static_cast<cudaStream_t>(stream));
+}
+
 int nvfp4_debug_decompose(const void* a, int64_t lda_elems, int M, int K, int scale_policy, void* q0, void* q1,
                           void* s0, void* s1, void* stream)
 {

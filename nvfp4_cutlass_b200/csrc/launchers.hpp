@@ -25,6 +25,13 @@ int launch_swiglu(const void* h, int64_t h_ld_elems, int64_t rows, int inter, vo
 int launch_combine_rows(const void* rows, int64_t rows_ld_elems, const int64_t* pos, const float* w, int64_t tokens, int k,
                         int hidden, void* y, int64_t y_ld_elems, int num_sms, cudaStream_t stream);
 
+int launch_dispatch_rows_peer(const void* src, int64_t src_ld_bytes, const int64_t* src_idx, int src_div, const int64_t* peers,
+                              const int64_t* dst_rank, const int64_t* dst_row, int64_t n_rows, int row_bytes,
+                              int64_t dst_ld_bytes, int num_sms, cudaStream_t stream);
+int launch_combine_rows_peer(const int64_t* peers, int64_t rows_ld_elems, const int64_t* src_rank, const int64_t* src_row,
+                             const float* w, int64_t tokens, int k, int hidden, void* y, int64_t y_ld_elems, int num_sms,
+                             cudaStream_t stream);
+
 int launch_gemm_swap(const void* a, int64_t lda, const void* b, const void* sfb, const float* gw, void* d,
                      int64_t ldd, const int32_t* m_indices, int M, int N, int K, int E, bool residual,
                      int token_tile, int block_k, int num_sms, int32_t* status, cudaStream_t stream);

@@ -85,6 +85,59 @@ combine_rows_kernel(const uint4* __restrict__ rows, int64_t rows_ld16, const int
     }
 }
 
+// Peer-memory variants for the expert-parallel layer on several GPUs of one NVLink domain.  `peers` holds, per
+// rank, the base address of that rank's copy of a symmetric buffer as mapped into this process.
+//
+// dispatch: row i of the send order (token src_idx[i] / src_div) is stored straight into row dst_row[i] of rank
+// dst_rank[i]'s expert-major buffer -- the gather, the all-to-all and the scatter in one pass, every byte
+// crossing NVLink once as plain 16-byte stores.
+__global__ void __launch_bounds__(256)
+dispatch_rows_peer_kernel(const uint4* __restrict__ src, int64_t src_ld16, const int64_t* __restrict__ src_idx, int src_div,
+                          const int64_t* __restrict__ peers, const int64_t* __restrict__ dst_rank,
+                          const int64_t* __restrict__ dst_row, int64_t n_rows, int row16, int64_t dst_ld16)
+{
+    for (int64_t i = blockIdx.x; i < n_rows; i += gridDim.x) {
+        const uint4* sp = src + (src_idx[i] / src_div) * src_ld16;
+        uint4* dp = reinterpret_cast<uint4*>(peers[dst_rank[i]]) + dst_row[i] * dst_ld16;
+        for (int c = threadIdx.x; c < row16; c += blockDim.x) dp[c] = __ldg(sp + c);
+    }
+}
+
+// combine: y[t] = sum_j w[t, j] * (row src_row[t, j] of rank src_rank[t, j]'s output buffer), read over NVLink
+// with plain loads (the data was written by another GPU during this step: no read-only cache path).
+__global__ void __launch_bounds__(256)
+combine_rows_peer_kernel(const int64_t* __restrict__ peers, int64_t rows_ld16, const int64_t* __restrict__ src_rank,
+                         const int64_t* __restrict__ src_row, const float* __restrict__ w, int64_t tokens, int k, int row16,
+                         uint4* __restrict__ y, int64_t y_ld16)
+{
+    for (int64_t t = blockIdx.x; t < tokens; t += gridDim.x) {
+        for (int c = threadIdx.x; c < row16; c += blockDim.x) {
+            float acc[8] = {0, 0, 0, 0, 0, 0, 0, 0};
+            for (int j = 0; j < k; ++j) {
+                const float wj = w[t * k + j];
+                const uint4* row = reinterpret_cast<const uint4*>(peers[src_rank[t * k + j]]) + src_row[t * k + j] * rows_ld16;
+                uint4 v;
+                asm volatile("ld.global.relaxed.sys.v4.u32 {%0, %1, %2, %3}, [%4];"
+                             : "=r"(v.x), "=r"(v.y), "=r"(v.z), "=r"(v.w) : "l"(row + c) : "memory");
+                const uint32_t vw[4] = {v.x, v.y, v.z, v.w};
+#pragma unroll
+                for (int i = 0; i < 4; ++i) {
+                    const float2 f = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162*>(&vw[i]));
+                    acc[2 * i] = fmaf(wj, f.x, acc[2 * i]);
+                    acc[2 * i + 1] = fmaf(wj, f.y, acc[2 * i + 1]);
+                }
+            }
+            uint32_t ow[4];
+#pragma unroll
+            for (int i = 0; i < 4; ++i) {
+                const __nv_bfloat162 p = __floats2bfloat162_rn(acc[2 * i], acc[2 * i + 1]);
+                ow[i] = *reinterpret_cast<const uint32_t*>(&p);
+            }
+            y[t * y_ld16 + c] = make_uint4(ow[0], ow[1], ow[2], ow[3]);
+        }
+    }
+}
+
 unsigned grid_for(int64_t rows, int num_sms)
 {
     const int64_t cap = static_cast<int64_t>(num_sms) * 8;
@@ -118,6 +171,27 @@ int launch_combine_rows(const void* rows, int64_t rows_ld_elems, const int64_t* 
     combine_rows_kernel<<<grid_for(tokens, num_sms), 256, 0, stream>>>(static_cast<const uint4*>(rows), rows_ld_elems / 8, pos, w,
                                                                         tokens, k, hidden / 8, static_cast<uint4*>(y),
                                                                         y_ld_elems / 8);
+    NVFP4_CUDA_CHECK(cudaGetLastError());
+    return NVFP4_OK;
+}
+
+int launch_dispatch_rows_peer(const void* src, int64_t src_ld_bytes, const int64_t* src_idx, int src_div, const int64_t* peers,
+                              const int64_t* dst_rank, const int64_t* dst_row, int64_t n_rows, int row_bytes,
+                              int64_t dst_ld_bytes, int num_sms, cudaStream_t stream)
+{
+    dispatch_rows_peer_kernel<<<grid_for(n_rows, num_sms), 256, 0, stream>>>(
+        static_cast<const uint4*>(src), src_ld_bytes / 16, src_idx, src_div, peers, dst_rank, dst_row, n_rows, row_bytes / 16,
+        dst_ld_bytes / 16);
+    NVFP4_CUDA_CHECK(cudaGetLastError());
+    return NVFP4_OK;
+}
+
+int launch_combine_rows_peer(const int64_t* peers, int64_t rows_ld_elems, const int64_t* src_rank, const int64_t* src_row,
+                             const float* w, int64_t tokens, int k, int hidden, void* y, int64_t y_ld_elems, int num_sms,
+                             cudaStream_t stream)
+{
+    combine_rows_peer_kernel<<<grid_for(tokens, num_sms), 256, 0, stream>>>(peers, rows_ld_elems / 8, src_rank, src_row, w, tokens,
+                                                                             k, hidden / 8, static_cast<uint4*>(y), y_ld_elems / 8);
     NVFP4_CUDA_CHECK(cudaGetLastError());
     return NVFP4_OK;
 }

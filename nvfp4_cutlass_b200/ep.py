@@ -81,6 +81,71 @@ def plan_dispatch(topk_ids: torch.Tensor, num_experts: int, world: int, alignmen
                     group_sizes=padded.tolist(), real_sizes=per_expert.tolist(), rows_padded=int(padded.sum()))
 
 
+@dataclass
+class PeerDispatch:
+    """Routing plan of the peer-memory path: where every (token, choice) pair lives in its owner's buffer."""
+    order: torch.Tensor          # (T*k,) pair index sorted by global expert id (the send order)
+    dst_rank: torch.Tensor       # (T*k,) owner rank of send-order row i
+    dst_row: torch.Tensor        # (T*k,) its row in the owner's padded expert-major buffer
+    group_sizes: list            # padded rows per local expert
+    real_sizes: list             # real rows per local expert
+    rows_padded: int
+    max_rows_padded: int         # the largest rows_padded over all ranks (capacity check, same on every rank)
+
+
+def plan_dispatch_peer(topk_ids: torch.Tensor, num_experts: int, world: int, rank: int, alignment: int,
+                       group: Optional[dist.ProcessGroup] = None) -> PeerDispatch:
+    """Every rank gathers the whole (source rank, expert) count matrix and from it works out, without a second
+    exchange, the row of each of its pairs in the owner's buffer.  The layout is the one plan_dispatch builds:
+    expert-major, groups padded to the alignment, inside a group the rows of lower source ranks first."""
+    e_local = num_experts // world
+    flat = topk_ids.reshape(-1)
+    order = torch.argsort(flat, stable=True)
+    counts = torch.bincount(flat, minlength=num_experts)
+    if world > 1:
+        gathered = counts.new_empty(world * num_experts)
+        dist.all_gather_into_tensor(gathered, counts.contiguous(), group=group)
+        all_counts = gathered.reshape(world, num_experts)
+    else:
+        all_counts = counts.reshape(1, -1)
+    per_expert = all_counts.sum(dim=0)
+    padded = _pad(per_expert, alignment).reshape(world, e_local)
+    starts = (torch.cumsum(padded, dim=1) - padded).reshape(-1)               # start of each expert in its owner's buffer
+    before = (torch.cumsum(all_counts, dim=0) - all_counts)[rank]             # rows of each expert from lower ranks
+    first = torch.cumsum(counts, 0) - counts                                  # first send-order index of each expert
+    expert_sorted = flat[order]
+    dst_row = (starts + before - first)[expert_sorted] + torch.arange(order.numel(), device=flat.device)
+    dst_rank = torch.div(expert_sorted, e_local, rounding_mode="floor")
+    sizes = torch.stack([padded[rank], per_expert.reshape(world, e_local)[rank],
+                         padded.sum(dim=1).max().expand(e_local)]).tolist()   # the one host synchronisation of a step
+    return PeerDispatch(order=order, dst_rank=dst_rank, dst_row=dst_row, group_sizes=sizes[0], real_sizes=sizes[1],
+                        rows_padded=int(sum(sizes[0])), max_rows_padded=int(sizes[2][0]))
+
+
+class PeerBuffers:
+    """The two symmetric buffers of the peer-memory path (GEMM input rows and GEMM output rows of this rank,
+    mapped into every rank of the group) and their address tables."""
+
+    def __init__(self, rows_cap: int, hidden: int, device: torch.device, group=None):
+        import torch.distributed._symmetric_memory as symm
+        group = group if group is not None else dist.group.WORLD
+        self.rows_cap, self.hidden = rows_cap, hidden
+        self.a = symm.empty(rows_cap, hidden, dtype=torch.bfloat16, device=device)
+        self.out = symm.empty(rows_cap, hidden, dtype=torch.bfloat16, device=device)
+        self._ha = symm.rendezvous(self.a, group)
+        self._ho = symm.rendezvous(self.out, group)
+        self.a.zero_()                      # padding rows are never written by anyone: keep them finite
+        self.out.zero_()
+        self.a_peers = torch.tensor(list(self._ha.buffer_ptrs), dtype=torch.int64, device=device)
+        self.out_peers = torch.tensor(list(self._ho.buffer_ptrs), dtype=torch.int64, device=device)
+        torch.cuda.synchronize(device)
+        self.barrier()
+
+    def barrier(self) -> None:
+        """All ranks of the group, ordered on the current stream."""
+        self._ha.barrier(channel=0)
+
+
 def _exchange(rows: torch.Tensor, send_counts, recv_counts, group) -> torch.Tensor:
     out = rows.new_empty(sum(recv_counts), rows.shape[1])
     dist.all_to_all_single(out, rows.contiguous(), output_split_sizes=recv_counts, input_split_sizes=send_counts,
@@ -106,7 +171,7 @@ class ExpertParallelMoE:
     """
 
     def __init__(self, num_experts: int, hidden: int, inter: int, up, down, group=None, alignment: int = 128,
-                 gemm: Optional[Callable] = None, native_glue: bool = True):
+                 gemm: Optional[Callable] = None, native_glue: bool = True, peer_rows_cap: int = 0):
         self.group = group
         self.world = dist.get_world_size(group) if dist.is_initialized() else 1
         self.rank = dist.get_rank(group) if dist.is_initialized() else 0
@@ -120,6 +185,16 @@ class ExpertParallelMoE:
             gemm = _C.m_grouped_bf16_dual_nvfp4_gemm_contiguous
         self.gemm = gemm
         self.native_glue = native_glue         # False: tensor operations even for CUDA tensors (a test's comparison arm)
+        # peer_rows_cap > 0 on several GPUs: dispatch and combine go through peer memory (one kernel each, stores
+        # into / loads from the owner rank's buffer) instead of staging buffers and NCCL all-to-alls; a step whose
+        # routing would overflow the buffer of some rank falls back to the all-to-all path on every rank
+        self.peer = None
+        self.peer_error = None
+        if peer_rows_cap > 0 and self.world > 1:
+            try:
+                self.peer = PeerBuffers(peer_rows_cap, hidden, torch.device("cuda", torch.cuda.current_device()), group)
+            except Exception as exc:                                   # symmetric memory unavailable: keep the NCCL path
+                self.peer_error = repr(exc)
         self.last = None                       # Dispatch of the most recent call (for accounting)
 
     def dispatch(self, x: torch.Tensor, topk_ids: torch.Tensor):
@@ -172,7 +247,35 @@ class ExpertParallelMoE:
         y.index_add_(0, plan.order // k, back.float() * topk_w.reshape(-1)[plan.order].unsqueeze(1))
         return y.to(torch.bfloat16)
 
+    def forward_peer(self, x: torch.Tensor, topk_ids: torch.Tensor, topk_w: torch.Tensor):
+        """One step over peer memory; returns None (on every rank alike) if the routing does not fit the buffers."""
+        from . import _C
+        from .layout import make_m_indices
+        k = topk_ids.shape[1]
+        plan = plan_dispatch_peer(topk_ids, self.num_experts, self.world, self.rank, self.alignment, self.group)
+        if plan.max_rows_padded > self.peer.rows_cap:
+            return None
+        self.last = plan
+        buf = self.peer
+        buf.barrier()                                   # every rank has finished with the buffers of the previous step
+        _C.dispatch_rows_peer(x, plan.order, k, buf.a_peers, plan.dst_rank, plan.dst_row, self.hidden)
+        buf.barrier()                                   # all rows have landed everywhere
+        a, out = buf.a[:plan.rows_padded], buf.out[:plan.rows_padded]
+        m_indices = make_m_indices(plan.group_sizes, device=a.device, alignment=self.alignment)
+        h = torch.empty(a.shape[0], 2 * self.inter, dtype=torch.bfloat16, device=a.device)
+        self.gemm(a, *self.up, h, m_indices)
+        self.gemm(swiglu(h), *self.down, out, m_indices)
+        buf.barrier()                                   # every rank's expert outputs are complete
+        inverse = torch.empty_like(plan.order)
+        inverse[plan.order] = torch.arange(plan.order.numel(), device=x.device)
+        return _C.combine_rows_peer(buf.out_peers, self.hidden, plan.dst_rank[inverse], plan.dst_row[inverse],
+                                    topk_w.float().contiguous().reshape(-1), x.shape[0], self.hidden)
+
     def forward(self, x: torch.Tensor, topk_ids: torch.Tensor, topk_w: torch.Tensor) -> torch.Tensor:
+        if self.peer is not None and x.is_cuda:
+            y = self.forward_peer(x, topk_ids, topk_w)
+            if y is not None:
+                return y
         plan, a = self.dispatch(x, topk_ids)
         self.last = plan
         out = self.experts(a, plan)

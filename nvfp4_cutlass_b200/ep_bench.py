@@ -44,7 +44,17 @@ def run(args, workload: str, world: int, rank: int, local: int) -> None:
     del z, chi
     logits = torch.randn(tokens, E_TOTAL, generator=torch.Generator(device=dev).manual_seed(30 + rank), device=dev)
     ids, wts = route_topk(logits, TOP_K)
-    layer = ExpertParallelMoE(E_TOTAL, HIDDEN, INTER, up, down, alignment=128)
+    extra = {kv.split('=')[0]: int(kv.split('=')[1]) for kv in getattr(args, "tune", [])}
+    # several GPUs: dispatch and combine over peer memory unless ep_peer=0 asks for the NCCL all-to-all path;
+    # room for 1.5 x the average rows a rank receives (a step that does not fit falls back by itself)
+    use_peer = world > 1 and extra.get("ep_peer", 1) != 0
+    cap = int(1.5 * tokens * TOP_K) + e_local * 128
+    layer = ExpertParallelMoE(E_TOTAL, HIDDEN, INTER, up, down, alignment=128, peer_rows_cap=cap if use_peer else 0)
+    exchange = "nccl all_to_all"
+    if layer.peer is not None:
+        exchange = "peer memory (one dispatch kernel of NVLink stores, one combine kernel of NVLink loads)"
+    elif use_peer:
+        exchange = "nccl all_to_all (symmetric memory unavailable: %s)" % (layer.peer_error or "?")[:200]
 
     def barrier():
         if world > 1:
@@ -58,7 +68,11 @@ def run(args, workload: str, world: int, rank: int, local: int) -> None:
     ms, t0, t1 = bench.timed(step, steps, warmup, barrier)
     clocks = sampler.stop(t0, t1)
 
-    # per-phase device times on this rank (one extra, untimed pass)
+    # per-phase device times on this rank (one extra, untimed pass over the all-to-all path, whose phases are
+    # separate calls)
+    plan, a = layer.dispatch(x, ids)                     # first use of the all-to-all path may set up NCCL channels
+    layer.combine(layer.experts(a, plan), plan, wts, tokens)
+    torch.cuda.synchronize()
     ev = [torch.cuda.Event(enable_timing=True) for _ in range(4)]
     ev[0].record()
     plan, a = layer.dispatch(x, ids)
@@ -70,6 +84,12 @@ def run(args, workload: str, world: int, rank: int, local: int) -> None:
     torch.cuda.synchronize()
     phases = [ev[i].elapsed_time(ev[i + 1]) for i in range(3)]
     real_rows = float(sum(plan.real_sizes))
+    # agreement of the two exchange paths on this rank's tokens
+    peer_vs_a2a = None
+    if layer.peer is not None:
+        y_peer = layer(x, ids, wts)
+        peer_vs_a2a = float((y_peer.float() - y.float()).norm() / y.float().norm().clamp_min(1e-30))
+    del plan, a, out
 
     # end to end: activations and routing come from pinned host memory, the layer output goes back
     x_host, ids_host, w_host = x.cpu().pin_memory(), ids.cpu().pin_memory(), wts.cpu().pin_memory()
@@ -94,6 +114,8 @@ def run(args, workload: str, world: int, rank: int, local: int) -> None:
     else:
         mx, sm = stats, stats
     ms_max, e2e_max, flops_all = float(mx[0]), float(mx[1]), float(sm[2])
+    # kernels of this library per step: 2 GEMMs x (activation quantisation + GEMM), SwiGLU, and the row movers
+    kernels_per_step = 4 + 1 + (2 if (layer.peer is not None or world == 1) else 4)
     if rank == 0:
         fp4_peak = bench.measure_fp4_peak()
         value = flops_all / (ms_max * 1e-3) / 1e12
@@ -105,18 +127,19 @@ def run(args, workload: str, world: int, rank: int, local: int) -> None:
                 "dtype": "nvfp4 (e2m1 x ue4m3 block 16), fp32 accumulate, bf16 in/out", "data": "synthetic",
                 "config": {"workload": f"expert-parallel MoE layer: E={E_TOTAL} over {world} ranks, {TOKENS} tokens/rank, top-{TOP_K}, "
                                        f"up N={2 * INTER} K={HIDDEN}, down N={HIDDEN} K={INTER}", "name": "c5",
-                           "parallelism": f"ep{world}", "l2": "operands larger than L2, no flush",
-                           "step": "dispatch all-to-all, up GEMM, SwiGLU (torch op), down GEMM, combine all-to-all"},
+                           "parallelism": f"ep{world}", "l2": "operands larger than L2, no flush", "exchange": exchange,
+                           "step": "dispatch, up GEMM, SwiGLU kernel, down GEMM, combine"},
                 "roofline": {"bound": "tensor", "achieved": achieved, "peak": fp4_peak, "unit": "TFLOP/s",
                              "frac": achieved / fp4_peak, "traffic": None,
                              "note": "the two grouped GEMMs + SwiGLU glue of rank 0, both NVFP4 passes counted",
                              "peak_source": "resident-operand tcgen05 kind::mxf4nvf4 loop measured in this run"},
-                "phases_ms_max_over_ranks": {"dispatch": float(mx[3]), "experts": gemm_ms, "combine": float(mx[5])},
+                "phases_ms_max_over_ranks_all_to_all_path": {"dispatch": float(mx[3]), "experts": gemm_ms, "combine": float(mx[5])},
+                "peer_vs_all_to_all_rel_l2": peer_vs_a2a,
                 "all_to_all_bytes_per_rank_per_direction": off_rank_bytes,
                 "e2e": {"value": flops_all / (e2e_max * 1e-3) / 1e12, "unit": "TFLOP/s", "ms_per_step": e2e_max,
                         "h2d_bytes_per_step": x_host.numel() * 2 + ids_host.numel() * 8 + w_host.numel() * 4,
                         "d2h_bytes_per_step": y_host.numel() * 2},
-                "gpu_launches": 4 * steps, "clocks": clocks}
+                "gpu_launches": kernels_per_step * steps, "kernels_per_step": kernels_per_step, "clocks": clocks}
         print(json.dumps(line))
     if world > 1:
         dist.barrier()

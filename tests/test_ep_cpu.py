@@ -104,3 +104,48 @@ def test_plan_dispatch_places_rows_by_expert():
     for pos, e in zip(plan.place.tolist(), experts_in_order.tolist()):
         assert 4 * e <= pos < 4 * e + plan.real_sizes[e]
     assert len(set(plan.place.tolist())) == flat.numel()
+
+
+def _peer_plan_worker(rank, world, port, results):
+    """The peer-memory plan against the all-to-all plan: storing every rank's rows at (dst_rank, dst_row) must
+    build, on every owner, exactly the buffer the all-to-all dispatch builds there."""
+    sys.path.insert(0, ROOT)
+    os.environ.update(MASTER_ADDR="127.0.0.1", MASTER_PORT=str(port))
+    dist.init_process_group("gloo", rank=rank, world_size=world)
+    try:
+        from nvfp4_cutlass_b200.ep import ExpertParallelMoE, plan_dispatch_peer, route_topk
+        num_experts, hidden, tokens, top_k, alignment = 8, 32, 24 + 5 * rank, 3, 16
+        g = torch.Generator().manual_seed(7 + rank)
+        x = torch.randn(tokens, hidden, generator=g).to(torch.bfloat16)
+        logits = torch.randn(tokens, num_experts, generator=g)
+        logits[:, 2] = -1e9
+        ids, _ = route_topk(logits, top_k)
+        layer = ExpertParallelMoE(num_experts, hidden, 16, None, None, alignment=alignment, gemm=_oracle_gemm)
+        plan_a2a, a_want = layer.dispatch(x, ids)
+        plan = plan_dispatch_peer(ids, num_experts, world, rank, alignment)
+        rows = x[plan.order // top_k]
+        mine = [None] * world
+        dist.all_gather_object(mine, (plan.dst_rank.tolist(), plan.dst_row.tolist(), rows.float().tolist()))
+        a_got = torch.zeros(plan.rows_padded, hidden, dtype=torch.bfloat16)
+        written = set()
+        for dst_rank, dst_row, r in mine:
+            for dr, row, vals in zip(dst_rank, dst_row, r):
+                if dr == rank:
+                    assert row not in written
+                    written.add(row)
+                    a_got[row] = torch.tensor(vals).to(torch.bfloat16)
+        results[rank] = (torch.equal(a_got, a_want), plan.group_sizes == plan_a2a.group_sizes,
+                         plan.real_sizes == plan_a2a.real_sizes, plan.max_rows_padded >= plan.rows_padded,
+                         len(written) == sum(plan.real_sizes))
+    finally:
+        dist.destroy_process_group()
+
+
+@pytest.mark.parametrize("world", [1, 2])
+def test_peer_plan_builds_the_same_buffers_as_the_all_to_all_plan(world):
+    mgr = mp.Manager()
+    results = mgr.dict()
+    mp.spawn(_peer_plan_worker, args=(world, _free_port(), results), nprocs=world, join=True)
+    assert len(results) == world
+    for rank in range(world):
+        assert all(results[rank]), results[rank]

@@ -78,3 +78,55 @@ def test_layer_step_native_glue_matches_tensor_glue(dev):
     torch.cuda.synchronize()
     assert native.shape == (tokens, hidden) and torch.isfinite(native.float()).all()
     assert rel_l2(native, plain) < 5e-3
+
+
+def _two_rank_worker(rank, world, port, results):
+    import os
+    import torch.distributed as dist
+    os.environ.update(MASTER_ADDR="127.0.0.1", MASTER_PORT=str(port))
+    torch.cuda.set_device(rank)
+    dev = torch.device("cuda", rank)
+    dist.init_process_group("nccl", rank=rank, world_size=world, device_id=dev)
+    try:
+        e, hidden, inter, tokens, k = 8, 512, 256, 384 + 128 * rank, 2
+        e_local = e // world
+        g = torch.Generator().manual_seed(4)
+        up_w = (torch.randn(e, 2 * inter, hidden, generator=g) * 0.05).to(torch.bfloat16)
+        down_w = (torch.randn(e, hidden, inter, generator=g) * 0.05).to(torch.bfloat16)
+        lo = rank * e_local
+        up = nvfp4_gemm.quantize_weight_nvfp4(up_w[lo:lo + e_local].to(dev))
+        down = nvfp4_gemm.quantize_weight_nvfp4(down_w[lo:lo + e_local].to(dev))
+        g = torch.Generator().manual_seed(40 + rank)
+        x = torch.randn(tokens, hidden, generator=g).to(torch.bfloat16).to(dev)
+        ids, wts = route_topk(torch.randn(tokens, e, generator=g).to(dev), k)
+        a2a = ExpertParallelMoE(e, hidden, inter, up, down, alignment=128)
+        peer = ExpertParallelMoE(e, hidden, inter, up, down, alignment=128, peer_rows_cap=4096)
+        y_a2a = a2a(x, ids, wts)
+        ys = [peer(x, ids, wts) for _ in range(3)]            # repeated steps reuse the buffers
+        tiny = ExpertParallelMoE(e, hidden, inter, up, down, alignment=128, peer_rows_cap=128)
+        y_fallback = tiny(x, ids, wts)                        # does not fit: every rank takes the all-to-all path
+        torch.cuda.synchronize()
+        results[rank] = (peer.peer is not None, peer.peer_error, rel_l2(ys[0], y_a2a), rel_l2(ys[2], y_a2a),
+                         rel_l2(y_fallback, y_a2a), bool(torch.isfinite(ys[2].float()).all()))
+    finally:
+        dist.destroy_process_group()
+
+
+def test_two_ranks_peer_memory_path_matches_all_to_all_path():
+    """Two GPUs: dispatch/combine over peer memory against the NCCL all-to-all path, same routing."""
+    if torch.cuda.device_count() < 2:
+        pytest.skip("needs two GPUs")
+    import socket
+    import torch.multiprocessing as mp
+    with socket.socket() as s:
+        s.bind(("127.0.0.1", 0))
+        port = s.getsockname()[1]
+    mgr = mp.Manager()
+    results = mgr.dict()
+    mp.spawn(_two_rank_worker, args=(2, port, results), nprocs=2, join=True)
+    for rank in range(2):
+        has_peer, err, first, third, fallback, finite = results[rank]
+        assert has_peer, err
+        assert finite
+        assert first < 1e-6 and third < 1e-6, (first, third)     # same rows, same kernels, same summation order
+        assert fallback < 1e-6
