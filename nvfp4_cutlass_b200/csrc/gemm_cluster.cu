@@ -67,7 +67,10 @@ struct Cfg {
     static constexpr uint32_t kOffSFA0 = kOffB + kDepthB * kSlotB;
     static constexpr uint32_t kOffSFA1 = kOffSFA0 + kDepthP * kSlotSFA;
     static constexpr uint32_t kOffSFB = kOffSFA1 + kDepthP * kSlotSFA;
-    static constexpr uint32_t kOffBars = kOffSFB + kDepthB * kSlotSFB;
+    // epilogue staging: per warp four output rows of 64 BF16 (128 bytes, padded to 144 against bank conflicts)
+    static constexpr uint32_t kStageRow = 144, kStageWarp = 4 * kStageRow;
+    static constexpr uint32_t kOffStage = kOffSFB + kDepthB * kSlotSFB;
+    static constexpr uint32_t kOffBars = kOffStage + kNumEpiWarps * kStageWarp;
     static constexpr uint32_t kNumBars = 2 * kDepthA + 4 * kDepthP + kDepthB + 2;
     static constexpr uint32_t kSmemAlloc = kOffBars + kNumBars * 8 + 16 + 1024;
     static_assert(kSmemAlloc <= 232448, "shared memory budget");
@@ -344,38 +347,52 @@ gemm_cluster_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_const
             const float g = __ldg(p.gw + e);
             if (!ptx::mbar_wait_impl(tmem_full, acc_phase, abort_flag)) { give_up(1); break; }
             ptx::tcgen05_fence_after_sync();
-            // accumulator lane m = 32 * quad + lane holds token row kRows * (lane / kRun) + kRun * quad + lane % kRun
-            const uint32_t row = m_blk * BM + C::kRows * (lane / C::kRun) + C::kRun * quad + lane % C::kRun;
-            __nv_bfloat16* drow = p.d + static_cast<int64_t>(row) * p.ldd + n_blk * BN + half * (BN / 2);
+            // Accumulator lane m = 32 * quad + lane holds token row kRows * (lane / kRun) + kRun * quad + lane % kRun.
+            // A store instruction should write whole 128-byte lines, but in tensor memory a lane is a row: so 64
+            // columns at a time are packed to BF16 in registers and go, four rows per pass, through a 576-byte
+            // staging area (four lanes write their 128 bytes, the warp reads 16 bytes per lane and stores four
+            // full lines).  One 16-byte store per lane and row cost thousands of partial-line requests per tile
+            // and held up the loads and MMAs of the next tile.
             const uint32_t taddr = tmem_base + ((quad * 32) << 16) + kColAcc + half * (BN / 2);
-            auto emit = [&](const uint32_t (&v)[16], uint32_t c) {
-                uint32_t o[8];
+            const uint32_t stage = smem + C::kOffStage + (warp - kWarpEpi0) * C::kStageWarp;
+            const uint32_t rd = stage + (lane >> 3) * C::kStageRow + (lane & 7u) * 16;
 #pragma unroll
-                for (int i = 0; i < 8; ++i) {
-                    const __nv_bfloat162 h = __floats2bfloat162_rn(__uint_as_float(v[2 * i]) * g, __uint_as_float(v[2 * i + 1]) * g);
-                    o[i] = *reinterpret_cast<const uint32_t*>(&h);
+            for (uint32_t hh = 0; hh < 2; ++hh) {
+                uint32_t o[32];
+#pragma unroll
+                for (uint32_t q = 0; q < 2; ++q) {
+                    uint32_t va[16], vb[16];
+                    ptx::tmem_ld_32x32b_x16(taddr + hh * 64 + q * 32, va);
+                    ptx::tmem_ld_32x32b_x16(taddr + hh * 64 + q * 32 + 16, vb);
+                    ptx::tmem_ld_wait();
+                    if (hh == 1 && q == 1) {
+                        ptx::tcgen05_fence_before_sync();         // everything has left tensor memory
+                        __syncwarp();
+                        if (lane == 0) ptx::mbar_arrive(tmem_empty);
+                    }
+#pragma unroll
+                    for (int i = 0; i < 8; ++i) {
+                        const __nv_bfloat162 h0 = __floats2bfloat162_rn(__uint_as_float(va[2 * i]) * g, __uint_as_float(va[2 * i + 1]) * g);
+                        const __nv_bfloat162 h1 = __floats2bfloat162_rn(__uint_as_float(vb[2 * i]) * g, __uint_as_float(vb[2 * i + 1]) * g);
+                        o[16 * q + i] = *reinterpret_cast<const uint32_t*>(&h0);
+                        o[16 * q + 8 + i] = *reinterpret_cast<const uint32_t*>(&h1);
+                    }
                 }
-                uint4* dst = reinterpret_cast<uint4*>(drow + c);
-                dst[0] = make_uint4(o[0], o[1], o[2], o[3]);
-                dst[1] = make_uint4(o[4], o[5], o[6], o[7]);
-            };
-            uint32_t va[16], vb[16];
-            ptx::tmem_ld_32x32b_x16(taddr, va);
-            ptx::tmem_ld_wait();
+#pragma unroll 1
+                for (uint32_t pass = 0; pass < 8; ++pass) {
+                    if ((lane >> 2) == pass) {
+                        const uint32_t wr = stage + (lane & 3u) * C::kStageRow;
 #pragma unroll
-            for (uint32_t c = 0; c < BN / 2; c += 32) {
-                ptx::tmem_ld_32x32b_x16(taddr + c + 16, vb);
-                emit(va, c);
-                ptx::tmem_ld_wait();
-                if (c + 32 < BN / 2) {
-                    ptx::tmem_ld_32x32b_x16(taddr + c + 32, va);
-                } else {
-                    ptx::tcgen05_fence_before_sync();             // everything has left tensor memory
+                        for (uint32_t c = 0; c < 8; ++c) ptx::sts128(wr + c * 16, o[4 * c], o[4 * c + 1], o[4 * c + 2], o[4 * c + 3]);
+                    }
                     __syncwarp();
-                    if (lane == 0) ptx::mbar_arrive(tmem_empty);
+                    const uint4 v = ptx::lds128(rd);
+                    const uint32_t sl = 4 * pass + (lane >> 3);   // the lane whose row this thread stores a piece of
+                    const uint32_t row = m_blk * BM + C::kRows * (sl / C::kRun) + C::kRun * quad + sl % C::kRun;
+                    *reinterpret_cast<uint4*>(p.d + static_cast<int64_t>(row) * p.ldd + n_blk * BN + half * (BN / 2) + hh * 64 +
+                                              (lane & 7u) * 8) = v;
+                    __syncwarp();
                 }
-                emit(vb, c + 16);
-                if (c + 32 < BN / 2) ptx::tmem_ld_wait();
             }
             acc_phase ^= 1;
         }
@@ -515,15 +532,16 @@ int launch_gemm_cluster(const void* a, int64_t lda, const void* b, const void* s
     p.m = M; p.n = N; p.k = K;
     p.group_m = group_m > 0 ? group_m : 8;
     p.status = status;
-    // transform warps: 16 (one 16-block per thread) for pairs, 8 for quads, unless the caller asks for 8
+    // transform warps: 8 unless the caller asks for 16 (pairs only; measured equally fast, and 8 leave the
+    // epilogue its registers)
     if (cluster == 4)
         return residual ? launch_variant<4, true, 8>(a, lda, b, sfb, M, N, K, E, p, num_sms, stream)
                         : launch_variant<4, false, 8>(a, lda, b, sfb, M, N, K, E, p, num_sms, stream);
-    if (xform_warps == 8)
-        return residual ? launch_variant<2, true, 8>(a, lda, b, sfb, M, N, K, E, p, num_sms, stream)
-                        : launch_variant<2, false, 8>(a, lda, b, sfb, M, N, K, E, p, num_sms, stream);
-    return residual ? launch_variant<2, true, 16>(a, lda, b, sfb, M, N, K, E, p, num_sms, stream)
-                    : launch_variant<2, false, 16>(a, lda, b, sfb, M, N, K, E, p, num_sms, stream);
+    if (xform_warps == 16)
+        return residual ? launch_variant<2, true, 16>(a, lda, b, sfb, M, N, K, E, p, num_sms, stream)
+                        : launch_variant<2, false, 16>(a, lda, b, sfb, M, N, K, E, p, num_sms, stream);
+    return residual ? launch_variant<2, true, 8>(a, lda, b, sfb, M, N, K, E, p, num_sms, stream)
+                    : launch_variant<2, false, 8>(a, lda, b, sfb, M, N, K, E, p, num_sms, stream);
 }
 
 #ifdef NVFP4_PROBE
