@@ -36,6 +36,15 @@ WORKLOADS = {
     "c3down": dict(E=256, N=7168, K=2048, desc="DeepSeek-V3-style prefill down: E=256, 32768 rows Zipf(1.1) padded to 128, N=7168, K=2048"),
     "c4": dict(E=256, N=4096, K=7168, desc="decode: E=256, 64 tokens x top-8 (1-16 rows per active expert, padded to 16), N=4096, K=7168"),
     # reduced copies of c2 / c4 (operands still larger than L2) for profiler captures
+    # the reference's own sweep (benchmarks/bench_moe_forward.py:37-52, bench_decode.py there): Qwen3.5-35B-A3B expert
+    # shapes, 32 local experts, balanced rows per expert; q*4k..32k = 128..1024 rows per expert, qdec* = decode
+    **{f"qup{t}k": dict(E=32, N=1024, K=2048, rows=t * 32, desc=f"reference sweep gate_up: E=32 x {t * 32} rows, N=1024, K=2048")
+       for t in (4, 8, 16, 32)},
+    **{f"qdown{t}k": dict(E=32, N=2048, K=512, rows=t * 32, desc=f"reference sweep down: E=32 x {t * 32} rows, N=2048, K=512")
+       for t in (4, 8, 16, 32)},
+    **{f"qdec{t}": dict(E=32, N=1024, K=2048, decode_tokens=t,
+                        desc=f"reference decode sweep gate_up: {t} tokens x top-8 of 256 experts, 32 local experts, N=1024, K=2048")
+       for t in (16, 32, 128)},
     "c2s": dict(E=8, N=8192, K=4096, desc="reduced c2 for profiling: E=8 x 512 rows, N=8192, K=4096"),
     "c4s": dict(E=64, N=4096, K=7168, desc="reduced c4 for profiling: E=64, 16 tokens x top-8, N=4096, K=7168"),
 }
@@ -118,6 +127,16 @@ def routing_rows(workload: str, E: int, gen: torch.Generator):
         for _ in range(64 if workload == "c4" else 16):     # 64 tokens, 8 distinct experts each
             counts[torch.randperm(E, generator=gen)[:8]] += 1
         real = counts.clamp(max=16).tolist()
+        return real, [((r + 15) // 16) * 16 for r in real], 16, True
+    cfg = WORKLOADS[workload]
+    if "rows" in cfg:
+        real = [cfg["rows"]] * E
+        return real, real, 128, False
+    if "decode_tokens" in cfg:                              # each token picks 8 of 256 experts; 32 of them live here
+        counts = torch.zeros(256, dtype=torch.int64)
+        for _ in range(cfg["decode_tokens"]):
+            counts[torch.randperm(256, generator=gen)[:8]] += 1
+        real = counts[:E].tolist()
         return real, [((r + 15) // 16) * 16 for r in real], 16, True
     raise ValueError(workload)
 
@@ -249,6 +268,35 @@ def run_reference_arm(args):
 
 
 # ----------------------------------------------------------------------------- main arm
+def timed_graph(fn, steps, warmup):
+    """The reference's timing method (benchmarks/bench_moe_forward.py:87-124 there): one call captured into a CUDA
+    graph, replayed back to back; host launch cost is out of the picture and the operands are the same (L2-warm
+    when they fit) on every replay."""
+    for _ in range(warmup):
+        fn()
+    torch.cuda.synchronize()
+    graph = torch.cuda.CUDAGraph()
+    side = torch.cuda.Stream()
+    side.wait_stream(torch.cuda.current_stream())
+    with torch.cuda.stream(side):
+        for _ in range(3):
+            fn()
+    torch.cuda.current_stream().wait_stream(side)
+    with torch.cuda.graph(graph):
+        fn()
+    for _ in range(warmup):
+        graph.replay()
+    torch.cuda.synchronize()
+    s, e = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    t0 = time.time()
+    s.record()
+    for _ in range(steps):
+        graph.replay()
+    e.record()
+    torch.cuda.synchronize()
+    return s.elapsed_time(e) / steps, t0, time.time()
+
+
 def timed(fn, steps, warmup, barrier):
     for _ in range(warmup):
         fn()
@@ -306,6 +354,7 @@ def main():
     ap.add_argument("--workload", default=None, help="c2 (default at 1 GPU), c3up, c3down, c4, c5 (default at >1 GPU)")
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--no-cpu-baseline", action="store_true")
+    ap.add_argument("--graph", action="store_true", help="time CUDA-graph replays of one call (the reference's method)")
     ap.add_argument("--tune", action="append", default=[], help="tune_xxx=int passed to the GEMM call (experiments)")
     args = ap.parse_args()
     if args.impl == "reference":
@@ -349,7 +398,10 @@ def main():
 
     sampler = ClockSampler(local)
     sampler.start()
-    ms, t0, t1 = timed(step, steps, warmup, lambda: None)
+    if args.graph:
+        ms, t0, t1 = timed_graph(step, steps, warmup)
+    else:
+        ms, t0, t1 = timed(step, steps, warmup, lambda: None)
     clocks = sampler.stop(t0, t1)
     assert int(status.item()) == 0, "kernel reported a device-side timeout"
     rel, cos = accuracy_sample(case, d, dev)
@@ -425,7 +477,10 @@ def main():
             "config": {"workload": WORKLOADS[workload]["desc"], "name": workload, "M_padded": M, "M_real": case["real_rows"],
                        "N": N, "K": K, "E": case["E"], "passes": 2, "orientation": "swap_ab" if case["swap"] else "normal",
                        "tune": extra, "path": path, "kernels_per_step": kernels_per_step,
-                       "l2": "operands larger than L2 (weights %.0f MB), no flush" % (case["b"].numel() / 1e6)},
+                       "timing": "CUDA-graph replay of one call" if args.graph else "back-to-back launches",
+                       "l2": ("operands larger than L2 (weights %.0f MB), no flush" if case["b"].numel() > 126e6 else
+                              "weights %.0f MB fit in L2 and are not flushed (the reference's sweep is timed the same way)")
+                             % (case["b"].numel() / 1e6)},
             "roofline": roofline, "e2e": e2e, "gpu_launches": steps * kernels_per_step, "clocks": clocks,
             "rel_l2_vs_fp32": rel, "cosine_vs_fp32": cos}
     if fused is not None:
