@@ -113,18 +113,29 @@ combine_rows_peer_kernel(const int64_t* __restrict__ peers, int64_t rows_ld16, c
     for (int64_t t = blockIdx.x; t < tokens; t += gridDim.x) {
         for (int c = threadIdx.x; c < row16; c += blockDim.x) {
             float acc[8] = {0, 0, 0, 0, 0, 0, 0, 0};
-            for (int j = 0; j < k; ++j) {
-                const float wj = w[t * k + j];
-                const uint4* row = reinterpret_cast<const uint4*>(peers[src_rank[t * k + j]]) + src_row[t * k + j] * rows_ld16;
-                uint4 v;
-                asm volatile("ld.global.relaxed.sys.v4.u32 {%0, %1, %2, %3}, [%4];"
-                             : "=r"(v.x), "=r"(v.y), "=r"(v.z), "=r"(v.w) : "l"(row + c) : "memory");
-                const uint32_t vw[4] = {v.x, v.y, v.z, v.w};
+            // four rows at a time: the loads go out together (a round trip over NVLink is a few microseconds) and
+            // are consumed in order, so the sum stays in ascending j
+            for (int j0 = 0; j0 < k; j0 += 4) {
+                uint4 v[4];
+                float wj[4];
 #pragma unroll
-                for (int i = 0; i < 4; ++i) {
-                    const float2 f = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162*>(&vw[i]));
-                    acc[2 * i] = fmaf(wj, f.x, acc[2 * i]);
-                    acc[2 * i + 1] = fmaf(wj, f.y, acc[2 * i + 1]);
+                for (int u = 0; u < 4; ++u) {
+                    const int j = j0 + u < k ? j0 + u : k - 1;
+                    wj[u] = j0 + u < k ? w[t * k + j] : 0.0f;
+                    const uint4* row = reinterpret_cast<const uint4*>(peers[src_rank[t * k + j]]) + src_row[t * k + j] * rows_ld16;
+                    asm volatile("ld.global.relaxed.sys.v4.u32 {%0, %1, %2, %3}, [%4];"
+                                 : "=r"(v[u].x), "=r"(v[u].y), "=r"(v[u].z), "=r"(v[u].w) : "l"(row + c));
+                }
+#pragma unroll
+                for (int u = 0; u < 4; ++u) {
+                    if (j0 + u >= k) break;
+                    const uint32_t vw[4] = {v[u].x, v[u].y, v[u].z, v[u].w};
+#pragma unroll
+                    for (int i = 0; i < 4; ++i) {
+                        const float2 f = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162*>(&vw[i]));
+                        acc[2 * i] = fmaf(wj[u], f.x, acc[2 * i]);
+                        acc[2 * i + 1] = fmaf(wj[u], f.y, acc[2 * i + 1]);
+                    }
                 }
             }
             uint32_t ow[4];

@@ -247,29 +247,45 @@ class ExpertParallelMoE:
         y.index_add_(0, plan.order // k, back.float() * topk_w.reshape(-1)[plan.order].unsqueeze(1))
         return y.to(torch.bfloat16)
 
-    def forward_peer(self, x: torch.Tensor, topk_ids: torch.Tensor, topk_w: torch.Tensor):
-        """One step over peer memory; returns None (on every rank alike) if the routing does not fit the buffers."""
+    def forward_peer(self, x: torch.Tensor, topk_ids: torch.Tensor, topk_w: torch.Tensor, marks: Optional[list] = None):
+        """One step over peer memory; returns None (on every rank alike) if the routing does not fit the buffers.
+        `marks`, if given, receives a CUDA event after each phase (plan, dispatch, experts, combine)."""
         from . import _C
         from .layout import make_m_indices
+
+        def mark():
+            if marks is not None:
+                ev = torch.cuda.Event(enable_timing=True)
+                ev.record()
+                marks.append(ev)
+
         k = topk_ids.shape[1]
+        mark()
         plan = plan_dispatch_peer(topk_ids, self.num_experts, self.world, self.rank, self.alignment, self.group)
         if plan.max_rows_padded > self.peer.rows_cap:
             return None
         self.last = plan
         buf = self.peer
+        # where pair (t, j) sits: the combine reads it back from there
+        inverse = torch.empty_like(plan.order)
+        inverse[plan.order] = torch.arange(plan.order.numel(), device=x.device)
+        src_rank, src_row = plan.dst_rank[inverse], plan.dst_row[inverse]
+        m_indices = make_m_indices(plan.group_sizes, device=x.device, alignment=self.alignment)
+        mark()
         buf.barrier()                                   # every rank has finished with the buffers of the previous step
         _C.dispatch_rows_peer(x, plan.order, k, buf.a_peers, plan.dst_rank, plan.dst_row, self.hidden)
         buf.barrier()                                   # all rows have landed everywhere
+        mark()
         a, out = buf.a[:plan.rows_padded], buf.out[:plan.rows_padded]
-        m_indices = make_m_indices(plan.group_sizes, device=a.device, alignment=self.alignment)
         h = torch.empty(a.shape[0], 2 * self.inter, dtype=torch.bfloat16, device=a.device)
         self.gemm(a, *self.up, h, m_indices)
         self.gemm(swiglu(h), *self.down, out, m_indices)
+        mark()
         buf.barrier()                                   # every rank's expert outputs are complete
-        inverse = torch.empty_like(plan.order)
-        inverse[plan.order] = torch.arange(plan.order.numel(), device=x.device)
-        return _C.combine_rows_peer(buf.out_peers, self.hidden, plan.dst_rank[inverse], plan.dst_row[inverse],
-                                    topk_w.float().contiguous().reshape(-1), x.shape[0], self.hidden)
+        y = _C.combine_rows_peer(buf.out_peers, self.hidden, src_rank, src_row,
+                                 topk_w.float().contiguous().reshape(-1), x.shape[0], self.hidden)
+        mark()
+        return y
 
     def forward(self, x: torch.Tensor, topk_ids: torch.Tensor, topk_w: torch.Tensor) -> torch.Tensor:
         if self.peer is not None and x.is_cuda:

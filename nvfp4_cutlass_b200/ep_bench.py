@@ -85,10 +85,13 @@ def run(args, workload: str, world: int, rank: int, local: int) -> None:
     phases = [ev[i].elapsed_time(ev[i + 1]) for i in range(3)]
     real_rows = float(sum(plan.real_sizes))
     # agreement of the two exchange paths on this rank's tokens
-    peer_vs_a2a = None
+    peer_vs_a2a, peer_phases = None, None
     if layer.peer is not None:
-        y_peer = layer(x, ids, wts)
+        marks = []
+        y_peer = layer.forward_peer(x, ids, wts, marks)
+        torch.cuda.synchronize()
         peer_vs_a2a = float((y_peer.float() - y.float()).norm() / y.float().norm().clamp_min(1e-30))
+        peer_phases = [marks[i].elapsed_time(marks[i + 1]) for i in range(4)]
     del plan, a, out
 
     # end to end: activations and routing come from pinned host memory, the layer output goes back
@@ -105,7 +108,8 @@ def run(args, workload: str, world: int, rank: int, local: int) -> None:
     e2e_ms, _, _ = bench.timed(e2e_step, max(3, min(steps, 10)), 3, barrier)
 
     flops_rank = 2.0 * real_rows * (2 * INTER * HIDDEN + HIDDEN * INTER)
-    stats = torch.tensor([ms, e2e_ms, flops_rank, phases[0], phases[1], phases[2]], dtype=torch.float64, device=dev)
+    stats = torch.tensor([ms, e2e_ms, flops_rank, phases[0], phases[1], phases[2]] + (peer_phases or [0.0] * 4),
+                         dtype=torch.float64, device=dev)
     if world > 1:
         mx = stats.clone()
         dist.all_reduce(mx, op=dist.ReduceOp.MAX)
@@ -134,6 +138,8 @@ def run(args, workload: str, world: int, rank: int, local: int) -> None:
                              "note": "the two grouped GEMMs + SwiGLU glue of rank 0, both NVFP4 passes counted",
                              "peak_source": "resident-operand tcgen05 kind::mxf4nvf4 loop measured in this run"},
                 "phases_ms_max_over_ranks_all_to_all_path": {"dispatch": float(mx[3]), "experts": gemm_ms, "combine": float(mx[5])},
+                "phases_ms_max_over_ranks_peer_path": ({"plan": float(mx[6]), "dispatch": float(mx[7]), "experts": float(mx[8]),
+                                                        "combine": float(mx[9])} if peer_phases else None),
                 "peer_vs_all_to_all_rel_l2": peer_vs_a2a,
                 "all_to_all_bytes_per_rank_per_direction": off_rank_bytes,
                 "e2e": {"value": flops_all / (e2e_max * 1e-3) / 1e12, "unit": "TFLOP/s", "ms_per_step": e2e_max,

@@ -244,6 +244,68 @@ def test_gemm_split_many_tiles_strided(dev, oracle):
     assert torch.isnan(d_wide[:, n:].float()).all()          # nothing written past the N columns
 
 
+@pytest.mark.parametrize("kw", [dict(tune_split_transform=1), dict(tune_split_transform=2), dict(tune_swap_ab=1, m_alignment=128)],
+                         ids=["split", "fused", "swap_ab"])
+def test_cuda_graph_replay_matches_eager(dev, kw):
+    """One warm-up call, then the call is captured into a CUDA graph (the reference's contract: capturable after a
+    warm-up) and replayed on fresh inputs written into the same buffers."""
+    e, rows, n, k = 2, 256, 1024, 1024
+    a0, w = make_case(e, rows, n, k, seed=31)
+    a1, _ = make_case(e, rows, n, k, seed=32)
+    b, sfb, gw = nvfp4_gemm.quantize_weight_nvfp4(w.to(dev))
+    mi = nvfp4_gemm.make_m_indices([rows] * e).to(dev)
+    a = a0.to(dev).clone()
+    d = torch.empty(e * rows, n, dtype=torch.bfloat16, device=dev)
+
+    def call():
+        nvfp4_gemm.m_grouped_bf16_dual_nvfp4_gemm_contiguous(a, b, sfb, gw, d, mi, **kw)
+
+    call()
+    torch.cuda.synchronize()
+    eager0 = d.clone()
+    side = torch.cuda.Stream()
+    side.wait_stream(torch.cuda.current_stream())
+    with torch.cuda.stream(side):
+        call()
+    torch.cuda.current_stream().wait_stream(side)
+    graph = torch.cuda.CUDAGraph()
+    with torch.cuda.graph(graph):
+        call()
+    d.zero_()
+    graph.replay()
+    torch.cuda.synchronize()
+    assert torch.equal(d, eager0)
+    a.copy_(a1.to(dev))
+    graph.replay()
+    torch.cuda.synchronize()
+    replayed = d.clone()
+    call()
+    torch.cuda.synchronize()
+    assert torch.equal(replayed, d) and not torch.equal(replayed, eager0)
+
+
+def test_split_path_on_two_streams_at_once(dev, oracle):
+    """The split path's workspace is allocated stream-ordered from a pool: calls in flight on two streams must not
+    share it."""
+    e, rows, n, k = 2, 256, 2048, 512
+    cases = [make_case(e, rows, n, k, seed=41 + i) for i in range(2)]
+    quant = [nvfp4_gemm.quantize_weight_nvfp4(w.to(dev)) for _, w in cases]
+    mi = nvfp4_gemm.make_m_indices([rows] * e)
+    streams = [torch.cuda.Stream(), torch.cuda.Stream()]
+    outs = [torch.empty(e * rows, n, dtype=torch.bfloat16, device=dev) for _ in range(2)]
+    acts = [a.to(dev) for a, _ in cases]
+    mid = mi.to(dev)
+    torch.cuda.synchronize()
+    for _ in range(8):
+        for i in range(2):
+            with torch.cuda.stream(streams[i]):
+                nvfp4_gemm.m_grouped_bf16_dual_nvfp4_gemm_contiguous(acts[i], *quant[i], outs[i], mid, tune_split_transform=1)
+    torch.cuda.synchronize()
+    for i in range(2):
+        want = oracle.grouped_gemm(cases[i][0], quant[i][0].cpu(), quant[i][1].cpu(), quant[i][2].cpu(), mi, n)
+        assert rel_l2(outs[i].cpu(), want) < REL_L2_VS_ORACLE
+
+
 def test_gemm_many_tiles_ragged_experts(dev, oracle):
     """More tiles than SMs, ragged expert sizes: every CTA loops over several tiles."""
     sizes = [128, 384, 256, 128, 512, 128, 256, 640]
