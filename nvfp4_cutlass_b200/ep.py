@@ -100,24 +100,26 @@ def plan_dispatch_peer(topk_ids: torch.Tensor, num_experts: int, world: int, ran
     expert-major, groups padded to the alignment, inside a group the rows of lower source ranks first."""
     e_local = num_experts // world
     flat = topk_ids.reshape(-1)
-    order = torch.argsort(flat, stable=True)
-    counts = torch.bincount(flat, minlength=num_experts)
+    # the sizes the host needs come first (histogram without a device synchronisation, one small all-gather, one
+    # read-back); the sort and the index arithmetic are queued behind it and run while the host moves on
+    counts = torch.zeros(num_experts, dtype=torch.int64, device=flat.device).scatter_add_(0, flat, torch.ones_like(flat))
     if world > 1:
         gathered = counts.new_empty(world * num_experts)
-        dist.all_gather_into_tensor(gathered, counts.contiguous(), group=group)
+        dist.all_gather_into_tensor(gathered, counts, group=group)
         all_counts = gathered.reshape(world, num_experts)
     else:
         all_counts = counts.reshape(1, -1)
     per_expert = all_counts.sum(dim=0)
     padded = _pad(per_expert, alignment).reshape(world, e_local)
+    sizes = torch.stack([padded[rank], per_expert.reshape(world, e_local)[rank],
+                         padded.sum(dim=1).max().expand(e_local)]).tolist()   # the one host synchronisation of a step
+    order = torch.argsort(flat, stable=True)
     starts = (torch.cumsum(padded, dim=1) - padded).reshape(-1)               # start of each expert in its owner's buffer
     before = (torch.cumsum(all_counts, dim=0) - all_counts)[rank]             # rows of each expert from lower ranks
     first = torch.cumsum(counts, 0) - counts                                  # first send-order index of each expert
     expert_sorted = flat[order]
     dst_row = (starts + before - first)[expert_sorted] + torch.arange(order.numel(), device=flat.device)
     dst_rank = torch.div(expert_sorted, e_local, rounding_mode="floor")
-    sizes = torch.stack([padded[rank], per_expert.reshape(world, e_local)[rank],
-                         padded.sum(dim=1).max().expand(e_local)]).tolist()   # the one host synchronisation of a step
     return PeerDispatch(order=order, dst_rank=dst_rank, dst_row=dst_row, group_sizes=sizes[0], real_sizes=sizes[1],
                         rows_padded=int(sum(sizes[0])), max_rows_padded=int(sizes[2][0]))
 
