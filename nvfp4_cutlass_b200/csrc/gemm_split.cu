@@ -351,7 +351,7 @@ gemm_split_kernel(const __grid_constant__ CUtensorMap tm_a0, const __grid_consta
             tile_coords(tile, num_m, num_n, p.group_m, m_blk, n_blk);
             const int32_t e = max(0, __ldg(p.m_indices + m_blk * BM));
             const float g = __ldg(p.gw + e);
-            if (!ptx::mbar_wait(tmem_full, acc_phase, abort_flag, pa, 3)) { give_up(1); break; }
+            if (!ptx::mbar_wait_relaxed(tmem_full, acc_phase, abort_flag, 400)) { give_up(1); break; }
             if (warp == kWarpEpi0) NVFP4_TRACE(5, (tile - blockIdx.x) / gridDim.x);
             ptx::tcgen05_fence_after_sync();
             const uint32_t taddr = tmem_base + ((quad * 32) << 16) + C::kColAcc + group * 64;

@@ -69,6 +69,22 @@ NVFP4_DEVICE bool mbar_wait_impl(uint64_t* bar, uint32_t parity, volatile uint32
     }
 }
 
+// The same bounded wait for roles that wait long and need not react within cycles (an epilogue warp waiting
+// for a whole tile): it sleeps between polls, which leaves issue slots and power to the warps that work.
+NVFP4_DEVICE bool mbar_wait_relaxed(uint64_t* bar, uint32_t parity, volatile uint32_t* abort_flag, uint32_t sleep_ns)
+{
+    if (mbar_try_wait(bar, parity)) return true;
+    const long long t0 = clock64();
+    for (;;) {
+#pragma unroll 1
+        for (int i = 0; i < 16; ++i) {
+            __nanosleep(sleep_ns);
+            if (mbar_try_wait(bar, parity)) return true;
+        }
+        if (*abort_flag != 0 || clock64() - t0 > kWaitBudgetCycles) return false;
+    }
+}
+
 // Optional per-site wait accounting for timing studies (NVFP4_PROBE is never defined in
 // the shipped build): waits add their duration to a thread-local counter that the role
 // flushes once, when it leaves its loop.
