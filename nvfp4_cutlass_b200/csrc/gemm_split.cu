@@ -87,7 +87,10 @@ quantize_activation_kernel(const __nv_bfloat16* __restrict__ a, int64_t lda, uin
 // ---------------------------------------------------------------------------------------------------
 // Kernel 2: block-scaled FP4 GEMM over the workspace.
 // ---------------------------------------------------------------------------------------------------
-template <uint32_t BK, bool kResidual>
+// kGroup ring positions share one "free again" barrier and one commit: the operands of a group are requested
+// together but land, and are consumed, one K block at a time, so the first MMAs of a group start while the rest
+// of its bytes are still in flight.
+template <uint32_t BK, bool kResidual, uint32_t kGroup = 1>
 struct Cfg {
     static_assert(BK == 128 || BK == 256, "K block");
     static constexpr uint32_t kAtoms = BK / 64, kPass = kResidual ? 2 : 1;
@@ -104,8 +107,10 @@ struct Cfg {
     static constexpr uint32_t kSfA = 0, kSfB = 4 * kAtoms * kPass, kSfCols = kSfB + 8 * kAtoms;
     static constexpr uint32_t kDepthSmem = (kSmemBudget - 1024 - kNumEpiWarps * 4 * 144) / kStage, kDepthTmem = (kTmemCols - kColSF) / kSfCols;
     static constexpr uint32_t kDepthRaw = kDepthSmem < kDepthTmem ? kDepthSmem : kDepthTmem;
-    static constexpr uint32_t kDepth = kDepthRaw > 8 ? 8 : kDepthRaw;
-    static_assert(kDepth >= 3, "ring too shallow");
+    static constexpr uint32_t kDepthCap = kDepthRaw > 8 ? 8 : kDepthRaw;
+    static constexpr uint32_t kDepth = kDepthCap / kGroup * kGroup;           // whole groups
+    static constexpr uint32_t kNumGroups = kDepth / kGroup;
+    static_assert(kDepth >= 3 && kNumGroups >= 2, "ring too shallow");
     static constexpr uint32_t kOffA = 0;                                       // [kDepth][kPass][kSlotA]
     static constexpr uint32_t kOffB = kOffA + kDepth * kPass * kSlotA;
     static constexpr uint32_t kOffSFA = kOffB + kDepth * kSlotB;
@@ -160,19 +165,19 @@ __device__ __forceinline__ void tile_coords(uint32_t tile, uint32_t num_m, uint3
     n_blk = r / rows;
 }
 
-template <uint32_t BK, bool kResidual>
+template <uint32_t BK, bool kResidual, uint32_t kGroup>
 __global__ void __launch_bounds__(kThreads, 1)
 gemm_split_kernel(const __grid_constant__ CUtensorMap tm_a0, const __grid_constant__ CUtensorMap tm_a1,
                   const __grid_constant__ CUtensorMap tm_b, const __grid_constant__ CUtensorMap tm_sfb, const Params p)
 {
-    using C = Cfg<BK, kResidual>;
+    using C = Cfg<BK, kResidual, kGroup>;
     extern __shared__ uint8_t smem_raw[];
     const uint32_t smem = (ptx::smem_u32(smem_raw) + 1023u) & ~1023u;
     uint8_t* smem_gen = smem_raw + (smem - ptx::smem_u32(smem_raw));
 
     uint64_t* bars = reinterpret_cast<uint64_t*>(smem_gen + C::kOffBars);
     uint64_t* full = bars;                           // operand tiles of a K block have landed (one arrive + bytes)
-    uint64_t* empty = full + C::kDepth;              // the MMAs that read a ring position have retired (one commit)
+    uint64_t* empty = full + C::kDepth;              // [kNumGroups] the MMAs that read a group of ring positions have retired
     uint64_t* sf_in = empty + C::kDepth;             // the scale factors of a K block have landed (they are requested
                                                      // first and are small, so the scale warps finish their copy
                                                      // while the operand tiles are still arriving)
@@ -186,7 +191,7 @@ gemm_split_kernel(const __grid_constant__ CUtensorMap tm_a0, const __grid_consta
     if (threadIdx.x == 0) {
         for (uint32_t i = 0; i < C::kDepth; ++i) {
             ptx::mbar_init(full + i, 1);
-            ptx::mbar_init(empty + i, 1);
+            if (i < C::kNumGroups) ptx::mbar_init(empty + i, 1);
             ptx::mbar_init(sf_in + i, 1);
             ptx::mbar_init(sf_full + i, kNumSfWarps);
         }
@@ -228,7 +233,8 @@ gemm_split_kernel(const __grid_constant__ CUtensorMap tm_a0, const __grid_consta
                 const int32_t e = max(0, __ldg(p.m_indices + m_blk * BM));
                 const uint8_t* sfa_row = p.sfa + static_cast<uint64_t>(m_blk) * (p.k / 64) * (C::kPass * 512);
                 for (uint32_t kb = 0; kb < num_kb; ++kb) {
-                    if (!ptx::mbar_wait(empty + r.slot, r.phase ^ 1, abort_flag, pa, 0)) { give_up(1); break; }
+                    if (r.slot % kGroup == 0 &&
+                        !ptx::mbar_wait(empty + r.slot / kGroup, r.phase ^ 1, abort_flag, pa, 0)) { give_up(1); break; }
                     NVFP4_TRACE(0, (tile - blockIdx.x) / gridDim.x * num_kb + kb);
                     ptx::mbar_arrive_expect_tx(sf_in + r.slot, C::kSlotSFA + C::kSlotSFB);
                     ptx::tma_load_2d(smem_gen + C::kOffSFB + r.slot * C::kSlotSFB, &tm_sfb, sf_in + r.slot, n_blk * BN,
@@ -249,7 +255,8 @@ gemm_split_kernel(const __grid_constant__ CUtensorMap tm_a0, const __grid_consta
     } else if (warp == kWarpMma) {
         // ================= MMA issue: one wait, 2 x kAtoms (x passes) MMAs, one commit per K block =================
         Ring r;
-        uint32_t acc_phase = 0, prev_slot = 0;
+        uint32_t acc_phase = 0;
+        int32_t pending = -1;                       // group whose commit is still to be issued
         constexpr uint32_t idesc = ptx::make_idesc_nvf4(BM, BN);
         for (uint32_t tile = blockIdx.x; tile < num_tiles && ok; tile += gridDim.x) {
             if (!ptx::mbar_wait(tmem_empty, acc_phase ^ 1, abort_flag, pa, 0)) { give_up(1); break; }
@@ -276,18 +283,19 @@ gemm_split_kernel(const __grid_constant__ CUtensorMap tm_a0, const __grid_consta
                         // A commit holds this thread until the MMAs before it have been handed to the tensor pipe.
                         // Issued at the end of a K block it would leave the pipe with nothing queued while this
                         // thread finds the next K block; issued after the first atom of the NEXT block it costs the
-                        // ring position a few hundred cycles but the pipe keeps its queue.
-                        if (a == 0 && kb != 0) ptx::tcgen05_commit(empty + prev_slot);
+                        // ring positions a few hundred cycles but the pipe keeps its queue.
+                        if (a == 0 && pending >= 0) ptx::tcgen05_commit(empty + pending);
                     }
                     const long long pt2 = ptx::probe_clock();
                     ptx::probe_count(pa, 5, pt2 - pt1);
                     if (kb == num_kb - 1) {
-                        ptx::tcgen05_commit(empty + r.slot);
+                        if (r.slot % kGroup == kGroup - 1) ptx::tcgen05_commit(empty + r.slot / kGroup);
                         ptx::tcgen05_commit(tmem_full);
                     }
                     ptx::probe_count(pa, 6, ptx::probe_clock() - pt2);
                 }
-                prev_slot = r.slot;
+                // a group is complete with its last ring position; at a tile end it has been committed above
+                pending = (r.slot % kGroup == kGroup - 1 && kb != num_kb - 1) ? static_cast<int32_t>(r.slot / kGroup) : -1;
                 NVFP4_TRACE(4, (tile - blockIdx.x) / gridDim.x * num_kb + kb);
                 __syncwarp();
                 r.advance<C::kDepth>();
@@ -437,11 +445,11 @@ int workspace_pool(int dev, cudaMemPool_t* out)
     return NVFP4_OK;
 }
 
-template <uint32_t BK, bool kResidual>
+template <uint32_t BK, bool kResidual, uint32_t kGroup>
 int launch_variant(const void* a, int64_t lda, const void* b, const void* sfb, int M, int N, int K, int E, Params p,
                    bool pdl, int num_sms, cudaStream_t stream)
 {
-    using C = Cfg<BK, kResidual>;
+    using C = Cfg<BK, kResidual, kGroup>;
     int dev = 0;
     NVFP4_CUDA_CHECK(cudaGetDevice(&dev));
     cudaMemPool_t pool;
@@ -479,7 +487,7 @@ int launch_variant(const void* a, int64_t lda, const void* b, const void* sfb, i
     if (cudaError_t err = cudaGetLastError(); err != cudaSuccess)
         return release(host::fail(NVFP4_E_CUDA, "activation quantisation launch failed: %s", cudaGetErrorString(err)));
 
-    auto kernel = gemm_split_kernel<BK, kResidual>;
+    auto kernel = gemm_split_kernel<BK, kResidual, kGroup>;
     static bool attr_set[host::kMaxDevices] = {};
     if (!attr_set[dev]) {
         if (cudaError_t err = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, C::kSmemAlloc);
@@ -519,11 +527,16 @@ int launch_gemm_split(const void* a, int64_t lda, const void* b, const void* sfb
     p.m = M; p.n = N; p.k = K;
     p.group_m = group_m > 0 ? group_m : 8;
     p.status = status;
+    // block_k: 0 = the library's choice, 256 = one 256-wide K block per ring position, 128 = 128-wide with a commit
+    // per position, 130 = 128-wide in groups of two (requested and freed together, consumed one by one)
+    if (block_k == 130)
+        return residual ? launch_variant<128, true, 2>(a, lda, b, sfb, M, N, K, E, p, pdl, num_sms, stream)
+                        : launch_variant<128, false, 2>(a, lda, b, sfb, M, N, K, E, p, pdl, num_sms, stream);
     if (K % 256 == 0 && block_k != 128)
-        return residual ? launch_variant<256, true>(a, lda, b, sfb, M, N, K, E, p, pdl, num_sms, stream)
-                        : launch_variant<256, false>(a, lda, b, sfb, M, N, K, E, p, pdl, num_sms, stream);
-    return residual ? launch_variant<128, true>(a, lda, b, sfb, M, N, K, E, p, pdl, num_sms, stream)
-                    : launch_variant<128, false>(a, lda, b, sfb, M, N, K, E, p, pdl, num_sms, stream);
+        return residual ? launch_variant<256, true, 1>(a, lda, b, sfb, M, N, K, E, p, pdl, num_sms, stream)
+                        : launch_variant<256, false, 1>(a, lda, b, sfb, M, N, K, E, p, pdl, num_sms, stream);
+    return residual ? launch_variant<128, true, 1>(a, lda, b, sfb, M, N, K, E, p, pdl, num_sms, stream)
+                    : launch_variant<128, false, 1>(a, lda, b, sfb, M, N, K, E, p, pdl, num_sms, stream);
 }
 
 #ifdef NVFP4_PROBE

@@ -204,7 +204,7 @@ def test_gemm_cluster_matches_oracle(dev, oracle, shape, residual, cluster):
 @pytest.mark.parametrize("shape", [(1, 128, 256, 128), (1, 128, 512, 1024), (4, 256, 1024, 2048), (3, 256, 2048, 640),
                                    (2, 384, 768, 256)])
 @pytest.mark.parametrize("residual", [True, False])
-@pytest.mark.parametrize("block_k", [0, 128])
+@pytest.mark.parametrize("block_k", [0, 128, 130])
 def test_gemm_split_matches_oracle(dev, oracle, shape, residual, block_k):
     """tune_split_transform=1: the activations are quantised once by a kernel of their own and the GEMM reads
     codes and scale atoms from the workspace; short and long K, K that only the 128-wide block divides,
