@@ -139,11 +139,21 @@ NVFP4_API int nvfp4_combine_rows(const void* rows, int64_t rows_ld_elems, const 
  * with one int64 per rank: the address, in THIS process, of that rank's copy of a symmetric buffer (rows of
  * `row_bytes`, stride dst_ld_bytes / rows_ld_elems, the same on every rank).  No counterpart in the reference.
  *
- * nvfp4_dispatch_rows_peer: for i < n_rows, row src[src_idx[i] / src_div] is stored into row dst_row[i] of
+ * nvfp4_dispatch_rows_peer: for i < n_rows, row src[(src_idx ? src_idx[i] : i) / src_div] is stored into row dst_row[i] of
  *   rank dst_rank[i]'s buffer (gather + all-to-all + scatter in one pass of plain stores).  The caller orders
  *   it after every rank has finished reading its buffer and tells the peers when the stores are complete.
  * nvfp4_combine_rows_peer: y[t] = sum over j < k of w[t*k+j] * (row src_row[t*k+j] of rank src_rank[t*k+j]'s
- *   buffer), read with plain loads over NVLink.  The caller orders it after every rank has written its buffer. */
+ *   buffer), read with plain loads over NVLink.  The caller orders it after every rank has written its buffer.
+ *
+ * nvfp4_plan_peer: the routing plan of that path.  all_counts[s * E + e] = pairs rank s routes to expert e (the
+ *   all-gathered histograms), ids[p] = expert of this rank's pair p (p = token * k + choice), n pairs.  Writes
+ *   base[e] (E entries: the row of the owner's buffer where this rank's rows of expert e start), sizes
+ *   (2 * E / world + 1 entries: padded rows per local expert, real rows per local expert, the largest padded total
+ *   over all ranks) and dst_row[p] (n entries: base[e] + the number of earlier pairs of this rank routed to e).
+ *   Experts are padded to `alignment` rows; E % world == 0, E <= 4096. */
+NVFP4_API int nvfp4_plan_peer(const int64_t* all_counts, int world, int num_experts, int rank, int alignment,
+                              const int64_t* ids, int64_t n, int64_t* base, int64_t* sizes, int64_t* dst_row,
+                              void* stream);
 NVFP4_API int nvfp4_dispatch_rows_peer(const void* src, int64_t src_ld_bytes, const int64_t* src_idx, int src_div,
                                        const int64_t* peers, const int64_t* dst_rank, const int64_t* dst_row,
                                        int64_t n_rows, int row_bytes, int64_t dst_ld_bytes, void* stream);

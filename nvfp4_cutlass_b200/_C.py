@@ -29,7 +29,7 @@ TUNE_KEYS = ("tune_block_n", "tune_transform_warps", "tune_epilogue_threads", "t
 EXPORTS = ("nvfp4_last_error", "nvfp4_version", "nvfp4_get_num_sms", "nvfp4_set_num_sms",
            "nvfp4_quantize_weight", "nvfp4_quantize_weight_static", "nvfp4_grouped_gemm_contiguous", "nvfp4_debug_decompose",
            "nvfp4_debug_mma_peak", "nvfp4_debug_mma_pattern", "nvfp4_permute_rows", "nvfp4_swiglu", "nvfp4_combine_rows",
-           "nvfp4_dispatch_rows_peer", "nvfp4_combine_rows_peer")
+           "nvfp4_dispatch_rows_peer", "nvfp4_combine_rows_peer", "nvfp4_plan_peer")
 
 
 def library_path() -> str:
@@ -58,6 +58,7 @@ def lib() -> ctypes.CDLL:
         L.nvfp4_permute_rows.argtypes = [vp, i64, vp, i32, vp, i64, i32, vp, i64, vp]
         L.nvfp4_swiglu.argtypes = [vp, i64, i64, i32, vp, i64, vp]
         L.nvfp4_dispatch_rows_peer.argtypes = [vp, i64, vp, i32, vp, vp, vp, i64, i32, i64, vp]
+        L.nvfp4_plan_peer.argtypes = [vp, i32, i32, i32, i32, vp, i64, vp, vp, vp, vp]
         L.nvfp4_combine_rows_peer.argtypes = [vp, i64, vp, vp, vp, i64, i32, i32, vp, i64, vp]
         L.nvfp4_combine_rows.argtypes = [vp, i64, vp, vp, i64, i32, i32, vp, i64, vp]
         L.nvfp4_debug_mma_peak.argtypes = [i32, ctypes.POINTER(ctypes.c_double), vp]
@@ -201,14 +202,30 @@ def _i64_ok(t: torch.Tensor, n: int) -> bool:
     return t.is_cuda and t.dtype == torch.int64 and t.is_contiguous() and t.numel() >= n
 
 
-def dispatch_rows_peer(src: torch.Tensor, src_idx: torch.Tensor, src_div: int, peers: torch.Tensor, dst_rank: torch.Tensor,
+def plan_peer(all_counts: torch.Tensor, ids: torch.Tensor, world: int, rank: int, alignment: int):
+    """Routing plan of the peer-memory path from the all-gathered (rank, expert) histograms; returns
+    (sizes, dst_row): sizes = int64 tensor [padded rows per local expert..., real rows per local expert...,
+    largest padded total over the ranks], dst_row[p] = row of pair p in its owner's buffer."""
+    num_experts = all_counts.numel() // world
+    _require(_i64_ok(all_counts, world * num_experts) and _i64_ok(ids, ids.numel()), "counts and ids are contiguous int64 CUDA tensors")
+    base = torch.empty(num_experts, dtype=torch.int64, device=ids.device)
+    sizes = torch.empty(2 * (num_experts // world) + 1, dtype=torch.int64, device=ids.device)
+    dst_row = torch.empty(ids.numel(), dtype=torch.int64, device=ids.device)
+    _check(lib().nvfp4_plan_peer(all_counts.data_ptr(), world, num_experts, rank, alignment, ids.data_ptr(), ids.numel(),
+                                 base.data_ptr(), sizes.data_ptr(), dst_row.data_ptr(), _stream()))
+    return sizes, dst_row
+
+
+def dispatch_rows_peer(src: torch.Tensor, src_idx, src_div: int, peers: torch.Tensor, dst_rank: torch.Tensor,
                        dst_row: torch.Tensor, dst_ld_elems: int) -> None:
-    """Row src[src_idx[i] // src_div] -> row dst_row[i] of rank dst_rank[i]'s buffer (`peers`: int64 base addresses)."""
-    n = src_idx.numel()
+    """Row src[(src_idx[i] or i) // src_div] -> row dst_row[i] of rank dst_rank[i]'s buffer (`peers`: int64 base
+    addresses)."""
+    n = dst_row.numel()
     _require(_rows_ok(src), "src is a 2-D BF16 CUDA tensor")
-    _require(_i64_ok(src_idx, n) and _i64_ok(dst_rank, n) and _i64_ok(dst_row, n) and _i64_ok(peers, 1),
+    _require((src_idx is None or _i64_ok(src_idx, n)) and _i64_ok(dst_rank, n) and _i64_ok(dst_row, n) and _i64_ok(peers, 1),
              "indices and peer addresses are contiguous int64 CUDA tensors")
-    _check(lib().nvfp4_dispatch_rows_peer(src.data_ptr(), src.stride(0) * 2, src_idx.data_ptr(), src_div, peers.data_ptr(),
+    _check(lib().nvfp4_dispatch_rows_peer(src.data_ptr(), src.stride(0) * 2, src_idx.data_ptr() if src_idx is not None else None,
+                                          src_div, peers.data_ptr(),
                                           dst_rank.data_ptr(), dst_row.data_ptr(), n, src.shape[1] * 2, dst_ld_elems * 2, _stream()))
 
 

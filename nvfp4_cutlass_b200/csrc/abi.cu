@@ -276,6 +276,18 @@ int nvfp4_combine_rows(const void* rows, int64_t rows_ld_elems, const int64_t* p
                                static_cast<cudaStream_t>(stream));
 }
 
+int nvfp4_plan_peer(const int64_t* all_counts, int world, int num_experts, int rank, int alignment, const int64_t* ids, int64_t n,
+                    int64_t* base, int64_t* sizes, int64_t* dst_row, void* stream)
+{
+    host::clear_error();
+    NVFP4_REQUIRE(world >= 1 && num_experts >= 1 && num_experts <= 4096 && num_experts % world == 0,
+                  "num_experts (%d) must be in [1, 4096] and a multiple of world (%d)", num_experts, world);
+    NVFP4_REQUIRE(rank >= 0 && rank < world && alignment >= 1 && n >= 0, "bad rank / alignment / pair count");
+    NVFP4_REQUIRE(all_counts && base && sizes && (n == 0 || (ids && dst_row)), "null pointer argument");
+    return launch_plan_peer(all_counts, world, num_experts, rank, alignment, ids, n, base, sizes, dst_row,
+                            static_cast<cudaStream_t>(stream));
+}
+
 int nvfp4_dispatch_rows_peer(const void* src, int64_t src_ld_bytes, const int64_t* src_idx, int src_div, const int64_t* peers,
                              const int64_t* dst_rank, const int64_t* dst_row, int64_t n_rows, int row_bytes, int64_t dst_ld_bytes,
                              void* stream)
@@ -283,7 +295,7 @@ int nvfp4_dispatch_rows_peer(const void* src, int64_t src_ld_bytes, const int64_
     host::clear_error();
     NVFP4_REQUIRE(n_rows >= 0 && row_bytes > 0 && row_bytes % 16 == 0, "row_bytes must be a positive multiple of 16 (got %d)", row_bytes);
     if (n_rows == 0) return NVFP4_OK;
-    NVFP4_REQUIRE(src && src_idx && peers && dst_rank && dst_row, "null pointer argument");
+    NVFP4_REQUIRE(src && peers && dst_rank && dst_row, "null pointer argument");
     NVFP4_REQUIRE(src_div >= 1, "src_div must be at least 1");
     NVFP4_REQUIRE(src_ld_bytes % 16 == 0 && dst_ld_bytes % 16 == 0 && src_ld_bytes >= row_bytes && dst_ld_bytes >= row_bytes,
                   "row strides must be multiples of 16 bytes and at least row_bytes");

@@ -97,7 +97,7 @@ dispatch_rows_peer_kernel(const uint4* __restrict__ src, int64_t src_ld16, const
                           const int64_t* __restrict__ dst_row, int64_t n_rows, int row16, int64_t dst_ld16)
 {
     for (int64_t i = blockIdx.x; i < n_rows; i += gridDim.x) {
-        const uint4* sp = src + (src_idx[i] / src_div) * src_ld16;
+        const uint4* sp = src + ((src_idx ? src_idx[i] : i) / src_div) * src_ld16;
         uint4* dp = reinterpret_cast<uint4*>(peers[dst_rank[i]]) + dst_row[i] * dst_ld16;
         for (int c = threadIdx.x; c < row16; c += blockDim.x) dp[c] = __ldg(sp + c);
     }
@@ -149,6 +149,79 @@ combine_rows_peer_kernel(const int64_t* __restrict__ peers, int64_t rows_ld16, c
     }
 }
 
+// Routing plan of the peer-memory path, from the gathered (source rank, expert) count matrix.
+//
+// plan_offsets (one block): for every global expert e, base[e] = the row of the owner's padded expert-major
+// buffer at which THIS rank's rows of e start (groups padded to `alignment`, inside a group the rows of lower
+// source ranks first); sizes[0..e_local) = padded rows of this rank's experts, sizes[e_local..2 e_local) their
+// real rows, sizes[2 e_local] = the largest padded total over all ranks (for the capacity check).
+__global__ void __launch_bounds__(1024)
+plan_offsets_kernel(const int64_t* __restrict__ all_counts, int world, int num_experts, int rank, int alignment,
+                    int64_t* __restrict__ base, int64_t* __restrict__ sizes)
+{
+    extern __shared__ int64_t sh[];                 // padded[num_experts], then per-rank totals[world]
+    int64_t* padded = sh;
+    int64_t* totals = sh + num_experts;
+    const int e_local = num_experts / world;
+    for (int e = threadIdx.x; e < num_experts; e += blockDim.x) {
+        int64_t total = 0, before = 0;
+        for (int s = 0; s < world; ++s) {
+            const int64_t c = all_counts[static_cast<int64_t>(s) * num_experts + e];
+            if (s < rank) before += c;
+            total += c;
+        }
+        padded[e] = (total + alignment - 1) / alignment * alignment;
+        base[e] = before;                           // the start of the expert's group is added below
+        if (e / e_local == rank) {
+            sizes[e % e_local] = padded[e];
+            sizes[e_local + e % e_local] = total;
+        }
+    }
+    __syncthreads();
+    for (int r = threadIdx.x; r < world; r += blockDim.x) {       // exclusive scan of the padded groups of each owner
+        int64_t run = 0;
+        for (int j = 0; j < e_local; ++j) {
+            const int e = r * e_local + j;
+            base[e] += run;
+            run += padded[e];
+        }
+        totals[r] = run;
+    }
+    __syncthreads();
+    if (threadIdx.x == 0) {
+        int64_t mx = 0;
+        for (int r = 0; r < world; ++r) mx = totals[r] > mx ? totals[r] : mx;
+        sizes[2 * e_local] = mx;
+    }
+}
+
+// plan_rows (one block per expert): dst_row[p] = base[e] + (number of pairs p' < p routed to e), for every pair p
+// routed to e -- a stable counting sort without the sort: pairs keep their order inside an expert's group.
+__global__ void __launch_bounds__(1024)
+plan_rows_kernel(const int64_t* __restrict__ ids, int64_t n, const int64_t* __restrict__ base, int64_t* __restrict__ dst_row)
+{
+    __shared__ int warp_tot[32];
+    const int e = blockIdx.x, lane = threadIdx.x & 31, wid = threadIdx.x >> 5;
+    int64_t running = base[e];
+    for (int64_t chunk = 0; chunk < n; chunk += blockDim.x) {
+        const int64_t p = chunk + threadIdx.x;
+        const bool mine = p < n && ids[p] == e;
+        const unsigned ballot = __ballot_sync(0xffffffffu, mine);
+        const int lane_rank = __popc(ballot & ((1u << lane) - 1u));
+        if (lane == 0) warp_tot[wid] = __popc(ballot);
+        __syncthreads();
+        int before = 0, total = 0;
+        for (int w = 0; w < static_cast<int>(blockDim.x >> 5); ++w) {
+            const int c = warp_tot[w];
+            before += w < wid ? c : 0;
+            total += c;
+        }
+        if (mine) dst_row[p] = running + before + lane_rank;
+        running += total;
+        __syncthreads();
+    }
+}
+
 unsigned grid_for(int64_t rows, int num_sms)
 {
     const int64_t cap = static_cast<int64_t>(num_sms) * 8;
@@ -182,6 +255,17 @@ int launch_combine_rows(const void* rows, int64_t rows_ld_elems, const int64_t* 
     combine_rows_kernel<<<grid_for(tokens, num_sms), 256, 0, stream>>>(static_cast<const uint4*>(rows), rows_ld_elems / 8, pos, w,
                                                                         tokens, k, hidden / 8, static_cast<uint4*>(y),
                                                                         y_ld_elems / 8);
+    NVFP4_CUDA_CHECK(cudaGetLastError());
+    return NVFP4_OK;
+}
+
+int launch_plan_peer(const int64_t* all_counts, int world, int num_experts, int rank, int alignment, const int64_t* ids,
+                     int64_t n, int64_t* base, int64_t* sizes, int64_t* dst_row, cudaStream_t stream)
+{
+    plan_offsets_kernel<<<1, 1024, (num_experts + world) * sizeof(int64_t), stream>>>(all_counts, world, num_experts, rank, alignment,
+                                                                                       base, sizes);
+    NVFP4_CUDA_CHECK(cudaGetLastError());
+    plan_rows_kernel<<<num_experts, 1024, 0, stream>>>(ids, n, base, dst_row);
     NVFP4_CUDA_CHECK(cudaGetLastError());
     return NVFP4_OK;
 }

@@ -84,9 +84,10 @@ def plan_dispatch(topk_ids: torch.Tensor, num_experts: int, world: int, alignmen
 @dataclass
 class PeerDispatch:
     """Routing plan of the peer-memory path: where every (token, choice) pair lives in its owner's buffer."""
-    order: torch.Tensor          # (T*k,) pair index sorted by global expert id (the send order)
-    dst_rank: torch.Tensor       # (T*k,) owner rank of send-order row i
-    dst_row: torch.Tensor        # (T*k,) its row in the owner's padded expert-major buffer
+    order: Optional[torch.Tensor]  # None: dst_* are indexed by the pair p = token * k + choice (CUDA plan); else the
+                                   # (T*k,) pair indices sorted by expert, and dst_* are indexed by that send order
+    dst_rank: torch.Tensor       # (T*k,) owner rank
+    dst_row: torch.Tensor        # (T*k,) row in the owner's padded expert-major buffer
     group_sizes: list            # padded rows per local expert
     real_sizes: list             # real rows per local expert
     rows_padded: int
@@ -99,20 +100,29 @@ def plan_dispatch_peer(topk_ids: torch.Tensor, num_experts: int, world: int, ran
     exchange, the row of each of its pairs in the owner's buffer.  The layout is the one plan_dispatch builds:
     expert-major, groups padded to the alignment, inside a group the rows of lower source ranks first."""
     e_local = num_experts // world
-    flat = topk_ids.reshape(-1)
-    # the sizes the host needs come first (histogram without a device synchronisation, one small all-gather, one
-    # read-back); the sort and the index arithmetic are queued behind it and run while the host moves on
+    flat = topk_ids.reshape(-1).contiguous()
     counts = torch.zeros(num_experts, dtype=torch.int64, device=flat.device).scatter_add_(0, flat, torch.ones_like(flat))
     if world > 1:
         gathered = counts.new_empty(world * num_experts)
         dist.all_gather_into_tensor(gathered, counts, group=group)
-        all_counts = gathered.reshape(world, num_experts)
     else:
-        all_counts = counts.reshape(1, -1)
+        gathered = counts
+    if flat.is_cuda:
+        # two kernels of the library: group offsets from the gathered histograms, then every pair's row (a stable
+        # counting sort without the sort); pairs are addressed by their own index p = token * k + choice
+        from . import _C
+        sizes_dev, dst_row = _C.plan_peer(gathered, flat, world, rank, alignment)
+        sizes = sizes_dev.tolist()                                            # the one host synchronisation of a step
+        dst_rank = torch.div(flat, e_local, rounding_mode="floor")
+        return PeerDispatch(order=None, dst_rank=dst_rank, dst_row=dst_row, group_sizes=sizes[:e_local],
+                            real_sizes=sizes[e_local:2 * e_local], rows_padded=int(sum(sizes[:e_local])),
+                            max_rows_padded=int(sizes[2 * e_local]))
+    # the same plan as tensor operations (CPU tests of the host logic); pairs in send order (sorted by expert)
+    all_counts = gathered.reshape(world, num_experts)
     per_expert = all_counts.sum(dim=0)
     padded = _pad(per_expert, alignment).reshape(world, e_local)
     sizes = torch.stack([padded[rank], per_expert.reshape(world, e_local)[rank],
-                         padded.sum(dim=1).max().expand(e_local)]).tolist()   # the one host synchronisation of a step
+                         padded.sum(dim=1).max().expand(e_local)]).tolist()
     order = torch.argsort(flat, stable=True)
     starts = (torch.cumsum(padded, dim=1) - padded).reshape(-1)               # start of each expert in its owner's buffer
     before = (torch.cumsum(all_counts, dim=0) - all_counts)[rank]             # rows of each expert from lower ranks
@@ -268,14 +278,10 @@ class ExpertParallelMoE:
             return None
         self.last = plan
         buf = self.peer
-        # where pair (t, j) sits: the combine reads it back from there
-        inverse = torch.empty_like(plan.order)
-        inverse[plan.order] = torch.arange(plan.order.numel(), device=x.device)
-        src_rank, src_row = plan.dst_rank[inverse], plan.dst_row[inverse]
         m_indices = make_m_indices(plan.group_sizes, device=x.device, alignment=self.alignment)
         mark()
         buf.barrier()                                   # every rank has finished with the buffers of the previous step
-        _C.dispatch_rows_peer(x, plan.order, k, buf.a_peers, plan.dst_rank, plan.dst_row, self.hidden)
+        _C.dispatch_rows_peer(x, None, k, buf.a_peers, plan.dst_rank, plan.dst_row, self.hidden)
         buf.barrier()                                   # all rows have landed everywhere
         mark()
         a, out = buf.a[:plan.rows_padded], buf.out[:plan.rows_padded]
@@ -284,7 +290,7 @@ class ExpertParallelMoE:
         self.gemm(swiglu(h), *self.down, out, m_indices)
         mark()
         buf.barrier()                                   # every rank's expert outputs are complete
-        y = _C.combine_rows_peer(buf.out_peers, self.hidden, src_rank, src_row,
+        y = _C.combine_rows_peer(buf.out_peers, self.hidden, plan.dst_rank, plan.dst_row,
                                  topk_w.float().contiguous().reshape(-1), x.shape[0], self.hidden)
         mark()
         return y

@@ -130,3 +130,32 @@ def test_two_ranks_peer_memory_path_matches_all_to_all_path():
         assert finite
         assert first < 1e-6 and third < 1e-6, (first, third)     # same rows, same kernels, same summation order
         assert fallback < 1e-6
+
+
+@pytest.mark.parametrize("rank", [0, 2, 3])
+def test_plan_peer_kernels_match_tensor_ops(dev, rank):
+    """The two plan kernels against the same plan written with tensor operations (stable sort by expert)."""
+    world, num_experts, alignment, n = 4, 16, 16, 3000
+    e_local = num_experts // world
+    g = torch.Generator().manual_seed(9)
+    ids_all = [torch.randint(0, num_experts, (n + 37 * s,), generator=g) for s in range(world)]
+    for t in ids_all:
+        t[t == 5] = 6                                            # an expert nobody routes to
+    all_counts = torch.stack([torch.bincount(t, minlength=num_experts) for t in ids_all])
+    flat = ids_all[rank]
+    sizes, dst_row = _C.plan_peer(all_counts.reshape(-1).to(dev), flat.to(dev), world, rank, alignment)
+    torch.cuda.synchronize()
+    per_expert = all_counts.sum(dim=0)
+    padded = ((per_expert + alignment - 1) // alignment * alignment).reshape(world, e_local)
+    starts = (torch.cumsum(padded, dim=1) - padded).reshape(-1)
+    before = (torch.cumsum(all_counts, dim=0) - all_counts)[rank]
+    counts = all_counts[rank]
+    first = torch.cumsum(counts, 0) - counts
+    order = torch.argsort(flat, stable=True)
+    expert_sorted = flat[order]
+    want_sorted = (starts + before - first)[expert_sorted] + torch.arange(order.numel())
+    want = torch.empty_like(want_sorted)
+    want[order] = want_sorted
+    assert torch.equal(dst_row.cpu(), want)
+    assert sizes.cpu().tolist() == padded[rank].tolist() + per_expert.reshape(world, e_local)[rank].tolist() + \
+        [int(padded.sum(dim=1).max())]
