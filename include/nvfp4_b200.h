@@ -145,12 +145,15 @@ NVFP4_API int nvfp4_combine_rows(const void* rows, int64_t rows_ld_elems, const 
  * nvfp4_combine_rows_peer: y[t] = sum over j < k of w[t*k+j] * (row src_row[t*k+j] of rank src_rank[t*k+j]'s
  *   buffer), read with plain loads over NVLink.  The caller orders it after every rank has written its buffer.
  *
+ * nvfp4_expert_histogram: counts[e] = number of i < n with ids[i] == e, for e < num_experts <= 4096 (ids outside
+ *   the range are ignored); what every rank all-gathers before the plan.
  * nvfp4_plan_peer: the routing plan of that path.  all_counts[s * E + e] = pairs rank s routes to expert e (the
  *   all-gathered histograms), ids[p] = expert of this rank's pair p (p = token * k + choice), n pairs.  Writes
  *   base[e] (E entries: the row of the owner's buffer where this rank's rows of expert e start), sizes
  *   (2 * E / world + 1 entries: padded rows per local expert, real rows per local expert, the largest padded total
  *   over all ranks) and dst_row[p] (n entries: base[e] + the number of earlier pairs of this rank routed to e).
  *   Experts are padded to `alignment` rows; E % world == 0, E <= 4096. */
+NVFP4_API int nvfp4_expert_histogram(const int64_t* ids, int64_t n, int num_experts, int64_t* counts, void* stream);
 NVFP4_API int nvfp4_plan_peer(const int64_t* all_counts, int world, int num_experts, int rank, int alignment,
                               const int64_t* ids, int64_t n, int64_t* base, int64_t* sizes, int64_t* dst_row,
                               void* stream);

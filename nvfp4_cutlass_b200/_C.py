@@ -29,7 +29,7 @@ TUNE_KEYS = ("tune_block_n", "tune_transform_warps", "tune_epilogue_threads", "t
 EXPORTS = ("nvfp4_last_error", "nvfp4_version", "nvfp4_get_num_sms", "nvfp4_set_num_sms",
            "nvfp4_quantize_weight", "nvfp4_quantize_weight_static", "nvfp4_grouped_gemm_contiguous", "nvfp4_debug_decompose",
            "nvfp4_debug_mma_peak", "nvfp4_debug_mma_pattern", "nvfp4_permute_rows", "nvfp4_swiglu", "nvfp4_combine_rows",
-           "nvfp4_dispatch_rows_peer", "nvfp4_combine_rows_peer", "nvfp4_plan_peer")
+           "nvfp4_dispatch_rows_peer", "nvfp4_combine_rows_peer", "nvfp4_plan_peer", "nvfp4_expert_histogram")
 
 
 def library_path() -> str:
@@ -58,6 +58,7 @@ def lib() -> ctypes.CDLL:
         L.nvfp4_permute_rows.argtypes = [vp, i64, vp, i32, vp, i64, i32, vp, i64, vp]
         L.nvfp4_swiglu.argtypes = [vp, i64, i64, i32, vp, i64, vp]
         L.nvfp4_dispatch_rows_peer.argtypes = [vp, i64, vp, i32, vp, vp, vp, i64, i32, i64, vp]
+        L.nvfp4_expert_histogram.argtypes = [vp, i64, i32, vp, vp]
         L.nvfp4_plan_peer.argtypes = [vp, i32, i32, i32, i32, vp, i64, vp, vp, vp, vp]
         L.nvfp4_combine_rows_peer.argtypes = [vp, i64, vp, vp, vp, i64, i32, i32, vp, i64, vp]
         L.nvfp4_combine_rows.argtypes = [vp, i64, vp, vp, i64, i32, i32, vp, i64, vp]
@@ -200,6 +201,14 @@ def combine_rows(rows: torch.Tensor, pos: torch.Tensor, w: torch.Tensor, tokens:
 
 def _i64_ok(t: torch.Tensor, n: int) -> bool:
     return t.is_cuda and t.dtype == torch.int64 and t.is_contiguous() and t.numel() >= n
+
+
+def expert_histogram(ids: torch.Tensor, num_experts: int) -> torch.Tensor:
+    """counts[e] = number of entries of ids equal to e (int64 CUDA tensors)."""
+    _require(_i64_ok(ids, ids.numel()), "ids is a contiguous int64 CUDA tensor")
+    counts = torch.empty(num_experts, dtype=torch.int64, device=ids.device)
+    _check(lib().nvfp4_expert_histogram(ids.data_ptr(), ids.numel(), num_experts, counts.data_ptr(), _stream()))
+    return counts
 
 
 def plan_peer(all_counts: torch.Tensor, ids: torch.Tensor, world: int, rank: int, alignment: int):

@@ -276,6 +276,14 @@ int nvfp4_combine_rows(const void* rows, int64_t rows_ld_elems, const int64_t* p
                                static_cast<cudaStream_t>(stream));
 }
 
+int nvfp4_expert_histogram(const int64_t* ids, int64_t n, int num_experts, int64_t* counts, void* stream)
+{
+    host::clear_error();
+    NVFP4_REQUIRE(num_experts >= 1 && num_experts <= 4096 && n >= 0, "num_experts (%d) must be in [1, 4096]", num_experts);
+    NVFP4_REQUIRE(counts && (n == 0 || ids), "null pointer argument");
+    return launch_expert_histogram(ids, n, num_experts, counts, static_cast<cudaStream_t>(stream));
+}
+
 int nvfp4_plan_peer(const int64_t* all_counts, int world, int num_experts, int rank, int alignment, const int64_t* ids, int64_t n,
                     int64_t* base, int64_t* sizes, int64_t* dst_row, void* stream)
 {

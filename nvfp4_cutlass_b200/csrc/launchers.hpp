@@ -25,6 +25,7 @@ int launch_swiglu(const void* h, int64_t h_ld_elems, int64_t rows, int inter, vo
 int launch_combine_rows(const void* rows, int64_t rows_ld_elems, const int64_t* pos, const float* w, int64_t tokens, int k,
                         int hidden, void* y, int64_t y_ld_elems, int num_sms, cudaStream_t stream);
 
+int launch_expert_histogram(const int64_t* ids, int64_t n, int num_experts, int64_t* counts, cudaStream_t stream);
 int launch_plan_peer(const int64_t* all_counts, int world, int num_experts, int rank, int alignment, const int64_t* ids,
                      int64_t n, int64_t* base, int64_t* sizes, int64_t* dst_row, cudaStream_t stream);
 int launch_dispatch_rows_peer(const void* src, int64_t src_ld_bytes, const int64_t* src_idx, int src_div, const int64_t* peers,

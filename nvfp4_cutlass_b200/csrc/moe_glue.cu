@@ -195,6 +195,23 @@ plan_offsets_kernel(const int64_t* __restrict__ all_counts, int world, int num_e
     }
 }
 
+// counts[e] += number of ids equal to e (counts zeroed by the caller); per-block histogram in shared memory first, so
+// that the global atomics are one per expert and block instead of one per pair on a handful of addresses
+__global__ void __launch_bounds__(1024)
+expert_histogram_kernel(const int64_t* __restrict__ ids, int64_t n, int num_experts, unsigned long long* __restrict__ counts)
+{
+    extern __shared__ unsigned int hist[];
+    for (int e = threadIdx.x; e < num_experts; e += blockDim.x) hist[e] = 0;
+    __syncthreads();
+    for (int64_t p = static_cast<int64_t>(blockIdx.x) * blockDim.x + threadIdx.x; p < n; p += static_cast<int64_t>(gridDim.x) * blockDim.x) {
+        const int64_t e = ids[p];
+        if (e >= 0 && e < num_experts) atomicAdd(&hist[e], 1u);
+    }
+    __syncthreads();
+    for (int e = threadIdx.x; e < num_experts; e += blockDim.x)
+        if (hist[e] != 0) atomicAdd(&counts[e], static_cast<unsigned long long>(hist[e]));
+}
+
 // plan_rows (one block per expert): dst_row[p] = base[e] + (number of pairs p' < p routed to e), for every pair p
 // routed to e -- a stable counting sort without the sort: pairs keep their order inside an expert's group.
 __global__ void __launch_bounds__(1024)
@@ -255,6 +272,17 @@ int launch_combine_rows(const void* rows, int64_t rows_ld_elems, const int64_t* 
     combine_rows_kernel<<<grid_for(tokens, num_sms), 256, 0, stream>>>(static_cast<const uint4*>(rows), rows_ld_elems / 8, pos, w,
                                                                         tokens, k, hidden / 8, static_cast<uint4*>(y),
                                                                         y_ld_elems / 8);
+    NVFP4_CUDA_CHECK(cudaGetLastError());
+    return NVFP4_OK;
+}
+
+int launch_expert_histogram(const int64_t* ids, int64_t n, int num_experts, int64_t* counts, cudaStream_t stream)
+{
+    NVFP4_CUDA_CHECK(cudaMemsetAsync(counts, 0, sizeof(int64_t) * num_experts, stream));
+    if (n == 0) return NVFP4_OK;
+    const unsigned blocks = static_cast<unsigned>((n + 8191) / 8192 < 64 ? (n + 8191) / 8192 : 64);
+    expert_histogram_kernel<<<blocks, 1024, num_experts * sizeof(unsigned int), stream>>>(
+        ids, n, num_experts, reinterpret_cast<unsigned long long*>(counts));
     NVFP4_CUDA_CHECK(cudaGetLastError());
     return NVFP4_OK;
 }

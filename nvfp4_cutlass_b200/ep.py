@@ -92,6 +92,7 @@ class PeerDispatch:
     real_sizes: list             # real rows per local expert
     rows_padded: int
     max_rows_padded: int         # the largest rows_padded over all ranks (capacity check, same on every rank)
+    padded_dev: Optional[torch.Tensor] = None    # group_sizes as a device tensor (to build m_indices without a copy)
 
 
 def plan_dispatch_peer(topk_ids: torch.Tensor, num_experts: int, world: int, rank: int, alignment: int,
@@ -101,7 +102,11 @@ def plan_dispatch_peer(topk_ids: torch.Tensor, num_experts: int, world: int, ran
     expert-major, groups padded to the alignment, inside a group the rows of lower source ranks first."""
     e_local = num_experts // world
     flat = topk_ids.reshape(-1).contiguous()
-    counts = torch.zeros(num_experts, dtype=torch.int64, device=flat.device).scatter_add_(0, flat, torch.ones_like(flat))
+    if flat.is_cuda:
+        from . import _C
+        counts = _C.expert_histogram(flat, num_experts)
+    else:
+        counts = torch.zeros(num_experts, dtype=torch.int64).scatter_add_(0, flat, torch.ones_like(flat))
     if world > 1:
         gathered = counts.new_empty(world * num_experts)
         dist.all_gather_into_tensor(gathered, counts, group=group)
@@ -110,13 +115,12 @@ def plan_dispatch_peer(topk_ids: torch.Tensor, num_experts: int, world: int, ran
     if flat.is_cuda:
         # two kernels of the library: group offsets from the gathered histograms, then every pair's row (a stable
         # counting sort without the sort); pairs are addressed by their own index p = token * k + choice
-        from . import _C
         sizes_dev, dst_row = _C.plan_peer(gathered, flat, world, rank, alignment)
         sizes = sizes_dev.tolist()                                            # the one host synchronisation of a step
         dst_rank = torch.div(flat, e_local, rounding_mode="floor")
         return PeerDispatch(order=None, dst_rank=dst_rank, dst_row=dst_row, group_sizes=sizes[:e_local],
                             real_sizes=sizes[e_local:2 * e_local], rows_padded=int(sum(sizes[:e_local])),
-                            max_rows_padded=int(sizes[2 * e_local]))
+                            max_rows_padded=int(sizes[2 * e_local]), padded_dev=sizes_dev[:e_local])
     # the same plan as tensor operations (CPU tests of the host logic); pairs in send order (sorted by expert)
     all_counts = gathered.reshape(world, num_experts)
     per_expert = all_counts.sum(dim=0)
@@ -138,10 +142,17 @@ class PeerBuffers:
     """The two symmetric buffers of the peer-memory path (GEMM input rows and GEMM output rows of this rank,
     mapped into every rank of the group) and their address tables."""
 
-    def __init__(self, rows_cap: int, hidden: int, device: torch.device, group=None):
+    def __init__(self, rows_cap: int, hidden: int, device: torch.device, group=None, world: int = 2):
+        self.rows_cap, self.hidden = rows_cap, hidden
+        if world == 1:                      # one rank: the same kernels on ordinary buffers, nobody to wait for
+            self._ha = None
+            self.a = torch.zeros(rows_cap, hidden, dtype=torch.bfloat16, device=device)
+            self.out = torch.zeros(rows_cap, hidden, dtype=torch.bfloat16, device=device)
+            self.a_peers = torch.tensor([self.a.data_ptr()], dtype=torch.int64, device=device)
+            self.out_peers = torch.tensor([self.out.data_ptr()], dtype=torch.int64, device=device)
+            return
         import torch.distributed._symmetric_memory as symm
         group = group if group is not None else dist.group.WORLD
-        self.rows_cap, self.hidden = rows_cap, hidden
         self.a = symm.empty(rows_cap, hidden, dtype=torch.bfloat16, device=device)
         self.out = symm.empty(rows_cap, hidden, dtype=torch.bfloat16, device=device)
         self._ha = symm.rendezvous(self.a, group)
@@ -155,7 +166,8 @@ class PeerBuffers:
 
     def barrier(self) -> None:
         """All ranks of the group, ordered on the current stream."""
-        self._ha.barrier(channel=0)
+        if self._ha is not None:
+            self._ha.barrier(channel=0)
 
 
 def _exchange(rows: torch.Tensor, send_counts, recv_counts, group) -> torch.Tensor:
@@ -197,14 +209,16 @@ class ExpertParallelMoE:
             gemm = _C.m_grouped_bf16_dual_nvfp4_gemm_contiguous
         self.gemm = gemm
         self.native_glue = native_glue         # False: tensor operations even for CUDA tensors (a test's comparison arm)
-        # peer_rows_cap > 0 on several GPUs: dispatch and combine go through peer memory (one kernel each, stores
-        # into / loads from the owner rank's buffer) instead of staging buffers and NCCL all-to-alls; a step whose
-        # routing would overflow the buffer of some rank falls back to the all-to-all path on every rank
+        # peer_rows_cap > 0: dispatch and combine go through peer memory (one kernel each, stores into / loads from
+        # the owner rank's buffer; with one rank the same kernels on local buffers) instead of staging buffers and
+        # NCCL all-to-alls; a step whose routing would overflow the buffer of some rank falls back to the
+        # all-to-all path on every rank
         self.peer = None
         self.peer_error = None
-        if peer_rows_cap > 0 and self.world > 1:
+        if peer_rows_cap > 0 and torch.cuda.is_available():
             try:
-                self.peer = PeerBuffers(peer_rows_cap, hidden, torch.device("cuda", torch.cuda.current_device()), group)
+                self.peer = PeerBuffers(peer_rows_cap, hidden, torch.device("cuda", torch.cuda.current_device()), group,
+                                        self.world)
             except Exception as exc:                                   # symmetric memory unavailable: keep the NCCL path
                 self.peer_error = repr(exc)
         self.last = None                       # Dispatch of the most recent call (for accounting)
@@ -278,7 +292,11 @@ class ExpertParallelMoE:
             return None
         self.last = plan
         buf = self.peer
-        m_indices = make_m_indices(plan.group_sizes, device=x.device, alignment=self.alignment)
+        if plan.padded_dev is not None:                 # expert id per row, built on the device
+            m_indices = torch.repeat_interleave(torch.arange(self.e_local, dtype=torch.int32, device=x.device), plan.padded_dev,
+                                                output_size=plan.rows_padded)
+        else:
+            m_indices = make_m_indices(plan.group_sizes, device=x.device, alignment=self.alignment)
         mark()
         buf.barrier()                                   # every rank has finished with the buffers of the previous step
         _C.dispatch_rows_peer(x, None, k, buf.a_peers, plan.dst_rank, plan.dst_row, self.hidden)

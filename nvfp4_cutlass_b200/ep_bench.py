@@ -47,12 +47,13 @@ def run(args, workload: str, world: int, rank: int, local: int) -> None:
     extra = {kv.split('=')[0]: int(kv.split('=')[1]) for kv in getattr(args, "tune", [])}
     # several GPUs: dispatch and combine over peer memory unless ep_peer=0 asks for the NCCL all-to-all path;
     # room for 1.5 x the average rows a rank receives (a step that does not fit falls back by itself)
-    use_peer = world > 1 and extra.get("ep_peer", 1) != 0
+    use_peer = extra.get("ep_peer", 1) != 0
     cap = int(1.5 * tokens * TOP_K) + e_local * 128
     layer = ExpertParallelMoE(E_TOTAL, HIDDEN, INTER, up, down, alignment=128, peer_rows_cap=cap if use_peer else 0)
     exchange = "nccl all_to_all"
     if layer.peer is not None:
-        exchange = "peer memory (one dispatch kernel of NVLink stores, one combine kernel of NVLink loads)"
+        exchange = ("peer memory (one dispatch kernel of NVLink stores, one combine kernel of NVLink loads)" if world > 1 else
+                    "one rank: the dispatch and combine kernels on local buffers")
     elif use_peer:
         exchange = "nccl all_to_all (symmetric memory unavailable: %s)" % (layer.peer_error or "?")[:200]
 
@@ -119,7 +120,8 @@ def run(args, workload: str, world: int, rank: int, local: int) -> None:
         mx, sm = stats, stats
     ms_max, e2e_max, flops_all = float(mx[0]), float(mx[1]), float(sm[2])
     # kernels of this library per step: 2 GEMMs x (activation quantisation + GEMM), SwiGLU, and the row movers
-    kernels_per_step = 4 + 1 + (2 if (layer.peer is not None or world == 1) else 4)
+    # (+ histogram and the two plan kernels on the peer-memory path)
+    kernels_per_step = 4 + 1 + (2 + 3 if layer.peer is not None else (2 if world == 1 else 4))
     if rank == 0:
         fp4_peak = bench.measure_fp4_peak()
         value = flops_all / (ms_max * 1e-3) / 1e12

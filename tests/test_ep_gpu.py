@@ -75,9 +75,13 @@ def test_layer_step_native_glue_matches_tensor_glue(dev):
     ids, wts = route_topk(torch.randn(tokens, e, generator=g).to(dev), k)
     native = ExpertParallelMoE(e, hidden, inter, up, down, alignment=128)(x, ids, wts)
     plain = ExpertParallelMoE(e, hidden, inter, up, down, alignment=128, native_glue=False)(x, ids, wts)
+    planned = ExpertParallelMoE(e, hidden, inter, up, down, alignment=128, peer_rows_cap=4096)   # plan kernels, local buffers
+    assert planned.peer is not None
+    fast = [planned(x, ids, wts) for _ in range(2)]
     torch.cuda.synchronize()
     assert native.shape == (tokens, hidden) and torch.isfinite(native.float()).all()
     assert rel_l2(native, plain) < 5e-3
+    assert torch.equal(fast[0], native) and torch.equal(fast[1], native)
 
 
 def _two_rank_worker(rank, world, port, results):
@@ -143,6 +147,7 @@ def test_plan_peer_kernels_match_tensor_ops(dev, rank):
         t[t == 5] = 6                                            # an expert nobody routes to
     all_counts = torch.stack([torch.bincount(t, minlength=num_experts) for t in ids_all])
     flat = ids_all[rank]
+    assert torch.equal(_C.expert_histogram(flat.to(dev), num_experts).cpu(), all_counts[rank])
     sizes, dst_row = _C.plan_peer(all_counts.reshape(-1).to(dev), flat.to(dev), world, rank, alignment)
     torch.cuda.synchronize()
     per_expert = all_counts.sum(dim=0)
