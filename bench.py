@@ -54,7 +54,7 @@ WORKLOADS = {
 # under profiles/, on the reduced workloads c2s / c4s (the full ones exceed what a multi-pass capture should
 # hold), as (bytes measured, algorithmic bytes of that captured launch).  Both kernels stream every operand
 # once, so traffic grows in proportion to the algorithmic bytes; a full launch is scaled by that ratio.
-NCU_TRAFFIC = {"normal": (246.13e6, 251.66e6, "profiles/gemm_split_kernel_c2s.md"),
+NCU_TRAFFIC = {"normal": (246.79e6, 251.66e6, "profiles/gemm_split_kernel_c2s.md"),
                "swap_ab": (925.54e6, 911.22e6, "profiles/gemm_swap_kernel_c4s.md")}
 
 
