@@ -91,11 +91,7 @@ NVFP4_DEVICE void decompose_block16(const uint32_t (&w)[8], Block16& out)
     m2 = ptx::max_abs_bf16x2(m2, m3);
     m0 = ptx::max_abs_bf16x2(m0, m2);
     m0 = ptx::max_abs_bf16x2(m0, m0 >> 16);
-#if defined(NVFP4_XFV) && NVFP4_XFV == 1   // timing studies only (wrong results)
-    const float amax = __uint_as_float((w[0] & 0x7fffu) << 16);
-#else
     const float amax = __uint_as_float((m0 & 0x7fffu) << 16);
-#endif
 
     // s0 = Q_e4m3(max(amax * fl(1/6), 2^-6)); always a normal E4M3 value
     const float s0_pre = fmaxf(__fmul_rn(amax, 0.16666667163372040f), 0.015625f);
@@ -104,66 +100,22 @@ NVFP4_DEVICE void decompose_block16(const uint32_t (&w)[8], Block16& out)
     out.s0 = s0c;
     out.s1 = ptx::cvt_e4m3(__fmul_rn(s0, 0.125f));
 
+    // u = x / s0 as the correctly rounded quotient: r_hi ~ 1 / s0, r_lo = its error term formed exactly by one FMA
     const float r_hi = ptx::rcp_approx(s0);
     const float r_lo = __fmul_rn(__fmaf_rn(-s0, r_hi, 1.0f), r_hi);
 
     float u[16];
 #pragma unroll
     for (int i = 0; i < 8; ++i) {
-#if defined(NVFP4_XFV) && NVFP4_XFV == 2   // timing studies only (wrong results)
-        const float x0 = __uint_as_float(w[i]), x1 = __uint_as_float(w[(i + 1) & 7]);
-#else
         const float x0 = __uint_as_float(w[i] << 16);
         const float x1 = __uint_as_float(w[i] & 0xffff0000u);
-#endif
         u[2 * i] = __fmaf_rn(x0, r_hi, __fmul_rn(x0, r_lo));
         u[2 * i + 1] = __fmaf_rn(x1, r_hi, __fmul_rn(x1, r_lo));
     }
-#if defined(NVFP4_XFV) && (NVFP4_XFV == 5 || NVFP4_XFV == 6)   // experimental fused per-pair path
-    if constexpr (kResidual) {
-        uint32_t b[8];
-        float r[16];
-#pragma unroll
-        for (int i = 0; i < 8; ++i) {
-            const float c0 = __fmul_rn(u[2 * i], 8.0f), c1 = __fmul_rn(u[2 * i + 1], 8.0f);
-#if NVFP4_XFV == 5
-            asm("{\n .reg .b8 t;\n .reg .b16 lo, hi, m8;\n .reg .b32 d;\n"
-                " cvt.rn.satfinite.e2m1x2.f32 t, %4, %3;\n cvt.u32.u8 %0, t;\n cvt.rn.f16x2.e2m1x2 d, t;\n"
-                " mov.b32 {lo, hi}, d;\n mov.b16 m8, 0xC800;\n"
-                " fma.rn.f32.f16 %1, lo, m8, %5;\n fma.rn.f32.f16 %2, hi, m8, %6;\n}\n"
-                : "=&r"(b[i]), "=&f"(r[2 * i]), "=&f"(r[2 * i + 1])
-                : "f"(u[2 * i]), "f"(u[2 * i + 1]), "f"(c0), "f"(c1));
-#else
-            float f0, f1;
-            asm("{\n .reg .b8 t;\n .reg .b16 lo, hi;\n .reg .b32 d;\n"
-                " cvt.rn.satfinite.e2m1x2.f32 t, %4, %3;\n cvt.u32.u8 %0, t;\n cvt.rn.f16x2.e2m1x2 d, t;\n"
-                " mov.b32 {lo, hi}, d;\n cvt.f32.f16 %1, lo;\n cvt.f32.f16 %2, hi;\n}\n"
-                : "=&r"(b[i]), "=&f"(f0), "=&f"(f1)
-                : "f"(u[2 * i]), "f"(u[2 * i + 1]));
-            r[2 * i] = __fmaf_rn(f0, -8.0f, c0);
-            r[2 * i + 1] = __fmaf_rn(f1, -8.0f, c1);
-#endif
-        }
-        out.q0[0] = __byte_perm(__byte_perm(b[0], b[1], 0x0040), __byte_perm(b[2], b[3], 0x0040), 0x5410);
-        out.q0[1] = __byte_perm(__byte_perm(b[4], b[5], 0x0040), __byte_perm(b[6], b[7], 0x0040), 0x5410);
-        out.q1[0] = ptx::cvt_e2m1x8(r[0], r[1], r[2], r[3], r[4], r[5], r[6], r[7]);
-        out.q1[1] = ptx::cvt_e2m1x8(r[8], r[9], r[10], r[11], r[12], r[13], r[14], r[15]);
-        return;
-    }
-#endif
-#if defined(NVFP4_XFV) && NVFP4_XFV == 3   // timing studies only (wrong results)
-    out.q0[0] = __float_as_uint(u[0]) ^ __float_as_uint(u[3]) ^ __float_as_uint(u[5]) ^ __float_as_uint(u[7]);
-    out.q0[1] = __float_as_uint(u[8]) ^ __float_as_uint(u[11]) ^ __float_as_uint(u[13]) ^ __float_as_uint(u[15]);
-#else
     out.q0[0] = ptx::cvt_e2m1x8(u[0], u[1], u[2], u[3], u[4], u[5], u[6], u[7]);
     out.q0[1] = ptx::cvt_e2m1x8(u[8], u[9], u[10], u[11], u[12], u[13], u[14], u[15]);
-#endif
 
-#if defined(NVFP4_XFV) && NVFP4_XFV == 4
-    if constexpr (false) {
-#else
     if constexpr (kResidual) {
-#endif
         // r = (u - dec(q0)) * 8 = 8u + dec(q0) * (-8): exact, the decode comes back as FP16
         float r[16];
 #pragma unroll
