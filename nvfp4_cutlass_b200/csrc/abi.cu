@@ -172,8 +172,10 @@ int nvfp4_grouped_gemm_contiguous(const void* a, int64_t lda_elems, const void* 
                   static_cast<long long>(lda_elems), static_cast<long long>(ldd_elems));
     NVFP4_REQUIRE(lda_elems % 8 == 0 && ldd_elems % 8 == 0, "row strides must be multiples of 8 elements (16 bytes)");
     NVFP4_REQUIRE((reinterpret_cast<uintptr_t>(d) & 15u) == 0, "d must be 16-byte aligned");
-    if (scale_policy != NVFP4_POLICY_DERIVED_DIV8)
-        return host::fail(NVFP4_E_UNSUPPORTED, "scale policy %d is not built; only derived_div8", scale_policy);
+    if (scale_policy != NVFP4_POLICY_DERIVED_DIV8 && scale_policy != NVFP4_POLICY_RESIDUAL_AMAX)
+        return host::fail(NVFP4_E_UNSUPPORTED, "scale policy %d is not built; derived_div8 and residual_amax are", scale_policy);
+    if (scale_policy == NVFP4_POLICY_RESIDUAL_AMAX && orientation == NVFP4_ORIENT_SWAP_AB)
+        return host::fail(NVFP4_E_UNSUPPORTED, "residual_amax is not built for the swap-AB orientation");
 
     host::DeviceInfo* dev;
     if (int rc = host::device_info(-1, &dev)) return rc;
@@ -210,8 +212,12 @@ int nvfp4_grouped_gemm_contiguous(const void* a, int64_t lda_elems, const void* 
     if (tune_split == 1 || (tune_split == 0 && !fused_knobs && N % 256 == 0 && N >= 1024)) {
         const int tune_block_k = tune ? tune[5] : 0;
         return launch_gemm_split(a, lda_elems, b, sfb, gw, d, ldd_elems, m_indices, M, N, K, E, enable_residual_pass != 0,
-                                 tune_block_k, tune_sched_group, !(tune && tune[11]), dev->num_sms, device_status, s);
+                                 tune_block_k, tune_sched_group, !(tune && tune[11]), scale_policy, dev->num_sms, device_status, s);
     }
+    // residual_amax exists in the split path (above) and in the single-CTA fused kernel, not in the cluster kernel
+    if (scale_policy == NVFP4_POLICY_RESIDUAL_AMAX)
+        return launch_gemm_normal(a, lda_elems, b, sfb, gw, d, ldd_elems, m_indices, M, N, K, E, enable_residual_pass != 0,
+                                  0, tune_sched_group, false, scale_policy, dev->num_sms, device_status, s);
     int cluster = tune ? tune[8] : 0;
     NVFP4_REQUIRE(cluster == 0 || cluster == 1 || cluster == 2 || cluster == 4, "tune_cluster must be 0, 1, 2 or 4");
     NVFP4_REQUIRE(cluster < 2 || N % (256 * cluster) == 0, "tune_cluster %d needs N %% %d == 0 (N=%d)", cluster, 256 * cluster, N);
@@ -226,7 +232,7 @@ int nvfp4_grouped_gemm_contiguous(const void* a, int64_t lda_elems, const void* 
     // shared-memory ring (measured slower on B200: 1.89 ms against 1.06 ms on the Mixtral-like shape)
     const bool direct_a = tune && tune[9] == 1 && tune_xform_warps != 16;
     return launch_gemm_normal(a, lda_elems, b, sfb, gw, d, ldd_elems, m_indices, M, N, K, E, enable_residual_pass != 0,
-                              tune_xform_warps, tune_sched_group, direct_a, dev->num_sms, device_status, s);
+                              tune_xform_warps, tune_sched_group, direct_a, scale_policy, dev->num_sms, device_status, s);
 }
 
 int nvfp4_permute_rows(const void* src, int64_t src_ld_bytes, const int64_t* src_idx, int src_div, const int64_t* dst_idx,
@@ -335,12 +341,12 @@ int nvfp4_debug_decompose(const void* a, int64_t lda_elems, int M, int K, int sc
 {
     host::clear_error();
     NVFP4_REQUIRE(M >= 0 && K >= 0 && M % 128 == 0 && K % 128 == 0, "M and K must be multiples of 128 (M=%d, K=%d)", M, K);
-    if (scale_policy != NVFP4_POLICY_DERIVED_DIV8)
-        return host::fail(NVFP4_E_UNSUPPORTED, "scale policy %d is not built; only derived_div8", scale_policy);
+    if (scale_policy != NVFP4_POLICY_DERIVED_DIV8 && scale_policy != NVFP4_POLICY_RESIDUAL_AMAX)
+        return host::fail(NVFP4_E_UNSUPPORTED, "scale policy %d is not built; derived_div8 and residual_amax are", scale_policy);
     if (M == 0 || K == 0) return NVFP4_OK;
     NVFP4_REQUIRE(a && q0 && q1 && s0 && s1, "null pointer argument");
     NVFP4_REQUIRE(lda_elems >= K && lda_elems % 8 == 0, "bad row stride %lld", static_cast<long long>(lda_elems));
-    return launch_debug_decompose(a, lda_elems, M, K, q0, q1, s0, s1, static_cast<cudaStream_t>(stream));
+    return launch_debug_decompose(a, lda_elems, M, K, scale_policy, q0, q1, s0, s1, static_cast<cudaStream_t>(stream));
 }
 
 int nvfp4_debug_mma_peak(int iters, double* flops_per_launch, void* stream)

@@ -14,7 +14,7 @@ namespace {
 // where TMA would put it, run the GEMM's transform, then copy the products out
 // through the same addressing functions the MMA descriptors assume.
 // Counterpart in the reference: tests/standalone/test_transform.cu:50-132.
-template <uint32_t kThreads>
+template <uint32_t kThreads, int kPolicy>
 __global__ void __launch_bounds__(kThreads) decompose_dump_kernel(const __nv_bfloat16* __restrict__ a, int64_t lda, int K,
                                                                   uint8_t* __restrict__ q0, uint8_t* __restrict__ q1,
                                                                   uint8_t* __restrict__ s0, uint8_t* __restrict__ s1)
@@ -32,7 +32,7 @@ __global__ void __launch_bounds__(kThreads) decompose_dump_kernel(const __nv_bfl
         *reinterpret_cast<uint4*>(tile + xform::a_bf16_offset<128>(row, k)) = v;
     }
     __syncthreads();
-    xform::transform_tile<128, 128, kThreads, true>(ptx::smem_u32(tile), ptx::smem_u32(a0), ptx::smem_u32(a1),
+    xform::transform_tile<128, 128, kThreads, true, 4, 0, kPolicy>(ptx::smem_u32(tile), ptx::smem_u32(a0), ptx::smem_u32(a1),
                                                ptx::smem_u32(sfa0), ptx::smem_u32(sfa1), t, [] {});
     __syncthreads();
     for (uint32_t c = t; c < 128 * 4; c += kThreads) {           // 16-byte chunks of packed codes: 4 per row
@@ -98,7 +98,7 @@ __global__ void __launch_bounds__(128, 1) mma_pattern_kernel(int iters, int num_
 
 }  // namespace
 
-int launch_debug_decompose(const void* a, int64_t lda, int M, int K, void* q0, void* q1, void* s0, void* s1,
+int launch_debug_decompose(const void* a, int64_t lda, int M, int K, int policy, void* q0, void* q1, void* s0, void* s1,
                            cudaStream_t stream)
 {
     if (M == 0 || K == 0) return NVFP4_OK;
@@ -107,10 +107,12 @@ int launch_debug_decompose(const void* a, int64_t lda, int M, int K, void* q0, v
     int dev = 0;
     NVFP4_CUDA_CHECK(cudaGetDevice(&dev));
     if (!dump_attr_set[dev]) {
-        NVFP4_CUDA_CHECK(cudaFuncSetAttribute(decompose_dump_kernel<256>, cudaFuncAttributeMaxDynamicSharedMemorySize, kDumpSmem));
+        NVFP4_CUDA_CHECK(cudaFuncSetAttribute(decompose_dump_kernel<256, 0>, cudaFuncAttributeMaxDynamicSharedMemorySize, kDumpSmem));
+        NVFP4_CUDA_CHECK(cudaFuncSetAttribute(decompose_dump_kernel<256, 1>, cudaFuncAttributeMaxDynamicSharedMemorySize, kDumpSmem));
         dump_attr_set[dev] = true;
     }
-    decompose_dump_kernel<256><<<dim3(K / 128, M / 128), 256, kDumpSmem, stream>>>(
+    auto kernel = policy == 1 ? decompose_dump_kernel<256, 1> : decompose_dump_kernel<256, 0>;
+    kernel<<<dim3(K / 128, M / 128), 256, kDumpSmem, stream>>>(
         static_cast<const __nv_bfloat16*>(a), lda, K, static_cast<uint8_t*>(q0), static_cast<uint8_t*>(q1),
         static_cast<uint8_t*>(s0), static_cast<uint8_t*>(s1));
     NVFP4_CUDA_CHECK(cudaGetLastError());

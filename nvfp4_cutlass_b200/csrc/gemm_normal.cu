@@ -104,7 +104,7 @@ __device__ __forceinline__ void tile_coords(uint32_t tile, uint32_t num_m, uint3
     n_blk = r / rows;
 }
 
-template <uint32_t BN, uint32_t kXformWarps, bool kResidual, bool kDirectA>
+template <uint32_t BN, uint32_t kXformWarps, bool kResidual, bool kDirectA, int kPolicy>
 __global__ void __launch_bounds__((kWarpXform0 + kXformWarps) * 32, 1)
 gemm_normal_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constant__ CUtensorMap tm_b,
                    const __grid_constant__ CUtensorMap tm_sfb, const Params p)
@@ -349,7 +349,7 @@ gemm_normal_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_consta
                 }
                 if (ntile < num_tiles) xform::load_tile_global(nxt, tile_ptr(nm, nkb), p.lda, t);
                 if (!ptx::mbar_wait(p_empty + rp.slot, rp.phase ^ 1, abort_flag, pa, 1)) { give_up(1); return; }
-                xform::emit_tile<BM, BK, kXformThreads, kResidual>(
+                xform::emit_tile<BM, BK, kXformThreads, kResidual, 4, 0, kPolicy>(
                     cur, smem + kOffA0 + rp.slot * kSlotA0, smem + kOffA1 + rp.slot * kSlotA0,
                     smem + kOffSFA0 + rp.slot * kSlotSFA, smem + kOffSFA1 + rp.slot * kSlotSFA, t);
                 ptx::fence_proxy_async_smem();
@@ -368,7 +368,7 @@ gemm_normal_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_consta
                 for (uint32_t kb = 0; kb < num_kb; ++kb) {
                     if (!ptx::mbar_wait(a_full + ra.slot, ra.phase, abort_flag, pa, 0)) { give_up(1); break; }
                     bool p_ok = true;
-                    xform::transform_tile<BM, BK, kXformThreads, kResidual>(
+                    xform::transform_tile<BM, BK, kXformThreads, kResidual, 4, 0, kPolicy>(
                         smem + kOffA + ra.slot * kSlotA, smem + kOffA0 + rp.slot * kSlotA0, smem + kOffA1 + rp.slot * kSlotA0,
                         smem + kOffSFA0 + rp.slot * kSlotSFA, smem + kOffSFA1 + rp.slot * kSlotSFA, t, [&] {
                             // the tile now lives in registers: hand the BF16 slot back before the arithmetic
@@ -403,7 +403,7 @@ gemm_normal_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_consta
     }
 }
 
-template <uint32_t BN, uint32_t kXformWarps, bool kResidual, bool kDirectA>
+template <uint32_t BN, uint32_t kXformWarps, bool kResidual, bool kDirectA, int kPolicy = 0>
 int launch_variant(const void* a, int64_t lda, const void* b, const void* sfb, int M, int N, int K, int E,
                    const Params& p, int num_sms, cudaStream_t stream)
 {
@@ -419,7 +419,7 @@ int launch_variant(const void* a, int64_t lda, const void* b, const void* sfb, i
                                     static_cast<uint64_t>(E) * (K / 64), static_cast<uint64_t>(N) * 4, BN, kKAtoms,
                                     CU_TENSOR_MAP_SWIZZLE_NONE);
     if (rc) return rc;
-    auto kernel = gemm_normal_kernel<BN, kXformWarps, kResidual, kDirectA>;
+    auto kernel = gemm_normal_kernel<BN, kXformWarps, kResidual, kDirectA, kPolicy>;
     static bool attr_set[host::kMaxDevices] = {};
     int dev = 0;
     NVFP4_CUDA_CHECK(cudaGetDevice(&dev));
@@ -436,8 +436,11 @@ int launch_variant(const void* a, int64_t lda, const void* b, const void* sfb, i
 
 template <uint32_t BN>
 int launch_for_bn(const void* a, int64_t lda, const void* b, const void* sfb, int M, int N, int K, int E,
-                  const Params& p, bool residual, int xform_warps, bool direct_a, int num_sms, cudaStream_t stream)
+                  const Params& p, bool residual, int xform_warps, bool direct_a, int policy, int num_sms, cudaStream_t stream)
 {
+    if (policy == 1)      // residual_amax: the TMA-staged kernel with eight transform warps only
+        return residual ? launch_variant<BN, 8, true, false, 1>(a, lda, b, sfb, M, N, K, E, p, num_sms, stream)
+                        : launch_variant<BN, 8, false, false, 1>(a, lda, b, sfb, M, N, K, E, p, num_sms, stream);
     if (!direct_a) {
         if (xform_warps == 16)
             return residual ? launch_variant<BN, 16, true, false>(a, lda, b, sfb, M, N, K, E, p, num_sms, stream)
@@ -454,7 +457,8 @@ int launch_for_bn(const void* a, int64_t lda, const void* b, const void* sfb, in
 // Validated arguments in, launch out.  See nvfp4_grouped_gemm_contiguous for meanings.
 int launch_gemm_normal(const void* a, int64_t lda, const void* b, const void* sfb, const float* gw, void* d,
                        int64_t ldd, const int32_t* m_indices, int M, int N, int K, int E, bool residual,
-                       int xform_warps, int group_m, bool direct_a, int num_sms, int32_t* status, cudaStream_t stream)
+                       int xform_warps, int group_m, bool direct_a, int policy, int num_sms, int32_t* status,
+                       cudaStream_t stream)
 {
     Params p;
     p.a = static_cast<const __nv_bfloat16*>(a);
@@ -466,8 +470,8 @@ int launch_gemm_normal(const void* a, int64_t lda, const void* b, const void* sf
     p.m = M; p.n = N; p.k = K; p.num_experts = E;
     p.group_m = group_m > 0 ? group_m : 8;
     p.status = status;
-    if (N % 256 == 0) return launch_for_bn<256>(a, lda, b, sfb, M, N, K, E, p, residual, xform_warps, direct_a, num_sms, stream);
-    return launch_for_bn<128>(a, lda, b, sfb, M, N, K, E, p, residual, xform_warps, direct_a, num_sms, stream);
+    if (N % 256 == 0) return launch_for_bn<256>(a, lda, b, sfb, M, N, K, E, p, residual, xform_warps, direct_a, policy, num_sms, stream);
+    return launch_for_bn<128>(a, lda, b, sfb, M, N, K, E, p, residual, xform_warps, direct_a, policy, num_sms, stream);
 }
 
 #ifdef NVFP4_PROBE

@@ -39,7 +39,7 @@ constexpr uint32_t kSmemBudget = 232448 - 1024;
 // One thread per 16-element block; the four threads of a 64-K atom row combine their scale bytes into one
 // 32-bit store.
 // ---------------------------------------------------------------------------------------------------
-template <bool kResidual>
+template <bool kResidual, int kPolicy>
 __global__ void __launch_bounds__(256)
 quantize_activation_kernel(const __nv_bfloat16* __restrict__ a, int64_t lda, uint32_t m, uint32_t k,
                            uint8_t* __restrict__ a0, uint8_t* __restrict__ a1, uint8_t* __restrict__ sfa)
@@ -63,7 +63,7 @@ quantize_activation_kernel(const __nv_bfloat16* __restrict__ a, int64_t lda, uin
         w[4] = hi.x; w[5] = hi.y; w[6] = hi.z; w[7] = hi.w;
     }
     xform::Block16 out;
-    xform::decompose_block16<kResidual>(w, out);
+    xform::decompose_block16<kResidual, kPolicy>(w, out);
     const uint64_t code_off = static_cast<uint64_t>(row) * (k / 2) + blk16 * 8;
     *reinterpret_cast<uint2*>(a0 + code_off) = make_uint2(out.q0[0], out.q0[1]);
     if constexpr (kResidual) *reinterpret_cast<uint2*>(a1 + code_off) = make_uint2(out.q1[0], out.q1[1]);
@@ -447,7 +447,7 @@ int workspace_pool(int dev, cudaMemPool_t* out)
 
 template <uint32_t BK, bool kResidual, uint32_t kGroup>
 int launch_variant(const void* a, int64_t lda, const void* b, const void* sfb, int M, int N, int K, int E, Params p,
-                   bool pdl, int num_sms, cudaStream_t stream)
+                   bool pdl, int policy, int num_sms, cudaStream_t stream)
 {
     using C = Cfg<BK, kResidual, kGroup>;
     int dev = 0;
@@ -482,7 +482,8 @@ int launch_variant(const void* a, int64_t lda, const void* b, const void* sfb, i
     if (rc) return release(rc);
 
     const uint64_t blocks16 = static_cast<uint64_t>(M) * (K / 16);
-    quantize_activation_kernel<kResidual><<<static_cast<unsigned>((blocks16 + 255) / 256), 256, 0, stream>>>(
+    auto quantize = policy == 1 ? quantize_activation_kernel<kResidual, 1> : quantize_activation_kernel<kResidual, 0>;
+    quantize<<<static_cast<unsigned>((blocks16 + 255) / 256), 256, 0, stream>>>(
         static_cast<const __nv_bfloat16*>(a), lda, static_cast<uint32_t>(M), static_cast<uint32_t>(K), a0, a1, sfa);
     if (cudaError_t err = cudaGetLastError(); err != cudaSuccess)
         return release(host::fail(NVFP4_E_CUDA, "activation quantisation launch failed: %s", cudaGetErrorString(err)));
@@ -516,7 +517,7 @@ int launch_variant(const void* a, int64_t lda, const void* b, const void* sfb, i
 // Two launches: activations -> NVFP4 workspace, then the block-scaled GEMM over it.  N % 256 == 0.
 int launch_gemm_split(const void* a, int64_t lda, const void* b, const void* sfb, const float* gw, void* d,
                       int64_t ldd, const int32_t* m_indices, int M, int N, int K, int E, bool residual,
-                      int block_k, int group_m, bool pdl, int num_sms, int32_t* status, cudaStream_t stream)
+                      int block_k, int group_m, bool pdl, int policy, int num_sms, int32_t* status, cudaStream_t stream)
 {
     Params p;
     p.gw = gw;
@@ -530,13 +531,13 @@ int launch_gemm_split(const void* a, int64_t lda, const void* b, const void* sfb
     // block_k: 0 = the library's choice, 256 = one 256-wide K block per ring position, 128 = 128-wide with a commit
     // per position, 130 = 128-wide in groups of two (requested and freed together, consumed one by one)
     if (block_k == 130)
-        return residual ? launch_variant<128, true, 2>(a, lda, b, sfb, M, N, K, E, p, pdl, num_sms, stream)
-                        : launch_variant<128, false, 2>(a, lda, b, sfb, M, N, K, E, p, pdl, num_sms, stream);
+        return residual ? launch_variant<128, true, 2>(a, lda, b, sfb, M, N, K, E, p, pdl, policy, num_sms, stream)
+                        : launch_variant<128, false, 2>(a, lda, b, sfb, M, N, K, E, p, pdl, policy, num_sms, stream);
     if (K % 256 == 0 && block_k != 128)
-        return residual ? launch_variant<256, true, 1>(a, lda, b, sfb, M, N, K, E, p, pdl, num_sms, stream)
-                        : launch_variant<256, false, 1>(a, lda, b, sfb, M, N, K, E, p, pdl, num_sms, stream);
-    return residual ? launch_variant<128, true, 1>(a, lda, b, sfb, M, N, K, E, p, pdl, num_sms, stream)
-                    : launch_variant<128, false, 1>(a, lda, b, sfb, M, N, K, E, p, pdl, num_sms, stream);
+        return residual ? launch_variant<256, true, 1>(a, lda, b, sfb, M, N, K, E, p, pdl, policy, num_sms, stream)
+                        : launch_variant<256, false, 1>(a, lda, b, sfb, M, N, K, E, p, pdl, policy, num_sms, stream);
+    return residual ? launch_variant<128, true, 1>(a, lda, b, sfb, M, N, K, E, p, pdl, policy, num_sms, stream)
+                    : launch_variant<128, false, 1>(a, lda, b, sfb, M, N, K, E, p, pdl, policy, num_sms, stream);
 }
 
 #ifdef NVFP4_PROBE

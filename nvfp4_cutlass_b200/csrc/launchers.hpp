@@ -7,7 +7,8 @@ namespace nvfp4 {
 
 int launch_gemm_normal(const void* a, int64_t lda, const void* b, const void* sfb, const float* gw, void* d,
                        int64_t ldd, const int32_t* m_indices, int M, int N, int K, int E, bool residual,
-                       int xform_warps, int group_m, bool direct_a, int num_sms, int32_t* status, cudaStream_t stream);
+                       int xform_warps, int group_m, bool direct_a, int policy, int num_sms, int32_t* status,
+                       cudaStream_t stream);
 
 // Cluster variant of the normal orientation (cluster = 2 or 4, N % (256 * cluster) == 0).
 int launch_gemm_cluster(const void* a, int64_t lda, const void* b, const void* sfb, const float* gw, void* d,
@@ -16,7 +17,7 @@ int launch_gemm_cluster(const void* a, int64_t lda, const void* b, const void* s
 
 int launch_gemm_split(const void* a, int64_t lda, const void* b, const void* sfb, const float* gw, void* d,
                       int64_t ldd, const int32_t* m_indices, int M, int N, int K, int E, bool residual,
-                      int block_k, int group_m, bool pdl, int num_sms, int32_t* status, cudaStream_t stream);
+                      int block_k, int group_m, bool pdl, int policy, int num_sms, int32_t* status, cudaStream_t stream);
 
 int launch_permute_rows(const void* src, int64_t src_ld_bytes, const int64_t* src_idx, int src_div, const int64_t* dst_idx,
                         int64_t n_rows, int row_bytes, void* dst, int64_t dst_ld_bytes, int num_sms, cudaStream_t stream);
@@ -45,7 +46,7 @@ int launch_quantize_weight(const void* w, int w_dtype, int E, int N, int K, void
 int launch_quantize_weight_static(const void* w, int w_dtype, int E, int N, int K, void* b, void* sfb, float* gw,
                                   cudaStream_t stream);
 
-int launch_debug_decompose(const void* a, int64_t lda, int M, int K, void* q0, void* q1, void* s0, void* s1,
+int launch_debug_decompose(const void* a, int64_t lda, int M, int K, int policy, void* q0, void* q1, void* s0, void* s1,
                            cudaStream_t stream);
 
 int launch_mma_peak(int iters, int num_sms, double* flops_per_launch, cudaStream_t stream);

@@ -15,6 +15,8 @@
 // r_hi within a few ulp of 1/s0 (checked exhaustively over all BF16 x and all E4M3
 // s0, with r_hi perturbed by +-2 ulp), so the approximate reciprocal is enough.
 #pragma once
+#include <cuda_fp16.h>
+
 #include "ptx.cuh"
 
 namespace nvfp4::xform {
@@ -74,9 +76,19 @@ struct Block16 {
     uint32_t s1;
 };
 
-template <bool kResidual>
+// E4M3 byte -> FP32, subnormals included (only the residual_amax policy can produce them)
+NVFP4_DEVICE float e4m3_to_f32(uint32_t c)
+{
+    return c < 8u ? static_cast<float>(c) * 0.001953125f : __uint_as_float((c << 20) + 0x3C000000u);
+}
+
+// kPolicy 0 = derived_div8: s1 = Q_e4m3(s0 / 8), q1 = Q((u - q0) * 8), s0 floored at 2^-6.
+// kPolicy 1 = residual_amax: r = x - q0 * s0 (exact in FP32), s1 = Q_e4m3(max(amax(r) / 6, 2^-9)), q1 = Q(r / s1),
+//             s0 floored at 2^-9 (tests/python/reference/dual_nvfp4.py:131-152 of the reference).
+template <bool kResidual, int kPolicy = 0>
 NVFP4_DEVICE void decompose_block16(const uint32_t (&w)[8], Block16& out)
 {
+    static_assert(kPolicy == 0 || kPolicy == 1, "scale policy");
 #ifdef NVFP4_ABLATE_XFORM   // timing experiments only (wrong results); never defined in the shipped build
     out.q0[0] = w[0] ^ w[1]; out.q0[1] = w[2] ^ w[3]; out.q1[0] = w[4] ^ w[5]; out.q1[1] = w[6] ^ w[7];
     out.s0 = 0x38; out.s1 = 0x20;
@@ -93,12 +105,12 @@ NVFP4_DEVICE void decompose_block16(const uint32_t (&w)[8], Block16& out)
     m0 = ptx::max_abs_bf16x2(m0, m0 >> 16);
     const float amax = __uint_as_float((m0 & 0x7fffu) << 16);
 
-    // s0 = Q_e4m3(max(amax * fl(1/6), 2^-6)); always a normal E4M3 value
-    const float s0_pre = fmaxf(__fmul_rn(amax, 0.16666667163372040f), 0.015625f);
+    // s0 = Q_e4m3(max(amax * fl(1/6), floor)); with the 2^-6 floor always a normal E4M3 value
+    const float s0_pre = fmaxf(__fmul_rn(amax, 0.16666667163372040f), kPolicy == 0 ? 0.015625f : 0.001953125f);
     const uint32_t s0c = ptx::cvt_e4m3(s0_pre);
-    const float s0 = __uint_as_float((s0c << 20) + 0x3C000000u);
+    const float s0 = kPolicy == 0 ? __uint_as_float((s0c << 20) + 0x3C000000u) : e4m3_to_f32(s0c);
     out.s0 = s0c;
-    out.s1 = ptx::cvt_e4m3(__fmul_rn(s0, 0.125f));
+    out.s1 = kPolicy == 0 ? ptx::cvt_e4m3(__fmul_rn(s0, 0.125f)) : 0u;
 
     // u = x / s0 as the correctly rounded quotient: r_hi ~ 1 / s0, r_lo = its error term formed exactly by one FMA
     const float r_hi = ptx::rcp_approx(s0);
@@ -115,7 +127,31 @@ NVFP4_DEVICE void decompose_block16(const uint32_t (&w)[8], Block16& out)
     out.q0[0] = ptx::cvt_e2m1x8(u[0], u[1], u[2], u[3], u[4], u[5], u[6], u[7]);
     out.q0[1] = ptx::cvt_e2m1x8(u[8], u[9], u[10], u[11], u[12], u[13], u[14], u[15]);
 
-    if constexpr (kResidual) {
+    if constexpr (kResidual && kPolicy == 1) {
+        // r = x - dec(q0) * s0: the product has at most 7 significant bits and x has 8, so the FMA is exact;
+        // dec(q0) comes back as FP16 and s0 (>= 2^-9) is an FP16 value too
+        const unsigned short neg_s0 = __half_as_ushort(__float2half_rn(-s0));
+        float r[16];
+        float rmax = 0.0f;
+#pragma unroll
+        for (int i = 0; i < 8; ++i) {
+            const uint32_t byte = (out.q0[i >> 2] >> (8 * (i & 3))) & 0xffu;
+            const uint32_t d = ptx::cvt_e2m1x2_to_f16x2(byte);
+            r[2 * i] = ptx::fma_f32_f16(static_cast<unsigned short>(d & 0xffffu), neg_s0, __uint_as_float(w[i] << 16));
+            r[2 * i + 1] = ptx::fma_f32_f16(static_cast<unsigned short>(d >> 16), neg_s0, __uint_as_float(w[i] & 0xffff0000u));
+            rmax = fmaxf(rmax, fmaxf(fabsf(r[2 * i]), fabsf(r[2 * i + 1])));
+        }
+        const uint32_t s1c = ptx::cvt_e4m3(fmaxf(__fmul_rn(rmax, 0.16666667163372040f), 0.001953125f));
+        const float s1 = e4m3_to_f32(s1c);
+        out.s1 = s1c;
+        // q1 = Q(r / s1), the quotient correctly rounded as for u
+        const float t_hi = ptx::rcp_approx(s1);
+        const float t_lo = __fmul_rn(__fmaf_rn(-s1, t_hi, 1.0f), t_hi);
+#pragma unroll
+        for (int i = 0; i < 16; ++i) r[i] = __fmaf_rn(r[i], t_hi, __fmul_rn(r[i], t_lo));
+        out.q1[0] = ptx::cvt_e2m1x8(r[0], r[1], r[2], r[3], r[4], r[5], r[6], r[7]);
+        out.q1[1] = ptx::cvt_e2m1x8(r[8], r[9], r[10], r[11], r[12], r[13], r[14], r[15]);
+    } else if constexpr (kResidual) {
         // r = (u - dec(q0)) * 8 = 8u + dec(q0) * (-8): exact, the decode comes back as FP16
         float r[16];
 #pragma unroll
@@ -197,7 +233,8 @@ NVFP4_DEVICE void load_tile_global(TileShare<kRows, kBK, kThreads>& s, const voi
     }
 }
 
-template <uint32_t kRows, uint32_t kBK, uint32_t kThreads, bool kResidual, uint32_t kSfCols = 4, uint32_t kSubRows = 0>
+template <uint32_t kRows, uint32_t kBK, uint32_t kThreads, bool kResidual, uint32_t kSfCols = 4, uint32_t kSubRows = 0,
+          int kPolicy = 0>
 NVFP4_DEVICE void emit_tile(const TileShare<kRows, kBK, kThreads>& s, uint32_t a0_smem, uint32_t a1_smem,
                             uint32_t sfa0_smem, uint32_t sfa1_smem, uint32_t t)
 {
@@ -208,7 +245,7 @@ NVFP4_DEVICE void emit_tile(const TileShare<kRows, kBK, kThreads>& s, uint32_t a
 
     if constexpr (kBlocksPerThread == 1) {
         Block16 blk;
-        decompose_block16<kResidual>(s.w[0], blk);
+        decompose_block16<kResidual, kPolicy>(s.w[0], blk);
         const uint32_t off = fp4_offset<kBK, kSubRows>(row, (first_block * 16u) & ~31u) + ((first_block & 1u) << 3);
         ptx::sts64(a0_smem + off, blk.q0[0], blk.q0[1]);
         if constexpr (kResidual) ptx::sts64(a1_smem + off, blk.q1[0], blk.q1[1]);
@@ -220,8 +257,8 @@ NVFP4_DEVICE void emit_tile(const TileShare<kRows, kBK, kThreads>& s, uint32_t a
 #pragma unroll
         for (uint32_t pair = 0; pair < kBlocksPerThread / 2; ++pair) {
             Block16 blk[2];
-            decompose_block16<kResidual>(s.w[pair * 2], blk[0]);
-            decompose_block16<kResidual>(s.w[pair * 2 + 1], blk[1]);
+            decompose_block16<kResidual, kPolicy>(s.w[pair * 2], blk[0]);
+            decompose_block16<kResidual, kPolicy>(s.w[pair * 2 + 1], blk[1]);
             // two blocks = 32 elements = one 16-byte chunk of each packed row
             const uint32_t off = fp4_offset<kBK, kSubRows>(row, (first_block + pair * 2) * 16u);
             ptx::sts128(a0_smem + off, blk[0].q0[0], blk[0].q0[1], blk[1].q0[0], blk[1].q0[1]);
@@ -248,14 +285,14 @@ NVFP4_DEVICE void emit_tile(const TileShare<kRows, kBK, kThreads>& s, uint32_t a
 // Shared-memory tile in, products out; `on_loaded()` runs between the reads and the
 // arithmetic (the caller releases the BF16 slot there).
 template <uint32_t kRows, uint32_t kBK, uint32_t kThreads, bool kResidual, uint32_t kSfCols = 4, uint32_t kSubRows = 0,
-          typename OnLoaded>
+          int kPolicy = 0, typename OnLoaded>
 NVFP4_DEVICE void transform_tile(uint32_t a_smem, uint32_t a0_smem, uint32_t a1_smem, uint32_t sfa0_smem,
                                  uint32_t sfa1_smem, uint32_t t, OnLoaded&& on_loaded)
 {
     TileShare<kRows, kBK, kThreads> s;
     load_tile_smem(s, a_smem, t);
     on_loaded();
-    emit_tile<kRows, kBK, kThreads, kResidual, kSfCols, kSubRows>(s, a0_smem, a1_smem, sfa0_smem, sfa1_smem, t);
+    emit_tile<kRows, kBK, kThreads, kResidual, kSfCols, kSubRows, kPolicy>(s, a0_smem, a1_smem, sfa0_smem, sfa1_smem, t);
 }
 
 }  // namespace nvfp4::xform

@@ -75,45 +75,53 @@ def test_weight_quantiser_fp32_input_and_zero_expert(dev, oracle):
 
 
 # ---------------------------------------------------------------- Algorithm 1
-def check_decompose(dev, oracle, a):
-    q0, q1, s0, s1 = _C.debug_decompose(a.to(dev))
-    o0, o1, os0, os1 = oracle.decompose(a)
+POLICIES = ["derived_div8", "residual_amax"]
+
+
+def check_decompose(dev, oracle, a, policy="derived_div8"):
+    q0, q1, s0, s1 = _C.debug_decompose(a.to(dev), scale_policy=policy)
+    o0, o1, os0, os1 = oracle.decompose(a, scale_policy=policy)
     assert torch.equal(s0.cpu(), os0), "s0 bytes differ"
     assert torch.equal(s1.cpu(), os1), "s1 bytes differ"
     assert torch.equal(grid_i8_from_codes(unpack_codes(q0)), grid_i8_from_codes(o0)), "q0 differs"
     assert torch.equal(grid_i8_from_codes(unpack_codes(q1)), grid_i8_from_codes(o1)), "q1 differs"
 
 
-def test_decompose_bit_exact_golden(dev, oracle):
+@pytest.mark.parametrize("policy", POLICIES)
+def test_decompose_bit_exact_golden(dev, oracle, policy):
     g = load_golden("decompose.npz")
     a = bf16_from_bits(g["a_bits"])                          # 42 x 256, incl. adversarial rows
     a = torch.cat([a, torch.zeros(128 - a.shape[0], a.shape[1], dtype=torch.bfloat16)])
-    q0, q1, s0, s1 = _C.debug_decompose(a.to(dev))
+    q0, q1, s0, s1 = _C.debug_decompose(a.to(dev), scale_policy=policy)
     n = g["a_bits"].shape[0]
-    assert torch.equal(s0.cpu()[:n], torch.from_numpy(g["derived_div8_s0"]))
-    assert torch.equal(s1.cpu()[:n], torch.from_numpy(g["derived_div8_s1"]))
-    assert torch.equal(grid_i8_from_codes(unpack_codes(q0))[:n], torch.from_numpy(g["derived_div8_q0"]))
-    assert torch.equal(grid_i8_from_codes(unpack_codes(q1))[:n], torch.from_numpy(g["derived_div8_q1"]))
+    assert torch.equal(s0.cpu()[:n], torch.from_numpy(g[policy + "_s0"]))
+    assert torch.equal(s1.cpu()[:n], torch.from_numpy(g[policy + "_s1"]))
+    assert torch.equal(grid_i8_from_codes(unpack_codes(q0))[:n], torch.from_numpy(g[policy + "_q0"]))
+    assert torch.equal(grid_i8_from_codes(unpack_codes(q1))[:n], torch.from_numpy(g[policy + "_q1"]))
 
 
-def test_decompose_bit_exact_c1_and_distributions(dev, oracle):
+@pytest.mark.parametrize("policy", POLICIES)
+def test_decompose_bit_exact_c1_and_distributions(dev, oracle, policy):
     g = torch.Generator().manual_seed(0)
     a = torch.randn(256, 1024, generator=g).to(torch.bfloat16)                       # config C1 activations
-    check_decompose(dev, oracle, a)
+    check_decompose(dev, oracle, a, policy)
     a = (torch.randn(256, 512, generator=g) * torch.exp(0.5 * torch.randn(256, 1, generator=g))).to(torch.bfloat16)
-    check_decompose(dev, oracle, a)
+    check_decompose(dev, oracle, a, policy)
     t = torch.randn(128, 512, generator=g) / torch.sqrt(torch.randn(128, 512, 4, generator=g).pow(2).mean(-1))
-    check_decompose(dev, oracle, t.clamp(-2688, 2688).to(torch.bfloat16))            # Student-t(4)
+    check_decompose(dev, oracle, t.clamp(-2688, 2688).to(torch.bfloat16), policy)    # Student-t(4)
     a = torch.randn(128, 1024, generator=g)
     a[:, torch.randperm(1024, generator=g)[:2]] *= 50.0                               # outlier channels
-    check_decompose(dev, oracle, a.to(torch.bfloat16))
+    check_decompose(dev, oracle, a.to(torch.bfloat16), policy)
+    a = torch.randn(128, 256, generator=g) * 1e-3                                     # tiny blocks: the scale floors
+    check_decompose(dev, oracle, a.to(torch.bfloat16), policy)
 
 
-def test_decompose_bit_exact_every_scale_and_value(dev, oracle):
+@pytest.mark.parametrize("policy", POLICIES)
+def test_decompose_bit_exact_every_scale_and_value(dev, oracle, policy):
     """Every E4M3 scale the floor allows x every BF16 magnitude up to the block maximum:
     each 16-block carries one element that pins s0 and fifteen probe values."""
     blocks = []
-    for code in range(0x08, 0x7F):
+    for code in range(0x08 if policy == "derived_div8" else 0x01, 0x7F):
         s0 = torch.tensor([code], dtype=torch.uint8).view(torch.float8_e4m3fn).float().item()
         top = torch.tensor(6.0 * s0).to(torch.bfloat16)
         bits = torch.arange(0, int(top.view(torch.int16).item()) + 1, 7, dtype=torch.int32)
@@ -127,7 +135,7 @@ def test_decompose_bit_exact_every_scale_and_value(dev, oracle):
     k = 1024
     pad = (-flat.numel()) % (128 * k)
     a = torch.cat([flat, torch.zeros(pad)]).reshape(-1, k).to(torch.bfloat16)
-    check_decompose(dev, oracle, a)
+    check_decompose(dev, oracle, a, policy)
 
 
 # ---------------------------------------------------------------- GEMM
@@ -304,6 +312,34 @@ def test_split_path_on_two_streams_at_once(dev, oracle):
     for i in range(2):
         want = oracle.grouped_gemm(cases[i][0], quant[i][0].cpu(), quant[i][1].cpu(), quant[i][2].cpu(), mi, n)
         assert rel_l2(outs[i].cpu(), want) < REL_L2_VS_ORACLE
+
+
+@pytest.mark.parametrize("shape", [(1, 128, 128, 256), (2, 128, 256, 512), (4, 256, 1024, 2048), (4, 512, 2048, 512), (3, 128, 384, 256)])
+@pytest.mark.parametrize("residual", [True, False])
+def test_gemm_residual_amax_policy_matches_oracle(dev, oracle, shape, residual):
+    """scale_policy="residual_amax" on the reference's acceptance shapes (tests/python/test_gemm.py:31-36 there): the
+    split path for N % 256 == 0 and N >= 1024, the single-CTA fused kernel otherwise."""
+    e, rows, n, k = shape
+    a, w = make_case(e, rows, n, k, seed=900 + n + k)
+    b, sfb, gw = nvfp4_gemm.quantize_weight_nvfp4(w.to(dev))
+    mi = nvfp4_gemm.make_m_indices([rows] * e)
+    d = run_gemm(dev, a, b, sfb, gw, mi, n, enable_residual_pass=residual, scale_policy="residual_amax")
+    want = oracle.grouped_gemm(a, b.cpu(), sfb.cpu(), gw.cpu(), mi, n, mode="dual" if residual else "single",
+                               scale_policy="residual_amax")
+    truth = oracle.grouped_gemm(a, b.cpu(), sfb.cpu(), gw.cpu(), mi, n, mode="truth")
+    assert rel_l2(d, want) < REL_L2_VS_ORACLE
+    if residual:
+        assert cosine(d, truth) > 0.999
+        div8 = run_gemm(dev, a, b, sfb, gw, mi, n)
+        assert rel_l2(d, truth) <= rel_l2(div8, truth) * 1.05       # the second amax pass buys accuracy
+
+
+def test_residual_amax_is_refused_for_swap_ab(dev):
+    a, w = make_case(1, 128, 128, 256, seed=1)
+    b, sfb, gw = nvfp4_gemm.quantize_weight_nvfp4(w.to(dev))
+    mi = nvfp4_gemm.make_m_indices([128])
+    with pytest.raises(RuntimeError, match="swap-AB"):
+        run_gemm(dev, a, b, sfb, gw, mi, 128, tune_swap_ab=1, m_alignment=128, scale_policy="residual_amax")
 
 
 def test_gemm_many_tiles_ragged_experts(dev, oracle):
