@@ -37,8 +37,8 @@ enum {
     NVFP4_E_DEVICE_TIMEOUT = 4     /* a bounded in-kernel wait expired (see nvfp4_read_status) */
 };
 
-/* activation scale policies (reference: src/api.hpp:106-112, transform/dual_nvfp4.cuh:31-61).  derived_div8 is built
- * for every kernel, residual_amax for the normal orientation; anything else returns NVFP4_E_UNSUPPORTED. */
+/* activation scale policies (reference: src/api.hpp:106-112, transform/dual_nvfp4.cuh:31-61).  derived_div8 and
+ * residual_amax are built (both orientations); anything else returns NVFP4_E_UNSUPPORTED. */
 enum { NVFP4_POLICY_DERIVED_DIV8 = 0, NVFP4_POLICY_RESIDUAL_AMAX = 1 };
 /* operand orientation (reference: tune_swap_ab, src/api.hpp:84-104) */
 enum { NVFP4_ORIENT_NORMAL = 0, NVFP4_ORIENT_SWAP_AB = 1 };

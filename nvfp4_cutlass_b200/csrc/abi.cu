@@ -174,8 +174,6 @@ int nvfp4_grouped_gemm_contiguous(const void* a, int64_t lda_elems, const void* 
     NVFP4_REQUIRE((reinterpret_cast<uintptr_t>(d) & 15u) == 0, "d must be 16-byte aligned");
     if (scale_policy != NVFP4_POLICY_DERIVED_DIV8 && scale_policy != NVFP4_POLICY_RESIDUAL_AMAX)
         return host::fail(NVFP4_E_UNSUPPORTED, "scale policy %d is not built; derived_div8 and residual_amax are", scale_policy);
-    if (scale_policy == NVFP4_POLICY_RESIDUAL_AMAX && orientation == NVFP4_ORIENT_SWAP_AB)
-        return host::fail(NVFP4_E_UNSUPPORTED, "residual_amax is not built for the swap-AB orientation");
 
     host::DeviceInfo* dev;
     if (int rc = host::device_info(-1, &dev)) return rc;
@@ -195,7 +193,7 @@ int nvfp4_grouped_gemm_contiguous(const void* a, int64_t lda_elems, const void* 
         NVFP4_REQUIRE(tune_block_k == 0 || tune_block_k == 128 || tune_block_k == 256 || tune_block_k == 512,
                       "tune_block_k must be 0, 128, 256 or 512");
         return launch_gemm_swap(a, lda_elems, b, sfb, gw, d, ldd_elems, m_indices, M, N, K, E, enable_residual_pass != 0,
-                                tile, tune_block_k, dev->num_sms, device_status, s);
+                                tile, tune_block_k, scale_policy, dev->num_sms, device_status, s);
     }
     NVFP4_REQUIRE(tune_xform_warps == 0 || tune_xform_warps == 8 || tune_xform_warps == 16,
                   "tune_transform_warps must be 0, 8 or 16");

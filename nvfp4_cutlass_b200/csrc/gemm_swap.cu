@@ -97,7 +97,7 @@ struct Ring {
     }
 };
 
-template <uint32_t T, uint32_t BK, bool kResidual>
+template <uint32_t T, uint32_t BK, bool kResidual, int kPolicy>
 __global__ void __launch_bounds__(kThreads, 1)
 gemm_swap_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constant__ CUtensorMap tm_w,
                  const __grid_constant__ CUtensorMap tm_sfw, const Params p)
@@ -331,7 +331,7 @@ gemm_swap_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constant
             for (uint32_t kb = 0; kb < num_kb; ++kb, ++cnt) {
                 if (!ptx::mbar_wait(a_full + ra.slot, ra.phase, abort_flag, pa, 0)) { give_up(1); break; }
                 bool p_ok = true;
-                xform::transform_tile<T, BK, kXformThreads, kResidual, C::kSfCols, C::kRowsP>(
+                xform::transform_tile<T, BK, kXformThreads, kResidual, C::kSfCols, C::kRowsP, kPolicy>(
                     smem + C::kOffA + ra.slot * C::kSlotA, smem + C::kOffP + rp.slot * C::kSlotP,
                     smem + C::kOffP + rp.slot * C::kSlotP + C::kA1Bytes, smem + C::kOffSFT + rp.slot * C::kSlotSFT,
                     smem + C::kOffSFT + rp.slot * C::kSlotSFT + C::kSF1Bytes, t, [&] {
@@ -367,7 +367,7 @@ gemm_swap_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constant
     }
 }
 
-template <uint32_t T, uint32_t BK, bool kResidual>
+template <uint32_t T, uint32_t BK, bool kResidual, int kPolicy = 0>
 int launch_variant(const void* a, int64_t lda, const void* b, const void* sfb, int M, int N, int K, int E,
                    const Params& p, int num_sms, cudaStream_t stream)
 {
@@ -383,7 +383,7 @@ int launch_variant(const void* a, int64_t lda, const void* b, const void* sfb, i
                                     static_cast<uint64_t>(E) * (K / 64), static_cast<uint64_t>(N) * 4, BW, C::kAtoms,
                                     CU_TENSOR_MAP_SWIZZLE_NONE);
     if (rc) return rc;
-    auto kernel = gemm_swap_kernel<T, BK, kResidual>;
+    auto kernel = gemm_swap_kernel<T, BK, kResidual, kPolicy>;
     static bool attr_set[host::kMaxDevices] = {};
     int dev = 0;
     NVFP4_CUDA_CHECK(cudaGetDevice(&dev));
@@ -400,8 +400,20 @@ int launch_variant(const void* a, int64_t lda, const void* b, const void* sfb, i
 
 template <uint32_t T>
 int launch_for_tile(const void* a, int64_t lda, const void* b, const void* sfb, int M, int N, int K, int E,
-                    const Params& p, bool residual, int block_k, int num_sms, cudaStream_t stream)
+                    const Params& p, bool residual, int block_k, int policy, int num_sms, cudaStream_t stream)
 {
+    if (policy == 1) {    // residual_amax: the default K-block choice only
+        if constexpr (T <= 32) {
+            if (K % 512 == 0)
+                return residual ? launch_variant<T, 512, true, 1>(a, lda, b, sfb, M, N, K, E, p, num_sms, stream)
+                                : launch_variant<T, 512, false, 1>(a, lda, b, sfb, M, N, K, E, p, num_sms, stream);
+        }
+        if (K % 256 == 0)
+            return residual ? launch_variant<T, 256, true, 1>(a, lda, b, sfb, M, N, K, E, p, num_sms, stream)
+                            : launch_variant<T, 256, false, 1>(a, lda, b, sfb, M, N, K, E, p, num_sms, stream);
+        return residual ? launch_variant<T, 128, true, 1>(a, lda, b, sfb, M, N, K, E, p, num_sms, stream)
+                        : launch_variant<T, 128, false, 1>(a, lda, b, sfb, M, N, K, E, p, num_sms, stream);
+    }
     // K blocks of 512 halve the per-block barrier traffic and commits; a 64-token tile has no room for them
     if constexpr (T <= 32) {
         if (K % 512 == 0 && (block_k == 0 || block_k == 512))
@@ -421,7 +433,7 @@ int launch_for_tile(const void* a, int64_t lda, const void* b, const void* sfb, 
 // multiple of it, which the caller guarantees through m_alignment % token_tile == 0.
 int launch_gemm_swap(const void* a, int64_t lda, const void* b, const void* sfb, const float* gw, void* d,
                      int64_t ldd, const int32_t* m_indices, int M, int N, int K, int E, bool residual,
-                     int token_tile, int block_k, int num_sms, int32_t* status, cudaStream_t stream)
+                     int token_tile, int block_k, int policy, int num_sms, int32_t* status, cudaStream_t stream)
 {
     Params p;
     p.gw = gw;
@@ -431,9 +443,9 @@ int launch_gemm_swap(const void* a, int64_t lda, const void* b, const void* sfb,
     p.m = M; p.n = N; p.k = K;
     p.status = status;
     switch (token_tile) {
-        case 16: return launch_for_tile<16>(a, lda, b, sfb, M, N, K, E, p, residual, block_k, num_sms, stream);
-        case 32: return launch_for_tile<32>(a, lda, b, sfb, M, N, K, E, p, residual, block_k, num_sms, stream);
-        case 64: return launch_for_tile<64>(a, lda, b, sfb, M, N, K, E, p, residual, block_k, num_sms, stream);
+        case 16: return launch_for_tile<16>(a, lda, b, sfb, M, N, K, E, p, residual, block_k, policy, num_sms, stream);
+        case 32: return launch_for_tile<32>(a, lda, b, sfb, M, N, K, E, p, residual, block_k, policy, num_sms, stream);
+        case 64: return launch_for_tile<64>(a, lda, b, sfb, M, N, K, E, p, residual, block_k, policy, num_sms, stream);
         default: return host::fail(NVFP4_E_INVALID_ARGUMENT, "token tile %d is not 16, 32 or 64", token_tile);
     }
 }

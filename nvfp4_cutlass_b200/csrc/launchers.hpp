@@ -38,7 +38,7 @@ int launch_combine_rows_peer(const int64_t* peers, int64_t rows_ld_elems, const 
 
 int launch_gemm_swap(const void* a, int64_t lda, const void* b, const void* sfb, const float* gw, void* d,
                      int64_t ldd, const int32_t* m_indices, int M, int N, int K, int E, bool residual,
-                     int token_tile, int block_k, int num_sms, int32_t* status, cudaStream_t stream);
+                     int token_tile, int block_k, int policy, int num_sms, int32_t* status, cudaStream_t stream);
 
 int launch_quantize_weight(const void* w, int w_dtype, int E, int N, int K, void* b, void* sfb, float* gw,
                            cudaStream_t stream);

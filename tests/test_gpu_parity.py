@@ -334,12 +334,17 @@ def test_gemm_residual_amax_policy_matches_oracle(dev, oracle, shape, residual):
         assert rel_l2(d, truth) <= rel_l2(div8, truth) * 1.05       # the second amax pass buys accuracy
 
 
-def test_residual_amax_is_refused_for_swap_ab(dev):
-    a, w = make_case(1, 128, 128, 256, seed=1)
+@pytest.mark.parametrize("case", [([16, 48, 16, 32], 16, 384, 1024), ([64, 128], 64, 256, 384), ([32] * 4, 32, 512, 2048)])
+def test_gemm_swap_ab_residual_amax_matches_oracle(dev, oracle, case):
+    sizes, align, n, k = case
+    g = torch.Generator().manual_seed(6000 + n + k)
+    a = torch.randn(sum(sizes), k, generator=g).to(torch.bfloat16)
+    w = (torch.randn(len(sizes), n, k, generator=g) * 0.02).to(torch.bfloat16)
     b, sfb, gw = nvfp4_gemm.quantize_weight_nvfp4(w.to(dev))
-    mi = nvfp4_gemm.make_m_indices([128])
-    with pytest.raises(RuntimeError, match="swap-AB"):
-        run_gemm(dev, a, b, sfb, gw, mi, 128, tune_swap_ab=1, m_alignment=128, scale_policy="residual_amax")
+    mi = nvfp4_gemm.make_m_indices(sizes, alignment=align)
+    d = run_gemm(dev, a, b, sfb, gw, mi, n, tune_swap_ab=1, m_alignment=align, scale_policy="residual_amax")
+    want = oracle.grouped_gemm(a, b.cpu(), sfb.cpu(), gw.cpu(), mi, n, scale_policy="residual_amax")
+    assert rel_l2(d, want) < REL_L2_VS_ORACLE
 
 
 def test_gemm_many_tiles_ragged_experts(dev, oracle):
