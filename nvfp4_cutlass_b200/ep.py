@@ -221,6 +221,14 @@ class ExpertParallelMoE:
                                         self.world)
             except Exception as exc:                                   # symmetric memory unavailable: keep the NCCL path
                 self.peer_error = repr(exc)
+            if self.world > 1:
+                # every rank must take the same path: one rank without buffers sends all of them to the all-to-all
+                ok = torch.tensor([1 if self.peer is not None else 0], dtype=torch.int32,
+                                  device=torch.device("cuda", torch.cuda.current_device()))
+                dist.all_reduce(ok, op=dist.ReduceOp.MIN, group=group)
+                if int(ok.item()) == 0 and self.peer is not None:
+                    self.peer = None
+                    self.peer_error = "symmetric memory unavailable on another rank"
         self.last = None                       # Dispatch of the most recent call (for accounting)
 
     def dispatch(self, x: torch.Tensor, topk_ids: torch.Tensor):
