@@ -45,6 +45,9 @@ WORKLOADS = {
     **{f"qdec{t}": dict(E=32, N=1024, K=2048, decode_tokens=t,
                         desc=f"reference decode sweep gate_up: {t} tokens x top-8 of 256 experts, 32 local experts, N=1024, K=2048")
        for t in (16, 32, 128)},
+    # the up-projection of the expert-parallel layer (the dominant GEMM of config C5); the layer itself is built in
+    # nvfp4_cutlass_b200/ep_bench.py, this entry gives the CPU reference arm its shape
+    "c5": dict(E=128, N=3072, K=4096, desc="expert-parallel MoE layer (C5): up-projection E=128, N=3072, K=4096"),
     "c2s": dict(E=8, N=8192, K=4096, desc="reduced c2 for profiling: E=8 x 512 rows, N=8192, K=4096"),
     "c4s": dict(E=64, N=4096, K=7168, desc="reduced c4 for profiling: E=64, 16 tokens x top-8, N=4096, K=7168"),
 }
@@ -251,8 +254,11 @@ def run_reference_arm(args):
         return
     times = []
     base = None
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+    workload = args.workload or ("c2" if max(world, args.gpus) == 1 else "c5")      # the same default as the main arm
+    args.workload = workload
     for i in range(args.warmup + args.steps):
-        base = cpu_reference_sample(args.workload or "c2", seconds_target=6.0)
+        base = cpu_reference_sample(workload, seconds_target=6.0)
         if i >= args.warmup:
             times.append(base["value"])
     value = statistics.mean(times)
