@@ -4,20 +4,26 @@ The GEMM shards by expert: tiles of different experts never meet, so rank r of R
 experts [r*E/R, (r+1)*E/R) with their quantised weights resident, tokens stay data
 parallel, and there is one exchange before and one after the two GEMMs:
 
-  dispatch   every (token, chosen expert) pair is sent as one BF16 row to the rank that
-             owns the expert: one ``all_to_all_single`` with per-peer split sizes, after a
-             small all-to-all of the per-expert row counts
-  compute    the receiver lays the rows out expert by expert, each group padded to the
-             kernel's row alignment, and runs up-GEMM -> SwiGLU -> down-GEMM
-  combine    rows travel back through the reverse all-to-all and are summed per token
-             with the routing weights
+  dispatch   every (token, chosen expert) pair is one BF16 row that goes to the rank that
+             owns the expert, into that rank's expert-major buffer with every group padded
+             to the kernel's row alignment
+  compute    up-GEMM -> SwiGLU -> down-GEMM on the local buffer
+  combine    every token sums the outputs of its k experts with the routing weights
+
+Two ways to move the rows.  Peer memory (``peer_rows_cap > 0``; GPUs of one NVLink domain, or
+one rank): the ranks all-gather the (rank, expert) histograms, two plan kernels give every
+pair its row in the owner's buffer, one kernel stores the token rows straight into the
+owners' symmetric buffers and one kernel loads the k output rows of every token back from
+them; three stream-ordered barriers separate the phases.  All-to-all (the fallback, and the
+form the CPU tests run on gloo): counts all-to-all, gather, ``all_to_all_single`` with split
+sizes, scatter; the reverse for the combine.  Both build the same buffers.
 
 The reference project has no multi-GPU mode; this one follows the contiguous-layout
 contract of its GEMM (python/nvfp4_gemm/layout.py:155-169 there: rows grouped by expert,
 group starts aligned).  Collectives go through ``torch.distributed`` (NCCL over NVLink on
-GPUs, gloo in the CPU tests).  The routing plan is plain tensor code and runs on either; the
-row movement, SwiGLU and the weighted sum run as CUDA kernels of the library for CUDA tensors
-and as tensor operations for the CPU tests of the host logic.  The GEMM is injectable so that
+GPUs, gloo in the CPU tests).  Row movement, SwiGLU, the weighted sum and the peer-path plan
+run as CUDA kernels of the library for CUDA tensors and as tensor operations for the CPU
+tests of the host logic.  The GEMM is injectable so that
 the CPU tests can stand in a checker.
 """
 from __future__ import annotations
