@@ -116,6 +116,17 @@ NVFP4_API int nvfp4_grouped_gemm_contiguous(const void* a, int64_t lda_elems, co
                                   int m_alignment, const int32_t* tune, int32_t* device_status,
                                   void* stream);
 
+/* The down-projection of a SwiGLU expert MLP with the activation folded into the activation-quantisation kernel:
+ * d[M,N] = Q(silu(h[:, :K]) * h[:, K:]) * W^T * gw[expert], where h (M, 2 K) BF16 with row stride ldh_elems is the
+ * output of the fused gate+up projection, Q is Algorithm 1 (derived_div8) on the BF16-rounded products, and the
+ * other arguments are those of nvfp4_grouped_gemm_contiguous.  Same result, bit for bit, as nvfp4_swiglu followed
+ * by nvfp4_grouped_gemm_contiguous on the split path, without writing and re-reading the (M, K) BF16 activation.
+ * Normal orientation, N % 256 == 0, M % 128 == 0.  No counterpart in the reference (its benchmarks stop at the GEMM). */
+NVFP4_API int nvfp4_grouped_gemm_swiglu_contiguous(const void* h, int64_t ldh_elems, const void* b, const void* sfb,
+                                                   const float* gw, void* d, int64_t ldd_elems, const int32_t* m_indices,
+                                                   int M, int N, int K, int E, int enable_residual_pass,
+                                                   const int32_t* tune, int32_t* device_status, void* stream);
+
 /* Row movers and activation of the expert-parallel MoE layer around the GEMM (dispatch, SwiGLU, combine).
  * They have no counterpart in the reference project, which has no multi-GPU mode; they exist because the
  * contiguous layout the GEMM wants (rows grouped by expert, groups padded to the tile height) has to be

@@ -29,7 +29,8 @@ TUNE_KEYS = ("tune_block_n", "tune_transform_warps", "tune_epilogue_threads", "t
 EXPORTS = ("nvfp4_last_error", "nvfp4_version", "nvfp4_get_num_sms", "nvfp4_set_num_sms",
            "nvfp4_quantize_weight", "nvfp4_quantize_weight_static", "nvfp4_grouped_gemm_contiguous", "nvfp4_debug_decompose",
            "nvfp4_debug_mma_peak", "nvfp4_debug_mma_pattern", "nvfp4_permute_rows", "nvfp4_swiglu", "nvfp4_combine_rows",
-           "nvfp4_dispatch_rows_peer", "nvfp4_combine_rows_peer", "nvfp4_plan_peer", "nvfp4_expert_histogram")
+           "nvfp4_dispatch_rows_peer", "nvfp4_combine_rows_peer", "nvfp4_plan_peer", "nvfp4_expert_histogram",
+           "nvfp4_grouped_gemm_swiglu_contiguous")
 
 
 def library_path() -> str:
@@ -59,6 +60,7 @@ def lib() -> ctypes.CDLL:
         L.nvfp4_swiglu.argtypes = [vp, i64, i64, i32, vp, i64, vp]
         L.nvfp4_dispatch_rows_peer.argtypes = [vp, i64, vp, i32, vp, vp, vp, i64, i32, i64, vp]
         L.nvfp4_expert_histogram.argtypes = [vp, i64, i32, vp, vp]
+        L.nvfp4_grouped_gemm_swiglu_contiguous.argtypes = [vp, i64, vp, vp, vp, vp, i64, vp, i32, i32, i32, i32, i32, vp, vp, vp]
         L.nvfp4_plan_peer.argtypes = [vp, i32, i32, i32, i32, vp, i64, vp, vp, vp, vp]
         L.nvfp4_combine_rows_peer.argtypes = [vp, i64, vp, vp, vp, i64, i32, i32, vp, i64, vp]
         L.nvfp4_combine_rows.argtypes = [vp, i64, vp, vp, i64, i32, i32, vp, i64, vp]
@@ -201,6 +203,23 @@ def combine_rows(rows: torch.Tensor, pos: torch.Tensor, w: torch.Tensor, tokens:
 
 def _i64_ok(t: torch.Tensor, n: int) -> bool:
     return t.is_cuda and t.dtype == torch.int64 and t.is_contiguous() and t.numel() >= n
+
+
+def m_grouped_swiglu_dual_nvfp4_gemm_contiguous(h, b, sfb, gw, d, m_indices, enable_residual_pass: bool = True,
+                                                device_status=None) -> None:
+    """d = Q(silu(h[:, :K]) * h[:, K:]) @ W^T * gw[expert]: the down-projection of a SwiGLU expert MLP with the
+    activation folded into the activation-quantisation kernel (normal orientation, N % 256 == 0)."""
+    _require(_rows_ok(h) and _rows_ok(d) and h.shape[1] % 2 == 0, "h and d are 2-D BF16 CUDA tensors")
+    m, k = h.shape[0], h.shape[1] // 2
+    n, e = d.shape[1], gw.numel()
+    _require(d.shape[0] == m and b.shape == (e * n, k // 2) and sfb.shape == (e * (k // 64), n) and m_indices.numel() == m,
+             "operand shapes do not fit together")
+    _require(b.is_contiguous() and sfb.is_contiguous() and gw.is_contiguous() and m_indices.is_contiguous(),
+             "b, sfb, gw and m_indices are contiguous")
+    _check(lib().nvfp4_grouped_gemm_swiglu_contiguous(
+        h.data_ptr(), h.stride(0), b.data_ptr(), sfb.data_ptr(), gw.data_ptr(), d.data_ptr(), d.stride(0),
+        m_indices.data_ptr(), m, n, k, e, 1 if enable_residual_pass else 0, None,
+        device_status.data_ptr() if device_status is not None else None, _stream()))
 
 
 def expert_histogram(ids: torch.Tensor, num_experts: int) -> torch.Tensor:

@@ -210,7 +210,7 @@ int nvfp4_grouped_gemm_contiguous(const void* a, int64_t lda_elems, const void* 
     if (tune_split == 1 || (tune_split == 0 && !fused_knobs && N % 256 == 0 && N >= 1024)) {
         const int tune_block_k = tune ? tune[5] : 0;
         return launch_gemm_split(a, lda_elems, b, sfb, gw, d, ldd_elems, m_indices, M, N, K, E, enable_residual_pass != 0,
-                                 tune_block_k, tune_sched_group, !(tune && tune[11]), scale_policy, dev->num_sms, device_status, s);
+                                 tune_block_k, tune_sched_group, !(tune && tune[11]), scale_policy, false, dev->num_sms, device_status, s);
     }
     // residual_amax exists in the split path (above) and in the single-CTA fused kernel, not in the cluster kernel
     if (scale_policy == NVFP4_POLICY_RESIDUAL_AMAX)
@@ -278,6 +278,29 @@ int nvfp4_combine_rows(const void* rows, int64_t rows_ld_elems, const int64_t* p
     if (int rc = host::device_info(-1, &dev)) return rc;
     return launch_combine_rows(rows, rows_ld_elems, pos, w, tokens, k, hidden, y, y_ld_elems, dev->hw_sms,
                                static_cast<cudaStream_t>(stream));
+}
+
+int nvfp4_grouped_gemm_swiglu_contiguous(const void* h, int64_t ldh_elems, const void* b, const void* sfb, const float* gw, void* d,
+                                         int64_t ldd_elems, const int32_t* m_indices, int M, int N, int K, int E,
+                                         int enable_residual_pass, const int32_t* tune, int32_t* device_status, void* stream)
+{
+    host::clear_error();
+    NVFP4_REQUIRE(M >= 0 && N >= 0 && K >= 0 && E >= 0, "negative size");
+    NVFP4_REQUIRE(N % 256 == 0 && K % 128 == 0, "N must be a multiple of 256 and K of 128 (N=%d, K=%d)", N, K);
+    NVFP4_REQUIRE(M % 128 == 0, "M must be a multiple of 128 (M=%d)", M);
+    if (M == 0 || N == 0) return NVFP4_OK;
+    NVFP4_REQUIRE(E > 0 && K > 0, "empty weights (E=%d, K=%d)", E, K);
+    NVFP4_REQUIRE(h && b && sfb && gw && d && m_indices, "null pointer argument");
+    NVFP4_REQUIRE(ldh_elems >= 2 * static_cast<int64_t>(K) && ldd_elems >= N, "row strides too small (ldh=%lld, ldd=%lld)",
+                  static_cast<long long>(ldh_elems), static_cast<long long>(ldd_elems));
+    NVFP4_REQUIRE(ldh_elems % 8 == 0 && ldd_elems % 8 == 0, "row strides must be multiples of 8 elements (16 bytes)");
+    NVFP4_REQUIRE(((reinterpret_cast<uintptr_t>(h) | reinterpret_cast<uintptr_t>(d)) & 15u) == 0, "h and d must be 16-byte aligned");
+    host::DeviceInfo* dev;
+    if (int rc = host::device_info(-1, &dev)) return rc;
+    if (dev->cc_major != 10) return host::fail(NVFP4_E_UNSUPPORTED, "needs an sm_100 GPU, found sm_%d%d", dev->cc_major, dev->cc_minor);
+    return launch_gemm_split(h, ldh_elems, b, sfb, gw, d, ldd_elems, m_indices, M, N, K, E, enable_residual_pass != 0,
+                             tune ? tune[5] : 0, tune ? tune[12] : 0, !(tune && tune[11]), NVFP4_POLICY_DERIVED_DIV8, true,
+                             dev->num_sms, device_status, static_cast<cudaStream_t>(stream));
 }
 
 int nvfp4_expert_histogram(const int64_t* ids, int64_t n, int num_experts, int64_t* counts, void* stream)

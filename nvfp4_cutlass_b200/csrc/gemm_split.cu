@@ -39,7 +39,10 @@ constexpr uint32_t kSmemBudget = 232448 - 1024;
 // One thread per 16-element block; the four threads of a 64-K atom row combine their scale bytes into one
 // 32-bit store.
 // ---------------------------------------------------------------------------------------------------
-template <bool kResidual, int kPolicy>
+// With kSwiglu the activation is not read but made: `a` is the (M, 2 K) output of a fused gate+up projection and
+// element (row, j) is bf16(silu(a[row, j]) * a[row, K + j]) -- the same arithmetic and the same BF16 rounding as
+// the stand-alone SwiGLU kernel (moe_glue.cu), so the codes are those of the unfused sequence, bit for bit.
+template <bool kResidual, int kPolicy, bool kSwiglu = false>
 __global__ void __launch_bounds__(256)
 quantize_activation_kernel(const __nv_bfloat16* __restrict__ a, int64_t lda, uint32_t m, uint32_t k,
                            uint8_t* __restrict__ a0, uint8_t* __restrict__ a1, uint8_t* __restrict__ sfa)
@@ -61,6 +64,22 @@ quantize_activation_kernel(const __nv_bfloat16* __restrict__ a, int64_t lda, uin
                      : "=r"(hi.x), "=r"(hi.y), "=r"(hi.z), "=r"(hi.w) : "l"(src + 1));
         w[0] = lo.x; w[1] = lo.y; w[2] = lo.z; w[3] = lo.w;
         w[4] = hi.x; w[5] = hi.y; w[6] = hi.z; w[7] = hi.w;
+    }
+    if constexpr (kSwiglu) {
+        const uint4* up = reinterpret_cast<const uint4*>(a + static_cast<int64_t>(row) * lda + k + blk16 * 16);
+        uint4 lo, hi;
+        asm volatile("ld.global.nc.L1::no_allocate.v4.u32 {%0, %1, %2, %3}, [%4];"
+                     : "=r"(lo.x), "=r"(lo.y), "=r"(lo.z), "=r"(lo.w) : "l"(up));
+        asm volatile("ld.global.nc.L1::no_allocate.v4.u32 {%0, %1, %2, %3}, [%4];"
+                     : "=r"(hi.x), "=r"(hi.y), "=r"(hi.z), "=r"(hi.w) : "l"(up + 1));
+        const uint32_t u[8] = {lo.x, lo.y, lo.z, lo.w, hi.x, hi.y, hi.z, hi.w};
+#pragma unroll
+        for (int i = 0; i < 8; ++i) {
+            const float2 gf = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162*>(&w[i]));
+            const float2 uf = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162*>(&u[i]));
+            const __nv_bfloat162 p = __floats2bfloat162_rn(gf.x / (1.0f + __expf(-gf.x)) * uf.x, gf.y / (1.0f + __expf(-gf.y)) * uf.y);
+            w[i] = *reinterpret_cast<const uint32_t*>(&p);
+        }
     }
     xform::Block16 out;
     xform::decompose_block16<kResidual, kPolicy>(w, out);
@@ -447,7 +466,7 @@ int workspace_pool(int dev, cudaMemPool_t* out)
 
 template <uint32_t BK, bool kResidual, uint32_t kGroup>
 int launch_variant(const void* a, int64_t lda, const void* b, const void* sfb, int M, int N, int K, int E, Params p,
-                   bool pdl, int policy, int num_sms, cudaStream_t stream)
+                   bool pdl, int policy, bool swiglu, int num_sms, cudaStream_t stream)
 {
     using C = Cfg<BK, kResidual, kGroup>;
     int dev = 0;
@@ -482,7 +501,8 @@ int launch_variant(const void* a, int64_t lda, const void* b, const void* sfb, i
     if (rc) return release(rc);
 
     const uint64_t blocks16 = static_cast<uint64_t>(M) * (K / 16);
-    auto quantize = policy == 1 ? quantize_activation_kernel<kResidual, 1> : quantize_activation_kernel<kResidual, 0>;
+    auto quantize = swiglu ? quantize_activation_kernel<kResidual, 0, true>
+                           : (policy == 1 ? quantize_activation_kernel<kResidual, 1> : quantize_activation_kernel<kResidual, 0>);
     quantize<<<static_cast<unsigned>((blocks16 + 255) / 256), 256, 0, stream>>>(
         static_cast<const __nv_bfloat16*>(a), lda, static_cast<uint32_t>(M), static_cast<uint32_t>(K), a0, a1, sfa);
     if (cudaError_t err = cudaGetLastError(); err != cudaSuccess)
@@ -517,7 +537,8 @@ int launch_variant(const void* a, int64_t lda, const void* b, const void* sfb, i
 // Two launches: activations -> NVFP4 workspace, then the block-scaled GEMM over it.  N % 256 == 0.
 int launch_gemm_split(const void* a, int64_t lda, const void* b, const void* sfb, const float* gw, void* d,
                       int64_t ldd, const int32_t* m_indices, int M, int N, int K, int E, bool residual,
-                      int block_k, int group_m, bool pdl, int policy, int num_sms, int32_t* status, cudaStream_t stream)
+                      int block_k, int group_m, bool pdl, int policy, bool swiglu, int num_sms, int32_t* status,
+                      cudaStream_t stream)
 {
     Params p;
     p.gw = gw;
@@ -531,13 +552,13 @@ int launch_gemm_split(const void* a, int64_t lda, const void* b, const void* sfb
     // block_k: 0 = the library's choice, 256 = one 256-wide K block per ring position, 128 = 128-wide with a commit
     // per position, 130 = 128-wide in groups of two (requested and freed together, consumed one by one)
     if (block_k == 130)
-        return residual ? launch_variant<128, true, 2>(a, lda, b, sfb, M, N, K, E, p, pdl, policy, num_sms, stream)
-                        : launch_variant<128, false, 2>(a, lda, b, sfb, M, N, K, E, p, pdl, policy, num_sms, stream);
+        return residual ? launch_variant<128, true, 2>(a, lda, b, sfb, M, N, K, E, p, pdl, policy, swiglu, num_sms, stream)
+                        : launch_variant<128, false, 2>(a, lda, b, sfb, M, N, K, E, p, pdl, policy, swiglu, num_sms, stream);
     if (K % 256 == 0 && block_k != 128)
-        return residual ? launch_variant<256, true, 1>(a, lda, b, sfb, M, N, K, E, p, pdl, policy, num_sms, stream)
-                        : launch_variant<256, false, 1>(a, lda, b, sfb, M, N, K, E, p, pdl, policy, num_sms, stream);
-    return residual ? launch_variant<128, true, 1>(a, lda, b, sfb, M, N, K, E, p, pdl, policy, num_sms, stream)
-                    : launch_variant<128, false, 1>(a, lda, b, sfb, M, N, K, E, p, pdl, policy, num_sms, stream);
+        return residual ? launch_variant<256, true, 1>(a, lda, b, sfb, M, N, K, E, p, pdl, policy, swiglu, num_sms, stream)
+                        : launch_variant<256, false, 1>(a, lda, b, sfb, M, N, K, E, p, pdl, policy, swiglu, num_sms, stream);
+    return residual ? launch_variant<128, true, 1>(a, lda, b, sfb, M, N, K, E, p, pdl, policy, swiglu, num_sms, stream)
+                    : launch_variant<128, false, 1>(a, lda, b, sfb, M, N, K, E, p, pdl, policy, swiglu, num_sms, stream);
 }
 
 #ifdef NVFP4_PROBE

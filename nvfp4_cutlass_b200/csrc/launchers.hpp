@@ -17,7 +17,8 @@ int launch_gemm_cluster(const void* a, int64_t lda, const void* b, const void* s
 
 int launch_gemm_split(const void* a, int64_t lda, const void* b, const void* sfb, const float* gw, void* d,
                       int64_t ldd, const int32_t* m_indices, int M, int N, int K, int E, bool residual,
-                      int block_k, int group_m, bool pdl, int policy, int num_sms, int32_t* status, cudaStream_t stream);
+                      int block_k, int group_m, bool pdl, int policy, bool swiglu, int num_sms, int32_t* status,
+                      cudaStream_t stream);
 
 int launch_permute_rows(const void* src, int64_t src_ld_bytes, const int64_t* src_idx, int src_div, const int64_t* dst_idx,
                         int64_t n_rows, int row_bytes, void* dst, int64_t dst_ld_bytes, int num_sms, cudaStream_t stream);

@@ -210,9 +210,12 @@ class ExpertParallelMoE:
         self.num_experts, self.hidden, self.inter, self.alignment = num_experts, hidden, inter, alignment
         self.e_local = num_experts // self.world
         self.up, self.down = up, down
+        self.gemm_swiglu = None                # SwiGLU folded into the down-projection (CUDA library only)
         if gemm is None:
             from . import _C
             gemm = _C.m_grouped_bf16_dual_nvfp4_gemm_contiguous
+            if hidden % 256 == 0:
+                self.gemm_swiglu = _C.m_grouped_swiglu_dual_nvfp4_gemm_contiguous
         self.gemm = gemm
         self.native_glue = native_glue         # False: tensor operations even for CUDA tensors (a test's comparison arm)
         # peer_rows_cap > 0: dispatch and combine go through peer memory (one kernel each, stores into / loads from
@@ -262,10 +265,16 @@ class ExpertParallelMoE:
         m_indices = make_m_indices(plan.group_sizes, device=a.device, alignment=self.alignment)
         h = torch.empty(a.shape[0], 2 * self.inter, dtype=torch.bfloat16, device=a.device)
         self.gemm(a, *self.up, h, m_indices)
-        act = swiglu(h, native=self.native_glue)
         out = torch.empty(a.shape[0], self.hidden, dtype=torch.bfloat16, device=a.device)
-        self.gemm(act, *self.down, out, m_indices)
+        self._down(h, out, m_indices)
         return out
+
+    def _down(self, h: torch.Tensor, out: torch.Tensor, m_indices: torch.Tensor) -> None:
+        """SwiGLU and the down-projection; one fused call where the library offers it."""
+        if self.gemm_swiglu is not None and self.native_glue and h.is_cuda:
+            self.gemm_swiglu(h, *self.down, out, m_indices)
+        else:
+            self.gemm(swiglu(h, native=self.native_glue), *self.down, out, m_indices)
 
     def combine(self, out: torch.Tensor, plan: Dispatch, topk_w: torch.Tensor, tokens: int) -> torch.Tensor:
         k = topk_w.shape[1]
@@ -319,7 +328,7 @@ class ExpertParallelMoE:
         a, out = buf.a[:plan.rows_padded], buf.out[:plan.rows_padded]
         h = torch.empty(a.shape[0], 2 * self.inter, dtype=torch.bfloat16, device=a.device)
         self.gemm(a, *self.up, h, m_indices)
-        self.gemm(swiglu(h), *self.down, out, m_indices)
+        self._down(h, out, m_indices)
         mark()
         buf.barrier()                                   # every rank's expert outputs are complete
         y = _C.combine_rows_peer(buf.out_peers, self.hidden, plan.dst_rank, plan.dst_row,

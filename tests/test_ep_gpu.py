@@ -52,6 +52,26 @@ def test_swiglu_matches_tensor_ops(dev):
     assert rel_l2(got, want) < 2e-3          # same FP32 formula; exp differs in the last bits
 
 
+@pytest.mark.parametrize("residual", [True, False])
+def test_swiglu_folded_into_the_down_projection_is_bit_identical(dev, residual):
+    """nvfp4_grouped_gemm_swiglu_contiguous against nvfp4_swiglu followed by the split-path GEMM."""
+    e, rows, inter, hidden = 3, 256, 384, 512
+    g = torch.Generator().manual_seed(12)
+    h = (torch.randn(e * rows, 2 * inter + 16, generator=g) * 2).to(torch.bfloat16).to(dev)[:, :2 * inter]   # strided rows
+    w = (torch.randn(e, hidden, inter, generator=g) * 0.05).to(torch.bfloat16).to(dev)
+    b, sfb, gw = nvfp4_gemm.quantize_weight_nvfp4(w)
+    mi = nvfp4_gemm.make_m_indices([rows] * e).to(dev)
+    status = torch.zeros(1, dtype=torch.int32, device=dev)
+    fused = torch.empty(e * rows, hidden, dtype=torch.bfloat16, device=dev)
+    _C.m_grouped_swiglu_dual_nvfp4_gemm_contiguous(h, b, sfb, gw, fused, mi, enable_residual_pass=residual, device_status=status)
+    plain = torch.empty_like(fused)
+    nvfp4_gemm.m_grouped_bf16_dual_nvfp4_gemm_contiguous(_C.swiglu(h.contiguous()), b, sfb, gw, plain, mi,
+                                                         enable_residual_pass=residual, tune_split_transform=1, device_status=status)
+    torch.cuda.synchronize()
+    assert int(status.item()) == 0
+    assert torch.isfinite(fused.float()).all() and torch.equal(fused, plain)
+
+
 def test_combine_rows_matches_tensor_ops(dev):
     g = torch.Generator().manual_seed(3)
     tokens, k, hidden = 50, 4, 384
