@@ -48,6 +48,10 @@ WORKLOADS = {
     # the up-projection of the expert-parallel layer (the dominant GEMM of config C5); the layer itself is built in
     # nvfp4_cutlass_b200/ep_bench.py, this entry gives the CPU reference arm its shape
     "c5": dict(E=128, N=3072, K=4096, desc="expert-parallel MoE layer (C5): up-projection E=128, N=3072, K=4096"),
+    # the two GEMMs of that layer at one rank, as plain grouped-GEMM workloads (same routing rule: top-8 softmax of
+    # Gaussian logits over 16384 tokens, groups padded to 128 rows, Student-t(4) activations)
+    "c5up": dict(E=128, N=3072, K=4096, ep_tokens=16384, desc="C5 up-projection at one rank: E=128, 131072 rows top-8 routed, N=3072, K=4096"),
+    "c5down": dict(E=128, N=4096, K=1536, ep_tokens=16384, desc="C5 down-projection at one rank: E=128, 131072 rows top-8 routed, N=4096, K=1536"),
     "c2s": dict(E=8, N=8192, K=4096, desc="reduced c2 for profiling: E=8 x 512 rows, N=8192, K=4096"),
     "c4s": dict(E=64, N=4096, K=7168, desc="reduced c4 for profiling: E=64, 16 tokens x top-8, N=4096, K=7168"),
 }
@@ -57,14 +61,14 @@ WORKLOADS = {
 # under profiles/, on the reduced workloads c2s / c4s (the full ones exceed what a multi-pass capture should
 # hold), as (bytes measured, algorithmic bytes of that captured launch).  Both kernels stream every operand
 # once, so traffic grows in proportion to the algorithmic bytes; a full launch is scaled by that ratio.
-NCU_TRAFFIC = {"normal": (246.79e6, 251.66e6, "profiles/gemm_split_kernel_c2s.md"),
-               "swap_ab": (925.54e6, 911.22e6, "profiles/gemm_swap_kernel_c4s.md")}
+NCU_TRAFFIC = {"normal": (246.79e6, 251.66e6, "split-path kernels on c2s, captured at commit 643bd80"),
+               "swap_ab": (925.54e6, 911.22e6, "decode kernel on c4s, captured at commit 643bd80")}
 
 
 def scaled_traffic(orientation: str, algo_bytes: float) -> dict:
     measured, algo_small, src = NCU_TRAFFIC[orientation]
     return {"traffic": measured / algo_small * algo_bytes,
-            "traffic_source": f"ncu capture on the reduced workload ({src}), scaled by algorithmic bytes"}
+            "traffic_source": f"one ncu capture of a launch on a reduced workload ({src}), scaled by algorithmic bytes"}
 
 
 def peaks() -> dict:
@@ -132,6 +136,11 @@ def routing_rows(workload: str, E: int, gen: torch.Generator):
         real = counts.clamp(max=16).tolist()
         return real, [((r + 15) // 16) * 16 for r in real], 16, True
     cfg = WORKLOADS[workload]
+    if "ep_tokens" in cfg:                                  # top-8 softmax routing of Gaussian logits
+        logits = torch.randn(cfg["ep_tokens"], E, generator=gen)
+        ids = torch.topk(torch.softmax(logits, dim=-1), 8, dim=-1).indices
+        real = torch.bincount(ids.reshape(-1), minlength=E).tolist()
+        return real, [((r + 127) // 128) * 128 for r in real], 128, False
     if "rows" in cfg:
         real = [cfg["rows"]] * E
         return real, real, 128, False
@@ -160,7 +169,9 @@ def build_weights(E: int, N: int, K: int, dev, seed: int):
     return b, sfb, gw
 
 
-def build_single_gpu_case(workload: str, dev, extra_kw=None):
+def build_single_gpu_case(workload: str, dev, extra_kw=None, weights=None):
+    """Seeded synthetic operands of a workload, on the device.  `weights` = (b, sfb, gw) of an earlier case with the
+    same E, N, K (c4 shares c3up's)."""
     import nvfp4_gemm
     cfg = WORKLOADS[workload]
     E, N, K = cfg["E"], cfg["N"], cfg["K"]
@@ -172,6 +183,11 @@ def build_single_gpu_case(workload: str, dev, extra_kw=None):
     x = torch.randn(sum(real), K, generator=ga, device=dev)
     if workload in ("c2", "c2s"):                           # per-row lognormal(0, 0.5) scale
         x = x * torch.exp(0.5 * torch.randn(sum(real), 1, generator=ga, device=dev))
+    if "ep_tokens" in cfg:                                  # Student-t(4), in row chunks to bound memory
+        for r0 in range(0, x.shape[0], 16384):
+            chi = torch.randn(min(16384, x.shape[0] - r0), K, 4, generator=ga, device=dev).pow(2).mean(-1).sqrt()
+            x[r0:r0 + 16384] /= chi
+            del chi
     if workload.startswith("c3"):                           # 0.1 % outlier channels x50
         cols = torch.randperm(K, generator=torch.Generator().manual_seed(1))[:max(1, K // 1000)]
         x[:, cols.to(dev)] *= 50.0
@@ -182,7 +198,7 @@ def build_single_gpu_case(workload: str, dev, extra_kw=None):
         off_r += r
         off_p += pz
     m_indices = nvfp4_gemm.make_m_indices(padded, alignment=align).to(dev)
-    b, sfb, gw = build_weights(E, N, K, dev, seed=2)
+    b, sfb, gw = weights if weights is not None else build_weights(E, N, K, dev, seed=2)
     kw = dict(tune_swap_ab=1, m_alignment=align) if swap else {}
     kw.update(extra_kw or {})
     active = sum(1 for r in real if r > 0)
@@ -210,42 +226,88 @@ def accuracy_sample(case, d, dev):
 
 
 # ----------------------------------------------------------------------------- CPU baseline
-def cpu_reference_sample(workload: str, seconds_target: float = 12.0):
-    """The reference's CPU chain (decompose, dequantise, FP32 dot products) on a bounded sample of the
-    workload: one expert's rows x a slice of its output columns, full K.  Uses the reference's own C++
-    host twin (oracle/_ref) when it was built, else the C restatement (oracle/)."""
-    import oracle
-    cfg = WORKLOADS.get(workload, WORKLOADS["c2"])
-    K = cfg["K"]
-    g = torch.Generator().manual_seed(0)
-    use_ref = oracle.ref_twin() is not None and hasattr(oracle.ref_twin(), "ref_twin_dual_gemm_mt")
-    rows, ncols = (64, 128) if use_ref else (128, 256)
-    threads = os.cpu_count() or 1
+class CpuReference:
+    """The reference's CPU chain on a bounded sample of the workload (the rows of one expert x a slice of its output
+    columns x full K), on all host threads.  Preferred: the reference's own PyTorch emulation
+    (tests/python/reference/dual_nvfp4.py there: decompose -> dequantise -> FP32 matmul -> G_W -> BF16), copied at
+    build time into the git-ignored oracle/_ref/ by oracle/Makefile.  Without it: the reference's C++ host twin
+    (oracle/_ref/libref_twin.so), else the C restatement (oracle/).  The sample is prepared once (weights quantised,
+    untimed, as on the GPU arm); run() times one pass of the chain over it."""
 
-    def run(rows, ncols):
-        a = torch.randn(rows, K, generator=g).to(torch.bfloat16)
-        w = (torch.randn(1, ncols, K, generator=g) * 0.02).to(torch.bfloat16)
-        mi = torch.zeros(rows, dtype=torch.int32)
-        if use_ref:
-            q, sf, gg = oracle.ref_twin_quantize_weight(w.float())
-            t = time.perf_counter()
-            oracle.ref_twin_dual_gemm_mt(a.float(), q, sf, gg, mi, ncols, threads)
-            return time.perf_counter() - t
-        b, sfb, gw = oracle.quantize_weight(w)
+    def __init__(self, workload: str, seconds_target: float = 10.0):
+        import oracle
+        self.oracle = oracle
+        cfg = WORKLOADS.get(workload, WORKLOADS["c2"])
+        self.K, N = cfg["K"], cfg["N"]
+        self.threads = os.cpu_count() or 1
+        self.emu = oracle.ref_emulation()
+        self.twin = oracle.ref_twin() is not None and hasattr(oracle.ref_twin(), "ref_twin_dual_gemm_mt")
+        self.kind = "reference" if self.emu is not None else ("reference-cpp" if self.twin else "port")
+        # one expert's rows as the workload has them (512 at C2), columns sized for the time target
+        rows = min(512, cfg.get("rows", 512))
+        ncols = min(N, 1024)
+        # one cheap probe, then the final sample prepared once: columns grow up to N, then the rows (large FP32 matmuls
+        # run ~2x more efficiently than the probe, hence the factor)
+        self._prepare(rows, ncols)
+        t_probe = min(self.run() for _ in range(2))
+        scale = 2.0 * seconds_target / max(t_probe, 1e-3)
+        if scale >= 1.5:
+            new_cols = min(N, max(ncols, int(ncols * scale) // 64 * 64))
+            scale /= new_cols / ncols
+            ncols = new_cols
+            if scale >= 1.5:
+                rows = min(4096, max(rows, int(rows * scale) // 128 * 128))
+            self._prepare(rows, ncols)
+
+    def _prepare(self, rows, ncols):
+        g = torch.Generator().manual_seed(0)
+        self.rows, self.ncols = rows, ncols
+        self.a = torch.randn(rows, self.K, generator=g).to(torch.bfloat16)
+        w = (torch.randn(1, ncols, self.K, generator=g) * 0.02).to(torch.bfloat16)
+        self.mi = torch.zeros(rows, dtype=torch.int32)
+        if self.emu is not None:
+            torch.set_num_threads(self.threads)
+            self.w = self.emu.quantize_weight_nvfp4(w.float())
+        elif self.twin:
+            self.w = self.oracle.ref_twin_quantize_weight(w.float())
+        else:
+            self.w = self.oracle.quantize_weight(w)
+
+    def run(self) -> float:
         t = time.perf_counter()
-        oracle.grouped_gemm(a, b, sfb, gw, mi, ncols, mode="dual")
+        if self.emu is not None:
+            self.emu.dual_nvfp4_grouped_gemm(self.a, *self.w, torch.tensor([0, self.rows]))
+        elif self.twin:
+            self.oracle.ref_twin_dual_gemm_mt(self.a.float(), *self.w, self.mi, self.ncols, self.threads)
+        else:
+            self.oracle.grouped_gemm(self.a, *self.w, self.mi, self.ncols, mode="dual")
         return time.perf_counter() - t
 
-    t_probe = run(rows, ncols)
-    scale = max(1.0, seconds_target / max(t_probe, 1e-3))
-    ncols2 = min(cfg["N"], int(ncols * scale) // 64 * 64)
-    rows = min(512, max(rows, int(rows * scale * ncols / ncols2) // 8 * 8))
-    t = run(rows, ncols2)
-    flops = 2.0 * rows * ncols2 * K
-    return dict(value=flops / t / 1e12, unit="TFLOP/s", cores=threads if use_ref else oracle.num_threads(),
-                kind="reference" if use_ref else "port",
-                sample=f"{rows} rows of one expert x {ncols2} output columns x K={K} ({flops / 1e9:.1f} GFLOP, {t:.1f} s)",
-                seconds=t)
+    def record(self, seconds: float) -> dict:
+        flops = 2.0 * self.rows * self.ncols * self.K
+        what = {"reference": "the reference's PyTorch emulation (dual_nvfp4_grouped_gemm, FP32 matmul)",
+                "reference-cpp": "the reference's C++ host twin", "port": "the C restatement of the reference's emulation"}[self.kind]
+        return dict(value=flops / seconds / 1e12, unit="TFLOP/s", cores=self.threads if self.kind != "port" else self.oracle.num_threads(),
+                    kind=self.kind, seconds=seconds,
+                    sample=f"{what}: {self.rows} rows of one expert x {self.ncols} output columns x K={self.K} "
+                           f"({flops / 1e9:.1f} GFLOP, {seconds:.1f} s)")
+
+
+def cpu_reference_sample(workload: str, seconds_target: float = 10.0):
+    ref = CpuReference(workload, seconds_target)
+    return ref.record(ref.run())
+
+
+def default_workload(args, world: int) -> str:
+    """C2 (the configuration the headline metric is quoted on) for a one-GPU run on a one-GPU box.  The expert-parallel
+    layer C5 for several ranks, and also for a one-rank run under a torchrun-style launcher or on a box with several
+    GPUs: that is the N = 1 point of a 1 -> 8 scaling series, which must be the same workload as its N > 1 points."""
+    if args.workload:
+        return args.workload
+    if world > 1 or args.gpus > 1:
+        return "c5"
+    scaling_series = "WORLD_SIZE" in os.environ or (torch.cuda.is_available() and torch.cuda.device_count() > 1)
+    return "c5" if scaling_series else "c2"
 
 
 def run_reference_arm(args):
@@ -255,17 +317,18 @@ def run_reference_arm(args):
     times = []
     base = None
     world = int(os.environ.get("WORLD_SIZE", "1"))
-    workload = args.workload or ("c2" if max(world, args.gpus) == 1 else "c5")      # the same default as the main arm
-    args.workload = workload
+    workload = default_workload(args, max(world, args.gpus))      # the same default as the main arm
+    # each step is one pass over the same bounded sample, sized so that warm-up + steps end within a few minutes
+    ref = CpuReference(workload, seconds_target=max(1.0, min(6.0, 150.0 / max(1, args.warmup + args.steps))))
     for i in range(args.warmup + args.steps):
-        base = cpu_reference_sample(workload, seconds_target=6.0)
+        base = ref.record(ref.run())
         if i >= args.warmup:
             times.append(base["value"])
     value = statistics.mean(times)
     line = {"impl": "reference", "metric": "grouped_gemm_logical_tflops", "value": value, "unit": "TFLOP/s",
             "n_gpus": args.gpus, "steps": args.steps, "warmup": args.warmup, "ms_per_step": base["seconds"] * 1e3,
             "higher_is_better": True, "scaling": "weak", "vs_baseline": None, "dtype": "nvfp4 codes, fp32 accumulate",
-            "data": "synthetic", "config": {"workload": WORKLOADS.get(args.workload or "c2", {}).get("desc", args.workload),
+            "data": "synthetic", "config": {"workload": WORKLOADS.get(workload, {}).get("desc", workload),
                                             "note": "bounded sample of the workload on the host cores"},
             "cpu_baseline": {k: base[k] for k in ("value", "unit", "cores", "kind", "sample")},
             "e2e": {"value": value, "unit": "TFLOP/s", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0}}
@@ -352,14 +415,132 @@ def measure_fp4_peak_sustained(seconds: float = 0.25):
     return n * fl / (s.elapsed_time(e) * 1e-3) / 1e12
 
 
+def split_default(case, extra) -> bool:
+    """Whether the dispatcher (csrc/abi.cu) sends this call to the two-kernel split path."""
+    fused_knobs = any(extra.get(k, 0) for k in ("tune_cluster", "tune_transform_warps", "tune_direct_a"))
+    mode = extra.get("tune_split_transform", 0)
+    return (not case["swap"]) and case["N"] % 256 == 0 and (mode == 1 or (mode == 0 and not fused_knobs and case["N"] >= 1024))
+
+
+def gemm_record(case, dev, steps, warmup, fp4_peak, graph=False, extra=None, sample_clocks=True, local=0):
+    """One timed run of the grouped GEMM on `case`: ms, logical TFLOP/s, roofline record, accuracy sample."""
+    import nvfp4_gemm
+    from nvfp4_gemm import _C
+    extra = dict(extra or {})
+    kw = dict(case["kw"], **extra)
+    M, N, K = case["M"], case["N"], case["K"]
+    d = torch.empty(M, N, dtype=torch.bfloat16, device=dev)
+    status = torch.zeros(1, dtype=torch.int32, device=dev)
+
+    def step():
+        nvfp4_gemm.m_grouped_bf16_dual_nvfp4_gemm_contiguous(case["a"], case["b"], case["sfb"], case["gw"], d,
+                                                             case["m_indices"], device_status=status, **kw)
+
+    sampler = ClockSampler(local) if sample_clocks else None
+    if sampler:
+        sampler.start()
+    ms, t0, t1 = (timed_graph(step, steps, warmup) if graph else timed(step, steps, warmup, lambda: None))
+    clocks = sampler.stop(t0, t1) if sampler else None
+    assert _C.read_status(status) == 0, "kernel reported a device-side timeout"
+    rel, cos = accuracy_sample(case, d, dev)
+    logical = 2.0 * case["real_rows"] * N * K
+    pk = peaks()
+    if case["swap"]:
+        algo_bytes = (case["active_experts"] * (N * K // 2 + N * K // 16) + 2 * case["real_rows"] * K +
+                      2 * case["real_rows"] * N + 4 * case["E"] + 4 * M)
+        achieved = algo_bytes / (ms * 1e-3) / 1e9
+        roofline = {"bound": "hbm", "achieved": achieved, "peak": pk["hbm_gbs"], "unit": "GB/s",
+                    "frac": achieved / pk["hbm_gbs"], **scaled_traffic("swap_ab", algo_bytes), "peak_source": pk["source"],
+                    "algorithmic_bytes_per_launch": algo_bytes}
+    else:
+        achieved = 2.0 * logical / (ms * 1e-3) / 1e12       # both NVFP4 passes run on the tensor pipe
+        algo_bytes = case["b"].numel() + case["sfb"].numel() * 4 + case["a"].numel() * 2 + d.numel() * 2
+        roofline = {"bound": "tensor", "achieved": achieved, "peak": fp4_peak, "unit": "TFLOP/s",
+                    "frac": achieved / fp4_peak, **scaled_traffic("normal", algo_bytes),
+                    "algorithmic_bytes_per_launch": algo_bytes, "tensor_flops_per_launch": 2.0 * logical,
+                    "hbm_gbs_min": algo_bytes / (ms * 1e-3) / 1e9, "hbm_frac_min": algo_bytes / (ms * 1e-3) / 1e9 / pk["hbm_gbs"]}
+    rec = {"ms_per_step": ms, "steps": steps, "value": logical / (ms * 1e-3) / 1e12, "unit": "TFLOP/s", "roofline": roofline,
+           "frac": roofline["frac"], "rel_l2_vs_fp32": rel, "cosine_vs_fp32": cos,
+           "timing": "CUDA-graph replay of one call" if graph else "back-to-back launches",
+           "kernels_per_step": 2 if split_default(case, extra) else 1}
+    if clocks is not None:
+        rec["clocks"] = clocks
+    return rec, d, step
+
+
+def north_star_record(case, dev, steps, fp4_peak, graph=False):
+    """The path the project is named for -- Algorithm 1 inside the GEMM main loop, nothing quantised written to
+    global memory -- on this workload: the fused cluster kernel for the normal orientation (the decode kernel
+    always decomposes in its main loop)."""
+    rec, _, _ = gemm_record(case, dev, steps, 3, fp4_peak, graph=graph, extra=dict(tune_split_transform=2), sample_clocks=False)
+    return {"ms_per_step": rec["ms_per_step"], "steps": rec["steps"], "value": rec["value"], "unit": "TFLOP/s", "frac": rec["frac"],
+            "rel_l2_vs_fp32": rec["rel_l2_vs_fp32"], "cosine_vs_fp32": rec["cosine_vs_fp32"], "kernels_per_step": 1,
+            "note": "tune_split_transform=2: Algorithm 1 inside the GEMM main loop (cluster kernel, transform shared over distributed shared memory)"}
+
+
+def slim(rec):
+    """A sub-record of the JSON line: the figures, without the long provenance strings."""
+    out = {k: rec[k] for k in ("ms_per_step", "steps", "value", "unit", "frac", "rel_l2_vs_fp32", "cosine_vs_fp32", "timing",
+                               "kernels_per_step") if k in rec}
+    out["bound"] = rec["roofline"]["bound"]
+    if "hbm_frac_min" in rec["roofline"]:
+        out["hbm_frac_min"] = rec["roofline"]["hbm_frac_min"]
+    if "clocks" in rec:
+        out["clocks"] = rec["clocks"]
+    if "north_star_path" in rec:
+        out["north_star_path"] = rec["north_star_path"]
+    return out
+
+
+def also_records(dev, fp4_peak, local, budget_s=120.0):
+    """The other configurations and the reference's own sweep, bounded, in the same run: C3 up / down, C4, and the
+    Qwen-shaped gate_up / down / decode shapes the reference publishes (graph-timed like there, split and fused)."""
+    t_start = time.time()
+    out = {}
+    shared = {}
+    for name, steps in (("c3up", 10), ("c4", 20), ("c3down", 10)):
+        if time.time() - t_start > budget_s:
+            out[name] = {"skipped": "time budget of the default run"}
+            continue
+        case = build_single_gpu_case(name, dev, weights=shared.get((WORKLOADS[name]["E"], WORKLOADS[name]["N"], WORKLOADS[name]["K"])))
+        shared[(case["E"], case["N"], case["K"])] = (case["b"], case["sfb"], case["gw"])
+        rec, _, _ = gemm_record(case, dev, steps, 3, fp4_peak, local=local)
+        if not case["swap"]:
+            rec["north_star_path"] = north_star_record(case, dev, max(3, steps // 2), fp4_peak)
+        out[name] = slim(rec)
+        out[name]["workload"] = WORKLOADS[name]["desc"]
+        del case
+        if name == "c4":
+            shared.clear()
+        torch.cuda.empty_cache()
+    sweep = {}
+    for name in ("qup8k", "qup16k", "qup32k", "qdown8k", "qdown16k", "qdown32k", "qdec16", "qdec32", "qdec128"):
+        if time.time() - t_start > budget_s:
+            sweep[name] = {"skipped": "time budget of the default run"}
+            continue
+        case = build_single_gpu_case(name, dev)
+        rec, _, _ = gemm_record(case, dev, 100, 3, fp4_peak, graph=True, sample_clocks=False)
+        entry = {"us": rec["ms_per_step"] * 1e3, "value": rec["value"], "frac": rec["frac"], "bound": rec["roofline"]["bound"],
+                 "cosine_vs_fp32": rec["cosine_vs_fp32"]}
+        if not case["swap"]:
+            ns, _, _ = gemm_record(case, dev, 100, 3, fp4_peak, graph=True, extra=dict(tune_split_transform=2), sample_clocks=False)
+            entry["fused_us"] = ns["ms_per_step"] * 1e3
+        sweep[name] = entry
+        del case
+    out["ref_sweep"] = {"timing": "CUDA-graph replay of one call, 100 replays (the reference's method)", "unit": "us per call",
+                        "shapes": sweep}
+    return out
+
+
 def main():
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
     ap.add_argument("--steps", type=int, default=None)
     ap.add_argument("--warmup", type=int, default=None)
-    ap.add_argument("--workload", default=None, help="c2 (default at 1 GPU), c3up, c3down, c4, c5 (default at >1 GPU)")
+    ap.add_argument("--workload", default=None, help="c2 (default at 1 GPU), c3up, c3down, c4, c5up, c5down, c5 (default at >1 GPU)")
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--no-cpu-baseline", action="store_true")
+    ap.add_argument("--no-also", action="store_true", help="skip the sub-records of the other configurations")
     ap.add_argument("--graph", action="store_true", help="time CUDA-graph replays of one call (the reference's method)")
     ap.add_argument("--tune", action="append", default=[], help="tune_xxx=int passed to the GEMM call (experiments)")
     args = ap.parse_args()
@@ -371,131 +552,117 @@ def main():
     world = int(os.environ.get("WORLD_SIZE", "1"))
     rank = int(os.environ.get("RANK", "0"))
     local = int(os.environ.get("LOCAL_RANK", "0"))
-    workload = args.workload or ("c2" if world == 1 else "c5")
+    workload = default_workload(args, world)
     torch.cuda.set_device(local)
     dev = torch.device("cuda", local)
     if world > 1 or workload == "c5":
         from nvfp4_cutlass_b200 import ep_bench
         return ep_bench.run(args, workload, world, rank, local)
 
-    import nvfp4_gemm
-    steps = args.steps or (300 if workload != "c4" else 300)
-    warmup = args.warmup if args.warmup is not None else 10
-    warmup = max(warmup, 3)
+    steps = args.steps or 20
+    warmup = max(args.warmup if args.warmup is not None else 5, 3)
     extra = {kv.split('=')[0]: int(kv.split('=')[1]) for kv in args.tune}
+    line = single_gpu_line(workload, dev, local, steps, warmup, extra, args.graph, cpu_baseline=not args.no_cpu_baseline,
+                           also=not args.no_also and workload == "c2" and not extra)
+    print(json.dumps(line))
+
+
+def single_gpu_line(workload, dev, local, steps, warmup, extra, graph=False, cpu_baseline=True, also=False, e2e=True, sustained=True):
+    """The JSON line of a one-GPU grouped-GEMM workload."""
+    import nvfp4_gemm
     case = build_single_gpu_case(workload, dev, extra)
     M, N, K = case["M"], case["N"], case["K"]
-    d = torch.empty(M, N, dtype=torch.bfloat16, device=dev)
-    status = torch.zeros(1, dtype=torch.int32, device=dev)
-
-    def step():
-        nvfp4_gemm.m_grouped_bf16_dual_nvfp4_gemm_contiguous(case["a"], case["b"], case["sfb"], case["gw"], d,
-                                                             case["m_indices"], device_status=status, **case["kw"])
-
-    # which kernels a step launches (mirrors the dispatch in csrc/abi.cu)
-    fused_knobs = any(extra.get(k, 0) for k in ("tune_cluster", "tune_transform_warps", "tune_direct_a"))
-    split_mode = extra.get("tune_split_transform", 0)
-    is_split = (not case["swap"]) and N % 256 == 0 and (split_mode == 1 or (split_mode == 0 and not fused_knobs and N >= 1024))
-    kernels_per_step = 2 if is_split else 1
+    fp4_peak = measure_fp4_peak()
+    rec, d, step = gemm_record(case, dev, steps, warmup, fp4_peak, graph=graph, extra=extra, local=local)
+    roofline = rec["roofline"]
+    is_split = split_default(case, extra)
     path = ("split: quantize_activation_kernel (Algorithm 1 once per element, into an L2-resident workspace) + "
             "gemm_split_kernel (block-scaled FP4 GEMM)") if is_split else (
             "decode: gemm_swap_kernel, Algorithm 1 in the main loop" if case["swap"] else
             "fused: Algorithm 1 in the main loop of the GEMM kernel")
-
-    sampler = ClockSampler(local)
-    sampler.start()
-    if args.graph:
-        ms, t0, t1 = timed_graph(step, steps, warmup)
-    else:
-        ms, t0, t1 = timed(step, steps, warmup, lambda: None)
-    clocks = sampler.stop(t0, t1)
-    assert int(status.item()) == 0, "kernel reported a device-side timeout"
-    rel, cos = accuracy_sample(case, d, dev)
-
-    # the fused kernel (activations decomposed inside the GEMM main loop, nothing quantised ever written to
-    # global memory) on the same inputs, for comparison with the split default
-    fused = None
-    if is_split and split_mode == 0:
-        fused_kw = dict(case["kw"], tune_split_transform=2)
-
-        def fused_step():
-            nvfp4_gemm.m_grouped_bf16_dual_nvfp4_gemm_contiguous(case["a"], case["b"], case["sfb"], case["gw"], d,
-                                                                 case["m_indices"], device_status=status, **fused_kw)
-
-        f_steps = max(5, min(steps, 50))
-        f_ms, _, _ = timed(fused_step, f_steps, 3, lambda: None)
-        assert int(status.item()) == 0, "kernel reported a device-side timeout"
-        f_rel, f_cos = accuracy_sample(case, d, dev)
-        fused = {"ms_per_step": f_ms, "steps": f_steps, "value": 2.0 * case["real_rows"] * N * K / (f_ms * 1e-3) / 1e12,
-                 "unit": "TFLOP/s", "rel_l2_vs_fp32": f_rel, "cosine_vs_fp32": f_cos, "kernels_per_step": 1,
-                 "note": "tune_split_transform=2: Algorithm 1 inside the GEMM main loop (pair-cluster kernel)"}
-        step()                                    # leave the default path's output in d
-
     logical = 2.0 * case["real_rows"] * N * K
-    value = logical / (ms * 1e-3) / 1e12
     pk = peaks()
-    if case["swap"]:
-        algo_bytes = (case["active_experts"] * (N * K // 2 + N * K // 16) + 2 * case["real_rows"] * K +
-                      2 * case["real_rows"] * N + 4 * case["E"] + 4 * M)
-        achieved = algo_bytes / (ms * 1e-3) / 1e9
-        roofline = {"bound": "hbm", "achieved": achieved, "peak": pk["hbm_gbs"], "unit": "GB/s",
-                    "frac": achieved / pk["hbm_gbs"], **scaled_traffic("swap_ab", algo_bytes), "peak_source": pk["source"],
-                    "algorithmic_bytes_per_launch": algo_bytes}
-    else:
-        fp4_peak = measure_fp4_peak()
+    if not case["swap"]:
         fp4_sustained = measure_fp4_peak_sustained()
-        achieved = 2.0 * logical / (ms * 1e-3) / 1e12       # both NVFP4 passes run on the tensor pipe
-        algo_bytes = case["b"].numel() + case["sfb"].numel() * 4 + case["a"].numel() * 2 + d.numel() * 2
-        roofline = {"bound": "tensor", "achieved": achieved, "peak": fp4_peak, "unit": "TFLOP/s",
-                    "frac": achieved / fp4_peak, **scaled_traffic("normal", algo_bytes),
-                    "algorithmic_bytes_per_launch": algo_bytes,
-                    "peak_source": "resident-operand tcgen05 kind::mxf4nvf4 loop measured in this run (burst)",
-                    "peak_sustained": fp4_sustained, "frac_of_sustained": achieved / fp4_sustained,
-                    "peak_sustained_source": "the same loop launched back to back for 0.25 s (power-capped clock)",
-                    "peak_4x_measured_bf16": 4.0 * pk["bf16_tflops"], "frac_of_4x_measured_bf16": achieved / (4.0 * pk["bf16_tflops"]),
-                    "peak_bf16_source": pk["source"], "tensor_flops_per_launch": 2.0 * logical,
-                    "hbm_gbs_min": algo_bytes / (ms * 1e-3) / 1e9}
+        roofline.update({"peak_source": "resident-operand tcgen05 kind::mxf4nvf4 loop measured in this run (burst)",
+                         "peak_sustained": fp4_sustained, "frac_of_sustained": roofline["achieved"] / fp4_sustained,
+                         "peak_sustained_source": "the same loop launched back to back for 0.25 s (power-capped clock)",
+                         "peak_4x_measured_bf16": 4.0 * pk["bf16_tflops"],
+                         "frac_of_4x_measured_bf16": roofline["achieved"] / (4.0 * pk["bf16_tflops"]), "peak_bf16_source": pk["source"]})
 
-    # end to end through the public call: activations and routing index come from pinned host
-    # memory every step and the output goes back to pinned host memory (weights are model state,
-    # resident on the device)
-    a_host = case["a"].cpu().pin_memory()
-    mi_host = case["m_indices"].cpu().pin_memory()
-    d_host = torch.empty(M, N, dtype=torch.bfloat16).pin_memory()
-    a_dev = torch.empty_like(case["a"])
-    mi_dev = torch.empty_like(case["m_indices"])
-
-    def e2e_step():
-        a_dev.copy_(a_host, non_blocking=True)
-        mi_dev.copy_(mi_host, non_blocking=True)
-        nvfp4_gemm.m_grouped_bf16_dual_nvfp4_gemm_contiguous(a_dev, case["b"], case["sfb"], case["gw"], d, mi_dev,
-                                                             device_status=status, **case["kw"])
-        d_host.copy_(d, non_blocking=True)
-
-    e2e_steps = max(5, min(steps, 30))
-    e2e_ms, _, _ = timed(e2e_step, e2e_steps, 3, lambda: None)
-    e2e = {"value": logical / (e2e_ms * 1e-3) / 1e12, "unit": "TFLOP/s", "ms_per_step": e2e_ms, "steps": e2e_steps,
-           "h2d_bytes_per_step": a_host.numel() * 2 + mi_host.numel() * 4, "d2h_bytes_per_step": d_host.numel() * 2}
-
-    line = {"metric": "grouped_gemm_logical_tflops", "value": value, "unit": "TFLOP/s", "n_gpus": 1, "steps": steps,
-            "warmup": warmup, "ms_per_step": ms, "higher_is_better": True, "scaling": "weak", "vs_baseline": None,
+    line = {"metric": "grouped_gemm_logical_tflops", "value": rec["value"], "unit": "TFLOP/s", "n_gpus": 1, "steps": steps,
+            "warmup": warmup, "ms_per_step": rec["ms_per_step"], "higher_is_better": True, "scaling": "weak", "vs_baseline": None,
             "dtype": "nvfp4 (e2m1 x ue4m3 block 16), fp32 accumulate, bf16 in/out", "data": "synthetic",
             "config": {"workload": WORKLOADS[workload]["desc"], "name": workload, "M_padded": M, "M_real": case["real_rows"],
                        "N": N, "K": K, "E": case["E"], "passes": 2, "orientation": "swap_ab" if case["swap"] else "normal",
-                       "tune": extra, "path": path, "kernels_per_step": kernels_per_step,
-                       "timing": "CUDA-graph replay of one call" if args.graph else "back-to-back launches",
+                       "tune": extra, "path": path, "kernels_per_step": rec["kernels_per_step"], "timing": rec["timing"],
                        "l2": ("operands larger than L2 (weights %.0f MB), no flush" if case["b"].numel() > 126e6 else
                               "weights %.0f MB fit in L2 and are not flushed (the reference's sweep is timed the same way)")
                              % (case["b"].numel() / 1e6)},
-            "roofline": roofline, "e2e": e2e, "gpu_launches": steps * kernels_per_step, "clocks": clocks,
-            "rel_l2_vs_fp32": rel, "cosine_vs_fp32": cos}
-    if fused is not None:
-        fused["roofline_frac"] = 2.0 * fused["value"] / roofline["peak"]
-        line["fused_in_mainloop"] = fused
-    if not args.no_cpu_baseline:
+            "roofline": roofline, "gpu_launches": steps * rec["kernels_per_step"], "clocks": rec["clocks"],
+            "rel_l2_vs_fp32": rec["rel_l2_vs_fp32"], "cosine_vs_fp32": rec["cosine_vs_fp32"]}
+
+    # the same call for >= 0.25 s back to back: what the kernel holds once the power cap has settled the clock
+    if sustained and not graph:
+        n_sus = max(steps, int(0.3 / max(rec["ms_per_step"] * 1e-3, 1e-6)))
+        sampler = ClockSampler(local)
+        sampler.start()
+        sus_ms, t0, t1 = timed(step, n_sus, 3, lambda: None)
+        sus_clocks = sampler.stop(t0, t1)
+        ach = (2.0 * logical / (sus_ms * 1e-3) / 1e12) if not case["swap"] else roofline["algorithmic_bytes_per_launch"] / (sus_ms * 1e-3) / 1e9
+        line["sustained"] = {"ms_per_step": sus_ms, "steps": n_sus, "value": logical / (sus_ms * 1e-3) / 1e12, "unit": "TFLOP/s",
+                             "frac": ach / roofline["peak"], "clocks": sus_clocks}
+        if not case["swap"]:
+            line["sustained"]["frac_of_sustained_peak"] = ach / roofline["peak_sustained"]
+
+    # the north-star path (Algorithm 1 inside the GEMM main loop) on the same inputs, whatever the default is
+    if case["swap"]:
+        line["north_star_path"] = {"ms_per_step": rec["ms_per_step"], "value": rec["value"], "unit": "TFLOP/s", "frac": rec["frac"],
+                                   "note": "the decode kernel decomposes the activations inside its main loop: this is the default path"}
+    elif not is_split:
+        line["north_star_path"] = {"ms_per_step": rec["ms_per_step"], "value": rec["value"], "unit": "TFLOP/s", "frac": rec["frac"],
+                                   "note": "the timed path is the fused kernel"}
+    else:
+        line["north_star_path"] = north_star_record(case, dev, max(5, min(steps, 50)), fp4_peak, graph=graph)
+        line["fused_in_mainloop"] = dict(line["north_star_path"], roofline_frac=line["north_star_path"]["frac"])
+        step()                                    # leave the default path's output in d
+
+    if e2e:
+        # end to end through the public call: activations and routing index come from pinned host memory every step and
+        # the output goes back to pinned host memory (weights are model state, resident on the device)
+        a_host = case["a"].cpu().pin_memory()
+        mi_host = case["m_indices"].cpu().pin_memory()
+        d_host = torch.empty(M, N, dtype=torch.bfloat16).pin_memory()
+        a_dev = torch.empty_like(case["a"])
+        mi_dev = torch.empty_like(case["m_indices"])
+        status = torch.zeros(1, dtype=torch.int32, device=dev)
+        kw = dict(case["kw"])
+
+        def e2e_step():
+            a_dev.copy_(a_host, non_blocking=True)
+            mi_dev.copy_(mi_host, non_blocking=True)
+            nvfp4_gemm.m_grouped_bf16_dual_nvfp4_gemm_contiguous(a_dev, case["b"], case["sfb"], case["gw"], d, mi_dev,
+                                                                 device_status=status, **kw)
+            d_host.copy_(d, non_blocking=True)
+
+        e2e_steps = max(5, min(steps, 30))
+        e2e_ms, _, _ = timed(e2e_step, e2e_steps, 3, lambda: None)
+        line["e2e"] = {"value": logical / (e2e_ms * 1e-3) / 1e12, "unit": "TFLOP/s", "ms_per_step": e2e_ms, "steps": e2e_steps,
+                       "h2d_bytes_per_step": a_host.numel() * 2 + mi_host.numel() * 4, "d2h_bytes_per_step": d_host.numel() * 2}
+        del a_host, d_host, a_dev
+    del case, d
+    torch.cuda.empty_cache()
+    if also:
+        line["also"] = also_records(dev, fp4_peak, local)
+        try:
+            from nvfp4_cutlass_b200 import ep_bench
+            line["also"]["c5_one_gpu"] = ep_bench.one_gpu_record(dev, local, fp4_peak)
+        except Exception as exc:                                  # the headline must survive a failure of a side record
+            line["also"]["c5_one_gpu"] = {"error": repr(exc)[:300]}
+    if cpu_baseline:
         base = cpu_reference_sample(workload)
         line["cpu_baseline"] = {k: base[k] for k in ("value", "unit", "cores", "kind", "sample")}
-    print(json.dumps(line))
+    return line
 
 
 if __name__ == "__main__":

@@ -34,12 +34,13 @@ enum {
     NVFP4_E_INVALID_ARGUMENT = 1,  /* bad pointer, dtype code, shape relation or alignment */
     NVFP4_E_UNSUPPORTED = 2,       /* well-formed request this build has no kernel for */
     NVFP4_E_CUDA = 3,              /* a CUDA runtime / driver call failed */
-    NVFP4_E_DEVICE_TIMEOUT = 4     /* a bounded in-kernel wait expired (see nvfp4_read_status) */
+    NVFP4_E_DEVICE_TIMEOUT = 4     /* a bounded in-kernel wait expired (returned by nvfp4_read_status) */
 };
 
-/* activation scale policies (reference: src/api.hpp:106-112, transform/dual_nvfp4.cuh:31-61).  derived_div8 and
- * residual_amax are built (both orientations); anything else returns NVFP4_E_UNSUPPORTED. */
-enum { NVFP4_POLICY_DERIVED_DIV8 = 0, NVFP4_POLICY_RESIDUAL_AMAX = 1 };
+/* activation scale policies (reference: src/api.hpp:106-112, include/nvfp4_gemm/transform/dual_nvfp4.cuh:31-61);
+ * all four are built in every kernel family. */
+enum { NVFP4_POLICY_DERIVED_DIV8 = 0, NVFP4_POLICY_RESIDUAL_AMAX = 1, NVFP4_POLICY_DERIVED_DIV4 = 2,
+       NVFP4_POLICY_DIV4_RADIX8 = 3 };
 /* operand orientation (reference: tune_swap_ab, src/api.hpp:84-104) */
 enum { NVFP4_ORIENT_NORMAL = 0, NVFP4_ORIENT_SWAP_AB = 1 };
 /* weight input dtypes of nvfp4_quantize_weight */
@@ -73,8 +74,9 @@ NVFP4_API int nvfp4_quantize_weight(const void* w, int w_dtype, int E, int N, in
 /* nvfp4_quantize_weight for callers that must not allocate.  It has no counterpart in the
  * reference project.
  *
- * nvfp4_quantize_weight keeps a small cudaMalloc'ed scratch buffer per device (one word per
- * expert, grown on demand).  Some callers cannot afford that: code running while a stream is
+ * nvfp4_quantize_weight takes a small scratch buffer (one word per expert) from a stream-ordered
+ * memory pool on every call; the pool grows with cudaMalloc-like driver work the first time and
+ * whenever it needs more.  Some callers cannot afford that: code running while a stream is
  * being captured, latency-critical loops in which a cudaMalloc would synchronise the whole
  * device, processes whose device memory has been handed out completely to a pool of their
  * own.  This variant does the same work with its scratch in a fixed array inside the library
@@ -103,8 +105,16 @@ NVFP4_API int nvfp4_quantize_weight_static(const void* w, int w_dtype, int E, in
  *              first row of each aligned block is read, negative ids read as 0
  *   enable_residual_pass 0 = the single_nvfp4 variant (second pass skipped)
  *   tune       optional host array of 18 int32 in the order of the reference's
- *              tune_* keywords (src/api.hpp:166-203), or NULL; 0 = default.  Knobs
- *              without a counterpart here are accepted and ignored.
+ *              tune_* keywords (src/api.hpp:166-203), or NULL; 0 = default.  Honoured: [0] block_n
+ *              (swap-AB token tile 16/32/64), [1] transform_warps (8/16: single-CTA fused kernel),
+ *              [5] block_k, [7] swap_ab is the `orientation` argument, [8] cluster (1/2/4 CTAs share
+ *              a transformed activation tile), [9] direct_a, [11] no_pdl, [12] sched_group,
+ *              [13] split_transform.  NOTE [13] means something else than in the reference (there:
+ *              signal A0 early inside its one kernel): here 1 = quantise the activations once in a
+ *              kernel of their own ahead of the GEMM, 2 = Algorithm 1 inside the GEMM main loop,
+ *              0 = the library's choice.  All other knobs (epilogue_threads, num_stages,
+ *              swizzle_cd, epilogue_stages, l2_pin_weights, timing_probe, tail_split,
+ *              shallow_stages, produced_stages, a token tile of 128) are accepted and ignored.
  *   device_status optional device int32 the kernel ORs error bits into (bit 0 =
  *              a bounded wait expired); may be NULL
  * Constraints as in the reference (src/api.hpp:58-79): N % 128 == 0, K % 128 == 0,
@@ -115,6 +125,45 @@ NVFP4_API int nvfp4_grouped_gemm_contiguous(const void* a, int64_t lda_elems, co
                                   int scale_policy, int enable_residual_pass, int orientation,
                                   int m_alignment, const int32_t* tune, int32_t* device_status,
                                   void* stream);
+
+/* The same GEMM over the masked layout: `E` groups (experts) with `max_m` rows reserved each in `a` and `d`
+ * (row g * max_m + r; max_m % 128 == 0), of which the first masked_m[g] are real.  masked_m is a DEVICE array that
+ * an earlier kernel of the stream may have written: the host never needs the row counts, so a routing step and the
+ * GEMMs after it can be enqueued (or captured) without a read-back.  Row blocks past a group's count are skipped;
+ * rows between the count and the end of its last 128-row block are computed like real rows (as in the contiguous
+ * layout).  Counts are clamped to [0, max_m].
+ * fold_swiglu != 0: `a` is the (E * max_m, 2 K) gate+up output and the activation is
+ * Q(silu(a[:, :K]) * a[:, K:]) as in nvfp4_grouped_gemm_swiglu_contiguous (derived_div8 only).
+ * Replaces: GemmType::MGroupedMasked of the reference's kernel (include/nvfp4_gemm/common/types.cuh:22-24,
+ * scheduler/grouped_gemm.cuh:139-156, epilogue/sm100_store_cd.cuh:134), which its host API never exposes.
+ * Normal orientation, N % 256 == 0, K % 128 == 0. */
+NVFP4_API int nvfp4_grouped_gemm_masked(const void* a, int64_t lda_elems, const void* b, const void* sfb, const float* gw,
+                                        void* d, int64_t ldd_elems, const int32_t* masked_m, int E, int max_m, int N, int K,
+                                        int scale_policy, int enable_residual_pass, int fold_swiglu, const int32_t* tune,
+                                        int32_t* device_status, void* stream);
+
+/* NVFP4 checkpoint tensors -> (b, sfb, gw) as the GEMM reads them, on the GPU.
+ * A checkpoint stores every projection of an expert separately: weight_packed (rows, K/2) two E2M1 codes per byte
+ * (even element low), weight_scale (rows, K/16) E4M3 bytes row-major, and one FP32 weight_global_scale.  Here every
+ * part p < num_parts is given stacked over the experts: weight_packed[p] (E, part_rows[p], K/2), weight_scale[p]
+ * (E, part_rows[p], K/16), weight_global_scale[p] (E,); the arrays of pointers are HOST arrays of DEVICE pointers.
+ * The parts are fused along N in the order given (gate then up for a fused gate+up projection; one part for a
+ * down projection): b (E * N, K/2), sfb (E * K/64, N) int32, N = sum of part_rows.  gw[e] becomes the largest of
+ * the parts' global multipliers and every block scale is re-folded to S' = Q_e4m3(S * (G_p / gw[e])), the step the
+ * reference leaves to "the real weight loader" (docs/bf16-dual-nvfp4-algorithm.html:235-244).  With one part the
+ * result is the checkpoint's own codes and scales bit for bit.
+ * global_scale_is_divisor != 0: w = dec(q) * dec(S) / weight_global_scale (the convention of checkpoints that use
+ * these tensor names); 0: w = dec(q) * dec(S) * weight_global_scale.  K % 64 == 0. */
+#define NVFP4_MAX_CHECKPOINT_PARTS 4
+NVFP4_API int nvfp4_load_checkpoint_weights(int num_parts, const void* const* weight_packed, const void* const* weight_scale,
+                                            const float* const* weight_global_scale, const int32_t* part_rows,
+                                            int global_scale_is_divisor, int E, int K, void* b, void* sfb, float* gw,
+                                            void* stream);
+
+/* Reads and clears a kernel status word: copies *device_status to the host on `stream`, resets it to 0, waits for the
+ * stream, stores the value through host_value (may be NULL) and returns NVFP4_OK if it was 0, NVFP4_E_DEVICE_TIMEOUT
+ * if a bounded in-kernel wait had expired (bit 0).  Synchronous; not for use during stream capture. */
+NVFP4_API int nvfp4_read_status(int32_t* device_status, int32_t* host_value, void* stream);
 
 /* The down-projection of a SwiGLU expert MLP with the activation folded into the activation-quantisation kernel:
  * d[M,N] = Q(silu(h[:, :K]) * h[:, K:]) * W^T * gw[expert], where h (M, 2 K) BF16 with row stride ldh_elems is the
@@ -185,6 +234,19 @@ NVFP4_API int nvfp4_combine_rows_peer(const int64_t* peers, int64_t rows_ld_elem
  *   q0, q1 (M, K/2) bytes (two codes per byte, even element low); s0, s1 (M, K/16) bytes */
 NVFP4_API int nvfp4_debug_decompose(const void* a, int64_t lda_elems, int M, int K, int scale_policy,
                           void* q0, void* q1, void* s0, void* s1, void* stream);
+
+/* Test hook: the first kernel of the two-kernel (split) path alone, into buffers of the caller, so that the
+ * quantised activations the GEMM consumes can be compared byte for byte: a0, a1 (M, K/2) packed codes, sfa
+ * (M/128, K/64, passes, 512) bytes, one tensor-memory-image scale atom per 128 rows x 64 K x pass (row r of an atom
+ * at byte (r % 32) * 16 + (r / 32) * 4, byte j = 16-block j).  M % 128 == 0, K % 128 == 0. */
+NVFP4_API int nvfp4_debug_split_workspace(const void* a, int64_t lda_elems, int M, int K, int scale_policy,
+                                          int enable_residual_pass, int fold_swiglu, void* a0, void* a1, void* sfa,
+                                          void* stream);
+
+/* Test hook: launches one CTA in which a thread waits, for at most budget_cycles clock cycles, on a barrier nobody
+ * signals, while the CTA holds tensor memory.  The wait runs out, the kernel ORs bit 0 into *device_status, unwinds
+ * the way the GEMM kernels do (every role leaves, tensor memory is freed) and returns: the context stays usable. */
+NVFP4_API int nvfp4_debug_wait_timeout(int64_t budget_cycles, int32_t* device_status, void* stream);
 
 /* Measurement hook: issues `iters` rounds of resident-operand block-scaled FP4 MMAs
  * (128 x 256 x 64 each) per SM with no memory traffic and returns through

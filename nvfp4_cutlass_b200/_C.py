@@ -30,7 +30,8 @@ EXPORTS = ("nvfp4_last_error", "nvfp4_version", "nvfp4_get_num_sms", "nvfp4_set_
            "nvfp4_quantize_weight", "nvfp4_quantize_weight_static", "nvfp4_grouped_gemm_contiguous", "nvfp4_debug_decompose",
            "nvfp4_debug_mma_peak", "nvfp4_debug_mma_pattern", "nvfp4_permute_rows", "nvfp4_swiglu", "nvfp4_combine_rows",
            "nvfp4_dispatch_rows_peer", "nvfp4_combine_rows_peer", "nvfp4_plan_peer", "nvfp4_expert_histogram",
-           "nvfp4_grouped_gemm_swiglu_contiguous")
+           "nvfp4_grouped_gemm_swiglu_contiguous", "nvfp4_grouped_gemm_masked", "nvfp4_load_checkpoint_weights",
+           "nvfp4_read_status", "nvfp4_debug_split_workspace", "nvfp4_debug_wait_timeout")
 
 
 def library_path() -> str:
@@ -64,6 +65,11 @@ def lib() -> ctypes.CDLL:
         L.nvfp4_plan_peer.argtypes = [vp, i32, i32, i32, i32, vp, i64, vp, vp, vp, vp]
         L.nvfp4_combine_rows_peer.argtypes = [vp, i64, vp, vp, vp, i64, i32, i32, vp, i64, vp]
         L.nvfp4_combine_rows.argtypes = [vp, i64, vp, vp, i64, i32, i32, vp, i64, vp]
+        L.nvfp4_grouped_gemm_masked.argtypes = [vp, i64, vp, vp, vp, vp, i64, vp, i32, i32, i32, i32, i32, i32, i32, vp, vp, vp]
+        L.nvfp4_load_checkpoint_weights.argtypes = [i32, vp, vp, vp, vp, i32, i32, i32, vp, vp, vp, vp]
+        L.nvfp4_read_status.argtypes = [vp, ctypes.POINTER(ctypes.c_int32), vp]
+        L.nvfp4_debug_split_workspace.argtypes = [vp, i64, i32, i32, i32, i32, i32, vp, vp, vp, vp]
+        L.nvfp4_debug_wait_timeout.argtypes = [i64, vp, vp]
         L.nvfp4_debug_mma_peak.argtypes = [i32, ctypes.POINTER(ctypes.c_double), vp]
         L.nvfp4_debug_mma_pattern.argtypes = [i32, i32, i32, i32, i32, ctypes.POINTER(ctypes.c_double), vp]
         _lib = L
@@ -82,6 +88,21 @@ def _stream() -> int:
 def _require(cond: bool, what: str) -> None:
     if not cond:
         raise RuntimeError(f"nvfp4_gemm: assertion failed: {what}")
+
+
+def _one_device(*tensors) -> torch.device:
+    """All tensors are CUDA tensors of ONE device; returns it.  The library launches on the current device and
+    stream, so every wrapper below makes that device current for the call (``with torch.cuda.device(...)``): stream,
+    memory pool, SM count and tensor maps then belong to the GPU that holds the operands."""
+    dev = None
+    for t in tensors:
+        if t is None:
+            continue
+        _require(isinstance(t, torch.Tensor) and t.is_cuda, "every operand is a CUDA tensor")
+        dev = t.device if dev is None else dev
+        _require(t.device == dev, f"all operands are on one device (found {dev} and {t.device})")
+    _require(dev is not None, "at least one tensor operand")
+    return dev
 
 
 def init(include_root: str = "", cuda_home: str = "") -> None:
@@ -131,6 +152,7 @@ def m_grouped_bf16_dual_nvfp4_gemm_contiguous(a, b, sfb, gw, d, m_indices, scale
     _require(sfb.shape[1] == n, "sfb.size(1) == n")
     for name, t in (("a", a), ("b", b), ("sfb", sfb), ("gw", gw), ("d", d), ("m_indices", m_indices)):
         _require(t.is_cuda, f"{name} is a CUDA tensor")
+    dev = _one_device(a, b, sfb, gw, d, m_indices, device_status)
     _require(a.stride(1) == 1 and d.stride(1) == 1, "a and d are contiguous along their last dimension")
     _require(b.is_contiguous() and sfb.is_contiguous() and gw.is_contiguous() and m_indices.is_contiguous(),
              "b, sfb, gw, m_indices are contiguous")
@@ -140,11 +162,117 @@ def m_grouped_bf16_dual_nvfp4_gemm_contiguous(a, b, sfb, gw, d, m_indices, scale
     tune_arr = (ctypes.c_int32 * len(TUNE_KEYS))(*[int(tune.get(key, 0)) for key in TUNE_KEYS])
     lda = a.stride(0) if m > 1 else max(a.stride(0), k)
     ldd = d.stride(0) if m > 1 else max(d.stride(0), n)
-    _check(lib().nvfp4_grouped_gemm_contiguous(
-        a.data_ptr(), lda, b.data_ptr(), sfb.data_ptr(), gw.data_ptr(), d.data_ptr(), ldd,
-        m_indices.data_ptr(), m, n, k, e, POLICY_CODES[scale_policy], 1 if enable_residual_pass else 0,
-        1 if swap else 0, int(m_alignment), ctypes.cast(tune_arr, ctypes.c_void_p),
-        device_status.data_ptr() if device_status is not None else None, _stream()))
+    with torch.cuda.device(dev):
+        _check(lib().nvfp4_grouped_gemm_contiguous(
+            a.data_ptr(), lda, b.data_ptr(), sfb.data_ptr(), gw.data_ptr(), d.data_ptr(), ldd,
+            m_indices.data_ptr(), m, n, k, e, POLICY_CODES[scale_policy], 1 if enable_residual_pass else 0,
+            1 if swap else 0, int(m_alignment), ctypes.cast(tune_arr, ctypes.c_void_p),
+            device_status.data_ptr() if device_status is not None else None, _stream()))
+
+
+def m_grouped_bf16_dual_nvfp4_gemm_masked(a, b, sfb, gw, d, masked_m, scale_policy: str = "derived_div8",
+                                          enable_residual_pass: bool = True, *, fold_swiglu: bool = False,
+                                          device_status=None, **tune) -> None:
+    """The same GEMM over the masked layout: ``a`` (E, max_m, K) and ``d`` (E, max_m, N) BF16 (last dimension
+    contiguous, groups max_m rows apart), ``masked_m`` int32 (E,) on the device = real rows of each group.  With
+    ``fold_swiglu`` ``a`` is the (E, max_m, 2 K) gate+up output and the activation is silu(gate) * up."""
+    for key in tune:
+        if key not in TUNE_KEYS:
+            raise TypeError(f"m_grouped_bf16_dual_nvfp4_gemm_masked() got an unexpected keyword argument {key!r}")
+    _require(a.dtype == torch.bfloat16 and d.dtype == torch.bfloat16, "a and d are bfloat16")
+    _require(b.dtype == torch.int8 and sfb.dtype == torch.int32 and gw.dtype == torch.float32 and masked_m.dtype == torch.int32,
+             "b int8, sfb int32, gw float32, masked_m int32")
+    _require(a.dim() == 3 and d.dim() == 3 and a.shape[:2] == d.shape[:2], "a (E, max_m, K) and d (E, max_m, N)")
+    e, max_m, ka = a.shape
+    k = ka // 2 if fold_swiglu else ka
+    n = d.shape[2]
+    _require(gw.numel() == e and masked_m.numel() == e, "gw and masked_m have one entry per group")
+    _require(b.shape == (e * n, k // 2) and sfb.shape == (e * (k // 64), n), "weight shapes do not fit")
+    dev = _one_device(a, b, sfb, gw, d, masked_m, device_status)
+    _require(a.stride(2) == 1 and d.stride(2) == 1 and a.stride(0) == max_m * a.stride(1) and d.stride(0) == max_m * d.stride(1),
+             "a and d: last dimension contiguous, groups max_m rows apart")
+    _require(b.is_contiguous() and sfb.is_contiguous() and gw.is_contiguous() and masked_m.is_contiguous(),
+             "b, sfb, gw, masked_m are contiguous")
+    if scale_policy not in POLICY_CODES:
+        raise RuntimeError("scale_policy must be 'derived_div8', 'derived_div4', 'div4_radix8' or 'residual_amax'")
+    tune_arr = (ctypes.c_int32 * len(TUNE_KEYS))(*[int(tune.get(key, 0)) for key in TUNE_KEYS])
+    with torch.cuda.device(dev):
+        _check(lib().nvfp4_grouped_gemm_masked(
+            a.data_ptr(), a.stride(1), b.data_ptr(), sfb.data_ptr(), gw.data_ptr(), d.data_ptr(), d.stride(1),
+            masked_m.data_ptr(), e, max_m, n, k, POLICY_CODES[scale_policy], 1 if enable_residual_pass else 0,
+            1 if fold_swiglu else 0, ctypes.cast(tune_arr, ctypes.c_void_p),
+            device_status.data_ptr() if device_status is not None else None, _stream()))
+
+
+def load_checkpoint_weights(parts, global_scale_is_divisor: bool = True):
+    """NVFP4 checkpoint tensors -> (b, sfb, gw).  ``parts`` lists the projections to fuse along N, in order, each as
+    (weight_packed uint8 (E, rows, K/2), weight_scale float8_e4m3fn or uint8 (E, rows, K/16), weight_global_scale
+    float32 (E,) or (E, 1)); gate and up of one expert MLP make a fused gate+up projection, a down projection is a
+    single part.  Runs on the GPU (nvfp4_load_checkpoint_weights); see the header for the re-folding rule."""
+    _require(1 <= len(parts) <= 4, "between one and four parts")
+    packed, scale, glob = [], [], []
+    for wp, ws, wg in parts:
+        _require(wp.dim() == 3 and ws.dim() == 3 and wp.dtype in (torch.uint8, torch.int8), "weight_packed is (E, rows, K/2) bytes")
+        if ws.dtype != torch.uint8:
+            _require(ws.dtype == torch.float8_e4m3fn, "weight_scale is float8_e4m3fn or uint8")
+            ws = ws.view(torch.uint8)
+        packed.append(wp.contiguous())
+        scale.append(ws.contiguous())
+        glob.append(wg.reshape(-1).to(torch.float32).contiguous())
+    e, _, k2 = packed[0].shape
+    k = 2 * k2
+    for wp, ws, wg in zip(packed, scale, glob):
+        _require(wp.shape[0] == e and wp.shape[2] == k2 and ws.shape == (e, wp.shape[1], k // 16) and wg.numel() == e,
+                 "parts disagree on E / K, or a scale tensor does not fit its codes")
+    if k % 64 != 0:
+        raise ValueError(f"K={k} must be a multiple of 64")
+    dev = _one_device(*packed, *scale, *glob)
+    n = sum(wp.shape[1] for wp in packed)
+    b = torch.empty(e * n, k // 2, dtype=torch.int8, device=dev)
+    sfb = torch.empty(e * k // 64, n, dtype=torch.int32, device=dev)
+    gw = torch.empty(e, dtype=torch.float32, device=dev)
+    ptrs = lambda ts: (ctypes.c_void_p * len(ts))(*[t.data_ptr() for t in ts])
+    rows = (ctypes.c_int32 * len(packed))(*[wp.shape[1] for wp in packed])
+    with torch.cuda.device(dev):
+        _check(lib().nvfp4_load_checkpoint_weights(len(packed), ctypes.cast(ptrs(packed), ctypes.c_void_p),
+                                                   ctypes.cast(ptrs(scale), ctypes.c_void_p), ctypes.cast(ptrs(glob), ctypes.c_void_p),
+                                                   ctypes.cast(rows, ctypes.c_void_p), 1 if global_scale_is_divisor else 0, e, k,
+                                                   b.data_ptr(), sfb.data_ptr(), gw.data_ptr(), _stream()))
+    return b, sfb, gw
+
+
+def read_status(device_status: torch.Tensor) -> int:
+    """Reads and clears a kernel status word (synchronises the current stream); raises RuntimeError carrying
+    NVFP4_E_DEVICE_TIMEOUT if a bounded in-kernel wait had expired, else returns 0."""
+    _require(device_status.is_cuda and device_status.dtype == torch.int32 and device_status.numel() >= 1, "an int32 CUDA tensor")
+    value = ctypes.c_int32(0)
+    with torch.cuda.device(device_status.device):
+        _check(lib().nvfp4_read_status(device_status.data_ptr(), ctypes.byref(value), _stream()))
+    return value.value
+
+
+def debug_wait_timeout(budget_cycles: int, device_status: torch.Tensor) -> None:
+    """Launches the kernel whose bounded wait runs out (test hook of the unwind path)."""
+    with torch.cuda.device(device_status.device):
+        _check(lib().nvfp4_debug_wait_timeout(int(budget_cycles), device_status.data_ptr(), _stream()))
+
+
+def debug_split_workspace(a: torch.Tensor, scale_policy: str = "derived_div8", enable_residual_pass: bool = True,
+                          fold_swiglu: bool = False):
+    """The split path's activation-quantisation kernel alone: returns (a0, a1, sfa) as uint8 CUDA tensors, a0 / a1
+    (M, K/2) packed codes and sfa (M/128, K/64, passes, 512) scale atoms -- exactly what the GEMM kernel reads."""
+    _require(a.is_cuda and a.dtype == torch.bfloat16 and a.dim() == 2 and a.stride(1) == 1, "a is a 2-D BF16 CUDA tensor")
+    m, ka = a.shape
+    k = ka // 2 if fold_swiglu else ka
+    passes = 2 if enable_residual_pass else 1
+    a0 = torch.zeros(m, k // 2, dtype=torch.uint8, device=a.device)
+    a1 = torch.zeros_like(a0)
+    sfa = torch.zeros(m // 128, k // 64, passes, 512, dtype=torch.uint8, device=a.device)
+    with torch.cuda.device(a.device):
+        _check(lib().nvfp4_debug_split_workspace(a.data_ptr(), a.stride(0), m, k, POLICY_CODES[scale_policy],
+                                                 1 if enable_residual_pass else 0, 1 if fold_swiglu else 0,
+                                                 a0.data_ptr(), a1.data_ptr(), sfa.data_ptr(), _stream()))
+    return a0, a1, sfa
 
 
 def quantize_weight(w: torch.Tensor):
@@ -174,9 +302,10 @@ def permute_rows(src: torch.Tensor, n_rows: int, dst: torch.Tensor, src_idx: tor
     for idx in (src_idx, dst_idx):
         _require(idx is None or (idx.is_cuda and idx.dtype == torch.int64 and idx.is_contiguous() and idx.numel() >= n_rows),
                  "indices are contiguous int64 CUDA tensors with at least n_rows entries")
-    _check(lib().nvfp4_permute_rows(src.data_ptr(), src.stride(0) * 2, src_idx.data_ptr() if src_idx is not None else None,
-                                    src_div, dst_idx.data_ptr() if dst_idx is not None else None, n_rows, src.shape[1] * 2,
-                                    dst.data_ptr(), dst.stride(0) * 2, _stream()))
+    with torch.cuda.device(_one_device(src, dst, src_idx, dst_idx)):
+        _check(lib().nvfp4_permute_rows(src.data_ptr(), src.stride(0) * 2, src_idx.data_ptr() if src_idx is not None else None,
+                                        src_div, dst_idx.data_ptr() if dst_idx is not None else None, n_rows, src.shape[1] * 2,
+                                        dst.data_ptr(), dst.stride(0) * 2, _stream()))
 
 
 def swiglu(h: torch.Tensor) -> torch.Tensor:
@@ -184,7 +313,8 @@ def swiglu(h: torch.Tensor) -> torch.Tensor:
     _require(_rows_ok(h) and h.shape[1] % 16 == 0, "h is a 2-D BF16 CUDA tensor whose width is a multiple of 16")
     inter = h.shape[1] // 2
     out = torch.empty(h.shape[0], inter, dtype=torch.bfloat16, device=h.device)
-    _check(lib().nvfp4_swiglu(h.data_ptr(), h.stride(0), h.shape[0], inter, out.data_ptr(), out.stride(0), _stream()))
+    with torch.cuda.device(_one_device(h)):
+        _check(lib().nvfp4_swiglu(h.data_ptr(), h.stride(0), h.shape[0], inter, out.data_ptr(), out.stride(0), _stream()))
     return out
 
 
@@ -196,8 +326,9 @@ def combine_rows(rows: torch.Tensor, pos: torch.Tensor, w: torch.Tensor, tokens:
              "pos (int64) and w (float32) are contiguous CUDA tensors of tokens * k entries")
     y = torch.empty(tokens, rows.shape[1], dtype=torch.bfloat16, device=rows.device)
     k = pos.numel() // tokens if tokens else 1
-    _check(lib().nvfp4_combine_rows(rows.data_ptr(), rows.stride(0), pos.data_ptr(), w.data_ptr(), tokens, k, rows.shape[1],
-                                    y.data_ptr(), y.stride(0), _stream()))
+    with torch.cuda.device(_one_device(rows, pos, w)):
+        _check(lib().nvfp4_combine_rows(rows.data_ptr(), rows.stride(0), pos.data_ptr(), w.data_ptr(), tokens, k, rows.shape[1],
+                                        y.data_ptr(), y.stride(0), _stream()))
     return y
 
 
@@ -216,17 +347,19 @@ def m_grouped_swiglu_dual_nvfp4_gemm_contiguous(h, b, sfb, gw, d, m_indices, ena
              "operand shapes do not fit together")
     _require(b.is_contiguous() and sfb.is_contiguous() and gw.is_contiguous() and m_indices.is_contiguous(),
              "b, sfb, gw and m_indices are contiguous")
-    _check(lib().nvfp4_grouped_gemm_swiglu_contiguous(
-        h.data_ptr(), h.stride(0), b.data_ptr(), sfb.data_ptr(), gw.data_ptr(), d.data_ptr(), d.stride(0),
-        m_indices.data_ptr(), m, n, k, e, 1 if enable_residual_pass else 0, None,
-        device_status.data_ptr() if device_status is not None else None, _stream()))
+    with torch.cuda.device(_one_device(h, b, sfb, gw, d, m_indices, device_status)):
+        _check(lib().nvfp4_grouped_gemm_swiglu_contiguous(
+            h.data_ptr(), h.stride(0), b.data_ptr(), sfb.data_ptr(), gw.data_ptr(), d.data_ptr(), d.stride(0),
+            m_indices.data_ptr(), m, n, k, e, 1 if enable_residual_pass else 0, None,
+            device_status.data_ptr() if device_status is not None else None, _stream()))
 
 
 def expert_histogram(ids: torch.Tensor, num_experts: int) -> torch.Tensor:
     """counts[e] = number of entries of ids equal to e (int64 CUDA tensors)."""
     _require(_i64_ok(ids, ids.numel()), "ids is a contiguous int64 CUDA tensor")
     counts = torch.empty(num_experts, dtype=torch.int64, device=ids.device)
-    _check(lib().nvfp4_expert_histogram(ids.data_ptr(), ids.numel(), num_experts, counts.data_ptr(), _stream()))
+    with torch.cuda.device(_one_device(ids)):
+        _check(lib().nvfp4_expert_histogram(ids.data_ptr(), ids.numel(), num_experts, counts.data_ptr(), _stream()))
     return counts
 
 
@@ -239,8 +372,9 @@ def plan_peer(all_counts: torch.Tensor, ids: torch.Tensor, world: int, rank: int
     base = torch.empty(num_experts, dtype=torch.int64, device=ids.device)
     sizes = torch.empty(2 * (num_experts // world) + 1, dtype=torch.int64, device=ids.device)
     dst_row = torch.empty(ids.numel(), dtype=torch.int64, device=ids.device)
-    _check(lib().nvfp4_plan_peer(all_counts.data_ptr(), world, num_experts, rank, alignment, ids.data_ptr(), ids.numel(),
-                                 base.data_ptr(), sizes.data_ptr(), dst_row.data_ptr(), _stream()))
+    with torch.cuda.device(_one_device(all_counts, ids)):
+        _check(lib().nvfp4_plan_peer(all_counts.data_ptr(), world, num_experts, rank, alignment, ids.data_ptr(), ids.numel(),
+                                     base.data_ptr(), sizes.data_ptr(), dst_row.data_ptr(), _stream()))
     return sizes, dst_row
 
 
@@ -252,9 +386,10 @@ def dispatch_rows_peer(src: torch.Tensor, src_idx, src_div: int, peers: torch.Te
     _require(_rows_ok(src), "src is a 2-D BF16 CUDA tensor")
     _require((src_idx is None or _i64_ok(src_idx, n)) and _i64_ok(dst_rank, n) and _i64_ok(dst_row, n) and _i64_ok(peers, 1),
              "indices and peer addresses are contiguous int64 CUDA tensors")
-    _check(lib().nvfp4_dispatch_rows_peer(src.data_ptr(), src.stride(0) * 2, src_idx.data_ptr() if src_idx is not None else None,
-                                          src_div, peers.data_ptr(),
-                                          dst_rank.data_ptr(), dst_row.data_ptr(), n, src.shape[1] * 2, dst_ld_elems * 2, _stream()))
+    with torch.cuda.device(_one_device(src, src_idx, peers, dst_rank, dst_row)):
+        _check(lib().nvfp4_dispatch_rows_peer(src.data_ptr(), src.stride(0) * 2, src_idx.data_ptr() if src_idx is not None else None,
+                                              src_div, peers.data_ptr(),
+                                              dst_rank.data_ptr(), dst_row.data_ptr(), n, src.shape[1] * 2, dst_ld_elems * 2, _stream()))
 
 
 def combine_rows_peer(peers: torch.Tensor, rows_ld_elems: int, src_rank: torch.Tensor, src_row: torch.Tensor, w: torch.Tensor,
@@ -265,8 +400,9 @@ def combine_rows_peer(peers: torch.Tensor, rows_ld_elems: int, src_rank: torch.T
              w.is_contiguous() and w.numel() == n and n % max(tokens, 1) == 0, "bad index / weight tensors")
     y = torch.empty(tokens, hidden, dtype=torch.bfloat16, device=w.device)
     k = n // tokens if tokens else 1
-    _check(lib().nvfp4_combine_rows_peer(peers.data_ptr(), rows_ld_elems, src_rank.data_ptr(), src_row.data_ptr(), w.data_ptr(),
-                                         tokens, k, hidden, y.data_ptr(), y.stride(0), _stream()))
+    with torch.cuda.device(_one_device(peers, src_rank, src_row, w)):
+        _check(lib().nvfp4_combine_rows_peer(peers.data_ptr(), rows_ld_elems, src_rank.data_ptr(), src_row.data_ptr(), w.data_ptr(),
+                                             tokens, k, hidden, y.data_ptr(), y.stride(0), _stream()))
     return y
 
 
@@ -279,8 +415,9 @@ def debug_decompose(a: torch.Tensor, scale_policy: str = "derived_div8"):
     q1 = torch.empty_like(q0)
     s0 = torch.empty(m, k // 16, dtype=torch.uint8, device=a.device)
     s1 = torch.empty_like(s0)
-    _check(lib().nvfp4_debug_decompose(a.data_ptr(), a.stride(0), m, k, POLICY_CODES[scale_policy],
-                                       q0.data_ptr(), q1.data_ptr(), s0.data_ptr(), s1.data_ptr(), _stream()))
+    with torch.cuda.device(_one_device(a)):
+        _check(lib().nvfp4_debug_decompose(a.data_ptr(), a.stride(0), m, k, POLICY_CODES[scale_policy],
+                                           q0.data_ptr(), q1.data_ptr(), s0.data_ptr(), s1.data_ptr(), _stream()))
     return q0, q1, s0, s1
 
 

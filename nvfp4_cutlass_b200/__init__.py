@@ -8,11 +8,14 @@ __version__ = "0.1.0"
 
 from . import _C, layout
 from ._C import get_num_sms, m_grouped_bf16_dual_nvfp4_gemm_contiguous, set_num_sms
-from .layout import dequantize_weight_nvfp4, make_m_indices, quantize_weight_nvfp4
+from ._C import m_grouped_bf16_dual_nvfp4_gemm_masked
+from .layout import dequantize_weight_nvfp4, load_checkpoint_weights_nvfp4, make_m_indices, quantize_weight_nvfp4
 
 __all__ = [
     "m_grouped_bf16_dual_nvfp4_gemm_contiguous",
+    "m_grouped_bf16_dual_nvfp4_gemm_masked",
     "quantize_weight_nvfp4",
+    "load_checkpoint_weights_nvfp4",
     "dequantize_weight_nvfp4",
     "make_m_indices",
     "layout",

@@ -1,6 +1,7 @@
 // The C ABI (include/nvfp4_b200.h): argument validation, per-device runtime
 // state, dispatch to the kernels.  Counterpart in the reference: src/api.hpp
 // (validation + dispatch), src/runtime/device.hpp, src/runtime/exception.hpp.
+#include <climits>
 #include <cstring>
 #include <mutex>
 
@@ -43,6 +44,27 @@ int device_info(int device, DeviceInfo** out)
     return NVFP4_OK;
 }
 
+int workspace_pool(int dev, cudaMemPool_t* out)
+{
+    static cudaMemPool_t pools[kMaxDevices] = {};
+    if (dev < 0 || dev >= kMaxDevices) return fail(NVFP4_E_INVALID_ARGUMENT, "device %d out of range", dev);
+    std::lock_guard<std::mutex> lock(g_mutex);
+    if (pools[dev] == nullptr) {
+        cudaMemPoolProps props = {};
+        props.allocType = cudaMemAllocationTypePinned;
+        props.handleTypes = cudaMemHandleTypeNone;
+        props.location.type = cudaMemLocationTypeDevice;
+        props.location.id = dev;
+        cudaMemPool_t pool = nullptr;
+        NVFP4_CUDA_CHECK(cudaMemPoolCreate(&pool, &props));
+        uint64_t keep = UINT64_MAX;
+        NVFP4_CUDA_CHECK(cudaMemPoolSetAttribute(pool, cudaMemPoolAttrReleaseThreshold, &keep));
+        pools[dev] = pool;
+    }
+    *out = pools[dev];
+    return NVFP4_OK;
+}
+
 int encode_tensor_map_2d(CUtensorMap* map, CUtensorMapDataType dtype, uint32_t elem_bytes, const void* base,
                          uint64_t dim0, uint64_t dim1, uint64_t row_stride_bytes, uint32_t box0, uint32_t box1,
                          CUtensorMapSwizzle swizzle)
@@ -64,6 +86,32 @@ int encode_tensor_map_2d(CUtensorMap* map, CUtensorMapDataType dtype, uint32_t e
     if (row_stride_bytes % 16 != 0)
         return fail(NVFP4_E_INVALID_ARGUMENT, "row stride of %llu bytes is not a multiple of 16",
                     static_cast<unsigned long long>(row_stride_bytes));
+    // Encoded maps are kept per (type, base, shape, stride, box, swizzle): weights keep their address from call to
+    // call and the pooled workspace usually does, so an eager call costs look-ups instead of driver calls.
+    // Counterpart in the reference: the per-launch encodes of src/runtime/tma_desc.hpp:56-67.
+    struct Key {
+        uint64_t base, dim0, dim1, stride;
+        uint32_t box0, box1, dtype, swizzle;
+        bool operator==(const Key& o) const
+        {
+            return base == o.base && dim0 == o.dim0 && dim1 == o.dim1 && stride == o.stride && box0 == o.box0 &&
+                   box1 == o.box1 && dtype == o.dtype && swizzle == o.swizzle;
+        }
+    };
+    struct Entry { Key key; CUtensorMap map; bool used; };
+    constexpr uint32_t kCacheSize = 256;                       // direct-mapped: a collision just re-encodes
+    static Entry cache[kCacheSize] = {};
+    static std::mutex cache_mutex;
+    const Key key{reinterpret_cast<uint64_t>(base), dim0, dim1, row_stride_bytes, box0, box1,
+                  static_cast<uint32_t>(dtype), static_cast<uint32_t>(swizzle)};
+    uint64_t h = key.base * 0x9e3779b97f4a7c15ull ^ (key.dim0 * 31 + key.dim1) * 0xbf58476d1ce4e5b9ull ^
+                 (static_cast<uint64_t>(key.box0) << 40 | static_cast<uint64_t>(key.box1) << 20 | key.swizzle << 8 | key.dtype);
+    h ^= h >> 29;
+    Entry& slot = cache[h % kCacheSize];
+    {
+        std::lock_guard<std::mutex> lock(cache_mutex);
+        if (slot.used && slot.key == key) { *map = slot.map; return NVFP4_OK; }
+    }
     const cuuint64_t dims[2] = {dim0, dim1};
     const cuuint64_t strides[1] = {row_stride_bytes};
     const cuuint32_t box[2] = {box0, box1};
@@ -76,6 +124,12 @@ int encode_tensor_map_2d(CUtensorMap* map, CUtensorMapDataType dtype, uint32_t e
         return fail(NVFP4_E_CUDA, "cuTensorMapEncodeTiled failed with CUresult %d (dims %llu x %llu, box %u x %u)",
                     static_cast<int>(r), static_cast<unsigned long long>(dim0),
                     static_cast<unsigned long long>(dim1), box0, box1);
+    {
+        std::lock_guard<std::mutex> lock(cache_mutex);
+        slot.key = key;
+        slot.map = *map;
+        slot.used = true;
+    }
     return NVFP4_OK;
 }
 
@@ -172,8 +226,8 @@ int nvfp4_grouped_gemm_contiguous(const void* a, int64_t lda_elems, const void* 
                   static_cast<long long>(lda_elems), static_cast<long long>(ldd_elems));
     NVFP4_REQUIRE(lda_elems % 8 == 0 && ldd_elems % 8 == 0, "row strides must be multiples of 8 elements (16 bytes)");
     NVFP4_REQUIRE((reinterpret_cast<uintptr_t>(d) & 15u) == 0, "d must be 16-byte aligned");
-    if (scale_policy != NVFP4_POLICY_DERIVED_DIV8 && scale_policy != NVFP4_POLICY_RESIDUAL_AMAX)
-        return host::fail(NVFP4_E_UNSUPPORTED, "scale policy %d is not built; derived_div8 and residual_amax are", scale_policy);
+    NVFP4_REQUIRE(scale_policy >= NVFP4_POLICY_DERIVED_DIV8 && scale_policy <= NVFP4_POLICY_DIV4_RADIX8,
+                  "unknown scale policy %d", scale_policy);
 
     host::DeviceInfo* dev;
     if (int rc = host::device_info(-1, &dev)) return rc;
@@ -193,15 +247,17 @@ int nvfp4_grouped_gemm_contiguous(const void* a, int64_t lda_elems, const void* 
         NVFP4_REQUIRE(tune_block_k == 0 || tune_block_k == 128 || tune_block_k == 256 || tune_block_k == 512,
                       "tune_block_k must be 0, 128, 256 or 512");
         return launch_gemm_swap(a, lda_elems, b, sfb, gw, d, ldd_elems, m_indices, M, N, K, E, enable_residual_pass != 0,
-                                tile, tune_block_k, scale_policy, dev->num_sms, device_status, s);
+                                tile, tune_block_k, scale_policy, !(tune && tune[11]), dev->num_sms, device_status, s);
     }
     NVFP4_REQUIRE(tune_xform_warps == 0 || tune_xform_warps == 8 || tune_xform_warps == 16,
                   "tune_transform_warps must be 0, 8 or 16");
     // tune_cluster: 2 / 4 = that many CTAs share one transformed activation tile (needs N % (256 * cluster) == 0),
     // 1 = single-CTA kernel, 0 = the library's choice
     // tune_split_transform: 1 = quantise the activations once, in a kernel of their own, ahead of a GEMM without
-    // transform warps (N % 256 == 0); 2 = decompose inside the GEMM main loop; 0 = the library's choice
+    // transform warps (N % 256 == 0); 2 = decompose inside the GEMM main loop; 0 = the library's choice.  (In the
+    // reference this keyword signals A0 readiness early inside its one kernel; here it chooses between the two paths.)
     const int tune_split = tune ? tune[13] : 0;
+    const bool pdl = !(tune && tune[11]);                           // tune_no_pdl
     NVFP4_REQUIRE(tune_split >= 0 && tune_split <= 2, "tune_split_transform must be 0, 1 or 2");
     NVFP4_REQUIRE(tune_split != 1 || N % 256 == 0, "tune_split_transform=1 needs N %% 256 == 0 (N=%d)", N);
     // The library's choice: the separate pass wins as soon as an activation tile is visited by several column
@@ -209,28 +265,27 @@ int nvfp4_grouped_gemm_contiguous(const void* a, int64_t lda_elems, const void* 
     const bool fused_knobs = tune && (tune[8] != 0 || tune[1] != 0 || tune[9] != 0);
     if (tune_split == 1 || (tune_split == 0 && !fused_knobs && N % 256 == 0 && N >= 1024)) {
         const int tune_block_k = tune ? tune[5] : 0;
-        return launch_gemm_split(a, lda_elems, b, sfb, gw, d, ldd_elems, m_indices, M, N, K, E, enable_residual_pass != 0,
-                                 tune_block_k, tune_sched_group, !(tune && tune[11]), scale_policy, false, dev->num_sms, device_status, s);
+        return launch_gemm_split(a, lda_elems, b, sfb, gw, d, ldd_elems, m_indices, nullptr, 0, M, N, K, E,
+                                 enable_residual_pass != 0, tune_block_k, tune_sched_group, pdl, scale_policy, false,
+                                 dev->num_sms, device_status, s);
     }
-    // residual_amax exists in the split path (above) and in the single-CTA fused kernel, not in the cluster kernel
-    if (scale_policy == NVFP4_POLICY_RESIDUAL_AMAX)
-        return launch_gemm_normal(a, lda_elems, b, sfb, gw, d, ldd_elems, m_indices, M, N, K, E, enable_residual_pass != 0,
-                                  0, tune_sched_group, false, scale_policy, dev->num_sms, device_status, s);
     int cluster = tune ? tune[8] : 0;
     NVFP4_REQUIRE(cluster == 0 || cluster == 1 || cluster == 2 || cluster == 4, "tune_cluster must be 0, 1, 2 or 4");
     NVFP4_REQUIRE(cluster < 2 || N % (256 * cluster) == 0, "tune_cluster %d needs N %% %d == 0 (N=%d)", cluster, 256 * cluster, N);
     if (cluster == 0) {
+        // the widest cluster N allows: every doubling halves the Algorithm-1 arithmetic per CTA
         const bool plain = tune_xform_warps == 0 && !(tune && tune[9]);
-        cluster = plain && N % (256 * kDefaultCluster) == 0 ? kDefaultCluster : (plain && N % 512 == 0 ? 2 : 1);
+        cluster = !plain ? 1 : (N % 1024 == 0 ? 4 : (N % 512 == 0 ? 2 : 1));
     }
     if (cluster >= 2 && dev->num_sms >= cluster)
         return launch_gemm_cluster(a, lda_elems, b, sfb, gw, d, ldd_elems, m_indices, M, N, K, E,
-                                   enable_residual_pass != 0, cluster, tune_xform_warps, tune_sched_group, dev->num_sms, device_status, s);
+                                   enable_residual_pass != 0, cluster, scale_policy, tune_sched_group, pdl, dev->num_sms,
+                                   device_status, s);
     // tune_direct_a = 1: the transform reads activations straight from global memory instead of a TMA-fed
     // shared-memory ring (measured slower on B200: 1.89 ms against 1.06 ms on the Mixtral-like shape)
     const bool direct_a = tune && tune[9] == 1 && tune_xform_warps != 16;
     return launch_gemm_normal(a, lda_elems, b, sfb, gw, d, ldd_elems, m_indices, M, N, K, E, enable_residual_pass != 0,
-                              tune_xform_warps, tune_sched_group, direct_a, scale_policy, dev->num_sms, device_status, s);
+                              tune_xform_warps, tune_sched_group, direct_a, scale_policy, pdl, dev->num_sms, device_status, s);
 }
 
 int nvfp4_permute_rows(const void* src, int64_t src_ld_bytes, const int64_t* src_idx, int src_div, const int64_t* dst_idx,
@@ -298,9 +353,108 @@ int nvfp4_grouped_gemm_swiglu_contiguous(const void* h, int64_t ldh_elems, const
     host::DeviceInfo* dev;
     if (int rc = host::device_info(-1, &dev)) return rc;
     if (dev->cc_major != 10) return host::fail(NVFP4_E_UNSUPPORTED, "needs an sm_100 GPU, found sm_%d%d", dev->cc_major, dev->cc_minor);
-    return launch_gemm_split(h, ldh_elems, b, sfb, gw, d, ldd_elems, m_indices, M, N, K, E, enable_residual_pass != 0,
-                             tune ? tune[5] : 0, tune ? tune[12] : 0, !(tune && tune[11]), NVFP4_POLICY_DERIVED_DIV8, true,
-                             dev->num_sms, device_status, static_cast<cudaStream_t>(stream));
+    return launch_gemm_split(h, ldh_elems, b, sfb, gw, d, ldd_elems, m_indices, nullptr, 0, M, N, K, E,
+                             enable_residual_pass != 0, tune ? tune[5] : 0, tune ? tune[12] : 0, !(tune && tune[11]),
+                             NVFP4_POLICY_DERIVED_DIV8, true, dev->num_sms, device_status, static_cast<cudaStream_t>(stream));
+}
+
+int nvfp4_grouped_gemm_masked(const void* a, int64_t lda_elems, const void* b, const void* sfb, const float* gw, void* d,
+                              int64_t ldd_elems, const int32_t* masked_m, int E, int max_m, int N, int K, int scale_policy,
+                              int enable_residual_pass, int fold_swiglu, const int32_t* tune, int32_t* device_status, void* stream)
+{
+    host::clear_error();
+    NVFP4_REQUIRE(E >= 0 && max_m >= 0 && N >= 0 && K >= 0, "negative size (E=%d, max_m=%d, N=%d, K=%d)", E, max_m, N, K);
+    NVFP4_REQUIRE(N % 256 == 0 && K % 128 == 0, "N must be a multiple of 256 and K of 128 (N=%d, K=%d)", N, K);
+    NVFP4_REQUIRE(max_m % 128 == 0, "max_m must be a multiple of 128 (max_m=%d)", max_m);
+    NVFP4_REQUIRE(static_cast<int64_t>(E) * max_m <= INT32_MAX, "E * max_m = %lld rows exceed the 32-bit row index",
+                  static_cast<long long>(E) * max_m);
+    if (E == 0 || max_m == 0 || N == 0) return NVFP4_OK;
+    NVFP4_REQUIRE(K > 0, "empty weights (K=%d)", K);
+    NVFP4_REQUIRE(a && b && sfb && gw && d && masked_m, "null pointer argument");
+    const int64_t a_cols = fold_swiglu ? 2 * static_cast<int64_t>(K) : K;
+    NVFP4_REQUIRE(lda_elems >= a_cols && ldd_elems >= N, "row strides too small (lda=%lld, ldd=%lld)",
+                  static_cast<long long>(lda_elems), static_cast<long long>(ldd_elems));
+    NVFP4_REQUIRE(lda_elems % 8 == 0 && ldd_elems % 8 == 0, "row strides must be multiples of 8 elements (16 bytes)");
+    NVFP4_REQUIRE(((reinterpret_cast<uintptr_t>(a) | reinterpret_cast<uintptr_t>(d)) & 15u) == 0, "a and d must be 16-byte aligned");
+    NVFP4_REQUIRE(scale_policy >= NVFP4_POLICY_DERIVED_DIV8 && scale_policy <= NVFP4_POLICY_DIV4_RADIX8,
+                  "unknown scale policy %d", scale_policy);
+    NVFP4_REQUIRE(!fold_swiglu || scale_policy == NVFP4_POLICY_DERIVED_DIV8, "the SwiGLU-folded form is built for derived_div8 only");
+    host::DeviceInfo* dev;
+    if (int rc = host::device_info(-1, &dev)) return rc;
+    if (dev->cc_major != 10) return host::fail(NVFP4_E_UNSUPPORTED, "needs an sm_100 GPU, found sm_%d%d", dev->cc_major, dev->cc_minor);
+    return launch_gemm_split(a, lda_elems, b, sfb, gw, d, ldd_elems, nullptr, masked_m, max_m, E * max_m, N, K, E,
+                             enable_residual_pass != 0, tune ? tune[5] : 0, tune ? tune[12] : 0, !(tune && tune[11]),
+                             scale_policy, fold_swiglu != 0, dev->num_sms, device_status, static_cast<cudaStream_t>(stream));
+}
+
+int nvfp4_load_checkpoint_weights(int num_parts, const void* const* weight_packed, const void* const* weight_scale,
+                                  const float* const* weight_global_scale, const int32_t* part_rows,
+                                  int global_scale_is_divisor, int E, int K, void* b, void* sfb, float* gw, void* stream)
+{
+    host::clear_error();
+    NVFP4_REQUIRE(num_parts >= 1 && num_parts <= NVFP4_MAX_CHECKPOINT_PARTS, "num_parts %d outside [1, %d]", num_parts,
+                  NVFP4_MAX_CHECKPOINT_PARTS);
+    NVFP4_REQUIRE(E >= 0 && K >= 0 && K % 64 == 0, "K=%d must be a non-negative multiple of 64 (E=%d)", K, E);
+    NVFP4_REQUIRE(weight_packed && weight_scale && weight_global_scale && part_rows, "null pointer argument");
+    int64_t n_total = 0;
+    for (int i = 0; i < num_parts; ++i) {
+        NVFP4_REQUIRE(part_rows[i] > 0, "part %d has %d rows", i, part_rows[i]);
+        NVFP4_REQUIRE(weight_packed[i] && weight_scale[i] && weight_global_scale[i], "null pointer in part %d", i);
+        NVFP4_REQUIRE((reinterpret_cast<uintptr_t>(weight_packed[i]) & 15u) == 0 && (reinterpret_cast<uintptr_t>(weight_scale[i]) & 3u) == 0,
+                      "part %d: weight_packed must be 16-byte and weight_scale 4-byte aligned", i);
+        n_total += part_rows[i];
+    }
+    NVFP4_REQUIRE(n_total <= INT32_MAX, "too many rows");
+    if (E == 0 || K == 0) return NVFP4_OK;
+    NVFP4_REQUIRE(b && sfb && gw, "null pointer argument");
+    NVFP4_REQUIRE((reinterpret_cast<uintptr_t>(b) & 15u) == 0, "b must be 16-byte aligned");
+    return launch_load_checkpoint(num_parts, weight_packed, weight_scale, weight_global_scale, part_rows,
+                                  global_scale_is_divisor != 0, E, K, static_cast<int>(n_total), b, sfb, gw,
+                                  static_cast<cudaStream_t>(stream));
+}
+
+int nvfp4_read_status(int32_t* device_status, int32_t* host_value, void* stream)
+{
+    host::clear_error();
+    NVFP4_REQUIRE(device_status != nullptr, "device_status is null");
+    cudaStream_t s = static_cast<cudaStream_t>(stream);
+    int32_t v = 0;
+    NVFP4_CUDA_CHECK(cudaMemcpyAsync(&v, device_status, sizeof v, cudaMemcpyDeviceToHost, s));
+    NVFP4_CUDA_CHECK(cudaMemsetAsync(device_status, 0, sizeof v, s));
+    NVFP4_CUDA_CHECK(cudaStreamSynchronize(s));
+    if (host_value != nullptr) *host_value = v;
+    if (v & 1)
+        return host::fail(NVFP4_E_DEVICE_TIMEOUT, "a bounded in-kernel wait expired (device status 0x%x); the kernel unwound and "
+                          "released its tensor memory, its output is undefined", v);
+    if (v != 0) return host::fail(NVFP4_E_DEVICE_TIMEOUT, "device status 0x%x", v);
+    return NVFP4_OK;
+}
+
+int nvfp4_debug_wait_timeout(int64_t budget_cycles, int32_t* device_status, void* stream)
+{
+    host::clear_error();
+    NVFP4_REQUIRE(budget_cycles > 0 && budget_cycles <= 2000000000ll, "budget_cycles outside (0, 2e9]");
+    NVFP4_REQUIRE(device_status != nullptr, "device_status is null");
+    host::DeviceInfo* dev;
+    if (int rc = host::device_info(-1, &dev)) return rc;
+    if (dev->cc_major != 10) return host::fail(NVFP4_E_UNSUPPORTED, "needs an sm_100 GPU");
+    return launch_debug_wait_timeout(budget_cycles, device_status, static_cast<cudaStream_t>(stream));
+}
+
+int nvfp4_debug_split_workspace(const void* a, int64_t lda_elems, int M, int K, int scale_policy, int enable_residual_pass,
+                                int fold_swiglu, void* a0, void* a1, void* sfa, void* stream)
+{
+    host::clear_error();
+    NVFP4_REQUIRE(M >= 0 && K >= 0 && M % 128 == 0 && K % 128 == 0, "M and K must be multiples of 128 (M=%d, K=%d)", M, K);
+    NVFP4_REQUIRE(scale_policy >= NVFP4_POLICY_DERIVED_DIV8 && scale_policy <= NVFP4_POLICY_DIV4_RADIX8,
+                  "unknown scale policy %d", scale_policy);
+    NVFP4_REQUIRE(!fold_swiglu || scale_policy == NVFP4_POLICY_DERIVED_DIV8, "the SwiGLU-folded form is built for derived_div8 only");
+    if (M == 0 || K == 0) return NVFP4_OK;
+    NVFP4_REQUIRE(a && a0 && sfa && (a1 || !enable_residual_pass), "null pointer argument");
+    NVFP4_REQUIRE(lda_elems >= (fold_swiglu ? 2 * static_cast<int64_t>(K) : K) && lda_elems % 8 == 0, "bad row stride %lld",
+                  static_cast<long long>(lda_elems));
+    return launch_debug_split_workspace(a, lda_elems, M, K, scale_policy, enable_residual_pass != 0, fold_swiglu != 0, a0,
+                                        enable_residual_pass ? a1 : a0, sfa, static_cast<cudaStream_t>(stream));
 }
 
 int nvfp4_expert_histogram(const int64_t* ids, int64_t n, int num_experts, int64_t* counts, void* stream)
@@ -362,8 +516,8 @@ int nvfp4_debug_decompose(const void* a, int64_t lda_elems, int M, int K, int sc
 {
     host::clear_error();
     NVFP4_REQUIRE(M >= 0 && K >= 0 && M % 128 == 0 && K % 128 == 0, "M and K must be multiples of 128 (M=%d, K=%d)", M, K);
-    if (scale_policy != NVFP4_POLICY_DERIVED_DIV8 && scale_policy != NVFP4_POLICY_RESIDUAL_AMAX)
-        return host::fail(NVFP4_E_UNSUPPORTED, "scale policy %d is not built; derived_div8 and residual_amax are", scale_policy);
+    NVFP4_REQUIRE(scale_policy >= NVFP4_POLICY_DERIVED_DIV8 && scale_policy <= NVFP4_POLICY_DIV4_RADIX8,
+                  "unknown scale policy %d", scale_policy);
     if (M == 0 || K == 0) return NVFP4_OK;
     NVFP4_REQUIRE(a && q0 && q1 && s0 && s1, "null pointer argument");
     NVFP4_REQUIRE(lda_elems >= K && lda_elems % 8 == 0, "bad row stride %lld", static_cast<long long>(lda_elems));

@@ -18,7 +18,7 @@ PKG = os.path.dirname(HERE)
 OUT_DIR = os.path.join(PKG, "lib")
 OBJ_DIR = os.path.join(HERE, "build")
 LIB = os.path.join(OUT_DIR, "libnvfp4_b200.so")
-SOURCES = ["abi.cu", "gemm_normal.cu", "gemm_cluster.cu", "gemm_split.cu", "gemm_swap.cu", "moe_glue.cu", "quantize_weight.cu", "debug_kernels.cu"]
+SOURCES = ["abi.cu", "gemm_normal.cu", "gemm_cluster.cu", "gemm_split.cu", "gemm_swap.cu", "moe_glue.cu", "quantize_weight.cu", "checkpoint_loader.cu", "debug_kernels.cu"]
 NVCC = os.environ.get("NVCC", "/usr/local/cuda/bin/nvcc")
 FLAGS = ["-std=c++17", "-O3", "-gencode", "arch=compute_100a,code=sm_100a", "-lineinfo",
          "-Xcompiler", "-fPIC", "-Xcompiler", "-fvisibility=hidden", "--expt-relaxed-constexpr",

@@ -49,6 +49,39 @@ __global__ void __launch_bounds__(kThreads) decompose_dump_kernel(const __nv_bfl
     }
 }
 
+// A bounded wait that runs out: one thread waits, with a budget of `budget` clock cycles, on an mbarrier nobody
+// arrives on, while the CTA holds tensor memory like a GEMM CTA does.  On expiry it takes the same way out as
+// the GEMM kernels: abort flag, status bit 0, every thread meets at the closing barrier, tensor memory is freed.
+// Nothing faults and nothing hangs; this exists so that the unwind path can be tested.
+__global__ void __launch_bounds__(64, 1) wait_timeout_kernel(long long budget, int32_t* status)
+{
+    __shared__ uint64_t bar;
+    __shared__ uint32_t tmem_slot, abort_word;
+    volatile uint32_t* abort_flag = &abort_word;
+    const uint32_t warp = threadIdx.x >> 5;
+    if (threadIdx.x == 0) { ptx::mbar_init(&bar, 1); *abort_flag = 0; ptx::fence_mbar_init(); }
+    if (warp == 1) ptx::tmem_alloc<32>(&tmem_slot);
+    ptx::tcgen05_fence_before_sync();
+    __syncthreads();
+    ptx::tcgen05_fence_after_sync();
+    const uint32_t tmem = tmem_slot;
+    if (threadIdx.x == 0) {
+        if (!ptx::mbar_wait_budget(&bar, 0, abort_flag, budget)) {
+            *abort_flag = 1;
+            atomicOr(status, 1);
+        }
+    } else if (warp == 1) {
+        // a second role that would wait for the first: it sees the abort flag and gives up at once
+        while (*abort_flag == 0 && !ptx::mbar_try_wait(&bar, 0)) { __nanosleep(200); }
+    }
+    ptx::tcgen05_fence_before_sync();
+    __syncthreads();
+    if (warp == 1) {
+        ptx::tcgen05_fence_after_sync();
+        ptx::tmem_dealloc<32>(tmem);
+    }
+}
+
 // Resident-operand tensor-pipe study: every CTA issues `iters` rounds of `num_cp`
 // scale-factor copies (tcgen05.cp 32x128b.warpx4) followed by `num_mma` block-scaled FP4
 // MMAs of 128 x mma_n x 64 on operands that never leave shared / tensor memory.  With
@@ -103,18 +136,20 @@ int launch_debug_decompose(const void* a, int64_t lda, int M, int K, int policy,
 {
     if (M == 0 || K == 0) return NVFP4_OK;
     constexpr int kDumpSmem = 32768 + 2 * 8192 + 2 * 1024 + 1024;
-    static bool dump_attr_set[host::kMaxDevices] = {};
-    int dev = 0;
-    NVFP4_CUDA_CHECK(cudaGetDevice(&dev));
-    if (!dump_attr_set[dev]) {
-        NVFP4_CUDA_CHECK(cudaFuncSetAttribute(decompose_dump_kernel<256, 0>, cudaFuncAttributeMaxDynamicSharedMemorySize, kDumpSmem));
-        NVFP4_CUDA_CHECK(cudaFuncSetAttribute(decompose_dump_kernel<256, 1>, cudaFuncAttributeMaxDynamicSharedMemorySize, kDumpSmem));
-        dump_attr_set[dev] = true;
-    }
-    auto kernel = policy == 1 ? decompose_dump_kernel<256, 1> : decompose_dump_kernel<256, 0>;
-    kernel<<<dim3(K / 128, M / 128), 256, kDumpSmem, stream>>>(
-        static_cast<const __nv_bfloat16*>(a), lda, K, static_cast<uint8_t*>(q0), static_cast<uint8_t*>(q1),
-        static_cast<uint8_t*>(s0), static_cast<uint8_t*>(s1));
+    return host::with_policy(policy, [&](auto pol) {
+        auto kernel = decompose_dump_kernel<256, decltype(pol)::value>;
+        NVFP4_CUDA_CHECK(cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, kDumpSmem));
+        kernel<<<dim3(K / 128, M / 128), 256, kDumpSmem, stream>>>(
+            static_cast<const __nv_bfloat16*>(a), lda, K, static_cast<uint8_t*>(q0), static_cast<uint8_t*>(q1),
+            static_cast<uint8_t*>(s0), static_cast<uint8_t*>(s1));
+        NVFP4_CUDA_CHECK(cudaGetLastError());
+        return static_cast<int>(NVFP4_OK);
+    });
+}
+
+int launch_debug_wait_timeout(int64_t budget_cycles, int32_t* status, cudaStream_t stream)
+{
+    wait_timeout_kernel<<<1, 64, 0, stream>>>(static_cast<long long>(budget_cycles), status);
     NVFP4_CUDA_CHECK(cudaGetLastError());
     return NVFP4_OK;
 }

@@ -155,6 +155,9 @@ gemm_normal_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_consta
     __syncthreads();
     ptx::tcgen05_fence_after_sync();
     const uint32_t tmem_base = *tmem_slot;
+    // launched with programmatic stream serialisation, the prologue above overlapped the tail of the previous
+    // kernel of the stream; its results are visible from here on
+    ptx::grid_dependency_wait();
 
     const long long probe_start = ptx::probe_clock();
     const uint32_t num_m = p.m / BM, num_n = p.n / BN, num_kb = p.k / BK;
@@ -185,6 +188,7 @@ gemm_normal_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_consta
                     rb.advance<kDepthB>();
                 }
             }
+            ptx::grid_launch_dependents();          // the last loads are on their way: the next kernel may start its prologue
         }
     } else if (warp == kWarpTmaA) {
         // ================= activation producer of the staged variant (its own lane) =====
@@ -405,7 +409,7 @@ gemm_normal_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_consta
 
 template <uint32_t BN, uint32_t kXformWarps, bool kResidual, bool kDirectA, int kPolicy = 0>
 int launch_variant(const void* a, int64_t lda, const void* b, const void* sfb, int M, int N, int K, int E,
-                   const Params& p, int num_sms, cudaStream_t stream)
+                   const Params& p, bool pdl, int num_sms, cudaStream_t stream)
 {
     using C = Cfg<BN, kDirectA>;
     CUtensorMap tm_a, tm_b, tm_sfb;
@@ -429,27 +433,29 @@ int launch_variant(const void* a, int64_t lda, const void* b, const void* sfb, i
     }
     const int num_tiles = (M / static_cast<int>(BM)) * (N / static_cast<int>(BN));
     const int grid = num_tiles < num_sms ? num_tiles : num_sms;
-    kernel<<<grid, (kWarpXform0 + kXformWarps) * 32, C::kSmemAlloc, stream>>>(tm_a, tm_b, tm_sfb, p);
-    NVFP4_CUDA_CHECK(cudaGetLastError());
-    return NVFP4_OK;
+    return host::launch_kernel(kernel, dim3(grid), dim3((kWarpXform0 + kXformWarps) * 32), C::kSmemAlloc, stream, pdl, tm_a, tm_b,
+                               tm_sfb, p);
 }
 
 template <uint32_t BN>
 int launch_for_bn(const void* a, int64_t lda, const void* b, const void* sfb, int M, int N, int K, int E,
-                  const Params& p, bool residual, int xform_warps, bool direct_a, int policy, int num_sms, cudaStream_t stream)
+                  const Params& p, bool residual, int xform_warps, bool direct_a, int policy, bool pdl, int num_sms, cudaStream_t stream)
 {
-    if (policy == 1)      // residual_amax: the TMA-staged kernel with eight transform warps only
-        return residual ? launch_variant<BN, 8, true, false, 1>(a, lda, b, sfb, M, N, K, E, p, num_sms, stream)
-                        : launch_variant<BN, 8, false, false, 1>(a, lda, b, sfb, M, N, K, E, p, num_sms, stream);
+    if (policy != 0)      // the other scale policies: the TMA-staged kernel with eight transform warps only
+        return host::with_policy(policy, [&](auto pol) {
+            constexpr int kP = decltype(pol)::value;
+            return residual ? launch_variant<BN, 8, true, false, kP>(a, lda, b, sfb, M, N, K, E, p, pdl, num_sms, stream)
+                            : launch_variant<BN, 8, false, false, kP>(a, lda, b, sfb, M, N, K, E, p, pdl, num_sms, stream);
+        });
     if (!direct_a) {
         if (xform_warps == 16)
-            return residual ? launch_variant<BN, 16, true, false>(a, lda, b, sfb, M, N, K, E, p, num_sms, stream)
-                            : launch_variant<BN, 16, false, false>(a, lda, b, sfb, M, N, K, E, p, num_sms, stream);
-        return residual ? launch_variant<BN, 8, true, false>(a, lda, b, sfb, M, N, K, E, p, num_sms, stream)
-                        : launch_variant<BN, 8, false, false>(a, lda, b, sfb, M, N, K, E, p, num_sms, stream);
+            return residual ? launch_variant<BN, 16, true, false>(a, lda, b, sfb, M, N, K, E, p, pdl, num_sms, stream)
+                            : launch_variant<BN, 16, false, false>(a, lda, b, sfb, M, N, K, E, p, pdl, num_sms, stream);
+        return residual ? launch_variant<BN, 8, true, false>(a, lda, b, sfb, M, N, K, E, p, pdl, num_sms, stream)
+                        : launch_variant<BN, 8, false, false>(a, lda, b, sfb, M, N, K, E, p, pdl, num_sms, stream);
     }
-    return residual ? launch_variant<BN, 8, true, true>(a, lda, b, sfb, M, N, K, E, p, num_sms, stream)
-                    : launch_variant<BN, 8, false, true>(a, lda, b, sfb, M, N, K, E, p, num_sms, stream);
+    return residual ? launch_variant<BN, 8, true, true>(a, lda, b, sfb, M, N, K, E, p, pdl, num_sms, stream)
+                    : launch_variant<BN, 8, false, true>(a, lda, b, sfb, M, N, K, E, p, pdl, num_sms, stream);
 }
 
 }  // namespace
@@ -457,7 +463,7 @@ int launch_for_bn(const void* a, int64_t lda, const void* b, const void* sfb, in
 // Validated arguments in, launch out.  See nvfp4_grouped_gemm_contiguous for meanings.
 int launch_gemm_normal(const void* a, int64_t lda, const void* b, const void* sfb, const float* gw, void* d,
                        int64_t ldd, const int32_t* m_indices, int M, int N, int K, int E, bool residual,
-                       int xform_warps, int group_m, bool direct_a, int policy, int num_sms, int32_t* status,
+                       int xform_warps, int group_m, bool direct_a, int policy, bool pdl, int num_sms, int32_t* status,
                        cudaStream_t stream)
 {
     Params p;
@@ -470,8 +476,8 @@ int launch_gemm_normal(const void* a, int64_t lda, const void* b, const void* sf
     p.m = M; p.n = N; p.k = K; p.num_experts = E;
     p.group_m = group_m > 0 ? group_m : 8;
     p.status = status;
-    if (N % 256 == 0) return launch_for_bn<256>(a, lda, b, sfb, M, N, K, E, p, residual, xform_warps, direct_a, policy, num_sms, stream);
-    return launch_for_bn<128>(a, lda, b, sfb, M, N, K, E, p, residual, xform_warps, direct_a, policy, num_sms, stream);
+    if (N % 256 == 0) return launch_for_bn<256>(a, lda, b, sfb, M, N, K, E, p, residual, xform_warps, direct_a, policy, pdl, num_sms, stream);
+    return launch_for_bn<128>(a, lda, b, sfb, M, N, K, E, p, residual, xform_warps, direct_a, policy, pdl, num_sms, stream);
 }
 
 #ifdef NVFP4_PROBE

@@ -15,12 +15,15 @@
 // (xform::decompose_block16), so the result is the same bit for bit up to FP32 summation order.
 #include <cuda_bf16.h>
 
+#include "gemm_common.cuh"
 #include "host_common.hpp"
 #include "launchers.hpp"
 #include "transform.cuh"
 
 namespace nvfp4 {
 namespace {
+
+using gemm::Ring;
 
 constexpr uint32_t BM = 128, BN = 256;
 // Eight scale warps (two per tensor-memory quadrant: weight scales, activation scales) and sixteen epilogue warps
@@ -42,18 +45,28 @@ constexpr uint32_t kSmemBudget = 232448 - 1024;
 // With kSwiglu the activation is not read but made: `a` is the (M, 2 K) output of a fused gate+up projection and
 // element (row, j) is bf16(silu(a[row, j]) * a[row, K + j]) -- the same arithmetic and the same BF16 rounding as
 // the stand-alone SwiGLU kernel (moe_glue.cu), so the codes are those of the unfused sequence, bit for bit.
+// Masked layout (masked_m != nullptr): the rows are `m / max_m` groups of max_m rows of which only the first
+// masked_m[g], rounded up to the 128-row tile, are quantised; the others are never read by the GEMM.
 template <bool kResidual, int kPolicy, bool kSwiglu = false>
 __global__ void __launch_bounds__(256)
 quantize_activation_kernel(const __nv_bfloat16* __restrict__ a, int64_t lda, uint32_t m, uint32_t k,
-                           uint8_t* __restrict__ a0, uint8_t* __restrict__ a1, uint8_t* __restrict__ sfa)
+                           uint8_t* __restrict__ a0, uint8_t* __restrict__ a1, uint8_t* __restrict__ sfa,
+                           const int32_t* __restrict__ masked_m, uint32_t max_m)
 {
     constexpr uint32_t kPass = kResidual ? 2 : 1;
     const uint32_t k16 = k / 16;
     const uint64_t idx = static_cast<uint64_t>(blockIdx.x) * blockDim.x + threadIdx.x;
     const uint64_t total = static_cast<uint64_t>(m) * k16;
+    // the activations (and the row counts) may be the previous kernel's output
+    ptx::grid_dependency_wait();
     // the grid is padded to whole warps of valid work: m * k16 is a multiple of 128 * 4
     if (idx >= total) { ptx::grid_launch_dependents(); return; }
     const uint32_t row = static_cast<uint32_t>(idx / k16), blk16 = static_cast<uint32_t>(idx % k16);
+    if (masked_m != nullptr) {      // whole warps leave together: a 128-row tile is 128 * k16 blocks, a multiple of 32, so
+                                    // the 32 blocks of a warp never straddle a tile boundary
+        const uint32_t rows = min(static_cast<uint32_t>(max(0, __ldg(masked_m + row / max_m))), max_m);
+        if (row % max_m >= (rows + BM - 1) / BM * BM) { ptx::grid_launch_dependents(); return; }
+    }
     const uint4* src = reinterpret_cast<const uint4*>(a + static_cast<int64_t>(row) * lda + blk16 * 16);
     uint32_t w[8];
     {
@@ -134,10 +147,9 @@ struct Cfg {
     static constexpr uint32_t kOffB = kOffA + kDepth * kPass * kSlotA;
     static constexpr uint32_t kOffSFA = kOffB + kDepth * kSlotB;
     static constexpr uint32_t kOffSFB = kOffSFA + kDepth * kSlotSFA;
-    // epilogue staging: per warp four output rows of 64 BF16 (128 bytes, padded to 144 against bank conflicts)
-    static constexpr uint32_t kStageRow = 144, kStageWarp = 4 * kStageRow;
+    // epilogue staging: per warp four output rows of 64 BF16 (gemm::store_rows_staged)
     static constexpr uint32_t kOffStage = kOffSFB + kDepth * kSlotSFB;
-    static constexpr uint32_t kOffBars = kOffStage + kNumEpiWarps * kStageWarp;
+    static constexpr uint32_t kOffBars = kOffStage + kNumEpiWarps * gemm::kStageWarp;
     static constexpr uint32_t kNumBars = 4 * kDepth + 2;
     static constexpr uint32_t kSmemAlloc = kOffBars + kNumBars * 8 + 16 + 1024;
     static_assert(kSmemAlloc <= 232448, "shared memory budget");
@@ -145,12 +157,13 @@ struct Cfg {
 
 struct Params {
     const float* gw;
-    const int32_t* m_indices;
+    const int32_t* layout;     // contiguous: m_indices (expert of every row); masked: real rows of every group
     const uint8_t* sfa;
     __nv_bfloat16* d;
     int64_t ldd;
-    uint32_t m, n, k;
+    uint32_t m, n, k;          // m: all rows of a / d (masked: groups * max_m)
     uint32_t group_m;
+    uint32_t groups, max_m;    // masked layout only
     int32_t* status;
 };
 
@@ -162,29 +175,7 @@ __device__ long long g_trace[10][64];
 #define NVFP4_TRACE(point, stage) do { } while (0)
 #endif
 
-struct Ring {
-    uint32_t slot = 0, phase = 0;
-    template <uint32_t kDepth>
-    __device__ __forceinline__ void advance()
-    {
-        if (++slot == kDepth) { slot = 0; phase ^= 1; }
-    }
-};
-
-// Tiles are walked in groups of `group_m` row blocks: inside a group the row block changes fastest, so the
-// CTAs running at the same time share a few weight tiles and a few activation tiles in L2.
-__device__ __forceinline__ void tile_coords(uint32_t tile, uint32_t num_m, uint32_t num_n, uint32_t group_m,
-                                            uint32_t& m_blk, uint32_t& n_blk)
-{
-    const uint32_t per_group = group_m * num_n;
-    const uint32_t g = tile / per_group, r = tile % per_group;
-    const uint32_t first = g * group_m;
-    const uint32_t rows = min(group_m, num_m - first);
-    m_blk = first + r % rows;
-    n_blk = r / rows;
-}
-
-template <uint32_t BK, bool kResidual, uint32_t kGroup>
+template <uint32_t BK, bool kResidual, uint32_t kGroup, bool kMasked>
 __global__ void __launch_bounds__(kThreads, 1)
 gemm_split_kernel(const __grid_constant__ CUtensorMap tm_a0, const __grid_constant__ CUtensorMap tm_a1,
                   const __grid_constant__ CUtensorMap tm_b, const __grid_constant__ CUtensorMap tm_sfb, const Params p)
@@ -231,8 +222,11 @@ gemm_split_kernel(const __grid_constant__ CUtensorMap tm_a0, const __grid_consta
     // everything above overlapped the quantisation kernel; its stores are visible from here on
     ptx::grid_dependency_wait();
 
-    const uint32_t num_m = p.m / BM, num_n = p.n / BN, num_kb = p.k / BK;
-    const uint32_t num_tiles = num_m * num_n;
+    const uint32_t num_kb = p.k / BK;
+    // every role walks the same sequence of tiles (static stride over the CTAs; masked layout: row blocks from the
+    // device-side row counts)
+    gemm::TileWalker<BM, kMasked> walk(p.layout, p.m, p.n, BN, p.group_m, p.groups, p.max_m);
+    gemm::Tile t;
     bool ok = true;
     ptx::ProbeAcc pa;
     const long long probe_start = ptx::probe_clock();
@@ -246,11 +240,10 @@ gemm_split_kernel(const __grid_constant__ CUtensorMap tm_a0, const __grid_consta
         // ================= producer: every operand of a K block on one barrier =================
         if (lane == 0) {
             Ring r;
-            for (uint32_t tile = blockIdx.x; tile < num_tiles && ok; tile += gridDim.x) {
-                uint32_t m_blk, n_blk;
-                tile_coords(tile, num_m, num_n, p.group_m, m_blk, n_blk);
-                const int32_t e = max(0, __ldg(p.m_indices + m_blk * BM));
-                const uint8_t* sfa_row = p.sfa + static_cast<uint64_t>(m_blk) * (p.k / 64) * (C::kPass * 512);
+            for (uint32_t tile = blockIdx.x; ok && walk.next(tile, t); tile += gridDim.x) {
+                const uint32_t n_blk = t.n_blk;
+                const int32_t e = t.expert;
+                const uint8_t* sfa_row = p.sfa + static_cast<uint64_t>(t.row0 / BM) * (p.k / 64) * (C::kPass * 512);
                 for (uint32_t kb = 0; kb < num_kb; ++kb) {
                     if (r.slot % kGroup == 0 &&
                         !ptx::mbar_wait(empty + r.slot / kGroup, r.phase ^ 1, abort_flag, pa, 0)) { give_up(1); break; }
@@ -262,14 +255,15 @@ gemm_split_kernel(const __grid_constant__ CUtensorMap tm_a0, const __grid_consta
                                    sfa_row + static_cast<uint64_t>(kb) * C::kSlotSFA, C::kSlotSFA, sf_in + r.slot);
                     ptx::mbar_arrive_expect_tx(full + r.slot, C::kPass * C::kSlotA + C::kSlotB);
                     uint8_t* a_dst = smem_gen + C::kOffA + r.slot * C::kPass * C::kSlotA;
-                    ptx::tma_load_2d(a_dst, &tm_a0, full + r.slot, kb * C::kRowBytes, m_blk * BM);
+                    ptx::tma_load_2d(a_dst, &tm_a0, full + r.slot, kb * C::kRowBytes, t.row0);
                     if constexpr (kResidual)
-                        ptx::tma_load_2d(a_dst + C::kSlotA, &tm_a1, full + r.slot, kb * C::kRowBytes, m_blk * BM);
+                        ptx::tma_load_2d(a_dst + C::kSlotA, &tm_a1, full + r.slot, kb * C::kRowBytes, t.row0);
                     ptx::tma_load_2d(smem_gen + C::kOffB + r.slot * C::kSlotB, &tm_b, full + r.slot, kb * C::kRowBytes,
                                      e * p.n + n_blk * BN);
                     r.advance<C::kDepth>();
                 }
             }
+            ptx::grid_launch_dependents();          // the last loads are on their way: the next kernel may start its prologue
         }
     } else if (warp == kWarpMma) {
         // ================= MMA issue: one wait, 2 x kAtoms (x passes) MMAs, one commit per K block =================
@@ -277,7 +271,7 @@ gemm_split_kernel(const __grid_constant__ CUtensorMap tm_a0, const __grid_consta
         uint32_t acc_phase = 0;
         int32_t pending = -1;                       // group whose commit is still to be issued
         constexpr uint32_t idesc = ptx::make_idesc_nvf4(BM, BN);
-        for (uint32_t tile = blockIdx.x; tile < num_tiles && ok; tile += gridDim.x) {
+        for (uint32_t tile = blockIdx.x; ok && walk.next(tile, t); tile += gridDim.x) {
             if (!ptx::mbar_wait(tmem_empty, acc_phase ^ 1, abort_flag, pa, 0)) { give_up(1); break; }
             ptx::tcgen05_fence_after_sync();
             for (uint32_t kb = 0; kb < num_kb; ++kb) {
@@ -331,7 +325,7 @@ gemm_split_kernel(const __grid_constant__ CUtensorMap tm_a0, const __grid_consta
         // go up in one store.
         const uint32_t quad = warp & 3, group = (warp - kWarpSf0) >> 2;     // group 0: weight scales, 1: activation scales
         Ring r;
-        for (uint32_t tile = blockIdx.x; tile < num_tiles && ok; tile += gridDim.x) {
+        for (uint32_t tile = blockIdx.x; ok && walk.next(tile, t); tile += gridDim.x) {
             for (uint32_t kb = 0; kb < num_kb; ++kb) {
                 // the scales of this phase were requested after the producer had seen the ring position free, so the
                 // MMAs that used its scale columns have retired
@@ -373,12 +367,9 @@ gemm_split_kernel(const __grid_constant__ CUtensorMap tm_a0, const __grid_consta
         // the MMA warp; scaling, packing and the stores then run under the next tile's main loop.
         const uint32_t quad = warp & 3, group = (warp - kWarpEpi0) >> 2;
         uint32_t acc_phase = 0;
-        for (uint32_t tile = blockIdx.x; tile < num_tiles && ok; tile += gridDim.x) {
-            uint32_t m_blk, n_blk;
-            tile_coords(tile, num_m, num_n, p.group_m, m_blk, n_blk);
-            const int32_t e = max(0, __ldg(p.m_indices + m_blk * BM));
-            const float g = __ldg(p.gw + e);
-            if (!ptx::mbar_wait_relaxed(tmem_full, acc_phase, abort_flag, 400)) { give_up(1); break; }
+        for (uint32_t tile = blockIdx.x; ok && walk.next(tile, t); tile += gridDim.x) {
+            const float g = __ldg(p.gw + t.expert);
+            if (!ptx::mbar_wait_relaxed(tmem_full, acc_phase, abort_flag, 100)) { give_up(1); break; }
             if (warp == kWarpEpi0) NVFP4_TRACE(5, (tile - blockIdx.x) / gridDim.x);
             ptx::tcgen05_fence_after_sync();
             const uint32_t taddr = tmem_base + ((quad * 32) << 16) + C::kColAcc + group * 64;
@@ -392,39 +383,13 @@ gemm_split_kernel(const __grid_constant__ CUtensorMap tm_a0, const __grid_consta
                 __syncwarp();
                 if (lane == 0) ptx::mbar_arrive(tmem_empty);
                 if (warp == kWarpEpi0) NVFP4_TRACE(6, (tile - blockIdx.x) / gridDim.x);
-#pragma unroll
-                for (int i = 0; i < 16; ++i) {
-                    const __nv_bfloat162 h0 = __floats2bfloat162_rn(__uint_as_float(va[2 * i]) * g, __uint_as_float(va[2 * i + 1]) * g);
-                    const __nv_bfloat162 h1 = __floats2bfloat162_rn(__uint_as_float(vb[2 * i]) * g, __uint_as_float(vb[2 * i + 1]) * g);
-                    o[i] = *reinterpret_cast<const uint32_t*>(&h0);
-                    o[16 + i] = *reinterpret_cast<const uint32_t*>(&h1);
-                }
+                gemm::scale_pack_bf16(va, g, o);
+                gemm::scale_pack_bf16(vb, g, o + 16);
             }
-            // Lane = row in tensor memory, but a store instruction should write whole 128-byte lines: with one row
-            // per lane every 16-byte store of the warp lands in a different line -- 4096 partial-line requests per
-            // tile, which were measured to hold up the operand loads and the tensor pipe of the next tile for
-            // thousands of cycles.  So four rows at a time go through a 576-byte staging area: four lanes write
-            // their 128 bytes, then the whole warp reads 16 bytes per lane and stores four full lines.
-            const uint32_t stage = smem + C::kOffStage + (warp - kWarpEpi0) * C::kStageWarp;
-            const uint32_t rd = stage + (lane >> 3) * C::kStageRow + (lane & 7u) * 16;
-            __nv_bfloat16* dbase = p.d + static_cast<int64_t>(m_blk * BM + quad * 32 + (lane >> 3)) * p.ldd + n_blk * BN +
-                                   group * 64 + (lane & 7u) * 8;
-#pragma unroll 1
-            for (uint32_t pass = 0; pass < 8; ++pass) {
-                if ((lane >> 2) == pass) {
-                    const uint32_t wr = stage + (lane & 3u) * C::kStageRow;
-#pragma unroll
-                    for (uint32_t c = 0; c < 8; ++c) ptx::sts128(wr + c * 16, o[4 * c], o[4 * c + 1], o[4 * c + 2], o[4 * c + 3]);
-                }
-                __syncwarp();
-                const uint4 q = ptx::lds128(rd);
-#ifndef NVFP4_ABLATE_NO_STORE      // timing experiments only (wrong results); never defined in the shipped build
-                *reinterpret_cast<uint4*>(dbase + static_cast<int64_t>(pass * 4) * p.ldd) = q;
-#else
-                if (q.x == 0x12345678u && p.m == 1) *reinterpret_cast<uint4*>(dbase) = q;
-#endif
-                __syncwarp();
-            }
+            const uint32_t stage = smem + C::kOffStage + (warp - kWarpEpi0) * gemm::kStageWarp;
+            __nv_bfloat16* d_lane = p.d + static_cast<int64_t>(t.row0 + quad * 32 + (lane >> 3)) * p.ldd + t.n_blk * BN +
+                                    group * 64 + (lane & 7u) * 8;
+            gemm::store_rows_staged(o, stage, d_lane, p.ldd, lane);
             if (warp == kWarpEpi0) NVFP4_TRACE(8, (tile - blockIdx.x) / gridDim.x);
             acc_phase ^= 1;
         }
@@ -442,49 +407,55 @@ gemm_split_kernel(const __grid_constant__ CUtensorMap tm_a0, const __grid_consta
     }
 }
 
-// Stream-ordered workspace: a private memory pool per device that keeps what it has been given, so that after
-// the first call an allocation is a pool look-up ordered on the caller's stream (no device synchronisation,
-// safe with concurrent streams, legal during stream capture).
-int workspace_pool(int dev, cudaMemPool_t* out)
+// What a call of the split path is made of, after validation.
+struct Call {
+    const void* a; int64_t lda;             // activations (SwiGLU-folded form: the (M, 2 K) gate+up output)
+    const void* b; const void* sfb;
+    int M, N, K, E;
+    bool pdl, swiglu;
+    int policy;
+    const int32_t* masked_m; int max_m;     // masked layout: device-side row counts, rows reserved per group
+    int num_sms;
+    cudaStream_t stream;
+};
+
+// Kernel 1 into the given workspace pieces.
+template <bool kResidual>
+int launch_quantize(const Call& c, uint8_t* a0, uint8_t* a1, uint8_t* sfa)
 {
-    static cudaMemPool_t pools[host::kMaxDevices] = {};
-    if (pools[dev] == nullptr) {
-        cudaMemPoolProps props = {};
-        props.allocType = cudaMemAllocationTypePinned;
-        props.handleTypes = cudaMemHandleTypeNone;
-        props.location.type = cudaMemLocationTypeDevice;
-        props.location.id = dev;
-        cudaMemPool_t pool = nullptr;
-        NVFP4_CUDA_CHECK(cudaMemPoolCreate(&pool, &props));
-        uint64_t keep = UINT64_MAX;
-        NVFP4_CUDA_CHECK(cudaMemPoolSetAttribute(pool, cudaMemPoolAttrReleaseThreshold, &keep));
-        pools[dev] = pool;
-    }
-    *out = pools[dev];
-    return NVFP4_OK;
+    auto quantize = quantize_activation_kernel<kResidual, 0, true>;
+    if (!c.swiglu)
+        host::with_policy(c.policy, [&](auto pol) {
+            quantize = quantize_activation_kernel<kResidual, decltype(pol)::value, false>;
+            return 0;
+        });
+    const uint64_t blocks16 = static_cast<uint64_t>(c.M) * (c.K / 16);
+    return host::launch_kernel(quantize, dim3(static_cast<unsigned>((blocks16 + 255) / 256)), dim3(256), 0, c.stream, c.pdl,
+                               static_cast<const __nv_bfloat16*>(c.a), c.lda, static_cast<uint32_t>(c.M),
+                               static_cast<uint32_t>(c.K), a0, a1, sfa, c.masked_m, static_cast<uint32_t>(c.max_m > 0 ? c.max_m : 1));
 }
 
-template <uint32_t BK, bool kResidual, uint32_t kGroup>
-int launch_variant(const void* a, int64_t lda, const void* b, const void* sfb, int M, int N, int K, int E, Params p,
-                   bool pdl, int policy, bool swiglu, int num_sms, cudaStream_t stream)
+template <uint32_t BK, bool kResidual, uint32_t kGroup, bool kMasked>
+int launch_variant(const Call& c, Params p)
 {
     using C = Cfg<BK, kResidual, kGroup>;
+    const int M = c.M, N = c.N, K = c.K;
     int dev = 0;
     NVFP4_CUDA_CHECK(cudaGetDevice(&dev));
     cudaMemPool_t pool;
-    if (int rc = workspace_pool(dev, &pool)) return rc;
+    if (int rc = host::workspace_pool(dev, &pool)) return rc;
     const size_t code_bytes = static_cast<size_t>(M) * (K / 2);
     const size_t sf_bytes = static_cast<size_t>(M) * (K / 16) * C::kPass;
     const size_t total = C::kPass * code_bytes + sf_bytes;
     uint8_t* ws = nullptr;
-    NVFP4_CUDA_CHECK(cudaMallocFromPoolAsync(reinterpret_cast<void**>(&ws), total, pool, stream));
+    NVFP4_CUDA_CHECK(cudaMallocFromPoolAsync(reinterpret_cast<void**>(&ws), total, pool, c.stream));
     uint8_t* a0 = ws;
     uint8_t* a1 = kResidual ? ws + code_bytes : ws;
     uint8_t* sfa = ws + C::kPass * code_bytes;
     p.sfa = sfa;
 
     auto release = [&](int rc) {
-        cudaFreeAsync(ws, stream);
+        cudaFreeAsync(ws, c.stream);
         return rc;
     };
     CUtensorMap tm_a0, tm_a1, tm_b, tm_sfb;
@@ -493,22 +464,16 @@ int launch_variant(const void* a, int64_t lda, const void* b, const void* sfb, i
     if (rc) return release(rc);
     rc = host::encode_tensor_map_2d(&tm_a1, CU_TENSOR_MAP_DATA_TYPE_UINT8, 1, a1, K / 2, M, K / 2, C::kRowBytes, BM, sw);
     if (rc) return release(rc);
-    rc = host::encode_tensor_map_2d(&tm_b, CU_TENSOR_MAP_DATA_TYPE_UINT8, 1, b, K / 2, static_cast<uint64_t>(E) * N, K / 2,
+    rc = host::encode_tensor_map_2d(&tm_b, CU_TENSOR_MAP_DATA_TYPE_UINT8, 1, c.b, K / 2, static_cast<uint64_t>(c.E) * N, K / 2,
                                     C::kRowBytes, BN, sw);
     if (rc) return release(rc);
-    rc = host::encode_tensor_map_2d(&tm_sfb, CU_TENSOR_MAP_DATA_TYPE_INT32, 4, sfb, N, static_cast<uint64_t>(E) * (K / 64),
+    rc = host::encode_tensor_map_2d(&tm_sfb, CU_TENSOR_MAP_DATA_TYPE_INT32, 4, c.sfb, N, static_cast<uint64_t>(c.E) * (K / 64),
                                     static_cast<uint64_t>(N) * 4, BN, C::kAtoms, CU_TENSOR_MAP_SWIZZLE_NONE);
     if (rc) return release(rc);
 
-    const uint64_t blocks16 = static_cast<uint64_t>(M) * (K / 16);
-    auto quantize = swiglu ? quantize_activation_kernel<kResidual, 0, true>
-                           : (policy == 1 ? quantize_activation_kernel<kResidual, 1> : quantize_activation_kernel<kResidual, 0>);
-    quantize<<<static_cast<unsigned>((blocks16 + 255) / 256), 256, 0, stream>>>(
-        static_cast<const __nv_bfloat16*>(a), lda, static_cast<uint32_t>(M), static_cast<uint32_t>(K), a0, a1, sfa);
-    if (cudaError_t err = cudaGetLastError(); err != cudaSuccess)
-        return release(host::fail(NVFP4_E_CUDA, "activation quantisation launch failed: %s", cudaGetErrorString(err)));
+    if (int qrc = launch_quantize<kResidual>(c, a0, a1, sfa)) return release(qrc);
 
-    auto kernel = gemm_split_kernel<BK, kResidual, kGroup>;
+    auto kernel = gemm_split_kernel<BK, kResidual, kGroup, kMasked>;
     static bool attr_set[host::kMaxDevices] = {};
     if (!attr_set[dev]) {
         if (cudaError_t err = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, C::kSmemAlloc);
@@ -516,49 +481,56 @@ int launch_variant(const void* a, int64_t lda, const void* b, const void* sfb, i
             return release(host::fail(NVFP4_E_CUDA, "cudaFuncSetAttribute failed: %s", cudaGetErrorString(err)));
         attr_set[dev] = true;
     }
+    // masked layout: the number of tiles is only known on the device; surplus CTAs find no tile and leave
     const int num_tiles = (M / static_cast<int>(BM)) * (N / static_cast<int>(BN));
-    cudaLaunchConfig_t cfg = {};
-    cudaLaunchAttribute attr[1];
-    attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
-    attr[0].val.programmaticStreamSerializationAllowed = 1;
-    cfg.gridDim = dim3(static_cast<unsigned>(num_tiles < num_sms ? num_tiles : num_sms));
-    cfg.blockDim = dim3(kThreads);
-    cfg.dynamicSmemBytes = C::kSmemAlloc;
-    cfg.stream = stream;
-    cfg.attrs = attr;
-    cfg.numAttrs = pdl ? 1 : 0;
-    if (cudaError_t err = cudaLaunchKernelEx(&cfg, kernel, tm_a0, tm_a1, tm_b, tm_sfb, p); err != cudaSuccess)
-        return release(host::fail(NVFP4_E_CUDA, "GEMM launch failed: %s", cudaGetErrorString(err)));
-    return release(NVFP4_OK);
+    const int grid = num_tiles < c.num_sms ? num_tiles : c.num_sms;
+    return release(host::launch_kernel(kernel, dim3(static_cast<unsigned>(grid)), dim3(kThreads), C::kSmemAlloc, c.stream, c.pdl,
+                                       tm_a0, tm_a1, tm_b, tm_sfb, p));
+}
+
+template <bool kMasked>
+int launch_for_layout(const Call& c, const Params& p, bool residual, int block_k)
+{
+    // block_k: 0 = the library's choice, 256 = one 256-wide K block per ring position, 128 = 128-wide with a commit
+    // per position, 130 = 128-wide in groups of two (requested and freed together, consumed one by one)
+    if (!kMasked && block_k == 130)
+        return residual ? launch_variant<128, true, 2, false>(c, p) : launch_variant<128, false, 2, false>(c, p);
+    if (c.K % 256 == 0 && block_k != 128)
+        return residual ? launch_variant<256, true, 1, kMasked>(c, p) : launch_variant<256, false, 1, kMasked>(c, p);
+    return residual ? launch_variant<128, true, 1, kMasked>(c, p) : launch_variant<128, false, 1, kMasked>(c, p);
 }
 
 }  // namespace
 
 // Two launches: activations -> NVFP4 workspace, then the block-scaled GEMM over it.  N % 256 == 0.
+// masked_m == nullptr: contiguous layout (layout = m_indices, M rows).  Otherwise the masked layout: E groups of
+// max_m rows (M = E * max_m), masked_m[g] of them real.
 int launch_gemm_split(const void* a, int64_t lda, const void* b, const void* sfb, const float* gw, void* d,
-                      int64_t ldd, const int32_t* m_indices, int M, int N, int K, int E, bool residual,
-                      int block_k, int group_m, bool pdl, int policy, bool swiglu, int num_sms, int32_t* status,
+                      int64_t ldd, const int32_t* m_indices, const int32_t* masked_m, int max_m, int M, int N, int K, int E,
+                      bool residual, int block_k, int group_m, bool pdl, int policy, bool swiglu, int num_sms, int32_t* status,
                       cudaStream_t stream)
 {
     Params p;
     p.gw = gw;
-    p.m_indices = m_indices;
+    p.layout = masked_m != nullptr ? masked_m : m_indices;
     p.sfa = nullptr;
     p.d = static_cast<__nv_bfloat16*>(d);
     p.ldd = ldd;
     p.m = M; p.n = N; p.k = K;
     p.group_m = group_m > 0 ? group_m : 8;
+    p.groups = E; p.max_m = max_m > 0 ? max_m : 1;
     p.status = status;
-    // block_k: 0 = the library's choice, 256 = one 256-wide K block per ring position, 128 = 128-wide with a commit
-    // per position, 130 = 128-wide in groups of two (requested and freed together, consumed one by one)
-    if (block_k == 130)
-        return residual ? launch_variant<128, true, 2>(a, lda, b, sfb, M, N, K, E, p, pdl, policy, swiglu, num_sms, stream)
-                        : launch_variant<128, false, 2>(a, lda, b, sfb, M, N, K, E, p, pdl, policy, swiglu, num_sms, stream);
-    if (K % 256 == 0 && block_k != 128)
-        return residual ? launch_variant<256, true, 1>(a, lda, b, sfb, M, N, K, E, p, pdl, policy, swiglu, num_sms, stream)
-                        : launch_variant<256, false, 1>(a, lda, b, sfb, M, N, K, E, p, pdl, policy, swiglu, num_sms, stream);
-    return residual ? launch_variant<128, true, 1>(a, lda, b, sfb, M, N, K, E, p, pdl, policy, swiglu, num_sms, stream)
-                    : launch_variant<128, false, 1>(a, lda, b, sfb, M, N, K, E, p, pdl, policy, swiglu, num_sms, stream);
+    const Call c{a, lda, b, sfb, M, N, K, E, pdl, swiglu, policy, masked_m, max_m, num_sms, stream};
+    return masked_m != nullptr ? launch_for_layout<true>(c, p, residual, block_k) : launch_for_layout<false>(c, p, residual, block_k);
+}
+
+// Test hook: kernel 1 alone, into buffers of the caller (a0, a1: (M, K/2) bytes; sfa: (M/128, K/64, passes, 512) bytes).
+int launch_debug_split_workspace(const void* a, int64_t lda, int M, int K, int policy, bool residual, bool swiglu, void* a0,
+                                 void* a1, void* sfa, cudaStream_t stream)
+{
+    const Call c{a, lda, nullptr, nullptr, M, 0, K, 0, false, swiglu, policy, nullptr, 0, 0, stream};
+    return residual ? launch_quantize<true>(c, static_cast<uint8_t*>(a0), static_cast<uint8_t*>(a1), static_cast<uint8_t*>(sfa))
+                    : launch_quantize<false>(c, static_cast<uint8_t*>(a0), static_cast<uint8_t*>(a1), static_cast<uint8_t*>(sfa));
 }
 
 #ifdef NVFP4_PROBE

@@ -143,6 +143,9 @@ gemm_swap_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constant
     __syncthreads();
     ptx::tcgen05_fence_after_sync();
     const uint32_t tmem_base = *tmem_slot;
+    // launched with programmatic stream serialisation, the prologue above overlapped the tail of the previous
+    // kernel of the stream; its results are visible from here on
+    ptx::grid_dependency_wait();
 
     // tiles: all weight-row blocks of one token block are neighbours, so the CTAs of a
     // wave share that token block's activations through L2 while streaming disjoint weights
@@ -177,6 +180,7 @@ gemm_swap_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constant
                     rw.advance<C::kDepthW>();
                 }
             }
+            ptx::grid_launch_dependents();          // the last loads are on their way: the next kernel may start its prologue
         }
     } else if (warp == kWarpTmaA) {
         // activation producer (a separate thread, so a full A ring never holds the weights back)
@@ -369,7 +373,7 @@ gemm_swap_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constant
 
 template <uint32_t T, uint32_t BK, bool kResidual, int kPolicy = 0>
 int launch_variant(const void* a, int64_t lda, const void* b, const void* sfb, int M, int N, int K, int E,
-                   const Params& p, int num_sms, cudaStream_t stream)
+                   const Params& p, bool pdl, int num_sms, cudaStream_t stream)
 {
     using C = Cfg<T, BK, kResidual>;
     CUtensorMap tm_a, tm_w, tm_sfw;
@@ -393,38 +397,38 @@ int launch_variant(const void* a, int64_t lda, const void* b, const void* sfb, i
     }
     const int num_tiles = (M / static_cast<int>(T)) * (N / static_cast<int>(BW));
     const int grid = num_tiles < num_sms ? num_tiles : num_sms;
-    kernel<<<grid, kThreads, C::kSmemAlloc, stream>>>(tm_a, tm_w, tm_sfw, p);
-    NVFP4_CUDA_CHECK(cudaGetLastError());
-    return NVFP4_OK;
+    return host::launch_kernel(kernel, dim3(grid), dim3(kThreads), C::kSmemAlloc, stream, pdl, tm_a, tm_w, tm_sfw, p);
 }
 
 template <uint32_t T>
 int launch_for_tile(const void* a, int64_t lda, const void* b, const void* sfb, int M, int N, int K, int E,
-                    const Params& p, bool residual, int block_k, int policy, int num_sms, cudaStream_t stream)
+                    const Params& p, bool residual, int block_k, int policy, bool pdl, int num_sms, cudaStream_t stream)
 {
-    if (policy == 1) {    // residual_amax: the default K-block choice only
-        if constexpr (T <= 32) {
-            if (K % 512 == 0)
-                return residual ? launch_variant<T, 512, true, 1>(a, lda, b, sfb, M, N, K, E, p, num_sms, stream)
-                                : launch_variant<T, 512, false, 1>(a, lda, b, sfb, M, N, K, E, p, num_sms, stream);
-        }
-        if (K % 256 == 0)
-            return residual ? launch_variant<T, 256, true, 1>(a, lda, b, sfb, M, N, K, E, p, num_sms, stream)
-                            : launch_variant<T, 256, false, 1>(a, lda, b, sfb, M, N, K, E, p, num_sms, stream);
-        return residual ? launch_variant<T, 128, true, 1>(a, lda, b, sfb, M, N, K, E, p, num_sms, stream)
-                        : launch_variant<T, 128, false, 1>(a, lda, b, sfb, M, N, K, E, p, num_sms, stream);
-    }
+    if (policy != 0)      // the other scale policies: the default K-block choice only
+        return host::with_policy(policy, [&](auto pol) {
+            constexpr int kP = decltype(pol)::value;
+            if constexpr (T <= 32) {
+                if (K % 512 == 0)
+                    return residual ? launch_variant<T, 512, true, kP>(a, lda, b, sfb, M, N, K, E, p, pdl, num_sms, stream)
+                                    : launch_variant<T, 512, false, kP>(a, lda, b, sfb, M, N, K, E, p, pdl, num_sms, stream);
+            }
+            if (K % 256 == 0)
+                return residual ? launch_variant<T, 256, true, kP>(a, lda, b, sfb, M, N, K, E, p, pdl, num_sms, stream)
+                                : launch_variant<T, 256, false, kP>(a, lda, b, sfb, M, N, K, E, p, pdl, num_sms, stream);
+            return residual ? launch_variant<T, 128, true, kP>(a, lda, b, sfb, M, N, K, E, p, pdl, num_sms, stream)
+                            : launch_variant<T, 128, false, kP>(a, lda, b, sfb, M, N, K, E, p, pdl, num_sms, stream);
+        });
     // K blocks of 512 halve the per-block barrier traffic and commits; a 64-token tile has no room for them
     if constexpr (T <= 32) {
         if (K % 512 == 0 && (block_k == 0 || block_k == 512))
-            return residual ? launch_variant<T, 512, true>(a, lda, b, sfb, M, N, K, E, p, num_sms, stream)
-                            : launch_variant<T, 512, false>(a, lda, b, sfb, M, N, K, E, p, num_sms, stream);
+            return residual ? launch_variant<T, 512, true>(a, lda, b, sfb, M, N, K, E, p, pdl, num_sms, stream)
+                            : launch_variant<T, 512, false>(a, lda, b, sfb, M, N, K, E, p, pdl, num_sms, stream);
     }
     if (K % 256 == 0 && block_k != 128)
-        return residual ? launch_variant<T, 256, true>(a, lda, b, sfb, M, N, K, E, p, num_sms, stream)
-                        : launch_variant<T, 256, false>(a, lda, b, sfb, M, N, K, E, p, num_sms, stream);
-    return residual ? launch_variant<T, 128, true>(a, lda, b, sfb, M, N, K, E, p, num_sms, stream)
-                    : launch_variant<T, 128, false>(a, lda, b, sfb, M, N, K, E, p, num_sms, stream);
+        return residual ? launch_variant<T, 256, true>(a, lda, b, sfb, M, N, K, E, p, pdl, num_sms, stream)
+                        : launch_variant<T, 256, false>(a, lda, b, sfb, M, N, K, E, p, pdl, num_sms, stream);
+    return residual ? launch_variant<T, 128, true>(a, lda, b, sfb, M, N, K, E, p, pdl, num_sms, stream)
+                    : launch_variant<T, 128, false>(a, lda, b, sfb, M, N, K, E, p, pdl, num_sms, stream);
 }
 
 }  // namespace
@@ -433,7 +437,7 @@ int launch_for_tile(const void* a, int64_t lda, const void* b, const void* sfb, 
 // multiple of it, which the caller guarantees through m_alignment % token_tile == 0.
 int launch_gemm_swap(const void* a, int64_t lda, const void* b, const void* sfb, const float* gw, void* d,
                      int64_t ldd, const int32_t* m_indices, int M, int N, int K, int E, bool residual,
-                     int token_tile, int block_k, int policy, int num_sms, int32_t* status, cudaStream_t stream)
+                     int token_tile, int block_k, int policy, bool pdl, int num_sms, int32_t* status, cudaStream_t stream)
 {
     Params p;
     p.gw = gw;
@@ -443,9 +447,9 @@ int launch_gemm_swap(const void* a, int64_t lda, const void* b, const void* sfb,
     p.m = M; p.n = N; p.k = K;
     p.status = status;
     switch (token_tile) {
-        case 16: return launch_for_tile<16>(a, lda, b, sfb, M, N, K, E, p, residual, block_k, policy, num_sms, stream);
-        case 32: return launch_for_tile<32>(a, lda, b, sfb, M, N, K, E, p, residual, block_k, policy, num_sms, stream);
-        case 64: return launch_for_tile<64>(a, lda, b, sfb, M, N, K, E, p, residual, block_k, policy, num_sms, stream);
+        case 16: return launch_for_tile<16>(a, lda, b, sfb, M, N, K, E, p, residual, block_k, policy, pdl, num_sms, stream);
+        case 32: return launch_for_tile<32>(a, lda, b, sfb, M, N, K, E, p, residual, block_k, policy, pdl, num_sms, stream);
+        case 64: return launch_for_tile<64>(a, lda, b, sfb, M, N, K, E, p, residual, block_k, policy, pdl, num_sms, stream);
         default: return host::fail(NVFP4_E_INVALID_ARGUMENT, "token tile %d is not 16, 32 or 64", token_tile);
     }
 }

@@ -6,6 +6,7 @@
 #include <cstdarg>
 #include <cstdint>
 #include <cstdio>
+#include <type_traits>
 #include <cuda.h>
 #include <cuda_runtime.h>
 
@@ -32,6 +33,20 @@ void clear_error();
 
 constexpr int kMaxDevices = 64;
 
+// Calls f(std::integral_constant<int, policy>{}) for an activation scale policy code (NVFP4_POLICY_*), so that
+// launchers can pick the kernel instantiation of a policy without a ladder of their own.
+template <typename F>
+int with_policy(int policy, F&& f)
+{
+    switch (policy) {
+        case NVFP4_POLICY_DERIVED_DIV8: return f(std::integral_constant<int, 0>{});
+        case NVFP4_POLICY_RESIDUAL_AMAX: return f(std::integral_constant<int, 1>{});
+        case NVFP4_POLICY_DERIVED_DIV4: return f(std::integral_constant<int, 2>{});
+        case NVFP4_POLICY_DIV4_RADIX8: return f(std::integral_constant<int, 3>{});
+        default: return fail(NVFP4_E_INVALID_ARGUMENT, "unknown scale policy %d", policy);
+    }
+}
+
 struct DeviceInfo {
     bool known = false;
     int hw_sms = 0;       // multiProcessorCount
@@ -40,8 +55,35 @@ struct DeviceInfo {
     int max_smem_optin = 0;
 };
 
+// Launch with, optionally, the programmatic-stream-serialisation attribute (programmatic dependent launch): the
+// kernel may then be scheduled while the previous kernel of the stream is still draining; it must execute
+// griddepcontrol.wait before it touches anything that kernel wrote.
+// Counterpart in the reference: src/jit/launch.hpp:63-96.
+template <typename... Params, typename... Args>
+int launch_kernel(void (*kernel)(Params...), dim3 grid, dim3 block, size_t smem, cudaStream_t stream, bool pdl, Args&&... args)
+{
+    cudaLaunchConfig_t cfg = {};
+    cudaLaunchAttribute attr[1];
+    attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+    attr[0].val.programmaticStreamSerializationAllowed = 1;
+    cfg.gridDim = grid;
+    cfg.blockDim = block;
+    cfg.dynamicSmemBytes = smem;
+    cfg.stream = stream;
+    cfg.attrs = attr;
+    cfg.numAttrs = pdl ? 1 : 0;
+    if (cudaError_t err = cudaLaunchKernelEx(&cfg, kernel, static_cast<Params>(args)...); err != cudaSuccess)
+        return fail(NVFP4_E_CUDA, "kernel launch failed: %s", cudaGetErrorString(err));
+    return NVFP4_OK;
+}
+
 // Properties of `device` (< 0: current), cached per device (not per process).
 int device_info(int device, DeviceInfo** out);
+
+// Stream-ordered workspace: a private memory pool per device that keeps what it has been given, so that after
+// the first call an allocation is a pool look-up ordered on the caller's stream (no device synchronisation,
+// safe with concurrent streams, legal during stream capture).
+int workspace_pool(int dev, cudaMemPool_t* out);
 
 // 2-D tiled tensor map.  dims/box: innermost first, in elements; row_stride_bytes
 // is the stride of dimension 1.  Returns NVFP4_E_CUDA with the driver's code on failure.

@@ -7,18 +7,22 @@ namespace nvfp4 {
 
 int launch_gemm_normal(const void* a, int64_t lda, const void* b, const void* sfb, const float* gw, void* d,
                        int64_t ldd, const int32_t* m_indices, int M, int N, int K, int E, bool residual,
-                       int xform_warps, int group_m, bool direct_a, int policy, int num_sms, int32_t* status,
+                       int xform_warps, int group_m, bool direct_a, int policy, bool pdl, int num_sms, int32_t* status,
                        cudaStream_t stream);
 
 // Cluster variant of the normal orientation (cluster = 2 or 4, N % (256 * cluster) == 0).
 int launch_gemm_cluster(const void* a, int64_t lda, const void* b, const void* sfb, const float* gw, void* d,
                         int64_t ldd, const int32_t* m_indices, int M, int N, int K, int E, bool residual,
-                        int cluster, int xform_warps, int group_m, int num_sms, int32_t* status, cudaStream_t stream);
+                        int cluster, int policy, int group_m, bool pdl, int num_sms, int32_t* status, cudaStream_t stream);
 
+// masked_m == nullptr: contiguous layout.  Otherwise E groups of max_m rows each (M = E * max_m), masked_m[g] real.
 int launch_gemm_split(const void* a, int64_t lda, const void* b, const void* sfb, const float* gw, void* d,
-                      int64_t ldd, const int32_t* m_indices, int M, int N, int K, int E, bool residual,
-                      int block_k, int group_m, bool pdl, int policy, bool swiglu, int num_sms, int32_t* status,
+                      int64_t ldd, const int32_t* m_indices, const int32_t* masked_m, int max_m, int M, int N, int K, int E,
+                      bool residual, int block_k, int group_m, bool pdl, int policy, bool swiglu, int num_sms, int32_t* status,
                       cudaStream_t stream);
+
+int launch_debug_split_workspace(const void* a, int64_t lda, int M, int K, int policy, bool residual, bool swiglu, void* a0,
+                                 void* a1, void* sfa, cudaStream_t stream);
 
 int launch_permute_rows(const void* src, int64_t src_ld_bytes, const int64_t* src_idx, int src_div, const int64_t* dst_idx,
                         int64_t n_rows, int row_bytes, void* dst, int64_t dst_ld_bytes, int num_sms, cudaStream_t stream);
@@ -39,7 +43,7 @@ int launch_combine_rows_peer(const int64_t* peers, int64_t rows_ld_elems, const 
 
 int launch_gemm_swap(const void* a, int64_t lda, const void* b, const void* sfb, const float* gw, void* d,
                      int64_t ldd, const int32_t* m_indices, int M, int N, int K, int E, bool residual,
-                     int token_tile, int block_k, int policy, int num_sms, int32_t* status, cudaStream_t stream);
+                     int token_tile, int block_k, int policy, bool pdl, int num_sms, int32_t* status, cudaStream_t stream);
 
 int launch_quantize_weight(const void* w, int w_dtype, int E, int N, int K, void* b, void* sfb, float* gw,
                            cudaStream_t stream);
@@ -48,6 +52,13 @@ int launch_quantize_weight_static(const void* w, int w_dtype, int E, int N, int 
                                   cudaStream_t stream);
 
 int launch_debug_decompose(const void* a, int64_t lda, int M, int K, int policy, void* q0, void* q1, void* s0, void* s1,
+                           cudaStream_t stream);
+
+int launch_debug_wait_timeout(int64_t budget_cycles, int32_t* status, cudaStream_t stream);
+
+// Checkpoint layout -> the GEMM's weight layout; see nvfp4_load_checkpoint_weights.
+int launch_load_checkpoint(int num_parts, const void* const* packed, const void* const* scale, const float* const* global_scale,
+                           const int32_t* part_rows, bool divisor, int E, int K, int n_total, void* b, void* sfb, float* gw,
                            cudaStream_t stream);
 
 int launch_mma_peak(int iters, int num_sms, double* flops_per_launch, cudaStream_t stream);

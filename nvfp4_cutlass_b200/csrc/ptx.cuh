@@ -55,9 +55,9 @@ NVFP4_DEVICE bool mbar_try_wait(uint64_t* bar, uint32_t parity)
 // in these kernels last microseconds.
 constexpr long long kWaitBudgetCycles = 2000000000ll;
 
-// Returns false if the phase did not complete within the budget, or if another
+// Returns false if the phase did not complete within `budget` clock cycles, or if another
 // thread of the CTA already gave up (`*abort_flag != 0`).
-NVFP4_DEVICE bool mbar_wait_impl(uint64_t* bar, uint32_t parity, volatile uint32_t* abort_flag)
+NVFP4_DEVICE bool mbar_wait_budget(uint64_t* bar, uint32_t parity, volatile uint32_t* abort_flag, long long budget)
 {
     if (mbar_try_wait(bar, parity)) return true;
     const long long t0 = clock64();
@@ -65,8 +65,12 @@ NVFP4_DEVICE bool mbar_wait_impl(uint64_t* bar, uint32_t parity, volatile uint32
 #pragma unroll 1
         for (int i = 0; i < 32; ++i)
             if (mbar_try_wait(bar, parity)) return true;
-        if (*abort_flag != 0 || clock64() - t0 > kWaitBudgetCycles) return false;
+        if (*abort_flag != 0 || clock64() - t0 > budget) return false;
     }
+}
+NVFP4_DEVICE bool mbar_wait_impl(uint64_t* bar, uint32_t parity, volatile uint32_t* abort_flag)
+{
+    return mbar_wait_budget(bar, parity, abort_flag, kWaitBudgetCycles);
 }
 
 // The same bounded wait for roles that wait long and need not react within cycles (an epilogue warp waiting
@@ -417,6 +421,10 @@ NVFP4_DEVICE void cluster_sync()
 NVFP4_DEVICE void st_cluster128(uint32_t addr, uint32_t a, uint32_t b, uint32_t c, uint32_t d)
 {
     asm volatile("st.shared::cluster.v4.u32 [%0], {%1, %2, %3, %4};" ::"r"(addr), "r"(a), "r"(b), "r"(c), "r"(d) : "memory");
+}
+NVFP4_DEVICE void st_cluster64(uint32_t addr, uint32_t a, uint32_t b)
+{
+    asm volatile("st.shared::cluster.v2.u32 [%0], {%1, %2};" ::"r"(addr), "r"(a), "r"(b) : "memory");
 }
 NVFP4_DEVICE void st_cluster32(uint32_t addr, uint32_t a) { asm volatile("st.shared::cluster.u32 [%0], %1;" ::"r"(addr), "r"(a) : "memory"); }
 NVFP4_DEVICE void st_cluster16(uint32_t addr, uint32_t a)

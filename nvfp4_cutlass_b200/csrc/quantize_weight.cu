@@ -10,6 +10,8 @@
 // words, which the kernel wants transposed to (K/64, N), are written coalesced.
 #include <cuda_bf16.h>
 
+#include <mutex>
+
 #include "host_common.hpp"
 #include "launchers.hpp"
 #include "ptx.cuh"
@@ -81,24 +83,11 @@ __global__ void quantize_weight_kernel(const T* __restrict__ w, int N, int K, co
     sfb[(static_cast<int64_t>(e) * atoms + at) * N + n] = static_cast<int32_t>(word);
 }
 
-}  // namespace
-
-// Two kernels, because G needs the whole expert's maximum first.  The per-expert
-// maxima are staged in a scratch array held for the life of the process.
-int launch_quantize_weight(const void* w, int w_dtype, int E, int N, int K, void* b, void* sfb, float* gw,
-                           cudaStream_t stream)
+// The two kernels (G needs the whole expert's maximum first) with the per-expert maxima staged in `amax_bits`,
+// E words the caller provides; they are cleared here, on the call's stream.
+int run_quantize_weight(const void* w, int w_dtype, int E, int N, int K, void* b, void* sfb, float* gw, uint32_t* amax_bits,
+                        cudaStream_t stream)
 {
-    if (E == 0 || N == 0 || K == 0) return NVFP4_OK;
-    static uint32_t* scratch[host::kMaxDevices] = {};
-    static int scratch_cap[host::kMaxDevices] = {};
-    int dev = 0;
-    NVFP4_CUDA_CHECK(cudaGetDevice(&dev));
-    if (scratch_cap[dev] < E) {
-        if (scratch[dev]) NVFP4_CUDA_CHECK(cudaFree(scratch[dev]));
-        NVFP4_CUDA_CHECK(cudaMalloc(&scratch[dev], sizeof(uint32_t) * E));
-        scratch_cap[dev] = E;
-    }
-    uint32_t* amax_bits = scratch[dev];
     NVFP4_CUDA_CHECK(cudaMemsetAsync(amax_bits, 0, sizeof(uint32_t) * E, stream));
     const int64_t per_expert = static_cast<int64_t>(N) * K;
     int blocks = static_cast<int>((per_expert + 256 * 16 - 1) / (256 * 16));
@@ -119,12 +108,32 @@ int launch_quantize_weight(const void* w, int w_dtype, int E, int N, int K, void
     return NVFP4_OK;
 }
 
+}  // namespace
+
+// The per-expert maxima live in a stream-ordered allocation from the library's memory pool: calls on
+// different streams never share it, nothing synchronises the device, and after the first call it is a pool look-up.
+int launch_quantize_weight(const void* w, int w_dtype, int E, int N, int K, void* b, void* sfb, float* gw,
+                           cudaStream_t stream)
+{
+    if (E == 0 || N == 0 || K == 0) return NVFP4_OK;
+    int dev = 0;
+    NVFP4_CUDA_CHECK(cudaGetDevice(&dev));
+    cudaMemPool_t pool;
+    if (int rc = host::workspace_pool(dev, &pool)) return rc;
+    uint32_t* amax_bits = nullptr;
+    NVFP4_CUDA_CHECK(cudaMallocFromPoolAsync(reinterpret_cast<void**>(&amax_bits), sizeof(uint32_t) * E, pool, stream));
+    const int rc = run_quantize_weight(w, w_dtype, E, N, K, b, sfb, gw, amax_bits, stream);
+    cudaFreeAsync(amax_bits, stream);
+    return rc;
+}
+
 // ---- allocation-free variant ----------------------------------------------------------
 // Same two kernels, but the per-expert maxima are staged in a fixed array that is part of
-// the library image instead of a cudaMalloc'ed buffer.  Every process that loads the
-// library holds NVFP4_STATIC_MAX_EXPERTS words of it on every GPU it uses, until it exits.
+// the library image instead of an allocation.  Every process that loads the library holds
+// NVFP4_STATIC_MAX_EXPERTS words of it on every GPU it uses, until it exits.
 namespace {
 static __device__ __align__(256) uint32_t g_static_amax[NVFP4_STATIC_MAX_EXPERTS];
+std::mutex g_static_mutex;
 }  // namespace
 
 // In host code `g_static_amax` is only the host-side handle of the symbol, not an address
@@ -138,32 +147,19 @@ int launch_quantize_weight_static(const void* w, int w_dtype, int E, int N, int 
     int dev = 0;
     NVFP4_CUDA_CHECK(cudaGetDevice(&dev));
     if (dev < 0 || dev >= host::kMaxDevices) return host::fail(NVFP4_E_INVALID_ARGUMENT, "device %d out of range", dev);
-    if (scratch_addr[dev] == nullptr) {
-        void* addr = nullptr;
-        NVFP4_CUDA_CHECK(cudaGetSymbolAddress(&addr, g_static_amax));
-        if (addr == nullptr) return host::fail(NVFP4_E_CUDA, "cudaGetSymbolAddress gave no address for the scratch array");
-        scratch_addr[dev] = static_cast<uint32_t*>(addr);
+    uint32_t* amax_bits = nullptr;
+    {
+        std::lock_guard<std::mutex> lock(g_static_mutex);
+        if (scratch_addr[dev] == nullptr) {
+            void* addr = nullptr;
+            NVFP4_CUDA_CHECK(cudaGetSymbolAddress(&addr, g_static_amax));
+            if (addr == nullptr) return host::fail(NVFP4_E_CUDA, "cudaGetSymbolAddress gave no address for the scratch array");
+            scratch_addr[dev] = static_cast<uint32_t*>(addr);
+        }
+        amax_bits = scratch_addr[dev];
     }
-    uint32_t* amax_bits = scratch_addr[dev];
-    // the array keeps whatever the previous call left in it: the maxima must start from zero
-    NVFP4_CUDA_CHECK(cudaMemsetAsync(amax_bits, 0, sizeof(uint32_t) * E, stream));
-    const int64_t per_expert = static_cast<int64_t>(N) * K;
-    int blocks = static_cast<int>((per_expert + 256 * 16 - 1) / (256 * 16));
-    blocks = blocks < 1 ? 1 : (blocks > 1024 ? 1024 : blocks);
-    const dim3 qgrid((N + 127) / 128, K / 64, E);
-    if (w_dtype == NVFP4_DTYPE_BF16) {
-        auto* wt = static_cast<const __nv_bfloat16*>(w);
-        expert_amax_kernel<<<dim3(blocks, E), 256, 0, stream>>>(wt, per_expert, amax_bits);
-        quantize_weight_kernel<<<qgrid, 128, 0, stream>>>(wt, N, K, amax_bits, static_cast<uint8_t*>(b),
-                                                          static_cast<int32_t*>(sfb), gw);
-    } else {
-        auto* wt = static_cast<const float*>(w);
-        expert_amax_kernel<<<dim3(blocks, E), 256, 0, stream>>>(wt, per_expert, amax_bits);
-        quantize_weight_kernel<<<qgrid, 128, 0, stream>>>(wt, N, K, amax_bits, static_cast<uint8_t*>(b),
-                                                          static_cast<int32_t*>(sfb), gw);
-    }
-    NVFP4_CUDA_CHECK(cudaGetLastError());
-    return NVFP4_OK;
+    // the array keeps whatever the previous call left in it: run_quantize_weight clears the maxima first
+    return run_quantize_weight(w, w_dtype, E, N, K, b, sfb, gw, amax_bits, stream);
 }
 
 }  // namespace nvfp4

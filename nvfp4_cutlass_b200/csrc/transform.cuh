@@ -21,7 +21,8 @@
 
 namespace nvfp4::xform {
 
-enum ScalePolicy : int { kDerivedDiv8 = 0, kResidualAmax = 1 };
+// The reference kernel's four activation scale policies (include/nvfp4_gemm/transform/dual_nvfp4.cuh:31-61 there).
+enum ScalePolicy : int { kDerivedDiv8 = 0, kResidualAmax = 1, kDerivedDiv4 = 2, kDiv4Radix8 = 3 };
 
 // ---- shared-memory addressing ----------------------------------------------------
 // BF16 activation tile as TMA lands it: boxes of 64 columns (128 B rows) x kRows,
@@ -85,10 +86,20 @@ NVFP4_DEVICE float e4m3_to_f32(uint32_t c)
 // kPolicy 0 = derived_div8: s1 = Q_e4m3(s0 / 8), q1 = Q((u - q0) * 8), s0 floored at 2^-6.
 // kPolicy 1 = residual_amax: r = x - q0 * s0 (exact in FP32), s1 = Q_e4m3(max(amax(r) / 6, 2^-9)), q1 = Q(r / s1),
 //             s0 floored at 2^-9 (tests/python/reference/dual_nvfp4.py:131-152 of the reference).
+// kPolicy 2 = derived_div4: as 0 with radix 4 (s1 = Q_e4m3(s0 / 4), q1 = Q((u - q0) * 4)): the residual never clips.
+// kPolicy 3 = div4_radix8: s0 = Q_e4m3(max(amax / 4, 2^-6)) so that q0 stays on the |u| <= 4 half of the E2M1 grid,
+//             radix 8 (include/nvfp4_gemm/transform/dual_nvfp4.cuh:31-61 of the reference; these two exist only in
+//             its kernel, so the CPU statement they are checked against follows the emulation's operation order with
+//             these constants).
 template <bool kResidual, int kPolicy = 0>
 NVFP4_DEVICE void decompose_block16(const uint32_t (&w)[8], Block16& out)
 {
-    static_assert(kPolicy == 0 || kPolicy == 1, "scale policy");
+    static_assert(kPolicy >= 0 && kPolicy <= 3, "scale policy");
+    constexpr bool kAmax2 = kPolicy == 1;                     // second amax over the residual
+    constexpr float kS0Mul = kPolicy == 3 ? 0.25f : 0.16666667163372040f;
+    constexpr float kS1Mul = kPolicy == 2 ? 0.25f : 0.125f;
+    constexpr float kRadix = kPolicy == 2 ? 4.0f : 8.0f;
+    constexpr unsigned short kNegRadixF16 = kPolicy == 2 ? 0xC400u : 0xC800u;
 #ifdef NVFP4_ABLATE_XFORM   // timing experiments only (wrong results); never defined in the shipped build
     out.q0[0] = w[0] ^ w[1]; out.q0[1] = w[2] ^ w[3]; out.q1[0] = w[4] ^ w[5]; out.q1[1] = w[6] ^ w[7];
     out.s0 = 0x38; out.s1 = 0x20;
@@ -106,11 +117,11 @@ NVFP4_DEVICE void decompose_block16(const uint32_t (&w)[8], Block16& out)
     const float amax = __uint_as_float((m0 & 0x7fffu) << 16);
 
     // s0 = Q_e4m3(max(amax * fl(1/6), floor)); with the 2^-6 floor always a normal E4M3 value
-    const float s0_pre = fmaxf(__fmul_rn(amax, 0.16666667163372040f), kPolicy == 0 ? 0.015625f : 0.001953125f);
+    const float s0_pre = fmaxf(__fmul_rn(amax, kS0Mul), kAmax2 ? 0.001953125f : 0.015625f);
     const uint32_t s0c = ptx::cvt_e4m3(s0_pre);
-    const float s0 = kPolicy == 0 ? __uint_as_float((s0c << 20) + 0x3C000000u) : e4m3_to_f32(s0c);
+    const float s0 = kAmax2 ? e4m3_to_f32(s0c) : __uint_as_float((s0c << 20) + 0x3C000000u);
     out.s0 = s0c;
-    out.s1 = kPolicy == 0 ? ptx::cvt_e4m3(__fmul_rn(s0, 0.125f)) : 0u;
+    out.s1 = kAmax2 ? 0u : ptx::cvt_e4m3(__fmul_rn(s0, kS1Mul));
 
     // u = x / s0 as the correctly rounded quotient: r_hi ~ 1 / s0, r_lo = its error term formed exactly by one FMA
     const float r_hi = ptx::rcp_approx(s0);
@@ -127,7 +138,7 @@ NVFP4_DEVICE void decompose_block16(const uint32_t (&w)[8], Block16& out)
     out.q0[0] = ptx::cvt_e2m1x8(u[0], u[1], u[2], u[3], u[4], u[5], u[6], u[7]);
     out.q0[1] = ptx::cvt_e2m1x8(u[8], u[9], u[10], u[11], u[12], u[13], u[14], u[15]);
 
-    if constexpr (kResidual && kPolicy == 1) {
+    if constexpr (kResidual && kAmax2) {
         // r = x - dec(q0) * s0: the product has at most 7 significant bits and x has 8, so the FMA is exact;
         // dec(q0) comes back as FP16 and s0 (>= 2^-9) is an FP16 value too
         const unsigned short neg_s0 = __half_as_ushort(__float2half_rn(-s0));
@@ -152,14 +163,14 @@ NVFP4_DEVICE void decompose_block16(const uint32_t (&w)[8], Block16& out)
         out.q1[0] = ptx::cvt_e2m1x8(r[0], r[1], r[2], r[3], r[4], r[5], r[6], r[7]);
         out.q1[1] = ptx::cvt_e2m1x8(r[8], r[9], r[10], r[11], r[12], r[13], r[14], r[15]);
     } else if constexpr (kResidual) {
-        // r = (u - dec(q0)) * 8 = 8u + dec(q0) * (-8): exact, the decode comes back as FP16
+        // r = (u - dec(q0)) * radix = radix * u + dec(q0) * (-radix): exact, the decode comes back as FP16
         float r[16];
 #pragma unroll
         for (int i = 0; i < 8; ++i) {
             const uint32_t byte = (out.q0[i >> 2] >> (8 * (i & 3))) & 0xffu;
             const uint32_t d = ptx::cvt_e2m1x2_to_f16x2(byte);
-            r[2 * i] = ptx::fma_f32_f16(static_cast<unsigned short>(d & 0xffffu), 0xC800u, __fmul_rn(u[2 * i], 8.0f));
-            r[2 * i + 1] = ptx::fma_f32_f16(static_cast<unsigned short>(d >> 16), 0xC800u, __fmul_rn(u[2 * i + 1], 8.0f));
+            r[2 * i] = ptx::fma_f32_f16(static_cast<unsigned short>(d & 0xffffu), kNegRadixF16, __fmul_rn(u[2 * i], kRadix));
+            r[2 * i + 1] = ptx::fma_f32_f16(static_cast<unsigned short>(d >> 16), kNegRadixF16, __fmul_rn(u[2 * i + 1], kRadix));
         }
         out.q1[0] = ptx::cvt_e2m1x8(r[0], r[1], r[2], r[3], r[4], r[5], r[6], r[7]);
         out.q1[1] = ptx::cvt_e2m1x8(r[8], r[9], r[10], r[11], r[12], r[13], r[14], r[15]);

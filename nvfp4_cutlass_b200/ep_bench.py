@@ -21,6 +21,39 @@ import torch.distributed as dist
 E_TOTAL, HIDDEN, INTER, TOKENS, TOP_K = 128, 4096, 1536, 16384, 8
 
 
+def one_gpu_record(dev, local: int, fp4_peak: float, steps: int = 5) -> dict:
+    """The layer at one rank (all 128 experts local, the dispatch and combine kernels on local buffers), as a
+    sub-record of the one-GPU benchmark line: ms per step and its phases."""
+    import bench
+    import nvfp4_gemm  # noqa: F401
+    from .ep import ExpertParallelMoE, route_topk
+    up = bench.build_weights(E_TOTAL, 2 * INTER, HIDDEN, dev, seed=20)
+    down = bench.build_weights(E_TOTAL, HIDDEN, INTER, dev, seed=40)
+    g = torch.Generator(device=dev).manual_seed(10)
+    z = torch.randn(TOKENS, HIDDEN, generator=g, device=dev)
+    chi = torch.randn(TOKENS, HIDDEN, 4, generator=g, device=dev).pow(2).mean(-1).sqrt()
+    x = (z / chi).clamp(-2688.0, 2688.0).to(torch.bfloat16)
+    del z, chi
+    logits = torch.randn(TOKENS, E_TOTAL, generator=torch.Generator(device=dev).manual_seed(30), device=dev)
+    ids, wts = route_topk(logits, TOP_K)
+    layer = ExpertParallelMoE(E_TOTAL, HIDDEN, INTER, up, down, alignment=128,
+                              peer_rows_cap=int(1.5 * TOKENS * TOP_K) + E_TOTAL * 128)
+    sampler = bench.ClockSampler(local)
+    sampler.start()
+    ms, t0, t1 = bench.timed(lambda: layer(x, ids, wts), steps, 3, lambda: None)
+    clocks = sampler.stop(t0, t1)
+    marks = []
+    layer.forward_peer(x, ids, wts, marks)
+    torch.cuda.synchronize()
+    phases = [marks[i].elapsed_time(marks[i + 1]) for i in range(4)]
+    real_rows = float(TOKENS * TOP_K)
+    flops = 2.0 * real_rows * (2 * INTER * HIDDEN + HIDDEN * INTER)
+    return {"workload": f"expert-parallel MoE layer at one rank: E={E_TOTAL}, {TOKENS} tokens, top-{TOP_K}", "ms_per_step": ms,
+            "steps": steps, "value": flops / (ms * 1e-3) / 1e12, "unit": "TFLOP/s",
+            "phases_ms": {"plan": phases[0], "dispatch": phases[1], "experts": phases[2], "combine": phases[3]},
+            "experts_frac": 2.0 * flops / (phases[2] * 1e-3) / 1e12 / fp4_peak, "bound": "tensor", "clocks": clocks}
+
+
 def run(args, workload: str, world: int, rank: int, local: int) -> None:
     import bench
     import nvfp4_gemm

@@ -80,6 +80,30 @@ def quantize_weight_nvfp4(w: torch.Tensor):
     return _quantize_weight_host(w)
 
 
+def load_checkpoint_weights_nvfp4(parts, global_scale_is_divisor: bool = True):
+    """NVFP4 checkpoint tensors -> (b, sfb, gw) for the grouped GEMM, on the GPU.
+
+    ``parts``: the projections to fuse along N, in order, each a triple (weight_packed uint8 (E, rows, K/2),
+    weight_scale float8_e4m3fn / uint8 (E, rows, K/16), weight_global_scale float32 (E,)) stacked over the experts:
+    [gate, up] for a fused gate+up projection, [down] for a down projection.  Projections with different global
+    scales get one shared gw per expert and re-folded block scales, the integration step the reference describes
+    and leaves to the weight loader (docs/bf16-dual-nvfp4-algorithm.html:235-244 there).  CUDA tensors only.
+    """
+    for part in parts:
+        if not all(t.is_cuda for t in part):
+            raise RuntimeError("load_checkpoint_weights_nvfp4 runs on the GPU: move the checkpoint tensors to a CUDA device")
+    from . import _C
+    return _C.load_checkpoint_weights(parts, global_scale_is_divisor)
+
+
+def unpack_sf_atoms(sfb: torch.Tensor, num_experts: int) -> torch.Tensor:
+    """Inverse of pack_sf_atoms: (E*K/64, N) int32 -> (E, N, K/16) E4M3 bytes (the checkpoint's weight_scale layout)."""
+    atoms = sfb.shape[0] // num_experts
+    n = sfb.shape[1]
+    words = sfb.reshape(num_experts, atoms, n).permute(0, 2, 1).contiguous()
+    return words.view(torch.uint8).reshape(num_experts, n, atoms * 4)
+
+
 def dequantize_weight_nvfp4(b, sfb, gw, num_experts: int, n: int, k: int) -> torch.Tensor:
     """Inverse of quantize_weight_nvfp4: FP32 (E, N, K) = dec(q) * dec(S) * G."""
     u = b.reshape(num_experts, n, k // 2).view(torch.uint8)

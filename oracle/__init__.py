@@ -4,7 +4,9 @@ Only the tests, the smoke test and the benchmark's CPU-baseline leg import this
 package.  It loads ``oracle/liboracle.so`` (the C restatement of the reference's
 PyTorch emulation, see ``dual_nvfp4_oracle.c``) and, if present,
 ``oracle/_ref/libref_twin.so`` (the reference's own C++ host twin compiled
-unmodified from its header).  Tensors in and out are CPU torch tensors.
+unmodified from its header) and ``oracle/_ref/ref_dual_nvfp4.py`` (a build-time copy
+of the reference's PyTorch emulation, the CPU baseline the benchmark times).
+Tensors in and out are CPU torch tensors.
 """
 from __future__ import annotations
 
@@ -19,7 +21,7 @@ _HERE = os.path.dirname(os.path.abspath(__file__))
 _LIB_PATH = os.path.join(_HERE, "liboracle.so")
 _REF_PATH = os.path.join(_HERE, "_ref", "libref_twin.so")
 
-POLICIES = {"derived_div8": 0, "residual_amax": 1}
+POLICIES = {"derived_div8": 0, "residual_amax": 1, "derived_div4": 2, "div4_radix8": 3}
 E2M1_LEVELS = (0.0, 0.5, 1.0, 1.5, 2.0, 3.0, 4.0, 6.0)
 
 
@@ -29,7 +31,7 @@ def build(force: bool = False) -> None:
     stale = (not os.path.exists(_LIB_PATH)) or os.path.getmtime(_LIB_PATH) < os.path.getmtime(src)
     if force or stale:
         subprocess.run(["make", "-C", _HERE, "liboracle.so", "-B"], check=True, capture_output=True)
-    subprocess.run(["make", "-C", _HERE, "ref"], check=True, capture_output=True)
+    subprocess.run(["make", "-C", _HERE, "ref", "ref_py"], check=True, capture_output=True)
 
 
 _lib = None
@@ -58,6 +60,25 @@ def ref_twin() -> ctypes.CDLL | None:
     if _ref is None and os.path.exists(_REF_PATH):
         _ref = ctypes.CDLL(_REF_PATH)
     return _ref
+
+
+_emu = None
+
+
+def ref_emulation():
+    """The reference's own PyTorch emulation module (decompose_dual_nvfp4, dual_nvfp4_grouped_gemm, ...), loaded from
+    the build-time copy in oracle/_ref/, or None when that copy was never made."""
+    global _emu
+    path = os.path.join(_HERE, "_ref", "ref_dual_nvfp4.py")
+    if _emu is None and os.path.exists(path):
+        import importlib.util
+        import sys
+        spec = importlib.util.spec_from_file_location("ref_dual_nvfp4", path)
+        mod = importlib.util.module_from_spec(spec)
+        sys.modules["ref_dual_nvfp4"] = mod          # its dataclasses look their module up by name
+        spec.loader.exec_module(mod)
+        _emu = mod
+    return _emu
 
 
 def num_threads() -> int:

@@ -75,7 +75,7 @@ def test_weight_quantiser_fp32_input_and_zero_expert(dev, oracle):
 
 
 # ---------------------------------------------------------------- Algorithm 1
-POLICIES = ["derived_div8", "residual_amax"]
+POLICIES = ["derived_div8", "residual_amax", "derived_div4", "div4_radix8"]
 
 
 def check_decompose(dev, oracle, a, policy="derived_div8"):
@@ -87,7 +87,7 @@ def check_decompose(dev, oracle, a, policy="derived_div8"):
     assert torch.equal(grid_i8_from_codes(unpack_codes(q1)), grid_i8_from_codes(o1)), "q1 differs"
 
 
-@pytest.mark.parametrize("policy", POLICIES)
+@pytest.mark.parametrize("policy", POLICIES[:2])       # the two policies the reference's emulation has
 def test_decompose_bit_exact_golden(dev, oracle, policy):
     g = load_golden("decompose.npz")
     a = bf16_from_bits(g["a_bits"])                          # 42 x 256, incl. adversarial rows
@@ -121,11 +121,11 @@ def test_decompose_bit_exact_every_scale_and_value(dev, oracle, policy):
     """Every E4M3 scale the floor allows x every BF16 magnitude up to the block maximum:
     each 16-block carries one element that pins s0 and fifteen probe values."""
     blocks = []
-    for code in range(0x08 if policy == "derived_div8" else 0x01, 0x7F):
+    for code in range(0x01 if policy == "residual_amax" else 0x08, 0x7F):
         s0 = torch.tensor([code], dtype=torch.uint8).view(torch.float8_e4m3fn).float().item()
-        top = torch.tensor(6.0 * s0).to(torch.bfloat16)
+        top = torch.tensor((4.0 if policy == "div4_radix8" else 6.0) * s0).to(torch.bfloat16)
         bits = torch.arange(0, int(top.view(torch.int16).item()) + 1, 7, dtype=torch.int32)
-        ties = (torch.tensor([0.25, 0.75, 1.25, 1.75, 2.5, 3.5, 5.0, 0.28125, 1.53125, 3.25, 5.5]) * s0)
+        ties = (torch.tensor([0.25, 0.75, 1.25, 1.75, 2.5, 3.5, 5.0, 0.28125, 1.53125, 3.25, 5.5, 0.3125, 1.0625, 2.15625]) * s0)
         vals = torch.cat([bits.to(torch.int16).view(torch.bfloat16).float(), ties])
         vals = torch.cat([vals, -vals])
         pad = (-vals.numel()) % 15
@@ -178,7 +178,8 @@ def test_gemm_matches_oracle(dev, oracle, shape, residual):
         assert rel_l2(d, truth) <= rel_l2(want, truth) * 1.02 + 1e-4     # no worse than the reference chain
 
 
-@pytest.mark.parametrize("tune", [dict(tune_direct_a=1), dict(tune_transform_warps=16), dict(tune_sched_group=4)])
+@pytest.mark.parametrize("tune", [dict(tune_direct_a=1), dict(tune_transform_warps=16), dict(tune_sched_group=4),
+                                  dict(tune_split_transform=2, tune_sched_group=4)])
 @pytest.mark.parametrize("residual", [True, False])
 def test_gemm_kernel_variants_agree(dev, oracle, tune, residual):
     """The direct-global-read transform, the 16-warp transform and another tile order against the
@@ -316,34 +317,51 @@ def test_split_path_on_two_streams_at_once(dev, oracle):
 
 @pytest.mark.parametrize("shape", [(1, 128, 128, 256), (2, 128, 256, 512), (4, 256, 1024, 2048), (4, 512, 2048, 512), (3, 128, 384, 256)])
 @pytest.mark.parametrize("residual", [True, False])
-def test_gemm_residual_amax_policy_matches_oracle(dev, oracle, shape, residual):
-    """scale_policy="residual_amax" on the reference's acceptance shapes (tests/python/test_gemm.py:31-36 there): the
-    split path for N % 256 == 0 and N >= 1024, the single-CTA fused kernel otherwise."""
+@pytest.mark.parametrize("policy", POLICIES[1:])
+def test_gemm_other_scale_policies_match_oracle(dev, oracle, shape, residual, policy):
+    """residual_amax, derived_div4 and div4_radix8 on the reference's acceptance shapes (tests/python/test_gemm.py:31-36
+    there) through the default dispatch: the split path for N % 256 == 0 and N >= 1024, a fused kernel otherwise."""
     e, rows, n, k = shape
     a, w = make_case(e, rows, n, k, seed=900 + n + k)
     b, sfb, gw = nvfp4_gemm.quantize_weight_nvfp4(w.to(dev))
     mi = nvfp4_gemm.make_m_indices([rows] * e)
-    d = run_gemm(dev, a, b, sfb, gw, mi, n, enable_residual_pass=residual, scale_policy="residual_amax")
+    d = run_gemm(dev, a, b, sfb, gw, mi, n, enable_residual_pass=residual, scale_policy=policy)
     want = oracle.grouped_gemm(a, b.cpu(), sfb.cpu(), gw.cpu(), mi, n, mode="dual" if residual else "single",
-                               scale_policy="residual_amax")
+                               scale_policy=policy)
     truth = oracle.grouped_gemm(a, b.cpu(), sfb.cpu(), gw.cpu(), mi, n, mode="truth")
     assert rel_l2(d, want) < REL_L2_VS_ORACLE
     if residual:
         assert cosine(d, truth) > 0.999
-        div8 = run_gemm(dev, a, b, sfb, gw, mi, n)
-        assert rel_l2(d, truth) <= rel_l2(div8, truth) * 1.05       # the second amax pass buys accuracy
+        if policy == "residual_amax":
+            div8 = run_gemm(dev, a, b, sfb, gw, mi, n)
+            assert rel_l2(d, truth) <= rel_l2(div8, truth) * 1.05       # the second amax pass buys accuracy
+
+
+@pytest.mark.parametrize("policy", POLICIES)
+@pytest.mark.parametrize("kw", [dict(tune_split_transform=2, tune_cluster=4), dict(tune_split_transform=2, tune_cluster=2),
+                                dict(tune_split_transform=2, tune_cluster=1), dict(tune_split_transform=1)],
+                         ids=["cluster4", "cluster2", "single_cta", "split"])
+def test_every_kernel_family_runs_every_policy(dev, oracle, policy, kw):
+    e, rows, n, k = 2, 256, 1024, 640
+    a, w = make_case(e, rows, n, k, seed=1234)
+    b, sfb, gw = nvfp4_gemm.quantize_weight_nvfp4(w.to(dev))
+    mi = nvfp4_gemm.make_m_indices([rows] * e)
+    d = run_gemm(dev, a, b, sfb, gw, mi, n, scale_policy=policy, **kw)
+    want = oracle.grouped_gemm(a, b.cpu(), sfb.cpu(), gw.cpu(), mi, n, scale_policy=policy)
+    assert rel_l2(d, want) < REL_L2_VS_ORACLE
 
 
 @pytest.mark.parametrize("case", [([16, 48, 16, 32], 16, 384, 1024), ([64, 128], 64, 256, 384), ([32] * 4, 32, 512, 2048)])
-def test_gemm_swap_ab_residual_amax_matches_oracle(dev, oracle, case):
+@pytest.mark.parametrize("policy", POLICIES[1:])
+def test_gemm_swap_ab_other_policies_match_oracle(dev, oracle, case, policy):
     sizes, align, n, k = case
     g = torch.Generator().manual_seed(6000 + n + k)
     a = torch.randn(sum(sizes), k, generator=g).to(torch.bfloat16)
     w = (torch.randn(len(sizes), n, k, generator=g) * 0.02).to(torch.bfloat16)
     b, sfb, gw = nvfp4_gemm.quantize_weight_nvfp4(w.to(dev))
     mi = nvfp4_gemm.make_m_indices(sizes, alignment=align)
-    d = run_gemm(dev, a, b, sfb, gw, mi, n, tune_swap_ab=1, m_alignment=align, scale_policy="residual_amax")
-    want = oracle.grouped_gemm(a, b.cpu(), sfb.cpu(), gw.cpu(), mi, n, scale_policy="residual_amax")
+    d = run_gemm(dev, a, b, sfb, gw, mi, n, tune_swap_ab=1, m_alignment=align, scale_policy=policy)
+    want = oracle.grouped_gemm(a, b.cpu(), sfb.cpu(), gw.cpu(), mi, n, scale_policy=policy)
     assert rel_l2(d, want) < REL_L2_VS_ORACLE
 
 
@@ -530,3 +548,191 @@ def test_both_orientations_agree(dev):
     d0 = run_gemm(dev, a, b, sfb, gw, mi, n)
     d1 = run_gemm(dev, a, b, sfb, gw, mi, n, tune_swap_ab=1, m_alignment=128)
     assert rel_l2(d1, d0) < 1e-3          # same codes, same products; only the summation order differs
+
+
+# ---------------------------------------------------------------- the split path's own bytes
+def workspace_from_oracle(oracle, a, policy, residual):
+    """oracle.decompose re-laid into the workspace layout of the split path."""
+    o0, o1, s0, s1 = oracle.decompose(a, scale_policy=policy)
+    m, k = a.shape
+    atoms = torch.zeros(m // 128, k // 64, 2 if residual else 1, 512, dtype=torch.uint8)
+    r = torch.arange(m)
+    off = (r % 128 % 32) * 16 + (r % 128 // 32) * 4
+    for p, sc in enumerate((s0, s1) if residual else (s0,)):
+        sc4 = sc.reshape(m, k // 64, 4)
+        for j in range(4):
+            atoms[r // 128, :, p, off + j] = sc4[:, :, j]
+    return o0, o1, atoms
+
+
+@pytest.mark.parametrize("policy", POLICIES)
+@pytest.mark.parametrize("residual", [True, False])
+def test_split_workspace_byte_for_byte(dev, oracle, policy, residual):
+    """The quantised activations the split GEMM consumes -- packed codes and the scale atoms in their tensor-memory
+    image -- against the oracle, on config C1's activations and on the lognormal / Student-t / outlier inputs."""
+    g = torch.Generator().manual_seed(0)
+    inputs = [torch.randn(256, 1024, generator=g)]
+    inputs.append(torch.randn(256, 512, generator=g) * torch.exp(0.5 * torch.randn(256, 1, generator=g)))
+    inputs.append((torch.randn(128, 512, generator=g) / torch.sqrt(torch.randn(128, 512, 4, generator=g).pow(2).mean(-1))).clamp(-2688, 2688))
+    x = torch.randn(128, 1024, generator=g)
+    x[:, torch.randperm(1024, generator=g)[:2]] *= 50.0
+    inputs.append(x)
+    inputs.append(torch.randn(128, 256, generator=g) * 1e-3)
+    for x in inputs:
+        a = x.to(torch.bfloat16)
+        a0, a1, sfa = _C.debug_split_workspace(a.to(dev), scale_policy=policy, enable_residual_pass=residual)
+        o0, o1, atoms = workspace_from_oracle(oracle, a, policy, residual)
+        assert torch.equal(sfa.cpu(), atoms), "scale atoms differ"
+        assert torch.equal(grid_i8_from_codes(unpack_codes(a0)), grid_i8_from_codes(o0)), "A0 codes differ"
+        if residual:
+            assert torch.equal(grid_i8_from_codes(unpack_codes(a1)), grid_i8_from_codes(o1)), "A1 codes differ"
+
+
+@pytest.mark.parametrize("residual", [True, False])
+def test_split_workspace_swiglu_fold_byte_for_byte(dev, oracle, residual):
+    """The SwiGLU-folded form: the workspace must hold Algorithm 1 of the BF16-rounded product silu(gate) * up as the
+    stand-alone SwiGLU kernel computes it."""
+    g = torch.Generator().manual_seed(5)
+    h = (torch.randn(256, 2 * 384 + 16, generator=g) * 2).to(torch.bfloat16).to(dev)[:, :2 * 384]      # strided rows
+    act = _C.swiglu(h.contiguous()).cpu()
+    a0, a1, sfa = _C.debug_split_workspace(h, enable_residual_pass=residual, fold_swiglu=True)
+    o0, o1, atoms = workspace_from_oracle(oracle, act, "derived_div8", residual)
+    assert torch.equal(sfa.cpu(), atoms)
+    assert torch.equal(grid_i8_from_codes(unpack_codes(a0)), grid_i8_from_codes(o0))
+    if residual:
+        assert torch.equal(grid_i8_from_codes(unpack_codes(a1)), grid_i8_from_codes(o1))
+
+
+# ---------------------------------------------------------------- masked layout
+@pytest.mark.parametrize("residual", [True, False])
+@pytest.mark.parametrize("k", [512, 640])
+def test_gemm_masked_layout_matches_oracle(dev, oracle, residual, k):
+    """Groups with device-side row counts: empty groups, a full group, counts that are not multiples of 128, a count
+    above max_m (clamped); rows past a group's last row block must stay untouched."""
+    e, max_m, n = 6, 512, 1024
+    counts = [300, 0, 512, 1, 129, 900]
+    g = torch.Generator().manual_seed(77 + k)
+    a = torch.randn(e, max_m, k, generator=g).to(torch.bfloat16)
+    w = (torch.randn(e, n, k, generator=g) * 0.02).to(torch.bfloat16)
+    b, sfb, gw = nvfp4_gemm.quantize_weight_nvfp4(w.to(dev))
+    d = torch.full((e, max_m, n), float("nan"), dtype=torch.bfloat16, device=dev)
+    status = torch.zeros(1, dtype=torch.int32, device=dev)
+    masked_m = torch.tensor(counts, dtype=torch.int32, device=dev)
+    nvfp4_gemm.m_grouped_bf16_dual_nvfp4_gemm_masked(a.to(dev), b, sfb, gw, d, masked_m, enable_residual_pass=residual,
+                                                     device_status=status)
+    torch.cuda.synchronize()
+    assert _C.read_status(status) == 0
+    dc = d.cpu()
+    for grp, c in enumerate(counts):
+        live = min((min(c, max_m) + 127) // 128 * 128, max_m)
+        assert torch.isnan(dc[grp, live:].float()).all(), "rows past the last row block were written"
+        if live == 0:
+            continue
+        want = oracle.grouped_gemm(a[grp, :live], b.cpu()[grp * n:(grp + 1) * n], sfb.cpu()[grp * (k // 64):(grp + 1) * (k // 64)],
+                                   gw.cpu()[grp:grp + 1], torch.zeros(live, dtype=torch.int32), n,
+                                   mode="dual" if residual else "single")
+        assert rel_l2(dc[grp, :live], want) < REL_L2_VS_ORACLE, grp
+
+
+def test_gemm_masked_layout_with_swiglu_fold_equals_contiguous(dev):
+    """The masked call on full groups against the contiguous call on the same rows: same kernels, same bits."""
+    e, max_m, inter, hidden = 3, 256, 384, 512
+    g = torch.Generator().manual_seed(21)
+    h = (torch.randn(e, max_m, 2 * inter, generator=g) * 2).to(torch.bfloat16).to(dev)
+    w = (torch.randn(e, hidden, inter, generator=g) * 0.05).to(torch.bfloat16).to(dev)
+    b, sfb, gw = nvfp4_gemm.quantize_weight_nvfp4(w)
+    d_masked = torch.zeros(e, max_m, hidden, dtype=torch.bfloat16, device=dev)
+    nvfp4_gemm.m_grouped_bf16_dual_nvfp4_gemm_masked(h, b, sfb, gw, d_masked, torch.full((e,), max_m, dtype=torch.int32, device=dev),
+                                                     fold_swiglu=True)
+    d_contig = torch.zeros(e * max_m, hidden, dtype=torch.bfloat16, device=dev)
+    _C.m_grouped_swiglu_dual_nvfp4_gemm_contiguous(h.reshape(e * max_m, -1), b, sfb, gw, d_contig,
+                                                   nvfp4_gemm.make_m_indices([max_m] * e).to(dev))
+    torch.cuda.synchronize()
+    assert torch.equal(d_masked.reshape(e * max_m, hidden), d_contig)
+
+
+# ---------------------------------------------------------------- checkpoint loader
+def to_checkpoint(b, sfb, gw, e, n, k, divisor):
+    from nvfp4_cutlass_b200.layout import unpack_sf_atoms
+    return (b.view(torch.uint8).reshape(e, n, k // 2), unpack_sf_atoms(sfb, e), (1.0 / gw) if divisor else gw.clone())
+
+
+@pytest.mark.parametrize("divisor", [False, True])
+def test_checkpoint_loader_fuses_gate_and_up_byte_exact(dev, oracle, divisor):
+    """Gate and up projections quantised separately (own global scales) -> one fused (b, sfb, gw): byte for byte
+    against the CPU restatement of the re-folding rule, and close to the two parts dequantised on their own."""
+    from oracle import checkpoint
+    e, n_half, k = 4, 192, 256
+    g = torch.Generator().manual_seed(8)
+    wg = (torch.randn(e, n_half, k, generator=g) * 0.02).to(torch.bfloat16)
+    wu = (torch.randn(e, n_half, k, generator=g) * 0.07).to(torch.bfloat16)
+    wu[2] *= 0.1                                                       # an expert whose gate scale is the larger one
+    qg, qu = oracle.quantize_weight(wg), oracle.quantize_weight(wu)
+    parts = [to_checkpoint(*qg, e, n_half, k, divisor), to_checkpoint(*qu, e, n_half, k, divisor)]
+    b, sfb, gw = nvfp4_gemm.load_checkpoint_weights_nvfp4([tuple(t.to(dev) for t in p) for p in parts], global_scale_is_divisor=divisor)
+    ob, osfb, ogw = checkpoint.load_checkpoint_weights(parts, global_scale_is_divisor=divisor)
+    assert torch.equal(gw.cpu(), ogw) and torch.equal(sfb.cpu(), osfb) and torch.equal(b.cpu(), ob)
+    fused = oracle.dequantize_weight(b.cpu(), sfb.cpu(), gw.cpu(), e, 2 * n_half, k)
+    apart = torch.cat([oracle.dequantize_weight(*qg, e, n_half, k), oracle.dequantize_weight(*qu, e, n_half, k)], dim=1)
+    assert rel_l2(fused, apart) < 0.03                                 # one more E4M3 rounding of the block scales
+    # and the fused weights run: GEMM on them against the oracle on the same bytes
+    a = torch.randn(e * 128, k, generator=g).to(torch.bfloat16)
+    mi = nvfp4_gemm.make_m_indices([128] * e)
+    d = run_gemm(dev, a, b, sfb, gw, mi, 2 * n_half)
+    assert rel_l2(d, oracle.grouped_gemm(a, ob, osfb, ogw, mi, 2 * n_half)) < REL_L2_VS_ORACLE
+
+
+def test_checkpoint_loader_single_part_round_trip(dev, oracle):
+    """A down projection (one part): the loader returns the checkpoint's own codes and scales bit for bit."""
+    e, n, k = 3, 256, 384 + 128
+    g = torch.Generator().manual_seed(9)
+    w = (torch.randn(e, n, k, generator=g) * 0.03).to(torch.bfloat16)
+    ob, osfb, ogw = oracle.quantize_weight(w)
+    part = to_checkpoint(ob, osfb, ogw, e, n, k, divisor=False)
+    b, sfb, gw = nvfp4_gemm.load_checkpoint_weights_nvfp4([tuple(t.to(dev) for t in part)], global_scale_is_divisor=False)
+    assert torch.equal(b.cpu(), ob) and torch.equal(sfb.cpu(), osfb) and torch.equal(gw.cpu(), ogw)
+
+
+# ---------------------------------------------------------------- bounded waits and status
+def test_bounded_wait_runs_out_cleanly(dev, oracle):
+    """A wait nobody satisfies expires after its budget: status bit 0 is set, the kernel returns, tensor memory is
+    free again (a GEMM that needs all 512 columns runs right after it) and read_status reports the timeout once."""
+    status = torch.zeros(1, dtype=torch.int32, device=dev)
+    _C.debug_wait_timeout(1_000_000, status)
+    torch.cuda.synchronize()
+    assert int(status.item()) == 1
+    with pytest.raises(RuntimeError, match="error 4"):
+        _C.read_status(status)
+    assert _C.read_status(status) == 0                         # cleared by the read
+    e, rows, n, k = 1, 128, 256, 256
+    a, w = make_case(e, rows, n, k, seed=3)
+    b, sfb, gw = nvfp4_gemm.quantize_weight_nvfp4(w.to(dev))
+    mi = nvfp4_gemm.make_m_indices([rows] * e)
+    d = run_gemm(dev, a, b, sfb, gw, mi, n)
+    assert rel_l2(d, oracle.grouped_gemm(a, b.cpu(), sfb.cpu(), gw.cpu(), mi, n)) < REL_L2_VS_ORACLE
+
+
+@pytest.mark.parametrize("no_pdl", [0, 1])
+def test_back_to_back_calls_chained_by_dependent_launch(dev, oracle, no_pdl):
+    """up -> down -> up ... on one stream without host synchronisation, every kernel launched with programmatic
+    stream serialisation (or without: tune_no_pdl): each call must see the previous call's output."""
+    e, rows, hidden, inter = 2, 256, 512, 1024
+    g = torch.Generator().manual_seed(15)
+    x = torch.randn(e * rows, hidden, generator=g).to(torch.bfloat16)
+    w1 = (torch.randn(e, inter, hidden, generator=g) * 0.05).to(torch.bfloat16)
+    w2 = (torch.randn(e, hidden, inter, generator=g) * 0.05).to(torch.bfloat16)
+    q1, q2 = nvfp4_gemm.quantize_weight_nvfp4(w1.to(dev)), nvfp4_gemm.quantize_weight_nvfp4(w2.to(dev))
+    mi = nvfp4_gemm.make_m_indices([rows] * e)
+    mid, xd = mi.to(dev), x.to(dev)
+    h = torch.empty(e * rows, inter, dtype=torch.bfloat16, device=dev)
+    y = torch.empty(e * rows, hidden, dtype=torch.bfloat16, device=dev)
+    for kw in (dict(), dict(tune_split_transform=2), dict(tune_swap_ab=1, m_alignment=128)):
+        h.zero_(); y.zero_()
+        for _ in range(3):
+            nvfp4_gemm.m_grouped_bf16_dual_nvfp4_gemm_contiguous(xd, *q1, h, mid, tune_no_pdl=no_pdl, **kw)
+            nvfp4_gemm.m_grouped_bf16_dual_nvfp4_gemm_contiguous(h, *q2, y, mid, tune_no_pdl=no_pdl, **kw)
+        torch.cuda.synchronize()
+        h_want = oracle.grouped_gemm(x, q1[0].cpu(), q1[1].cpu(), q1[2].cpu(), mi, inter)
+        assert rel_l2(h.cpu(), h_want) < REL_L2_VS_ORACLE
+        y_want = oracle.grouped_gemm(h.cpu(), q2[0].cpu(), q2[1].cpu(), q2[2].cpu(), mi, hidden)
+        assert rel_l2(y.cpu(), y_want) < REL_L2_VS_ORACLE

@@ -125,3 +125,82 @@ def test_c_abi_validation_without_gpu():
                                            None, None, None)
     assert rc == 0                                          # M == 0 returns silently
     assert lib.nvfp4_quantize_weight(None, 0, 1, 4, 96, None, None, None, None) == 1
+
+
+def test_new_entry_points_validate_without_gpu():
+    lib = nvfp4_gemm._C.lib()
+    # masked layout: max_m must be a multiple of 128, N of 256
+    rc = lib.nvfp4_grouped_gemm_masked(None, 0, None, None, None, None, 0, None, 4, 100, 256, 128, 0, 1, 0, None, None, None)
+    assert rc == 1 and b"max_m" in lib.nvfp4_last_error()
+    rc = lib.nvfp4_grouped_gemm_masked(None, 0, None, None, None, None, 0, None, 4, 128, 128, 128, 0, 1, 0, None, None, None)
+    assert rc == 1 and b"256" in lib.nvfp4_last_error()
+    assert lib.nvfp4_grouped_gemm_masked(None, 0, None, None, None, None, 0, None, 0, 128, 256, 128, 0, 1, 0, None, None, None) == 0
+    # unknown scale policy is an argument error now that all four policies exist
+    rc = lib.nvfp4_grouped_gemm_contiguous(ctypes.c_void_p(16), 256, ctypes.c_void_p(16), ctypes.c_void_p(16), ctypes.c_void_p(16),
+                                           ctypes.c_void_p(16), 128, ctypes.c_void_p(16), 128, 128, 256, 1, 7, 1, 0, 0, None, None, None)
+    assert rc == 1 and b"scale policy" in lib.nvfp4_last_error()
+    # checkpoint loader: part count and K
+    assert lib.nvfp4_load_checkpoint_weights(0, None, None, None, None, 1, 1, 64, None, None, None, None) == 1
+    assert lib.nvfp4_load_checkpoint_weights(9, None, None, None, None, 1, 1, 64, None, None, None, None) == 1
+    assert lib.nvfp4_read_status(None, None, None) == 1
+    assert lib.nvfp4_debug_wait_timeout(0, None, None) == 1
+
+
+def test_operands_must_share_one_device():
+    """The wrappers launch on the device that holds the operands; tensors spread over devices are refused before any
+    pointer reaches the library (checked here with stand-ins that only carry what the check reads)."""
+    from unittest import mock
+    from nvfp4_gemm import _C
+
+    def fake(index):
+        t = mock.MagicMock(spec=torch.Tensor)
+        t.is_cuda = True
+        t.device = torch.device("cuda", index)
+        return t
+
+    assert _C._one_device(fake(1), None, fake(1)) == torch.device("cuda", 1)
+    with pytest.raises(RuntimeError, match="one device"):
+        _C._one_device(fake(0), fake(1))
+    with pytest.raises(RuntimeError, match="CUDA tensor"):
+        _C._one_device(torch.zeros(1))
+
+
+def test_oracle_radix_policies_follow_the_kernel_constants(oracle):
+    """derived_div4 and div4_radix8 exist only in the reference's kernel (include/nvfp4_gemm/transform/dual_nvfp4.cuh:31-61
+    there); the oracle states them in the emulation's operation order.  Known answers by hand for one block."""
+    x = torch.zeros(1, 16)
+    x[0, :4] = torch.tensor([6.0, 2.75, -0.3125, 1.0])
+    q0, q1, s0, s1 = oracle.decompose(x.to(torch.bfloat16), "derived_div4")
+    # amax 6 -> s0 = 1 (0x38), s1 = Q(1/4) = 0x28; u = x: q0 = {6, 3 (2.75 -> 3), -0.5 (0.3125 -> 0.5), 1}
+    assert s0[0, 0] == 0x38 and s1[0, 0] == 0x28
+    assert oracle.e2m1_decode(q0[0, :4]).tolist() == [6.0, 3.0, -0.5, 1.0]
+    # residual x4: (2.75 - 3) * 4 = -1 ; (-0.3125 + 0.5) * 4 = 0.75 -> tie to 1.0
+    assert oracle.e2m1_decode(q1[0, :4]).tolist() == [0.0, -1.0, 1.0, 0.0]
+    q0, q1, s0, s1 = oracle.decompose(x.to(torch.bfloat16), "div4_radix8")
+    # s0 = Q(6 / 4) = 1.5 (0x3c), s1 = Q(1.5 / 8) = 0.1875 (0x24); u = x / 1.5 = {4, 1.8333, -0.20833, 0.6667}
+    assert s0[0, 0] == 0x3c and s1[0, 0] == 0x24
+    assert oracle.e2m1_decode(q0[0, :4]).tolist() == [4.0, 2.0, -0.0, 0.5]
+    # residual x8: (1.8333 - 2) * 8 = -1.333 -> -1.5 ; -0.20833 * 8 = -1.667 -> -1.5 ; (0.6667 - 0.5) * 8 = 1.333 -> 1.5
+    assert oracle.e2m1_decode(q1[0, :4]).tolist() == [0.0, -1.5, -1.5, 1.5]
+    # both give a usable reconstruction on Gaussian data
+    g = torch.Generator().manual_seed(0)
+    a = torch.randn(64, 256, generator=g).to(torch.bfloat16)
+    for policy in ("derived_div4", "div4_radix8"):
+        q0, q1, s0, s1 = oracle.decompose(a, policy)
+        rec = (oracle.e2m1_decode(q0) * oracle.e4m3_decode(s0).repeat_interleave(16, dim=1) +
+               oracle.e2m1_decode(q1) * oracle.e4m3_decode(s1).repeat_interleave(16, dim=1))
+        assert float((rec - a.float()).norm() / a.float().norm()) < 0.02
+
+
+def test_checkpoint_restatement_single_part_is_identity(oracle):
+    from oracle import checkpoint
+    g = torch.Generator().manual_seed(1)
+    e, n, k = 2, 64, 128
+    w = (torch.randn(e, n, k, generator=g) * 0.02).to(torch.bfloat16)
+    b, sfb, gw = oracle.quantize_weight(w)
+    part = (b.view(torch.uint8).reshape(e, n, k // 2), layout.unpack_sf_atoms(sfb, e), gw)
+    assert torch.equal(layout.pack_sf_atoms(layout.unpack_sf_atoms(sfb, e)), sfb)
+    ob, osfb, ogw = checkpoint.load_checkpoint_weights([part], global_scale_is_divisor=False)
+    assert torch.equal(ob, b) and torch.equal(osfb, sfb) and torch.equal(ogw, gw)
+    with pytest.raises(RuntimeError):                      # the loader itself is GPU-only: no CPU path
+        nvfp4_gemm.load_checkpoint_weights_nvfp4([part])
