@@ -419,7 +419,7 @@ def split_default(case, extra) -> bool:
     """Whether the dispatcher (csrc/abi.cu) sends this call to the two-kernel split path."""
     fused_knobs = any(extra.get(k, 0) for k in ("tune_cluster", "tune_transform_warps", "tune_direct_a"))
     mode = extra.get("tune_split_transform", 0)
-    return (not case["swap"]) and case["N"] % 256 == 0 and (mode == 1 or (mode == 0 and not fused_knobs and case["N"] >= 1024))
+    return (not case["swap"]) and case["N"] % 256 == 0 and (mode == 1 or (mode == 0 and not fused_knobs and case["N"] > 1024))
 
 
 def gemm_record(case, dev, steps, warmup, fp4_peak, graph=False, extra=None, sample_clocks=True, local=0):
@@ -523,8 +523,10 @@ def also_records(dev, fp4_peak, local, budget_s=120.0):
         entry = {"us": rec["ms_per_step"] * 1e3, "value": rec["value"], "frac": rec["frac"], "bound": rec["roofline"]["bound"],
                  "cosine_vs_fp32": rec["cosine_vs_fp32"]}
         if not case["swap"]:
-            ns, _, _ = gemm_record(case, dev, 100, 3, fp4_peak, graph=True, extra=dict(tune_split_transform=2), sample_clocks=False)
-            entry["fused_us"] = ns["ms_per_step"] * 1e3
+            other = 1 if rec["kernels_per_step"] == 1 else 2         # the path the dispatcher did not take
+            ns, _, _ = gemm_record(case, dev, 100, 3, fp4_peak, graph=True, extra=dict(tune_split_transform=other), sample_clocks=False)
+            entry["path"] = "fused" if rec["kernels_per_step"] == 1 else "split"
+            entry["fused_us" if other == 2 else "split_us"] = ns["ms_per_step"] * 1e3
         sweep[name] = entry
         del case
     out["ref_sweep"] = {"timing": "CUDA-graph replay of one call, 100 replays (the reference's method)", "unit": "us per call",

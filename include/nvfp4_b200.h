@@ -203,27 +203,48 @@ NVFP4_API int nvfp4_combine_rows(const void* rows, int64_t rows_ld_elems, const 
  * nvfp4_dispatch_rows_peer: for i < n_rows, row src[(src_idx ? src_idx[i] : i) / src_div] is stored into row dst_row[i] of
  *   rank dst_rank[i]'s buffer (gather + all-to-all + scatter in one pass of plain stores).  The caller orders
  *   it after every rank has finished reading its buffer and tells the peers when the stores are complete.
+ *   A pair with dst_rank outside [0, world) or dst_row outside [0, rows_cap) is skipped; row -1 is the plan's mark
+ *   for "does not fit", anything else out of range also ORs bit 3 into *device_status (may be NULL).
  * nvfp4_combine_rows_peer: y[t] = sum over j < k of w[t*k+j] * (row src_row[t*k+j] of rank src_rank[t*k+j]'s
  *   buffer), read with plain loads over NVLink.  The caller orders it after every rank has written its buffer.
+ *   Pairs out of range (as above) contribute nothing.
+ * Precondition of both plans: expert ids lie in [0, num_experts); ids outside are ignored by the histogram, get no
+ *   row and are skipped by the two movers.
  *
  * nvfp4_expert_histogram: counts[e] = number of i < n with ids[i] == e, for e < num_experts <= 4096 (ids outside
  *   the range are ignored); what every rank all-gathers before the plan.
- * nvfp4_plan_peer: the routing plan of that path.  all_counts[s * E + e] = pairs rank s routes to expert e (the
- *   all-gathered histograms), ids[p] = expert of this rank's pair p (p = token * k + choice), n pairs.  Writes
- *   base[e] (E entries: the row of the owner's buffer where this rank's rows of expert e start), sizes
- *   (2 * E / world + 1 entries: padded rows per local expert, real rows per local expert, the largest padded total
- *   over all ranks) and dst_row[p] (n entries: base[e] + the number of earlier pairs of this rank routed to e).
- *   Experts are padded to `alignment` rows; E % world == 0, E <= 4096. */
+ *   (the routing plan built from the gathered histograms is nvfp4_plan_peer_masked below) */
 NVFP4_API int nvfp4_expert_histogram(const int64_t* ids, int64_t n, int num_experts, int64_t* counts, void* stream);
-NVFP4_API int nvfp4_plan_peer(const int64_t* all_counts, int world, int num_experts, int rank, int alignment,
-                              const int64_t* ids, int64_t n, int64_t* base, int64_t* sizes, int64_t* dst_row,
-                              void* stream);
 NVFP4_API int nvfp4_dispatch_rows_peer(const void* src, int64_t src_ld_bytes, const int64_t* src_idx, int src_div,
                                        const int64_t* peers, const int64_t* dst_rank, const int64_t* dst_row,
-                                       int64_t n_rows, int row_bytes, int64_t dst_ld_bytes, void* stream);
+                                       int64_t n_rows, int row_bytes, int64_t dst_ld_bytes, int world, int64_t rows_cap,
+                                       int32_t* device_status, void* stream);
 NVFP4_API int nvfp4_combine_rows_peer(const int64_t* peers, int64_t rows_ld_elems, const int64_t* src_rank,
                                       const int64_t* src_row, const float* w, int64_t tokens, int k, int hidden,
-                                      void* y, int64_t y_ld_elems, void* stream);
+                                      void* y, int64_t y_ld_elems, int world, int64_t rows_cap, void* stream);
+
+/* The routing plan for the masked layout (nvfp4_grouped_gemm_masked): every local expert owns cap_m rows of its
+ * rank's buffer, so nothing about the plan has to come back to the host.  all_counts[s * E + e] = pairs rank s routes
+ * to expert e (the all-gathered histograms), ids[p] = expert of this rank's pair p (p = token * k + choice), n pairs,
+ * E % world == 0, E <= 4096.  From these it writes
+ *   base[e], limit[e] (E entries each: first row of this rank's pairs of expert e in the owner's buffer, end of that
+ *   expert's cap_m rows), masked_m[j] (E / world int32: real rows of local expert j, clamped to cap_m -- the GEMM's
+ *   row counts) and dst_row[p] (n entries; -1 for a pair that does not fit its expert's capacity).
+ * If any expert of any rank receives more than cap_m rows, bit 2 of *device_status is set -- on every rank alike,
+ * since all see the same histograms; the step's result is then incomplete and the caller repeats it another way.
+ * cap_m % 128 == 0.  No counterpart in the reference.
+ *
+ * nvfp4_peer_barrier: a barrier over the ranks of one NVLink domain whose wait is bounded.  flag_peers[r] is the
+ * address, in this process, of rank r's flag array: int64 [NVFP4_BARRIER_SLOTS][world] in symmetric memory, zero
+ * before the first use.  Every rank calls it with the same slot and the same epoch, epochs growing by one per call
+ * and slot.  A rank whose peers do not arrive within budget_cycles clock cycles ORs bit 1 into *device_status and
+ * carries on: the kernel never traps and never spins for ever; the host reads the status word after the step. */
+#define NVFP4_BARRIER_SLOTS 8
+NVFP4_API int nvfp4_plan_peer_masked(const int64_t* all_counts, int world, int num_experts, int rank, int cap_m,
+                                     const int64_t* ids, int64_t n, int64_t* base, int64_t* limit, int32_t* masked_m,
+                                     int64_t* dst_row, int32_t* device_status, void* stream);
+NVFP4_API int nvfp4_peer_barrier(const int64_t* flag_peers, int rank, int world, int slot, int64_t epoch,
+                                 int64_t budget_cycles, int32_t* device_status, void* stream);
 
 /* Test hook: Algorithm 1 exactly as the GEMM's transform warps run it (same device
  * code, same shared-memory layouts), with the codes copied out instead of being fed to

@@ -29,9 +29,10 @@ TUNE_KEYS = ("tune_block_n", "tune_transform_warps", "tune_epilogue_threads", "t
 EXPORTS = ("nvfp4_last_error", "nvfp4_version", "nvfp4_get_num_sms", "nvfp4_set_num_sms",
            "nvfp4_quantize_weight", "nvfp4_quantize_weight_static", "nvfp4_grouped_gemm_contiguous", "nvfp4_debug_decompose",
            "nvfp4_debug_mma_peak", "nvfp4_debug_mma_pattern", "nvfp4_permute_rows", "nvfp4_swiglu", "nvfp4_combine_rows",
-           "nvfp4_dispatch_rows_peer", "nvfp4_combine_rows_peer", "nvfp4_plan_peer", "nvfp4_expert_histogram",
+           "nvfp4_dispatch_rows_peer", "nvfp4_combine_rows_peer", "nvfp4_expert_histogram",
            "nvfp4_grouped_gemm_swiglu_contiguous", "nvfp4_grouped_gemm_masked", "nvfp4_load_checkpoint_weights",
-           "nvfp4_read_status", "nvfp4_debug_split_workspace", "nvfp4_debug_wait_timeout")
+           "nvfp4_read_status", "nvfp4_debug_split_workspace", "nvfp4_debug_wait_timeout", "nvfp4_plan_peer_masked",
+           "nvfp4_peer_barrier")
 
 
 def library_path() -> str:
@@ -59,11 +60,12 @@ def lib() -> ctypes.CDLL:
         L.nvfp4_debug_decompose.argtypes = [vp, i64, i32, i32, i32, vp, vp, vp, vp, vp]
         L.nvfp4_permute_rows.argtypes = [vp, i64, vp, i32, vp, i64, i32, vp, i64, vp]
         L.nvfp4_swiglu.argtypes = [vp, i64, i64, i32, vp, i64, vp]
-        L.nvfp4_dispatch_rows_peer.argtypes = [vp, i64, vp, i32, vp, vp, vp, i64, i32, i64, vp]
+        L.nvfp4_dispatch_rows_peer.argtypes = [vp, i64, vp, i32, vp, vp, vp, i64, i32, i64, i32, i64, vp, vp]
+        L.nvfp4_plan_peer_masked.argtypes = [vp, i32, i32, i32, i32, vp, i64, vp, vp, vp, vp, vp, vp]
+        L.nvfp4_peer_barrier.argtypes = [vp, i32, i32, i32, i64, i64, vp, vp]
         L.nvfp4_expert_histogram.argtypes = [vp, i64, i32, vp, vp]
         L.nvfp4_grouped_gemm_swiglu_contiguous.argtypes = [vp, i64, vp, vp, vp, vp, i64, vp, i32, i32, i32, i32, i32, vp, vp, vp]
-        L.nvfp4_plan_peer.argtypes = [vp, i32, i32, i32, i32, vp, i64, vp, vp, vp, vp]
-        L.nvfp4_combine_rows_peer.argtypes = [vp, i64, vp, vp, vp, i64, i32, i32, vp, i64, vp]
+        L.nvfp4_combine_rows_peer.argtypes = [vp, i64, vp, vp, vp, i64, i32, i32, vp, i64, i32, i64, vp]
         L.nvfp4_combine_rows.argtypes = [vp, i64, vp, vp, i64, i32, i32, vp, i64, vp]
         L.nvfp4_grouped_gemm_masked.argtypes = [vp, i64, vp, vp, vp, vp, i64, vp, i32, i32, i32, i32, i32, i32, i32, vp, vp, vp]
         L.nvfp4_load_checkpoint_weights.argtypes = [i32, vp, vp, vp, vp, i32, i32, i32, vp, vp, vp, vp]
@@ -363,46 +365,57 @@ def expert_histogram(ids: torch.Tensor, num_experts: int) -> torch.Tensor:
     return counts
 
 
-def plan_peer(all_counts: torch.Tensor, ids: torch.Tensor, world: int, rank: int, alignment: int):
-    """Routing plan of the peer-memory path from the all-gathered (rank, expert) histograms; returns
-    (sizes, dst_row): sizes = int64 tensor [padded rows per local expert..., real rows per local expert...,
-    largest padded total over the ranks], dst_row[p] = row of pair p in its owner's buffer."""
+def plan_peer_masked(all_counts: torch.Tensor, ids: torch.Tensor, world: int, rank: int, cap_m: int, status: torch.Tensor):
+    """Routing plan for the masked layout; returns (masked_m int32 (E / world,), dst_row int64 (pairs,)), all on the
+    device.  Overflow of an expert's capacity sets bit 2 of ``status``."""
     num_experts = all_counts.numel() // world
     _require(_i64_ok(all_counts, world * num_experts) and _i64_ok(ids, ids.numel()), "counts and ids are contiguous int64 CUDA tensors")
-    base = torch.empty(num_experts, dtype=torch.int64, device=ids.device)
-    sizes = torch.empty(2 * (num_experts // world) + 1, dtype=torch.int64, device=ids.device)
-    dst_row = torch.empty(ids.numel(), dtype=torch.int64, device=ids.device)
-    with torch.cuda.device(_one_device(all_counts, ids)):
-        _check(lib().nvfp4_plan_peer(all_counts.data_ptr(), world, num_experts, rank, alignment, ids.data_ptr(), ids.numel(),
-                                     base.data_ptr(), sizes.data_ptr(), dst_row.data_ptr(), _stream()))
-    return sizes, dst_row
+    dev = _one_device(all_counts, ids, status)
+    base = torch.empty(num_experts, dtype=torch.int64, device=dev)
+    limit = torch.empty(num_experts, dtype=torch.int64, device=dev)
+    masked_m = torch.empty(num_experts // world, dtype=torch.int32, device=dev)
+    dst_row = torch.empty(ids.numel(), dtype=torch.int64, device=dev)
+    with torch.cuda.device(dev):
+        _check(lib().nvfp4_plan_peer_masked(all_counts.data_ptr(), world, num_experts, rank, cap_m, ids.data_ptr(), ids.numel(),
+                                            base.data_ptr(), limit.data_ptr(), masked_m.data_ptr(), dst_row.data_ptr(),
+                                            status.data_ptr(), _stream()))
+    return masked_m, dst_row
+
+
+def peer_barrier(flag_peers: torch.Tensor, rank: int, world: int, slot: int, epoch: int, status: torch.Tensor,
+                 budget_cycles: int = 2_000_000_000) -> None:
+    """Bounded barrier over the ranks whose flag arrays ``flag_peers`` lists (see the header)."""
+    with torch.cuda.device(_one_device(flag_peers, status)):
+        _check(lib().nvfp4_peer_barrier(flag_peers.data_ptr(), rank, world, slot, epoch, budget_cycles, status.data_ptr(), _stream()))
 
 
 def dispatch_rows_peer(src: torch.Tensor, src_idx, src_div: int, peers: torch.Tensor, dst_rank: torch.Tensor,
-                       dst_row: torch.Tensor, dst_ld_elems: int) -> None:
+                       dst_row: torch.Tensor, dst_ld_elems: int, rows_cap: int, status: torch.Tensor = None) -> None:
     """Row src[(src_idx[i] or i) // src_div] -> row dst_row[i] of rank dst_rank[i]'s buffer (`peers`: int64 base
-    addresses)."""
+    addresses, `rows_cap` rows each); pairs out of range are skipped."""
     n = dst_row.numel()
     _require(_rows_ok(src), "src is a 2-D BF16 CUDA tensor")
     _require((src_idx is None or _i64_ok(src_idx, n)) and _i64_ok(dst_rank, n) and _i64_ok(dst_row, n) and _i64_ok(peers, 1),
              "indices and peer addresses are contiguous int64 CUDA tensors")
-    with torch.cuda.device(_one_device(src, src_idx, peers, dst_rank, dst_row)):
+    with torch.cuda.device(_one_device(src, src_idx, peers, dst_rank, dst_row, status)):
         _check(lib().nvfp4_dispatch_rows_peer(src.data_ptr(), src.stride(0) * 2, src_idx.data_ptr() if src_idx is not None else None,
-                                              src_div, peers.data_ptr(),
-                                              dst_rank.data_ptr(), dst_row.data_ptr(), n, src.shape[1] * 2, dst_ld_elems * 2, _stream()))
+                                              src_div, peers.data_ptr(), dst_rank.data_ptr(), dst_row.data_ptr(), n, src.shape[1] * 2,
+                                              dst_ld_elems * 2, peers.numel(), rows_cap,
+                                              status.data_ptr() if status is not None else None, _stream()))
 
 
 def combine_rows_peer(peers: torch.Tensor, rows_ld_elems: int, src_rank: torch.Tensor, src_row: torch.Tensor, w: torch.Tensor,
-                      tokens: int, hidden: int) -> torch.Tensor:
-    """y[t] = sum_j w[t, j] * (row src_row[t, j] of rank src_rank[t, j]'s buffer), BF16 out."""
+                      tokens: int, hidden: int, rows_cap: int, out: torch.Tensor = None) -> torch.Tensor:
+    """y[t] = sum_j w[t, j] * (row src_row[t, j] of rank src_rank[t, j]'s buffer), BF16, into `out` if given."""
     n = src_rank.numel()
     _require(_i64_ok(src_rank, n) and _i64_ok(src_row, n) and _i64_ok(peers, 1) and w.is_cuda and w.dtype == torch.float32 and
              w.is_contiguous() and w.numel() == n and n % max(tokens, 1) == 0, "bad index / weight tensors")
-    y = torch.empty(tokens, hidden, dtype=torch.bfloat16, device=w.device)
+    _require(out is None or (_rows_ok(out) and out.shape == (tokens, hidden)), "out is a (tokens, hidden) BF16 CUDA tensor")
+    y = out if out is not None else torch.empty(tokens, hidden, dtype=torch.bfloat16, device=w.device)
     k = n // tokens if tokens else 1
     with torch.cuda.device(_one_device(peers, src_rank, src_row, w)):
         _check(lib().nvfp4_combine_rows_peer(peers.data_ptr(), rows_ld_elems, src_rank.data_ptr(), src_row.data_ptr(), w.data_ptr(),
-                                             tokens, k, hidden, y.data_ptr(), y.stride(0), _stream()))
+                                             tokens, k, hidden, y.data_ptr(), y.stride(0), peers.numel(), rows_cap, _stream()))
     return y
 
 

@@ -137,8 +137,8 @@ int encode_tensor_map_2d(CUtensorMap* map, CUtensorMapDataType dtype, uint32_t e
 
 using namespace nvfp4;
 
-// cluster size the dispatcher picks when the caller leaves tune_cluster at 0
-static constexpr int kDefaultCluster = 2;
+
+
 
 extern "C" {
 
@@ -260,10 +260,12 @@ int nvfp4_grouped_gemm_contiguous(const void* a, int64_t lda_elems, const void* 
     const bool pdl = !(tune && tune[11]);                           // tune_no_pdl
     NVFP4_REQUIRE(tune_split >= 0 && tune_split <= 2, "tune_split_transform must be 0, 1 or 2");
     NVFP4_REQUIRE(tune_split != 1 || N % 256 == 0, "tune_split_transform=1 needs N %% 256 == 0 (N=%d)", N);
-    // The library's choice: the separate pass wins as soon as an activation tile is visited by several column
-    // tiles (N >= 1024); explicit fused-kernel knobs (cluster, transform warps, direct A) keep the fused kernels.
+    // The library's choice: a cluster of the fused kernel spans 1024 (512) columns, so up to there an activation tile is
+    // transformed once either way and the fused kernel saves the workspace round trip (measured 10 % faster at N = 1024,
+    // K = 2048); on wider layers the fused kernel repeats Algorithm 1 per column span and the separate pass wins.
+    // Explicit fused-kernel knobs (cluster, transform warps, direct A) keep the fused kernels.
     const bool fused_knobs = tune && (tune[8] != 0 || tune[1] != 0 || tune[9] != 0);
-    if (tune_split == 1 || (tune_split == 0 && !fused_knobs && N % 256 == 0 && N >= 1024)) {
+    if (tune_split == 1 || (tune_split == 0 && !fused_knobs && N % 256 == 0 && N > 1024)) {
         const int tune_block_k = tune ? tune[5] : 0;
         return launch_gemm_split(a, lda_elems, b, sfb, gw, d, ldd_elems, m_indices, nullptr, 0, M, N, K, E,
                                  enable_residual_pass != 0, tune_block_k, tune_sched_group, pdl, scale_policy, false,
@@ -465,50 +467,65 @@ int nvfp4_expert_histogram(const int64_t* ids, int64_t n, int num_experts, int64
     return launch_expert_histogram(ids, n, num_experts, counts, static_cast<cudaStream_t>(stream));
 }
 
-int nvfp4_plan_peer(const int64_t* all_counts, int world, int num_experts, int rank, int alignment, const int64_t* ids, int64_t n,
-                    int64_t* base, int64_t* sizes, int64_t* dst_row, void* stream)
+int nvfp4_plan_peer_masked(const int64_t* all_counts, int world, int num_experts, int rank, int cap_m, const int64_t* ids,
+                           int64_t n, int64_t* base, int64_t* limit, int32_t* masked_m, int64_t* dst_row, int32_t* device_status,
+                           void* stream)
 {
     host::clear_error();
     NVFP4_REQUIRE(world >= 1 && num_experts >= 1 && num_experts <= 4096 && num_experts % world == 0,
                   "num_experts (%d) must be in [1, 4096] and a multiple of world (%d)", num_experts, world);
-    NVFP4_REQUIRE(rank >= 0 && rank < world && alignment >= 1 && n >= 0, "bad rank / alignment / pair count");
-    NVFP4_REQUIRE(all_counts && base && sizes && (n == 0 || (ids && dst_row)), "null pointer argument");
-    return launch_plan_peer(all_counts, world, num_experts, rank, alignment, ids, n, base, sizes, dst_row,
-                            static_cast<cudaStream_t>(stream));
+    NVFP4_REQUIRE(rank >= 0 && rank < world && cap_m >= 128 && cap_m % 128 == 0 && n >= 0, "bad rank / capacity / pair count");
+    NVFP4_REQUIRE(all_counts && base && limit && masked_m && (n == 0 || (ids && dst_row)), "null pointer argument");
+    return launch_plan_peer_masked(all_counts, world, num_experts, rank, cap_m, ids, n, base, limit, masked_m, dst_row, device_status,
+                                   static_cast<cudaStream_t>(stream));
+}
+
+int nvfp4_peer_barrier(const int64_t* flag_peers, int rank, int world, int slot, int64_t epoch, int64_t budget_cycles,
+                       int32_t* device_status, void* stream)
+{
+    host::clear_error();
+    NVFP4_REQUIRE(world >= 1 && world <= 64 && rank >= 0 && rank < world, "world (%d) must be in [1, 64] and rank (%d) inside it", world, rank);
+    NVFP4_REQUIRE(slot >= 0 && slot < NVFP4_BARRIER_SLOTS && epoch > 0, "slot (%d) must be in [0, %d) and epoch positive", slot,
+                  NVFP4_BARRIER_SLOTS);
+    NVFP4_REQUIRE(budget_cycles > 0 && budget_cycles <= 4000000000ll, "budget_cycles outside (0, 4e9]");
+    NVFP4_REQUIRE(flag_peers != nullptr, "null pointer argument");
+    return launch_peer_barrier(flag_peers, rank, world, slot, epoch, budget_cycles, device_status, static_cast<cudaStream_t>(stream));
 }
 
 int nvfp4_dispatch_rows_peer(const void* src, int64_t src_ld_bytes, const int64_t* src_idx, int src_div, const int64_t* peers,
                              const int64_t* dst_rank, const int64_t* dst_row, int64_t n_rows, int row_bytes, int64_t dst_ld_bytes,
-                             void* stream)
+                             int world, int64_t rows_cap, int32_t* device_status, void* stream)
 {
     host::clear_error();
     NVFP4_REQUIRE(n_rows >= 0 && row_bytes > 0 && row_bytes % 16 == 0, "row_bytes must be a positive multiple of 16 (got %d)", row_bytes);
     if (n_rows == 0) return NVFP4_OK;
     NVFP4_REQUIRE(src && peers && dst_rank && dst_row, "null pointer argument");
-    NVFP4_REQUIRE(src_div >= 1, "src_div must be at least 1");
+    NVFP4_REQUIRE(src_div >= 1 && world >= 1 && rows_cap >= 0, "src_div and world must be at least 1, rows_cap non-negative");
     NVFP4_REQUIRE(src_ld_bytes % 16 == 0 && dst_ld_bytes % 16 == 0 && src_ld_bytes >= row_bytes && dst_ld_bytes >= row_bytes,
                   "row strides must be multiples of 16 bytes and at least row_bytes");
     NVFP4_REQUIRE((reinterpret_cast<uintptr_t>(src) & 15u) == 0, "rows must be 16-byte aligned");
     host::DeviceInfo* dev;
     if (int rc = host::device_info(-1, &dev)) return rc;
     return launch_dispatch_rows_peer(src, src_ld_bytes, src_idx, src_div, peers, dst_rank, dst_row, n_rows, row_bytes, dst_ld_bytes,
-                                     dev->hw_sms, static_cast<cudaStream_t>(stream));
+                                     world, rows_cap, device_status, dev->num_sms, static_cast<cudaStream_t>(stream));
 }
 
 int nvfp4_combine_rows_peer(const int64_t* peers, int64_t rows_ld_elems, const int64_t* src_rank, const int64_t* src_row,
-                            const float* w, int64_t tokens, int k, int hidden, void* y, int64_t y_ld_elems, void* stream)
+                            const float* w, int64_t tokens, int k, int hidden, void* y, int64_t y_ld_elems, int world,
+                            int64_t rows_cap, void* stream)
 {
     host::clear_error();
     NVFP4_REQUIRE(tokens >= 0 && k >= 1 && hidden > 0 && hidden % 8 == 0, "k >= 1 and hidden a positive multiple of 8 (k=%d, hidden=%d)", k, hidden);
     if (tokens == 0) return NVFP4_OK;
     NVFP4_REQUIRE(peers && src_rank && src_row && w && y, "null pointer argument");
+    NVFP4_REQUIRE(world >= 1 && rows_cap >= 0, "world must be at least 1, rows_cap non-negative");
     NVFP4_REQUIRE(rows_ld_elems % 8 == 0 && y_ld_elems % 8 == 0 && rows_ld_elems >= hidden && y_ld_elems >= hidden,
                   "row strides must be multiples of 8 elements and cover the row");
     NVFP4_REQUIRE((reinterpret_cast<uintptr_t>(y) & 15u) == 0, "rows must be 16-byte aligned");
     host::DeviceInfo* dev;
     if (int rc = host::device_info(-1, &dev)) return rc;
-    return launch_combine_rows_peer(peers, rows_ld_elems, src_rank, src_row, w, tokens, k, hidden, y, y_ld_elems, dev->hw_sms,
-                                    static_cast<cudaStream_t>(stream));
+    return launch_combine_rows_peer(peers, rows_ld_elems, src_rank, src_row, w, tokens, k, hidden, y, y_ld_elems, world, rows_cap,
+                                    dev->num_sms, static_cast<cudaStream_t>(stream));
 }
 
 int nvfp4_debug_decompose(const void* a, int64_t lda_elems, int M, int K, int scale_policy, void* q0, void* q1,

@@ -32,14 +32,17 @@ int launch_combine_rows(const void* rows, int64_t rows_ld_elems, const int64_t* 
                         int hidden, void* y, int64_t y_ld_elems, int num_sms, cudaStream_t stream);
 
 int launch_expert_histogram(const int64_t* ids, int64_t n, int num_experts, int64_t* counts, cudaStream_t stream);
-int launch_plan_peer(const int64_t* all_counts, int world, int num_experts, int rank, int alignment, const int64_t* ids,
-                     int64_t n, int64_t* base, int64_t* sizes, int64_t* dst_row, cudaStream_t stream);
+int launch_plan_peer_masked(const int64_t* all_counts, int world, int num_experts, int rank, int cap_m, const int64_t* ids,
+                            int64_t n, int64_t* base, int64_t* limit, int32_t* masked_m, int64_t* dst_row, int32_t* status,
+                            cudaStream_t stream);
+int launch_peer_barrier(const int64_t* flag_peers, int rank, int world, int slot, int64_t epoch, int64_t budget_cycles,
+                        int32_t* status, cudaStream_t stream);
 int launch_dispatch_rows_peer(const void* src, int64_t src_ld_bytes, const int64_t* src_idx, int src_div, const int64_t* peers,
                               const int64_t* dst_rank, const int64_t* dst_row, int64_t n_rows, int row_bytes,
-                              int64_t dst_ld_bytes, int num_sms, cudaStream_t stream);
+                              int64_t dst_ld_bytes, int world, int64_t rows_cap, int32_t* status, int num_sms, cudaStream_t stream);
 int launch_combine_rows_peer(const int64_t* peers, int64_t rows_ld_elems, const int64_t* src_rank, const int64_t* src_row,
-                             const float* w, int64_t tokens, int k, int hidden, void* y, int64_t y_ld_elems, int num_sms,
-                             cudaStream_t stream);
+                             const float* w, int64_t tokens, int k, int hidden, void* y, int64_t y_ld_elems, int world,
+                             int64_t rows_cap, int num_sms, cudaStream_t stream);
 
 int launch_gemm_swap(const void* a, int64_t lda, const void* b, const void* sfb, const float* gw, void* d,
                      int64_t ldd, const int32_t* m_indices, int M, int N, int K, int E, bool residual,

@@ -9,6 +9,8 @@
 // The reference project has no multi-GPU mode; these have no counterpart there.
 #include <cuda_bf16.h>
 
+#include <cstdint>
+
 #include "host_common.hpp"
 #include "launchers.hpp"
 
@@ -91,14 +93,22 @@ combine_rows_kernel(const uint4* __restrict__ rows, int64_t rows_ld16, const int
 // dispatch: row i of the send order (token src_idx[i] / src_div) is stored straight into row dst_row[i] of rank
 // dst_rank[i]'s expert-major buffer -- the gather, the all-to-all and the scatter in one pass, every byte
 // crossing NVLink once as plain 16-byte stores.
+// A pair whose rank or row is outside [0, world) x [0, rows_cap) is skipped (row -1 is how the plan marks a pair that
+// does not fit its expert's capacity; anything else out of range also raises bit 3 of the status word).
 __global__ void __launch_bounds__(256)
 dispatch_rows_peer_kernel(const uint4* __restrict__ src, int64_t src_ld16, const int64_t* __restrict__ src_idx, int src_div,
                           const int64_t* __restrict__ peers, const int64_t* __restrict__ dst_rank,
-                          const int64_t* __restrict__ dst_row, int64_t n_rows, int row16, int64_t dst_ld16)
+                          const int64_t* __restrict__ dst_row, int64_t n_rows, int row16, int64_t dst_ld16, int world,
+                          int64_t rows_cap, int32_t* __restrict__ status)
 {
     for (int64_t i = blockIdx.x; i < n_rows; i += gridDim.x) {
+        const int64_t r = dst_rank[i], row = dst_row[i];
+        if (r < 0 || r >= world || row < 0 || row >= rows_cap) {
+            if (row != -1 && threadIdx.x == 0 && status != nullptr) atomicOr(status, 8);
+            continue;
+        }
         const uint4* sp = src + ((src_idx ? src_idx[i] : i) / src_div) * src_ld16;
-        uint4* dp = reinterpret_cast<uint4*>(peers[dst_rank[i]]) + dst_row[i] * dst_ld16;
+        uint4* dp = reinterpret_cast<uint4*>(peers[r]) + row * dst_ld16;
         for (int c = threadIdx.x; c < row16; c += blockDim.x) dp[c] = __ldg(sp + c);
     }
 }
@@ -108,7 +118,7 @@ dispatch_rows_peer_kernel(const uint4* __restrict__ src, int64_t src_ld16, const
 __global__ void __launch_bounds__(256)
 combine_rows_peer_kernel(const int64_t* __restrict__ peers, int64_t rows_ld16, const int64_t* __restrict__ src_rank,
                          const int64_t* __restrict__ src_row, const float* __restrict__ w, int64_t tokens, int k, int row16,
-                         uint4* __restrict__ y, int64_t y_ld16)
+                         uint4* __restrict__ y, int64_t y_ld16, int world, int64_t rows_cap)
 {
     for (int64_t t = blockIdx.x; t < tokens; t += gridDim.x) {
         for (int c = threadIdx.x; c < row16; c += blockDim.x) {
@@ -121,10 +131,15 @@ combine_rows_peer_kernel(const int64_t* __restrict__ peers, int64_t rows_ld16, c
 #pragma unroll
                 for (int u = 0; u < 4; ++u) {
                     const int j = j0 + u < k ? j0 + u : k - 1;
-                    wj[u] = j0 + u < k ? w[t * k + j] : 0.0f;
-                    const uint4* row = reinterpret_cast<const uint4*>(peers[src_rank[t * k + j]]) + src_row[t * k + j] * rows_ld16;
-                    asm volatile("ld.global.relaxed.sys.v4.u32 {%0, %1, %2, %3}, [%4];"
-                                 : "=r"(v[u].x), "=r"(v[u].y), "=r"(v[u].z), "=r"(v[u].w) : "l"(row + c));
+                    const int64_t pr = src_rank[t * k + j], prow = src_row[t * k + j];
+                    const bool valid = j0 + u < k && pr >= 0 && pr < world && prow >= 0 && prow < rows_cap;   // else: contributes nothing
+                    wj[u] = valid ? w[t * k + j] : 0.0f;
+                    v[u] = make_uint4(0u, 0u, 0u, 0u);
+                    if (valid) {
+                        const uint4* row = reinterpret_cast<const uint4*>(peers[pr]) + prow * rows_ld16;
+                        asm volatile("ld.global.relaxed.sys.v4.u32 {%0, %1, %2, %3}, [%4];"
+                                     : "=r"(v[u].x), "=r"(v[u].y), "=r"(v[u].z), "=r"(v[u].w) : "l"(row + c));
+                    }
                 }
 #pragma unroll
                 for (int u = 0; u < 4; ++u) {
@@ -149,52 +164,6 @@ combine_rows_peer_kernel(const int64_t* __restrict__ peers, int64_t rows_ld16, c
     }
 }
 
-// Routing plan of the peer-memory path, from the gathered (source rank, expert) count matrix.
-//
-// plan_offsets (one block): for every global expert e, base[e] = the row of the owner's padded expert-major
-// buffer at which THIS rank's rows of e start (groups padded to `alignment`, inside a group the rows of lower
-// source ranks first); sizes[0..e_local) = padded rows of this rank's experts, sizes[e_local..2 e_local) their
-// real rows, sizes[2 e_local] = the largest padded total over all ranks (for the capacity check).
-__global__ void __launch_bounds__(1024)
-plan_offsets_kernel(const int64_t* __restrict__ all_counts, int world, int num_experts, int rank, int alignment,
-                    int64_t* __restrict__ base, int64_t* __restrict__ sizes)
-{
-    extern __shared__ int64_t sh[];                 // padded[num_experts], then per-rank totals[world]
-    int64_t* padded = sh;
-    int64_t* totals = sh + num_experts;
-    const int e_local = num_experts / world;
-    for (int e = threadIdx.x; e < num_experts; e += blockDim.x) {
-        int64_t total = 0, before = 0;
-        for (int s = 0; s < world; ++s) {
-            const int64_t c = all_counts[static_cast<int64_t>(s) * num_experts + e];
-            if (s < rank) before += c;
-            total += c;
-        }
-        padded[e] = (total + alignment - 1) / alignment * alignment;
-        base[e] = before;                           // the start of the expert's group is added below
-        if (e / e_local == rank) {
-            sizes[e % e_local] = padded[e];
-            sizes[e_local + e % e_local] = total;
-        }
-    }
-    __syncthreads();
-    for (int r = threadIdx.x; r < world; r += blockDim.x) {       // exclusive scan of the padded groups of each owner
-        int64_t run = 0;
-        for (int j = 0; j < e_local; ++j) {
-            const int e = r * e_local + j;
-            base[e] += run;
-            run += padded[e];
-        }
-        totals[r] = run;
-    }
-    __syncthreads();
-    if (threadIdx.x == 0) {
-        int64_t mx = 0;
-        for (int r = 0; r < world; ++r) mx = totals[r] > mx ? totals[r] : mx;
-        sizes[2 * e_local] = mx;
-    }
-}
-
 // counts[e] += number of ids equal to e (counts zeroed by the caller); per-block histogram in shared memory first, so
 // that the global atomics are one per expert and block instead of one per pair on a handful of addresses
 __global__ void __launch_bounds__(1024)
@@ -212,13 +181,18 @@ expert_histogram_kernel(const int64_t* __restrict__ ids, int64_t n, int num_expe
         if (hist[e] != 0) atomicAdd(&counts[e], static_cast<unsigned long long>(hist[e]));
 }
 
+// Routing plan of the peer-memory path, from the gathered (source rank, expert) count matrix (plan_offsets_masked_kernel
+// below gives base and limit).
 // plan_rows (one block per expert): dst_row[p] = base[e] + (number of pairs p' < p routed to e), for every pair p
 // routed to e -- a stable counting sort without the sort: pairs keep their order inside an expert's group.
+// With `limit` (fixed-capacity plan) a pair whose row would reach limit[e] does not fit and gets row -1.
 __global__ void __launch_bounds__(1024)
-plan_rows_kernel(const int64_t* __restrict__ ids, int64_t n, const int64_t* __restrict__ base, int64_t* __restrict__ dst_row)
+plan_rows_kernel(const int64_t* __restrict__ ids, int64_t n, const int64_t* __restrict__ base, const int64_t* __restrict__ limit,
+                 int64_t* __restrict__ dst_row)
 {
     __shared__ int warp_tot[32];
     const int e = blockIdx.x, lane = threadIdx.x & 31, wid = threadIdx.x >> 5;
+    const int64_t end = limit != nullptr ? limit[e] : INT64_MAX;
     int64_t running = base[e];
     for (int64_t chunk = 0; chunk < n; chunk += blockDim.x) {
         const int64_t p = chunk + threadIdx.x;
@@ -233,9 +207,64 @@ plan_rows_kernel(const int64_t* __restrict__ ids, int64_t n, const int64_t* __re
             before += w < wid ? c : 0;
             total += c;
         }
-        if (mine) dst_row[p] = running + before + lane_rank;
+        if (mine) dst_row[p] = running + before + lane_rank < end ? running + before + lane_rank : -1;
         running += total;
         __syncthreads();
+    }
+}
+
+// Fixed-capacity plan: every local expert owns `cap_m` rows of its rank's buffer (the masked layout of the GEMM),
+// so a pair's row depends only on the gathered counts, never on a host-side prefix sum of padded group sizes.
+//   base[e]  = (e % e_local) * cap_m + rows of e from lower ranks      limit[e] = (e % e_local + 1) * cap_m
+//   masked_m[j] = min(rows of local expert j, cap_m)                   status |= 4 if some expert anywhere overflows
+// Every rank sees the same gathered counts, hence the same overflow verdict.
+__global__ void __launch_bounds__(1024)
+plan_offsets_masked_kernel(const int64_t* __restrict__ all_counts, int world, int num_experts, int rank, int cap_m,
+                           int64_t* __restrict__ base, int64_t* __restrict__ limit, int32_t* __restrict__ masked_m,
+                           int32_t* __restrict__ status)
+{
+    const int e_local = num_experts / world;
+    for (int e = threadIdx.x; e < num_experts; e += blockDim.x) {
+        int64_t total = 0, before = 0;
+        for (int s = 0; s < world; ++s) {
+            const int64_t c = all_counts[static_cast<int64_t>(s) * num_experts + e];
+            if (s < rank) before += c;
+            total += c;
+        }
+        const int64_t group = static_cast<int64_t>(e % e_local) * cap_m;
+        base[e] = group + before;
+        limit[e] = group + cap_m;
+        if (e / e_local == rank) masked_m[e % e_local] = static_cast<int32_t>(total < cap_m ? total : cap_m);
+        if (total > cap_m && status != nullptr) atomicOr(status, 4);
+    }
+}
+
+// Barrier over the GPUs of one NVLink domain with a bounded wait.  `flag_peers[r]` is the address, in this process,
+// of rank r's flag array (int64 [slots][world], symmetric, zero at start).  Thread p tells rank p "rank `rank` has
+// reached `epoch`" with a releasing system-scope store into flags[slot][rank] over there, then waits until its own
+// flags[slot][p] shows that rank p has reached it too.  Epochs only grow, so no reset is needed.  A wait that lasts
+// longer than `budget` clock cycles gives up: bit 1 of the status word is set and the kernel returns -- nothing
+// traps and nothing spins for ever, the host reads the word and raises.
+__global__ void __launch_bounds__(64)
+peer_barrier_kernel(const int64_t* __restrict__ flag_peers, int rank, int world, int slot, long long epoch, long long budget,
+                    int32_t* __restrict__ status)
+{
+    const int p = threadIdx.x;
+    if (p >= world) return;
+    __threadfence_system();                      // everything this stream wrote before the barrier, peers' memory included
+    long long* theirs = reinterpret_cast<long long*>(flag_peers[p]) + static_cast<int64_t>(slot) * world + rank;
+    asm volatile("st.release.sys.global.s64 [%0], %1;" ::"l"(theirs), "l"(epoch) : "memory");
+    const long long* mine = reinterpret_cast<const long long*>(flag_peers[rank]) + static_cast<int64_t>(slot) * world + p;
+    const long long t0 = clock64();
+    for (;;) {
+        long long seen;
+        asm volatile("ld.acquire.sys.global.s64 %0, [%1];" : "=l"(seen) : "l"(mine) : "memory");
+        if (seen >= epoch) break;
+        if (clock64() - t0 > budget) {
+            if (status != nullptr) atomicOr(status, 2);
+            break;
+        }
+        __nanosleep(100);
     }
 }
 
@@ -287,34 +316,44 @@ int launch_expert_histogram(const int64_t* ids, int64_t n, int num_experts, int6
     return NVFP4_OK;
 }
 
-int launch_plan_peer(const int64_t* all_counts, int world, int num_experts, int rank, int alignment, const int64_t* ids,
-                     int64_t n, int64_t* base, int64_t* sizes, int64_t* dst_row, cudaStream_t stream)
+int launch_plan_peer_masked(const int64_t* all_counts, int world, int num_experts, int rank, int cap_m, const int64_t* ids,
+                            int64_t n, int64_t* base, int64_t* limit, int32_t* masked_m, int64_t* dst_row, int32_t* status,
+                            cudaStream_t stream)
 {
-    plan_offsets_kernel<<<1, 1024, (num_experts + world) * sizeof(int64_t), stream>>>(all_counts, world, num_experts, rank, alignment,
-                                                                                       base, sizes);
+    plan_offsets_masked_kernel<<<1, 1024, 0, stream>>>(all_counts, world, num_experts, rank, cap_m, base, limit, masked_m, status);
     NVFP4_CUDA_CHECK(cudaGetLastError());
-    plan_rows_kernel<<<num_experts, 1024, 0, stream>>>(ids, n, base, dst_row);
+    if (n > 0) plan_rows_kernel<<<num_experts, 1024, 0, stream>>>(ids, n, base, limit, dst_row);
+    NVFP4_CUDA_CHECK(cudaGetLastError());
+    return NVFP4_OK;
+}
+
+int launch_peer_barrier(const int64_t* flag_peers, int rank, int world, int slot, int64_t epoch, int64_t budget_cycles,
+                        int32_t* status, cudaStream_t stream)
+{
+    peer_barrier_kernel<<<1, 64, 0, stream>>>(flag_peers, rank, world, slot, static_cast<long long>(epoch),
+                                              static_cast<long long>(budget_cycles), status);
     NVFP4_CUDA_CHECK(cudaGetLastError());
     return NVFP4_OK;
 }
 
 int launch_dispatch_rows_peer(const void* src, int64_t src_ld_bytes, const int64_t* src_idx, int src_div, const int64_t* peers,
                               const int64_t* dst_rank, const int64_t* dst_row, int64_t n_rows, int row_bytes,
-                              int64_t dst_ld_bytes, int num_sms, cudaStream_t stream)
+                              int64_t dst_ld_bytes, int world, int64_t rows_cap, int32_t* status, int num_sms, cudaStream_t stream)
 {
     dispatch_rows_peer_kernel<<<grid_for(n_rows, num_sms), 256, 0, stream>>>(
         static_cast<const uint4*>(src), src_ld_bytes / 16, src_idx, src_div, peers, dst_rank, dst_row, n_rows, row_bytes / 16,
-        dst_ld_bytes / 16);
+        dst_ld_bytes / 16, world, rows_cap, status);
     NVFP4_CUDA_CHECK(cudaGetLastError());
     return NVFP4_OK;
 }
 
 int launch_combine_rows_peer(const int64_t* peers, int64_t rows_ld_elems, const int64_t* src_rank, const int64_t* src_row,
-                             const float* w, int64_t tokens, int k, int hidden, void* y, int64_t y_ld_elems, int num_sms,
-                             cudaStream_t stream)
+                             const float* w, int64_t tokens, int k, int hidden, void* y, int64_t y_ld_elems, int world,
+                             int64_t rows_cap, int num_sms, cudaStream_t stream)
 {
     combine_rows_peer_kernel<<<grid_for(tokens, num_sms), 256, 0, stream>>>(peers, rows_ld_elems / 8, src_rank, src_row, w, tokens,
-                                                                             k, hidden / 8, static_cast<uint4*>(y), y_ld_elems / 8);
+                                                                             k, hidden / 8, static_cast<uint4*>(y), y_ld_elems / 8,
+                                                                             world, rows_cap);
     NVFP4_CUDA_CHECK(cudaGetLastError());
     return NVFP4_OK;
 }

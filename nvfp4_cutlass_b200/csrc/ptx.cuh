@@ -466,6 +466,29 @@ NVFP4_DEVICE bool mbar_wait_cluster(uint64_t* bar, uint32_t parity, volatile uin
     probe_count(acc, idx, probe_clock() - t0);
     return ok;
 }
+// Bounded waits that sleep between polls, at CTA or cluster scope: for roles that run ahead and wait long (producers
+// waiting for ring space, transform warps waiting for a slot).  Every poll of an mbarrier is an instruction of the
+// shared-memory pipe, which the latency-critical roles (MMA issue, scale warps) need for their own barriers and loads:
+// a dozen warps polling without pause were measured to stretch a completed-barrier check of the MMA thread to ~350 cycles.
+template <bool kCluster>
+NVFP4_DEVICE bool mbar_wait_sleep(uint64_t* bar, uint32_t parity, volatile uint32_t* abort_flag, uint32_t sleep_ns, ProbeAcc& acc,
+                                  int idx)
+{
+    auto poll = [&] { return kCluster ? mbar_try_wait_cluster(bar, parity) : mbar_try_wait(bar, parity); };
+    if (poll()) return true;
+    const long long t0 = clock64();
+    bool ok = false;
+    for (;;) {
+#pragma unroll 1
+        for (int i = 0; i < 16 && !ok; ++i) {
+            __nanosleep(sleep_ns);
+            ok = poll();
+        }
+        if (ok || *abort_flag != 0 || clock64() - t0 > kWaitBudgetCycles) break;
+    }
+    probe_count(acc, idx, clock64() - t0);
+    return ok;
+}
 // All earlier tcgen05 operations of this thread arrive, when they retire, on the barrier at
 // this offset in every CTA of the cluster named by `cta_mask`.
 NVFP4_DEVICE void tcgen05_commit_cluster(uint64_t* bar, uint16_t cta_mask)

@@ -100,11 +100,6 @@ NVFP4_DEVICE void decompose_block16(const uint32_t (&w)[8], Block16& out)
     constexpr float kS1Mul = kPolicy == 2 ? 0.25f : 0.125f;
     constexpr float kRadix = kPolicy == 2 ? 4.0f : 8.0f;
     constexpr unsigned short kNegRadixF16 = kPolicy == 2 ? 0xC400u : 0xC800u;
-#ifdef NVFP4_ABLATE_XFORM   // timing experiments only (wrong results); never defined in the shipped build
-    out.q0[0] = w[0] ^ w[1]; out.q0[1] = w[2] ^ w[3]; out.q1[0] = w[4] ^ w[5]; out.q1[1] = w[6] ^ w[7];
-    out.s0 = 0x38; out.s1 = 0x20;
-    return;
-#endif
     // block amax over 16 BF16 values (pairs packed low = even element)
     uint32_t m0 = ptx::max_abs_bf16x2(w[0], w[1]);
     uint32_t m1 = ptx::max_abs_bf16x2(w[2], w[3]);
@@ -209,11 +204,6 @@ NVFP4_DEVICE void load_tile_smem(TileShare<kRows, kBK, kThreads>& s, uint32_t a_
     using S = TileShare<kRows, kBK, kThreads>;
     if (t >= S::kActive) return;
     const uint32_t row = t % kRows, first_block = (t / kRows) * S::kBlocksPerThread;
-#ifdef NVFP4_ABLATE_LDS   // timing experiments only (wrong results); never defined in the shipped build
-    for (uint32_t j = 0; j < S::kBlocksPerThread; ++j)
-        for (uint32_t i = 0; i < 8; ++i) s.w[j][i] = a_smem + row + j + i;
-    return;
-#endif
 #pragma unroll
     for (uint32_t j = 0; j < S::kBlocksPerThread; ++j) {
         const uint32_t k = (first_block + j) * 16u;

@@ -11,12 +11,17 @@ parallel, and there is one exchange before and one after the two GEMMs:
   combine    every token sums the outputs of its k experts with the routing weights
 
 Two ways to move the rows.  Peer memory (``peer_rows_cap > 0``; GPUs of one NVLink domain, or
-one rank): the ranks all-gather the (rank, expert) histograms, two plan kernels give every
-pair its row in the owner's buffer, one kernel stores the token rows straight into the
-owners' symmetric buffers and one kernel loads the k output rows of every token back from
-them; three stream-ordered barriers separate the phases.  All-to-all (the fallback, and the
-form the CPU tests run on gloo): counts all-to-all, gather, ``all_to_all_single`` with split
-sizes, scatter; the reverse for the combine.  Both build the same buffers.
+one rank): every local expert owns a fixed number of rows of its rank's symmetric buffer (the
+GEMM's masked layout), the ranks all-gather the (rank, expert) histograms, two plan kernels
+give every pair its row in the owner's buffer and the owner its per-expert row counts -- all
+on the device, nothing about the routing comes back to the host -- one kernel stores the
+token rows straight into the owners' buffers, the two masked GEMMs run on them, and one
+kernel loads the k output rows of every token back; three bounded barriers separate the
+phases, and with ``micro_batches`` > 1 the tokens are split and the parts run on streams of
+their own so that one part's NVLink traffic overlaps another's GEMMs.  All-to-all (the
+fallback when an expert overflows its rows, and the form the CPU tests run on gloo): counts
+all-to-all, gather, ``all_to_all_single`` with split sizes, scatter; the reverse for the
+combine.  Both give every expert the same rows in the same order.
 
 The reference project has no multi-GPU mode; this one follows the contiguous-layout
 contract of its GEMM (python/nvfp4_gemm/layout.py:155-169 there: rows grouped by expert,
@@ -88,24 +93,21 @@ def plan_dispatch(topk_ids: torch.Tensor, num_experts: int, world: int, alignmen
 
 
 @dataclass
-class PeerDispatch:
-    """Routing plan of the peer-memory path: where every (token, choice) pair lives in its owner's buffer."""
-    order: Optional[torch.Tensor]  # None: dst_* are indexed by the pair p = token * k + choice (CUDA plan); else the
-                                   # (T*k,) pair indices sorted by expert, and dst_* are indexed by that send order
-    dst_rank: torch.Tensor       # (T*k,) owner rank
-    dst_row: torch.Tensor        # (T*k,) row in the owner's padded expert-major buffer
-    group_sizes: list            # padded rows per local expert
-    real_sizes: list             # real rows per local expert
-    rows_padded: int
-    max_rows_padded: int         # the largest rows_padded over all ranks (capacity check, same on every rank)
-    padded_dev: Optional[torch.Tensor] = None    # group_sizes as a device tensor (to build m_indices without a copy)
+class MaskedDispatch:
+    """Routing plan of the peer-memory path: where every (token, choice) pair lives in its owner's buffer, in which
+    every local expert owns `cap_m` rows (the masked layout).  Everything is a device tensor."""
+    dst_rank: torch.Tensor       # (T*k,) owner rank of pair p = token * k + choice
+    dst_row: torch.Tensor        # (T*k,) row in the owner's buffer (local expert * cap_m + position), -1 = does not fit
+    masked_m: torch.Tensor       # (E_local,) int32 real rows of this rank's experts (clamped to cap_m)
+    overflow: Optional[torch.Tensor] = None    # CPU form only: whether some expert anywhere exceeds cap_m
 
 
-def plan_dispatch_peer(topk_ids: torch.Tensor, num_experts: int, world: int, rank: int, alignment: int,
-                       group: Optional[dist.ProcessGroup] = None) -> PeerDispatch:
+def plan_dispatch_masked(topk_ids: torch.Tensor, num_experts: int, world: int, rank: int, cap_m: int,
+                         group: Optional[dist.ProcessGroup] = None, status: Optional[torch.Tensor] = None) -> MaskedDispatch:
     """Every rank gathers the whole (source rank, expert) count matrix and from it works out, without a second
-    exchange, the row of each of its pairs in the owner's buffer.  The layout is the one plan_dispatch builds:
-    expert-major, groups padded to the alignment, inside a group the rows of lower source ranks first."""
+    exchange and without a host read-back, the row of each of its pairs in the owner's buffer: expert-major with
+    cap_m rows per expert, inside an expert the rows of lower source ranks first and a rank's own pairs in their
+    order -- the same order the all-to-all plan produces."""
     e_local = num_experts // world
     flat = topk_ids.reshape(-1).contiguous()
     if flat.is_cuda:
@@ -118,62 +120,69 @@ def plan_dispatch_peer(topk_ids: torch.Tensor, num_experts: int, world: int, ran
         dist.all_gather_into_tensor(gathered, counts, group=group)
     else:
         gathered = counts
+    dst_rank = torch.div(flat, e_local, rounding_mode="floor")
     if flat.is_cuda:
-        # two kernels of the library: group offsets from the gathered histograms, then every pair's row (a stable
-        # counting sort without the sort); pairs are addressed by their own index p = token * k + choice
-        sizes_dev, dst_row = _C.plan_peer(gathered, flat, world, rank, alignment)
-        sizes = sizes_dev.tolist()                                            # the one host synchronisation of a step
-        dst_rank = torch.div(flat, e_local, rounding_mode="floor")
-        return PeerDispatch(order=None, dst_rank=dst_rank, dst_row=dst_row, group_sizes=sizes[:e_local],
-                            real_sizes=sizes[e_local:2 * e_local], rows_padded=int(sum(sizes[:e_local])),
-                            max_rows_padded=int(sizes[2 * e_local]), padded_dev=sizes_dev[:e_local])
-    # the same plan as tensor operations (CPU tests of the host logic); pairs in send order (sorted by expert)
+        masked_m, dst_row = _C.plan_peer_masked(gathered, flat, world, rank, cap_m, status)
+        return MaskedDispatch(dst_rank=dst_rank, dst_row=dst_row, masked_m=masked_m)
+    # the same plan as tensor operations (CPU tests of the host logic)
     all_counts = gathered.reshape(world, num_experts)
-    per_expert = all_counts.sum(dim=0)
-    padded = _pad(per_expert, alignment).reshape(world, e_local)
-    sizes = torch.stack([padded[rank], per_expert.reshape(world, e_local)[rank],
-                         padded.sum(dim=1).max().expand(e_local)]).tolist()
-    order = torch.argsort(flat, stable=True)
-    starts = (torch.cumsum(padded, dim=1) - padded).reshape(-1)               # start of each expert in its owner's buffer
+    total = all_counts.sum(dim=0)
     before = (torch.cumsum(all_counts, dim=0) - all_counts)[rank]             # rows of each expert from lower ranks
-    first = torch.cumsum(counts, 0) - counts                                  # first send-order index of each expert
+    order = torch.argsort(flat, stable=True)
+    first = torch.cumsum(counts, 0) - counts                                  # first sorted index of each expert
     expert_sorted = flat[order]
-    dst_row = (starts + before - first)[expert_sorted] + torch.arange(order.numel(), device=flat.device)
-    dst_rank = torch.div(expert_sorted, e_local, rounding_mode="floor")
-    return PeerDispatch(order=order, dst_rank=dst_rank, dst_row=dst_row, group_sizes=sizes[0], real_sizes=sizes[1],
-                        rows_padded=int(sum(sizes[0])), max_rows_padded=int(sizes[2][0]))
+    within = before[expert_sorted] + torch.arange(order.numel()) - first[expert_sorted]
+    row_sorted = torch.where(within < cap_m, (expert_sorted % e_local) * cap_m + within, torch.full_like(within, -1))
+    dst_row = torch.empty_like(row_sorted)
+    dst_row[order] = row_sorted
+    masked_m = total.reshape(world, e_local)[rank].clamp(max=cap_m).to(torch.int32)
+    return MaskedDispatch(dst_rank=dst_rank, dst_row=dst_row, masked_m=masked_m, overflow=(total > cap_m).any())
 
 
 class PeerBuffers:
-    """The two symmetric buffers of the peer-memory path (GEMM input rows and GEMM output rows of this rank,
-    mapped into every rank of the group) and their address tables."""
+    """What one in-flight step of the peer-memory path owns: the symmetric input and output buffers of this rank's
+    experts in the masked layout (E_local, cap_m, hidden), mapped into every rank of the group, the local gate+up
+    buffer, the address tables, the flag array of the bounded barrier and the step's status word."""
 
-    def __init__(self, rows_cap: int, hidden: int, device: torch.device, group=None, world: int = 2):
-        self.rows_cap, self.hidden = rows_cap, hidden
+    NUM_SLOTS = 8
+
+    def __init__(self, e_local: int, cap_m: int, hidden: int, inter: int, device: torch.device, group=None, world: int = 1,
+                 rank: int = 0):
+        self.e_local, self.cap_m, self.hidden, self.world, self.rank = e_local, cap_m, hidden, world, rank
+        self.rows_cap = e_local * cap_m
+        self.status = torch.zeros(1, dtype=torch.int32, device=device)
+        self.h = torch.zeros(e_local, cap_m, 2 * inter, dtype=torch.bfloat16, device=device)
+        self.epoch = [0] * self.NUM_SLOTS
         if world == 1:                      # one rank: the same kernels on ordinary buffers, nobody to wait for
-            self._ha = None
-            self.a = torch.zeros(rows_cap, hidden, dtype=torch.bfloat16, device=device)
-            self.out = torch.zeros(rows_cap, hidden, dtype=torch.bfloat16, device=device)
+            self.a = torch.zeros(e_local, cap_m, hidden, dtype=torch.bfloat16, device=device)
+            self.out = torch.zeros(e_local, cap_m, hidden, dtype=torch.bfloat16, device=device)
             self.a_peers = torch.tensor([self.a.data_ptr()], dtype=torch.int64, device=device)
             self.out_peers = torch.tensor([self.out.data_ptr()], dtype=torch.int64, device=device)
+            self.flag_peers = None
             return
         import torch.distributed._symmetric_memory as symm
         group = group if group is not None else dist.group.WORLD
-        self.a = symm.empty(rows_cap, hidden, dtype=torch.bfloat16, device=device)
-        self.out = symm.empty(rows_cap, hidden, dtype=torch.bfloat16, device=device)
-        self._ha = symm.rendezvous(self.a, group)
-        self._ho = symm.rendezvous(self.out, group)
-        self.a.zero_()                      # padding rows are never written by anyone: keep them finite
+        self.a = symm.empty(e_local, cap_m, hidden, dtype=torch.bfloat16, device=device)
+        self.out = symm.empty(e_local, cap_m, hidden, dtype=torch.bfloat16, device=device)
+        self.flags = symm.empty(self.NUM_SLOTS * world, dtype=torch.int64, device=device)
+        handles = [symm.rendezvous(t, group) for t in (self.a, self.out, self.flags)]
+        self.a.zero_()                      # rows past an expert's count are computed like real rows: keep them finite
         self.out.zero_()
-        self.a_peers = torch.tensor(list(self._ha.buffer_ptrs), dtype=torch.int64, device=device)
-        self.out_peers = torch.tensor(list(self._ho.buffer_ptrs), dtype=torch.int64, device=device)
+        self.flags.zero_()
+        self.a_peers, self.out_peers, self.flag_peers = (
+            torch.tensor(list(h.buffer_ptrs), dtype=torch.int64, device=device) for h in handles)
         torch.cuda.synchronize(device)
-        self.barrier()
+        handles[0].barrier(channel=0)       # set-up only: every rank's buffers and flags are zero before the first step
+        torch.cuda.synchronize(device)
 
-    def barrier(self) -> None:
-        """All ranks of the group, ordered on the current stream."""
-        if self._ha is not None:
-            self._ha.barrier(channel=0)
+    def barrier(self, slot: int, budget_cycles: int = 2_000_000_000) -> None:
+        """All ranks of the group, ordered on the current stream.  The wait is bounded: a peer that never arrives costs
+        `budget_cycles` clock cycles and bit 1 of the status word, not a hung GPU."""
+        if self.world == 1:
+            return
+        from . import _C
+        self.epoch[slot] += 1
+        _C.peer_barrier(self.flag_peers, self.rank, self.world, slot, self.epoch[slot], self.status, budget_cycles)
 
 
 def _exchange(rows: torch.Tensor, send_counts, recv_counts, group) -> torch.Tensor:
@@ -201,7 +210,8 @@ class ExpertParallelMoE:
     """
 
     def __init__(self, num_experts: int, hidden: int, inter: int, up, down, group=None, alignment: int = 128,
-                 gemm: Optional[Callable] = None, native_glue: bool = True, peer_rows_cap: int = 0):
+                 gemm: Optional[Callable] = None, native_glue: bool = True, peer_rows_cap: int = 0, micro_batches: int = 1,
+                 check_each_step: bool = True):
         self.group = group
         self.world = dist.get_world_size(group) if dist.is_initialized() else 1
         self.rank = dist.get_rank(group) if dist.is_initialized() else 0
@@ -211,29 +221,37 @@ class ExpertParallelMoE:
         self.e_local = num_experts // self.world
         self.up, self.down = up, down
         self.gemm_swiglu = None                # SwiGLU folded into the down-projection (CUDA library only)
+        self.gemm_masked = None
         if gemm is None:
             from . import _C
             gemm = _C.m_grouped_bf16_dual_nvfp4_gemm_contiguous
+            self.gemm_masked = _C.m_grouped_bf16_dual_nvfp4_gemm_masked
             if hidden % 256 == 0:
                 self.gemm_swiglu = _C.m_grouped_swiglu_dual_nvfp4_gemm_contiguous
         self.gemm = gemm
         self.native_glue = native_glue         # False: tensor operations even for CUDA tensors (a test's comparison arm)
-        # peer_rows_cap > 0: dispatch and combine go through peer memory (one kernel each, stores into / loads from
-        # the owner rank's buffer; with one rank the same kernels on local buffers) instead of staging buffers and
-        # NCCL all-to-alls; a step whose routing would overflow the buffer of some rank falls back to the
-        # all-to-all path on every rank
-        self.peer = None
+        # peer_rows_cap > 0: dispatch and combine go through peer memory.  It is the number of rows every local expert
+        # owns in this rank's buffers, per micro-batch (rounded up to the GEMM's 128-row tile); a step in which some
+        # expert receives more takes the all-to-all path instead -- on every rank, since all see the same histograms.
+        self.micro = max(1, int(micro_batches))
+        self.check_each_step = check_each_step
+        self.peer = None                       # list of PeerBuffers, one per micro-batch in flight
         self.peer_error = None
-        if peer_rows_cap > 0 and torch.cuda.is_available():
+        self.steps_repeated = 0                # steps that overflowed the buffers and were repeated over the all-to-all path
+        masked_ok = self.gemm_masked is not None and (2 * inter) % 256 == 0 and hidden % 256 == 0
+        if peer_rows_cap > 0 and torch.cuda.is_available() and masked_ok:
+            dev = torch.device("cuda", torch.cuda.current_device())
+            cap_m = (int(peer_rows_cap) + 127) // 128 * 128
             try:
-                self.peer = PeerBuffers(peer_rows_cap, hidden, torch.device("cuda", torch.cuda.current_device()), group,
-                                        self.world)
+                self.peer = [PeerBuffers(self.e_local, cap_m, hidden, inter, dev, group, self.world, self.rank)
+                             for _ in range(self.micro)]
+                self.streams = [torch.cuda.Stream(device=dev) for _ in range(self.micro)] if self.micro > 1 else []
             except Exception as exc:                                   # symmetric memory unavailable: keep the NCCL path
+                self.peer = None
                 self.peer_error = repr(exc)
             if self.world > 1:
                 # every rank must take the same path: one rank without buffers sends all of them to the all-to-all
-                ok = torch.tensor([1 if self.peer is not None else 0], dtype=torch.int32,
-                                  device=torch.device("cuda", torch.cuda.current_device()))
+                ok = torch.tensor([1 if self.peer is not None else 0], dtype=torch.int32, device=dev)
                 dist.all_reduce(ok, op=dist.ReduceOp.MIN, group=group)
                 if int(ok.item()) == 0 and self.peer is not None:
                     self.peer = None
@@ -296,11 +314,12 @@ class ExpertParallelMoE:
         y.index_add_(0, plan.order // k, back.float() * topk_w.reshape(-1)[plan.order].unsqueeze(1))
         return y.to(torch.bfloat16)
 
-    def forward_peer(self, x: torch.Tensor, topk_ids: torch.Tensor, topk_w: torch.Tensor, marks: Optional[list] = None):
-        """One step over peer memory; returns None (on every rank alike) if the routing does not fit the buffers.
-        `marks`, if given, receives a CUDA event after each phase (plan, dispatch, experts, combine)."""
+    def _peer_step(self, buf: "PeerBuffers", x, topk_ids, topk_w, y, marks: Optional[list] = None) -> None:
+        """One (micro-)step over peer memory on the current stream, into `y`.  Nothing here reads anything back to the
+        host.  Everything that can fail on this rank alone -- argument checks, allocations -- happens before the first
+        barrier; if a call between the barriers raises all the same, the remaining barriers are still enqueued before
+        the exception travels on, so that the other ranks' waits are not left to run into their time limit."""
         from . import _C
-        from .layout import make_m_indices
 
         def mark():
             if marks is not None:
@@ -309,38 +328,75 @@ class ExpertParallelMoE:
                 marks.append(ev)
 
         k = topk_ids.shape[1]
+        _C._require(x.is_cuda and x.dtype == torch.bfloat16 and x.dim() == 2 and x.shape[1] == self.hidden and x.stride(1) == 1,
+                    "x is a (tokens, hidden) BF16 CUDA tensor")
+        _C._require(topk_ids.shape == topk_w.shape and topk_ids.shape[0] == x.shape[0] and topk_ids.dtype == torch.int64,
+                    "topk_ids (int64) and topk_w have one row per token")
+        w_flat = topk_w.float().contiguous().reshape(-1)
         mark()
-        plan = plan_dispatch_peer(topk_ids, self.num_experts, self.world, self.rank, self.alignment, self.group)
-        if plan.max_rows_padded > self.peer.rows_cap:
-            return None
+        plan = plan_dispatch_masked(topk_ids, self.num_experts, self.world, self.rank, buf.cap_m, self.group, buf.status)
         self.last = plan
-        buf = self.peer
-        if plan.padded_dev is not None:                 # expert id per row, built on the device
-            m_indices = torch.repeat_interleave(torch.arange(self.e_local, dtype=torch.int32, device=x.device), plan.padded_dev,
-                                                output_size=plan.rows_padded)
-        else:
-            m_indices = make_m_indices(plan.group_sizes, device=x.device, alignment=self.alignment)
         mark()
-        buf.barrier()                                   # every rank has finished with the buffers of the previous step
-        _C.dispatch_rows_peer(x, None, k, buf.a_peers, plan.dst_rank, plan.dst_row, self.hidden)
-        buf.barrier()                                   # all rows have landed everywhere
-        mark()
-        a, out = buf.a[:plan.rows_padded], buf.out[:plan.rows_padded]
-        h = torch.empty(a.shape[0], 2 * self.inter, dtype=torch.bfloat16, device=a.device)
-        self.gemm(a, *self.up, h, m_indices)
-        self._down(h, out, m_indices)
-        mark()
-        buf.barrier()                                   # every rank's expert outputs are complete
-        y = _C.combine_rows_peer(buf.out_peers, self.hidden, plan.dst_rank, plan.dst_row,
-                                 topk_w.float().contiguous().reshape(-1), x.shape[0], self.hidden)
-        mark()
+        pending = [0, 1, 2]                         # barrier slots of this step still to be enqueued
+        try:
+            buf.barrier(pending.pop(0))             # every rank has finished with these buffers (its previous step on them)
+            _C.dispatch_rows_peer(x, None, k, buf.a_peers, plan.dst_rank, plan.dst_row, self.hidden, buf.rows_cap, buf.status)
+            buf.barrier(pending.pop(0))             # all rows have landed everywhere
+            mark()
+            self.gemm_masked(buf.a, *self.up, buf.h, plan.masked_m, device_status=buf.status)
+            self.gemm_masked(buf.h, *self.down, buf.out, plan.masked_m, fold_swiglu=True, device_status=buf.status)
+            mark()
+            buf.barrier(pending.pop(0))             # every rank's expert outputs are complete
+            _C.combine_rows_peer(buf.out_peers, self.hidden, plan.dst_rank, plan.dst_row, w_flat, x.shape[0], self.hidden,
+                                 buf.rows_cap, out=y)
+            mark()
+        except BaseException:
+            for slot in pending:
+                buf.barrier(slot)
+            raise
+
+    def forward_peer(self, x: torch.Tensor, topk_ids: torch.Tensor, topk_w: torch.Tensor, marks: Optional[list] = None):
+        """One step over peer memory.  With micro_batches > 1 the tokens are cut into that many parts, each with buffers
+        and a stream of its own, so that the NVLink traffic of one part runs under the GEMMs of another; every token's
+        result is the same whichever part it is in.  `marks`, if given, receives a CUDA event after each phase of the
+        (first) part: start, plan, dispatch, experts, combine."""
+        tokens = x.shape[0]
+        y = torch.empty(tokens, self.hidden, dtype=torch.bfloat16, device=x.device)
+        if self.micro == 1 or tokens < self.micro:
+            self._peer_step(self.peer[0], x, topk_ids, topk_w, y, marks)
+            return y
+        cur = torch.cuda.current_stream()
+        bounds = [tokens * i // self.micro for i in range(self.micro + 1)]
+        for i, stream in enumerate(self.streams):
+            lo, hi = bounds[i], bounds[i + 1]
+            stream.wait_stream(cur)
+            with torch.cuda.stream(stream):
+                self._peer_step(self.peer[i], x[lo:hi], topk_ids[lo:hi], topk_w[lo:hi], y[lo:hi], marks if i == 0 else None)
+        for stream in self.streams:
+            cur.wait_stream(stream)
         return y
+
+    def read_status(self) -> int:
+        """Reads and clears the status words of the peer-memory buffers (synchronises): bit 0 a GEMM's wait expired,
+        bit 1 a barrier's wait expired (a peer never arrived), bit 2 an expert received more rows than it owns, bit 3 a
+        routing entry out of range.  Bits 0, 1 and 3 raise; the overflow bit is returned for the caller to act on."""
+        bits = 0
+        for buf in self.peer or []:
+            bits |= int(buf.status.item())
+            buf.status.zero_()
+        if bits & 0b1011:
+            raise RuntimeError(f"expert-parallel step failed on the device (status {bits:#x}: "
+                               f"{'GEMM wait expired; ' if bits & 1 else ''}{'a peer never reached a barrier; ' if bits & 2 else ''}"
+                               f"{'routing entry out of range' if bits & 8 else ''})")
+        return bits
 
     def forward(self, x: torch.Tensor, topk_ids: torch.Tensor, topk_w: torch.Tensor) -> torch.Tensor:
         if self.peer is not None and x.is_cuda:
             y = self.forward_peer(x, topk_ids, topk_w)
-            if y is not None:
+            # the one host read of a step, after everything has been enqueued: did every expert fit its rows?
+            if not self.check_each_step or not (self.read_status() & 4):
                 return y
+            self.steps_repeated += 1
         plan, a = self.dispatch(x, topk_ids)
         self.last = plan
         out = self.experts(a, plan)

@@ -21,6 +21,12 @@ import torch.distributed as dist
 E_TOTAL, HIDDEN, INTER, TOKENS, TOP_K = 128, 4096, 1536, 16384, 8
 
 
+def expert_rows_cap(world: int, micro: int) -> int:
+    """Rows every local expert owns per micro-batch: 1.5 x the average it receives, plus a tile."""
+    avg = TOKENS * TOP_K * world // E_TOTAL // micro
+    return (avg * 3 // 2 + 128 + 127) // 128 * 128
+
+
 def one_gpu_record(dev, local: int, fp4_peak: float, steps: int = 5) -> dict:
     """The layer at one rank (all 128 experts local, the dispatch and combine kernels on local buffers), as a
     sub-record of the one-GPU benchmark line: ms per step and its phases."""
@@ -36,12 +42,13 @@ def one_gpu_record(dev, local: int, fp4_peak: float, steps: int = 5) -> dict:
     del z, chi
     logits = torch.randn(TOKENS, E_TOTAL, generator=torch.Generator(device=dev).manual_seed(30), device=dev)
     ids, wts = route_topk(logits, TOP_K)
-    layer = ExpertParallelMoE(E_TOTAL, HIDDEN, INTER, up, down, alignment=128,
-                              peer_rows_cap=int(1.5 * TOKENS * TOP_K) + E_TOTAL * 128)
+    layer = ExpertParallelMoE(E_TOTAL, HIDDEN, INTER, up, down, alignment=128, peer_rows_cap=expert_rows_cap(1, 1),
+                              check_each_step=False)
     sampler = bench.ClockSampler(local)
     sampler.start()
     ms, t0, t1 = bench.timed(lambda: layer(x, ids, wts), steps, 3, lambda: None)
     clocks = sampler.stop(t0, t1)
+    assert layer.read_status() == 0, "an expert overflowed its rows"
     marks = []
     layer.forward_peer(x, ids, wts, marks)
     torch.cuda.synchronize()
@@ -81,12 +88,15 @@ def run(args, workload: str, world: int, rank: int, local: int) -> None:
     # several GPUs: dispatch and combine over peer memory unless ep_peer=0 asks for the NCCL all-to-all path;
     # room for 1.5 x the average rows a rank receives (a step that does not fit falls back by itself)
     use_peer = extra.get("ep_peer", 1) != 0
-    cap = int(1.5 * tokens * TOP_K) + e_local * 128
-    layer = ExpertParallelMoE(E_TOTAL, HIDDEN, INTER, up, down, alignment=128, peer_rows_cap=cap if use_peer else 0)
+    micro = extra.get("ep_micro", 2 if world > 1 else 1)
+    layer = ExpertParallelMoE(E_TOTAL, HIDDEN, INTER, up, down, alignment=128,
+                              peer_rows_cap=expert_rows_cap(world, micro) if use_peer else 0, micro_batches=micro,
+                              check_each_step=False)
     exchange = "nccl all_to_all"
     if layer.peer is not None:
-        exchange = ("peer memory (one dispatch kernel of NVLink stores, one combine kernel of NVLink loads)" if world > 1 else
-                    "one rank: the dispatch and combine kernels on local buffers")
+        exchange = ((f"peer memory, masked layout, {micro} micro-batch(es) on streams of their own (dispatch: NVLink stores, "
+                     "combine: NVLink loads, bounded flag barriers)") if world > 1 else
+                    "one rank: the dispatch and combine kernels on local buffers, masked layout")
     elif use_peer:
         exchange = "nccl all_to_all (symmetric memory unavailable: %s)" % (layer.peer_error or "?")[:200]
 
@@ -101,6 +111,9 @@ def run(args, workload: str, world: int, rank: int, local: int) -> None:
     sampler.start()
     ms, t0, t1 = bench.timed(step, steps, warmup, barrier)
     clocks = sampler.stop(t0, t1)
+    # the timed steps checked nothing on the host: did every step fit its buffers, did every wait end in time?
+    status_bits = layer.read_status() if layer.peer is not None else 0
+    assert status_bits == 0, f"peer-memory steps reported status {status_bits:#x}"
 
     # per-phase device times on this rank (one extra, untimed pass over the all-to-all path, whose phases are
     # separate calls)
@@ -124,6 +137,7 @@ def run(args, workload: str, world: int, rank: int, local: int) -> None:
         marks = []
         y_peer = layer.forward_peer(x, ids, wts, marks)
         torch.cuda.synchronize()
+        assert layer.read_status() == 0
         peer_vs_a2a = float((y_peer.float() - y.float()).norm() / y.float().norm().clamp_min(1e-30))
         peer_phases = [marks[i].elapsed_time(marks[i + 1]) for i in range(4)]
     del plan, a, out
@@ -154,7 +168,9 @@ def run(args, workload: str, world: int, rank: int, local: int) -> None:
     ms_max, e2e_max, flops_all = float(mx[0]), float(mx[1]), float(sm[2])
     # kernels of this library per step: 2 GEMMs x (activation quantisation + GEMM), SwiGLU, and the row movers
     # (+ histogram and the two plan kernels on the peer-memory path)
-    kernels_per_step = 4 + (0 if layer.gemm_swiglu is not None else 1) + (2 + 3 if layer.peer is not None else (2 if world == 1 else 4))
+    # peer path: per micro-batch histogram + 2 plan kernels + dispatch + 2 x (quantise + GEMM) + combine (+ 3 barriers)
+    kernels_per_step = (micro * (9 + (3 if world > 1 else 0)) if layer.peer is not None else
+                        4 + (0 if layer.gemm_swiglu is not None else 1) + (2 if world == 1 else 4))
     if rank == 0:
         fp4_peak = bench.measure_fp4_peak()
         value = flops_all / (ms_max * 1e-3) / 1e12
@@ -174,13 +190,27 @@ def run(args, workload: str, world: int, rank: int, local: int) -> None:
                              "peak_source": "resident-operand tcgen05 kind::mxf4nvf4 loop measured in this run"},
                 "phases_ms_max_over_ranks_all_to_all_path": {"dispatch": float(mx[3]), "experts": gemm_ms, "combine": float(mx[5])},
                 "phases_ms_max_over_ranks_peer_path": ({"plan": float(mx[6]), "dispatch": float(mx[7]), "experts": float(mx[8]),
-                                                        "combine": float(mx[9])} if peer_phases else None),
+                                                        "combine": float(mx[9]),
+                                                        "note": "first micro-batch of one extra step, its stream sharing the GPU with the others'"}
+                                                       if peer_phases else None),
+                "micro_batches": micro,
                 "peer_vs_all_to_all_rel_l2": peer_vs_a2a,
                 "all_to_all_bytes_per_rank_per_direction": off_rank_bytes,
                 "e2e": {"value": flops_all / (e2e_max * 1e-3) / 1e12, "unit": "TFLOP/s", "ms_per_step": e2e_max,
                         "h2d_bytes_per_step": x_host.numel() * 2 + ids_host.numel() * 8 + w_host.numel() * 4,
                         "d2h_bytes_per_step": y_host.numel() * 2},
                 "gpu_launches": kernels_per_step * steps, "kernels_per_step": kernels_per_step, "clocks": clocks}
+        if world == 1:
+            # the one-GPU point of a scaling series: the headline configuration C2 rides along as a sub-record, and the
+            # CPU baseline is timed here as on every one-GPU line
+            del layer, up, down, x, logits
+            torch.cuda.empty_cache()
+            c2 = bench.single_gpu_line("c2", dev, local, 20, 5, {}, cpu_baseline=False, also=False, e2e=False, sustained=False)
+            line["also"] = {"c2": {k: c2[k] for k in ("ms_per_step", "value", "unit", "north_star_path", "rel_l2_vs_fp32")}
+                            | {"frac": c2["roofline"]["frac"], "workload": c2["config"]["workload"]}}
+            if not getattr(args, "no_cpu_baseline", False):
+                base = bench.cpu_reference_sample("c5")
+                line["cpu_baseline"] = {k: base[k] for k in ("value", "unit", "cores", "kind", "sample")}
         print(json.dumps(line))
     if world > 1:
         dist.barrier()

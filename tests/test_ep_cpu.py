@@ -107,14 +107,16 @@ def test_plan_dispatch_places_rows_by_expert():
 
 
 def _peer_plan_worker(rank, world, port, results):
-    """The peer-memory plan against the all-to-all plan: storing every rank's rows at (dst_rank, dst_row) must
-    build, on every owner, exactly the buffer the all-to-all dispatch builds there."""
+    """The peer-memory (masked layout) plan against the all-to-all plan: storing every rank's rows at (dst_rank,
+    dst_row) must give every local expert, in the first masked_m rows of its cap_m-row group, exactly the rows -- in
+    the same order -- that the all-to-all dispatch puts into that expert's padded group."""
     sys.path.insert(0, ROOT)
     os.environ.update(MASTER_ADDR="127.0.0.1", MASTER_PORT=str(port))
     dist.init_process_group("gloo", rank=rank, world_size=world)
     try:
-        from nvfp4_cutlass_b200.ep import ExpertParallelMoE, plan_dispatch_peer, route_topk
-        num_experts, hidden, tokens, top_k, alignment = 8, 32, 24 + 5 * rank, 3, 16
+        from nvfp4_cutlass_b200.ep import ExpertParallelMoE, plan_dispatch_masked, route_topk
+        num_experts, hidden, tokens, top_k, alignment, cap_m = 8, 32, 24 + 5 * rank, 3, 16, 48
+        e_local = num_experts // world
         g = torch.Generator().manual_seed(7 + rank)
         x = torch.randn(tokens, hidden, generator=g).to(torch.bfloat16)
         logits = torch.randn(tokens, num_experts, generator=g)
@@ -122,27 +124,35 @@ def _peer_plan_worker(rank, world, port, results):
         ids, _ = route_topk(logits, top_k)
         layer = ExpertParallelMoE(num_experts, hidden, 16, None, None, alignment=alignment, gemm=_oracle_gemm)
         plan_a2a, a_want = layer.dispatch(x, ids)
-        plan = plan_dispatch_peer(ids, num_experts, world, rank, alignment)
-        rows = x[plan.order // top_k]
+        plan = plan_dispatch_masked(ids, num_experts, world, rank, cap_m)
+        tight = plan_dispatch_masked(ids, num_experts, world, rank, 2)          # a capacity nobody fits
+        rows = x[torch.arange(tokens * top_k) // top_k]
         mine = [None] * world
         dist.all_gather_object(mine, (plan.dst_rank.tolist(), plan.dst_row.tolist(), rows.float().tolist()))
-        a_got = torch.zeros(plan.rows_padded, hidden, dtype=torch.bfloat16)
+        a_got = torch.zeros(e_local, cap_m, hidden, dtype=torch.bfloat16)
         written = set()
         for dst_rank, dst_row, r in mine:
             for dr, row, vals in zip(dst_rank, dst_row, r):
                 if dr == rank:
-                    assert row not in written
+                    assert row not in written and 0 <= row < e_local * cap_m
                     written.add(row)
-                    a_got[row] = torch.tensor(vals).to(torch.bfloat16)
-        results[rank] = (torch.equal(a_got, a_want), plan.group_sizes == plan_a2a.group_sizes,
-                         plan.real_sizes == plan_a2a.real_sizes, plan.max_rows_padded >= plan.rows_padded,
-                         len(written) == sum(plan.real_sizes))
+                    a_got.reshape(-1, hidden)[row] = torch.tensor(vals).to(torch.bfloat16)
+        same = True
+        start = 0
+        for j in range(e_local):
+            real, padded = plan_a2a.real_sizes[j], plan_a2a.group_sizes[j]
+            same &= int(plan.masked_m[j]) == real
+            same &= torch.equal(a_got[j, :real], a_want[start:start + real])
+            same &= bool((a_got[j, real:] == 0).all())
+            start += padded
+        results[rank] = (same, len(written) == sum(plan_a2a.real_sizes), not bool(plan.overflow), bool(tight.overflow),
+                         int((tight.dst_row == -1).sum()) > 0 and int(tight.masked_m.max()) <= 2)
     finally:
         dist.destroy_process_group()
 
 
 @pytest.mark.parametrize("world", [1, 2])
-def test_peer_plan_builds_the_same_buffers_as_the_all_to_all_plan(world):
+def test_masked_peer_plan_gives_every_expert_the_rows_of_the_all_to_all_plan(world):
     mgr = mp.Manager()
     results = mgr.dict()
     mp.spawn(_peer_plan_worker, args=(world, _free_port(), results), nprocs=world, join=True)

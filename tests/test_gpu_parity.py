@@ -320,7 +320,7 @@ def test_split_path_on_two_streams_at_once(dev, oracle):
 @pytest.mark.parametrize("policy", POLICIES[1:])
 def test_gemm_other_scale_policies_match_oracle(dev, oracle, shape, residual, policy):
     """residual_amax, derived_div4 and div4_radix8 on the reference's acceptance shapes (tests/python/test_gemm.py:31-36
-    there) through the default dispatch: the split path for N % 256 == 0 and N >= 1024, a fused kernel otherwise."""
+    there) through the default dispatch: the split path for N % 256 == 0 and N > 1024, a fused kernel otherwise."""
     e, rows, n, k = shape
     a, w = make_case(e, rows, n, k, seed=900 + n + k)
     b, sfb, gw = nvfp4_gemm.quantize_weight_nvfp4(w.to(dev))
