@@ -208,6 +208,8 @@ NVFP4_API int nvfp4_combine_rows(const void* rows, int64_t rows_ld_elems, const 
  * nvfp4_combine_rows_peer: y[t] = sum over j < k of w[t*k+j] * (row src_row[t*k+j] of rank src_rank[t*k+j]'s
  *   buffer), read with plain loads over NVLink.  The caller orders it after every rank has written its buffer.
  *   Pairs out of range (as above) contribute nothing.
+ * sm_budget: the number of SMs the kernel may fill (one 1024-thread block each); 0 = all.  A caller that overlaps these
+ *   kernels with GEMMs on another stream gives them a few SMs and sizes the GEMMs to the rest with nvfp4_set_num_sms.
  * Precondition of both plans: expert ids lie in [0, num_experts); ids outside are ignored by the histogram, get no
  *   row and are skipped by the two movers.
  *
@@ -218,10 +220,10 @@ NVFP4_API int nvfp4_expert_histogram(const int64_t* ids, int64_t n, int num_expe
 NVFP4_API int nvfp4_dispatch_rows_peer(const void* src, int64_t src_ld_bytes, const int64_t* src_idx, int src_div,
                                        const int64_t* peers, const int64_t* dst_rank, const int64_t* dst_row,
                                        int64_t n_rows, int row_bytes, int64_t dst_ld_bytes, int world, int64_t rows_cap,
-                                       int32_t* device_status, void* stream);
+                                       int sm_budget, int32_t* device_status, void* stream);
 NVFP4_API int nvfp4_combine_rows_peer(const int64_t* peers, int64_t rows_ld_elems, const int64_t* src_rank,
                                       const int64_t* src_row, const float* w, int64_t tokens, int k, int hidden,
-                                      void* y, int64_t y_ld_elems, int world, int64_t rows_cap, void* stream);
+                                      void* y, int64_t y_ld_elems, int world, int64_t rows_cap, int sm_budget, void* stream);
 
 /* The routing plan for the masked layout (nvfp4_grouped_gemm_masked): every local expert owns cap_m rows of its
  * rank's buffer, so nothing about the plan has to come back to the host.  all_counts[s * E + e] = pairs rank s routes

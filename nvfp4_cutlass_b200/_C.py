@@ -60,12 +60,12 @@ def lib() -> ctypes.CDLL:
         L.nvfp4_debug_decompose.argtypes = [vp, i64, i32, i32, i32, vp, vp, vp, vp, vp]
         L.nvfp4_permute_rows.argtypes = [vp, i64, vp, i32, vp, i64, i32, vp, i64, vp]
         L.nvfp4_swiglu.argtypes = [vp, i64, i64, i32, vp, i64, vp]
-        L.nvfp4_dispatch_rows_peer.argtypes = [vp, i64, vp, i32, vp, vp, vp, i64, i32, i64, i32, i64, vp, vp]
+        L.nvfp4_dispatch_rows_peer.argtypes = [vp, i64, vp, i32, vp, vp, vp, i64, i32, i64, i32, i64, i32, vp, vp]
         L.nvfp4_plan_peer_masked.argtypes = [vp, i32, i32, i32, i32, vp, i64, vp, vp, vp, vp, vp, vp]
         L.nvfp4_peer_barrier.argtypes = [vp, i32, i32, i32, i64, i64, vp, vp]
         L.nvfp4_expert_histogram.argtypes = [vp, i64, i32, vp, vp]
         L.nvfp4_grouped_gemm_swiglu_contiguous.argtypes = [vp, i64, vp, vp, vp, vp, i64, vp, i32, i32, i32, i32, i32, vp, vp, vp]
-        L.nvfp4_combine_rows_peer.argtypes = [vp, i64, vp, vp, vp, i64, i32, i32, vp, i64, i32, i64, vp]
+        L.nvfp4_combine_rows_peer.argtypes = [vp, i64, vp, vp, vp, i64, i32, i32, vp, i64, i32, i64, i32, vp]
         L.nvfp4_combine_rows.argtypes = [vp, i64, vp, vp, i64, i32, i32, vp, i64, vp]
         L.nvfp4_grouped_gemm_masked.argtypes = [vp, i64, vp, vp, vp, vp, i64, vp, i32, i32, i32, i32, i32, i32, i32, vp, vp, vp]
         L.nvfp4_load_checkpoint_weights.argtypes = [i32, vp, vp, vp, vp, i32, i32, i32, vp, vp, vp, vp]
@@ -390,7 +390,7 @@ def peer_barrier(flag_peers: torch.Tensor, rank: int, world: int, slot: int, epo
 
 
 def dispatch_rows_peer(src: torch.Tensor, src_idx, src_div: int, peers: torch.Tensor, dst_rank: torch.Tensor,
-                       dst_row: torch.Tensor, dst_ld_elems: int, rows_cap: int, status: torch.Tensor = None) -> None:
+                       dst_row: torch.Tensor, dst_ld_elems: int, rows_cap: int, status: torch.Tensor = None, sm_budget: int = 0) -> None:
     """Row src[(src_idx[i] or i) // src_div] -> row dst_row[i] of rank dst_rank[i]'s buffer (`peers`: int64 base
     addresses, `rows_cap` rows each); pairs out of range are skipped."""
     n = dst_row.numel()
@@ -400,12 +400,12 @@ def dispatch_rows_peer(src: torch.Tensor, src_idx, src_div: int, peers: torch.Te
     with torch.cuda.device(_one_device(src, src_idx, peers, dst_rank, dst_row, status)):
         _check(lib().nvfp4_dispatch_rows_peer(src.data_ptr(), src.stride(0) * 2, src_idx.data_ptr() if src_idx is not None else None,
                                               src_div, peers.data_ptr(), dst_rank.data_ptr(), dst_row.data_ptr(), n, src.shape[1] * 2,
-                                              dst_ld_elems * 2, peers.numel(), rows_cap,
+                                              dst_ld_elems * 2, peers.numel(), rows_cap, int(sm_budget),
                                               status.data_ptr() if status is not None else None, _stream()))
 
 
 def combine_rows_peer(peers: torch.Tensor, rows_ld_elems: int, src_rank: torch.Tensor, src_row: torch.Tensor, w: torch.Tensor,
-                      tokens: int, hidden: int, rows_cap: int, out: torch.Tensor = None) -> torch.Tensor:
+                      tokens: int, hidden: int, rows_cap: int, out: torch.Tensor = None, sm_budget: int = 0) -> torch.Tensor:
     """y[t] = sum_j w[t, j] * (row src_row[t, j] of rank src_rank[t, j]'s buffer), BF16, into `out` if given."""
     n = src_rank.numel()
     _require(_i64_ok(src_rank, n) and _i64_ok(src_row, n) and _i64_ok(peers, 1) and w.is_cuda and w.dtype == torch.float32 and
@@ -415,7 +415,7 @@ def combine_rows_peer(peers: torch.Tensor, rows_ld_elems: int, src_rank: torch.T
     k = n // tokens if tokens else 1
     with torch.cuda.device(_one_device(peers, src_rank, src_row, w)):
         _check(lib().nvfp4_combine_rows_peer(peers.data_ptr(), rows_ld_elems, src_rank.data_ptr(), src_row.data_ptr(), w.data_ptr(),
-                                             tokens, k, hidden, y.data_ptr(), y.stride(0), peers.numel(), rows_cap, _stream()))
+                                             tokens, k, hidden, y.data_ptr(), y.stride(0), peers.numel(), rows_cap, int(sm_budget), _stream()))
     return y
 
 

@@ -494,7 +494,7 @@ int nvfp4_peer_barrier(const int64_t* flag_peers, int rank, int world, int slot,
 
 int nvfp4_dispatch_rows_peer(const void* src, int64_t src_ld_bytes, const int64_t* src_idx, int src_div, const int64_t* peers,
                              const int64_t* dst_rank, const int64_t* dst_row, int64_t n_rows, int row_bytes, int64_t dst_ld_bytes,
-                             int world, int64_t rows_cap, int32_t* device_status, void* stream)
+                             int world, int64_t rows_cap, int sm_budget, int32_t* device_status, void* stream)
 {
     host::clear_error();
     NVFP4_REQUIRE(n_rows >= 0 && row_bytes > 0 && row_bytes % 16 == 0, "row_bytes must be a positive multiple of 16 (got %d)", row_bytes);
@@ -506,13 +506,15 @@ int nvfp4_dispatch_rows_peer(const void* src, int64_t src_ld_bytes, const int64_
     NVFP4_REQUIRE((reinterpret_cast<uintptr_t>(src) & 15u) == 0, "rows must be 16-byte aligned");
     host::DeviceInfo* dev;
     if (int rc = host::device_info(-1, &dev)) return rc;
+    NVFP4_REQUIRE(sm_budget >= 0, "sm_budget must not be negative");
     return launch_dispatch_rows_peer(src, src_ld_bytes, src_idx, src_div, peers, dst_rank, dst_row, n_rows, row_bytes, dst_ld_bytes,
-                                     world, rows_cap, device_status, dev->num_sms, static_cast<cudaStream_t>(stream));
+                                     world, rows_cap, device_status, sm_budget > 0 && sm_budget < dev->hw_sms ? sm_budget : dev->hw_sms,
+                                     static_cast<cudaStream_t>(stream));
 }
 
 int nvfp4_combine_rows_peer(const int64_t* peers, int64_t rows_ld_elems, const int64_t* src_rank, const int64_t* src_row,
                             const float* w, int64_t tokens, int k, int hidden, void* y, int64_t y_ld_elems, int world,
-                            int64_t rows_cap, void* stream)
+                            int64_t rows_cap, int sm_budget, void* stream)
 {
     host::clear_error();
     NVFP4_REQUIRE(tokens >= 0 && k >= 1 && hidden > 0 && hidden % 8 == 0, "k >= 1 and hidden a positive multiple of 8 (k=%d, hidden=%d)", k, hidden);
@@ -524,8 +526,10 @@ int nvfp4_combine_rows_peer(const int64_t* peers, int64_t rows_ld_elems, const i
     NVFP4_REQUIRE((reinterpret_cast<uintptr_t>(y) & 15u) == 0, "rows must be 16-byte aligned");
     host::DeviceInfo* dev;
     if (int rc = host::device_info(-1, &dev)) return rc;
+    NVFP4_REQUIRE(sm_budget >= 0, "sm_budget must not be negative");
     return launch_combine_rows_peer(peers, rows_ld_elems, src_rank, src_row, w, tokens, k, hidden, y, y_ld_elems, world, rows_cap,
-                                    dev->num_sms, static_cast<cudaStream_t>(stream));
+                                    sm_budget > 0 && sm_budget < dev->hw_sms ? sm_budget : dev->hw_sms,
+                                    static_cast<cudaStream_t>(stream));
 }
 
 int nvfp4_debug_decompose(const void* a, int64_t lda_elems, int M, int K, int scale_policy, void* q0, void* q1,

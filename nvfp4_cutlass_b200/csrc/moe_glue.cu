@@ -95,41 +95,60 @@ combine_rows_kernel(const uint4* __restrict__ rows, int64_t rows_ld16, const int
 // crossing NVLink once as plain 16-byte stores.
 // A pair whose rank or row is outside [0, world) x [0, rows_cap) is skipped (row -1 is how the plan marks a pair that
 // does not fit its expert's capacity; anything else out of range also raises bit 3 of the status word).
-__global__ void __launch_bounds__(256)
+//
+// Both peer kernels run as a few FAT blocks -- 1024 threads, one warp per row, eight 16-byte accesses in flight per
+// thread -- on as many SMs as the caller grants them (`sm_budget`; 0 = every SM).  A block fills its SM, so it never
+// shares one with a GEMM block: with the micro-batches of a step on streams of their own and the GEMMs sized to the
+// other SMs (nvfp4_set_num_sms), the NVLink traffic of one micro-batch runs beside the GEMMs of another whichever
+// kernel is launched first.  (Slim blocks tucked into the registers a resident GEMM block leaves free were tried
+// first: ~170 threads per SM cannot keep enough loads in flight for NVLink's latency.)  Sixteen SMs carry more than
+// the ~0.7 TB/s an NVLink port takes.
+constexpr int kPeerThreads = 1024;
+__global__ void __launch_bounds__(kPeerThreads, 1)
 dispatch_rows_peer_kernel(const uint4* __restrict__ src, int64_t src_ld16, const int64_t* __restrict__ src_idx, int src_div,
                           const int64_t* __restrict__ peers, const int64_t* __restrict__ dst_rank,
                           const int64_t* __restrict__ dst_row, int64_t n_rows, int row16, int64_t dst_ld16, int world,
                           int64_t rows_cap, int32_t* __restrict__ status)
 {
-    for (int64_t i = blockIdx.x; i < n_rows; i += gridDim.x) {
+    const int lane = threadIdx.x & 31, warps = kPeerThreads / 32;
+    for (int64_t i = static_cast<int64_t>(blockIdx.x) * warps + (threadIdx.x >> 5); i < n_rows; i += static_cast<int64_t>(gridDim.x) * warps) {
         const int64_t r = dst_rank[i], row = dst_row[i];
         if (r < 0 || r >= world || row < 0 || row >= rows_cap) {
-            if (row != -1 && threadIdx.x == 0 && status != nullptr) atomicOr(status, 8);
+            if (row != -1 && lane == 0 && status != nullptr) atomicOr(status, 8);
             continue;
         }
         const uint4* sp = src + ((src_idx ? src_idx[i] : i) / src_div) * src_ld16;
         uint4* dp = reinterpret_cast<uint4*>(peers[r]) + row * dst_ld16;
-        for (int c = threadIdx.x; c < row16; c += blockDim.x) dp[c] = __ldg(sp + c);
+        int c = lane;
+        for (; c + 7 * 32 < row16; c += 8 * 32) {
+            uint4 v[8];
+#pragma unroll
+            for (int u = 0; u < 8; ++u) v[u] = __ldg(sp + c + u * 32);
+#pragma unroll
+            for (int u = 0; u < 8; ++u) dp[c + u * 32] = v[u];
+        }
+        for (; c < row16; c += 32) dp[c] = __ldg(sp + c);
     }
 }
 
 // combine: y[t] = sum_j w[t, j] * (row src_row[t, j] of rank src_rank[t, j]'s output buffer), read over NVLink
-// with plain loads (the data was written by another GPU during this step: no read-only cache path).
-__global__ void __launch_bounds__(256)
+// with plain loads (the data was written by another GPU during this step: no read-only cache path).  One warp per
+// token; for every 16-byte piece of the row the loads of up to eight experts go out together (a round trip over NVLink
+// is a few microseconds) and are consumed in order, so the sum stays in ascending j.
+__global__ void __launch_bounds__(kPeerThreads, 1)
 combine_rows_peer_kernel(const int64_t* __restrict__ peers, int64_t rows_ld16, const int64_t* __restrict__ src_rank,
                          const int64_t* __restrict__ src_row, const float* __restrict__ w, int64_t tokens, int k, int row16,
                          uint4* __restrict__ y, int64_t y_ld16, int world, int64_t rows_cap)
 {
-    for (int64_t t = blockIdx.x; t < tokens; t += gridDim.x) {
-        for (int c = threadIdx.x; c < row16; c += blockDim.x) {
+    const int lane = threadIdx.x & 31, warps = kPeerThreads / 32;
+    for (int64_t t = static_cast<int64_t>(blockIdx.x) * warps + (threadIdx.x >> 5); t < tokens; t += static_cast<int64_t>(gridDim.x) * warps) {
+        for (int c = lane; c < row16; c += 32) {
             float acc[8] = {0, 0, 0, 0, 0, 0, 0, 0};
-            // four rows at a time: the loads go out together (a round trip over NVLink is a few microseconds) and
-            // are consumed in order, so the sum stays in ascending j
-            for (int j0 = 0; j0 < k; j0 += 4) {
-                uint4 v[4];
-                float wj[4];
+            for (int j0 = 0; j0 < k; j0 += 8) {
+                uint4 v[8];
+                float wj[8];
 #pragma unroll
-                for (int u = 0; u < 4; ++u) {
+                for (int u = 0; u < 8; ++u) {
                     const int j = j0 + u < k ? j0 + u : k - 1;
                     const int64_t pr = src_rank[t * k + j], prow = src_row[t * k + j];
                     const bool valid = j0 + u < k && pr >= 0 && pr < world && prow >= 0 && prow < rows_cap;   // else: contributes nothing
@@ -142,7 +161,7 @@ combine_rows_peer_kernel(const int64_t* __restrict__ peers, int64_t rows_ld16, c
                     }
                 }
 #pragma unroll
-                for (int u = 0; u < 4; ++u) {
+                for (int u = 0; u < 8; ++u) {
                     if (j0 + u >= k) break;
                     const uint32_t vw[4] = {v[u].x, v[u].y, v[u].z, v[u].w};
 #pragma unroll
@@ -340,7 +359,7 @@ int launch_dispatch_rows_peer(const void* src, int64_t src_ld_bytes, const int64
                               const int64_t* dst_rank, const int64_t* dst_row, int64_t n_rows, int row_bytes,
                               int64_t dst_ld_bytes, int world, int64_t rows_cap, int32_t* status, int num_sms, cudaStream_t stream)
 {
-    dispatch_rows_peer_kernel<<<grid_for(n_rows, num_sms), 256, 0, stream>>>(
+    dispatch_rows_peer_kernel<<<static_cast<unsigned>(num_sms), kPeerThreads, 0, stream>>>(
         static_cast<const uint4*>(src), src_ld_bytes / 16, src_idx, src_div, peers, dst_rank, dst_row, n_rows, row_bytes / 16,
         dst_ld_bytes / 16, world, rows_cap, status);
     NVFP4_CUDA_CHECK(cudaGetLastError());
@@ -351,7 +370,7 @@ int launch_combine_rows_peer(const int64_t* peers, int64_t rows_ld_elems, const 
                              const float* w, int64_t tokens, int k, int hidden, void* y, int64_t y_ld_elems, int world,
                              int64_t rows_cap, int num_sms, cudaStream_t stream)
 {
-    combine_rows_peer_kernel<<<grid_for(tokens, num_sms), 256, 0, stream>>>(peers, rows_ld_elems / 8, src_rank, src_row, w, tokens,
+    combine_rows_peer_kernel<<<static_cast<unsigned>(num_sms), kPeerThreads, 0, stream>>>(peers, rows_ld_elems / 8, src_rank, src_row, w, tokens,
                                                                              k, hidden / 8, static_cast<uint4*>(y), y_ld_elems / 8,
                                                                              world, rows_cap);
     NVFP4_CUDA_CHECK(cudaGetLastError());

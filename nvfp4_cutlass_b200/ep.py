@@ -211,7 +211,7 @@ class ExpertParallelMoE:
 
     def __init__(self, num_experts: int, hidden: int, inter: int, up, down, group=None, alignment: int = 128,
                  gemm: Optional[Callable] = None, native_glue: bool = True, peer_rows_cap: int = 0, micro_batches: int = 1,
-                 check_each_step: bool = True):
+                 check_each_step: bool = True, comm_sms: int = 16):
         self.group = group
         self.world = dist.get_world_size(group) if dist.is_initialized() else 1
         self.rank = dist.get_rank(group) if dist.is_initialized() else 0
@@ -235,6 +235,10 @@ class ExpertParallelMoE:
         # expert receives more takes the all-to-all path instead -- on every rank, since all see the same histograms.
         self.micro = max(1, int(micro_batches))
         self.check_each_step = check_each_step
+        # With several micro-batches the dispatch and combine kernels get `comm_sms` SMs to themselves and the GEMMs are
+        # sized to the others, so that one micro-batch's NVLink traffic runs beside another's GEMMs whichever is
+        # launched first; with one micro-batch nothing overlaps and every kernel uses the whole GPU.
+        self.comm_sms = int(comm_sms) if self.micro > 1 else 0
         self.peer = None                       # list of PeerBuffers, one per micro-batch in flight
         self.peer_error = None
         self.steps_repeated = 0                # steps that overflowed the buffers and were repeated over the all-to-all path
@@ -340,7 +344,8 @@ class ExpertParallelMoE:
         pending = [0, 1, 2]                         # barrier slots of this step still to be enqueued
         try:
             buf.barrier(pending.pop(0))             # every rank has finished with these buffers (its previous step on them)
-            _C.dispatch_rows_peer(x, None, k, buf.a_peers, plan.dst_rank, plan.dst_row, self.hidden, buf.rows_cap, buf.status)
+            _C.dispatch_rows_peer(x, None, k, buf.a_peers, plan.dst_rank, plan.dst_row, self.hidden, buf.rows_cap, buf.status,
+                                  sm_budget=self.comm_sms)
             buf.barrier(pending.pop(0))             # all rows have landed everywhere
             mark()
             self.gemm_masked(buf.a, *self.up, buf.h, plan.masked_m, device_status=buf.status)
@@ -348,7 +353,7 @@ class ExpertParallelMoE:
             mark()
             buf.barrier(pending.pop(0))             # every rank's expert outputs are complete
             _C.combine_rows_peer(buf.out_peers, self.hidden, plan.dst_rank, plan.dst_row, w_flat, x.shape[0], self.hidden,
-                                 buf.rows_cap, out=y)
+                                 buf.rows_cap, out=y, sm_budget=self.comm_sms)
             mark()
         except BaseException:
             for slot in pending:
@@ -365,15 +370,21 @@ class ExpertParallelMoE:
         if self.micro == 1 or tokens < self.micro:
             self._peer_step(self.peer[0], x, topk_ids, topk_w, y, marks)
             return y
+        from . import _C
         cur = torch.cuda.current_stream()
         bounds = [tokens * i // self.micro for i in range(self.micro + 1)]
-        for i, stream in enumerate(self.streams):
-            lo, hi = bounds[i], bounds[i + 1]
-            stream.wait_stream(cur)
-            with torch.cuda.stream(stream):
-                self._peer_step(self.peer[i], x[lo:hi], topk_ids[lo:hi], topk_w[lo:hi], y[lo:hi], marks if i == 0 else None)
-        for stream in self.streams:
-            cur.wait_stream(stream)
+        all_sms = _C.get_num_sms()
+        _C.set_num_sms(max(all_sms - self.comm_sms, 1))      # the GEMMs leave the communication kernels their SMs
+        try:
+            for i, stream in enumerate(self.streams):
+                lo, hi = bounds[i], bounds[i + 1]
+                stream.wait_stream(cur)
+                with torch.cuda.stream(stream):
+                    self._peer_step(self.peer[i], x[lo:hi], topk_ids[lo:hi], topk_w[lo:hi], y[lo:hi], marks if i == 0 else None)
+            for stream in self.streams:
+                cur.wait_stream(stream)
+        finally:
+            _C.set_num_sms(all_sms)
         return y
 
     def read_status(self) -> int:

@@ -88,10 +88,12 @@ def run(args, workload: str, world: int, rank: int, local: int) -> None:
     # several GPUs: dispatch and combine over peer memory unless ep_peer=0 asks for the NCCL all-to-all path;
     # room for 1.5 x the average rows a rank receives (a step that does not fit falls back by itself)
     use_peer = extra.get("ep_peer", 1) != 0
-    micro = extra.get("ep_micro", 2 if world > 1 else 1)
+    # micro-batches on streams of their own were measured no faster on 2 GPUs (4.5-5.3 ms against 4.64 ms: the SMs the
+    # communication kernels need to keep NVLink busy are taken from the GEMMs), so a step is one batch unless asked
+    micro = extra.get("ep_micro", 1)
     layer = ExpertParallelMoE(E_TOTAL, HIDDEN, INTER, up, down, alignment=128,
                               peer_rows_cap=expert_rows_cap(world, micro) if use_peer else 0, micro_batches=micro,
-                              check_each_step=False)
+                              check_each_step=False, comm_sms=extra.get("ep_comm_sms", 16))
     exchange = "nccl all_to_all"
     if layer.peer is not None:
         exchange = ((f"peer memory, masked layout, {micro} micro-batch(es) on streams of their own (dispatch: NVLink stores, "
