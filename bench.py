@@ -61,8 +61,8 @@ WORKLOADS = {
 # under profiles/, on the reduced workloads c2s / c4s (the full ones exceed what a multi-pass capture should
 # hold), as (bytes measured, algorithmic bytes of that captured launch).  Both kernels stream every operand
 # once, so traffic grows in proportion to the algorithmic bytes; a full launch is scaled by that ratio.
-NCU_TRAFFIC = {"normal": (246.79e6, 251.66e6, "split-path kernels on c2s, captured at commit 643bd80"),
-               "swap_ab": (925.54e6, 911.22e6, "decode kernel on c4s, captured at commit 643bd80")}
+NCU_TRAFFIC = {"normal": (246.59e6, 251.66e6, "split-path kernels on c2s, captured at commit 70bfc9c"),
+               "swap_ab": (925.44e6, 911.22e6, "decode kernel on c4s, captured at commit 70bfc9c")}
 
 
 def scaled_traffic(orientation: str, algo_bytes: float) -> dict:
@@ -543,6 +543,8 @@ def main():
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--no-cpu-baseline", action="store_true")
     ap.add_argument("--no-also", action="store_true", help="skip the sub-records of the other configurations")
+    ap.add_argument("--quick", action="store_true", help="the timed region only: no sustained / end-to-end / north-star / "
+                    "other-configuration / CPU legs (what a profiler capture wants)")
     ap.add_argument("--graph", action="store_true", help="time CUDA-graph replays of one call (the reference's method)")
     ap.add_argument("--tune", action="append", default=[], help="tune_xxx=int passed to the GEMM call (experiments)")
     args = ap.parse_args()
@@ -564,12 +566,17 @@ def main():
     steps = args.steps or 20
     warmup = max(args.warmup if args.warmup is not None else 5, 3)
     extra = {kv.split('=')[0]: int(kv.split('=')[1]) for kv in args.tune}
-    line = single_gpu_line(workload, dev, local, steps, warmup, extra, args.graph, cpu_baseline=not args.no_cpu_baseline,
-                           also=not args.no_also and workload == "c2" and not extra)
+    if args.quick:
+        line = single_gpu_line(workload, dev, local, steps, warmup, extra, args.graph, cpu_baseline=False, also=False, e2e=False,
+                               sustained=False, north_star=False)
+    else:
+        line = single_gpu_line(workload, dev, local, steps, warmup, extra, args.graph, cpu_baseline=not args.no_cpu_baseline,
+                               also=not args.no_also and workload == "c2" and not extra)
     print(json.dumps(line))
 
 
-def single_gpu_line(workload, dev, local, steps, warmup, extra, graph=False, cpu_baseline=True, also=False, e2e=True, sustained=True):
+def single_gpu_line(workload, dev, local, steps, warmup, extra, graph=False, cpu_baseline=True, also=False, e2e=True, sustained=True,
+                    north_star=True):
     """The JSON line of a one-GPU grouped-GEMM workload."""
     import nvfp4_gemm
     case = build_single_gpu_case(workload, dev, extra)
@@ -618,7 +625,9 @@ def single_gpu_line(workload, dev, local, steps, warmup, extra, graph=False, cpu
             line["sustained"]["frac_of_sustained_peak"] = ach / roofline["peak_sustained"]
 
     # the north-star path (Algorithm 1 inside the GEMM main loop) on the same inputs, whatever the default is
-    if case["swap"]:
+    if not north_star:
+        pass
+    elif case["swap"]:
         line["north_star_path"] = {"ms_per_step": rec["ms_per_step"], "value": rec["value"], "unit": "TFLOP/s", "frac": rec["frac"],
                                    "note": "the decode kernel decomposes the activations inside its main loop: this is the default path"}
     elif not is_split:
