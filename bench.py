@@ -200,6 +200,8 @@ def build_single_gpu_case(workload: str, dev, extra_kw=None, weights=None):
     m_indices = nvfp4_gemm.make_m_indices(padded, alignment=align).to(dev)
     b, sfb, gw = weights if weights is not None else build_weights(E, N, K, dev, seed=2)
     kw = dict(tune_swap_ab=1, m_alignment=align) if swap else {}
+    if not swap and all(pz % 256 == 0 for pz in padded):
+        kw["m_alignment"] = 256                             # every group is whole 256-row pairs: the caller may say so
     kw.update(extra_kw or {})
     active = sum(1 for r in real if r > 0)
     return dict(a=a, b=b, sfb=sfb, gw=gw, m_indices=m_indices, M=M, N=N, K=K, E=E, real_rows=sum(real),
@@ -585,8 +587,12 @@ def single_gpu_line(workload, dev, local, steps, warmup, extra, graph=False, cpu
     rec, d, step = gemm_record(case, dev, steps, warmup, fp4_peak, graph=graph, extra=extra, local=local)
     roofline = rec["roofline"]
     is_split = split_default(case, extra)
-    path = ("split: quantize_activation_kernel (Algorithm 1 once per element, into an L2-resident workspace) + "
-            "gemm_split_kernel (block-scaled FP4 GEMM)") if is_split else (
+    pair = case["kw"].get("m_alignment") == 256 or extra.get("tune_cluster") == 2 or case["M"] // case["E"] >= 2048
+    if extra.get("tune_cluster") == 1:
+        pair = False
+    path = ("split: quantize_activation_kernel (Algorithm 1 once per element, into an L2-resident workspace) + " +
+            ("gemm_split_pair_kernel (block-scaled FP4 GEMM, CTA pairs: tcgen05.mma.cta_group::2 over 256 rows x 256 columns; "
+             "the call states m_alignment=256)" if pair else "gemm_split_kernel (block-scaled FP4 GEMM)")) if is_split else (
             "decode: gemm_swap_kernel, Algorithm 1 in the main loop" if case["swap"] else
             "fused: Algorithm 1 in the main loop of the GEMM kernel")
     logical = 2.0 * case["real_rows"] * N * K

@@ -102,13 +102,16 @@ NVFP4_API int nvfp4_quantize_weight_static(const void* w, int w_dtype, int E, in
  *   d          (M, N) BF16, row stride ldd_elems, written in place
  *   m_indices  (M,) int32 expert id of each row; each expert's rows start on an
  *              m_alignment boundary (128 normal, 16/32/64/128 swap-AB); only the
- *              first row of each aligned block is read, negative ids read as 0
+ *              first row of each aligned block is read, negative ids read as 0.  Normal
+ *              orientation also takes m_alignment 256: a statement that every expert's rows
+ *              are a multiple of 256, which lets the split path run its CTA-pair GEMM
+ *              (two CTAs, one tcgen05.mma.cta_group::2 over 256 rows) without left-over blocks
  *   enable_residual_pass 0 = the single_nvfp4 variant (second pass skipped)
  *   tune       optional host array of 18 int32 in the order of the reference's
  *              tune_* keywords (src/api.hpp:166-203), or NULL; 0 = default.  Honoured: [0] block_n
  *              (swap-AB token tile 16/32/64), [1] transform_warps (8/16: single-CTA fused kernel),
- *              [5] block_k, [7] swap_ab is the `orientation` argument, [8] cluster (1/2/4 CTAs share
- *              a transformed activation tile), [9] direct_a, [11] no_pdl, [12] sched_group,
+ *              [5] block_k, [7] swap_ab is the `orientation` argument, [8] cluster (fused kernels: 1/2/4 CTAs share
+ *              a transformed activation tile; split path: 2 = CTA-pair GEMM kernel, 1 = single-CTA), [9] direct_a, [11] no_pdl, [12] sched_group,
  *              [13] split_transform.  NOTE [13] means something else than in the reference (there:
  *              signal A0 early inside its one kernel): here 1 = quantise the activations once in a
  *              kernel of their own ahead of the GEMM, 2 = Algorithm 1 inside the GEMM main loop,
@@ -276,6 +279,10 @@ NVFP4_API int nvfp4_debug_wait_timeout(int64_t budget_cycles, int32_t* device_st
  * `flops_per_launch` the number of floating-point operations one launch performs.
  * Used to measure the tensor-pipe ceiling the roofline fractions are quoted against. */
 NVFP4_API int nvfp4_debug_mma_peak(int iters, double* flops_per_launch, void* stream);
+
+/* The same for CTA pairs: every two SMs run one thread-block cluster of two CTAs whose even CTA issues
+ * 256 x 256 x 64 MMAs (tcgen05.mma.cta_group::2) over both tensor cores. */
+NVFP4_API int nvfp4_debug_mma_peak_pair(int iters, double* flops_per_launch, void* stream);
 
 /* Measurement hook: like nvfp4_debug_mma_peak, with the issue pattern of a K block made
  * explicit: per round `num_cp` scale-factor copies (tcgen05.cp 32x128b.warpx4) followed by

@@ -28,7 +28,7 @@ TUNE_KEYS = ("tune_block_n", "tune_transform_warps", "tune_epilogue_threads", "t
 
 EXPORTS = ("nvfp4_last_error", "nvfp4_version", "nvfp4_get_num_sms", "nvfp4_set_num_sms",
            "nvfp4_quantize_weight", "nvfp4_quantize_weight_static", "nvfp4_grouped_gemm_contiguous", "nvfp4_debug_decompose",
-           "nvfp4_debug_mma_peak", "nvfp4_debug_mma_pattern", "nvfp4_permute_rows", "nvfp4_swiglu", "nvfp4_combine_rows",
+           "nvfp4_debug_mma_peak", "nvfp4_debug_mma_peak_pair", "nvfp4_debug_mma_pattern", "nvfp4_permute_rows", "nvfp4_swiglu", "nvfp4_combine_rows",
            "nvfp4_dispatch_rows_peer", "nvfp4_combine_rows_peer", "nvfp4_expert_histogram",
            "nvfp4_grouped_gemm_swiglu_contiguous", "nvfp4_grouped_gemm_masked", "nvfp4_load_checkpoint_weights",
            "nvfp4_read_status", "nvfp4_debug_split_workspace", "nvfp4_debug_wait_timeout", "nvfp4_plan_peer_masked",
@@ -73,6 +73,7 @@ def lib() -> ctypes.CDLL:
         L.nvfp4_debug_split_workspace.argtypes = [vp, i64, i32, i32, i32, i32, i32, vp, vp, vp, vp]
         L.nvfp4_debug_wait_timeout.argtypes = [i64, vp, vp]
         L.nvfp4_debug_mma_peak.argtypes = [i32, ctypes.POINTER(ctypes.c_double), vp]
+        L.nvfp4_debug_mma_peak_pair.argtypes = [i32, ctypes.POINTER(ctypes.c_double), vp]
         L.nvfp4_debug_mma_pattern.argtypes = [i32, i32, i32, i32, i32, ctypes.POINTER(ctypes.c_double), vp]
         _lib = L
     return _lib
@@ -438,6 +439,13 @@ def debug_mma_peak(iters: int) -> float:
     """Launches the resident-operand FP4 MMA loop once; returns the FLOPs of the launch."""
     flops = ctypes.c_double(0.0)
     _check(lib().nvfp4_debug_mma_peak(int(iters), ctypes.byref(flops), _stream()))
+    return flops.value
+
+
+def debug_mma_peak_pair(iters: int) -> float:
+    """Launch the CTA-pair (cta_group::2) resident-operand MMA loop; returns the FLOPs of the launch."""
+    flops = ctypes.c_double(0.0)
+    _check(lib().nvfp4_debug_mma_peak_pair(int(iters), ctypes.byref(flops), _stream()))
     return flops.value
 
 

@@ -200,6 +200,19 @@ int nvfp4_quantize_weight_static(const void* w, int w_dtype, int E, int N, int K
     return launch_quantize_weight_static(w, w_dtype, E, N, K, b, sfb, gw, static_cast<cudaStream_t>(stream));
 }
 
+// Which GEMM kernel the split path runs: tune_cluster = 2 the CTA-pair kernel (cta_group::2, 256 rows x 256 columns per
+// pair), 1 the single-CTA kernel, 0 the library's choice.  A pair tile needs two row blocks of one expert, and an
+// expert's odd last block costs a whole pair tile.  The pair kernel's main loop is ~5 % faster, so it is chosen when that
+// waste is known to be nil (the caller states that every group is a multiple of 256 rows) or small (experts with
+// 16 row blocks and more on average).
+static bool split_gemm_as_pair(const int32_t* tune, int64_t rows, int experts, bool groups_of_256)
+{
+    const int knob = tune ? tune[8] : 0;
+    if (knob == 2) return true;
+    if (knob == 1) return false;
+    return groups_of_256 || (experts > 0 && rows / experts >= 2048);
+}
+
 int nvfp4_grouped_gemm_contiguous(const void* a, int64_t lda_elems, const void* b, const void* sfb, const float* gw,
                                   void* d, int64_t ldd_elems, const int32_t* m_indices, int M, int N, int K, int E,
                                   int scale_policy, int enable_residual_pass, int orientation, int m_alignment,
@@ -212,7 +225,8 @@ int nvfp4_grouped_gemm_contiguous(const void* a, int64_t lda_elems, const void* 
     NVFP4_REQUIRE(orientation == NVFP4_ORIENT_NORMAL || orientation == NVFP4_ORIENT_SWAP_AB, "unknown orientation %d", orientation);
     if (orientation == NVFP4_ORIENT_NORMAL) {
         if (m_alignment == 0) m_alignment = 128;
-        NVFP4_REQUIRE(m_alignment == 128, "normal orientation needs m_alignment 128, got %d", m_alignment);
+        NVFP4_REQUIRE(m_alignment == 128 || m_alignment == 256, "normal orientation needs m_alignment 128 or 256, got %d",
+                      m_alignment);
     } else {
         if (m_alignment == 0) m_alignment = 32;
         NVFP4_REQUIRE(m_alignment == 16 || m_alignment == 32 || m_alignment == 64 || m_alignment == 128,
@@ -269,7 +283,7 @@ int nvfp4_grouped_gemm_contiguous(const void* a, int64_t lda_elems, const void* 
         const int tune_block_k = tune ? tune[5] : 0;
         return launch_gemm_split(a, lda_elems, b, sfb, gw, d, ldd_elems, m_indices, nullptr, 0, M, N, K, E,
                                  enable_residual_pass != 0, tune_block_k, tune_sched_group, pdl, scale_policy, false,
-                                 dev->num_sms, device_status, s);
+                                 dev->num_sms, split_gemm_as_pair(tune, M, E, m_alignment == 256), device_status, s);
     }
     int cluster = tune ? tune[8] : 0;
     NVFP4_REQUIRE(cluster == 0 || cluster == 1 || cluster == 2 || cluster == 4, "tune_cluster must be 0, 1, 2 or 4");
@@ -357,7 +371,8 @@ int nvfp4_grouped_gemm_swiglu_contiguous(const void* h, int64_t ldh_elems, const
     if (dev->cc_major != 10) return host::fail(NVFP4_E_UNSUPPORTED, "needs an sm_100 GPU, found sm_%d%d", dev->cc_major, dev->cc_minor);
     return launch_gemm_split(h, ldh_elems, b, sfb, gw, d, ldd_elems, m_indices, nullptr, 0, M, N, K, E,
                              enable_residual_pass != 0, tune ? tune[5] : 0, tune ? tune[12] : 0, !(tune && tune[11]),
-                             NVFP4_POLICY_DERIVED_DIV8, true, dev->num_sms, device_status, static_cast<cudaStream_t>(stream));
+                             NVFP4_POLICY_DERIVED_DIV8, true, dev->num_sms, split_gemm_as_pair(tune, M, E, false), device_status,
+                             static_cast<cudaStream_t>(stream));
 }
 
 int nvfp4_grouped_gemm_masked(const void* a, int64_t lda_elems, const void* b, const void* sfb, const float* gw, void* d,
@@ -386,7 +401,8 @@ int nvfp4_grouped_gemm_masked(const void* a, int64_t lda_elems, const void* b, c
     if (dev->cc_major != 10) return host::fail(NVFP4_E_UNSUPPORTED, "needs an sm_100 GPU, found sm_%d%d", dev->cc_major, dev->cc_minor);
     return launch_gemm_split(a, lda_elems, b, sfb, gw, d, ldd_elems, nullptr, masked_m, max_m, E * max_m, N, K, E,
                              enable_residual_pass != 0, tune ? tune[5] : 0, tune ? tune[12] : 0, !(tune && tune[11]),
-                             scale_policy, fold_swiglu != 0, dev->num_sms, device_status, static_cast<cudaStream_t>(stream));
+                             scale_policy, fold_swiglu != 0, dev->num_sms, split_gemm_as_pair(tune, static_cast<int64_t>(E) * (max_m / 2), E, false), device_status,
+                             static_cast<cudaStream_t>(stream));
 }
 
 int nvfp4_load_checkpoint_weights(int num_parts, const void* const* weight_packed, const void* const* weight_scale,
@@ -553,6 +569,16 @@ int nvfp4_debug_mma_peak(int iters, double* flops_per_launch, void* stream)
     if (int rc = host::device_info(-1, &dev)) return rc;
     if (dev->cc_major != 10) return host::fail(NVFP4_E_UNSUPPORTED, "needs an sm_100 GPU");
     return launch_mma_peak(iters, dev->hw_sms, flops_per_launch, static_cast<cudaStream_t>(stream));
+}
+
+int nvfp4_debug_mma_peak_pair(int iters, double* flops_per_launch, void* stream)
+{
+    host::clear_error();
+    NVFP4_REQUIRE(iters > 0, "iters must be positive");
+    host::DeviceInfo* dev;
+    if (int rc = host::device_info(-1, &dev)) return rc;
+    if (dev->cc_major != 10) return host::fail(NVFP4_E_UNSUPPORTED, "needs an sm_100 GPU, found sm_%d%d", dev->cc_major, dev->cc_minor);
+    return launch_mma_peak_pair(iters, dev->hw_sms, flops_per_launch, static_cast<cudaStream_t>(stream));
 }
 
 int nvfp4_debug_mma_pattern(int iters, int num_cp, int num_mma, int mma_n, int alt_cols, double* flops_per_launch,

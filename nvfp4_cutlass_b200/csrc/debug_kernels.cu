@@ -129,6 +129,53 @@ __global__ void __launch_bounds__(128, 1) mma_pattern_kernel(int iters, int num_
     if (threadIdx.x < 32) { ptx::tcgen05_fence_after_sync(); ptx::tmem_dealloc<512>(tmem); }
 }
 
+
+// The same ceiling for CTA pairs: one thread of the even CTA of every 2-CTA cluster issues 256 x 256 x 64 MMAs
+// (tcgen05.mma.cta_group::2) on operands resident in the two CTAs' shared memories (each holds its 128 rows of A and
+// 128 of the 256 rows of B) and scales resident in their tensor memories.
+__global__ void __launch_bounds__(128, 1) mma_pair_peak_kernel(int iters, int num_mma, int32_t* status)
+{
+    extern __shared__ uint8_t smem_raw[];
+    const uint32_t smem = (ptx::smem_u32(smem_raw) + 1023u) & ~1023u;
+    uint8_t* gen = smem_raw + (smem - ptx::smem_u32(smem_raw));
+    constexpr uint32_t kA = 0, kB = 8192, kBar = kB + 8192;
+    uint64_t* bar = reinterpret_cast<uint64_t*>(gen + kBar);
+    uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(gen + kBar + 8);
+    volatile uint32_t* abort_flag = tmem_slot + 1;
+    for (uint32_t i = threadIdx.x; i < kBar / 4; i += blockDim.x)
+        reinterpret_cast<uint32_t*>(gen)[i] = 0x9e3779b9u * (i + 1u + blockIdx.x);       // arbitrary FP4 codes
+    if (threadIdx.x == 0) { ptx::mbar_init(bar, 1); *abort_flag = 0; ptx::fence_mbar_init(); }
+    if (threadIdx.x < 32) ptx::tmem_alloc_pair<512>(tmem_slot);
+    ptx::fence_proxy_async_smem();
+    ptx::tcgen05_fence_before_sync();
+    ptx::cluster_sync();
+    ptx::tcgen05_fence_after_sync();
+    const uint32_t tmem = *tmem_slot;
+    {
+        uint32_t ones[32];                                                              // scales of 1.0 in 32 columns
+#pragma unroll
+        for (int i = 0; i < 32; ++i) ones[i] = 0x38383838u;
+        ptx::tmem_st_32x32b(tmem + (((threadIdx.x >> 5) * 32) << 16) + 256, ones);
+        ptx::tmem_st_wait();
+    }
+    ptx::tcgen05_fence_before_sync();
+    ptx::cluster_sync();
+    ptx::tcgen05_fence_after_sync();
+    if (threadIdx.x == 0 && ptx::cluster_cta_rank() == 0) {
+        constexpr uint32_t idesc = ptx::make_idesc_nvf4(256, 256);
+        for (int it = 0; it < iters; ++it)
+            for (int j = 0; j < num_mma; ++j)
+                ptx::tcgen05_mma_nvf4_pair(tmem, ptx::make_smem_desc(smem + kA + (j & 1u) * 32, 512, ptx::kSwizzle64B),
+                                           ptx::make_smem_desc(smem + kB + (j & 1u) * 32, 512, ptx::kSwizzle64B), idesc,
+                                           tmem + 256, tmem + 264, (it | j) != 0 ? 1u : 0u);
+        ptx::tcgen05_commit_pair(bar, 3);
+    }
+    if (threadIdx.x == 0 && !ptx::mbar_wait_impl(bar, 0, abort_flag) && status != nullptr) atomicOr(status, 1);
+    ptx::tcgen05_fence_before_sync();
+    ptx::cluster_sync();
+    if (threadIdx.x < 32) { ptx::tcgen05_fence_after_sync(); ptx::tmem_dealloc_pair<512>(tmem); }
+}
+
 }  // namespace
 
 int launch_debug_decompose(const void* a, int64_t lda, int M, int K, int policy, void* q0, void* q1, void* s0, void* s1,
@@ -171,6 +218,19 @@ int launch_mma_pattern(int iters, int num_cp, int num_mma, int mma_n, int alt_co
     kernel<<<num_sms, 128, kSmem, stream>>>(iters, num_cp, num_mma, alt_cols, nullptr);
     NVFP4_CUDA_CHECK(cudaGetLastError());
     if (flops_per_launch) *flops_per_launch = 2.0 * 128 * mma_n * 64 * static_cast<double>(num_mma) * iters * num_sms;
+    return NVFP4_OK;
+}
+
+int launch_mma_peak_pair(int iters, int num_sms, double* flops_per_launch, cudaStream_t stream)
+{
+    constexpr int kSmem = 8192 + 8192 + 64 + 1024;
+    const int pairs = num_sms / 2;
+    if (pairs < 1) return host::fail(NVFP4_E_UNSUPPORTED, "a CTA pair needs two SMs");
+    NVFP4_CUDA_CHECK(cudaFuncSetAttribute(mma_pair_peak_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, kSmem));
+    if (int rc = host::launch_kernel_cluster(mma_pair_peak_kernel, dim3(static_cast<unsigned>(2 * pairs)), dim3(128), kSmem, stream,
+                                             false, 2u, iters, 8, static_cast<int32_t*>(nullptr)))
+        return rc;
+    if (flops_per_launch) *flops_per_launch = 2.0 * 256 * 256 * 64 * 8.0 * iters * pairs;
     return NVFP4_OK;
 }
 

@@ -15,6 +15,8 @@
 // (xform::decompose_block16), so the result is the same bit for bit up to FP32 summation order.
 #include <cuda_bf16.h>
 
+#include <type_traits>
+
 #include "gemm_common.cuh"
 #include "host_common.hpp"
 #include "launchers.hpp"
@@ -407,6 +409,405 @@ gemm_split_kernel(const __grid_constant__ CUtensorMap tm_a0, const __grid_consta
     }
 }
 
+
+// ---------------------------------------------------------------------------------------------------
+// Kernel 2, CTA-pair form: two CTAs of a cluster on 256 token rows x 256 weight columns.
+// ---------------------------------------------------------------------------------------------------
+// One tcgen05.mma.cta_group::2 drives both tensor cores: each CTA contributes its own 128 rows of A0 / A1 (and their
+// scales) and HALF of the weight tile's rows; the hardware shows each tensor core the other half out of the peer's
+// shared memory.  Per K block a CTA therefore takes in 16 KB of weights instead of 32 KB, and the tensor core reads
+// each weight row from shared memory once per 256 token rows instead of once per 128 -- the single-CTA kernel's
+// shared-memory pipe (TMA writes + operand reads, ~115 of 128 B/clk) is what stretches its MMAs.
+//
+// Who signals whom.  The MMA thread exists only in the pair's even CTA (the leader).  Its barriers `full` (operands of
+// both CTAs: the peer's loads complete their bytes on the leader's barrier), `sf_full` (scale warps of both CTAs) and
+// `tmem_empty` (epilogue warps of both) live in the leader; `empty`, `sf_in`, `tmem_full` are local to each CTA and
+// the leader's commits reach both through the commit's CTA mask.
+//
+// A pair tile cannot straddle two experts (one weight tile per MMA), so the rows are cut into units: two
+// consecutive row blocks of the same expert, or a single left-over block (then the odd CTA repeats the even CTA's
+// rows and stores nothing).  Masked layout: units follow from the per-group row counts.  Contiguous layout: a table
+// of units is built in shared memory from m_indices at kernel start (prefix scan over the row blocks by one warp).
+constexpr uint32_t kMaxUnitBlocks = 4096;   // row blocks the unit table covers (contiguous layout)
+
+// Shared and tensor memory of the pair kernel.  What limits the operand ring is the time a tile needs to arrive
+// (~2200 cycles for the 48 KB of a K block, measured) against the MMA time of the positions in flight, so the operands
+// get as many positions as fit -- four of 48 KB at BK = 256 -- and the scale factors, which the scale warps lift into
+// tensor memory as soon as they land, go through a ring of their own that is half as deep.
+// (Tried: scale factors from global memory through registers, with no shared-memory stage at all.  The four warps of
+// a group need the same words, and four trips through L1 cost more than one TMA write and four shared-memory reads:
+// 0.42 ms against 0.38 ms on E=8 x 512 rows, N=28672, K=4096.)
+template <uint32_t BK, bool kResidual>
+struct PairCfg {
+    static_assert(BK == 128 || BK == 256, "K block");
+    static constexpr uint32_t kAtoms = BK / 64, kPass = kResidual ? 2 : 1;
+    static constexpr uint32_t kRowBytes = BK / 2;
+    static constexpr uint64_t kSwizzle = BK == 256 ? ptx::kSwizzle128B : ptx::kSwizzle64B;
+    static constexpr uint32_t kSBO = 8 * kRowBytes;
+    static constexpr uint32_t kSlotA = BM * kRowBytes;                         // one pass, this CTA's 128 rows
+    static constexpr uint32_t kSlotB = BN / 2 * kRowBytes;                     // this CTA's half of the weight tile's rows
+    static constexpr uint32_t kStage = kPass * kSlotA + kSlotB;
+    static constexpr uint32_t kSlotSFA = kAtoms * kPass * 512, kSlotSFB = kAtoms * 2 * 512, kSfStage = kSlotSFA + kSlotSFB;
+    static constexpr uint32_t kTmemCols = 512, kColAcc = 0, kColSF = 256;
+    static constexpr uint32_t kSfA = 0, kSfB = 4 * kAtoms * kPass, kSfCols = 4 * kAtoms * 2 + 8 * kAtoms;
+    static constexpr uint32_t kDepth = 1024 / BK, kDepthSf = kDepth / 2;       // 4 + 2 (BK = 256), 8 + 4 (BK = 128)
+    static_assert(kColSF + kDepth * kSfCols <= kTmemCols, "scale columns");
+    static constexpr uint32_t kOffA = 0;                                       // [kDepth][A0, A1, B]
+    static constexpr uint32_t kOffSf = kDepth * kStage;                        // [kDepthSf][SFA, SFB]
+    static constexpr uint32_t kOffStage = kOffSf + kDepthSf * kSfStage;
+    static constexpr uint32_t kOffUnits = kOffStage + kNumEpiWarps * gemm::kStageWarp;
+    static constexpr uint32_t kOffBars = kOffUnits + kMaxUnitBlocks * 2;
+    static constexpr uint32_t kNumBars = 3 * kDepth + 2 * kDepthSf + 2;
+    static constexpr uint32_t kSmemAlloc = kOffBars + kNumBars * 8 + 16 + 1024;
+    static_assert(kSmemAlloc <= 232448, "shared memory budget");
+    static_assert(kDepth * kStage >= kMaxUnitBlocks * 4, "the expert table of the unit builder borrows the ring");
+};
+
+// nanoseconds between barrier polls of the roles that run ahead (producer, scale warps)
+constexpr uint32_t PAIR_SLEEP_TMA = 64, PAIR_SLEEP_SF = 32;
+
+struct PairTile {
+    uint32_t row0;     // first row of the unit
+    uint32_t n_blk;
+    int32_t expert;
+    bool pair;         // two row blocks (else one)
+};
+
+template <bool kMasked>
+struct PairWalker {
+    const int32_t* layout;
+    const uint16_t* units;
+    uint32_t num_units, num_n, group_m, groups, max_m;
+    uint32_t g = 0, units_before = 0, blocks_here = 0;
+    bool primed = false;
+
+    __device__ __forceinline__ uint32_t blocks_of(uint32_t group) const
+    {
+        const uint32_t rows = min(static_cast<uint32_t>(max(0, __ldg(layout + group))), max_m);
+        return (rows + BM - 1) / BM;
+    }
+    __device__ __forceinline__ bool next(uint32_t linear, PairTile& t)
+    {
+        uint32_t unit;
+        if constexpr (!kMasked) {
+            if (linear >= num_units * num_n) return false;
+            gemm::tile_coords(linear, num_units, num_n, group_m, unit, t.n_blk);
+            const uint32_t w = units[unit];
+            t.row0 = (w & 0x7fffu) * BM;
+            t.pair = (w >> 15) != 0;
+            t.expert = max(0, __ldg(layout + t.row0));
+            return true;
+        } else {
+            if (!primed) { blocks_here = groups ? blocks_of(0) : 0; primed = true; }
+            for (;;) {
+                if (g >= groups) return false;
+                if (linear < (units_before + (blocks_here + 1) / 2) * num_n) break;
+                units_before += (blocks_here + 1) / 2;
+                if (++g < groups) blocks_here = blocks_of(g);
+            }
+            gemm::tile_coords(linear - units_before * num_n, (blocks_here + 1) / 2, num_n, group_m, unit, t.n_blk);
+            t.row0 = g * max_m + unit * 2 * BM;
+            t.pair = unit * 2 + 1 < blocks_here;
+            t.expert = static_cast<int32_t>(g);
+            return true;
+        }
+    }
+};
+
+// Contiguous layout: cut the num_m row blocks into units.  Block i starts a unit when it sits an even number of blocks
+// after the start of its run of equal expert ids; the unit is a pair when block i + 1 belongs to the same run.  Every
+// thread of the CTA calls this; `experts` is scratch for num_m words; the table and *num_units are valid on return.
+__device__ __forceinline__ void build_units(const int32_t* m_indices, uint32_t num_m, int32_t* experts, uint16_t* units,
+                                            uint32_t* num_units)
+{
+    for (uint32_t i = threadIdx.x; i < num_m; i += blockDim.x) experts[i] = max(0, __ldg(m_indices + static_cast<uint64_t>(i) * BM));
+    __syncthreads();
+    if (threadIdx.x < 32) {                          // one warp: three short walks over the table and two shuffle scans
+        const uint32_t lane = threadIdx.x, per = (num_m + 31) / 32;
+        const uint32_t lo = min(lane * per, num_m), hi = min(lo + per, num_m);
+        // effect of this lane's chunk on the parity p = (distance from the run start) & 1: p_out = reset ? val : p_in ^ val
+        bool reset = false;
+        uint32_t val = 0;
+        for (uint32_t i = lo; i < hi; ++i) {
+            if (i == 0 || experts[i] != experts[i - 1]) { reset = true; val = 0; } else val ^= 1;
+        }
+        // inclusive scan of the chunk effects over the lanes, then shift by one lane
+        bool r = reset;
+        uint32_t v = val;
+        for (uint32_t d = 1; d < 32; d <<= 1) {
+            const bool r_up = __shfl_up_sync(0xffffffffu, r ? 1u : 0u, d) != 0;
+            const uint32_t v_up = __shfl_up_sync(0xffffffffu, v, d);
+            if (lane >= d && !r) { r = r_up; v ^= v_up; }
+        }
+        // Block 0 starts a run, so every non-empty prefix ends in a known parity: lane L now holds the parity of the last
+        // block before its successor's chunk.
+        const uint32_t v_prev = __shfl_up_sync(0xffffffffu, v, 1);
+        const uint32_t p = lane == 0 ? 0u : v_prev;
+        // count the unit starts of the chunk
+        uint32_t count = 0, q = p;
+        for (uint32_t i = lo; i < hi; ++i) {
+            q = (i == 0 || experts[i] != experts[i - 1]) ? 0u : (q ^ 1u);
+            count += q == 0;
+        }
+        uint32_t incl = count;
+        for (uint32_t d = 1; d < 32; d <<= 1) {
+            const uint32_t up = __shfl_up_sync(0xffffffffu, incl, d);
+            if (lane >= d) incl += up;
+        }
+        uint32_t at = incl - count;
+        q = p;
+        for (uint32_t i = lo; i < hi; ++i) {
+            q = (i == 0 || experts[i] != experts[i - 1]) ? 0u : (q ^ 1u);
+            if (q == 0) {
+                const bool pair = i + 1 < num_m && experts[i + 1] == experts[i];
+                units[at++] = static_cast<uint16_t>(i | (pair ? 0x8000u : 0u));
+            }
+        }
+        if (lane == 31) *num_units = incl;
+    }
+    ptx::fence_proxy_async_smem();                   // the scratch is about to be overwritten by bulk copies
+    __syncthreads();
+}
+
+
+template <uint32_t BK, bool kResidual, bool kMasked>
+__global__ void __launch_bounds__(kThreads, 1)
+gemm_split_pair_kernel(const __grid_constant__ CUtensorMap tm_a0, const __grid_constant__ CUtensorMap tm_a1,
+                       const __grid_constant__ CUtensorMap tm_b, const __grid_constant__ CUtensorMap tm_sfb, const Params p)
+{
+    using C = PairCfg<BK, kResidual>;
+    extern __shared__ uint8_t smem_raw[];
+    const uint32_t smem = (ptx::smem_u32(smem_raw) + 1023u) & ~1023u;
+    uint8_t* smem_gen = smem_raw + (smem - ptx::smem_u32(smem_raw));
+
+    uint64_t* bars = reinterpret_cast<uint64_t*>(smem_gen + C::kOffBars);
+    uint64_t* full = bars;                           // LEADER: the operand tiles of both CTAs have landed
+    uint64_t* empty = full + C::kDepth;              // each CTA: the pair MMAs that read a ring position have retired
+    uint64_t* sf_full = empty + C::kDepth;           // LEADER: the scales of both CTAs are in their tensor memories
+    uint64_t* sf_in = sf_full + C::kDepth;           // each CTA, scale ring: its scale factors have landed
+    uint64_t* sf_free = sf_in + C::kDepthSf;         // each CTA, scale ring: the scale warps have lifted them out
+    uint64_t* tmem_full = sf_free + C::kDepthSf;     // each CTA: the accumulator is complete
+    uint64_t* tmem_empty = tmem_full + 1;            // LEADER: the epilogue warps of both CTAs have drained theirs
+    uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(tmem_empty + 1);
+    volatile uint32_t* abort_flag = tmem_slot + 1;
+    uint32_t* num_units_slot = tmem_slot + 2;
+    uint16_t* units = reinterpret_cast<uint16_t*>(smem_gen + C::kOffUnits);
+
+    const uint32_t warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const uint32_t rank = ptx::cluster_cta_rank();   // 0: leader (issues the MMAs), 1: peer
+    const uint32_t pair_id = ptx::cluster_id_x(), num_pairs = ptx::num_clusters_x();
+    if (threadIdx.x == 0) {
+        for (uint32_t i = 0; i < C::kDepth; ++i) {
+            ptx::mbar_init(full + i, 1);
+            ptx::mbar_init(empty + i, 1);
+            ptx::mbar_init(sf_full + i, 2 * kNumSfWarps);
+            if (i < C::kDepthSf) {
+                ptx::mbar_init(sf_in + i, 1);
+                ptx::mbar_init(sf_free + i, kNumSfWarps);
+            }
+        }
+        ptx::mbar_init(tmem_full, 1);
+        ptx::mbar_init(tmem_empty, 2 * kNumEpiWarps);
+        *abort_flag = 0;
+        *num_units_slot = 0;
+        ptx::fence_mbar_init();
+        ptx::prefetch_tensormap(&tm_a0);
+        if constexpr (kResidual) ptx::prefetch_tensormap(&tm_a1);
+        ptx::prefetch_tensormap(&tm_b);
+        ptx::prefetch_tensormap(&tm_sfb);
+    }
+    if (warp == kWarpMma) ptx::tmem_alloc_pair<C::kTmemCols>(tmem_slot);
+    ptx::tcgen05_fence_before_sync();
+    ptx::cluster_sync();                             // the peer's barriers exist before anything signals them
+    ptx::tcgen05_fence_after_sync();
+    const uint32_t tmem_base = *tmem_slot;
+    // everything above overlapped the quantisation kernel; its stores (and the routing index) are visible from here on
+    ptx::grid_dependency_wait();
+    if constexpr (!kMasked)
+        build_units(p.layout, p.m / BM, reinterpret_cast<int32_t*>(smem_gen + C::kOffA), units, num_units_slot);
+
+    const uint32_t num_kb = p.k / BK;
+    PairWalker<kMasked> walk{p.layout, units, *num_units_slot, p.n / BN, p.group_m, p.groups, p.max_m};
+    PairTile t;
+    bool ok = true;
+    ptx::ProbeAcc pa;
+    auto give_up = [&](uint32_t code) {
+        *abort_flag = 1;
+        if (p.status != nullptr) atomicOr(p.status, static_cast<int32_t>(code));
+        ok = false;
+    };
+    // rows of this CTA inside a unit: the odd CTA of a single-block unit repeats the even CTA's rows
+    auto my_row0 = [&](const PairTile& pt) { return pt.row0 + (pt.pair ? rank * BM : 0u); };
+
+    if (warp == kWarpTma) {
+        // ================= producer =================
+        if (lane == 0) {
+            Ring r, rs;
+            const uint32_t full_leader = ptx::map_to_cta(ptx::smem_u32(full), 0);
+            for (uint32_t tile = pair_id; ok && walk.next(tile, t); tile += num_pairs) {
+                const uint32_t row0 = my_row0(t);
+                const uint8_t* sfa_row = p.sfa + static_cast<uint64_t>(row0 / BM) * (p.k / 64) * (C::kPass * 512);
+                for (uint32_t kb = 0; kb < num_kb; ++kb) {
+                    // the roles that run ahead sleep between polls: every poll is an instruction of the shared-memory pipe
+                    if (!ptx::mbar_wait_sleep<false>(empty + r.slot, r.phase ^ 1, abort_flag, PAIR_SLEEP_TMA, pa, 0)) { give_up(1); break; }
+                    if (!ptx::mbar_wait_sleep<false>(sf_free + rs.slot, rs.phase ^ 1, abort_flag, PAIR_SLEEP_TMA, pa, 0)) { give_up(1); break; }
+                    NVFP4_TRACE(0, (tile - pair_id) / num_pairs * num_kb + kb);
+                    uint8_t* sf_dst = smem_gen + C::kOffSf + rs.slot * C::kSfStage;
+                    ptx::mbar_arrive_expect_tx(sf_in + rs.slot, C::kSfStage);
+                    ptx::tma_load_2d(sf_dst + C::kSlotSFA, &tm_sfb, sf_in + rs.slot, t.n_blk * BN,
+                                     t.expert * (p.k / 64) + kb * C::kAtoms);
+                    ptx::bulk_load(sf_dst, sfa_row + static_cast<uint64_t>(kb) * C::kSlotSFA, C::kSlotSFA, sf_in + rs.slot);
+                    // the leader announces the operand bytes of both CTAs; the peer's bytes complete on the leader's barrier
+                    if (rank == 0) ptx::mbar_arrive_expect_tx(full + r.slot, 2 * (C::kPass * C::kSlotA + C::kSlotB));
+                    const uint32_t bar = full_leader + r.slot * 8;
+                    uint8_t* a_dst = smem_gen + C::kOffA + r.slot * C::kStage;
+                    ptx::tma_load_2d_pair(a_dst, &tm_a0, bar, kb * C::kRowBytes, row0);
+                    if constexpr (kResidual) ptx::tma_load_2d_pair(a_dst + C::kSlotA, &tm_a1, bar, kb * C::kRowBytes, row0);
+                    ptx::tma_load_2d_pair(a_dst + C::kPass * C::kSlotA, &tm_b, bar, kb * C::kRowBytes,
+                                          t.expert * p.n + t.n_blk * BN + rank * (BN / 2));
+                    r.advance<C::kDepth>();
+                    rs.advance<C::kDepthSf>();
+                }
+            }
+            ptx::grid_launch_dependents();
+        }
+    } else if (warp == kWarpMma) {
+        // ================= MMA issue (leader only) =================
+        if (rank == 0) {
+            Ring r;
+            uint32_t acc_phase = 0;
+            int32_t pending = -1;                   // ring position whose commit is still to be issued
+            constexpr uint32_t idesc = ptx::make_idesc_nvf4(2 * BM, BN);
+            constexpr uint16_t kBoth = 3;
+            for (uint32_t tile = pair_id; ok && walk.next(tile, t); tile += num_pairs) {
+                if (!ptx::mbar_wait(tmem_empty, acc_phase ^ 1, abort_flag, pa, 0)) { give_up(1); break; }
+                ptx::tcgen05_fence_after_sync();
+                for (uint32_t kb = 0; kb < num_kb; ++kb) {
+                    if (!ptx::mbar_wait(sf_full + r.slot, r.phase, abort_flag, pa, 1) ||
+                        !ptx::mbar_wait(full + r.slot, r.phase, abort_flag, pa, 2)) { give_up(1); break; }
+                    NVFP4_TRACE(3, (tile - pair_id) / num_pairs * num_kb + kb);
+                    ptx::tcgen05_fence_after_sync();
+                    if (lane == 0) {
+                        const uint32_t a0 = smem + C::kOffA + r.slot * C::kStage, a1 = a0 + C::kSlotA;
+                        const uint32_t b = a0 + C::kPass * C::kSlotA;
+                        const uint32_t sf = tmem_base + C::kColSF + r.slot * C::kSfCols;
+#pragma unroll
+                        for (uint32_t a = 0; a < C::kAtoms; ++a) {
+                            const uint64_t desc_b = ptx::make_smem_desc(b + a * 32, C::kSBO, C::kSwizzle);
+                            ptx::tcgen05_mma_nvf4_pair(tmem_base + C::kColAcc, ptx::make_smem_desc(a0 + a * 32, C::kSBO, C::kSwizzle),
+                                                       desc_b, idesc, sf + C::kSfA + 4 * (a * C::kPass), sf + C::kSfB + 8 * a,
+                                                       (kb | a) != 0 ? 1u : 0u);
+                            if constexpr (kResidual)
+                                ptx::tcgen05_mma_nvf4_pair(tmem_base + C::kColAcc,
+                                                           ptx::make_smem_desc(a1 + a * 32, C::kSBO, C::kSwizzle), desc_b, idesc,
+                                                           sf + C::kSfA + 4 * (a * C::kPass + 1), sf + C::kSfB + 8 * a, 1u);
+                            // as in the single-CTA kernel: the commit of a K block goes out after the first atom of the next
+                            if (a == 0 && pending >= 0) ptx::tcgen05_commit_pair(empty + pending, kBoth);
+                        }
+                        if (kb == num_kb - 1) {
+                            ptx::tcgen05_commit_pair(empty + r.slot, kBoth);
+                            ptx::tcgen05_commit_pair(tmem_full, kBoth);
+                        }
+                    }
+                    pending = kb != num_kb - 1 ? static_cast<int32_t>(r.slot) : -1;
+                    NVFP4_TRACE(4, (tile - pair_id) / num_pairs * num_kb + kb);
+                    __syncwarp();
+                    r.advance<C::kDepth>();
+                }
+                acc_phase ^= 1;
+            }
+        }
+    } else if (warp >= kWarpSf0 && warp < kWarpEpi0) {
+        // ================= scale warps: as in the single-CTA kernel, signalling the leader =================
+        const uint32_t quad = warp & 3, group = (warp - kWarpSf0) >> 2;     // group 0: weight scales, 1: activation scales
+        const uint32_t sf_full_leader = ptx::map_to_cta(ptx::smem_u32(sf_full), 0);
+        Ring r, rs;
+        for (uint32_t tile = pair_id; ok && walk.next(tile, t); tile += num_pairs) {
+            for (uint32_t kb = 0; kb < num_kb; ++kb) {
+                // the scale columns of ring position r are free: the producer requested these scales only after it had
+                // seen the position's MMAs retire
+                if (!ptx::mbar_wait_sleep<false>(sf_in + rs.slot, rs.phase, abort_flag, PAIR_SLEEP_SF, pa, 2)) { give_up(1); break; }
+                if (warp == kWarpSf0) NVFP4_TRACE(1, (tile - pair_id) / num_pairs * num_kb + kb);
+                const uint32_t sf = tmem_base + ((quad * 32) << 16) + C::kColSF + r.slot * C::kSfCols;
+                if (group == 0) {
+                    const uint32_t sfb = smem + C::kOffSf + rs.slot * C::kSfStage + C::kSlotSFA + lane * 4;
+                    uint32_t v[8 * C::kAtoms];
+#pragma unroll
+                    for (uint32_t i = 0; i < C::kAtoms * 2; ++i)
+#pragma unroll
+                        for (uint32_t j = 0; j < 4; ++j) v[4 * i + j] = ptx::lds32(sfb + i * 512 + j * 128);
+                    ptx::tmem_st_32x32b(sf + C::kSfB, v);
+                } else {
+                    const uint32_t sfa = smem + C::kOffSf + rs.slot * C::kSfStage + lane * 16;
+                    uint32_t v[4 * C::kAtoms * C::kPass];
+#pragma unroll
+                    for (uint32_t i = 0; i < C::kAtoms * C::kPass; ++i) {
+                        const uint4 q = ptx::lds128(sfa + i * 512);
+                        v[4 * i] = q.x; v[4 * i + 1] = q.y; v[4 * i + 2] = q.z; v[4 * i + 3] = q.w;
+                    }
+                    ptx::tmem_st_32x32b(sf + C::kSfA, v);
+                }
+                ptx::tmem_st_wait();
+                ptx::tcgen05_fence_before_sync();
+                __syncwarp();
+                // A cluster-scope releasing arrive (mbarrier.arrive.release.cluster) was measured to cost ~1500 cycles here
+                // and to set the pace of the whole kernel (0.52 ms against 0.38 ms).  The scales went to tensor memory,
+                // which the tcgen05 fences order, so the plain form is enough.
+                if (lane == 0) {
+                    ptx::mbar_arrive_remote(sf_full_leader + r.slot * 8);
+                    ptx::mbar_arrive(sf_free + rs.slot);      // the words are in tensor memory: the slot may be refilled
+                }
+                if (warp == kWarpSf0) NVFP4_TRACE(2, (tile - pair_id) / num_pairs * num_kb + kb);
+                r.advance<C::kDepth>();
+                rs.advance<C::kDepthSf>();
+            }
+        }
+    } else if (warp >= kWarpEpi0) {
+        // ================= epilogue: each CTA drains and stores its own 128 rows =================
+        const uint32_t quad = warp & 3, group = (warp - kWarpEpi0) >> 2;
+        const uint32_t tmem_empty_leader = ptx::map_to_cta(ptx::smem_u32(tmem_empty), 0);
+        uint32_t acc_phase = 0;
+        for (uint32_t tile = pair_id; ok && walk.next(tile, t); tile += num_pairs) {
+            const float g = __ldg(p.gw + t.expert);
+            if (!ptx::mbar_wait_relaxed(tmem_full, acc_phase, abort_flag, 100)) { give_up(1); break; }
+            if (warp == kWarpEpi0) NVFP4_TRACE(5, (tile - pair_id) / num_pairs);
+            ptx::tcgen05_fence_after_sync();
+            acc_phase ^= 1;
+            if (!t.pair && rank != 0) {             // nothing of ours in this unit
+                if (lane == 0) ptx::mbar_arrive_remote(tmem_empty_leader);
+                continue;
+            }
+            const uint32_t taddr = tmem_base + ((quad * 32) << 16) + C::kColAcc + group * 64;
+            uint32_t o[32];
+            {
+                uint32_t va[32], vb[32];
+                ptx::tmem_ld_32x32b_x32(taddr, va);
+                ptx::tmem_ld_32x32b_x32(taddr + 32, vb);
+                ptx::tmem_ld_wait();
+                ptx::tcgen05_fence_before_sync();
+                __syncwarp();
+                if (lane == 0) ptx::mbar_arrive_remote(tmem_empty_leader);
+                if (warp == kWarpEpi0) NVFP4_TRACE(6, (tile - pair_id) / num_pairs);
+                gemm::scale_pack_bf16(va, g, o);
+                gemm::scale_pack_bf16(vb, g, o + 16);
+            }
+            const uint32_t stage = smem + C::kOffStage + (warp - kWarpEpi0) * gemm::kStageWarp;
+            __nv_bfloat16* d_lane = p.d + static_cast<int64_t>(my_row0(t) + quad * 32 + (lane >> 3)) * p.ldd + t.n_blk * BN +
+                                    group * 64 + (lane & 7u) * 8;
+            gemm::store_rows_staged(o, stage, d_lane, p.ldd, lane);
+            if (warp == kWarpEpi0) NVFP4_TRACE(8, (tile - pair_id) / num_pairs);
+        }
+    }
+
+    // neither CTA may leave (or give up its tensor memory) while the other can still signal it or read its operands
+    ptx::tcgen05_fence_before_sync();
+    ptx::cluster_sync();
+    if (warp == kWarpMma) {
+        ptx::tcgen05_fence_after_sync();
+        ptx::tmem_dealloc_pair<C::kTmemCols>(tmem_base);
+    }
+}
+
 // What a call of the split path is made of, after validation.
 struct Call {
     const void* a; int64_t lda;             // activations (SwiGLU-folded form: the (M, 2 K) gate+up output)
@@ -416,6 +817,7 @@ struct Call {
     int policy;
     const int32_t* masked_m; int max_m;     // masked layout: device-side row counts, rows reserved per group
     int num_sms;
+    bool pair;                              // CTA-pair GEMM kernel
     cudaStream_t stream;
 };
 
@@ -435,10 +837,10 @@ int launch_quantize(const Call& c, uint8_t* a0, uint8_t* a1, uint8_t* sfa)
                                static_cast<uint32_t>(c.K), a0, a1, sfa, c.masked_m, static_cast<uint32_t>(c.max_m > 0 ? c.max_m : 1));
 }
 
-template <uint32_t BK, bool kResidual, uint32_t kGroup, bool kMasked>
+template <uint32_t BK, bool kResidual, uint32_t kGroup, bool kMasked, bool kPair = false>
 int launch_variant(const Call& c, Params p)
 {
-    using C = Cfg<BK, kResidual, kGroup>;
+    using C = std::conditional_t<kPair, PairCfg<BK, kResidual>, Cfg<BK, kResidual, kGroup>>;
     const int M = c.M, N = c.N, K = c.K;
     int dev = 0;
     NVFP4_CUDA_CHECK(cudaGetDevice(&dev));
@@ -465,7 +867,7 @@ int launch_variant(const Call& c, Params p)
     rc = host::encode_tensor_map_2d(&tm_a1, CU_TENSOR_MAP_DATA_TYPE_UINT8, 1, a1, K / 2, M, K / 2, C::kRowBytes, BM, sw);
     if (rc) return release(rc);
     rc = host::encode_tensor_map_2d(&tm_b, CU_TENSOR_MAP_DATA_TYPE_UINT8, 1, c.b, K / 2, static_cast<uint64_t>(c.E) * N, K / 2,
-                                    C::kRowBytes, BN, sw);
+                                    C::kRowBytes, BN / (kPair ? 2 : 1), sw);
     if (rc) return release(rc);
     rc = host::encode_tensor_map_2d(&tm_sfb, CU_TENSOR_MAP_DATA_TYPE_INT32, 4, c.sfb, N, static_cast<uint64_t>(c.E) * (K / 64),
                                     static_cast<uint64_t>(N) * 4, BN, C::kAtoms, CU_TENSOR_MAP_SWIZZLE_NONE);
@@ -473,7 +875,10 @@ int launch_variant(const Call& c, Params p)
 
     if (int qrc = launch_quantize<kResidual>(c, a0, a1, sfa)) return release(qrc);
 
-    auto kernel = gemm_split_kernel<BK, kResidual, kGroup, kMasked>;
+    auto kernel = [] {
+        if constexpr (kPair) return gemm_split_pair_kernel<BK, kResidual, kMasked>;
+        else return gemm_split_kernel<BK, kResidual, kGroup, kMasked>;
+    }();
     static bool attr_set[host::kMaxDevices] = {};
     if (!attr_set[dev]) {
         if (cudaError_t err = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, C::kSmemAlloc);
@@ -483,9 +888,19 @@ int launch_variant(const Call& c, Params p)
     }
     // masked layout: the number of tiles is only known on the device; surplus CTAs find no tile and leave
     const int num_tiles = (M / static_cast<int>(BM)) * (N / static_cast<int>(BN));
-    const int grid = num_tiles < c.num_sms ? num_tiles : c.num_sms;
-    return release(host::launch_kernel(kernel, dim3(static_cast<unsigned>(grid)), dim3(kThreads), C::kSmemAlloc, c.stream, c.pdl,
-                                       tm_a0, tm_a1, tm_b, tm_sfb, p));
+    if constexpr (kPair) {
+        // one cluster of two CTAs per pair of SMs; a unit is at most two row blocks, so there are at least num_tiles / 2
+        // and at most num_tiles pair tiles
+        int pairs = c.num_sms / 2;
+        if (pairs > num_tiles) pairs = num_tiles;
+        if (pairs < 1) pairs = 1;
+        return release(host::launch_kernel_cluster(kernel, dim3(static_cast<unsigned>(2 * pairs)), dim3(kThreads), C::kSmemAlloc,
+                                                   c.stream, c.pdl, 2u, tm_a0, tm_a1, tm_b, tm_sfb, p));
+    } else {
+        const int grid = num_tiles < c.num_sms ? num_tiles : c.num_sms;
+        return release(host::launch_kernel(kernel, dim3(static_cast<unsigned>(grid)), dim3(kThreads), C::kSmemAlloc, c.stream,
+                                           c.pdl, tm_a0, tm_a1, tm_b, tm_sfb, p));
+    }
 }
 
 template <bool kMasked>
@@ -495,6 +910,11 @@ int launch_for_layout(const Call& c, const Params& p, bool residual, int block_k
     // per position, 130 = 128-wide in groups of two (requested and freed together, consumed one by one)
     if (!kMasked && block_k == 130)
         return residual ? launch_variant<128, true, 2, false>(c, p) : launch_variant<128, false, 2, false>(c, p);
+    if (c.pair) {
+        if (c.K % 256 == 0 && block_k != 128)
+            return residual ? launch_variant<256, true, 1, kMasked, true>(c, p) : launch_variant<256, false, 1, kMasked, true>(c, p);
+        return residual ? launch_variant<128, true, 1, kMasked, true>(c, p) : launch_variant<128, false, 1, kMasked, true>(c, p);
+    }
     if (c.K % 256 == 0 && block_k != 128)
         return residual ? launch_variant<256, true, 1, kMasked>(c, p) : launch_variant<256, false, 1, kMasked>(c, p);
     return residual ? launch_variant<128, true, 1, kMasked>(c, p) : launch_variant<128, false, 1, kMasked>(c, p);
@@ -507,8 +927,8 @@ int launch_for_layout(const Call& c, const Params& p, bool residual, int block_k
 // max_m rows (M = E * max_m), masked_m[g] of them real.
 int launch_gemm_split(const void* a, int64_t lda, const void* b, const void* sfb, const float* gw, void* d,
                       int64_t ldd, const int32_t* m_indices, const int32_t* masked_m, int max_m, int M, int N, int K, int E,
-                      bool residual, int block_k, int group_m, bool pdl, int policy, bool swiglu, int num_sms, int32_t* status,
-                      cudaStream_t stream)
+                      bool residual, int block_k, int group_m, bool pdl, int policy, bool swiglu, int num_sms, bool pair,
+                      int32_t* status, cudaStream_t stream)
 {
     Params p;
     p.gw = gw;
@@ -520,7 +940,9 @@ int launch_gemm_split(const void* a, int64_t lda, const void* b, const void* sfb
     p.group_m = group_m > 0 ? group_m : 8;
     p.groups = E; p.max_m = max_m > 0 ? max_m : 1;
     p.status = status;
-    const Call c{a, lda, b, sfb, M, N, K, E, pdl, swiglu, policy, masked_m, max_m, num_sms, stream};
+    // the pair kernel's unit table covers kMaxUnitBlocks row blocks of the contiguous layout
+    const bool use_pair = pair && num_sms >= 2 && (masked_m != nullptr || M / static_cast<int>(BM) <= static_cast<int>(kMaxUnitBlocks));
+    const Call c{a, lda, b, sfb, M, N, K, E, pdl, swiglu, policy, masked_m, max_m, num_sms, use_pair, stream};
     return masked_m != nullptr ? launch_for_layout<true>(c, p, residual, block_k) : launch_for_layout<false>(c, p, residual, block_k);
 }
 
@@ -528,7 +950,7 @@ int launch_gemm_split(const void* a, int64_t lda, const void* b, const void* sfb
 int launch_debug_split_workspace(const void* a, int64_t lda, int M, int K, int policy, bool residual, bool swiglu, void* a0,
                                  void* a1, void* sfa, cudaStream_t stream)
 {
-    const Call c{a, lda, nullptr, nullptr, M, 0, K, 0, false, swiglu, policy, nullptr, 0, 0, stream};
+    const Call c{a, lda, nullptr, nullptr, M, 0, K, 0, false, swiglu, policy, nullptr, 0, 0, false, stream};
     return residual ? launch_quantize<true>(c, static_cast<uint8_t*>(a0), static_cast<uint8_t*>(a1), static_cast<uint8_t*>(sfa))
                     : launch_quantize<false>(c, static_cast<uint8_t*>(a0), static_cast<uint8_t*>(a1), static_cast<uint8_t*>(sfa));
 }

@@ -60,21 +60,38 @@ struct DeviceInfo {
 // griddepcontrol.wait before it touches anything that kernel wrote.
 // Counterpart in the reference: src/jit/launch.hpp:63-96.
 template <typename... Params, typename... Args>
-int launch_kernel(void (*kernel)(Params...), dim3 grid, dim3 block, size_t smem, cudaStream_t stream, bool pdl, Args&&... args)
+int launch_kernel_cluster(void (*kernel)(Params...), dim3 grid, dim3 block, size_t smem, cudaStream_t stream, bool pdl,
+                          unsigned cluster_x, Args&&... args)
 {
     cudaLaunchConfig_t cfg = {};
-    cudaLaunchAttribute attr[1];
-    attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
-    attr[0].val.programmaticStreamSerializationAllowed = 1;
+    cudaLaunchAttribute attr[2];
+    unsigned n = 0;
+    if (cluster_x > 1) {
+        attr[n].id = cudaLaunchAttributeClusterDimension;
+        attr[n].val.clusterDim.x = cluster_x;
+        attr[n].val.clusterDim.y = 1;
+        attr[n].val.clusterDim.z = 1;
+        ++n;
+    }
+    if (pdl) {
+        attr[n].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+        attr[n].val.programmaticStreamSerializationAllowed = 1;
+        ++n;
+    }
     cfg.gridDim = grid;
     cfg.blockDim = block;
     cfg.dynamicSmemBytes = smem;
     cfg.stream = stream;
     cfg.attrs = attr;
-    cfg.numAttrs = pdl ? 1 : 0;
+    cfg.numAttrs = n;
     if (cudaError_t err = cudaLaunchKernelEx(&cfg, kernel, static_cast<Params>(args)...); err != cudaSuccess)
         return fail(NVFP4_E_CUDA, "kernel launch failed: %s", cudaGetErrorString(err));
     return NVFP4_OK;
+}
+template <typename... Params, typename... Args>
+int launch_kernel(void (*kernel)(Params...), dim3 grid, dim3 block, size_t smem, cudaStream_t stream, bool pdl, Args&&... args)
+{
+    return launch_kernel_cluster(kernel, grid, block, smem, stream, pdl, 1u, static_cast<Args&&>(args)...);
 }
 
 // Properties of `device` (< 0: current), cached per device (not per process).

@@ -18,8 +18,8 @@ int launch_gemm_cluster(const void* a, int64_t lda, const void* b, const void* s
 // masked_m == nullptr: contiguous layout.  Otherwise E groups of max_m rows each (M = E * max_m), masked_m[g] real.
 int launch_gemm_split(const void* a, int64_t lda, const void* b, const void* sfb, const float* gw, void* d,
                       int64_t ldd, const int32_t* m_indices, const int32_t* masked_m, int max_m, int M, int N, int K, int E,
-                      bool residual, int block_k, int group_m, bool pdl, int policy, bool swiglu, int num_sms, int32_t* status,
-                      cudaStream_t stream);
+                      bool residual, int block_k, int group_m, bool pdl, int policy, bool swiglu, int num_sms, bool pair,
+                      int32_t* status, cudaStream_t stream);
 
 int launch_debug_split_workspace(const void* a, int64_t lda, int M, int K, int policy, bool residual, bool swiglu, void* a0,
                                  void* a1, void* sfa, cudaStream_t stream);
@@ -65,6 +65,7 @@ int launch_load_checkpoint(int num_parts, const void* const* packed, const void*
                            cudaStream_t stream);
 
 int launch_mma_peak(int iters, int num_sms, double* flops_per_launch, cudaStream_t stream);
+int launch_mma_peak_pair(int iters, int num_sms, double* flops_per_launch, cudaStream_t stream);
 
 int launch_mma_pattern(int iters, int num_cp, int num_mma, int mma_n, int alt_cols, int num_sms, double* flops_per_launch,
                        cudaStream_t stream);

@@ -437,6 +437,12 @@ NVFP4_DEVICE void mbar_arrive_cluster(uint32_t cluster_addr)
 {
     asm volatile("mbarrier.arrive.release.cluster.shared::cluster.b64 _, [%0];" ::"r"(cluster_addr) : "memory");
 }
+// The same with the default (CTA-scope release) semantics: enough when what the waiter consumes was not written by
+// this thread's generic-proxy stores (tensor-memory traffic is ordered by the tcgen05 fences around the barrier).
+NVFP4_DEVICE void mbar_arrive_remote(uint32_t cluster_addr)
+{
+    asm volatile("mbarrier.arrive.shared::cluster.b64 _, [%0];" ::"r"(cluster_addr) : "memory");
+}
 NVFP4_DEVICE bool mbar_try_wait_cluster(uint64_t* bar, uint32_t parity)
 {
     uint32_t ok;
@@ -504,6 +510,54 @@ NVFP4_DEVICE void bulk_copy_to_cta(uint32_t dst_cluster_addr, uint32_t src_cta_a
 {
     asm volatile("cp.async.bulk.shared::cluster.shared::cta.mbarrier::complete_tx::bytes [%0], [%1], %2, [%3];"
                  ::"r"(dst_cluster_addr), "r"(src_cta_addr), "r"(bytes), "r"(dst_bar)
+                 : "memory");
+}
+// ---- CTA pairs (cta_group::2): one MMA instruction drives the tensor cores of two SMs ----------------
+// Tensor memory of both CTAs of a pair at once; one warp of EACH CTA executes it, with the same arguments.
+template <uint32_t kCols>
+NVFP4_DEVICE void tmem_alloc_pair(uint32_t* smem_result)
+{
+    static_assert(kCols >= 32 && kCols <= 512 && (kCols & (kCols - 1)) == 0, "TMEM columns: power of two in [32, 512]");
+    asm volatile("tcgen05.alloc.cta_group::2.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_u32(smem_result)),
+                 "n"(kCols)
+                 : "memory");
+    asm volatile("tcgen05.relinquish_alloc_permit.cta_group::2.sync.aligned;" ::: "memory");
+}
+template <uint32_t kCols>
+NVFP4_DEVICE void tmem_dealloc_pair(uint32_t taddr)
+{
+    asm volatile("tcgen05.dealloc.cta_group::2.sync.aligned.b32 %0, %1;" ::"r"(taddr), "n"(kCols) : "memory");
+}
+// Tiled load into this CTA's shared memory whose bytes complete on an mbarrier that may live in the other CTA
+// of the pair (`bar_cluster_addr` from map_to_cta).  Not a multicast: every CTA fetches its own tile.
+NVFP4_DEVICE void tma_load_2d_pair(void* smem_dst, const CUtensorMap* map, uint32_t bar_cluster_addr, int32_t c0, int32_t c1)
+{
+    asm volatile(
+        "cp.async.bulk.tensor.2d.cta_group::2.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%3, %4}], [%2];"
+        ::"r"(smem_u32(smem_dst)), "l"(reinterpret_cast<uint64_t>(map)), "r"(bar_cluster_addr), "r"(c0), "r"(c1)
+        : "memory");
+}
+// D[tmem of both CTAs] (+)= A * B over a CTA pair: M = 256 (each CTA its own 128 rows of A, from its own shared
+// memory at the descriptor's offset), N up to 256 (each CTA holds half of the rows of B), block scales from each
+// CTA's own tensor memory (SFA of its rows, SFB of all N).  Issued by one thread of the pair's even CTA.
+NVFP4_DEVICE void tcgen05_mma_nvf4_pair(uint32_t tmem_d, uint64_t desc_a, uint64_t desc_b, uint32_t idesc,
+                                        uint32_t tmem_sfa, uint32_t tmem_sfb, uint32_t accumulate)
+{
+    asm volatile(
+        "{\n"
+        " .reg .pred p;\n"
+        " setp.ne.b32 p, %6, 0;\n"
+        " tcgen05.mma.cta_group::2.kind::mxf4nvf4.block_scale.block16 [%0], %1, %2, %3, [%4], [%5], p;\n"
+        "}\n" ::"r"(tmem_d),
+        "l"(desc_a), "l"(desc_b), "r"(idesc), "r"(tmem_sfa), "r"(tmem_sfb), "r"(accumulate)
+        : "memory");
+}
+// All earlier pair MMAs of this thread arrive, when they retire, on the barrier at this offset in the CTAs of
+// the cluster named by `cta_mask`.
+NVFP4_DEVICE void tcgen05_commit_pair(uint64_t* bar, uint16_t cta_mask)
+{
+    asm volatile("tcgen05.commit.cta_group::2.mbarrier::arrive::one.shared::cluster.multicast::cluster.b64 [%0], %1;"
+                 ::"r"(smem_u32(bar)), "h"(cta_mask)
                  : "memory");
 }
 NVFP4_DEVICE void fence_proxy_async_all() { asm volatile("fence.proxy.async;" ::: "memory"); }

@@ -230,7 +230,52 @@ def test_gemm_split_matches_oracle(dev, oracle, shape, residual, block_k):
     assert rel_l2(d, fused) < 1e-3        # same codes and scales; only the summation order may differ
 
 
-def test_gemm_split_many_tiles_strided(dev, oracle):
+PAIR = dict(tune_split_transform=1, tune_cluster=2)     # split path with the CTA-pair (cta_group::2) GEMM kernel
+
+
+@pytest.mark.parametrize("sizes", [[256], [128], [128, 128], [384, 128, 256, 640, 128], [256, 256, 256], [128] * 5, [1152]],
+                         ids=lambda s: "x".join(map(str, s)))
+@pytest.mark.parametrize("nk", [(256, 128), (1024, 2048), (2048, 640)])
+@pytest.mark.parametrize("residual", [True, False])
+def test_gemm_split_pair_kernel_matches_oracle(dev, oracle, sizes, nk, residual):
+    """tune_split_transform=1 + tune_cluster=2: two CTAs share one MMA over 256 rows x 256 columns.  Experts with one,
+    an even and an odd number of row blocks (a left-over block is a unit of its own: the odd CTA stores nothing),
+    expert boundaries on odd row blocks, short and long K, K that only the 128-wide block divides.  Same K order as
+    the single-CTA kernel, so the two must agree bit for bit."""
+    n, k = nk
+    g = torch.Generator().manual_seed(900 + n + k + len(sizes))
+    a = torch.randn(sum(sizes), k, generator=g).to(torch.bfloat16)
+    w = (torch.randn(len(sizes), n, k, generator=g) * 0.02).to(torch.bfloat16)
+    b, sfb, gw = nvfp4_gemm.quantize_weight_nvfp4(w.to(dev))
+    mi = nvfp4_gemm.make_m_indices(sizes)
+    d = run_gemm(dev, a, b, sfb, gw, mi, n, enable_residual_pass=residual, **PAIR)
+    want = oracle.grouped_gemm(a, b.cpu(), sfb.cpu(), gw.cpu(), mi, n, mode="dual" if residual else "single")
+    assert torch.isfinite(d.float()).all()
+    assert rel_l2(d, want) < REL_L2_VS_ORACLE
+    single = run_gemm(dev, a, b, sfb, gw, mi, n, enable_residual_pass=residual, tune_split_transform=1, tune_cluster=1)
+    assert torch.equal(d, single)
+
+
+def test_groups_of_256_rows_take_the_pair_kernel_by_default(dev, oracle):
+    """m_alignment=256 is the caller's statement that every expert's rows are whole 256-row pairs; the split path then
+    runs the CTA-pair kernel by itself.  Same bits as the explicitly chosen kernels; M % 256 is enforced."""
+    sizes, n, k = [512, 256, 768], 2048, 1024
+    g = torch.Generator().manual_seed(4242)
+    a = torch.randn(sum(sizes), k, generator=g).to(torch.bfloat16)
+    w = (torch.randn(len(sizes), n, k, generator=g) * 0.02).to(torch.bfloat16)
+    b, sfb, gw = nvfp4_gemm.quantize_weight_nvfp4(w.to(dev))
+    mi = nvfp4_gemm.make_m_indices(sizes, alignment=256)
+    d = run_gemm(dev, a, b, sfb, gw, mi, n, m_alignment=256)
+    want = oracle.grouped_gemm(a, b.cpu(), sfb.cpu(), gw.cpu(), mi, n)
+    assert rel_l2(d, want) < REL_L2_VS_ORACLE
+    assert torch.equal(d, run_gemm(dev, a, b, sfb, gw, mi, n, **PAIR))
+    assert torch.equal(d, run_gemm(dev, a, b, sfb, gw, mi, n, tune_split_transform=1, tune_cluster=1))
+    with pytest.raises(RuntimeError, match="multiple of the token-tile alignment"):
+        run_gemm(dev, a[:384], b, sfb, gw, mi[:384], n, m_alignment=256)
+
+
+@pytest.mark.parametrize("tune", [dict(tune_split_transform=1), PAIR], ids=["single", "pair"])
+def test_gemm_split_many_tiles_strided(dev, oracle, tune):
     """Split path with more tiles than SMs, ragged experts, a strided activation matrix and a strided output."""
     sizes = [128, 384, 256, 128, 512, 128, 256, 640]
     n, k = 4096, 512
@@ -244,8 +289,7 @@ def test_gemm_split_many_tiles_strided(dev, oracle):
     d = d_wide[:, :n]
     status = torch.zeros(1, dtype=torch.int32, device=dev)
     for _ in range(3):                    # repeated calls reuse the pooled workspace
-        nvfp4_gemm.m_grouped_bf16_dual_nvfp4_gemm_contiguous(a, b, sfb, gw, d, mi.to(dev), device_status=status,
-                                                             tune_split_transform=1)
+        nvfp4_gemm.m_grouped_bf16_dual_nvfp4_gemm_contiguous(a, b, sfb, gw, d, mi.to(dev), device_status=status, **tune)
     torch.cuda.synchronize()
     assert int(status.item()) == 0
     want = oracle.grouped_gemm(a.cpu().contiguous(), b.cpu(), sfb.cpu(), gw.cpu(), mi, n)
@@ -606,7 +650,8 @@ def test_split_workspace_swiglu_fold_byte_for_byte(dev, oracle, residual):
 # ---------------------------------------------------------------- masked layout
 @pytest.mark.parametrize("residual", [True, False])
 @pytest.mark.parametrize("k", [512, 640])
-def test_gemm_masked_layout_matches_oracle(dev, oracle, residual, k):
+@pytest.mark.parametrize("tune", [{}, dict(tune_cluster=2)], ids=["single", "pair"])
+def test_gemm_masked_layout_matches_oracle(dev, oracle, residual, k, tune):
     """Groups with device-side row counts: empty groups, a full group, counts that are not multiples of 128, a count
     above max_m (clamped); rows past a group's last row block must stay untouched."""
     e, max_m, n = 6, 512, 1024
@@ -619,7 +664,7 @@ def test_gemm_masked_layout_matches_oracle(dev, oracle, residual, k):
     status = torch.zeros(1, dtype=torch.int32, device=dev)
     masked_m = torch.tensor(counts, dtype=torch.int32, device=dev)
     nvfp4_gemm.m_grouped_bf16_dual_nvfp4_gemm_masked(a.to(dev), b, sfb, gw, d, masked_m, enable_residual_pass=residual,
-                                                     device_status=status)
+                                                     device_status=status, **tune)
     torch.cuda.synchronize()
     assert _C.read_status(status) == 0
     dc = d.cpu()
