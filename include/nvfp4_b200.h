@@ -199,6 +199,32 @@ NVFP4_API int nvfp4_swiglu(const void* h, int64_t h_ld_elems, int64_t rows, int 
 NVFP4_API int nvfp4_combine_rows(const void* rows, int64_t rows_ld_elems, const int64_t* pos, const float* w,
                                  int64_t tokens, int k, int hidden, void* y, int64_t y_ld_elems, void* stream);
 
+/* Dispatch of QUANTISED rows over peer memory: every token row of `x` (tokens, K) BF16 is decomposed once (Algorithm 1,
+ * derived_div8, both passes -- the codes the GEMM's own activation quantisation would produce, bit for bit) and stored
+ * for each of its k (token, choice) pairs into row dst_row of rank dst_rank's buffer, which has three planes:
+ * packed codes of the first pass (rows_cap, K/2) at offset 0, of the residual pass at a1_offset_bytes, and the block
+ * scales (rows_cap, 2, K/16) at scale_offset_bytes.  1.125 bytes per element cross NVLink instead of 2, and Algorithm 1
+ * runs once per token instead of once per pair.  K in 1024 ... 8192, a multiple of 1024.  Pairs out of range are
+ * skipped as in nvfp4_dispatch_rows_peer.  No counterpart in the reference. */
+NVFP4_API int nvfp4_dispatch_quantized_peer(const void* x, int64_t x_ld_elems, int64_t tokens, int k, int K, const int64_t* peers,
+                                            int64_t a1_offset_bytes, int64_t scale_offset_bytes, const int64_t* dst_rank,
+                                            const int64_t* dst_row, int world, int64_t rows_cap, int sm_budget,
+                                            int32_t* device_status, void* stream);
+
+/* Scale rows as the quantised dispatch delivers them, (E * max_m, 2, K/16) bytes, -> the (E * max_m / 128, K/64, 2, 512)
+ * atoms nvfp4_grouped_gemm_masked_quantized reads.  masked_m (device, may be NULL = every row) limits the work to each
+ * group's live row blocks. */
+NVFP4_API int nvfp4_relayout_scales(const void* scale_rows, const int32_t* masked_m, int E, int max_m, int K, void* scale_atoms,
+                                    void* stream);
+
+/* nvfp4_grouped_gemm_masked over activations that are already quantised: a0, a1 (E * max_m, K/2) packed codes of the
+ * two passes (a1 may be NULL when enable_residual_pass is 0), scale_atoms from nvfp4_relayout_scales.  One launch (the
+ * GEMM kernel of the split path); same result as nvfp4_grouped_gemm_masked on the BF16 rows the codes came from. */
+NVFP4_API int nvfp4_grouped_gemm_masked_quantized(const void* a0, const void* a1, const void* scale_atoms, const void* b,
+                                                  const void* sfb, const float* gw, void* d, int64_t ldd_elems,
+                                                  const int32_t* masked_m, int E, int max_m, int N, int K, int enable_residual_pass,
+                                                  const int32_t* tune, int32_t* device_status, void* stream);
+
 /* The same two steps over peer memory, for ranks on the GPUs of one NVLink domain.  `peers` is a device array
  * with one int64 per rank: the address, in THIS process, of that rank's copy of a symmetric buffer (rows of
  * `row_bytes`, stride dst_ld_bytes / rows_ld_elems, the same on every rank).  No counterpart in the reference.

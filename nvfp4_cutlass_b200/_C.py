@@ -29,7 +29,8 @@ TUNE_KEYS = ("tune_block_n", "tune_transform_warps", "tune_epilogue_threads", "t
 EXPORTS = ("nvfp4_last_error", "nvfp4_version", "nvfp4_get_num_sms", "nvfp4_set_num_sms",
            "nvfp4_quantize_weight", "nvfp4_quantize_weight_static", "nvfp4_grouped_gemm_contiguous", "nvfp4_debug_decompose",
            "nvfp4_debug_mma_peak", "nvfp4_debug_mma_peak_pair", "nvfp4_debug_mma_pattern", "nvfp4_permute_rows", "nvfp4_swiglu", "nvfp4_combine_rows",
-           "nvfp4_dispatch_rows_peer", "nvfp4_combine_rows_peer", "nvfp4_expert_histogram",
+           "nvfp4_dispatch_rows_peer", "nvfp4_dispatch_quantized_peer", "nvfp4_relayout_scales",
+           "nvfp4_grouped_gemm_masked_quantized", "nvfp4_combine_rows_peer", "nvfp4_expert_histogram",
            "nvfp4_grouped_gemm_swiglu_contiguous", "nvfp4_grouped_gemm_masked", "nvfp4_load_checkpoint_weights",
            "nvfp4_read_status", "nvfp4_debug_split_workspace", "nvfp4_debug_wait_timeout", "nvfp4_plan_peer_masked",
            "nvfp4_peer_barrier")
@@ -67,6 +68,9 @@ def lib() -> ctypes.CDLL:
         L.nvfp4_grouped_gemm_swiglu_contiguous.argtypes = [vp, i64, vp, vp, vp, vp, i64, vp, i32, i32, i32, i32, i32, vp, vp, vp]
         L.nvfp4_combine_rows_peer.argtypes = [vp, i64, vp, vp, vp, i64, i32, i32, vp, i64, i32, i64, i32, vp]
         L.nvfp4_combine_rows.argtypes = [vp, i64, vp, vp, i64, i32, i32, vp, i64, vp]
+        L.nvfp4_dispatch_quantized_peer.argtypes = [vp, i64, i64, i32, i32, vp, i64, i64, vp, vp, i32, i64, i32, vp, vp]
+        L.nvfp4_relayout_scales.argtypes = [vp, vp, i32, i32, i32, vp, vp]
+        L.nvfp4_grouped_gemm_masked_quantized.argtypes = [vp, vp, vp, vp, vp, vp, vp, i64, vp, i32, i32, i32, i32, i32, vp, vp, vp]
         L.nvfp4_grouped_gemm_masked.argtypes = [vp, i64, vp, vp, vp, vp, i64, vp, i32, i32, i32, i32, i32, i32, i32, vp, vp, vp]
         L.nvfp4_load_checkpoint_weights.argtypes = [i32, vp, vp, vp, vp, i32, i32, i32, vp, vp, vp, vp]
         L.nvfp4_read_status.argtypes = [vp, ctypes.POINTER(ctypes.c_int32), vp]
@@ -403,6 +407,68 @@ def dispatch_rows_peer(src: torch.Tensor, src_idx, src_div: int, peers: torch.Te
                                               src_div, peers.data_ptr(), dst_rank.data_ptr(), dst_row.data_ptr(), n, src.shape[1] * 2,
                                               dst_ld_elems * 2, peers.numel(), rows_cap, int(sm_budget),
                                               status.data_ptr() if status is not None else None, _stream()))
+
+
+class QuantizedRows:
+    """The three planes of a buffer of quantised activation rows, (E, max_m) rows of K elements, in one uint8 tensor
+    `store` of E * max_m * (K + K // 8) bytes: packed codes of the first pass, of the residual pass, block scales
+    (rows, 2, K // 16) -- the layout nvfp4_dispatch_quantized_peer writes -- plus a local tensor of scale atoms."""
+
+    def __init__(self, store: torch.Tensor, e: int, max_m: int, k: int):
+        rows = e * max_m
+        _require(store.dtype == torch.uint8 and store.is_contiguous() and store.numel() == rows * (k + k // 8),
+                 "store is a contiguous uint8 tensor of E * max_m * (K + K / 8) bytes")
+        self.store, self.e, self.max_m, self.k = store, e, max_m, k
+        self.a1_offset, self.scale_offset = rows * (k // 2), rows * k
+        self.a0 = store[:self.a1_offset].view(rows, k // 2)
+        self.a1 = store[self.a1_offset:self.scale_offset].view(rows, k // 2)
+        self.scale_rows = store[self.scale_offset:].view(rows, 2, k // 16)
+        self.scale_atoms = torch.zeros(rows // 128, k // 64, 2, 512, dtype=torch.uint8, device=store.device)
+
+
+def dispatch_quantized_peer(x: torch.Tensor, k_choices: int, peers: torch.Tensor, dst_rank: torch.Tensor, dst_row: torch.Tensor,
+                            rows: "QuantizedRows", status: torch.Tensor = None, sm_budget: int = 0) -> None:
+    """Every token row of x, decomposed once, -> the quantised buffers (planes as in `rows`) of the ranks in `peers`."""
+    n = dst_row.numel()
+    _require(_rows_ok(x) and x.shape[1] == rows.k, "x is a (tokens, K) BF16 CUDA tensor")
+    _require(_i64_ok(dst_rank, n) and _i64_ok(dst_row, n) and _i64_ok(peers, 1) and n == x.shape[0] * k_choices,
+             "indices and peer addresses are contiguous int64 CUDA tensors, one entry per (token, choice)")
+    with torch.cuda.device(_one_device(x, peers, dst_rank, dst_row, status)):
+        _check(lib().nvfp4_dispatch_quantized_peer(x.data_ptr(), x.stride(0), x.shape[0], int(k_choices), rows.k, peers.data_ptr(),
+                                                   rows.a1_offset, rows.scale_offset, dst_rank.data_ptr(), dst_row.data_ptr(),
+                                                   peers.numel(), rows.e * rows.max_m, int(sm_budget),
+                                                   status.data_ptr() if status is not None else None, _stream()))
+
+
+def relayout_scales(rows: "QuantizedRows", masked_m: torch.Tensor = None) -> None:
+    """rows.scale_rows -> rows.scale_atoms for the live row blocks of every group."""
+    with torch.cuda.device(_one_device(rows.store, rows.scale_atoms, masked_m)):
+        _check(lib().nvfp4_relayout_scales(rows.scale_rows.data_ptr(), masked_m.data_ptr() if masked_m is not None else None,
+                                           rows.e, rows.max_m, rows.k, rows.scale_atoms.data_ptr(), _stream()))
+
+
+def m_grouped_quantized_dual_nvfp4_gemm_masked(rows: "QuantizedRows", b, sfb, gw, d, masked_m, enable_residual_pass: bool = True,
+                                               *, device_status=None, **tune) -> None:
+    """The masked GEMM over activations that are already quantised (`rows` after relayout_scales)."""
+    for key in tune:
+        if key not in TUNE_KEYS:
+            raise TypeError(f"m_grouped_quantized_dual_nvfp4_gemm_masked() got an unexpected keyword argument {key!r}")
+    e, max_m, k = rows.e, rows.max_m, rows.k
+    _require(d.dtype == torch.bfloat16 and d.dim() == 3 and d.shape[:2] == (e, max_m) and d.stride(2) == 1 and
+             d.stride(0) == max_m * d.stride(1), "d is (E, max_m, N) BF16, last dimension contiguous, groups max_m rows apart")
+    n = d.shape[2]
+    _require(b.dtype == torch.int8 and sfb.dtype == torch.int32 and gw.dtype == torch.float32 and masked_m.dtype == torch.int32,
+             "b int8, sfb int32, gw float32, masked_m int32")
+    _require(gw.numel() == e and masked_m.numel() == e and b.shape == (e * n, k // 2) and sfb.shape == (e * (k // 64), n),
+             "weight shapes do not fit")
+    _require(b.is_contiguous() and sfb.is_contiguous() and gw.is_contiguous() and masked_m.is_contiguous(),
+             "b, sfb, gw, masked_m are contiguous")
+    tune_arr = (ctypes.c_int32 * len(TUNE_KEYS))(*[int(tune.get(key, 0)) for key in TUNE_KEYS])
+    with torch.cuda.device(_one_device(rows.store, rows.scale_atoms, b, sfb, gw, d, masked_m, device_status)):
+        _check(lib().nvfp4_grouped_gemm_masked_quantized(
+            rows.a0.data_ptr(), rows.a1.data_ptr(), rows.scale_atoms.data_ptr(), b.data_ptr(), sfb.data_ptr(), gw.data_ptr(),
+            d.data_ptr(), d.stride(1), masked_m.data_ptr(), e, max_m, n, k, 1 if enable_residual_pass else 0,
+            ctypes.cast(tune_arr, ctypes.c_void_p), device_status.data_ptr() if device_status is not None else None, _stream()))
 
 
 def combine_rows_peer(peers: torch.Tensor, rows_ld_elems: int, src_rank: torch.Tensor, src_row: torch.Tensor, w: torch.Tensor,

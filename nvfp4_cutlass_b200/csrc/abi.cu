@@ -528,6 +528,67 @@ int nvfp4_dispatch_rows_peer(const void* src, int64_t src_ld_bytes, const int64_
                                      static_cast<cudaStream_t>(stream));
 }
 
+int nvfp4_dispatch_quantized_peer(const void* x, int64_t x_ld_elems, int64_t tokens, int k, int K, const int64_t* peers,
+                                  int64_t a1_offset_bytes, int64_t scale_offset_bytes, const int64_t* dst_rank,
+                                  const int64_t* dst_row, int world, int64_t rows_cap, int sm_budget, int32_t* device_status,
+                                  void* stream)
+{
+    host::clear_error();
+    NVFP4_REQUIRE(tokens >= 0 && k >= 1, "tokens must not be negative and k at least 1 (tokens=%lld, k=%d)", static_cast<long long>(tokens), k);
+    NVFP4_REQUIRE(K >= 1024 && K <= 8192 && K % 1024 == 0, "quantised dispatch needs K in 1024 ... 8192, a multiple of 1024 (K=%d)", K);
+    if (tokens == 0) return NVFP4_OK;
+    NVFP4_REQUIRE(x && peers && dst_rank && dst_row, "null pointer argument");
+    NVFP4_REQUIRE(world >= 1 && rows_cap >= 0 && sm_budget >= 0, "world must be at least 1, rows_cap and sm_budget non-negative");
+    NVFP4_REQUIRE(x_ld_elems >= K && x_ld_elems % 8 == 0 && (reinterpret_cast<uintptr_t>(x) & 15u) == 0,
+                  "token rows must be 16-byte aligned with a stride of at least K elements");
+    NVFP4_REQUIRE(a1_offset_bytes >= rows_cap * (K / 2) && scale_offset_bytes >= a1_offset_bytes + rows_cap * (K / 2) &&
+                      a1_offset_bytes % 16 == 0 && scale_offset_bytes % 16 == 0,
+                  "the three planes (a0, a1, scales) must not overlap and must start on 16-byte boundaries");
+    host::DeviceInfo* dev;
+    if (int rc = host::device_info(-1, &dev)) return rc;
+    return launch_dispatch_quantized_peer(x, x_ld_elems * 2, tokens, k, K, peers, a1_offset_bytes, scale_offset_bytes, dst_rank, dst_row,
+                                          world, rows_cap, device_status,
+                                          sm_budget > 0 && sm_budget < dev->hw_sms ? sm_budget : dev->hw_sms,
+                                          static_cast<cudaStream_t>(stream));
+}
+
+int nvfp4_relayout_scales(const void* scale_rows, const int32_t* masked_m, int E, int max_m, int K, void* scale_atoms, void* stream)
+{
+    host::clear_error();
+    NVFP4_REQUIRE(E >= 0 && max_m >= 0 && max_m % 128 == 0 && K > 0 && K % 64 == 0,
+                  "max_m must be a multiple of 128 and K of 64 (E=%d, max_m=%d, K=%d)", E, max_m, K);
+    if (E == 0 || max_m == 0) return NVFP4_OK;
+    NVFP4_REQUIRE(scale_rows && scale_atoms, "null pointer argument");
+    NVFP4_REQUIRE(((reinterpret_cast<uintptr_t>(scale_rows) | reinterpret_cast<uintptr_t>(scale_atoms)) & 3u) == 0, "scale buffers must be 4-byte aligned");
+    return launch_relayout_scales(scale_rows, masked_m, max_m, static_cast<int64_t>(E) * max_m, K, scale_atoms, true,
+                                  static_cast<cudaStream_t>(stream));
+}
+
+int nvfp4_grouped_gemm_masked_quantized(const void* a0, const void* a1, const void* scale_atoms, const void* b, const void* sfb,
+                                        const float* gw, void* d, int64_t ldd_elems, const int32_t* masked_m, int E, int max_m, int N,
+                                        int K, int enable_residual_pass, const int32_t* tune, int32_t* device_status, void* stream)
+{
+    host::clear_error();
+    NVFP4_REQUIRE(E >= 0 && max_m >= 0 && N >= 0 && K >= 0, "negative size (E=%d, max_m=%d, N=%d, K=%d)", E, max_m, N, K);
+    NVFP4_REQUIRE(N % 256 == 0 && K % 128 == 0, "N must be a multiple of 256 and K of 128 (N=%d, K=%d)", N, K);
+    NVFP4_REQUIRE(max_m % 128 == 0, "max_m must be a multiple of 128 (max_m=%d)", max_m);
+    NVFP4_REQUIRE(static_cast<int64_t>(E) * max_m <= INT32_MAX, "E * max_m = %lld rows exceed the 32-bit row index",
+                  static_cast<long long>(E) * max_m);
+    if (E == 0 || max_m == 0 || N == 0) return NVFP4_OK;
+    NVFP4_REQUIRE(K > 0, "empty weights (K=%d)", K);
+    NVFP4_REQUIRE(a0 && scale_atoms && b && sfb && gw && d && masked_m && (a1 || !enable_residual_pass), "null pointer argument");
+    NVFP4_REQUIRE(ldd_elems >= N && ldd_elems % 8 == 0, "bad output row stride %lld", static_cast<long long>(ldd_elems));
+    NVFP4_REQUIRE(((reinterpret_cast<uintptr_t>(a0) | reinterpret_cast<uintptr_t>(a1) | reinterpret_cast<uintptr_t>(scale_atoms) |
+                    reinterpret_cast<uintptr_t>(d)) & 15u) == 0, "a0, a1, scale_atoms and d must be 16-byte aligned");
+    host::DeviceInfo* dev;
+    if (int rc = host::device_info(-1, &dev)) return rc;
+    if (dev->cc_major != 10) return host::fail(NVFP4_E_UNSUPPORTED, "needs an sm_100 GPU, found sm_%d%d", dev->cc_major, dev->cc_minor);
+    return launch_gemm_split_quantized(a0, a1, scale_atoms, b, sfb, gw, d, ldd_elems, masked_m, max_m, N, K, E, enable_residual_pass != 0,
+                                       tune ? tune[5] : 0, tune ? tune[12] : 0, !(tune && tune[11]), dev->num_sms,
+                                       split_gemm_as_pair(tune, static_cast<int64_t>(E) * (max_m / 2), E, false), device_status,
+                                       static_cast<cudaStream_t>(stream));
+}
+
 int nvfp4_combine_rows_peer(const int64_t* peers, int64_t rows_ld_elems, const int64_t* src_rank, const int64_t* src_row,
                             const float* w, int64_t tokens, int k, int hidden, void* y, int64_t y_ld_elems, int world,
                             int64_t rows_cap, int sm_budget, void* stream)

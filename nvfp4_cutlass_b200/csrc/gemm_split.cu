@@ -819,6 +819,9 @@ struct Call {
     int num_sms;
     bool pair;                              // CTA-pair GEMM kernel
     cudaStream_t stream;
+    // activations that arrive quantised (the expert-parallel layer's quantised dispatch): the caller's a0, a1
+    // (M, K/2) and scale atoms (M/128, K/64, passes, 512) stand in for the workspace and kernel 1 is skipped
+    const uint8_t* ext_a0 = nullptr; const uint8_t* ext_a1 = nullptr; const uint8_t* ext_sfa = nullptr;
 };
 
 // Kernel 1 into the given workspace pieces.
@@ -844,20 +847,27 @@ int launch_variant(const Call& c, Params p)
     const int M = c.M, N = c.N, K = c.K;
     int dev = 0;
     NVFP4_CUDA_CHECK(cudaGetDevice(&dev));
-    cudaMemPool_t pool;
-    if (int rc = host::workspace_pool(dev, &pool)) return rc;
     const size_t code_bytes = static_cast<size_t>(M) * (K / 2);
     const size_t sf_bytes = static_cast<size_t>(M) * (K / 16) * C::kPass;
-    const size_t total = C::kPass * code_bytes + sf_bytes;
+    const bool ext = c.ext_a0 != nullptr;
     uint8_t* ws = nullptr;
-    NVFP4_CUDA_CHECK(cudaMallocFromPoolAsync(reinterpret_cast<void**>(&ws), total, pool, c.stream));
-    uint8_t* a0 = ws;
-    uint8_t* a1 = kResidual ? ws + code_bytes : ws;
-    uint8_t* sfa = ws + C::kPass * code_bytes;
+    uint8_t *a0, *a1, *sfa;
+    if (ext) {
+        a0 = const_cast<uint8_t*>(c.ext_a0);
+        a1 = const_cast<uint8_t*>(kResidual ? c.ext_a1 : c.ext_a0);
+        sfa = const_cast<uint8_t*>(c.ext_sfa);
+    } else {
+        cudaMemPool_t pool;
+        if (int rc = host::workspace_pool(dev, &pool)) return rc;
+        NVFP4_CUDA_CHECK(cudaMallocFromPoolAsync(reinterpret_cast<void**>(&ws), C::kPass * code_bytes + sf_bytes, pool, c.stream));
+        a0 = ws;
+        a1 = kResidual ? ws + code_bytes : ws;
+        sfa = ws + C::kPass * code_bytes;
+    }
     p.sfa = sfa;
 
     auto release = [&](int rc) {
-        cudaFreeAsync(ws, c.stream);
+        if (ws != nullptr) cudaFreeAsync(ws, c.stream);
         return rc;
     };
     CUtensorMap tm_a0, tm_a1, tm_b, tm_sfb;
@@ -873,7 +883,8 @@ int launch_variant(const Call& c, Params p)
                                     static_cast<uint64_t>(N) * 4, BN, C::kAtoms, CU_TENSOR_MAP_SWIZZLE_NONE);
     if (rc) return release(rc);
 
-    if (int qrc = launch_quantize<kResidual>(c, a0, a1, sfa)) return release(qrc);
+    if (!ext)
+        if (int qrc = launch_quantize<kResidual>(c, a0, a1, sfa)) return release(qrc);
 
     auto kernel = [] {
         if constexpr (kPair) return gemm_split_pair_kernel<BK, kResidual, kMasked>;
@@ -944,6 +955,28 @@ int launch_gemm_split(const void* a, int64_t lda, const void* b, const void* sfb
     const bool use_pair = pair && num_sms >= 2 && (masked_m != nullptr || M / static_cast<int>(BM) <= static_cast<int>(kMaxUnitBlocks));
     const Call c{a, lda, b, sfb, M, N, K, E, pdl, swiglu, policy, masked_m, max_m, num_sms, use_pair, stream};
     return masked_m != nullptr ? launch_for_layout<true>(c, p, residual, block_k) : launch_for_layout<false>(c, p, residual, block_k);
+}
+
+// The GEMM alone over activations the caller holds quantised (masked layout: E groups of max_m rows).
+int launch_gemm_split_quantized(const void* a0, const void* a1, const void* sfa, const void* b, const void* sfb, const float* gw,
+                                void* d, int64_t ldd, const int32_t* masked_m, int max_m, int N, int K, int E, bool residual,
+                                int block_k, int group_m, bool pdl, int num_sms, bool pair, int32_t* status, cudaStream_t stream)
+{
+    Params p;
+    p.gw = gw;
+    p.layout = masked_m;
+    p.sfa = nullptr;
+    p.d = static_cast<__nv_bfloat16*>(d);
+    p.ldd = ldd;
+    p.m = E * max_m; p.n = N; p.k = K;
+    p.group_m = group_m > 0 ? group_m : 8;
+    p.groups = E; p.max_m = max_m > 0 ? max_m : 1;
+    p.status = status;
+    Call c{nullptr, 0, b, sfb, E * max_m, N, K, E, pdl, false, 0, masked_m, max_m, num_sms, pair && num_sms >= 2, stream};
+    c.ext_a0 = static_cast<const uint8_t*>(a0);
+    c.ext_a1 = static_cast<const uint8_t*>(a1);
+    c.ext_sfa = static_cast<const uint8_t*>(sfa);
+    return launch_for_layout<true>(c, p, residual, block_k);
 }
 
 // Test hook: kernel 1 alone, into buffers of the caller (a0, a1: (M, K/2) bytes; sfa: (M/128, K/64, passes, 512) bytes).

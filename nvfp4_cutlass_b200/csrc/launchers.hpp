@@ -21,6 +21,10 @@ int launch_gemm_split(const void* a, int64_t lda, const void* b, const void* sfb
                       bool residual, int block_k, int group_m, bool pdl, int policy, bool swiglu, int num_sms, bool pair,
                       int32_t* status, cudaStream_t stream);
 
+int launch_gemm_split_quantized(const void* a0, const void* a1, const void* sfa, const void* b, const void* sfb, const float* gw,
+                                void* d, int64_t ldd, const int32_t* masked_m, int max_m, int N, int K, int E, bool residual,
+                                int block_k, int group_m, bool pdl, int num_sms, bool pair, int32_t* status, cudaStream_t stream);
+
 int launch_debug_split_workspace(const void* a, int64_t lda, int M, int K, int policy, bool residual, bool swiglu, void* a0,
                                  void* a1, void* sfa, cudaStream_t stream);
 
@@ -40,6 +44,11 @@ int launch_peer_barrier(const int64_t* flag_peers, int rank, int world, int slot
 int launch_dispatch_rows_peer(const void* src, int64_t src_ld_bytes, const int64_t* src_idx, int src_div, const int64_t* peers,
                               const int64_t* dst_rank, const int64_t* dst_row, int64_t n_rows, int row_bytes,
                               int64_t dst_ld_bytes, int world, int64_t rows_cap, int32_t* status, int num_sms, cudaStream_t stream);
+int launch_dispatch_quantized_peer(const void* x, int64_t x_ld_bytes, int64_t tokens, int k, int kdim, const int64_t* peers,
+                                   int64_t a1_off, int64_t sf_off, const int64_t* dst_rank, const int64_t* dst_row, int world,
+                                   int64_t rows_cap, int32_t* status, int num_sms, cudaStream_t stream);
+int launch_relayout_scales(const void* sf_rows, const int32_t* masked_m, int max_m, int64_t rows, int kdim, void* atoms, bool pdl,
+                           cudaStream_t stream);
 int launch_combine_rows_peer(const int64_t* peers, int64_t rows_ld_elems, const int64_t* src_rank, const int64_t* src_row,
                              const float* w, int64_t tokens, int k, int hidden, void* y, int64_t y_ld_elems, int world,
                              int64_t rows_cap, int num_sms, cudaStream_t stream);

@@ -13,6 +13,7 @@
 
 #include "host_common.hpp"
 #include "launchers.hpp"
+#include "transform.cuh"
 
 namespace nvfp4 {
 namespace {
@@ -129,6 +130,117 @@ dispatch_rows_peer_kernel(const uint4* __restrict__ src, int64_t src_ld16, const
         }
         for (; c < row16; c += 32) dp[c] = __ldg(sp + c);
     }
+}
+
+// Dispatch of QUANTISED rows.  A token goes to k experts and every owner would run Algorithm 1 on its copy of the
+// row: the same arithmetic k times, on BF16 rows that crossed NVLink at 2 bytes per element.  Here the sender
+// decomposes each token once (xform::decompose_block16, the function every GEMM path uses, so the codes are the same
+// bit for bit) and stores, for each of the k pairs, the two packed code rows (K/2 bytes each) and the two rows of
+// block scales (K/16 bytes each) into the owner's buffers: 1.125 bytes per element instead of 2.  The owner's
+// buffers are three planes of one symmetric allocation: a0 (rows, K/2), a1 (rows, K/2), scales (rows, 2, K/16) --
+// the first two are what the split path's GEMM reads through its tensor maps; the scale rows are re-laid into
+// 512-byte tensor-memory atoms by relayout_scales_kernel on the owner (scattering 4-byte words over NVLink instead
+// would cost more than the BF16 rows did).
+// One warp per token.  In round j lane l owns the block pair j * 32 + l (32 elements): its loads are 64-byte pieces of
+// one row, its code stores 16 bytes next to its neighbours' (512 contiguous bytes per warp instruction).  Scale bytes
+// are gathered by shuffles so that every lane stores 8 consecutive bytes per pass.  K % 1024 == 0.
+template <int kRounds>
+__global__ void __launch_bounds__(kPeerThreads, 1)
+dispatch_quantized_peer_kernel(const uint4* __restrict__ x, int64_t x_ld16, int64_t tokens, int k,
+                               const int64_t* __restrict__ peers, int64_t a1_off, int64_t sf_off,
+                               const int64_t* __restrict__ dst_rank, const int64_t* __restrict__ dst_row, int world,
+                               int64_t rows_cap, int32_t* __restrict__ status)
+{
+    constexpr int kMaxRounds = kRounds, rounds = kRounds, kdim = kRounds * 1024;
+    const int lane = threadIdx.x & 31, warps = kPeerThreads / 32;
+    for (int64_t t = static_cast<int64_t>(blockIdx.x) * warps + (threadIdx.x >> 5); t < tokens; t += static_cast<int64_t>(gridDim.x) * warps) {
+        const uint4* row = x + t * x_ld16;
+        uint4 q0[kMaxRounds], q1[kMaxRounds];
+        uint32_t s0[kMaxRounds], s1[kMaxRounds];         // two scale bytes each
+#pragma unroll
+        for (int j = 0; j < kMaxRounds; ++j) {
+            if (j >= rounds) break;
+            const uint4* src = row + (j * 32 + lane) * 4;
+            const uint4 v0 = __ldg(src), v1 = __ldg(src + 1), v2 = __ldg(src + 2), v3 = __ldg(src + 3);
+            const uint32_t wa[8] = {v0.x, v0.y, v0.z, v0.w, v1.x, v1.y, v1.z, v1.w};
+            const uint32_t wb[8] = {v2.x, v2.y, v2.z, v2.w, v3.x, v3.y, v3.z, v3.w};
+            xform::Block16 a, b;
+            xform::decompose_block16<true, 0>(wa, a);
+            xform::decompose_block16<true, 0>(wb, b);
+            q0[j] = make_uint4(a.q0[0], a.q0[1], b.q0[0], b.q0[1]);
+            q1[j] = make_uint4(a.q1[0], a.q1[1], b.q1[0], b.q1[1]);
+            s0[j] = static_cast<uint32_t>(a.s0) | (static_cast<uint32_t>(b.s0) << 8);
+            s1[j] = static_cast<uint32_t>(a.s1) | (static_cast<uint32_t>(b.s1) << 8);
+        }
+        // scale bytes [8 l, 8 l + 8) of the row belong to round l / 8, lanes 4 (l % 8) ... + 3
+        uint32_t s0w[2] = {0, 0}, s1w[2] = {0, 0};
+#pragma unroll
+        for (int j = 0; j < kMaxRounds; ++j) {
+            if (j >= rounds) break;
+#pragma unroll
+            for (int i = 0; i < 4; ++i) {
+                const uint32_t g0 = __shfl_sync(0xffffffffu, s0[j], 4 * (lane & 7) + i);
+                const uint32_t g1 = __shfl_sync(0xffffffffu, s1[j], 4 * (lane & 7) + i);
+                if (j == (lane >> 3)) {
+                    s0w[i >> 1] |= g0 << (16 * (i & 1));
+                    s1w[i >> 1] |= g1 << (16 * (i & 1));
+                }
+            }
+        }
+        for (int c = 0; c < k; ++c) {
+            const int64_t r = dst_rank[t * k + c], dr = dst_row[t * k + c];
+            if (r < 0 || r >= world || dr < 0 || dr >= rows_cap) {
+                if (dr != -1 && lane == 0 && status != nullptr) atomicOr(status, 8);
+                continue;
+            }
+            uint8_t* base = reinterpret_cast<uint8_t*>(peers[r]);
+            uint4* d0 = reinterpret_cast<uint4*>(base + dr * (kdim / 2));
+            uint4* d1 = reinterpret_cast<uint4*>(base + a1_off + dr * (kdim / 2));
+#pragma unroll
+            for (int j = 0; j < kMaxRounds; ++j) {
+                if (j >= rounds) break;
+                d0[j * 32 + lane] = q0[j];
+                d1[j * 32 + lane] = q1[j];
+            }
+            // a row's scale bytes: K / 16 per pass; the lanes of rounds that exist cover them 8 bytes each
+            if (lane < rounds * 8) {
+                uint2* ds = reinterpret_cast<uint2*>(base + sf_off + dr * (kdim / 8));
+                ds[lane] = make_uint2(s0w[0], s0w[1]);
+                ds[kdim / 128 + lane] = make_uint2(s1w[0], s1w[1]);
+            }
+        }
+    }
+}
+
+// Scale rows (rows, 2, K/16) as the quantised dispatch delivers them -> the (rows/128, K/64, 2, 512) atoms the GEMM's
+// scale warps read (inside an atom the four bytes of row r at (r % 32) * 16 + (r / 32) * 4).  One thread per row and K
+// atom; masked layout: groups of max_m rows of which the first masked_m[g], rounded up to the 128-row tile, are
+// converted.  Runs on the owner, on local memory.
+__global__ void __launch_bounds__(256)
+relayout_scales_kernel(const uint8_t* __restrict__ sf_rows, const int32_t* __restrict__ masked_m, uint32_t max_m, uint64_t rows,
+                       uint32_t kdim, uint8_t* __restrict__ atoms)
+{
+    ptx::grid_dependency_wait();
+    const uint32_t k64 = kdim / 64;
+    const uint64_t idx = static_cast<uint64_t>(blockIdx.x) * blockDim.x + threadIdx.x;
+    if (idx < rows * k64) {
+        const uint64_t row = idx / k64;
+        const uint32_t katom = static_cast<uint32_t>(idx % k64);
+        bool live = true;
+        if (masked_m != nullptr) {
+            const uint32_t count = min(static_cast<uint32_t>(max(0, __ldg(masked_m + row / max_m))), max_m);
+            live = row % max_m < (count + 127) / 128 * 128;
+        }
+        if (live) {
+            const uint8_t* src = sf_rows + row * (kdim / 8) + katom * 4;
+            const uint32_t w0 = *reinterpret_cast<const uint32_t*>(src), w1 = *reinterpret_cast<const uint32_t*>(src + kdim / 16);
+            const uint32_t r = static_cast<uint32_t>(row % 128);
+            uint8_t* dst = atoms + ((row / 128) * k64 + katom) * 1024 + (r % 32) * 16 + (r / 32) * 4;
+            *reinterpret_cast<uint32_t*>(dst) = w0;
+            *reinterpret_cast<uint32_t*>(dst + 512) = w1;
+        }
+    }
+    ptx::grid_launch_dependents();
 }
 
 // combine: y[t] = sum_j w[t, j] * (row src_row[t, j] of rank src_rank[t, j]'s output buffer), read over NVLink
@@ -375,6 +487,39 @@ int launch_combine_rows_peer(const int64_t* peers, int64_t rows_ld_elems, const 
                                                                              world, rows_cap);
     NVFP4_CUDA_CHECK(cudaGetLastError());
     return NVFP4_OK;
+}
+
+int launch_dispatch_quantized_peer(const void* x, int64_t x_ld_bytes, int64_t tokens, int k, int kdim, const int64_t* peers,
+                                   int64_t a1_off, int64_t sf_off, const int64_t* dst_rank, const int64_t* dst_row, int world,
+                                   int64_t rows_cap, int32_t* status, int num_sms, cudaStream_t stream)
+{
+    auto go = [&](auto kernel) {
+        kernel<<<static_cast<unsigned>(num_sms), kPeerThreads, 0, stream>>>(static_cast<const uint4*>(x), x_ld_bytes / 16, tokens, k, peers,
+                                                                           a1_off, sf_off, dst_rank, dst_row, world, rows_cap, status);
+    };
+    switch (kdim / 1024) {
+        case 1: go(dispatch_quantized_peer_kernel<1>); break;
+        case 2: go(dispatch_quantized_peer_kernel<2>); break;
+        case 3: go(dispatch_quantized_peer_kernel<3>); break;
+        case 4: go(dispatch_quantized_peer_kernel<4>); break;
+        case 5: go(dispatch_quantized_peer_kernel<5>); break;
+        case 6: go(dispatch_quantized_peer_kernel<6>); break;
+        case 7: go(dispatch_quantized_peer_kernel<7>); break;
+        case 8: go(dispatch_quantized_peer_kernel<8>); break;
+        default: return host::fail(NVFP4_E_UNSUPPORTED, "quantised dispatch is built for K = 1024 ... 8192 in steps of 1024 (K=%d)", kdim);
+    }
+    NVFP4_CUDA_CHECK(cudaGetLastError());
+    return NVFP4_OK;
+}
+
+int launch_relayout_scales(const void* sf_rows, const int32_t* masked_m, int max_m, int64_t rows, int kdim, void* atoms, bool pdl,
+                           cudaStream_t stream)
+{
+    const uint64_t threads = static_cast<uint64_t>(rows) * (kdim / 64);
+    if (threads == 0) return NVFP4_OK;
+    return host::launch_kernel(relayout_scales_kernel, dim3(static_cast<unsigned>((threads + 255) / 256)), dim3(256), 0, stream, pdl,
+                               static_cast<const uint8_t*>(sf_rows), masked_m, static_cast<uint32_t>(max_m > 0 ? max_m : 1),
+                               static_cast<uint64_t>(rows), static_cast<uint32_t>(kdim), static_cast<uint8_t*>(atoms));
 }
 
 }  // namespace nvfp4

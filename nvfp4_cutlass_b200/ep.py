@@ -147,28 +147,39 @@ class PeerBuffers:
     NUM_SLOTS = 8
 
     def __init__(self, e_local: int, cap_m: int, hidden: int, inter: int, device: torch.device, group=None, world: int = 1,
-                 rank: int = 0):
+                 rank: int = 0, quantized: bool = False):
         self.e_local, self.cap_m, self.hidden, self.world, self.rank = e_local, cap_m, hidden, world, rank
         self.rows_cap = e_local * cap_m
         self.status = torch.zeros(1, dtype=torch.int32, device=device)
         self.h = torch.zeros(e_local, cap_m, 2 * inter, dtype=torch.bfloat16, device=device)
         self.epoch = [0] * self.NUM_SLOTS
+        # the input buffer holds BF16 rows, or -- quantised dispatch -- the senders' NVFP4 codes and block scales
+        # (1.125 bytes per element: three planes in one allocation, see _C.QuantizedRows)
+        in_shape = (self.rows_cap * (hidden + hidden // 8),) if quantized else (e_local, cap_m, hidden)
+        in_dtype = torch.uint8 if quantized else torch.bfloat16
+        self.q = None
         if world == 1:                      # one rank: the same kernels on ordinary buffers, nobody to wait for
-            self.a = torch.zeros(e_local, cap_m, hidden, dtype=torch.bfloat16, device=device)
+            self.a = torch.zeros(in_shape, dtype=in_dtype, device=device)
             self.out = torch.zeros(e_local, cap_m, hidden, dtype=torch.bfloat16, device=device)
             self.a_peers = torch.tensor([self.a.data_ptr()], dtype=torch.int64, device=device)
             self.out_peers = torch.tensor([self.out.data_ptr()], dtype=torch.int64, device=device)
             self.flag_peers = None
+            if quantized:
+                from . import _C
+                self.q = _C.QuantizedRows(self.a, e_local, cap_m, hidden)
             return
         import torch.distributed._symmetric_memory as symm
         group = group if group is not None else dist.group.WORLD
-        self.a = symm.empty(e_local, cap_m, hidden, dtype=torch.bfloat16, device=device)
+        self.a = symm.empty(*in_shape, dtype=in_dtype, device=device)
         self.out = symm.empty(e_local, cap_m, hidden, dtype=torch.bfloat16, device=device)
         self.flags = symm.empty(self.NUM_SLOTS * world, dtype=torch.int64, device=device)
         handles = [symm.rendezvous(t, group) for t in (self.a, self.out, self.flags)]
         self.a.zero_()                      # rows past an expert's count are computed like real rows: keep them finite
         self.out.zero_()
         self.flags.zero_()
+        if quantized:
+            from . import _C
+            self.q = _C.QuantizedRows(self.a, e_local, cap_m, hidden)
         self.a_peers, self.out_peers, self.flag_peers = (
             torch.tensor(list(h.buffer_ptrs), dtype=torch.int64, device=device) for h in handles)
         torch.cuda.synchronize(device)
@@ -211,7 +222,7 @@ class ExpertParallelMoE:
 
     def __init__(self, num_experts: int, hidden: int, inter: int, up, down, group=None, alignment: int = 128,
                  gemm: Optional[Callable] = None, native_glue: bool = True, peer_rows_cap: int = 0, micro_batches: int = 1,
-                 check_each_step: bool = True, comm_sms: int = 16):
+                 check_each_step: bool = True, comm_sms: int = 16, quantized_dispatch: bool = True):
         self.group = group
         self.world = dist.get_world_size(group) if dist.is_initialized() else 1
         self.rank = dist.get_rank(group) if dist.is_initialized() else 0
@@ -243,11 +254,16 @@ class ExpertParallelMoE:
         self.peer_error = None
         self.steps_repeated = 0                # steps that overflowed the buffers and were repeated over the all-to-all path
         masked_ok = self.gemm_masked is not None and (2 * inter) % 256 == 0 and hidden % 256 == 0
+        # Quantised dispatch: the sender runs Algorithm 1 once per token and the rows cross NVLink as NVFP4 codes and
+        # scales (1.125 instead of 2 bytes per element); the owners' up-projection then starts from the codes.  Same
+        # codes as quantising the BF16 rows on arrival, so the layer's output does not change by a bit.
+        self.quantized_dispatch = bool(quantized_dispatch) and hidden % 1024 == 0 and hidden <= 8192
         if peer_rows_cap > 0 and torch.cuda.is_available() and masked_ok:
             dev = torch.device("cuda", torch.cuda.current_device())
             cap_m = (int(peer_rows_cap) + 127) // 128 * 128
             try:
-                self.peer = [PeerBuffers(self.e_local, cap_m, hidden, inter, dev, group, self.world, self.rank)
+                self.peer = [PeerBuffers(self.e_local, cap_m, hidden, inter, dev, group, self.world, self.rank,
+                                         quantized=self.quantized_dispatch)
                              for _ in range(self.micro)]
                 self.streams = [torch.cuda.Stream(device=dev) for _ in range(self.micro)] if self.micro > 1 else []
             except Exception as exc:                                   # symmetric memory unavailable: keep the NCCL path
@@ -344,11 +360,18 @@ class ExpertParallelMoE:
         pending = [0, 1, 2]                         # barrier slots of this step still to be enqueued
         try:
             buf.barrier(pending.pop(0))             # every rank has finished with these buffers (its previous step on them)
-            _C.dispatch_rows_peer(x, None, k, buf.a_peers, plan.dst_rank, plan.dst_row, self.hidden, buf.rows_cap, buf.status,
-                                  sm_budget=self.comm_sms)
+            if buf.q is not None:
+                _C.dispatch_quantized_peer(x, k, buf.a_peers, plan.dst_rank, plan.dst_row, buf.q, buf.status, sm_budget=self.comm_sms)
+            else:
+                _C.dispatch_rows_peer(x, None, k, buf.a_peers, plan.dst_rank, plan.dst_row, self.hidden, buf.rows_cap, buf.status,
+                                      sm_budget=self.comm_sms)
             buf.barrier(pending.pop(0))             # all rows have landed everywhere
             mark()
-            self.gemm_masked(buf.a, *self.up, buf.h, plan.masked_m, device_status=buf.status)
+            if buf.q is not None:
+                _C.relayout_scales(buf.q, plan.masked_m)
+                _C.m_grouped_quantized_dual_nvfp4_gemm_masked(buf.q, *self.up, buf.h, plan.masked_m, device_status=buf.status)
+            else:
+                self.gemm_masked(buf.a, *self.up, buf.h, plan.masked_m, device_status=buf.status)
             self.gemm_masked(buf.h, *self.down, buf.out, plan.masked_m, fold_swiglu=True, device_status=buf.status)
             mark()
             buf.barrier(pending.pop(0))             # every rank's expert outputs are complete

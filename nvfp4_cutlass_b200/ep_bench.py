@@ -93,12 +93,15 @@ def run(args, workload: str, world: int, rank: int, local: int) -> None:
     micro = extra.get("ep_micro", 1)
     layer = ExpertParallelMoE(E_TOTAL, HIDDEN, INTER, up, down, alignment=128,
                               peer_rows_cap=expert_rows_cap(world, micro) if use_peer else 0, micro_batches=micro,
-                              check_each_step=False, comm_sms=extra.get("ep_comm_sms", 16))
+                              check_each_step=False, comm_sms=extra.get("ep_comm_sms", 16),
+                              quantized_dispatch=extra.get("ep_quant", 1) != 0)
     exchange = "nccl all_to_all"
     if layer.peer is not None:
-        exchange = ((f"peer memory, masked layout, {micro} micro-batch(es) on streams of their own (dispatch: NVLink stores, "
+        rows_as = ("rows quantised by the sender, NVFP4 codes + scales over NVLink (1.125 B/element)" if layer.peer[0].q is not None
+                   else "BF16 rows over NVLink")
+        exchange = ((f"peer memory, masked layout, {micro} micro-batch(es) on streams of their own (dispatch: {rows_as}, NVLink stores; "
                      "combine: NVLink loads, bounded flag barriers)") if world > 1 else
-                    "one rank: the dispatch and combine kernels on local buffers, masked layout")
+                    f"one rank: the dispatch and combine kernels on local buffers, masked layout ({rows_as})")
     elif use_peer:
         exchange = "nccl all_to_all (symmetric memory unavailable: %s)" % (layer.peer_error or "?")[:200]
 
@@ -178,7 +181,9 @@ def run(args, workload: str, world: int, rank: int, local: int) -> None:
         value = flops_all / (ms_max * 1e-3) / 1e12
         gemm_ms = float(mx[4])
         achieved = 2.0 * flops_rank / (gemm_ms * 1e-3) / 1e12
-        off_rank_bytes = tokens * TOP_K * HIDDEN * 2 * (world - 1) / world
+        dispatch_bytes_per_elem = 1.125 if (layer.peer is not None and layer.peer[0].q is not None) else 2.0
+        off_rank_elems = tokens * TOP_K * HIDDEN * (world - 1) / world
+        off_rank_bytes = off_rank_elems * 2.0
         line = {"metric": "grouped_gemm_logical_tflops", "value": value, "unit": "TFLOP/s", "n_gpus": world, "steps": steps,
                 "warmup": warmup, "ms_per_step": ms_max, "higher_is_better": True, "scaling": "weak", "vs_baseline": None,
                 "dtype": "nvfp4 (e2m1 x ue4m3 block 16), fp32 accumulate, bf16 in/out", "data": "synthetic",
@@ -198,6 +203,7 @@ def run(args, workload: str, world: int, rank: int, local: int) -> None:
                 "micro_batches": micro,
                 "peer_vs_all_to_all_rel_l2": peer_vs_a2a,
                 "all_to_all_bytes_per_rank_per_direction": off_rank_bytes,
+                "nvlink_bytes_per_rank_peer_path": {"dispatch": off_rank_elems * dispatch_bytes_per_elem, "combine": off_rank_bytes},
                 "e2e": {"value": flops_all / (e2e_max * 1e-3) / 1e12, "unit": "TFLOP/s", "ms_per_step": e2e_max,
                         "h2d_bytes_per_step": x_host.numel() * 2 + ids_host.numel() * 8 + w_host.numel() * 4,
                         "d2h_bytes_per_step": y_host.numel() * 2},

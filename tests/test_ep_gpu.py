@@ -109,6 +109,65 @@ def test_layer_step_native_glue_matches_tensor_glue(dev):
     assert planned.steps_repeated == 0 and tiny.steps_repeated == 1 and torch.equal(repeated, native)
 
 
+@pytest.mark.parametrize("hidden", [1024, 3072])
+def test_quantized_dispatch_writes_the_gemm_workspace_byte_for_byte(dev, hidden):
+    """The sender-side quantisation against the GEMM's own: rows scattered as NVFP4 codes + scale rows (and re-laid into
+    atoms) must equal, byte for byte, what the split path's quantisation kernel makes of the same BF16 rows after the
+    BF16 dispatch.  Out-of-range pairs are skipped and reported."""
+    tokens, k, e, cap_m = 200, 3, 2, 384
+    g = torch.Generator().manual_seed(77)
+    x = (torch.randn(tokens, hidden, generator=g) * torch.exp(torch.randn(tokens, 1, generator=g))).to(torch.bfloat16).to(dev)
+    perm = torch.randperm(e * cap_m, generator=g)[:tokens * k]
+    dst_row = perm.to(dev)
+    dst_row[5] = -1                                                        # a pair that did not fit: skipped silently
+    dst_rank = torch.zeros(tokens * k, dtype=torch.int64, device=dev)
+    status = torch.zeros(1, dtype=torch.int32, device=dev)
+    rows = _C.QuantizedRows(torch.zeros(e * cap_m * (hidden + hidden // 8), dtype=torch.uint8, device=dev), e, cap_m, hidden)
+    peers = torch.tensor([rows.store.data_ptr()], dtype=torch.int64, device=dev)
+    _C.dispatch_quantized_peer(x, k, peers, dst_rank, dst_row, rows, status)
+    _C.relayout_scales(rows)
+    bf16 = torch.zeros(e * cap_m, hidden, dtype=torch.bfloat16, device=dev)
+    _C.dispatch_rows_peer(x, None, k, torch.tensor([bf16.data_ptr()], dtype=torch.int64, device=dev), dst_rank, dst_row, hidden,
+                          e * cap_m, status)
+    a0, a1, sfa = _C.debug_split_workspace(bf16)
+    torch.cuda.synchronize()
+    assert int(status.item()) == 0
+    live = torch.zeros(e * cap_m, dtype=torch.bool, device=dev)
+    live[dst_row[dst_row >= 0]] = True
+    assert torch.equal(rows.a0[live], a0[live]) and torch.equal(rows.a1[live], a1[live])
+    # scale atoms: compare the words of the live rows (rows nobody wrote hold zeros on one side, the scale floor on the other)
+    r = torch.arange(e * cap_m, device=dev)
+    def words(atoms):
+        at = atoms.reshape(e * cap_m // 128, hidden // 64, 2, 32, 4, 4)    # [row block][atom][pass][r % 32][r / 32][byte]
+        return at[r // 128, :, :, r % 32, (r % 128) // 32]                 # (rows, atoms, passes, 4 bytes)
+    assert torch.equal(words(rows.scale_atoms)[live], words(sfa)[live])
+    dst_row[7] = e * cap_m + 3                                             # out of range: skipped, bit 3
+    _C.dispatch_quantized_peer(x, k, peers, dst_rank, dst_row, rows, status)
+    torch.cuda.synchronize()
+    assert int(status.item()) == 8
+
+
+def test_layer_with_quantized_dispatch_equals_bf16_dispatch(dev):
+    """One rank: the layer whose dispatch sends NVFP4 codes against the layer whose dispatch sends BF16 rows -- the same
+    codes reach the same GEMM kernels, so the outputs are identical; both against the all-to-all path."""
+    e, hidden, inter, tokens, k = 4, 1024, 128, 300, 2
+    g = torch.Generator().manual_seed(15)
+    up_w = (torch.randn(e, 2 * inter, hidden, generator=g) * 0.05).to(torch.bfloat16).to(dev)
+    down_w = (torch.randn(e, hidden, inter, generator=g) * 0.05).to(torch.bfloat16).to(dev)
+    up, down = nvfp4_gemm.quantize_weight_nvfp4(up_w), nvfp4_gemm.quantize_weight_nvfp4(down_w)
+    x = torch.randn(tokens, hidden, generator=g).to(torch.bfloat16).to(dev)
+    ids, wts = route_topk(torch.randn(tokens, e, generator=g).to(dev), k)
+    quant = ExpertParallelMoE(e, hidden, inter, up, down, alignment=128, peer_rows_cap=256)
+    plain = ExpertParallelMoE(e, hidden, inter, up, down, alignment=128, peer_rows_cap=256, quantized_dispatch=False)
+    assert quant.peer[0].q is not None and plain.peer[0].q is None
+    yq = [quant(x, ids, wts) for _ in range(2)]
+    yp = plain(x, ids, wts)
+    ya = ExpertParallelMoE(e, hidden, inter, up, down, alignment=128)(x, ids, wts)
+    torch.cuda.synchronize()
+    assert quant.steps_repeated == 0 and plain.steps_repeated == 0
+    assert torch.equal(yq[0], yp) and torch.equal(yq[1], yp) and torch.equal(yp, ya)
+
+
 def test_layer_step_against_the_oracle_dense_reference(dev):
     """One rank, the layer with the CUDA kernels against the single-process oracle statement of the same layer (per
     expert, oracle GEMMs on its rows): the layer is compared with the CPU oracle, not only with itself."""
@@ -149,7 +208,7 @@ def test_bounded_barrier_times_out_without_hanging(dev):
     assert int(status.item()) == 0
 
 
-def _two_rank_worker(rank, world, port, results):
+def _two_rank_worker(rank, world, port, results, hidden):
     import os
     import torch.distributed as dist
     os.environ.update(MASTER_ADDR="127.0.0.1", MASTER_PORT=str(port))
@@ -157,7 +216,7 @@ def _two_rank_worker(rank, world, port, results):
     dev = torch.device("cuda", rank)
     dist.init_process_group("nccl", rank=rank, world_size=world, device_id=dev)
     try:
-        e, hidden, inter, tokens, k = 8, 512, 256, 384 + 128 * rank, 2
+        e, hidden, inter, tokens, k = 8, hidden, 256, 384 + 128 * rank, 2
         e_local = e // world
         g = torch.Generator().manual_seed(4)
         up_w = (torch.randn(e, 2 * inter, hidden, generator=g) * 0.05).to(torch.bfloat16)
@@ -177,14 +236,17 @@ def _two_rank_worker(rank, world, port, results):
         tiny = ExpertParallelMoE(e, hidden, inter, up, down, alignment=128, peer_rows_cap=128)
         y_fallback = tiny(x, ids, wts)                        # does not fit: every rank takes the all-to-all path
         torch.cuda.synchronize()
-        results[rank] = (peer.peer is not None, peer.peer_error, rel_l2(ys[0], y_a2a), rel_l2(ys[2], y_a2a),
+        results[rank] = (peer.peer is not None and (peer.peer[0].q is not None) == (hidden % 1024 == 0), peer.peer_error,
+                         rel_l2(ys[0], y_a2a), rel_l2(ys[2], y_a2a),
                          max(rel_l2(y_fallback, y_a2a), rel_l2(y_halves, y_a2a)), bool(torch.isfinite(ys[2].float()).all()))
     finally:
         dist.destroy_process_group()
 
 
-def test_two_ranks_peer_memory_path_matches_all_to_all_path():
-    """Two GPUs: dispatch/combine over peer memory against the NCCL all-to-all path, same routing."""
+@pytest.mark.parametrize("hidden", [512, 1024], ids=["bf16_rows", "quantised_rows"])
+def test_two_ranks_peer_memory_path_matches_all_to_all_path(hidden):
+    """Two GPUs: dispatch/combine over peer memory against the NCCL all-to-all path, same routing; hidden = 1024 sends
+    the rows quantised."""
     if torch.cuda.device_count() < 2:
         pytest.skip("needs two GPUs")
     import socket
@@ -194,7 +256,7 @@ def test_two_ranks_peer_memory_path_matches_all_to_all_path():
         port = s.getsockname()[1]
     mgr = mp.Manager()
     results = mgr.dict()
-    mp.spawn(_two_rank_worker, args=(2, port, results), nprocs=2, join=True)
+    mp.spawn(_two_rank_worker, args=(2, port, results, hidden), nprocs=2, join=True)
     for rank in range(2):
         has_peer, err, first, third, fallback, finite = results[rank]
         assert has_peer, err
