@@ -19,7 +19,8 @@
 // Measured on B200 (E=8 x 512 rows, N=28672, K=4096): twelve small copies per peer and K block (an earlier
 // layout with strided shares) ran at ~6 B/clk per CTA and set the pace of the kernel at 0.78 ms; transform
 // threads storing straight into the peers' shared memory (st.shared::cluster + a releasing remote arrive) were
-// slower still, 1.65 ms for pairs and 1.78 ms for quads, because every transform warp then sits out the round trip.
+// slower still, 1.65 ms for pairs and 1.78 ms for quads: every transform warp then sits out the round trip, and a
+// cluster-scope releasing arrive alone costs ~1500 cycles on this GPU (measured later, in the split path's pair kernel).
 //
 // The scale factors reach tensor memory through tcgen05.st issued by the (otherwise idle) epilogue warps, not
 // through tensor-memory copies issued by the MMA thread; see the MMA role below.
@@ -49,10 +50,8 @@ using gemm::Ring;
 
 constexpr uint32_t BM = 128, BN = 256, BK = 128, kKAtoms = 2;
 constexpr uint32_t kSlotB = BN * BK / 2, kSlotSFB = kKAtoms * 2 * 512;
-// the epilogue warps sit on warp ids whose low two bits are their tensor-memory quadrant
-// four scale warps (one per tensor-memory quadrant) that do nothing else, so the scale factors of the next tile's first
-// K blocks go up while the eight epilogue warps (two per quadrant, 128 accumulator columns each) are still storing
-// 32 warps: four single-thread roles, eight scale warps (per tensor-memory quadrant one for the weight scales and one
+// 32 warps (scale and epilogue warps sit on warp ids whose low two bits are their tensor-memory quadrant): four
+// single-thread roles, eight scale warps (per tensor-memory quadrant one for the weight scales and one
 // for the activation scales), eight epilogue warps (two per quadrant, 128 accumulator columns each), twelve transform
 // warps.  The scale warps do nothing else: an event trace showed one warp per quadrant carrying both kinds of scales
 // to be the slowest stage of the pipeline (it shares its scheduler with seven other warps), and scale warps that double

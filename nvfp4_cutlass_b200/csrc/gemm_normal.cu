@@ -26,6 +26,7 @@
 // (G_W epilogue), src/kernels/sm100_bf16_dual_nvfp4_gemm.hpp:226-480 (launcher).
 #include <cuda_bf16.h>
 
+#include "gemm_common.cuh"
 #include "host_common.hpp"
 #include "launchers.hpp"
 #include "transform.cuh"
@@ -55,7 +56,8 @@ struct Cfg {
     static constexpr uint32_t kOffSFA0 = kOffB + kDepthB * kSlotB;
     static constexpr uint32_t kOffSFA1 = kOffSFA0 + kDepthP * kSlotSFA;
     static constexpr uint32_t kOffSFB = kOffSFA1 + kDepthP * kSlotSFA;
-    static constexpr uint32_t kOffBars = kOffSFB + kDepthB * kSlotSFB;
+    static constexpr uint32_t kOffStage = kOffSFB + kDepthB * kSlotSFB;     // epilogue staging (gemm::store_rows_staged)
+    static constexpr uint32_t kOffBars = kOffStage + 4 * gemm::kStageWarp;
     static constexpr uint32_t kNumBars = 2 * 3 + 2 * kDepthP + 3 * kDepthB + 2;
     static constexpr uint32_t kSmemBytes = kOffBars + kNumBars * 8 + 16;
     static constexpr uint32_t kSmemAlloc = kSmemBytes + 1024;            // slack to align the base to 1024 B
@@ -81,28 +83,8 @@ struct Params {
     int32_t* status;           // may be null
 };
 
-struct Ring {
-    uint32_t slot = 0, phase = 0;
-    template <uint32_t kDepth>
-    __device__ __forceinline__ void advance()
-    {
-        if (++slot == kDepth) { slot = 0; phase ^= 1; }
-    }
-};
-
-__device__ __forceinline__ void tile_coords(uint32_t tile, uint32_t num_m, uint32_t num_n, uint32_t group_m,
-                                            uint32_t& m_blk, uint32_t& n_blk)
-{
-    // groups of `group_m` row blocks; inside a group consecutive tiles walk the row
-    // blocks first, so CTAs running side by side share weight tiles and, across the
-    // wave, activation tiles (both served from L2).
-    const uint32_t per_group = group_m * num_n;
-    const uint32_t g = tile / per_group, r = tile % per_group;
-    const uint32_t first = g * group_m;
-    const uint32_t rows = min(group_m, num_m - first);
-    m_blk = first + r % rows;
-    n_blk = r / rows;
-}
+using gemm::Ring;
+using gemm::tile_coords;
 
 template <uint32_t BN, uint32_t kXformWarps, bool kResidual, bool kDirectA, int kPolicy>
 __global__ void __launch_bounds__((kWarpXform0 + kXformWarps) * 32, 1)
@@ -303,29 +285,29 @@ gemm_normal_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_consta
             const float g = __ldg(p.gw + e);
             if (!ptx::mbar_wait(tmem_full, acc_phase, abort_flag, pa, 0)) { give_up(1); break; }
             ptx::tcgen05_fence_after_sync();
-            const uint32_t row = m_blk * BM + quad * 32 + lane;
-            __nv_bfloat16* drow = p.d + static_cast<int64_t>(row) * p.ldd + n_blk * BN;
+            // 64 columns at a time: tensor memory -> registers -> x G_W -> BF16 -> four whole 128-byte lines per store
+            // instruction through the warp's staging area; the accumulator goes back to the MMA warp as soon as this
+            // warp's last columns are in registers, so the stores of the tail run under the next tile's main loop
+            const uint32_t stage = smem + C::kOffStage + (warp - kWarpEpi0) * gemm::kStageWarp;
+            __nv_bfloat16* d_lane = p.d + static_cast<int64_t>(m_blk * BM + quad * 32 + (lane >> 3)) * p.ldd + n_blk * BN + (lane & 7u) * 8;
 #pragma unroll 1
-            for (uint32_t c = 0; c < BN; c += 32) {
-                uint32_t v[32];
-                ptx::tmem_ld_32x32b_x32(tmem_base + ((quad * 32) << 16) + kColAcc + c, v);
-                ptx::tmem_ld_wait();
+            for (uint32_t c = 0; c < BN; c += 64) {
+                uint32_t o[32];
                 {
-                    uint32_t o[16];
-#pragma unroll
-                    for (int i = 0; i < 16; ++i) {
-                        const __nv_bfloat162 h = __floats2bfloat162_rn(__uint_as_float(v[2 * i]) * g,
-                                                                       __uint_as_float(v[2 * i + 1]) * g);
-                        o[i] = *reinterpret_cast<const uint32_t*>(&h);
+                    uint32_t va[32], vb[32];
+                    ptx::tmem_ld_32x32b_x32(tmem_base + ((quad * 32) << 16) + kColAcc + c, va);
+                    ptx::tmem_ld_32x32b_x32(tmem_base + ((quad * 32) << 16) + kColAcc + c + 32, vb);
+                    ptx::tmem_ld_wait();
+                    if (c + 64 == BN) {
+                        ptx::tcgen05_fence_before_sync();
+                        __syncwarp();
+                        if (lane == 0) ptx::mbar_arrive(tmem_empty);
                     }
-                    uint4* dst = reinterpret_cast<uint4*>(drow + c);
-#pragma unroll
-                    for (int i = 0; i < 4; ++i) dst[i] = make_uint4(o[4 * i], o[4 * i + 1], o[4 * i + 2], o[4 * i + 3]);
+                    gemm::scale_pack_bf16(va, g, o);
+                    gemm::scale_pack_bf16(vb, g, o + 16);
                 }
+                gemm::store_rows_staged(o, stage, d_lane + c, p.ldd, lane);
             }
-            ptx::tcgen05_fence_before_sync();
-            __syncwarp();
-            if (lane == 0) ptx::mbar_arrive(tmem_empty);
             acc_phase ^= 1;
         }
     } else if (warp >= kWarpXform0) {
