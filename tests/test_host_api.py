@@ -144,6 +144,24 @@ def test_new_entry_points_validate_without_gpu():
     assert lib.nvfp4_load_checkpoint_weights(9, None, None, None, None, 1, 1, 64, None, None, None, None) == 1
     assert lib.nvfp4_read_status(None, None, None) == 1
     assert lib.nvfp4_debug_wait_timeout(0, None, None) == 1
+    # normal orientation: alignment 128, or 256 as the caller's statement of whole row pairs; nothing else
+    rc = lib.nvfp4_grouped_gemm_contiguous(None, 0, None, None, None, None, 0, None, 384, 256, 128, 1, 0, 1, 0, 256, None, None, None)
+    assert rc == 1 and b"multiple of the token-tile alignment" in lib.nvfp4_last_error()
+    rc = lib.nvfp4_grouped_gemm_contiguous(None, 0, None, None, None, None, 0, None, 384, 256, 128, 1, 0, 1, 0, 64, None, None, None)
+    assert rc == 1 and b"128 or 256" in lib.nvfp4_last_error()
+    # quantised dispatch: K in steps of 1024 up to 8192; planes must not overlap
+    rc = lib.nvfp4_dispatch_quantized_peer(None, 0, 4, 2, 1536, None, 0, 0, None, None, 1, 128, 0, None, None)
+    assert rc == 1 and b"1024" in lib.nvfp4_last_error()
+    rc = lib.nvfp4_dispatch_quantized_peer(ctypes.c_void_p(16), 1024, 4, 2, 1024, ctypes.c_void_p(16), 100, 200, ctypes.c_void_p(16),
+                                           ctypes.c_void_p(16), 1, 128, 0, None, None)
+    assert rc == 1 and b"planes" in lib.nvfp4_last_error()
+    assert lib.nvfp4_dispatch_quantized_peer(None, 0, 0, 2, 1024, None, 0, 0, None, None, 1, 128, 0, None, None) == 0   # no tokens
+    rc = lib.nvfp4_relayout_scales(None, None, 2, 100, 1024, None, None)
+    assert rc == 1 and b"max_m" in lib.nvfp4_last_error()
+    rc = lib.nvfp4_grouped_gemm_masked_quantized(None, None, None, None, None, None, None, 0, None, 2, 128, 128, 128, 1, None, None, None)
+    assert rc == 1 and b"256" in lib.nvfp4_last_error()
+    assert lib.nvfp4_grouped_gemm_masked_quantized(None, None, None, None, None, None, None, 0, None, 0, 128, 256, 128, 1, None, None, None) == 0
+    assert lib.nvfp4_debug_mma_peak_pair(0, None, None) == 1
 
 
 def test_operands_must_share_one_device():
