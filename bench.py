@@ -61,7 +61,7 @@ WORKLOADS = {
 # under profiles/, on the reduced workloads c2s / c4s (the full ones exceed what a multi-pass capture should
 # hold), as (bytes measured, algorithmic bytes of that captured launch).  Both kernels stream every operand
 # once, so traffic grows in proportion to the algorithmic bytes; a full launch is scaled by that ratio.
-NCU_TRAFFIC = {"normal": (246.59e6, 251.66e6, "split-path kernels on c2s, captured at commit 70bfc9c"),
+NCU_TRAFFIC = {"normal": (246.45e6, 251.66e6, "split-path kernels (CTA-pair GEMM) on c2s, captured at commit 253fbe0"),
                "swap_ab": (925.44e6, 911.22e6, "decode kernel on c4s, captured at commit 70bfc9c")}
 
 
