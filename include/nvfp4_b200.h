@@ -235,8 +235,11 @@ NVFP4_API int nvfp4_grouped_gemm_masked_quantized(const void* a0, const void* a1
  *   A pair with dst_rank outside [0, world) or dst_row outside [0, rows_cap) is skipped; row -1 is the plan's mark
  *   for "does not fit", anything else out of range also ORs bit 3 into *device_status (may be NULL).
  * nvfp4_combine_rows_peer: y[t] = sum over j < k of w[t*k+j] * (row src_row[t*k+j] of rank src_rank[t*k+j]'s
- *   buffer), read with plain loads over NVLink.  The caller orders it after every rank has written its buffer.
- *   Pairs out of range (as above) contribute nothing.
+ *   buffer), read over NVLink: with per-thread loads (bulk_copies = 0), or with one bulk copy per row into shared memory
+ *   (bulk_copies != 0; needs two tokens' rows, 2 * k * hidden * 2 bytes, to fit in shared memory, else the first form
+ *   runs) -- a few SMs then saturate the NVLink port, where per-thread loads need most of the GPU.  Same summation order,
+ *   same bits.  The caller orders it after every rank has written its buffer.  Pairs out of range (as above) contribute
+ *   nothing.  device_status (may be NULL) receives bit 0 if a bounded wait of the bulk form expires.
  * sm_budget: the number of SMs the kernel may fill (one 1024-thread block each); 0 = all.  A caller that overlaps these
  *   kernels with GEMMs on another stream gives them a few SMs and sizes the GEMMs to the rest with nvfp4_set_num_sms.
  * Precondition of both plans: expert ids lie in [0, num_experts); ids outside are ignored by the histogram, get no
@@ -252,7 +255,8 @@ NVFP4_API int nvfp4_dispatch_rows_peer(const void* src, int64_t src_ld_bytes, co
                                        int sm_budget, int32_t* device_status, void* stream);
 NVFP4_API int nvfp4_combine_rows_peer(const int64_t* peers, int64_t rows_ld_elems, const int64_t* src_rank,
                                       const int64_t* src_row, const float* w, int64_t tokens, int k, int hidden,
-                                      void* y, int64_t y_ld_elems, int world, int64_t rows_cap, int sm_budget, void* stream);
+                                      void* y, int64_t y_ld_elems, int world, int64_t rows_cap, int sm_budget, int bulk_copies,
+                                      int32_t* device_status, void* stream);
 
 /* The routing plan for the masked layout (nvfp4_grouped_gemm_masked): every local expert owns cap_m rows of its
  * rank's buffer, so nothing about the plan has to come back to the host.  all_counts[s * E + e] = pairs rank s routes

@@ -66,7 +66,7 @@ def lib() -> ctypes.CDLL:
         L.nvfp4_peer_barrier.argtypes = [vp, i32, i32, i32, i64, i64, vp, vp]
         L.nvfp4_expert_histogram.argtypes = [vp, i64, i32, vp, vp]
         L.nvfp4_grouped_gemm_swiglu_contiguous.argtypes = [vp, i64, vp, vp, vp, vp, i64, vp, i32, i32, i32, i32, i32, vp, vp, vp]
-        L.nvfp4_combine_rows_peer.argtypes = [vp, i64, vp, vp, vp, i64, i32, i32, vp, i64, i32, i64, i32, vp]
+        L.nvfp4_combine_rows_peer.argtypes = [vp, i64, vp, vp, vp, i64, i32, i32, vp, i64, i32, i64, i32, i32, vp, vp]
         L.nvfp4_combine_rows.argtypes = [vp, i64, vp, vp, i64, i32, i32, vp, i64, vp]
         L.nvfp4_dispatch_quantized_peer.argtypes = [vp, i64, i64, i32, i32, vp, i64, i64, vp, vp, i32, i64, i32, vp, vp]
         L.nvfp4_relayout_scales.argtypes = [vp, vp, i32, i32, i32, vp, vp]
@@ -472,17 +472,20 @@ def m_grouped_quantized_dual_nvfp4_gemm_masked(rows: "QuantizedRows", b, sfb, gw
 
 
 def combine_rows_peer(peers: torch.Tensor, rows_ld_elems: int, src_rank: torch.Tensor, src_row: torch.Tensor, w: torch.Tensor,
-                      tokens: int, hidden: int, rows_cap: int, out: torch.Tensor = None, sm_budget: int = 0) -> torch.Tensor:
-    """y[t] = sum_j w[t, j] * (row src_row[t, j] of rank src_rank[t, j]'s buffer), BF16, into `out` if given."""
+                      tokens: int, hidden: int, rows_cap: int, out: torch.Tensor = None, sm_budget: int = 0, bulk: bool = True,
+                      status: torch.Tensor = None) -> torch.Tensor:
+    """y[t] = sum_j w[t, j] * (row src_row[t, j] of rank src_rank[t, j]'s buffer), BF16, into `out` if given.  `bulk`:
+    rows fetched by bulk copies into shared memory (a few SMs saturate NVLink) instead of per-thread loads."""
     n = src_rank.numel()
     _require(_i64_ok(src_rank, n) and _i64_ok(src_row, n) and _i64_ok(peers, 1) and w.is_cuda and w.dtype == torch.float32 and
              w.is_contiguous() and w.numel() == n and n % max(tokens, 1) == 0, "bad index / weight tensors")
     _require(out is None or (_rows_ok(out) and out.shape == (tokens, hidden)), "out is a (tokens, hidden) BF16 CUDA tensor")
     y = out if out is not None else torch.empty(tokens, hidden, dtype=torch.bfloat16, device=w.device)
     k = n // tokens if tokens else 1
-    with torch.cuda.device(_one_device(peers, src_rank, src_row, w)):
+    with torch.cuda.device(_one_device(peers, src_rank, src_row, w, status)):
         _check(lib().nvfp4_combine_rows_peer(peers.data_ptr(), rows_ld_elems, src_rank.data_ptr(), src_row.data_ptr(), w.data_ptr(),
-                                             tokens, k, hidden, y.data_ptr(), y.stride(0), peers.numel(), rows_cap, int(sm_budget), _stream()))
+                                             tokens, k, hidden, y.data_ptr(), y.stride(0), peers.numel(), rows_cap, int(sm_budget),
+                                             1 if bulk else 0, status.data_ptr() if status is not None else None, _stream()))
     return y
 
 

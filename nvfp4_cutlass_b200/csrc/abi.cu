@@ -591,7 +591,7 @@ int nvfp4_grouped_gemm_masked_quantized(const void* a0, const void* a1, const vo
 
 int nvfp4_combine_rows_peer(const int64_t* peers, int64_t rows_ld_elems, const int64_t* src_rank, const int64_t* src_row,
                             const float* w, int64_t tokens, int k, int hidden, void* y, int64_t y_ld_elems, int world,
-                            int64_t rows_cap, int sm_budget, void* stream)
+                            int64_t rows_cap, int sm_budget, int bulk_copies, int32_t* device_status, void* stream)
 {
     host::clear_error();
     NVFP4_REQUIRE(tokens >= 0 && k >= 1 && hidden > 0 && hidden % 8 == 0, "k >= 1 and hidden a positive multiple of 8 (k=%d, hidden=%d)", k, hidden);
@@ -605,8 +605,8 @@ int nvfp4_combine_rows_peer(const int64_t* peers, int64_t rows_ld_elems, const i
     if (int rc = host::device_info(-1, &dev)) return rc;
     NVFP4_REQUIRE(sm_budget >= 0, "sm_budget must not be negative");
     return launch_combine_rows_peer(peers, rows_ld_elems, src_rank, src_row, w, tokens, k, hidden, y, y_ld_elems, world, rows_cap,
-                                    sm_budget > 0 && sm_budget < dev->hw_sms ? sm_budget : dev->hw_sms,
-                                    static_cast<cudaStream_t>(stream));
+                                    sm_budget > 0 && sm_budget < dev->hw_sms ? sm_budget : dev->hw_sms, bulk_copies != 0,
+                                    device_status, static_cast<cudaStream_t>(stream));
 }
 
 int nvfp4_debug_decompose(const void* a, int64_t lda_elems, int M, int K, int scale_policy, void* q0, void* q1,

@@ -51,7 +51,7 @@ int launch_relayout_scales(const void* sf_rows, const int32_t* masked_m, int max
                            cudaStream_t stream);
 int launch_combine_rows_peer(const int64_t* peers, int64_t rows_ld_elems, const int64_t* src_rank, const int64_t* src_row,
                              const float* w, int64_t tokens, int k, int hidden, void* y, int64_t y_ld_elems, int world,
-                             int64_t rows_cap, int num_sms, cudaStream_t stream);
+                             int64_t rows_cap, int num_sms, bool bulk, int32_t* status, cudaStream_t stream);
 
 int launch_gemm_swap(const void* a, int64_t lda, const void* b, const void* sfb, const float* gw, void* d,
                      int64_t ldd, const int32_t* m_indices, int M, int N, int K, int E, bool residual,

@@ -295,6 +295,103 @@ combine_rows_peer_kernel(const int64_t* __restrict__ peers, int64_t rows_ld16, c
     }
 }
 
+// The same combine with the rows fetched by bulk copies (cp.async.bulk global -> shared, completing on an mbarrier)
+// instead of per-thread loads: a bulk copy is one request for a whole row, and a CTA can have its entire shared memory
+// in flight, where a thread's loads over NVLink are bounded by what the SM's load path keeps outstanding (sixteen SMs of
+// the kernel above pull ~250 GB/s, all 148 about 600).
+// One CTA per granted SM.  Shared memory is a ring of slots, a slot = the k rows of one token.  Thread 0 walks the CTA's
+// tokens, waits for a slot to be free and requests the rows of every valid pair; the other warps wait for the slot's
+// bytes, form y[t] = sum_j w[t, j] * row_j in FP32 in ascending j (the order of the kernel above and of the all-to-all
+// path: the same bits), store the BF16 row and free the slot.  No multicast; every wait is bounded.
+// Measured (2 GPUs, 16384 tokens x 8 rows of 8 KB per rank): on the whole GPU 0.85 ms against 0.88 ms for the kernel
+// above; on 8 SMs the eight arithmetic warps, not NVLink, set the pace (2.5 ms for half the tokens).
+constexpr int kBulkThreads = 288;                       // warp 0: requests; warps 1-8: arithmetic
+__global__ void __launch_bounds__(kBulkThreads, 1)
+combine_rows_bulk_kernel(const int64_t* __restrict__ peers, int64_t rows_ld_bytes, const int64_t* __restrict__ src_rank,
+                         const int64_t* __restrict__ src_row, const float* __restrict__ w, int64_t tokens, int k, int row_bytes,
+                         uint4* __restrict__ y, int64_t y_ld16, int world, int64_t rows_cap, int slots, int32_t* __restrict__ status)
+{
+    extern __shared__ uint8_t smem_raw[];
+    const uint32_t smem = (ptx::smem_u32(smem_raw) + 127u) & ~127u;
+    uint8_t* gen = smem_raw + (smem - ptx::smem_u32(smem_raw));
+    const uint32_t slot_bytes = static_cast<uint32_t>(k) * row_bytes;
+    uint64_t* full = reinterpret_cast<uint64_t*>(gen + static_cast<size_t>(slots) * slot_bytes);
+    uint64_t* empty = full + slots;
+    volatile uint32_t* abort_flag = reinterpret_cast<volatile uint32_t*>(empty + slots);
+    constexpr int kWorkers = kBulkThreads / 32 - 1;
+    if (threadIdx.x == 0) {
+        for (int i = 0; i < slots; ++i) { ptx::mbar_init(full + i, 1); ptx::mbar_init(empty + i, kWorkers); }
+        *abort_flag = 0;
+        ptx::fence_mbar_init();
+    }
+    __syncthreads();
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    auto valid_pair = [&](int64_t p) {
+        const int64_t pr = src_rank[p], prow = src_row[p];
+        return pr >= 0 && pr < world && prow >= 0 && prow < rows_cap;
+    };
+    if (warp == 0) {
+        if (lane == 0) {
+            uint32_t slot = 0, phase = 0;
+            for (int64_t t = blockIdx.x; t < tokens; t += gridDim.x) {
+                if (!ptx::mbar_wait_impl(empty + slot, phase ^ 1, abort_flag)) {
+                    *abort_flag = 1;
+                    if (status != nullptr) atomicOr(status, 1);
+                    break;
+                }
+                uint32_t bytes = 0;
+                for (int j = 0; j < k; ++j) bytes += valid_pair(t * k + j) ? row_bytes : 0;
+                ptx::mbar_arrive_expect_tx(full + slot, bytes);
+                for (int j = 0; j < k; ++j) {
+                    const int64_t p = t * k + j;
+                    if (!valid_pair(p)) continue;
+                    const uint8_t* row = reinterpret_cast<const uint8_t*>(peers[src_rank[p]]) + src_row[p] * rows_ld_bytes;
+                    ptx::bulk_load(gen + static_cast<size_t>(slot) * slot_bytes + static_cast<size_t>(j) * row_bytes, row, row_bytes, full + slot);
+                }
+                if (++slot == static_cast<uint32_t>(slots)) { slot = 0; phase ^= 1; }
+            }
+        }
+    } else {
+        uint32_t slot = 0, phase = 0;
+        const int worker = threadIdx.x - 32, row16 = row_bytes / 16;
+        for (int64_t t = blockIdx.x; t < tokens; t += gridDim.x) {
+            float wj[16];
+            bool live[16];
+            for (int j = 0; j < k; ++j) { live[j] = valid_pair(t * k + j); wj[j] = live[j] ? w[t * k + j] : 0.0f; }
+            if (!ptx::mbar_wait_impl(full + slot, phase, abort_flag)) {
+                *abort_flag = 1;
+                if (status != nullptr) atomicOr(status, 1);
+                break;
+            }
+            const uint32_t base = smem + slot * slot_bytes;
+            for (int c = worker; c < row16; c += kWorkers * 32) {
+                float acc[8] = {0, 0, 0, 0, 0, 0, 0, 0};
+                for (int j = 0; j < k; ++j) {
+                    if (!live[j]) continue;                     // contributes nothing (its bytes were never requested)
+                    const uint4 v = ptx::lds128(base + j * row_bytes + c * 16);
+                    const uint32_t vw[4] = {v.x, v.y, v.z, v.w};
+#pragma unroll
+                    for (int i = 0; i < 4; ++i) {
+                        const float2 f = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162*>(&vw[i]));
+                        acc[2 * i] = fmaf(wj[j], f.x, acc[2 * i]);
+                        acc[2 * i + 1] = fmaf(wj[j], f.y, acc[2 * i + 1]);
+                    }
+                }
+                uint32_t ow[4];
+#pragma unroll
+                for (int i = 0; i < 4; ++i) {
+                    const __nv_bfloat162 pk = __floats2bfloat162_rn(acc[2 * i], acc[2 * i + 1]);
+                    ow[i] = *reinterpret_cast<const uint32_t*>(&pk);
+                }
+                y[t * y_ld16 + c] = make_uint4(ow[0], ow[1], ow[2], ow[3]);
+            }
+            __syncwarp();
+            if (lane == 0) ptx::mbar_arrive(empty + slot);
+            if (++slot == static_cast<uint32_t>(slots)) { slot = 0; phase ^= 1; }
+        }
+    }
+}
+
 // counts[e] += number of ids equal to e (counts zeroed by the caller); per-block histogram in shared memory first, so
 // that the global atomics are one per expert and block instead of one per pair on a handful of addresses
 __global__ void __launch_bounds__(1024)
@@ -480,8 +577,28 @@ int launch_dispatch_rows_peer(const void* src, int64_t src_ld_bytes, const int64
 
 int launch_combine_rows_peer(const int64_t* peers, int64_t rows_ld_elems, const int64_t* src_rank, const int64_t* src_row,
                              const float* w, int64_t tokens, int k, int hidden, void* y, int64_t y_ld_elems, int world,
-                             int64_t rows_cap, int num_sms, cudaStream_t stream)
+                             int64_t rows_cap, int num_sms, bool bulk, int32_t* status, cudaStream_t stream)
 {
+    // bulk copies: a slot holds the k rows of a token; at least two slots must fit beside the barriers
+    const size_t slot_bytes = static_cast<size_t>(k) * hidden * 2;
+    constexpr size_t kSmemMax = 232448 - 1024;
+    const int slots = slot_bytes ? static_cast<int>((kSmemMax - 256) / slot_bytes) : 0;
+    if (bulk && slots >= 2 && k <= 16 && (hidden * 2) % 16 == 0) {
+        const int use = slots > 8 ? 8 : slots;
+        const size_t smem = use * slot_bytes + 2 * use * 8 + 16 + 128;
+        static bool attr_set[host::kMaxDevices] = {};
+        int dev = 0;
+        NVFP4_CUDA_CHECK(cudaGetDevice(&dev));
+        if (!attr_set[dev]) {
+            NVFP4_CUDA_CHECK(cudaFuncSetAttribute(combine_rows_bulk_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, static_cast<int>(kSmemMax)));
+            attr_set[dev] = true;
+        }
+        combine_rows_bulk_kernel<<<static_cast<unsigned>(num_sms), kBulkThreads, smem, stream>>>(
+            peers, rows_ld_elems * 2, src_rank, src_row, w, tokens, k, hidden * 2, static_cast<uint4*>(y), y_ld_elems / 8, world, rows_cap,
+            use, status);
+        NVFP4_CUDA_CHECK(cudaGetLastError());
+        return NVFP4_OK;
+    }
     combine_rows_peer_kernel<<<static_cast<unsigned>(num_sms), kPeerThreads, 0, stream>>>(peers, rows_ld_elems / 8, src_rank, src_row, w, tokens,
                                                                              k, hidden / 8, static_cast<uint4*>(y), y_ld_elems / 8,
                                                                              world, rows_cap);

@@ -222,7 +222,7 @@ class ExpertParallelMoE:
 
     def __init__(self, num_experts: int, hidden: int, inter: int, up, down, group=None, alignment: int = 128,
                  gemm: Optional[Callable] = None, native_glue: bool = True, peer_rows_cap: int = 0, micro_batches: int = 1,
-                 check_each_step: bool = True, comm_sms: int = 16, quantized_dispatch: bool = True):
+                 check_each_step: bool = True, comm_sms: int = 16, quantized_dispatch: bool = True, bulk_combine: bool = True):
         self.group = group
         self.world = dist.get_world_size(group) if dist.is_initialized() else 1
         self.rank = dist.get_rank(group) if dist.is_initialized() else 0
@@ -258,6 +258,7 @@ class ExpertParallelMoE:
         # scales (1.125 instead of 2 bytes per element); the owners' up-projection then starts from the codes.  Same
         # codes as quantising the BF16 rows on arrival, so the layer's output does not change by a bit.
         self.quantized_dispatch = bool(quantized_dispatch) and hidden % 1024 == 0 and hidden <= 8192
+        self.bulk_combine = bool(bulk_combine)   # combine fetches rows by bulk copies into shared memory (see combine_rows_bulk_kernel)
         if peer_rows_cap > 0 and torch.cuda.is_available() and masked_ok:
             dev = torch.device("cuda", torch.cuda.current_device())
             cap_m = (int(peer_rows_cap) + 127) // 128 * 128
@@ -376,7 +377,7 @@ class ExpertParallelMoE:
             mark()
             buf.barrier(pending.pop(0))             # every rank's expert outputs are complete
             _C.combine_rows_peer(buf.out_peers, self.hidden, plan.dst_rank, plan.dst_row, w_flat, x.shape[0], self.hidden,
-                                 buf.rows_cap, out=y, sm_budget=self.comm_sms)
+                                 buf.rows_cap, out=y, sm_budget=self.comm_sms, bulk=self.bulk_combine, status=buf.status)
             mark()
         except BaseException:
             for slot in pending:

@@ -94,7 +94,7 @@ def run(args, workload: str, world: int, rank: int, local: int) -> None:
     layer = ExpertParallelMoE(E_TOTAL, HIDDEN, INTER, up, down, alignment=128,
                               peer_rows_cap=expert_rows_cap(world, micro) if use_peer else 0, micro_batches=micro,
                               check_each_step=False, comm_sms=extra.get("ep_comm_sms", 16),
-                              quantized_dispatch=extra.get("ep_quant", 1) != 0)
+                              quantized_dispatch=extra.get("ep_quant", 1) != 0, bulk_combine=extra.get("ep_bulk", 1) != 0)
     exchange = "nccl all_to_all"
     if layer.peer is not None:
         rows_as = ("rows quantised by the sender, NVFP4 codes + scales over NVLink (1.125 B/element)" if layer.peer[0].q is not None

@@ -83,6 +83,33 @@ def test_combine_rows_matches_tensor_ops(dev):
     assert rel_l2(got, want) < 2e-3
 
 
+@pytest.mark.parametrize("hidden,k", [(1024, 8), (4096, 8), (2048, 3), (512, 16)])
+def test_combine_over_peer_memory_bulk_copies_equal_thread_loads(dev, hidden, k):
+    """The combine that fetches rows by bulk copies into shared memory against the one that loads them per thread and
+    against tensor operations: same ascending-j FP32 sum, same bits; pairs out of range contribute nothing; more tokens
+    than the ring has slots per CTA."""
+    tokens, rows_cap = 700, 3000
+    g = torch.Generator().manual_seed(31 + hidden)
+    rows = torch.randn(rows_cap, hidden, generator=g).to(torch.bfloat16).to(dev)
+    src_row = torch.randint(0, rows_cap, (tokens * k,), generator=g).to(dev)
+    src_row[3] = -1
+    src_row[11] = rows_cap + 5
+    src_rank = torch.zeros(tokens * k, dtype=torch.int64, device=dev)
+    src_rank[20] = 7                                                       # no such rank
+    w = torch.rand(tokens * k, generator=g).to(dev)
+    peers = torch.tensor([rows.data_ptr()], dtype=torch.int64, device=dev)
+    status = torch.zeros(1, dtype=torch.int32, device=dev)
+    bulk = _C.combine_rows_peer(peers, hidden, src_rank, src_row, w, tokens, hidden, rows_cap, bulk=True, status=status)
+    few = _C.combine_rows_peer(peers, hidden, src_rank, src_row, w, tokens, hidden, rows_cap, bulk=True, status=status, sm_budget=3)
+    plain = _C.combine_rows_peer(peers, hidden, src_rank, src_row, w, tokens, hidden, rows_cap, bulk=False)
+    torch.cuda.synchronize()
+    assert int(status.item()) == 0
+    assert torch.equal(bulk, plain) and torch.equal(few, plain)
+    ok = (src_row >= 0) & (src_row < rows_cap) & (src_rank == 0)
+    want = (rows[src_row.clamp(0, rows_cap - 1)].float() * (w * ok).unsqueeze(1)).reshape(tokens, k, hidden).sum(dim=1)
+    assert rel_l2(bulk, want.to(torch.bfloat16)) < 4e-3
+
+
 def test_layer_step_native_glue_matches_tensor_glue(dev):
     """One rank, 8 experts: the layer with the library's kernels against the layer with tensor operations
     around the same GEMM calls."""
@@ -231,6 +258,9 @@ def _two_rank_worker(rank, world, port, results, hidden):
         peer = ExpertParallelMoE(e, hidden, inter, up, down, alignment=128, peer_rows_cap=512)
         y_a2a = a2a(x, ids, wts)
         ys = [peer(x, ids, wts) for _ in range(3)]            # repeated steps reuse the buffers
+        # other tokens through the same buffers: nothing of the earlier steps may survive in any cache on the way
+        x2 = (x.float() * -0.5 + 0.25).to(torch.bfloat16)
+        fresh = rel_l2(peer(x2, ids, wts), a2a(x2, ids, wts))
         halves = ExpertParallelMoE(e, hidden, inter, up, down, alignment=128, peer_rows_cap=512, micro_batches=2)
         y_halves = [halves(x, ids, wts) for _ in range(2)][1]
         tiny = ExpertParallelMoE(e, hidden, inter, up, down, alignment=128, peer_rows_cap=128)
@@ -238,7 +268,7 @@ def _two_rank_worker(rank, world, port, results, hidden):
         torch.cuda.synchronize()
         results[rank] = (peer.peer is not None and (peer.peer[0].q is not None) == (hidden % 1024 == 0), peer.peer_error,
                          rel_l2(ys[0], y_a2a), rel_l2(ys[2], y_a2a),
-                         max(rel_l2(y_fallback, y_a2a), rel_l2(y_halves, y_a2a)), bool(torch.isfinite(ys[2].float()).all()))
+                         max(rel_l2(y_fallback, y_a2a), rel_l2(y_halves, y_a2a), fresh), bool(torch.isfinite(ys[2].float()).all()))
     finally:
         dist.destroy_process_group()
 

@@ -85,9 +85,14 @@ def run_case(dev, oracle, workload, extra_kw=None, **check_kw):
     return worst
 
 
-@pytest.mark.parametrize("path", ["default", "fused"])
+PATHS = {"default": None, "fused": dict(tune_split_transform=2), "single_cta_split": dict(tune_split_transform=1, tune_cluster=1),
+         "pair_split": dict(tune_split_transform=1, tune_cluster=2)}
+
+
+@pytest.mark.parametrize("path", ["default", "fused", "single_cta_split"])
 def test_c2_mixtral_up_projection(dev, oracle, path):
-    run_case(dev, oracle, "c2", dict(tune_split_transform=2) if path == "fused" else None)
+    """The default is the CTA-pair GEMM here: every expert has 512 rows and the case says m_alignment=256."""
+    run_case(dev, oracle, "c2", PATHS[path])
 
 
 @pytest.mark.parametrize("workload", ["c3up", "c3down"])
@@ -101,5 +106,7 @@ def test_c4_decode(dev, oracle):
 
 
 @pytest.mark.parametrize("workload", ["c5up", "c5down"])
-def test_c5_expert_parallel_gemms_at_one_rank(dev, oracle, workload):
-    run_case(dev, oracle, workload)
+@pytest.mark.parametrize("path", ["default", "pair_split"])
+def test_c5_expert_parallel_gemms_at_one_rank(dev, oracle, workload, path):
+    """pair_split: 128 experts with ragged row counts, so about half of them end in a left-over single row block."""
+    run_case(dev, oracle, workload, PATHS[path])
