@@ -335,7 +335,7 @@ class ExpertParallelMoE:
         y.index_add_(0, plan.order // k, back.float() * topk_w.reshape(-1)[plan.order].unsqueeze(1))
         return y.to(torch.bfloat16)
 
-    def _peer_step(self, buf: "PeerBuffers", x, topk_ids, topk_w, y, marks: Optional[list] = None) -> None:
+    def _peer_step(self, buf: "PeerBuffers", x, topk_ids, topk_w, y, marks: Optional[list] = None, gemm_gate=None) -> None:
         """One (micro-)step over peer memory on the current stream, into `y`.  Nothing here reads anything back to the
         host.  Everything that can fail on this rank alone -- argument checks, allocations -- happens before the first
         barrier; if a call between the barriers raises all the same, the remaining barriers are still enqueued before
@@ -368,12 +368,20 @@ class ExpertParallelMoE:
                                       sm_budget=self.comm_sms)
             buf.barrier(pending.pop(0))             # all rows have landed everywhere
             mark()
+            # Micro-batches: the GEMMs of the parts run one part after the other (each fills the SMs it is given), so
+            # that a part's combine has the whole GEMM phase of the next part to hide under.  Left to the hardware's
+            # choice the parts' GEMM kernels alternate, every part finishes late and the combines pile up at the end.
+            if gemm_gate is not None and gemm_gate[0] is not None:
+                torch.cuda.current_stream().wait_event(gemm_gate[0])
             if buf.q is not None:
                 _C.relayout_scales(buf.q, plan.masked_m)
                 _C.m_grouped_quantized_dual_nvfp4_gemm_masked(buf.q, *self.up, buf.h, plan.masked_m, device_status=buf.status)
             else:
                 self.gemm_masked(buf.a, *self.up, buf.h, plan.masked_m, device_status=buf.status)
             self.gemm_masked(buf.h, *self.down, buf.out, plan.masked_m, fold_swiglu=True, device_status=buf.status)
+            if gemm_gate is not None:
+                gemm_gate[0] = torch.cuda.Event()
+                gemm_gate[0].record()
             mark()
             buf.barrier(pending.pop(0))             # every rank's expert outputs are complete
             _C.combine_rows_peer(buf.out_peers, self.hidden, plan.dst_rank, plan.dst_row, w_flat, x.shape[0], self.hidden,
@@ -399,12 +407,13 @@ class ExpertParallelMoE:
         bounds = [tokens * i // self.micro for i in range(self.micro + 1)]
         all_sms = _C.get_num_sms()
         _C.set_num_sms(max(all_sms - self.comm_sms, 1))      # the GEMMs leave the communication kernels their SMs
+        gate = [None]                                        # event after the previous part's GEMMs
         try:
             for i, stream in enumerate(self.streams):
                 lo, hi = bounds[i], bounds[i + 1]
                 stream.wait_stream(cur)
                 with torch.cuda.stream(stream):
-                    self._peer_step(self.peer[i], x[lo:hi], topk_ids[lo:hi], topk_w[lo:hi], y[lo:hi], marks if i == 0 else None)
+                    self._peer_step(self.peer[i], x[lo:hi], topk_ids[lo:hi], topk_w[lo:hi], y[lo:hi], marks if i == 0 else None, gate)
             for stream in self.streams:
                 cur.wait_stream(stream)
         finally:
