@@ -222,7 +222,7 @@ class ExpertParallelMoE:
 
     def __init__(self, num_experts: int, hidden: int, inter: int, up, down, group=None, alignment: int = 128,
                  gemm: Optional[Callable] = None, native_glue: bool = True, peer_rows_cap: int = 0, micro_batches: int = 1,
-                 check_each_step: bool = True, comm_sms: int = 16, quantized_dispatch: bool = True, bulk_combine: bool = True):
+                 check_each_step: bool = True, comm_sms: int = 24, quantized_dispatch: bool = True, bulk_combine: bool = True):
         self.group = group
         self.world = dist.get_world_size(group) if dist.is_initialized() else 1
         self.rank = dist.get_rank(group) if dist.is_initialized() else 0

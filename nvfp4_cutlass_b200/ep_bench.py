@@ -88,12 +88,13 @@ def run(args, workload: str, world: int, rank: int, local: int) -> None:
     # several GPUs: dispatch and combine over peer memory unless ep_peer=0 asks for the NCCL all-to-all path;
     # room for 1.5 x the average rows a rank receives (a step that does not fit falls back by itself)
     use_peer = extra.get("ep_peer", 1) != 0
-    # micro-batches on streams of their own were measured no faster on 2 GPUs (4.5-5.3 ms against 4.64 ms: the SMs the
-    # communication kernels need to keep NVLink busy are taken from the GEMMs), so a step is one batch unless asked
-    micro = extra.get("ep_micro", 1)
+    # Micro-batches on streams of their own (the NVLink traffic of one part under the GEMMs of another, the parts' GEMM
+    # phases chained one after the other): measured on 4 GPUs 4.07 ms with four parts and 24 communication SMs against
+    # 4.44 ms for one batch; on 2 GPUs, where less crosses NVLink, 4.10 against 4.04 ms.  So four parts from 4 GPUs up.
+    micro = extra.get("ep_micro", 4 if world >= 4 else 1)
     layer = ExpertParallelMoE(E_TOTAL, HIDDEN, INTER, up, down, alignment=128,
                               peer_rows_cap=expert_rows_cap(world, micro) if use_peer else 0, micro_batches=micro,
-                              check_each_step=False, comm_sms=extra.get("ep_comm_sms", 16),
+                              check_each_step=False, comm_sms=extra.get("ep_comm_sms", 24),
                               quantized_dispatch=extra.get("ep_quant", 1) != 0, bulk_combine=extra.get("ep_bulk", 1) != 0)
     exchange = "nccl all_to_all"
     if layer.peer is not None:
