@@ -141,7 +141,7 @@ dispatch_rows_peer_kernel(const uint4* __restrict__ src, int64_t src_ld16, const
 // the first two are what the split path's GEMM reads through its tensor maps; the scale rows are re-laid into
 // 512-byte tensor-memory atoms by relayout_scales_kernel on the owner (scattering 4-byte words over NVLink instead
 // would cost more than the BF16 rows did).
-// One warp per token.  In round j lane l owns the block pair j * 32 + l (32 elements): its loads are 64-byte pieces of
+// One warp per token.  In step j lane l owns the block pair j * 32 + l (32 elements): its loads are 64-byte pieces of
 // one row, its code stores 16 bytes next to its neighbours' (512 contiguous bytes per warp instruction).  Scale bytes
 // are gathered by shuffles so that every lane stores 8 consecutive bytes per pass.  K % 1024 == 0.
 template <int kRounds>
