@@ -159,10 +159,56 @@ def run(args, workload: str, world: int, rank: int, local: int) -> None:
         wd.copy_(w_host, non_blocking=True)
         y_host.copy_(layer(xd, idd, wd), non_blocking=True)
 
-    e2e_ms, _, _ = bench.timed(e2e_step, max(3, min(steps, 10)), 3, barrier)
+    e2e_steps = max(4, min(steps, 10)) // 2 * 2
+    e2e_seq_ms, _, _ = bench.timed(e2e_step, e2e_steps, 3, barrier)
+
+    # The same steps as a three-stage pipeline: inputs of step i + 1 go up and the result of step i - 1 comes back (both over
+    # PCIe, on streams of their own) while step i computes.  Every step still copies its own inputs and its own result.
+    up, down, cur = torch.cuda.Stream(device=dev), torch.cuda.Stream(device=dev), torch.cuda.current_stream()
+    bufs = [dict(x=torch.empty_like(x), ids=torch.empty_like(ids), w=torch.empty_like(wts),
+                 out=torch.empty(tokens, HIDDEN, dtype=torch.bfloat16).pin_memory(), loaded=None, computed=None, stored=None)
+            for _ in range(2)]
+
+    def piped_step(i):
+        b = bufs[i % 2]
+        with torch.cuda.stream(up):
+            if b["computed"] is not None:
+                up.wait_event(b["computed"])              # step i - 2 has read these inputs
+            b["x"].copy_(x_host, non_blocking=True)
+            b["ids"].copy_(ids_host, non_blocking=True)
+            b["w"].copy_(w_host, non_blocking=True)
+            b["loaded"] = torch.cuda.Event()
+            b["loaded"].record()
+        cur.wait_event(b["loaded"])
+        y_dev = layer(b["x"], b["ids"], b["w"])
+        b["computed"] = torch.cuda.Event()
+        b["computed"].record()
+        with torch.cuda.stream(down):
+            down.wait_event(b["computed"])
+            y_dev.record_stream(down)
+            b["out"].copy_(y_dev, non_blocking=True)
+
+    for i in range(4):
+        piped_step(i)
+    torch.cuda.synchronize()
+    barrier()
+    ev0, ev1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    ev0.record()
+    up.wait_event(ev0)
+    down.wait_event(ev0)
+    for i in range(e2e_steps):
+        piped_step(i)
+    cur.wait_stream(up)
+    cur.wait_stream(down)
+    ev1.record()
+    torch.cuda.synchronize()
+    barrier()
+    e2e_ms = ev0.elapsed_time(ev1) / e2e_steps
+    e2e_same = bool(torch.equal(bufs[0]["out"], y_host))
+    del bufs
 
     flops_rank = 2.0 * real_rows * (2 * INTER * HIDDEN + HIDDEN * INTER)
-    stats = torch.tensor([ms, e2e_ms, flops_rank, phases[0], phases[1], phases[2]] + (peer_phases or [0.0] * 4),
+    stats = torch.tensor([ms, e2e_ms, flops_rank, phases[0], phases[1], phases[2]] + (peer_phases or [0.0] * 4) + [e2e_seq_ms],
                          dtype=torch.float64, device=dev)
     if world > 1:
         mx = stats.clone()
@@ -207,7 +253,10 @@ def run(args, workload: str, world: int, rank: int, local: int) -> None:
                 "nvlink_bytes_per_rank_peer_path": {"dispatch": off_rank_elems * dispatch_bytes_per_elem, "combine": off_rank_bytes},
                 "e2e": {"value": flops_all / (e2e_max * 1e-3) / 1e12, "unit": "TFLOP/s", "ms_per_step": e2e_max,
                         "h2d_bytes_per_step": x_host.numel() * 2 + ids_host.numel() * 8 + w_host.numel() * 4,
-                        "d2h_bytes_per_step": y_host.numel() * 2},
+                        "d2h_bytes_per_step": y_host.numel() * 2, "one_step_at_a_time_ms": float(mx[10]),
+                        "result_equals_sequential": e2e_same,
+                        "note": "three-stage pipeline: the next step's inputs go up and the previous step's result comes back "
+                                "(PCIe, streams of their own) while a step computes; each step copies its own inputs and result"},
                 "gpu_launches": kernels_per_step * steps, "kernels_per_step": kernels_per_step, "clocks": clocks}
         if world == 1:
             # the one-GPU point of a scaling series: the headline configuration C2 rides along as a sub-record, and the
