@@ -410,34 +410,66 @@ expert_histogram_kernel(const int64_t* __restrict__ ids, int64_t n, int num_expe
 }
 
 // Routing plan of the peer-memory path, from the gathered (source rank, expert) count matrix (plan_offsets_masked_kernel
-// below gives base and limit).
-// plan_rows (one block per expert): dst_row[p] = base[e] + (number of pairs p' < p routed to e), for every pair p
-// routed to e -- a stable counting sort without the sort: pairs keep their order inside an expert's group.
-// With `limit` (fixed-capacity plan) a pair whose row would reach limit[e] does not fit and gets row -1.
-__global__ void __launch_bounds__(1024)
-plan_rows_kernel(const int64_t* __restrict__ ids, int64_t n, const int64_t* __restrict__ base, const int64_t* __restrict__ limit,
-                 int64_t* __restrict__ dst_row)
+// below gives base and limit): dst_row[p] = base[e] + (number of pairs p' < p routed to e), for every pair p routed to e
+// -- a stable counting sort without the sort: pairs keep their order inside an expert's group.  With `limit`
+// (fixed-capacity plan) a pair whose row would reach limit[e] does not fit and gets row -1.
+// Two passes over the pairs, each block on its own chunk: plan_chunk_hist_kernel counts every chunk's pairs per expert;
+// plan_rows_kernel starts each expert's counter at base[e] + (pairs of e in earlier chunks) and hands out rows chunk-locally:
+// 1024 pairs at a time, the warps take turns in order (inside a warp __match_any_sync ranks the lanes of one expert), so
+// the order of the pairs is kept.  (The first version gave every expert a block that scanned ALL pairs: 128 experts x
+// 131072 pairs took 0.2 ms.)
+constexpr int kPlanThreads = 1024;
+__global__ void __launch_bounds__(kPlanThreads)
+plan_chunk_hist_kernel(const int64_t* __restrict__ ids, int64_t n, int64_t chunk, int num_experts, int32_t* __restrict__ chunk_hist)
 {
-    __shared__ int warp_tot[32];
-    const int e = blockIdx.x, lane = threadIdx.x & 31, wid = threadIdx.x >> 5;
-    const int64_t end = limit != nullptr ? limit[e] : INT64_MAX;
-    int64_t running = base[e];
-    for (int64_t chunk = 0; chunk < n; chunk += blockDim.x) {
-        const int64_t p = chunk + threadIdx.x;
-        const bool mine = p < n && ids[p] == e;
-        const unsigned ballot = __ballot_sync(0xffffffffu, mine);
-        const int lane_rank = __popc(ballot & ((1u << lane) - 1u));
-        if (lane == 0) warp_tot[wid] = __popc(ballot);
-        __syncthreads();
-        int before = 0, total = 0;
-        for (int w = 0; w < static_cast<int>(blockDim.x >> 5); ++w) {
-            const int c = warp_tot[w];
-            before += w < wid ? c : 0;
-            total += c;
+    extern __shared__ int hist_s[];
+    for (int e = threadIdx.x; e < num_experts; e += blockDim.x) hist_s[e] = 0;
+    __syncthreads();
+    const int64_t lo = blockIdx.x * chunk, hi = min(lo + chunk, n);
+    for (int64_t p = lo + threadIdx.x; p < hi; p += blockDim.x) {
+        const int64_t e = ids[p];
+        if (e >= 0 && e < num_experts) atomicAdd(&hist_s[e], 1);
+    }
+    __syncthreads();
+    for (int e = threadIdx.x; e < num_experts; e += blockDim.x) chunk_hist[static_cast<int64_t>(blockIdx.x) * num_experts + e] = hist_s[e];
+}
+
+__global__ void __launch_bounds__(kPlanThreads)
+plan_rows_kernel(const int64_t* __restrict__ ids, int64_t n, int64_t chunk, int num_experts, const int32_t* __restrict__ chunk_hist,
+                 const int64_t* __restrict__ base, const int64_t* __restrict__ limit, int64_t* __restrict__ dst_row)
+{
+    extern __shared__ long long next_row[];          // [num_experts] next free row of every expert, for this chunk onwards
+    for (int e = threadIdx.x; e < num_experts; e += blockDim.x) {
+        long long r = base[e];
+        for (int c = 0; c < static_cast<int>(blockIdx.x); ++c) r += chunk_hist[static_cast<int64_t>(c) * num_experts + e];
+        next_row[e] = r;
+    }
+    __syncthreads();
+    const int lane = threadIdx.x & 31, wid = threadIdx.x >> 5;
+    const int64_t lo = blockIdx.x * chunk, hi = min(lo + chunk, n);
+    for (int64_t p0 = lo; p0 < hi; p0 += blockDim.x) {
+        const int64_t p = p0 + threadIdx.x;
+        const int64_t e = p < hi ? ids[p] : -1;
+        const bool valid = e >= 0 && e < num_experts;
+        // lanes of this warp with the same expert, and this lane's rank among them
+        const unsigned same = __match_any_sync(0xffffffffu, valid ? static_cast<int>(e) : -1 - lane);
+        const int rank_in_warp = __popc(same & ((1u << lane) - 1u));
+        const int leader = __ffs(same) - 1;
+        for (int w = 0; w < kPlanThreads / 32; ++w) {
+            if (w == wid) {
+                long long first = 0;
+                if (valid && lane == leader) {       // one lane per expert present in the warp; experts differ, no race
+                    first = next_row[e];
+                    next_row[e] = first + __popc(same);
+                }
+                first = __shfl_sync(0xffffffffu, first, leader);
+                if (valid) {
+                    const long long row = first + rank_in_warp;
+                    dst_row[p] = (limit == nullptr || row < limit[e]) ? row : -1;
+                }
+            }
+            __syncthreads();
         }
-        if (mine) dst_row[p] = running + before + lane_rank < end ? running + before + lane_rank : -1;
-        running += total;
-        __syncthreads();
     }
 }
 
@@ -550,8 +582,23 @@ int launch_plan_peer_masked(const int64_t* all_counts, int world, int num_expert
 {
     plan_offsets_masked_kernel<<<1, 1024, 0, stream>>>(all_counts, world, num_experts, rank, cap_m, base, limit, masked_m, status);
     NVFP4_CUDA_CHECK(cudaGetLastError());
-    if (n > 0) plan_rows_kernel<<<num_experts, 1024, 0, stream>>>(ids, n, base, limit, dst_row);
-    NVFP4_CUDA_CHECK(cudaGetLastError());
+    if (n == 0) return NVFP4_OK;
+    // chunks of whole 1024-pair steps, at most 128 of them
+    int64_t chunk = (n + 127) / 128;
+    chunk = (chunk + kPlanThreads - 1) / kPlanThreads * kPlanThreads;
+    const unsigned blocks = static_cast<unsigned>((n + chunk - 1) / chunk);
+    int dev = 0;
+    NVFP4_CUDA_CHECK(cudaGetDevice(&dev));
+    cudaMemPool_t pool;
+    if (int rc = host::workspace_pool(dev, &pool)) return rc;
+    int32_t* chunk_hist = nullptr;
+    NVFP4_CUDA_CHECK(cudaMallocFromPoolAsync(reinterpret_cast<void**>(&chunk_hist), sizeof(int32_t) * blocks * num_experts, pool, stream));
+    plan_chunk_hist_kernel<<<blocks, kPlanThreads, num_experts * sizeof(int), stream>>>(ids, n, chunk, num_experts, chunk_hist);
+    plan_rows_kernel<<<blocks, kPlanThreads, num_experts * sizeof(long long), stream>>>(ids, n, chunk, num_experts, chunk_hist, base, limit,
+                                                                                      dst_row);
+    const cudaError_t err = cudaGetLastError();
+    cudaFreeAsync(chunk_hist, stream);
+    if (err != cudaSuccess) return host::fail(NVFP4_E_CUDA, "plan kernels failed to launch: %s", cudaGetErrorString(err));
     return NVFP4_OK;
 }
 

@@ -220,8 +220,9 @@ def run(args, workload: str, world: int, rank: int, local: int) -> None:
     ms_max, e2e_max, flops_all = float(mx[0]), float(mx[1]), float(sm[2])
     # kernels of this library per step: 2 GEMMs x (activation quantisation + GEMM), SwiGLU, and the row movers
     # (+ histogram and the two plan kernels on the peer-memory path)
-    # peer path: per micro-batch histogram + 2 plan kernels + dispatch + 2 x (quantise + GEMM) + combine (+ 3 barriers)
-    kernels_per_step = (micro * (9 + (3 if world > 1 else 0)) if layer.peer is not None else
+    # peer path, per micro-batch: histogram, 3 plan kernels, dispatch, scale relayout, up GEMM, down quantise + GEMM, combine
+    # (+ 3 barriers); with BF16 dispatch the relayout is an activation-quantisation kernel instead
+    kernels_per_step = (micro * (10 + (3 if world > 1 else 0)) if layer.peer is not None else
                         4 + (0 if layer.gemm_swiglu is not None else 1) + (2 if world == 1 else 4))
     if rank == 0:
         fp4_peak = bench.measure_fp4_peak()
