@@ -225,6 +225,19 @@ NVFP4_API int nvfp4_grouped_gemm_masked_quantized(const void* a0, const void* a1
                                                   const int32_t* masked_m, int E, int max_m, int N, int K, int enable_residual_pass,
                                                   const int32_t* tune, int32_t* device_status, void* stream);
 
+/* The up-projection of a SwiGLU expert MLP with the activation AND the next GEMM's activation quantisation folded into
+ * its epilogue.  The weights (N = 2 I rows per expert) must be interleaved in runs of 32: rows [256 t + 64 g, +32) are gate
+ * rows 128 t + 32 g ..., rows [256 t + 64 g + 32, +32) the matching up rows (I % 128 == 0), so that every 64 accumulator
+ * columns a thread holds are 32 gate values and their 32 up values.  The epilogue forms bf16(silu(bf16 gate) * bf16 up) --
+ * the arithmetic of nvfp4_swiglu -- runs Algorithm 1 (derived_div8, both passes) on it and writes the quantised workspace of
+ * the down-projection: out_a0, out_a1 (E * max_m, I / 2) packed codes and out_scale_atoms (E * max_m / 128, I / 64, 2, 512),
+ * ready for nvfp4_grouped_gemm_masked_quantized with K = I.  The (rows, 2 I) BF16 intermediate is never written.  Inputs as
+ * nvfp4_grouped_gemm_masked_quantized.  No counterpart in the reference (its benchmarks stop at the GEMM). */
+NVFP4_API int nvfp4_grouped_gemm_masked_quantized_swiglu(const void* a0, const void* a1, const void* scale_atoms, const void* b,
+                                                         const void* sfb, const float* gw, void* out_a0, void* out_a1,
+                                                         void* out_scale_atoms, const int32_t* masked_m, int E, int max_m, int N, int K,
+                                                         const int32_t* tune, int32_t* device_status, void* stream);
+
 /* The same two steps over peer memory, for ranks on the GPUs of one NVLink domain.  `peers` is a device array
  * with one int64 per rank: the address, in THIS process, of that rank's copy of a symmetric buffer (rows of
  * `row_bytes`, stride dst_ld_bytes / rows_ld_elems, the same on every rank).  No counterpart in the reference.

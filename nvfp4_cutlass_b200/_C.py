@@ -30,7 +30,7 @@ EXPORTS = ("nvfp4_last_error", "nvfp4_version", "nvfp4_get_num_sms", "nvfp4_set_
            "nvfp4_quantize_weight", "nvfp4_quantize_weight_static", "nvfp4_grouped_gemm_contiguous", "nvfp4_debug_decompose",
            "nvfp4_debug_mma_peak", "nvfp4_debug_mma_peak_pair", "nvfp4_debug_mma_pattern", "nvfp4_permute_rows", "nvfp4_swiglu", "nvfp4_combine_rows",
            "nvfp4_dispatch_rows_peer", "nvfp4_dispatch_quantized_peer", "nvfp4_relayout_scales",
-           "nvfp4_grouped_gemm_masked_quantized", "nvfp4_combine_rows_peer", "nvfp4_expert_histogram",
+           "nvfp4_grouped_gemm_masked_quantized", "nvfp4_grouped_gemm_masked_quantized_swiglu", "nvfp4_combine_rows_peer", "nvfp4_expert_histogram",
            "nvfp4_grouped_gemm_swiglu_contiguous", "nvfp4_grouped_gemm_masked", "nvfp4_load_checkpoint_weights",
            "nvfp4_read_status", "nvfp4_debug_split_workspace", "nvfp4_debug_wait_timeout", "nvfp4_plan_peer_masked",
            "nvfp4_peer_barrier")
@@ -71,6 +71,7 @@ def lib() -> ctypes.CDLL:
         L.nvfp4_dispatch_quantized_peer.argtypes = [vp, i64, i64, i32, i32, vp, i64, i64, vp, vp, i32, i64, i32, vp, vp]
         L.nvfp4_relayout_scales.argtypes = [vp, vp, i32, i32, i32, vp, vp]
         L.nvfp4_grouped_gemm_masked_quantized.argtypes = [vp, vp, vp, vp, vp, vp, vp, i64, vp, i32, i32, i32, i32, i32, vp, vp, vp]
+        L.nvfp4_grouped_gemm_masked_quantized_swiglu.argtypes = [vp, vp, vp, vp, vp, vp, vp, vp, vp, vp, i32, i32, i32, i32, vp, vp, vp]
         L.nvfp4_grouped_gemm_masked.argtypes = [vp, i64, vp, vp, vp, vp, i64, vp, i32, i32, i32, i32, i32, i32, i32, vp, vp, vp]
         L.nvfp4_load_checkpoint_weights.argtypes = [i32, vp, vp, vp, vp, i32, i32, i32, vp, vp, vp, vp]
         L.nvfp4_read_status.argtypes = [vp, ctypes.POINTER(ctypes.c_int32), vp]
@@ -468,6 +469,43 @@ def m_grouped_quantized_dual_nvfp4_gemm_masked(rows: "QuantizedRows", b, sfb, gw
         _check(lib().nvfp4_grouped_gemm_masked_quantized(
             rows.a0.data_ptr(), rows.a1.data_ptr(), rows.scale_atoms.data_ptr(), b.data_ptr(), sfb.data_ptr(), gw.data_ptr(),
             d.data_ptr(), d.stride(1), masked_m.data_ptr(), e, max_m, n, k, 1 if enable_residual_pass else 0,
+            ctypes.cast(tune_arr, ctypes.c_void_p), device_status.data_ptr() if device_status is not None else None, _stream()))
+
+
+def interleave_gate_up(b: torch.Tensor, sfb: torch.Tensor, num_experts: int, inter: int):
+    """Weights of a fused gate+up projection, (E * 2 I, K / 2) codes and (E * K / 64, 2 I) scale words, with their rows
+    re-ordered for m_grouped_quantized_swiglu_dual_nvfp4_gemm_masked: runs of 32 gate rows followed by the 32 matching
+    up rows, so that every 256-row tile holds 128 (gate, up) pairs.  inter % 128 == 0."""
+    _require(inter % 128 == 0 and b.shape[0] == num_experts * 2 * inter and sfb.shape[1] == 2 * inter, "shapes do not fit I % 128 == 0")
+    new = torch.arange(2 * inter, device=b.device)
+    t, g, hh, i = new // 256, (new // 64) % 4, (new // 32) % 2, new % 32
+    orig = hh * inter + 128 * t + 32 * g + i
+    b2 = b.reshape(num_experts, 2 * inter, -1)[:, orig].reshape(b.shape).contiguous()
+    return b2, sfb[:, orig].contiguous()
+
+
+def m_grouped_quantized_swiglu_dual_nvfp4_gemm_masked(rows: "QuantizedRows", b, sfb, gw, out: "QuantizedRows", masked_m, *,
+                                                      device_status=None, **tune) -> None:
+    """Up-projection over quantised activations `rows` (E, max_m, K) with gate/up-interleaved weights (interleave_gate_up);
+    writes silu(gate) * up, quantised, into `out` (E, max_m, I): its code planes and scale atoms, ready for
+    m_grouped_quantized_dual_nvfp4_gemm_masked with the down-projection's weights."""
+    for key in tune:
+        if key not in TUNE_KEYS:
+            raise TypeError(f"m_grouped_quantized_swiglu_dual_nvfp4_gemm_masked() got an unexpected keyword argument {key!r}")
+    e, max_m, k = rows.e, rows.max_m, rows.k
+    n = 2 * out.k
+    _require(out.e == e and out.max_m == max_m and out.k % 128 == 0, "out is (E, max_m, I) with I % 128 == 0")
+    _require(b.dtype == torch.int8 and sfb.dtype == torch.int32 and gw.dtype == torch.float32 and masked_m.dtype == torch.int32,
+             "b int8, sfb int32, gw float32, masked_m int32")
+    _require(gw.numel() == e and masked_m.numel() == e and b.shape == (e * n, k // 2) and sfb.shape == (e * (k // 64), n),
+             "weight shapes do not fit")
+    _require(b.is_contiguous() and sfb.is_contiguous() and gw.is_contiguous() and masked_m.is_contiguous(),
+             "b, sfb, gw, masked_m are contiguous")
+    tune_arr = (ctypes.c_int32 * len(TUNE_KEYS))(*[int(tune.get(key, 0)) for key in TUNE_KEYS])
+    with torch.cuda.device(_one_device(rows.store, rows.scale_atoms, out.store, out.scale_atoms, b, sfb, gw, masked_m, device_status)):
+        _check(lib().nvfp4_grouped_gemm_masked_quantized_swiglu(
+            rows.a0.data_ptr(), rows.a1.data_ptr(), rows.scale_atoms.data_ptr(), b.data_ptr(), sfb.data_ptr(), gw.data_ptr(),
+            out.a0.data_ptr(), out.a1.data_ptr(), out.scale_atoms.data_ptr(), masked_m.data_ptr(), e, max_m, n, k,
             ctypes.cast(tune_arr, ctypes.c_void_p), device_status.data_ptr() if device_status is not None else None, _stream()))
 
 

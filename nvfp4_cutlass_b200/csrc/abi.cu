@@ -586,8 +586,34 @@ int nvfp4_grouped_gemm_masked_quantized(const void* a0, const void* a1, const vo
     if (dev->cc_major != 10) return host::fail(NVFP4_E_UNSUPPORTED, "needs an sm_100 GPU, found sm_%d%d", dev->cc_major, dev->cc_minor);
     return launch_gemm_split_quantized(a0, a1, scale_atoms, b, sfb, gw, d, ldd_elems, masked_m, max_m, N, K, E, enable_residual_pass != 0,
                                        tune ? tune[5] : 0, tune ? tune[12] : 0, !(tune && tune[11]), dev->num_sms,
-                                       split_gemm_as_pair(tune, static_cast<int64_t>(E) * (max_m / 2), E, false), device_status,
-                                       static_cast<cudaStream_t>(stream));
+                                       split_gemm_as_pair(tune, static_cast<int64_t>(E) * (max_m / 2), E, false), nullptr, nullptr, nullptr,
+                                       device_status, static_cast<cudaStream_t>(stream));
+}
+
+int nvfp4_grouped_gemm_masked_quantized_swiglu(const void* a0, const void* a1, const void* scale_atoms, const void* b, const void* sfb,
+                                               const float* gw, void* out_a0, void* out_a1, void* out_scale_atoms,
+                                               const int32_t* masked_m, int E, int max_m, int N, int K, const int32_t* tune,
+                                               int32_t* device_status, void* stream)
+{
+    host::clear_error();
+    NVFP4_REQUIRE(E >= 0 && max_m >= 0 && N >= 0 && K >= 0, "negative size (E=%d, max_m=%d, N=%d, K=%d)", E, max_m, N, K);
+    NVFP4_REQUIRE(N % 256 == 0 && K % 128 == 0, "N must be a multiple of 256 and K of 128 (N=%d, K=%d)", N, K);
+    NVFP4_REQUIRE(max_m % 128 == 0, "max_m must be a multiple of 128 (max_m=%d)", max_m);
+    NVFP4_REQUIRE(static_cast<int64_t>(E) * max_m <= INT32_MAX, "E * max_m = %lld rows exceed the 32-bit row index",
+                  static_cast<long long>(E) * max_m);
+    if (E == 0 || max_m == 0 || N == 0) return NVFP4_OK;
+    NVFP4_REQUIRE(K > 0, "empty weights (K=%d)", K);
+    NVFP4_REQUIRE(a0 && a1 && scale_atoms && b && sfb && gw && out_a0 && out_a1 && out_scale_atoms && masked_m, "null pointer argument");
+    NVFP4_REQUIRE(((reinterpret_cast<uintptr_t>(a0) | reinterpret_cast<uintptr_t>(a1) | reinterpret_cast<uintptr_t>(scale_atoms) |
+                    reinterpret_cast<uintptr_t>(out_a0) | reinterpret_cast<uintptr_t>(out_a1) | reinterpret_cast<uintptr_t>(out_scale_atoms)) & 15u) == 0,
+                  "all activation buffers must be 16-byte aligned");
+    host::DeviceInfo* dev;
+    if (int rc = host::device_info(-1, &dev)) return rc;
+    if (dev->cc_major != 10) return host::fail(NVFP4_E_UNSUPPORTED, "needs an sm_100 GPU, found sm_%d%d", dev->cc_major, dev->cc_minor);
+    return launch_gemm_split_quantized(a0, a1, scale_atoms, b, sfb, gw, nullptr, 0, masked_m, max_m, N, K, E, true, tune ? tune[5] : 0,
+                                       tune ? tune[12] : 0, !(tune && tune[11]), dev->num_sms,
+                                       split_gemm_as_pair(tune, static_cast<int64_t>(E) * (max_m / 2), E, false), out_a0, out_a1,
+                                       out_scale_atoms, device_status, static_cast<cudaStream_t>(stream));
 }
 
 int nvfp4_combine_rows_peer(const int64_t* peers, int64_t rows_ld_elems, const int64_t* src_rank, const int64_t* src_row,

@@ -166,8 +166,47 @@ struct Params {
     uint32_t m, n, k;          // m: all rows of a / d (masked: groups * max_m)
     uint32_t group_m;
     uint32_t groups, max_m;    // masked layout only
+    // SwiGLU-quantised output (kSwigluOut kernels): the workspace of the NEXT GEMM, whose K is n / 2
+    uint8_t* out_a0;
+    uint8_t* out_a1;
+    uint8_t* out_sf;
     int32_t* status;
 };
+
+
+// Epilogue of an up-projection whose weight rows were interleaved in runs of 32 (gate rows, then the matching up rows):
+// the 64 accumulator columns a lane holds for its row are 32 gate values and their 32 up values.  The activation
+// silu(gate) * up is formed exactly as the stand-alone kernels form it -- both factors rounded to BF16 first, the product
+// rounded to BF16 -- and decomposed on the spot (two 16-blocks per lane), so what leaves the kernel is the quantised
+// workspace of the down-projection: 8 + 8 code bytes per block and pass, and the blocks' scale bytes in their
+// tensor-memory atoms.  The (rows, 2 I) BF16 intermediate is never written and never read back.
+//   o[0..15]: gate columns as BF16 pairs, o[16..31]: up columns; row: row of a / d; pcol: first of the 32 product columns
+__device__ __forceinline__ void store_swiglu_quantized(const uint32_t (&o)[32], const Params& p, uint32_t row, uint32_t pcol)
+{
+    const uint32_t k_out = p.n / 2;
+    uint32_t pw[16];
+#pragma unroll
+    for (int i = 0; i < 16; ++i) {
+        const float2 gf = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162*>(&o[i]));
+        const float2 uf = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162*>(&o[16 + i]));
+        const __nv_bfloat162 pr = __floats2bfloat162_rn(gf.x / (1.0f + __expf(-gf.x)) * uf.x, gf.y / (1.0f + __expf(-gf.y)) * uf.y);
+        pw[i] = *reinterpret_cast<const uint32_t*>(&pr);
+    }
+    const uint32_t w0[8] = {pw[0], pw[1], pw[2], pw[3], pw[4], pw[5], pw[6], pw[7]};
+    const uint32_t w1[8] = {pw[8], pw[9], pw[10], pw[11], pw[12], pw[13], pw[14], pw[15]};
+    xform::Block16 b0, b1;
+    xform::decompose_block16<true, 0>(w0, b0);
+    xform::decompose_block16<true, 0>(w1, b1);
+    const uint64_t code_off = static_cast<uint64_t>(row) * (k_out / 2) + pcol / 2;
+    *reinterpret_cast<uint4*>(p.out_a0 + code_off) = make_uint4(b0.q0[0], b0.q0[1], b1.q0[0], b1.q0[1]);
+    *reinterpret_cast<uint4*>(p.out_a1 + code_off) = make_uint4(b0.q1[0], b0.q1[1], b1.q1[0], b1.q1[1]);
+    // the two blocks are bytes (pcol / 16) % 4 and + 1 of the row's word in the atom of K atom pcol / 64
+    const uint32_t r = row % BM;
+    uint8_t* word = p.out_sf + ((static_cast<uint64_t>(row / BM) * (k_out / 64) + pcol / 64) * 2) * 512 + (r % 32) * 16 + (r / 32) * 4 +
+                    (pcol / 16) % 4;
+    *reinterpret_cast<uint16_t*>(word) = static_cast<uint16_t>(b0.s0 | (b1.s0 << 8));
+    *reinterpret_cast<uint16_t*>(word + 512) = static_cast<uint16_t>(b0.s1 | (b1.s1 << 8));
+}
 
 #ifdef NVFP4_PROBE
 // event trace of block 0 (timing studies): g_trace[point][stage] = clock64 at the event
@@ -177,7 +216,7 @@ __device__ long long g_trace[10][64];
 #define NVFP4_TRACE(point, stage) do { } while (0)
 #endif
 
-template <uint32_t BK, bool kResidual, uint32_t kGroup, bool kMasked>
+template <uint32_t BK, bool kResidual, uint32_t kGroup, bool kMasked, bool kSwigluOut = false>
 __global__ void __launch_bounds__(kThreads, 1)
 gemm_split_kernel(const __grid_constant__ CUtensorMap tm_a0, const __grid_constant__ CUtensorMap tm_a1,
                   const __grid_constant__ CUtensorMap tm_b, const __grid_constant__ CUtensorMap tm_sfb, const Params p)
@@ -388,10 +427,14 @@ gemm_split_kernel(const __grid_constant__ CUtensorMap tm_a0, const __grid_consta
                 gemm::scale_pack_bf16(va, g, o);
                 gemm::scale_pack_bf16(vb, g, o + 16);
             }
-            const uint32_t stage = smem + C::kOffStage + (warp - kWarpEpi0) * gemm::kStageWarp;
-            __nv_bfloat16* d_lane = p.d + static_cast<int64_t>(t.row0 + quad * 32 + (lane >> 3)) * p.ldd + t.n_blk * BN +
-                                    group * 64 + (lane & 7u) * 8;
-            gemm::store_rows_staged(o, stage, d_lane, p.ldd, lane);
+            if constexpr (kSwigluOut) {
+                store_swiglu_quantized(o, p, t.row0 + quad * 32 + lane, t.n_blk * (BN / 2) + group * 32);
+            } else {
+                const uint32_t stage = smem + C::kOffStage + (warp - kWarpEpi0) * gemm::kStageWarp;
+                __nv_bfloat16* d_lane = p.d + static_cast<int64_t>(t.row0 + quad * 32 + (lane >> 3)) * p.ldd + t.n_blk * BN +
+                                        group * 64 + (lane & 7u) * 8;
+                gemm::store_rows_staged(o, stage, d_lane, p.ldd, lane);
+            }
             if (warp == kWarpEpi0) NVFP4_TRACE(8, (tile - blockIdx.x) / gridDim.x);
             acc_phase ^= 1;
         }
@@ -570,7 +613,7 @@ __device__ __forceinline__ void build_units(const int32_t* m_indices, uint32_t n
 }
 
 
-template <uint32_t BK, bool kResidual, bool kMasked>
+template <uint32_t BK, bool kResidual, bool kMasked, bool kSwigluOut = false>
 __global__ void __launch_bounds__(kThreads, 1)
 gemm_split_pair_kernel(const __grid_constant__ CUtensorMap tm_a0, const __grid_constant__ CUtensorMap tm_a1,
                        const __grid_constant__ CUtensorMap tm_b, const __grid_constant__ CUtensorMap tm_sfb, const Params p)
@@ -791,10 +834,14 @@ gemm_split_pair_kernel(const __grid_constant__ CUtensorMap tm_a0, const __grid_c
                 gemm::scale_pack_bf16(va, g, o);
                 gemm::scale_pack_bf16(vb, g, o + 16);
             }
-            const uint32_t stage = smem + C::kOffStage + (warp - kWarpEpi0) * gemm::kStageWarp;
-            __nv_bfloat16* d_lane = p.d + static_cast<int64_t>(my_row0(t) + quad * 32 + (lane >> 3)) * p.ldd + t.n_blk * BN +
-                                    group * 64 + (lane & 7u) * 8;
-            gemm::store_rows_staged(o, stage, d_lane, p.ldd, lane);
+            if constexpr (kSwigluOut) {
+                store_swiglu_quantized(o, p, my_row0(t) + quad * 32 + lane, t.n_blk * (BN / 2) + group * 32);
+            } else {
+                const uint32_t stage = smem + C::kOffStage + (warp - kWarpEpi0) * gemm::kStageWarp;
+                __nv_bfloat16* d_lane = p.d + static_cast<int64_t>(my_row0(t) + quad * 32 + (lane >> 3)) * p.ldd + t.n_blk * BN +
+                                        group * 64 + (lane & 7u) * 8;
+                gemm::store_rows_staged(o, stage, d_lane, p.ldd, lane);
+            }
             if (warp == kWarpEpi0) NVFP4_TRACE(8, (tile - pair_id) / num_pairs);
         }
     }
@@ -822,6 +869,8 @@ struct Call {
     // activations that arrive quantised (the expert-parallel layer's quantised dispatch): the caller's a0, a1
     // (M, K/2) and scale atoms (M/128, K/64, passes, 512) stand in for the workspace and kernel 1 is skipped
     const uint8_t* ext_a0 = nullptr; const uint8_t* ext_a1 = nullptr; const uint8_t* ext_sfa = nullptr;
+    // SwiGLU-quantised output instead of BF16 rows (see store_swiglu_quantized): the next GEMM's a0, a1, scale atoms
+    uint8_t* out_a0 = nullptr; uint8_t* out_a1 = nullptr; uint8_t* out_sf = nullptr;
 };
 
 // Kernel 1 into the given workspace pieces.
@@ -840,7 +889,7 @@ int launch_quantize(const Call& c, uint8_t* a0, uint8_t* a1, uint8_t* sfa)
                                static_cast<uint32_t>(c.K), a0, a1, sfa, c.masked_m, static_cast<uint32_t>(c.max_m > 0 ? c.max_m : 1));
 }
 
-template <uint32_t BK, bool kResidual, uint32_t kGroup, bool kMasked, bool kPair = false>
+template <uint32_t BK, bool kResidual, uint32_t kGroup, bool kMasked, bool kPair = false, bool kSwigluOut = false>
 int launch_variant(const Call& c, Params p)
 {
     using C = std::conditional_t<kPair, PairCfg<BK, kResidual>, Cfg<BK, kResidual, kGroup>>;
@@ -887,8 +936,8 @@ int launch_variant(const Call& c, Params p)
         if (int qrc = launch_quantize<kResidual>(c, a0, a1, sfa)) return release(qrc);
 
     auto kernel = [] {
-        if constexpr (kPair) return gemm_split_pair_kernel<BK, kResidual, kMasked>;
-        else return gemm_split_kernel<BK, kResidual, kGroup, kMasked>;
+        if constexpr (kPair) return gemm_split_pair_kernel<BK, kResidual, kMasked, kSwigluOut>;
+        else return gemm_split_kernel<BK, kResidual, kGroup, kMasked, kSwigluOut>;
     }();
     static bool attr_set[host::kMaxDevices] = {};
     if (!attr_set[dev]) {
@@ -919,6 +968,14 @@ int launch_for_layout(const Call& c, const Params& p, bool residual, int block_k
 {
     // block_k: 0 = the library's choice, 256 = one 256-wide K block per ring position, 128 = 128-wide with a commit
     // per position, 130 = 128-wide in groups of two (requested and freed together, consumed one by one)
+    if constexpr (kMasked) {
+        if (c.out_a0 != nullptr) {          // SwiGLU-quantised output: built for the masked layout with both passes
+            if (!residual) return host::fail(NVFP4_E_UNSUPPORTED, "the SwiGLU-quantised output needs the residual pass");
+            const bool wide = c.K % 256 == 0 && block_k != 128;
+            if (c.pair) return wide ? launch_variant<256, true, 1, true, true, true>(c, p) : launch_variant<128, true, 1, true, true, true>(c, p);
+            return wide ? launch_variant<256, true, 1, true, false, true>(c, p) : launch_variant<128, true, 1, true, false, true>(c, p);
+        }
+    }
     if (!kMasked && block_k == 130)
         return residual ? launch_variant<128, true, 2, false>(c, p) : launch_variant<128, false, 2, false>(c, p);
     if (c.pair) {
@@ -950,6 +1007,7 @@ int launch_gemm_split(const void* a, int64_t lda, const void* b, const void* sfb
     p.m = M; p.n = N; p.k = K;
     p.group_m = group_m > 0 ? group_m : 8;
     p.groups = E; p.max_m = max_m > 0 ? max_m : 1;
+    p.out_a0 = p.out_a1 = p.out_sf = nullptr;
     p.status = status;
     // the pair kernel's unit table covers kMaxUnitBlocks row blocks of the contiguous layout
     const bool use_pair = pair && num_sms >= 2 && (masked_m != nullptr || M / static_cast<int>(BM) <= static_cast<int>(kMaxUnitBlocks));
@@ -960,7 +1018,8 @@ int launch_gemm_split(const void* a, int64_t lda, const void* b, const void* sfb
 // The GEMM alone over activations the caller holds quantised (masked layout: E groups of max_m rows).
 int launch_gemm_split_quantized(const void* a0, const void* a1, const void* sfa, const void* b, const void* sfb, const float* gw,
                                 void* d, int64_t ldd, const int32_t* masked_m, int max_m, int N, int K, int E, bool residual,
-                                int block_k, int group_m, bool pdl, int num_sms, bool pair, int32_t* status, cudaStream_t stream)
+                                int block_k, int group_m, bool pdl, int num_sms, bool pair, void* out_a0, void* out_a1, void* out_sf,
+                                int32_t* status, cudaStream_t stream)
 {
     Params p;
     p.gw = gw;
@@ -971,11 +1030,16 @@ int launch_gemm_split_quantized(const void* a0, const void* a1, const void* sfa,
     p.m = E * max_m; p.n = N; p.k = K;
     p.group_m = group_m > 0 ? group_m : 8;
     p.groups = E; p.max_m = max_m > 0 ? max_m : 1;
+    p.out_a0 = p.out_a1 = p.out_sf = nullptr;
     p.status = status;
     Call c{nullptr, 0, b, sfb, E * max_m, N, K, E, pdl, false, 0, masked_m, max_m, num_sms, pair && num_sms >= 2, stream};
     c.ext_a0 = static_cast<const uint8_t*>(a0);
     c.ext_a1 = static_cast<const uint8_t*>(a1);
     c.ext_sfa = static_cast<const uint8_t*>(sfa);
+    c.out_a0 = static_cast<uint8_t*>(out_a0);
+    c.out_a1 = static_cast<uint8_t*>(out_a1);
+    c.out_sf = static_cast<uint8_t*>(out_sf);
+    p.out_a0 = c.out_a0; p.out_a1 = c.out_a1; p.out_sf = c.out_sf;
     return launch_for_layout<true>(c, p, residual, block_k);
 }
 

@@ -23,7 +23,8 @@ int launch_gemm_split(const void* a, int64_t lda, const void* b, const void* sfb
 
 int launch_gemm_split_quantized(const void* a0, const void* a1, const void* sfa, const void* b, const void* sfb, const float* gw,
                                 void* d, int64_t ldd, const int32_t* masked_m, int max_m, int N, int K, int E, bool residual,
-                                int block_k, int group_m, bool pdl, int num_sms, bool pair, int32_t* status, cudaStream_t stream);
+                                int block_k, int group_m, bool pdl, int num_sms, bool pair, void* out_a0, void* out_a1, void* out_sf,
+                                int32_t* status, cudaStream_t stream);
 
 int launch_debug_split_workspace(const void* a, int64_t lda, int M, int K, int policy, bool residual, bool swiglu, void* a0,
                                  void* a1, void* sfa, cudaStream_t stream);

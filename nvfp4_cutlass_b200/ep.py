@@ -147,11 +147,18 @@ class PeerBuffers:
     NUM_SLOTS = 8
 
     def __init__(self, e_local: int, cap_m: int, hidden: int, inter: int, device: torch.device, group=None, world: int = 1,
-                 rank: int = 0, quantized: bool = False):
+                 rank: int = 0, quantized: bool = False, fused_swiglu: bool = False):
         self.e_local, self.cap_m, self.hidden, self.world, self.rank = e_local, cap_m, hidden, world, rank
         self.rows_cap = e_local * cap_m
         self.status = torch.zeros(1, dtype=torch.int32, device=device)
-        self.h = torch.zeros(e_local, cap_m, 2 * inter, dtype=torch.bfloat16, device=device)
+        # between the two GEMMs: the (rows, 2 I) BF16 gate+up output, or -- SwiGLU and the down-projection's activation
+        # quantisation folded into the up-projection's epilogue -- the quantised (rows, I) activation itself
+        self.h, self.hq = None, None
+        if fused_swiglu:
+            from . import _C
+            self.hq = _C.QuantizedRows(torch.zeros(self.rows_cap * (inter + inter // 8), dtype=torch.uint8, device=device), e_local, cap_m, inter)
+        else:
+            self.h = torch.zeros(e_local, cap_m, 2 * inter, dtype=torch.bfloat16, device=device)
         self.epoch = [0] * self.NUM_SLOTS
         # the input buffer holds BF16 rows, or -- quantised dispatch -- the senders' NVFP4 codes and block scales
         # (1.125 bytes per element: three planes in one allocation, see _C.QuantizedRows)
@@ -222,7 +229,8 @@ class ExpertParallelMoE:
 
     def __init__(self, num_experts: int, hidden: int, inter: int, up, down, group=None, alignment: int = 128,
                  gemm: Optional[Callable] = None, native_glue: bool = True, peer_rows_cap: int = 0, micro_batches: int = 1,
-                 check_each_step: bool = True, comm_sms: int = 24, quantized_dispatch: bool = True, bulk_combine: bool = True):
+                 check_each_step: bool = True, comm_sms: int = 24, quantized_dispatch: bool = True, bulk_combine: bool = True,
+                 fused_swiglu: bool = True):
         self.group = group
         self.world = dist.get_world_size(group) if dist.is_initialized() else 1
         self.rank = dist.get_rank(group) if dist.is_initialized() else 0
@@ -259,13 +267,20 @@ class ExpertParallelMoE:
         # codes as quantising the BF16 rows on arrival, so the layer's output does not change by a bit.
         self.quantized_dispatch = bool(quantized_dispatch) and hidden % 1024 == 0 and hidden <= 8192
         self.bulk_combine = bool(bulk_combine)   # combine fetches rows by bulk copies into shared memory (see combine_rows_bulk_kernel)
+        # SwiGLU and the down-projection's activation quantisation in the up-projection's epilogue (needs the quantised
+        # dispatch's GEMM entry and gate/up-interleaved weights; same bits as the separate kernels)
+        self.fused_swiglu = bool(fused_swiglu) and self.quantized_dispatch and inter % 128 == 0 and self.gemm_masked is not None
+        self.up_interleaved = None
         if peer_rows_cap > 0 and torch.cuda.is_available() and masked_ok:
             dev = torch.device("cuda", torch.cuda.current_device())
             cap_m = (int(peer_rows_cap) + 127) // 128 * 128
             try:
                 self.peer = [PeerBuffers(self.e_local, cap_m, hidden, inter, dev, group, self.world, self.rank,
-                                         quantized=self.quantized_dispatch)
+                                         quantized=self.quantized_dispatch, fused_swiglu=self.fused_swiglu)
                              for _ in range(self.micro)]
+                if self.fused_swiglu:
+                    from . import _C
+                    self.up_interleaved = (*_C.interleave_gate_up(up[0], up[1], self.e_local, inter), up[2])
                 self.streams = [torch.cuda.Stream(device=dev) for _ in range(self.micro)] if self.micro > 1 else []
             except Exception as exc:                                   # symmetric memory unavailable: keep the NCCL path
                 self.peer = None
@@ -373,12 +388,18 @@ class ExpertParallelMoE:
             # choice the parts' GEMM kernels alternate, every part finishes late and the combines pile up at the end.
             if gemm_gate is not None and gemm_gate[0] is not None:
                 torch.cuda.current_stream().wait_event(gemm_gate[0])
-            if buf.q is not None:
+            if buf.hq is not None:
                 _C.relayout_scales(buf.q, plan.masked_m)
-                _C.m_grouped_quantized_dual_nvfp4_gemm_masked(buf.q, *self.up, buf.h, plan.masked_m, device_status=buf.status)
+                _C.m_grouped_quantized_swiglu_dual_nvfp4_gemm_masked(buf.q, *self.up_interleaved, buf.hq, plan.masked_m,
+                                                                     device_status=buf.status)
+                _C.m_grouped_quantized_dual_nvfp4_gemm_masked(buf.hq, *self.down, buf.out, plan.masked_m, device_status=buf.status)
             else:
-                self.gemm_masked(buf.a, *self.up, buf.h, plan.masked_m, device_status=buf.status)
-            self.gemm_masked(buf.h, *self.down, buf.out, plan.masked_m, fold_swiglu=True, device_status=buf.status)
+                if buf.q is not None:
+                    _C.relayout_scales(buf.q, plan.masked_m)
+                    _C.m_grouped_quantized_dual_nvfp4_gemm_masked(buf.q, *self.up, buf.h, plan.masked_m, device_status=buf.status)
+                else:
+                    self.gemm_masked(buf.a, *self.up, buf.h, plan.masked_m, device_status=buf.status)
+                self.gemm_masked(buf.h, *self.down, buf.out, plan.masked_m, fold_swiglu=True, device_status=buf.status)
             if gemm_gate is not None:
                 gemm_gate[0] = torch.cuda.Event()
                 gemm_gate[0].record()

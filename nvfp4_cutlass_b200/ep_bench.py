@@ -95,7 +95,8 @@ def run(args, workload: str, world: int, rank: int, local: int) -> None:
     layer = ExpertParallelMoE(E_TOTAL, HIDDEN, INTER, up, down, alignment=128,
                               peer_rows_cap=expert_rows_cap(world, micro) if use_peer else 0, micro_batches=micro,
                               check_each_step=False, comm_sms=extra.get("ep_comm_sms", 24),
-                              quantized_dispatch=extra.get("ep_quant", 1) != 0, bulk_combine=extra.get("ep_bulk", 1) != 0)
+                              quantized_dispatch=extra.get("ep_quant", 1) != 0, bulk_combine=extra.get("ep_bulk", 1) != 0,
+                              fused_swiglu=extra.get("ep_fuse", 1) != 0)
     exchange = "nccl all_to_all"
     if layer.peer is not None:
         rows_as = ("rows quantised by the sender, NVFP4 codes + scales over NVLink (1.125 B/element)" if layer.peer[0].q is not None
@@ -222,7 +223,8 @@ def run(args, workload: str, world: int, rank: int, local: int) -> None:
     # (+ histogram and the two plan kernels on the peer-memory path)
     # peer path, per micro-batch: histogram, 3 plan kernels, dispatch, scale relayout, up GEMM, down quantise + GEMM, combine
     # (+ 3 barriers); with BF16 dispatch the relayout is an activation-quantisation kernel instead
-    kernels_per_step = (micro * (10 + (3 if world > 1 else 0)) if layer.peer is not None else
+    fused = layer.peer is not None and layer.peer[0].hq is not None     # no activation-quantisation kernel between the GEMMs
+    kernels_per_step = (micro * ((9 if fused else 10) + (3 if world > 1 else 0)) if layer.peer is not None else
                         4 + (0 if layer.gemm_swiglu is not None else 1) + (2 if world == 1 else 4))
     if rank == 0:
         fp4_peak = bench.measure_fp4_peak()
@@ -238,7 +240,9 @@ def run(args, workload: str, world: int, rank: int, local: int) -> None:
                 "config": {"workload": f"expert-parallel MoE layer: E={E_TOTAL} over {world} ranks, {TOKENS} tokens/rank, top-{TOP_K}, "
                                        f"up N={2 * INTER} K={HIDDEN}, down N={HIDDEN} K={INTER}", "name": "c5",
                            "parallelism": f"ep{world}", "l2": "operands larger than L2, no flush", "exchange": exchange,
-                           "step": "dispatch, up GEMM, down GEMM with SwiGLU folded into its activation quantisation, combine"},
+                           "step": ("dispatch, up GEMM with SwiGLU and the down-projection's activation quantisation in its epilogue, "
+                                    "down GEMM, combine") if fused else
+                                   "dispatch, up GEMM, down GEMM with SwiGLU folded into its activation quantisation, combine"},
                 "roofline": {"bound": "tensor", "achieved": achieved, "peak": fp4_peak, "unit": "TFLOP/s",
                              "frac": achieved / fp4_peak, "traffic": None,
                              "note": "the two grouped GEMMs + SwiGLU glue of rank 0, both NVFP4 passes counted",

@@ -186,9 +186,13 @@ def test_layer_with_quantized_dispatch_equals_bf16_dispatch(dev):
     ids, wts = route_topk(torch.randn(tokens, e, generator=g).to(dev), k)
     quant = ExpertParallelMoE(e, hidden, inter, up, down, alignment=128, peer_rows_cap=256)
     plain = ExpertParallelMoE(e, hidden, inter, up, down, alignment=128, peer_rows_cap=256, quantized_dispatch=False)
+    unfused = ExpertParallelMoE(e, hidden, inter, up, down, alignment=128, peer_rows_cap=256, fused_swiglu=False)
     assert quant.peer[0].q is not None and plain.peer[0].q is None
+    # SwiGLU + the down-projection's quantisation in the up-projection's epilogue is on by default with quantised rows
+    assert quant.peer[0].hq is not None and unfused.peer[0].hq is None and unfused.peer[0].q is not None
     yq = [quant(x, ids, wts) for _ in range(2)]
     yp = plain(x, ids, wts)
+    assert torch.equal(unfused(x, ids, wts), yp)
     ya = ExpertParallelMoE(e, hidden, inter, up, down, alignment=128)(x, ids, wts)
     torch.cuda.synchronize()
     assert quant.steps_repeated == 0 and plain.steps_repeated == 0

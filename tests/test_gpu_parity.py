@@ -696,6 +696,49 @@ def test_gemm_masked_layout_with_swiglu_fold_equals_contiguous(dev):
     assert torch.equal(d_masked.reshape(e * max_m, hidden), d_contig)
 
 
+@pytest.mark.parametrize("inter,k", [(128, 256), (384, 640), (512, 1024)])
+@pytest.mark.parametrize("cluster", [1, 2], ids=["single", "pair"])
+def test_up_projection_with_swiglu_and_quantisation_in_its_epilogue(dev, inter, k, cluster):
+    """The masked up-projection that writes the down-projection's quantised workspace straight from its epilogue
+    (gate/up-interleaved weights) against the unfused sequence -- BF16 gate+up output, then the SwiGLU-folded activation
+    quantisation: codes and scale atoms of every live row block byte for byte; then the down-projection on both."""
+    e, max_m, hidden_out = 3, 384, 256
+    counts = [384, 130, 0]
+    g = torch.Generator().manual_seed(60 + inter + k)
+    a = torch.randn(e * max_m, k, generator=g).to(torch.bfloat16).to(dev)
+    w_up = (torch.randn(e, 2 * inter, k, generator=g) * 0.08).to(torch.bfloat16).to(dev)
+    w_down = (torch.randn(e, hidden_out, inter, generator=g) * 0.05).to(torch.bfloat16).to(dev)
+    up, down = nvfp4_gemm.quantize_weight_nvfp4(w_up), nvfp4_gemm.quantize_weight_nvfp4(w_down)
+    masked_m = torch.tensor(counts, dtype=torch.int32, device=dev)
+    status = torch.zeros(1, dtype=torch.int32, device=dev)
+    rows = _C.QuantizedRows(torch.zeros(e * max_m * (k + k // 8), dtype=torch.uint8, device=dev), e, max_m, k)
+    a0, a1, sfa = _C.debug_split_workspace(a)
+    rows.a0.copy_(a0); rows.a1.copy_(a1); rows.scale_atoms.copy_(sfa)
+    tune = dict(tune_cluster=cluster)
+    # unfused: BF16 h, then quantise silu(gate) * up
+    h = torch.zeros(e, max_m, 2 * inter, dtype=torch.bfloat16, device=dev)
+    _C.m_grouped_quantized_dual_nvfp4_gemm_masked(rows, *up, h, masked_m, device_status=status, **tune)
+    want0, want1, want_sf = _C.debug_split_workspace(h.reshape(e * max_m, 2 * inter), fold_swiglu=True)
+    # fused
+    hq = _C.QuantizedRows(torch.zeros(e * max_m * (inter + inter // 8), dtype=torch.uint8, device=dev), e, max_m, inter)
+    bi, sfbi = _C.interleave_gate_up(up[0], up[1], e, inter)
+    _C.m_grouped_quantized_swiglu_dual_nvfp4_gemm_masked(rows, bi, sfbi, up[2], hq, masked_m, device_status=status, **tune)
+    torch.cuda.synchronize()
+    assert _C.read_status(status) == 0
+    for grp, c in enumerate(counts):
+        live = (c + 127) // 128 * 128
+        lo = grp * max_m
+        assert torch.equal(hq.a0[lo:lo + live], want0[lo:lo + live]) and torch.equal(hq.a1[lo:lo + live], want1[lo:lo + live]), grp
+        assert torch.equal(hq.scale_atoms[lo // 128:(lo + live) // 128], want_sf[lo // 128:(lo + live) // 128]), grp
+        assert int(hq.a0[lo + live:lo + max_m].max() if live < max_m else 0) == 0          # dead row blocks untouched
+    d_fused = torch.zeros(e, max_m, hidden_out, dtype=torch.bfloat16, device=dev)
+    d_plain = torch.zeros_like(d_fused)
+    _C.m_grouped_quantized_dual_nvfp4_gemm_masked(hq, *down, d_fused, masked_m, device_status=status)
+    nvfp4_gemm.m_grouped_bf16_dual_nvfp4_gemm_masked(h, *down, d_plain, masked_m, fold_swiglu=True, device_status=status)
+    torch.cuda.synchronize()
+    assert _C.read_status(status) == 0 and torch.equal(d_fused, d_plain)
+
+
 # ---------------------------------------------------------------- checkpoint loader
 def to_checkpoint(b, sfb, gw, e, n, k, divisor):
     from nvfp4_cutlass_b200.layout import unpack_sf_atoms
