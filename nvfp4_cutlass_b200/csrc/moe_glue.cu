@@ -213,31 +213,38 @@ dispatch_quantized_peer_kernel(const uint4* __restrict__ x, int64_t x_ld16, int6
 }
 
 // Scale rows (rows, 2, K/16) as the quantised dispatch delivers them -> the (rows/128, K/64, 2, 512) atoms the GEMM's
-// scale warps read (inside an atom the four bytes of row r at (r % 32) * 16 + (r / 32) * 4).  One thread per row and K
-// atom; masked layout: groups of max_m rows of which the first masked_m[g], rounded up to the 128-row tile, are
-// converted.  Runs on the owner, on local memory.
+// scale warps read (inside an atom the four bytes of row r at (r % 32) * 16 + (r / 32) * 4).  One block per 128-row block,
+// one warp per atom at a time: lane l gathers the words of rows l, l + 32, l + 64, l + 96 (a row's consecutive K atoms are
+// consecutive words, so neighbouring warps share the sectors they read) and the warp writes the atom as 512 contiguous
+// bytes per pass.  Masked layout: groups of max_m rows of which the first masked_m[g], rounded up to the 128-row tile,
+// are converted.  Runs on the owner, on local memory.  (One thread per row and atom, with its two scattered 4-byte stores,
+// took three times as long.)
 __global__ void __launch_bounds__(256)
 relayout_scales_kernel(const uint8_t* __restrict__ sf_rows, const int32_t* __restrict__ masked_m, uint32_t max_m, uint64_t rows,
                        uint32_t kdim, uint8_t* __restrict__ atoms)
 {
     ptx::grid_dependency_wait();
-    const uint32_t k64 = kdim / 64;
-    const uint64_t idx = static_cast<uint64_t>(blockIdx.x) * blockDim.x + threadIdx.x;
-    if (idx < rows * k64) {
-        const uint64_t row = idx / k64;
-        const uint32_t katom = static_cast<uint32_t>(idx % k64);
-        bool live = true;
-        if (masked_m != nullptr) {
-            const uint32_t count = min(static_cast<uint32_t>(max(0, __ldg(masked_m + row / max_m))), max_m);
-            live = row % max_m < (count + 127) / 128 * 128;
-        }
-        if (live) {
-            const uint8_t* src = sf_rows + row * (kdim / 8) + katom * 4;
-            const uint32_t w0 = *reinterpret_cast<const uint32_t*>(src), w1 = *reinterpret_cast<const uint32_t*>(src + kdim / 16);
-            const uint32_t r = static_cast<uint32_t>(row % 128);
-            uint8_t* dst = atoms + ((row / 128) * k64 + katom) * 1024 + (r % 32) * 16 + (r / 32) * 4;
-            *reinterpret_cast<uint32_t*>(dst) = w0;
-            *reinterpret_cast<uint32_t*>(dst + 512) = w1;
+    const uint32_t k64 = kdim / 64, lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+    const uint64_t row0 = static_cast<uint64_t>(blockIdx.x) * 128;
+    bool live = row0 < rows;
+    if (live && masked_m != nullptr) {
+        const uint32_t count = min(static_cast<uint32_t>(max(0, __ldg(masked_m + row0 / max_m))), max_m);
+        live = row0 % max_m < (count + 127) / 128 * 128;
+    }
+    if (live) {
+        const uint8_t* src = sf_rows + (row0 + lane) * (kdim / 8);
+        const uint64_t row_step = static_cast<uint64_t>(32) * (kdim / 8);
+        for (uint32_t katom = warp; katom < k64; katom += 8) {
+            uint32_t w0[4], w1[4];
+#pragma unroll
+            for (int j = 0; j < 4; ++j) {
+                const uint8_t* p = src + j * row_step + katom * 4;
+                w0[j] = *reinterpret_cast<const uint32_t*>(p);
+                w1[j] = *reinterpret_cast<const uint32_t*>(p + kdim / 16);
+            }
+            uint4* dst = reinterpret_cast<uint4*>(atoms + ((row0 / 128) * k64 + katom) * 1024) + lane;
+            dst[0] = make_uint4(w0[0], w0[1], w0[2], w0[3]);
+            dst[32] = make_uint4(w1[0], w1[1], w1[2], w1[3]);
         }
     }
     ptx::grid_launch_dependents();
@@ -679,9 +686,8 @@ int launch_dispatch_quantized_peer(const void* x, int64_t x_ld_bytes, int64_t to
 int launch_relayout_scales(const void* sf_rows, const int32_t* masked_m, int max_m, int64_t rows, int kdim, void* atoms, bool pdl,
                            cudaStream_t stream)
 {
-    const uint64_t threads = static_cast<uint64_t>(rows) * (kdim / 64);
-    if (threads == 0) return NVFP4_OK;
-    return host::launch_kernel(relayout_scales_kernel, dim3(static_cast<unsigned>((threads + 255) / 256)), dim3(256), 0, stream, pdl,
+    if (rows == 0) return NVFP4_OK;
+    return host::launch_kernel(relayout_scales_kernel, dim3(static_cast<unsigned>((rows + 127) / 128)), dim3(256), 0, stream, pdl,
                                static_cast<const uint8_t*>(sf_rows), masked_m, static_cast<uint32_t>(max_m > 0 ? max_m : 1),
                                static_cast<uint64_t>(rows), static_cast<uint32_t>(kdim), static_cast<uint8_t*>(atoms));
 }
