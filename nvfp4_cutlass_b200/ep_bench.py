@@ -89,9 +89,10 @@ def run(args, workload: str, world: int, rank: int, local: int) -> None:
     # room for 1.5 x the average rows a rank receives (a step that does not fit falls back by itself)
     use_peer = extra.get("ep_peer", 1) != 0
     # Micro-batches on streams of their own (the NVLink traffic of one part under the GEMMs of another, the parts' GEMM
-    # phases chained one after the other): measured on 4 GPUs 4.07 ms with four parts and 24 communication SMs against
-    # 4.44 ms for one batch; on 2 GPUs, where less crosses NVLink, 4.10 against 4.04 ms.  So four parts from 4 GPUs up.
-    micro = extra.get("ep_micro", 4 if world >= 4 else 1)
+    # phases chained one after the other).  Measured, ms per step as one batch / two / four parts: 2 GPUs 4.04 / 4.19 / 4.10,
+    # 4 GPUs 4.12 / 4.76 / 3.83, 8 GPUs 4.37 / 4.73 / 4.77 (with 16 local experts a quarter of the rows makes GEMMs too small
+    # to pay for what they hide).  So four parts on 4 GPUs, one batch otherwise.
+    micro = extra.get("ep_micro", 4 if world == 4 else 1)
     layer = ExpertParallelMoE(E_TOTAL, HIDDEN, INTER, up, down, alignment=128,
                               peer_rows_cap=expert_rows_cap(world, micro) if use_peer else 0, micro_batches=micro,
                               check_each_step=False, comm_sms=extra.get("ep_comm_sms", 24),
