@@ -587,7 +587,7 @@ def single_gpu_line(workload, dev, local, steps, warmup, extra, graph=False, cpu
     rec, d, step = gemm_record(case, dev, steps, warmup, fp4_peak, graph=graph, extra=extra, local=local)
     roofline = rec["roofline"]
     is_split = split_default(case, extra)
-    pair = case["kw"].get("m_alignment") == 256 or extra.get("tune_cluster") == 2 or case["M"] // case["E"] >= 1024
+    pair = case["kw"].get("m_alignment") == 256 or extra.get("tune_cluster") == 2 or case["M"] // case["E"] >= 2048
     if extra.get("tune_cluster") == 1:
         pair = False
     path = ("split: quantize_activation_kernel (Algorithm 1 once per element, into an L2-resident workspace) + " +

@@ -204,14 +204,14 @@ int nvfp4_quantize_weight_static(const void* w, int w_dtype, int E, int N, int K
 // pair), 1 the single-CTA kernel, 0 the library's choice.  A pair tile needs two row blocks of one expert, and an
 // expert's odd last block costs a whole pair tile.  The pair kernel's main loop is ~5 % faster, so it is chosen when that
 // waste is known to be nil (the caller states that every group is a multiple of 256 rows) or small (experts with
-// eight row blocks and more on average: measured 3 % faster than the single-CTA kernel on 128 experts of ~1000 rows,
-// timed alternately; with ~1.5 row blocks per expert it is 20-30 % slower).
+// 16 row blocks and more on average; with ~8 ragged row blocks per expert the two kernels measured within 3 % of each
+// other either way, with ~1.5 row blocks per expert the pair kernel is 20-30 % slower).
 static bool split_gemm_as_pair(const int32_t* tune, int64_t rows, int experts, bool groups_of_256)
 {
     const int knob = tune ? tune[8] : 0;
     if (knob == 2) return true;
     if (knob == 1) return false;
-    return groups_of_256 || (experts > 0 && rows / experts >= 1024);
+    return groups_of_256 || (experts > 0 && rows / experts >= 2048);
 }
 
 int nvfp4_grouped_gemm_contiguous(const void* a, int64_t lda_elems, const void* b, const void* sfb, const float* gw,
