@@ -222,3 +222,22 @@ def test_checkpoint_restatement_single_part_is_identity(oracle):
     assert torch.equal(ob, b) and torch.equal(osfb, sfb) and torch.equal(ogw, gw)
     with pytest.raises(RuntimeError):                      # the loader itself is GPU-only: no CPU path
         nvfp4_gemm.load_checkpoint_weights_nvfp4([part])
+
+
+def test_gate_up_interleave_puts_every_pair_in_one_64_column_group():
+    """The row order the fused up-projection epilogue relies on: in every run of 64 output columns the first 32 are gate
+    rows and the next 32 the up rows of the same 32 products, 128 products per 256-column tile, products in order."""
+    from nvfp4_gemm import _C
+    e, inter, k = 2, 256, 128
+    b = torch.arange(e * 2 * inter, dtype=torch.int64).repeat_interleave(k // 2).reshape(e * 2 * inter, k // 2)   # row id in every byte slot
+    sfb = torch.arange(2 * inter, dtype=torch.int64).repeat(e * (k // 64), 1)                                      # column id in every word
+    b2, sfb2 = _C.interleave_gate_up(b, sfb, e, inter)
+    rows = b2[:, 0].reshape(e, 2 * inter)
+    for ex in range(e):
+        r = rows[ex] - ex * 2 * inter                           # original row (0 .. I: gate, I .. 2 I: up) at every new position
+        groups = r.reshape(-1, 2, 32)                            # [64-column group][gate | up][32]
+        assert torch.equal(groups[:, 1], groups[:, 0] + inter)   # the up row of the same product sits 32 columns further
+        assert torch.equal(groups[:, 0].reshape(-1), torch.arange(inter))   # products in ascending order
+    assert torch.equal(sfb2[0], rows[0]) and torch.equal(sfb2[-1], rows[0])                                        # scale columns move with the rows
+    with pytest.raises(RuntimeError):
+        _C.interleave_gate_up(b, sfb, e, 192)                    # I must be a multiple of 128
